@@ -1,0 +1,307 @@
+"""Benchmark of the NVFP4 decode GEMV path: weight GB/s over a Llama-shaped layer stack.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl ours|reference]
+
+A "step" is one pass of the hot path over the whole layer stack (four weight-streaming GEMVs per
+layer) at decode batch B, replayed as one CUDA graph.  `value` = algorithmic weight bytes of all
+ranks / device time, inputs resident in HBM; `e2e` = the same metric with pinned host activations
+copied in and results copied out inside the timed region.  One JSON line is printed by rank 0.
+
+N = 1 runs the Llama-3-8B-shaped stack (32 layers, 3.9 GB of NVFP4 weights -- larger than L2, so
+every replay streams from HBM).  N > 1 runs the Llama-3-70B-shaped stack tensor-parallel
+(column-parallel QKV and gate/up, row-parallel o and down with an all-reduce of the partial
+hidden vector), total work fixed: strong scaling.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "nvfp4_decode_gemv_weight_gbps"
+UNIT = "GB/s"
+LLAMA_8B = dict(name="llama-3-8b", hidden=4096, q_heads=32, kv_heads=8, head_dim=128, inter=14336, layers=32)
+LLAMA_70B = dict(name="llama-3-70b", hidden=8192, q_heads=64, kv_heads=8, head_dim=128, inter=28672, layers=80)
+
+
+def measured_peak_gbs():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def build_stack(model, batch, rank, world, dev_index):
+    import torch
+
+    import crit_hub_b200 as qg
+    from crit_hub_b200.stack import LayerStack, llama_layer_shapes, synth_nvfp4
+
+    device = torch.device("cuda", dev_index)
+    handle = qg.QGemv(device=dev_index, use_pdl=True)
+    shapes = llama_layer_shapes(model["hidden"], model["q_heads"], model["kv_heads"], model["head_dim"],
+                                model["inter"])
+    weights, total_bytes = [], 0
+    for layer in range(model["layers"]):
+        for mi, (name, N, K) in enumerate(shapes):
+            codes, scales = synth_nvfp4(N, K, 1000 * layer + mi, device)
+            shard = None
+            if world > 1:
+                if name in ("qkv", "gate_up"):   # column-parallel: split output rows
+                    shard = qg.Shard(rank * N // world, (rank + 1) * N // world, 0, K)
+                else:                             # row-parallel: split K
+                    shard = qg.Shard(0, N, rank * K // world, (rank + 1) * K // world)
+            blob = qg.pack(qg.FMT_NVFP4, codes, scales, 1.0, shard=shard)
+            w = handle.load(blob)
+            weights.append(w)
+            total_bytes += w.weight_bytes
+    stack = LayerStack(handle, weights, batch, qg.OUT_BF16, device=dev_index)
+    g = torch.Generator()
+    g.manual_seed(7 + rank)
+    stack.set_inputs([torch.randn((batch, w.K), generator=g).to(torch.bfloat16) for w in weights])
+    return handle, stack, total_bytes
+
+
+def cpu_reference_sample(model, batch, steps, warmup):
+    """Times the CPU restatement (fp32-accumulate OpenMP GEMV) on one layer of the stack."""
+    import numpy as np
+
+    from crit_hub_b200.stack import llama_layer_shapes
+    from oracle import oracle as O
+
+    shapes = llama_layer_shapes(model["hidden"], model["q_heads"], model["kv_heads"], model["head_dim"],
+                                model["inter"])
+    mats = []
+    for mi, (name, N, K) in enumerate(shapes):
+        codes, scales, ts = O.make_nvfp4(N, K, seed=mi)
+        mats.append((codes, scales, ts, O.make_x(batch, K, seed=mi)))
+    layer_bytes = sum(m[1].shape[0] * m[1].shape[1] * 16 * 9 // 16 + 4 for m in mats)
+    threads = O.num_threads()
+    times = []
+    for it in range(warmup + steps):
+        t0 = time.perf_counter()
+        for codes, scales, ts, x in mats:
+            O.gemv_nvfp4_fast(codes, scales, ts, x)
+        if it >= warmup:
+            times.append(time.perf_counter() - t0)
+    sec = sum(times) / len(times)
+    return layer_bytes / sec / 1e9, sec, threads, layer_bytes
+
+
+def run_reference(args):
+    """The reference arm: the CPU restatement of the path on the host cores.  The registry holds
+    no implementation of this arithmetic to install or compile, so the port is what runs."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    model = LLAMA_8B if args.gpus == 1 else LLAMA_70B
+    steps, warmup = min(args.steps, 5), min(args.warmup, 2)
+    gbs, sec, threads, layer_bytes = cpu_reference_sample(model, args.batch, max(steps, 1), warmup)
+    sample = f"one {model['name']}-shaped layer (4 GEMVs, {layer_bytes} weight bytes) per step, {max(steps,1)} steps"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(gbs, 3), "unit": UNIT, "n_gpus": args.gpus,
+        "steps": max(steps, 1), "warmup": warmup, "ms_per_step": round(sec * 1e3, 3), "higher_is_better": True,
+        "scaling": "weak" if args.gpus == 1 else "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{model['name']} layer stack, NVFP4, batch {args.batch} (CPU port, bounded sample)"},
+        "cpu_baseline": {"value": round(gbs, 3), "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": round(gbs, 3), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=0, help="override the layer count (profiling small cases)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    warmup = max(args.warmup, 3)
+    model = dict(LLAMA_8B if world == 1 else LLAMA_70B)
+    if args.layers > 0:
+        model["layers"] = args.layers
+
+    handle, stack, rank_bytes = build_stack(model, args.batch, rank, world, local)
+    stack.capture()
+    st = handle.device_status(stack.stream.cuda_stream)
+    if st.code != 0:
+        raise SystemExit(f"kernel reported {st}")
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def all_reduce_partials():
+        # row-parallel o_proj / down outputs are partial sums: one all-reduce per block
+        if world > 1:
+            for i, c in enumerate(stack.calls):
+                if i % 4 in (1, 3):
+                    dist.all_reduce(stack.output(i))
+
+    def timed(fn, n):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        with torch.cuda.stream(stack.stream):
+            e0.record()
+        for _ in range(n):
+            fn()
+        with torch.cuda.stream(stack.stream):
+            e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    def dev_step():
+        stack.step()
+        if world > 1:
+            with torch.cuda.stream(stack.stream):
+                all_reduce_partials()
+
+    def host_step():
+        stack.step_host()
+
+    for _ in range(warmup):
+        dev_step()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms = timed(dev_step, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    for _ in range(2):
+        host_step()
+    ms_host = timed(host_step, args.steps)
+    st = handle.device_status(stack.stream.cuda_stream)
+    if st.code != 0:
+        raise SystemExit(f"kernel reported {st}")
+
+    total_bytes = rank_bytes
+    if world > 1:
+        t = torch.tensor([float(rank_bytes)], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t)
+        total_bytes = float(t.item())
+    if rank == 0:
+        peak, peak_kind = measured_peak_gbs()
+        gbs = total_bytes * args.steps / (ms * 1e-3) / 1e9
+        gbs_host = total_bytes * args.steps / (ms_host * 1e-3) / 1e9
+        launches = stack.launches_per_step * args.steps
+        per_launch_bytes = rank_bytes / stack.launches_per_step
+        per_launch_us = ms * 1e3 / launches
+        achieved = per_launch_bytes / (per_launch_us * 1e-6) / 1e9
+        line = {
+            "metric": METRIC, "value": round(gbs, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": warmup, "ms_per_step": round(ms / args.steps, 5), "higher_is_better": True,
+            "scaling": "weak" if world == 1 else "strong", "vs_baseline": None, "dtype": "f16xf16->f32",
+            "data": "synthetic",
+            "config": {
+                "workload": f"{model['name']}-shaped decode layer stack, NVFP4 weights, batch {args.batch}, "
+                            f"{model['layers']} layers x (qkv, o, gate_up, down)",
+                "batch": args.batch, "layers": model["layers"], "tp": world,
+                "weight_bytes_per_step": int(total_bytes),
+                "us_per_layer": round(ms * 1e3 / args.steps / model["layers"], 3),
+                "cache": "weights per step exceed L2 (126 MB); every replay streams from HBM",
+                "pct_of_8TBps": round(gbs / world / 8000.0 * 100, 2),
+            },
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
+                         "frac": round(achieved / peak, 4), "traffic": None, "peak_kind": peak_kind,
+                         "kernel": "gemv_kernel<NVFP4>", "bytes_per_launch": int(per_launch_bytes),
+                         "us_per_launch": round(per_launch_us, 3)},
+            "e2e": {"value": round(gbs_host, 2), "unit": UNIT, "h2d_bytes_per_step": stack.h2d_bytes,
+                    "d2h_bytes_per_step": stack.d2h_bytes, "ms_per_step": round(ms_host / args.steps, 5)},
+            "gpu_launches": launches,
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            cg, sec, threads, layer_bytes = cpu_reference_sample(LLAMA_8B, args.batch, 3, 1)
+            line["cpu_baseline"] = {
+                "value": round(cg, 3), "unit": UNIT, "cores": threads, "kind": "port",
+                "sample": f"one llama-3-8b-shaped layer ({layer_bytes} weight bytes), 3 timed passes, fp32-accumulate "
+                          f"OpenMP port of the host reference"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

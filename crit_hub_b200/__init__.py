@@ -1,0 +1,251 @@
+"""Python binding of the qgemv C ABI (include/qgemv.h) -- a ctypes layer, no torch types.
+
+Device buffers are passed as integer addresses (`tensor.data_ptr()` of a torch CUDA tensor, or
+any other allocator's pointer); streams as integer `cudaStream_t` handles.  Every compute call
+goes to the CUDA library; if it cannot be loaded the import of the binding fails loudly --
+there is no CPU path in this package.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import _build
+
+FMT_NVFP4 = 1
+FMT_FP8 = 2
+OUT_BF16 = 0
+OUT_F32 = 1
+MAX_BATCH = 8
+
+ERR_INVALID_ARG = -1
+ERR_BAD_BLOB = -2
+ERR_UNSUPPORTED_SHAPE = -3
+ERR_CUDA = -4
+ERR_NCCL = -5
+ERR_TIMEOUT = -6
+ERR_BOUNDS = -7
+ERR_NO_DEVICE = -8
+
+
+class QgemvError(RuntimeError):
+    def __init__(self, status: int, what: str):
+        super().__init__(f"{what}: {status_string(status)} ({status})")
+        self.status = status
+
+
+class _Config(C.Structure):
+    _fields_ = [("device", C.c_int32), ("use_pdl", C.c_int32), ("grid_override", C.c_int32),
+                ("debug", C.c_int32), ("spin_limit", C.c_int64)]
+
+
+class Shard(C.Structure):
+    """Rows [n0, n1) and columns [k0, k1) of the canonical matrix."""
+    _fields_ = [("n0", C.c_int64), ("n1", C.c_int64), ("k0", C.c_int64), ("k1", C.c_int64)]
+
+
+class _DevStatus(C.Structure):
+    _fields_ = [("code", C.c_int32), ("where", C.c_int32), ("block", C.c_int32), ("extra", C.c_int32)]
+
+
+@dataclass
+class DeviceStatus:
+    code: int
+    where: int
+    block: int
+    extra: int
+
+
+_LIB = None
+
+
+def lib_path() -> str:
+    return _build.LIB_PATH
+
+
+def _load() -> C.CDLL:
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    path = _build.LIB_PATH
+    if not os.path.exists(path):
+        path = _build.build()
+    L = C.CDLL(path)
+    vp, i32, i64, sz = C.c_void_p, C.c_int, C.c_int64, C.c_size_t
+    L.qgemv_status_string.restype = C.c_char_p
+    L.qgemv_status_string.argtypes = [i32]
+    L.qgemv_init.argtypes = [C.POINTER(_Config), C.POINTER(vp)]
+    L.qgemv_destroy.argtypes = [vp]
+    L.qgemv_sm_count.argtypes = [vp]
+    L.qgemv_packed_size.restype = sz
+    L.qgemv_packed_size.argtypes = [i32, i64, i64, C.POINTER(Shard)]
+    L.qgemv_pack_host.argtypes = [i32, vp, vp, C.c_float, i64, i64, C.POINTER(Shard), vp]
+    L.qgemv_unpack_host.argtypes = [vp, sz, vp, vp, C.POINTER(C.c_float)]
+    L.qgemv_blob_info.argtypes = [vp, sz, C.POINTER(i32), C.POINTER(i64), C.POINTER(i64)]
+    L.qgemv_blob_verify.argtypes = [vp, sz]
+    L.qgemv_load.argtypes = [vp, vp, sz, C.POINTER(vp)]
+    L.qgemv_load_stacked.argtypes = [vp, vp, sz, i32, C.POINTER(vp)]
+    L.qgemv_unload.argtypes = [vp, vp]
+    L.qgemv_weight_bytes.restype = i64
+    L.qgemv_weight_bytes.argtypes = [vp]
+    L.qgemv_gemv.argtypes = [vp, vp, vp, i32, vp, i32, vp]
+    L.qgemv_moe_gemv.argtypes = [vp, vp, vp, vp, i32, i32, i32, vp, i32, vp]
+    L.qgemv_moe_combine.argtypes = [vp, vp, i32, vp, i32, i32, i64, vp, i32, vp]
+    L.qgemv_dequant_f32.argtypes = [vp, vp, i32, vp, vp]
+    L.qgemv_last_device_status.argtypes = [vp, vp, C.POINTER(_DevStatus)]
+    _LIB = L
+    return L
+
+
+def status_string(status: int) -> str:
+    return _load().qgemv_status_string(int(status)).decode()
+
+
+def _check(status: int, what: str) -> None:
+    if status != 0:
+        raise QgemvError(status, what)
+
+
+def _np_ptr(a: np.ndarray) -> C.c_void_p:
+    if not a.flags["C_CONTIGUOUS"]:
+        raise ValueError("array must be C-contiguous")
+    return a.ctypes.data_as(C.c_void_p)
+
+
+# ---- host packer ---------------------------------------------------------------------------------
+def packed_size(fmt: int, N: int, K: int, shard: Shard | None = None) -> int:
+    return int(_load().qgemv_packed_size(fmt, N, K, C.byref(shard) if shard else None))
+
+
+def pack(fmt: int, codes: np.ndarray, scales: np.ndarray, tensor_scale: float = 1.0,
+         shard: Shard | None = None, out: np.ndarray | None = None) -> np.ndarray:
+    """Pack canonical codes / scales into the device layout; returns the blob as a u8 array.
+
+    NVFP4: codes u8 [N][K/2], scales u8 [N][K/16].  FP8: codes u8 [N][K], scales f32 [N].
+    """
+    if fmt == FMT_NVFP4:
+        N, K = scales.shape[0], scales.shape[1] * 16
+        if codes.dtype != np.uint8 or scales.dtype != np.uint8 or codes.shape != (N, K // 2):
+            raise ValueError("NVFP4 wants codes u8 [N][K/2] and scales u8 [N][K/16]")
+    elif fmt == FMT_FP8:
+        N, K = codes.shape
+        if codes.dtype != np.uint8 or scales.dtype != np.float32 or scales.shape != (N,):
+            raise ValueError("FP8 wants codes u8 [N][K] and scales f32 [N]")
+    else:
+        raise QgemvError(ERR_INVALID_ARG, "pack")
+    size = packed_size(fmt, N, K, shard)
+    if size == 0:
+        raise QgemvError(ERR_UNSUPPORTED_SHAPE, "pack")
+    blob = out if out is not None else np.empty(size, dtype=np.uint8)
+    if blob.size != size or blob.dtype != np.uint8:
+        raise ValueError("output blob has the wrong size")
+    _check(_load().qgemv_pack_host(fmt, _np_ptr(codes), _np_ptr(scales), C.c_float(tensor_scale), N, K,
+                                   C.byref(shard) if shard else None, _np_ptr(blob)), "pack")
+    return blob
+
+
+def blob_info(blob: np.ndarray):
+    fmt, N, K = C.c_int(), C.c_int64(), C.c_int64()
+    _check(_load().qgemv_blob_info(_np_ptr(blob), blob.size, C.byref(fmt), C.byref(N), C.byref(K)), "blob_info")
+    return fmt.value, N.value, K.value
+
+
+def blob_verify(blob: np.ndarray) -> int:
+    return int(_load().qgemv_blob_verify(_np_ptr(blob), blob.size))
+
+
+def unpack(blob: np.ndarray):
+    """Inverse of pack(): returns (codes, scales, tensor_scale) of the sub-matrix in the blob."""
+    fmt, N, K = blob_info(blob)
+    if fmt == FMT_NVFP4:
+        codes = np.empty((N, K // 2), dtype=np.uint8)
+        scales = np.empty((N, K // 16), dtype=np.uint8)
+    else:
+        codes = np.empty((N, K), dtype=np.uint8)
+        scales = np.empty((N,), dtype=np.float32)
+    ts = C.c_float()
+    _check(_load().qgemv_unpack_host(_np_ptr(blob), blob.size, _np_ptr(codes), _np_ptr(scales), C.byref(ts)),
+           "unpack")
+    return codes, scales, ts.value
+
+
+# ---- device side -----------------------------------------------------------------------------------
+class Weight:
+    """A packed weight resident on the device (one matrix, or a stack of experts)."""
+
+    def __init__(self, owner: "QGemv", ptr: int, fmt: int, N: int, K: int, n_stack: int):
+        self._owner, self._ptr = owner, ptr
+        self.fmt, self.N, self.K, self.n_stack = fmt, N, K, n_stack
+
+    @property
+    def weight_bytes(self) -> int:
+        """Algorithmic weight bytes of one matrix (codes + scales)."""
+        return int(_load().qgemv_weight_bytes(self._ptr))
+
+    def unload(self) -> None:
+        if self._ptr:
+            _check(_load().qgemv_unload(self._owner._ptr, self._ptr), "unload")
+            self._ptr = None
+
+
+class QGemv:
+    """One library handle on one device."""
+
+    def __init__(self, device: int = 0, use_pdl: bool = True, grid_override: int = 0, debug: bool = False,
+                 spin_limit: int = 0, inject_drop_copies: bool = False):
+        L = _load()
+        cfg = _Config(device, 1 if use_pdl else 0, grid_override,
+                      (1 if debug else 0) | (2 if inject_drop_copies else 0), spin_limit)
+        h = C.c_void_p()
+        _check(L.qgemv_init(C.byref(cfg), C.byref(h)), "init")
+        self._ptr = h.value
+        self.device = device
+
+    def close(self) -> None:
+        if self._ptr:
+            _load().qgemv_destroy(self._ptr)
+            self._ptr = None
+
+    @property
+    def sm_count(self) -> int:
+        return int(_load().qgemv_sm_count(self._ptr))
+
+    def load(self, blob: np.ndarray) -> Weight:
+        fmt, N, K = blob_info(blob)
+        w = C.c_void_p()
+        _check(_load().qgemv_load(self._ptr, _np_ptr(blob), blob.size, C.byref(w)), "load")
+        return Weight(self, w.value, fmt, N, K, 1)
+
+    def load_stacked(self, blobs: np.ndarray) -> Weight:
+        """blobs: u8 [E][bytes_each], every row a packed blob of the same shape and format."""
+        if blobs.ndim != 2:
+            raise ValueError("blobs must be [E][bytes_each]")
+        fmt, N, K = blob_info(blobs[0])
+        w = C.c_void_p()
+        _check(_load().qgemv_load_stacked(self._ptr, _np_ptr(blobs), blobs.shape[1], blobs.shape[0], C.byref(w)),
+               "load_stacked")
+        return Weight(self, w.value, fmt, N, K, blobs.shape[0])
+
+    def gemv(self, w: Weight, x_ptr: int, B: int, y_ptr: int, y_dtype: int = OUT_BF16, stream: int = 0) -> None:
+        _check(_load().qgemv_gemv(self._ptr, w._ptr, x_ptr, B, y_ptr, y_dtype, stream), "gemv")
+
+    def moe_gemv(self, experts: Weight, expert_ids_ptr: int, x_ptr: int, T: int, topk: int,
+                 per_slot_input: bool, out_ptr: int, out_dtype: int = OUT_F32, stream: int = 0) -> None:
+        _check(_load().qgemv_moe_gemv(self._ptr, experts._ptr, expert_ids_ptr, x_ptr, T, topk,
+                                      1 if per_slot_input else 0, out_ptr, out_dtype, stream), "moe_gemv")
+
+    def moe_combine(self, slot_out_ptr: int, slot_dtype: int, expert_w_ptr: int, T: int, topk: int, N: int,
+                    y_ptr: int, y_dtype: int = OUT_BF16, stream: int = 0) -> None:
+        _check(_load().qgemv_moe_combine(self._ptr, slot_out_ptr, slot_dtype, expert_w_ptr, T, topk, N, y_ptr,
+                                         y_dtype, stream), "moe_combine")
+
+    def dequant_f32(self, w: Weight, out_ptr: int, which: int = 0, stream: int = 0) -> None:
+        _check(_load().qgemv_dequant_f32(self._ptr, w._ptr, which, out_ptr, stream), "dequant_f32")
+
+    def device_status(self, stream: int = 0) -> DeviceStatus:
+        st = _DevStatus()
+        _check(_load().qgemv_last_device_status(self._ptr, stream, C.byref(st)), "device_status")
+        return DeviceStatus(st.code, st.where, st.block, st.extra)

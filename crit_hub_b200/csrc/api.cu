@@ -1,0 +1,342 @@
+// C ABI of the quantized GEMV library (include/qgemv.h): handle and weight lifetime, launches.
+// Host code only decides shapes and launch attributes; there is no CPU compute path.
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "../../include/qgemv.h"
+#include "aux_kernels.cuh"
+#include "gemv_kernel.cuh"
+#include "qgemv_layout.h"
+
+extern "C" int qgemv_blob_verify(const void* blob, size_t bytes);
+
+struct qgemv_handle {
+    qgemv_config cfg;
+    int sm_count;
+    int32_t* status_dev;
+};
+
+struct qgemv_weight {
+    int fmt;
+    int64_t N, K;
+    int64_t n_panels, units;
+    int n_stack;
+    uint64_t blob_bytes;     // bytes of one stacked blob (header + aux + payload)
+    uint64_t aux_bytes;
+    uint64_t payload_bytes;
+    uint8_t* dev_blob;       // n_stack blobs back to back
+    float* dev_tensor_scale; // [n_stack]
+    float* ws;               // partial slots
+    int32_t* counters;       // per virtual panel
+    int32_t* prob;           // MoE problem table (stacked weights only)
+    int max_prob;
+    float* host_tensor_scale; // [n_stack], host copy
+};
+
+namespace {
+
+#define QG_CUDA(expr)                                   \
+    do {                                                \
+        cudaError_t err__ = (expr);                     \
+        if (err__ != cudaSuccess) return QGEMV_ERR_CUDA; \
+    } while (0)
+
+constexpr int kMaxMoeSlots = 4096;
+
+int64_t default_spin(const qgemv_handle* h) {
+    return h->cfg.spin_limit > 0 ? h->cfg.spin_limit : (int64_t(1) << 26);
+}
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch(const qgemv_handle* h, void (*kernel)(KArgs...), dim3 grid, dim3 block,
+                   size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg;
+    std::memset(&cfg, 0, sizeof cfg);
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = h->cfg.use_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+int gemv_grid(const qgemv_handle* h) {
+    return h->cfg.grid_override > 0 ? h->cfg.grid_override : h->sm_count;
+}
+
+qg::GemvParams base_params(const qgemv_handle* h, const qgemv_weight* w) {
+    qg::GemvParams P;
+    std::memset(&P, 0, sizeof P);
+    P.payload = w->dev_blob + QG_HEADER_BYTES + w->aux_bytes;
+    P.stack_stride = w->blob_bytes;
+    P.chan_scale = reinterpret_cast<const float*>(w->dev_blob + QG_HEADER_BYTES);
+    P.chan_stride = w->blob_bytes;
+    P.tensor_scale = w->dev_tensor_scale;
+    P.ws = w->ws;
+    P.counters = w->counters;
+    P.status = h->status_dev;
+    P.spin_limit = default_spin(h);
+    P.N = int32_t(w->N);
+    P.K = int32_t(w->K);
+    P.n_panels = int32_t(w->n_panels);
+    P.units = int32_t(w->units);
+    P.debug = h->cfg.debug;
+    P.payload_bytes = w->payload_bytes;
+    return P;
+}
+
+int launch_gemv(const qgemv_handle* h, const qgemv_weight* w, const qg::GemvParams& P,
+                cudaStream_t stream) {
+    const dim3 grid(gemv_grid(h)), block(qg::kThreads);
+    cudaError_t err;
+    if (w->fmt == QGEMV_FMT_NVFP4) {
+        err = launch(h, qg::gemv_kernel<QGEMV_FMT_NVFP4>, grid, block,
+                     qg::Smem::total<QGEMV_FMT_NVFP4>(), stream, P);
+    } else {
+        err = launch(h, qg::gemv_kernel<QGEMV_FMT_FP8>, grid, block, qg::Smem::total<QGEMV_FMT_FP8>(),
+                     stream, P);
+    }
+    return err == cudaSuccess ? QGEMV_OK : QGEMV_ERR_CUDA;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* qgemv_status_string(int status) {
+    switch (status) {
+        case QGEMV_OK: return "ok";
+        case QGEMV_ERR_INVALID_ARG: return "invalid argument";
+        case QGEMV_ERR_BAD_BLOB: return "bad packed-weight blob";
+        case QGEMV_ERR_UNSUPPORTED_SHAPE: return "unsupported shape";
+        case QGEMV_ERR_CUDA: return "CUDA error";
+        case QGEMV_ERR_NCCL: return "NCCL error";
+        case QGEMV_ERR_TIMEOUT: return "device wait timed out";
+        case QGEMV_ERR_BOUNDS: return "device bounds check failed";
+        case QGEMV_ERR_NO_DEVICE: return "no CUDA device";
+        default: return "unknown status";
+    }
+}
+
+int qgemv_init(const qgemv_config* cfg, qgemv_handle** out) {
+    if (!cfg || !out) return QGEMV_ERR_INVALID_ARG;
+    *out = nullptr;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count <= 0) {
+        (void)cudaGetLastError();
+        return QGEMV_ERR_NO_DEVICE;
+    }
+    if (cfg->device < 0 || cfg->device >= count) return QGEMV_ERR_INVALID_ARG;
+    QG_CUDA(cudaSetDevice(cfg->device));
+    cudaDeviceProp prop;
+    QG_CUDA(cudaGetDeviceProperties(&prop, cfg->device));
+    if (prop.major != 10) return QGEMV_ERR_NO_DEVICE;  // built for sm_100a only
+    qgemv_handle* h = new (std::nothrow) qgemv_handle;
+    if (!h) return QGEMV_ERR_INVALID_ARG;
+    h->cfg = *cfg;
+    h->sm_count = prop.multiProcessorCount;
+    h->status_dev = nullptr;
+    if (cudaMalloc(&h->status_dev, 4 * sizeof(int32_t)) != cudaSuccess ||
+        cudaMemset(h->status_dev, 0, 4 * sizeof(int32_t)) != cudaSuccess) {
+        delete h;
+        return QGEMV_ERR_CUDA;
+    }
+    if (cudaFuncSetAttribute(qg::gemv_kernel<QGEMV_FMT_NVFP4>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             qg::Smem::total<QGEMV_FMT_NVFP4>()) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_kernel<QGEMV_FMT_FP8>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             qg::Smem::total<QGEMV_FMT_FP8>()) != cudaSuccess) {
+        cudaFree(h->status_dev);
+        delete h;
+        return QGEMV_ERR_CUDA;
+    }
+    *out = h;
+    return QGEMV_OK;
+}
+
+int qgemv_destroy(qgemv_handle* h) {
+    if (!h) return QGEMV_ERR_INVALID_ARG;
+    cudaSetDevice(h->cfg.device);
+    cudaFree(h->status_dev);
+    delete h;
+    return QGEMV_OK;
+}
+
+int qgemv_sm_count(const qgemv_handle* h) { return h ? h->sm_count : QGEMV_ERR_INVALID_ARG; }
+
+int qgemv_load_stacked(qgemv_handle* h, const void* host_blobs, size_t bytes_each, int n_stacked,
+                       qgemv_weight** out) {
+    if (!h || !host_blobs || !out || n_stacked <= 0) return QGEMV_ERR_INVALID_ARG;
+    *out = nullptr;
+    const uint8_t* src = static_cast<const uint8_t*>(host_blobs);
+    const qg_blob_header* h0 = reinterpret_cast<const qg_blob_header*>(src);
+    std::vector<float> ts(size_t(n_stacked), 1.0f);
+    for (int i = 0; i < n_stacked; ++i) {
+        const uint8_t* b = src + size_t(i) * bytes_each;
+        if (qgemv_blob_verify(b, bytes_each) != QGEMV_OK) return QGEMV_ERR_BAD_BLOB;
+        const qg_blob_header* hi = reinterpret_cast<const qg_blob_header*>(b);
+        if (hi->fmt != h0->fmt || hi->N != h0->N || hi->K != h0->K) return QGEMV_ERR_BAD_BLOB;
+        ts[size_t(i)] = hi->tensor_scale;
+    }
+    if (h0->N > INT32_MAX || h0->K > INT32_MAX || h0->n_panels * h0->units_per_panel > (int64_t(1) << 40))
+        return QGEMV_ERR_UNSUPPORTED_SHAPE;
+    QG_CUDA(cudaSetDevice(h->cfg.device));
+    qgemv_weight* w = new (std::nothrow) qgemv_weight;
+    if (!w) return QGEMV_ERR_INVALID_ARG;
+    std::memset(w, 0, sizeof *w);
+    w->fmt = int(h0->fmt);
+    w->N = h0->N;
+    w->K = h0->K;
+    w->n_panels = h0->n_panels;
+    w->units = h0->units_per_panel;
+    w->n_stack = n_stacked;
+    w->blob_bytes = bytes_each;
+    w->aux_bytes = h0->aux_bytes;
+    w->payload_bytes = h0->payload_bytes;
+    w->host_tensor_scale = new (std::nothrow) float[size_t(n_stacked)];
+    if (!w->host_tensor_scale) {
+        delete w;
+        return QGEMV_ERR_INVALID_ARG;
+    }
+    std::memcpy(w->host_tensor_scale, ts.data(), size_t(n_stacked) * 4);
+    w->max_prob = n_stacked > 1 ? n_stacked + kMaxMoeSlots / 8 : 1;
+    const size_t n_counters = size_t(w->max_prob) * size_t(w->n_panels);
+    const size_t ws_bytes = size_t(2) * size_t(gemv_grid(h) > h->sm_count ? gemv_grid(h) : h->sm_count) * 512;
+    bool ok = cudaMalloc(&w->dev_blob, size_t(n_stacked) * bytes_each) == cudaSuccess &&
+              cudaMalloc(&w->dev_tensor_scale, size_t(n_stacked) * 4) == cudaSuccess &&
+              cudaMalloc(&w->ws, ws_bytes) == cudaSuccess &&
+              cudaMalloc(&w->counters, n_counters * 4) == cudaSuccess;
+    if (ok && n_stacked > 1)
+        ok = cudaMalloc(&w->prob, (size_t(w->max_prob) * qg::kProbInts + 1) * 4) == cudaSuccess;
+    ok = ok && cudaMemcpy(w->dev_blob, src, size_t(n_stacked) * bytes_each, cudaMemcpyHostToDevice) == cudaSuccess &&
+         cudaMemcpy(w->dev_tensor_scale, ts.data(), size_t(n_stacked) * 4, cudaMemcpyHostToDevice) == cudaSuccess &&
+         cudaMemset(w->counters, 0, n_counters * 4) == cudaSuccess &&
+         cudaMemset(w->ws, 0, ws_bytes) == cudaSuccess;
+    if (ok && w->prob) ok = cudaMemset(w->prob, 0, (size_t(w->max_prob) * qg::kProbInts + 1) * 4) == cudaSuccess;
+    if (!ok) {
+        (void)cudaGetLastError();
+        qgemv_unload(h, w);
+        return QGEMV_ERR_CUDA;
+    }
+    *out = w;
+    return QGEMV_OK;
+}
+
+int qgemv_load(qgemv_handle* h, const void* host_blob, size_t bytes, qgemv_weight** out) {
+    return qgemv_load_stacked(h, host_blob, bytes, 1, out);
+}
+
+int qgemv_unload(qgemv_handle* h, qgemv_weight* w) {
+    if (!h || !w) return QGEMV_ERR_INVALID_ARG;
+    cudaSetDevice(h->cfg.device);
+    cudaFree(w->dev_blob);
+    cudaFree(w->dev_tensor_scale);
+    cudaFree(w->ws);
+    cudaFree(w->counters);
+    cudaFree(w->prob);
+    delete[] w->host_tensor_scale;
+    delete w;
+    return QGEMV_OK;
+}
+
+int64_t qgemv_weight_bytes(const qgemv_weight* w) {
+    if (!w) return QGEMV_ERR_INVALID_ARG;
+    if (w->fmt == QGEMV_FMT_NVFP4) return w->N * w->K / 2 + w->N * w->K / 16 + 4;
+    return w->N * w->K + 4 * w->N;
+}
+
+int qgemv_gemv(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, int B, void* y,
+               int y_dtype, void* stream) {
+    if (!h || !w || !x_bf16 || !y) return QGEMV_ERR_INVALID_ARG;
+    if (B < 1 || B > QGEMV_MAX_BATCH) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+    if (y_dtype != QGEMV_OUT_BF16 && y_dtype != QGEMV_OUT_F32) return QGEMV_ERR_INVALID_ARG;
+    if ((reinterpret_cast<uintptr_t>(x_bf16) & 15u) != 0) return QGEMV_ERR_INVALID_ARG;
+    qg::GemvParams P = base_params(h, w);
+    P.x = static_cast<const uint16_t*>(x_bf16);
+    P.y = y;
+    P.B = B;
+    P.y_dtype = y_dtype;
+    P.prob = nullptr;
+    return launch_gemv(h, w, P, static_cast<cudaStream_t>(stream));
+}
+
+int qgemv_moe_gemv(qgemv_handle* h, const qgemv_weight* experts, const int32_t* expert_ids,
+                   const void* x_bf16, int T, int topk, int per_slot_input, void* out,
+                   int out_dtype, void* stream) {
+    if (!h || !experts || !expert_ids || !x_bf16 || !out) return QGEMV_ERR_INVALID_ARG;
+    if (!experts->prob) return QGEMV_ERR_INVALID_ARG;  // not a stacked weight
+    if (T < 1 || topk < 1 || int64_t(T) * topk > kMaxMoeSlots) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+    if (out_dtype != QGEMV_OUT_BF16 && out_dtype != QGEMV_OUT_F32) return QGEMV_ERR_INVALID_ARG;
+    if ((reinterpret_cast<uintptr_t>(x_bf16) & 15u) != 0) return QGEMV_ERR_INVALID_ARG;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int threads = experts->n_stack < 1024 ? ((experts->n_stack + 31) / 32) * 32 : 1024;
+    cudaError_t err = launch(h, qg::moe_prep_kernel, dim3(1), dim3(threads),
+                             size_t(experts->n_stack) * 8, s, expert_ids, T, topk, experts->n_stack,
+                             per_slot_input, experts->max_prob, experts->prob, h->status_dev);
+    if (err != cudaSuccess) return QGEMV_ERR_CUDA;
+    qg::GemvParams P = base_params(h, experts);
+    P.x = static_cast<const uint16_t*>(x_bf16);
+    P.y = out;
+    P.B = 0;
+    P.y_dtype = out_dtype;
+    P.prob = experts->prob;
+    return launch_gemv(h, experts, P, s);
+}
+
+int qgemv_moe_combine(qgemv_handle* h, const void* slot_out, int slot_dtype, const float* expert_w,
+                      int T, int topk, int64_t N, void* y, int y_dtype, void* stream) {
+    if (!h || !slot_out || !expert_w || !y || T < 1 || topk < 1 || N < 1) return QGEMV_ERR_INVALID_ARG;
+    const int64_t total = int64_t(T) * N;
+    const int threads = 256;
+    const unsigned blocks = unsigned((total + threads - 1) / threads);
+    cudaError_t err = launch(h, qg::moe_combine_kernel, dim3(blocks), dim3(threads), 0,
+                             static_cast<cudaStream_t>(stream), slot_out, slot_dtype, expert_w, T,
+                             topk, N, y, y_dtype);
+    return err == cudaSuccess ? QGEMV_OK : QGEMV_ERR_CUDA;
+}
+
+int qgemv_dequant_f32(qgemv_handle* h, const qgemv_weight* w, int which, float* out_dev,
+                      void* stream) {
+    if (!h || !w || !out_dev || which < 0 || which >= w->n_stack) return QGEMV_ERR_INVALID_ARG;
+    const uint8_t* blob = w->dev_blob + uint64_t(which) * w->blob_bytes;
+    const uint8_t* payload = blob + QG_HEADER_BYTES + w->aux_bytes;
+    const float* chan = reinterpret_cast<const float*>(blob + QG_HEADER_BYTES);
+    const float ts = w->fmt == QGEMV_FMT_NVFP4 ? w->host_tensor_scale[which] : 1.0f;
+    const int64_t warps = w->n_panels * w->units;
+    const int threads = 128;
+    const unsigned blocks = unsigned((warps * 32 + threads - 1) / threads);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (w->fmt == QGEMV_FMT_NVFP4) {
+        qg::dequant_kernel<QGEMV_FMT_NVFP4><<<blocks, threads, 0, s>>>(payload, chan, ts, int32_t(w->N),
+                                                                      int32_t(w->K), int32_t(w->units), out_dev);
+    } else {
+        qg::dequant_kernel<QGEMV_FMT_FP8><<<blocks, threads, 0, s>>>(payload, chan, ts, int32_t(w->N),
+                                                                    int32_t(w->K), int32_t(w->units), out_dev);
+    }
+    return cudaGetLastError() == cudaSuccess ? QGEMV_OK : QGEMV_ERR_CUDA;
+}
+
+int qgemv_last_device_status(qgemv_handle* h, void* stream, qgemv_dev_status* out) {
+    if (!h || !out) return QGEMV_ERR_INVALID_ARG;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    QG_CUDA(cudaStreamSynchronize(s));
+    int32_t v[4];
+    QG_CUDA(cudaMemcpy(v, h->status_dev, sizeof v, cudaMemcpyDeviceToHost));
+    out->code = v[0];
+    out->where = v[1];
+    out->block = v[2];
+    out->extra = v[3];
+    if (v[0] != 0) QG_CUDA(cudaMemset(h->status_dev, 0, sizeof v));
+    return QGEMV_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,139 @@
+"""Layer-stack runner: a fixed list of projection GEMVs replayed as one CUDA graph.
+
+A decode step of a dense model is, for this library, a sequence of weight-streaming GEMVs
+(QKV, o_proj, gate/up, down per layer; "one CUDA graph per round",
+tools/fixtures/engines/crit-labs/mtp4-nvfp4-mma/card.yaml:75).  The runner owns the activation
+and output buffers of every call, captures the launches once, and replays the graph.  With
+programmatic dependent launch enabled on the handle each kernel's weight prefetch overlaps the
+tail of the one before it.
+
+torch is used for device memory, streams and graph capture only; every kernel is the
+library's own, reached through the C ABI.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from . import OUT_BF16, OUT_F32, QGemv, Weight
+
+
+@dataclass
+class _Call:
+    weight: Weight
+    x_off: int  # element offsets into the stack's activation / output arenas
+    y_off: int
+
+
+class LayerStack:
+    """Owns an activation arena [sum B*K] bf16 and an output arena [sum B*N]; one GEMV per weight."""
+
+    def __init__(self, handle: QGemv, weights: list[Weight], batch: int, out_dtype: int = OUT_BF16,
+                 device: int = 0):
+        self.handle, self.batch, self.out_dtype = handle, batch, out_dtype
+        self.device = torch.device("cuda", device)
+        self.calls: list[_Call] = []
+        x_total = y_total = 0
+        for w in weights:
+            self.calls.append(_Call(w, x_total, y_total))
+            x_total += ((batch * w.K + 7) // 8) * 8      # keep every row block 16-byte aligned
+            y_total += ((batch * w.N + 7) // 8) * 8
+        self.x_dev = torch.zeros(x_total, dtype=torch.bfloat16, device=self.device)
+        ydt = torch.bfloat16 if out_dtype == OUT_BF16 else torch.float32
+        self.y_dev = torch.zeros(y_total, dtype=ydt, device=self.device)
+        self.x_host = torch.zeros(x_total, dtype=torch.bfloat16).pin_memory()
+        self.y_host = torch.zeros(y_total, dtype=ydt).pin_memory()
+        self.stream = torch.cuda.Stream(device=self.device)
+        self.graph: torch.cuda.CUDAGraph | None = None
+        self.weight_bytes = sum(w.weight_bytes for w in weights)
+
+    # ---- buffers --------------------------------------------------------------------------
+    def set_inputs(self, xs: list[torch.Tensor]) -> None:
+        """xs[i]: bf16 [batch][K_i] activations of call i (host or device tensors)."""
+        for c, x in zip(self.calls, xs):
+            n = self.batch * c.weight.K
+            self.x_host[c.x_off:c.x_off + n].copy_(x.reshape(-1).to(torch.bfloat16).cpu())
+        self.x_dev.copy_(self.x_host, non_blocking=False)
+
+    def output(self, i: int, host: bool = False) -> torch.Tensor:
+        c = self.calls[i]
+        src = self.y_host if host else self.y_dev
+        return src[c.y_off:c.y_off + self.batch * c.weight.N].view(self.batch, c.weight.N)
+
+    @property
+    def h2d_bytes(self) -> int:
+        return self.x_host.numel() * self.x_host.element_size()
+
+    @property
+    def d2h_bytes(self) -> int:
+        return self.y_host.numel() * self.y_host.element_size()
+
+    # ---- launches -------------------------------------------------------------------------
+    def _enqueue(self, stream_handle: int) -> None:
+        xe, ye = self.x_dev.element_size(), self.y_dev.element_size()
+        xb, yb = self.x_dev.data_ptr(), self.y_dev.data_ptr()
+        for c in self.calls:
+            self.handle.gemv(c.weight, xb + c.x_off * xe, self.batch, yb + c.y_off * ye, self.out_dtype,
+                             stream_handle)
+
+    def capture(self) -> None:
+        """Run once eagerly (loads modules, warms caches), then capture the stack into a graph."""
+        with torch.cuda.stream(self.stream):
+            self._enqueue(self.stream.cuda_stream)
+        self.stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=self.stream):
+            self._enqueue(torch.cuda.current_stream().cuda_stream)
+        self.graph = g
+
+    def step(self) -> None:
+        """One pass over the stack, inputs and outputs resident on the device (asynchronous)."""
+        with torch.cuda.stream(self.stream):
+            if self.graph is not None:
+                self.graph.replay()
+            else:
+                self._enqueue(self.stream.cuda_stream)
+
+    def step_host(self) -> None:
+        """One pass with host buffers: pinned activations in, pinned results out, then a sync."""
+        with torch.cuda.stream(self.stream):
+            self.x_dev.copy_(self.x_host, non_blocking=True)
+            if self.graph is not None:
+                self.graph.replay()
+            else:
+                self._enqueue(self.stream.cuda_stream)
+            self.y_host.copy_(self.y_dev, non_blocking=True)
+        self.stream.synchronize()
+
+    @property
+    def launches_per_step(self) -> int:
+        return len(self.calls)
+
+
+def llama_layer_shapes(hidden: int, q_heads: int, kv_heads: int, head_dim: int, inter: int):
+    """(name, N, K) of the four projections of one decoder layer (fused QKV and gate/up)."""
+    return [("qkv", (q_heads + 2 * kv_heads) * head_dim, hidden), ("o", hidden, q_heads * head_dim),
+            ("gate_up", 2 * inter, hidden), ("down", hidden, inter)]
+
+
+def synth_nvfp4(N: int, K: int, seed: int, device: torch.device):
+    """Seeded synthetic NVFP4 matrix: codes uniform over the 16 E2M1 codes, E4M3 scales of
+    |N(0,1)| * 0.05 per 16-element block, tensor scale 1.0.  Returns host numpy (codes, scales)."""
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    codes = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=device, generator=g)
+    sc = torch.randn((N, K // 16), dtype=torch.float32, device=device, generator=g).abs_().mul_(0.05)
+    scales = sc.to(torch.float8_e4m3fn).view(torch.uint8)
+    return codes.cpu().numpy(), scales.cpu().numpy()
+
+
+def synth_fp8(N: int, K: int, seed: int, device: torch.device):
+    """Codes uniform over the 254 finite E4M3 codes; channel scales fp32 |N(0,1)| * 0.02."""
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    c = torch.randint(0, 254, (N, K), dtype=torch.int16, device=device, generator=g)
+    c = torch.where(c >= 127, c + 1, c).to(torch.uint8)
+    s = torch.randn((N,), dtype=torch.float32, device=device, generator=g).abs_().mul_(0.02)
+    return c.cpu().numpy(), s.cpu().numpy().astype(np.float32)

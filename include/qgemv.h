@@ -1,0 +1,167 @@
+/*
+ * qgemv.h -- C ABI of the B200 (sm_100a) weight-only quantized GEMV library.
+ *
+ * The crit-hub registry holds no operator interface for this path: its engine
+ * cards describe the projection kernels in prose and point at external
+ * sources.  Each entry point below therefore cites the card text whose
+ * described behaviour it provides.  Listed engines ship native code as an
+ * nvcc-built shared object "behind a small C ABI"
+ * (tools/fixtures/engines/crit-labs/mtp-adaptive-width/card.yaml:76,103); this
+ * header is that boundary for the quantized projections.
+ *
+ * Conventions
+ *   - Every call returns an int status (QGEMV_OK == 0, errors negative); nothing
+ *     throws, aborts or exits across the boundary.
+ *   - Plain pointers and sizes only.  `stream` is a cudaStream_t passed as void*.
+ *   - The caller owns host blobs and all activation / output device buffers; the
+ *     library owns handles, loaded weights and their device workspaces.
+ *   - One handle per device.  Calls on one handle are serialised by the caller.
+ *     gemv / moe / dequant calls are asynchronous on `stream`, allocate nothing,
+ *     never synchronise the host, and may be captured into a CUDA graph.
+ *   - There is no CPU fallback: compute entry points need a CUDA device.
+ */
+#ifndef QGEMV_H_
+#define QGEMV_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------------------------ */
+enum {
+    QGEMV_OK = 0,
+    QGEMV_ERR_INVALID_ARG = -1,
+    QGEMV_ERR_BAD_BLOB = -2,
+    QGEMV_ERR_UNSUPPORTED_SHAPE = -3,
+    QGEMV_ERR_CUDA = -4,
+    QGEMV_ERR_NCCL = -5,
+    QGEMV_ERR_TIMEOUT = -6,
+    QGEMV_ERR_BOUNDS = -7,
+    QGEMV_ERR_NO_DEVICE = -8
+};
+
+/* ---- weight formats ---------------------------------------------------------------------- */
+enum {
+    /* E2M1 codes, one E4M3 scale per 16 consecutive K elements, one fp32 per-tensor scale
+     * ("NVFP4 E2M1 with E4M3 group scales",
+     *  tools/fixtures/engines/crit-labs/mtp-adaptive-width/card.yaml:74). */
+    QGEMV_FMT_NVFP4 = 1,
+    /* E4M3 codes with one fp32 scale per output channel ("FP8 per-channel ... output head",
+     *  tools/fixtures/engines/crit-labs/mtp4-nvfp4-mma/card.yaml:74). */
+    QGEMV_FMT_FP8 = 2
+};
+
+enum { QGEMV_OUT_BF16 = 0, QGEMV_OUT_F32 = 1 };
+
+#define QGEMV_MAX_BATCH 8 /* activation rows per gemv call (decode batch / draft width) */
+
+typedef struct qgemv_handle qgemv_handle;
+typedef struct qgemv_weight qgemv_weight;
+
+typedef struct qgemv_config {
+    int32_t device;        /* CUDA device ordinal */
+    int32_t use_pdl;       /* 1: launch kernels with programmatic dependent launch so that a
+                              kernel's weight prefetch overlaps the previous kernel's tail */
+    int32_t grid_override; /* 0: one CTA per SM; >0: fixed CTA count (testing the K split) */
+    int32_t debug;         /* bit 0: kernels bounds-check every staged address and report through
+                              the device status word instead of touching memory;
+                              bit 1: fault injection for tests -- the weight copies are never
+                              issued, so the bounded waits must run out and report */
+    int64_t spin_limit;    /* poll budget of every in-kernel wait; 0 = default */
+} qgemv_config;
+
+/* Rows [n0,n1) and columns [k0,k1) of the canonical matrix: a tensor-parallel shard.
+ * Column-parallel shards split N, row-parallel shards split K (k0, k1 multiples of 16). */
+typedef struct qgemv_shard {
+    int64_t n0, n1, k0, k1;
+} qgemv_shard;
+
+/* Last error a kernel reported (bounded wait ran out, debug bounds check failed). */
+typedef struct qgemv_dev_status {
+    int32_t code;  /* 0 or a QGEMV_ERR_* value */
+    int32_t where; /* kernel-internal site id */
+    int32_t block; /* CTA that reported */
+    int32_t extra; /* site-specific detail (stage, item, index) */
+} qgemv_dev_status;
+
+/* ---- lifetime ---------------------------------------------------------------------------- */
+int qgemv_init(const qgemv_config* cfg, qgemv_handle** out);
+int qgemv_destroy(qgemv_handle* h);
+const char* qgemv_status_string(int status);
+/* Number of SMs of the handle's device (the CTA count the kernels are scheduled over). */
+int qgemv_sm_count(const qgemv_handle* h);
+
+/* ---- weight packer (pure host code, no GPU needed) ------------------------------------------
+ * Canonical inputs ("weights as stored", engines/crit-labs/mtp5-nvfp4-drafts/card.yaml:69,77):
+ *   NVFP4: codes u8 [N][K/2] (low nibble = even k), scales u8 [N][K/16] (E4M3), tensor_scale.
+ *   FP8:   codes u8 [N][K] (E4M3), scales = const float[N] per-output-channel scales;
+ *          tensor_scale is ignored.
+ * The blob interleaves codes and scales so that every lane of a warp issues one aligned
+ * 128-bit load per 32 codes and a bulk copy of whole K ranges of a 16-row panel is contiguous.
+ * K must be a multiple of 16; rows and K are zero-padded to the panel / unit size. */
+size_t qgemv_packed_size(int fmt, int64_t N, int64_t K, const qgemv_shard* shard /* nullable */);
+int qgemv_pack_host(int fmt, const void* codes, const void* scales, float tensor_scale, int64_t N,
+                    int64_t K, const qgemv_shard* shard /* nullable */, void* blob_out);
+/* Inverse of qgemv_pack_host for the (possibly sharded) sub-matrix held by the blob.
+ * scales_out is u8 [n][k/16] (NVFP4) or float [n] (FP8). */
+int qgemv_unpack_host(const void* blob, size_t bytes, void* codes_out, void* scales_out,
+                      float* tensor_scale_out);
+/* QGEMV_OK when the header is consistent and the checksum over scales and codes matches. */
+int qgemv_blob_verify(const void* blob, size_t bytes);
+/* Shape of the matrix a blob holds. Any out pointer may be NULL. */
+int qgemv_blob_info(const void* blob, size_t bytes, int* fmt, int64_t* N, int64_t* K);
+
+/* ---- load / unload ---------------------------------------------------------------------------
+ * Copies a packed blob to the device.  `n_stacked` > 1 loads that many equally shaped blobs laid
+ * back to back in host memory as one stacked weight (the experts of an MoE layer). */
+int qgemv_load(qgemv_handle* h, const void* host_blob, size_t bytes, qgemv_weight** out);
+int qgemv_load_stacked(qgemv_handle* h, const void* host_blobs, size_t bytes_each, int n_stacked,
+                       qgemv_weight** out);
+int qgemv_unload(qgemv_handle* h, qgemv_weight* w);
+/* Algorithmic weight bytes of one matrix: N*K*0.5625 + 4 (NVFP4) or N*K + 4*N (FP8). */
+int64_t qgemv_weight_bytes(const qgemv_weight* w);
+
+/* ---- decode GEMV, batch 1..8 -------------------------------------------------------------------
+ * y[b][n] = sum_k dequant(W)[n][k] * x[b][k], fp32 accumulation, output bf16 or fp32.
+ * x: device bf16 [B][K] row-major; y: device [B][N] row-major.
+ * The decode rows / decode-gemv of engines/crit-labs/mtp5-nvfp4-drafts/card.yaml:77 and the
+ * tensor-core NVFP4 GEMV of tools/fixtures/engines/crit-labs/mtp4-nvfp4-mma/card.yaml:76
+ * ("hardware E2M1 conversion into mma.m16n8k16 ... one instruction stream for every column
+ * count").  As there, row b of the result does not depend on B, and the split along K is fixed
+ * by the shape and the CTA count, never by timing ("column invariant with a deterministic split
+ * along K", tools/fixtures/engines/crit-labs/mtp-adaptive-width/card.yaml:77). */
+int qgemv_gemv(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, int B, void* y,
+               int y_dtype, void* stream);
+
+/* ---- MoE grouped GEMV ---------------------------------------------------------------------------
+ * One launch walks the router's top-k lists.  For every token t and slot j:
+ *   out[t*topk + j][:] = W[expert_ids[t][j]] . x[row][:],
+ *   row = t (per_slot_input == 0, gate/up stage) or t*topk + j (per_slot_input == 1, down stage).
+ * experts: a stacked weight from qgemv_load_stacked; expert_ids: device int32 [T][topk];
+ * x: device bf16; out: device [T*topk][N] bf16 or fp32.  T*topk <= 4096.
+ * No listed engine publishes an MoE kernel; the shape is the registry's `host_expert_gbs`
+ * probe slot (engines/crit-labs/mtp5-nvfp4-drafts/evidence/crit-eval.json:124). */
+int qgemv_moe_gemv(qgemv_handle* h, const qgemv_weight* experts, const int32_t* expert_ids,
+                   const void* x_bf16, int T, int topk, int per_slot_input, void* out,
+                   int out_dtype, void* stream);
+/* y[t][:] = sum_j expert_w[t][j] * slot_out[t*topk + j][:]  (fixed j order, fp32 accumulate). */
+int qgemv_moe_combine(qgemv_handle* h, const void* slot_out, int slot_dtype, const float* expert_w,
+                      int T, int topk, int64_t N, void* y, int y_dtype, void* stream);
+
+/* ---- parity hook ----------------------------------------------------------------------------
+ * Writes dequant(W) as fp32 [N][K] (index `which` of a stacked weight) using the same in-kernel
+ * conversion instructions as the GEMV; compared bit for bit with the host definition. */
+int qgemv_dequant_f32(qgemv_handle* h, const qgemv_weight* w, int which, float* out_dev,
+                      void* stream);
+
+/* ---- diagnostics ------------------------------------------------------------------------------ */
+/* Synchronises `stream`, reads and clears the device status word. */
+int qgemv_last_device_status(qgemv_handle* h, void* stream, qgemv_dev_status* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QGEMV_H_ */

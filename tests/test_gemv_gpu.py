@@ -1,0 +1,270 @@
+"""GPU parity tests proper: every call goes through the C ABI to the sm_100a kernels and is
+compared with the CPU oracle on the same seeded inputs."""
+import os
+
+import numpy as np
+import pytest
+
+import gpu_util as U
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+G = np.load(os.path.join(os.path.dirname(__file__), "golden", "qgemv_golden.npz"))
+
+TOL_F32 = 5e-5   # fp32 accumulation on the tensor cores vs the fp64 oracle (relative L2)
+TOL_BF16 = 2e-3  # the stated bound for bf16 outputs (relative L2)
+
+
+# ---- dequantisation: bit exact ----------------------------------------------------------------
+def test_dequant_nvfp4_exhaustive(qg, handle):
+    """All 16 codes x all 256 scale bytes, through the kernel's cvt + f16x2 multiply."""
+    N = 256
+    nib = np.tile(np.arange(16, dtype=np.uint8), (N, 1))
+    codes = (nib[:, 0::2] | (nib[:, 1::2] << 4)).astype(np.uint8)
+    scales = np.arange(256, dtype=np.uint8).reshape(N, 1)
+    for ts in (1.0, 0.3):
+        w = handle.load(qg.pack(qg.FMT_NVFP4, codes, scales, ts))
+        U.assert_bits_equal(U.dequant(qg, handle, w), O.dequant_nvfp4(codes, scales, ts))
+        w.unload()
+    U.assert_bits_equal(O.dequant_nvfp4(codes, scales, 1.0), G["nvfp4_prod"].T)
+
+
+@pytest.mark.parametrize("N,K", [(64, 256), (100, 448), (4096, 4096), (17, 1040)])
+def test_dequant_nvfp4_random(qg, handle, N, K):
+    codes, scales, ts = O.make_nvfp4(N, K, seed=N + K, ts=0.8125)
+    w = handle.load(qg.pack(qg.FMT_NVFP4, codes, scales, ts))
+    U.assert_bits_equal(U.dequant(qg, handle, w), O.dequant_nvfp4(codes, scales, ts))
+    w.unload()
+
+
+def test_dequant_fp8_exhaustive(qg, handle):
+    codes = np.tile(np.arange(256, dtype=np.uint8), (32, 1))
+    scales = (np.abs(np.random.default_rng(3).standard_normal(32)) * 0.02).astype(np.float32)
+    w = handle.load(qg.pack(qg.FMT_FP8, codes, scales))
+    U.assert_bits_equal(U.dequant(qg, handle, w), O.dequant_fp8(codes, scales))
+    w.unload()
+
+
+def test_dequant_golden_fixture(qg, handle):
+    w = handle.load(qg.pack(qg.FMT_NVFP4, G["codes"], G["scales"], float(G["ts"])))
+    U.assert_bits_equal(U.dequant(qg, handle, w), G["w"])
+    w.unload()
+    w = handle.load(qg.pack(qg.FMT_FP8, G["fp8_codes"], G["fp8_scales"]))
+    U.assert_bits_equal(U.dequant(qg, handle, w), G["fp8_w"])
+    w.unload()
+
+
+# ---- GEMV parity --------------------------------------------------------------------------------
+def test_golden_gemv(qg, handle):
+    w = handle.load(qg.pack(qg.FMT_NVFP4, G["codes"], G["scales"], float(G["ts"])))
+    y = U.run_gemv(qg, handle, w, G["x"])
+    U.status_ok(handle)
+    assert O.rel_l2(y, G["y"]) < TOL_F32
+    w.unload()
+    w = handle.load(qg.pack(qg.FMT_FP8, G["fp8_codes"], G["fp8_scales"]))
+    y = U.run_gemv(qg, handle, w, G["fp8_x"])
+    U.status_ok(handle)
+    assert O.rel_l2(y, G["fp8_y"]) < TOL_F32
+    w.unload()
+
+
+def test_config0(qg, handle):
+    """BASELINE configs[0]: 4096 x 4096 NVFP4, batch 1, bf16 output, tensor scale 1."""
+    codes, scales, ts = O.make_nvfp4(4096, 4096, seed=1)
+    x = O.make_x(1, 4096, seed=1)
+    ref = O.gemv_nvfp4_f64(codes, scales, ts, x)
+    w = handle.load(qg.pack(qg.FMT_NVFP4, codes, scales, ts))
+    y32 = U.run_gemv(qg, handle, w, x, out_f32=True)
+    y16 = U.run_gemv(qg, handle, w, x, out_f32=False)
+    U.status_ok(handle)
+    assert O.rel_l2(y32, ref) < TOL_F32
+    assert O.rel_l2(O.bf16_decode(y16), ref) < TOL_BF16
+    # the bf16 output is the fp32 result rounded once
+    assert np.array_equal(y16, O.bf16_encode(y32))
+    w.unload()
+
+
+@pytest.mark.parametrize("N,K", [(16, 64), (48, 1024), (100, 448), (33, 1104), (1000, 2112), (6144, 4096),
+                                 (4096, 14336), (272, 16)])
+@pytest.mark.parametrize("B", [1, 2, 3, 8])
+def test_gemv_nvfp4_shapes(qg, handle, N, K, B):
+    codes, scales, ts = O.make_nvfp4(N, K, seed=N * 3 + K, ts=1.25)
+    x = O.make_x(B, K, seed=B + K)
+    w = handle.load(qg.pack(qg.FMT_NVFP4, codes, scales, ts))
+    y = U.run_gemv(qg, handle, w, x)
+    U.status_ok(handle)
+    assert not np.isnan(y).any()
+    assert O.rel_l2(y, O.gemv_nvfp4_f64(codes, scales, ts, x)) < TOL_F32
+    w.unload()
+
+
+@pytest.mark.parametrize("N,K,B", [(64, 128, 1), (4096, 4096, 4), (500, 1344, 8), (28672, 4096, 1)])
+def test_gemv_fp8_shapes(qg, handle, N, K, B):
+    codes, scales = O.make_fp8(N, K, seed=N + K)
+    x = O.make_x(B, K, seed=B)
+    w = handle.load(qg.pack(qg.FMT_FP8, codes, scales))
+    y32 = U.run_gemv(qg, handle, w, x)
+    y16 = U.run_gemv(qg, handle, w, x, out_f32=False)
+    U.status_ok(handle)
+    ref = O.gemv_fp8_f64(codes, scales, x)
+    assert O.rel_l2(y32, ref) < TOL_F32
+    assert O.rel_l2(O.bf16_decode(y16), ref) < TOL_BF16
+    w.unload()
+
+
+def test_column_invariance_and_determinism(qg, handle):
+    """Row b of the result has the same bits whatever the batch is, and from run to run."""
+    N, K = 1024, 4096
+    codes, scales, ts = O.make_nvfp4(N, K, seed=11)
+    x = O.make_x(8, K, seed=12)
+    w = handle.load(qg.pack(qg.FMT_NVFP4, codes, scales, ts))
+    y8 = U.run_gemv(qg, handle, w, x)
+    assert np.array_equal(U.bits(y8), U.bits(U.run_gemv(qg, handle, w, x)))
+    for B in (1, 2, 5):
+        yb = U.run_gemv(qg, handle, w, x[:B])
+        assert np.array_equal(U.bits(yb), U.bits(y8[:B]))
+    # a single row placed anywhere gives the same bits
+    y1 = U.run_gemv(qg, handle, w, x[3:4])
+    assert np.array_equal(U.bits(y1[0]), U.bits(y8[3]))
+    U.status_ok(handle)
+    w.unload()
+
+
+@pytest.mark.parametrize("grid", [1, 3, 37, 148, 296])
+def test_k_split_across_ctas(qg, grid):
+    """Different CTA counts move the K split; every split sums its parts in a fixed order."""
+    h = qg.QGemv(device=0, grid_override=grid, debug=True)
+    N, K = 160, 4288
+    codes, scales, ts = O.make_nvfp4(N, K, seed=grid)
+    x = O.make_x(4, K, seed=grid + 1)
+    w = h.load(qg.pack(qg.FMT_NVFP4, codes, scales, ts))
+    ref = O.gemv_nvfp4_f64(codes, scales, ts, x)
+    y = U.run_gemv(qg, h, w, x, h=h)
+    U.status_ok(h)
+    assert O.rel_l2(y, ref) < TOL_F32
+    # the workspace counters are back to zero: a second launch gives the same bits
+    assert np.array_equal(U.bits(y), U.bits(U.run_gemv(qg, h, w, x, h=h)))
+    w.unload()
+    h.close()
+
+
+def test_activation_ranges(qg, handle):
+    """Huge, tiny, zero and mixed-magnitude activation rows: the per-row power-of-two scaling of
+    the f16 fragments is exact, so the tolerance does not move."""
+    N, K = 256, 2048
+    codes, scales, ts = O.make_nvfp4(N, K, seed=21)
+    rng = np.random.default_rng(22)
+    base = rng.standard_normal((6, K)).astype(np.float32)
+    base[0] *= 1e30
+    base[1] *= 1e-30
+    base[2] = 0.0
+    base[3, : K // 2] *= 1e4      # phases with very different maxima
+    base[3, K // 2:] *= 1e-4
+    base[4, 5] = 1e37
+    base[5] *= 70000.0            # beyond the f16 range before scaling
+    x = O.bf16_encode(base)
+    w = handle.load(qg.pack(qg.FMT_NVFP4, codes, scales, ts))
+    y = U.run_gemv(qg, handle, w, x)
+    U.status_ok(handle)
+    ref = O.gemv_nvfp4_f64(codes, scales, ts, x)
+    assert np.isfinite(y).all()
+    for b in range(6):
+        assert O.rel_l2(y[b], ref[b]) < TOL_F32, b
+    assert not y[2].any()
+    w.unload()
+
+
+def test_bad_arguments(qg, handle):
+    codes, scales, ts = O.make_nvfp4(16, 64, seed=1)
+    w = handle.load(qg.pack(qg.FMT_NVFP4, codes, scales, ts))
+    import torch
+    x = torch.zeros(9 * 64, dtype=torch.bfloat16, device="cuda")
+    y = torch.zeros(9 * 16, dtype=torch.float32, device="cuda")
+    for B in (0, 9, -1):
+        with pytest.raises(qg.QgemvError) as e:
+            handle.gemv(w, x.data_ptr(), B, y.data_ptr(), qg.OUT_F32)
+        assert e.value.status == qg.ERR_UNSUPPORTED_SHAPE
+    with pytest.raises(qg.QgemvError):
+        handle.gemv(w, 0, 1, y.data_ptr(), qg.OUT_F32)
+    with pytest.raises(qg.QgemvError):
+        handle.gemv(w, x.data_ptr() + 2, 1, y.data_ptr(), qg.OUT_F32)  # misaligned activations
+    bad = qg.pack(qg.FMT_NVFP4, codes, scales, ts)
+    bad[400] ^= 1
+    with pytest.raises(qg.QgemvError) as e:
+        handle.load(bad)
+    assert e.value.status == qg.ERR_BAD_BLOB
+    w.unload()
+
+
+def test_bounded_wait_reports_timeout(qg):
+    """A wait on a barrier that nothing completes ends the kernel with a status word instead of
+    hanging: the host-set injection makes the producer issue no copy, so the consumers' wait on
+    the first stage runs out of its (small) poll budget."""
+    h = qg.QGemv(device=0, spin_limit=2000, inject_drop_copies=True)
+    codes, scales, ts = O.make_nvfp4(512, 4096, seed=5)
+    w = h.load(qg.pack(qg.FMT_NVFP4, codes, scales, ts))
+    x = O.make_x(1, 4096, seed=5)
+    U.run_gemv(qg, h, w, x, h=h)
+    st = h.device_status()
+    assert st.code == qg.ERR_TIMEOUT and st.where in (1, 3, 4, 5)
+    assert h.device_status().code == 0  # reading clears it
+    w.unload()
+    h.close()
+    # the context is still usable
+    h2 = qg.QGemv(device=0)
+    w2 = h2.load(qg.pack(qg.FMT_NVFP4, codes, scales, ts))
+    y = U.run_gemv(qg, h2, w2, x, h=h2)
+    assert O.rel_l2(y, O.gemv_nvfp4_f64(codes, scales, ts, x)) < TOL_F32
+    w2.unload()
+    h2.close()
+
+
+# ---- MoE ------------------------------------------------------------------------------------------
+def _experts(E, N, K, seed):
+    cs = [O.make_nvfp4(N, K, seed + e, ts=1.0 + (e % 5) / 8) for e in range(E)]
+    return (np.stack([c[0] for c in cs]), np.stack([c[1] for c in cs]),
+            np.array([c[2] for c in cs], dtype=np.float32))
+
+
+def _route(T, E, topk, seed):
+    rng = np.random.default_rng(seed)
+    logits = rng.standard_normal((T, E)).astype(np.float32)
+    p = np.exp(logits - logits.max(axis=1, keepdims=True))
+    p /= p.sum(axis=1, keepdims=True)
+    ids = np.argsort(-p, axis=1, kind="stable")[:, :topk].astype(np.int32)
+    wts = np.take_along_axis(p, ids, axis=1)
+    wts = (wts / wts.sum(axis=1, keepdims=True)).astype(np.float32)
+    return ids, wts
+
+
+@pytest.mark.parametrize("T", [1, 8, 64])
+@pytest.mark.parametrize("per_slot", [False, True])
+def test_moe_gemv(qg, handle, T, per_slot):
+    import torch
+    E, topk = 32, 4
+    N, K = (96, 256) if not per_slot else (128, 192)
+    codes, scales, ts = _experts(E, N, K, seed=300)
+    blobs = np.stack([qg.pack(qg.FMT_NVFP4, codes[e], scales[e], float(ts[e])) for e in range(E)])
+    w = handle.load_stacked(blobs)
+    ids, wts = _route(T, E, topk, seed=T)
+    rows = T * topk if per_slot else T
+    x = O.make_x(rows, K, seed=T + 1)
+    ref = O.moe_gemv_nvfp4_f64(codes, scales, ts, ids, x, per_slot_input=per_slot)
+    xd = U.dev_u16(x)
+    idd = torch.from_numpy(ids).cuda()
+    out = torch.full((T * topk, N), float("nan"), dtype=torch.float32, device="cuda")
+    handle.moe_gemv(w, idd.data_ptr(), xd.data_ptr(), T, topk, per_slot, out.data_ptr(), qg.OUT_F32)
+    torch.cuda.synchronize()
+    U.status_ok(handle)
+    got = out.cpu().numpy()
+    assert not np.isnan(got).any()
+    assert O.rel_l2(got, ref) < TOL_F32
+    # weighted combine, fixed slot order
+    wd = torch.from_numpy(wts).cuda()
+    y = torch.empty((T, N), dtype=torch.float32, device="cuda")
+    handle.moe_combine(out.data_ptr(), qg.OUT_F32, wd.data_ptr(), T, topk, N, y.data_ptr(), qg.OUT_F32)
+    torch.cuda.synchronize()
+    yref = np.einsum("tj,tjn->tn", wts.astype(np.float64), ref.reshape(T, topk, N))
+    assert O.rel_l2(y.cpu().numpy(), yref) < TOL_F32
+    w.unload()
