@@ -195,10 +195,10 @@ class QGemv:
     """One library handle on one device."""
 
     def __init__(self, device: int = 0, use_pdl: bool = True, grid_override: int = 0, debug: bool = False,
-                 spin_limit: int = 0, inject_drop_copies: bool = False):
+                 spin_limit: int = 0, inject_drop_copies: bool = False, debug_bits: int = 0):
         L = _load()
         cfg = _Config(device, 1 if use_pdl else 0, grid_override,
-                      (1 if debug else 0) | (2 if inject_drop_copies else 0), spin_limit)
+                      (1 if debug else 0) | (2 if inject_drop_copies else 0) | debug_bits, spin_limit)
         h = C.c_void_p()
         _check(L.qgemv_init(C.byref(cfg), C.byref(h)), "init")
         self._ptr = h.value

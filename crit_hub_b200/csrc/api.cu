@@ -96,13 +96,16 @@ qg::GemvParams base_params(const qgemv_handle* h, const qgemv_weight* w) {
 int launch_gemv(const qgemv_handle* h, const qgemv_weight* w, const qg::GemvParams& P,
                 cudaStream_t stream) {
     const dim3 grid(gemv_grid(h)), block(qg::kThreads);
+    const bool res = qg::use_resident_path(P.prob == nullptr, P.B, w->units);
     cudaError_t err;
     if (w->fmt == QGEMV_FMT_NVFP4) {
-        err = launch(h, qg::gemv_kernel<QGEMV_FMT_NVFP4>, grid, block,
-                     qg::Smem::total<QGEMV_FMT_NVFP4>(), stream, P);
+        const size_t smem = qg::Smem::total<QGEMV_FMT_NVFP4>();
+        err = res ? launch(h, qg::gemv_kernel<QGEMV_FMT_NVFP4, true>, grid, block, smem, stream, P)
+                  : launch(h, qg::gemv_kernel<QGEMV_FMT_NVFP4, false>, grid, block, smem, stream, P);
     } else {
-        err = launch(h, qg::gemv_kernel<QGEMV_FMT_FP8>, grid, block, qg::Smem::total<QGEMV_FMT_FP8>(),
-                     stream, P);
+        const size_t smem = qg::Smem::total<QGEMV_FMT_FP8>();
+        err = res ? launch(h, qg::gemv_kernel<QGEMV_FMT_FP8, true>, grid, block, smem, stream, P)
+                  : launch(h, qg::gemv_kernel<QGEMV_FMT_FP8, false>, grid, block, smem, stream, P);
     }
     return err == cudaSuccess ? QGEMV_OK : QGEMV_ERR_CUDA;
 }
@@ -149,12 +152,11 @@ int qgemv_init(const qgemv_config* cfg, qgemv_handle** out) {
         delete h;
         return QGEMV_ERR_CUDA;
     }
-    if (cudaFuncSetAttribute(qg::gemv_kernel<QGEMV_FMT_NVFP4>,
-                             cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             qg::Smem::total<QGEMV_FMT_NVFP4>()) != cudaSuccess ||
-        cudaFuncSetAttribute(qg::gemv_kernel<QGEMV_FMT_FP8>,
-                             cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             qg::Smem::total<QGEMV_FMT_FP8>()) != cudaSuccess) {
+    const cudaFuncAttribute dyn = cudaFuncAttributeMaxDynamicSharedMemorySize;
+    if (cudaFuncSetAttribute(qg::gemv_kernel<QGEMV_FMT_NVFP4, true>, dyn, qg::Smem::total<QGEMV_FMT_NVFP4>()) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_kernel<QGEMV_FMT_NVFP4, false>, dyn, qg::Smem::total<QGEMV_FMT_NVFP4>()) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_kernel<QGEMV_FMT_FP8, true>, dyn, qg::Smem::total<QGEMV_FMT_FP8>()) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_kernel<QGEMV_FMT_FP8, false>, dyn, qg::Smem::total<QGEMV_FMT_FP8>()) != cudaSuccess) {
         cudaFree(h->status_dev);
         delete h;
         return QGEMV_ERR_CUDA;

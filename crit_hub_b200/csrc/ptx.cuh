@@ -24,13 +24,15 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                  : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+// One poll; the thread may be suspended by the hardware for up to `hint_ns` while the phase is
+// pending, so a waiting warp does not burn issue slots.
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uint32_t hint_ns = 20000u) {
     uint32_t ok;
     asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
         " selp.u32 %0, 1, 0, p;\n}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
         : "memory");
     return ok != 0;
 }
@@ -45,7 +47,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int64_t
     const uint64_t t0 = globaltimer_ns();
     for (int64_t i = 0; i < spin_limit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 1023) == 1023 && globaltimer_ns() - t0 > 2000000000ull) return false;
+        if ((i & 63) == 63 && globaltimer_ns() - t0 > 2000000000ull) return false;
     }
     return false;
 }
