@@ -10,6 +10,7 @@
 #include "../../include/qgemv.h"
 #include "aux_kernels.cuh"
 #include "gemv_kernel.cuh"
+#include "gemv_stream.cuh"
 #include "qgemv_layout.h"
 
 extern "C" int qgemv_blob_verify(const void* blob, size_t bytes);
@@ -96,8 +97,23 @@ qg::GemvParams base_params(const qgemv_handle* h, const qgemv_weight* w) {
 int launch_gemv(const qgemv_handle* h, const qgemv_weight* w, const qg::GemvParams& P,
                 cudaStream_t stream) {
     const dim3 grid(gemv_grid(h)), block(qg::kThreads);
-    const bool res = qg::use_resident_path(P.prob == nullptr, P.B, w->units);
     cudaError_t err;
+    if (qg::use_stream_path(P.prob == nullptr, P.B, w->units) && !(h->cfg.debug & 256)) {
+        const dim3 sblock(qg::kSThreads);
+        // whole panels per CTA (no cross-CTA fix-up) once every CTA gets at least one panel
+        const bool whole = w->n_panels >= int64_t(grid.x) && !(h->cfg.debug & 512);
+        if (w->fmt == QGEMV_FMT_NVFP4) {
+            const size_t smem = qg::SSmem::total<QGEMV_FMT_NVFP4>();
+            err = whole ? launch(h, qg::gemv_stream_wp_kernel<QGEMV_FMT_NVFP4>, grid, sblock, smem, stream, P)
+                        : launch(h, qg::gemv_stream_kernel<QGEMV_FMT_NVFP4>, grid, sblock, smem, stream, P);
+        } else {
+            const size_t smem = qg::SSmem::total<QGEMV_FMT_FP8>();
+            err = whole ? launch(h, qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8>, grid, sblock, smem, stream, P)
+                        : launch(h, qg::gemv_stream_kernel<QGEMV_FMT_FP8>, grid, sblock, smem, stream, P);
+        }
+        return err == cudaSuccess ? QGEMV_OK : QGEMV_ERR_CUDA;
+    }
+    const bool res = qg::use_resident_path(P.prob == nullptr, P.B, w->units);
     if (w->fmt == QGEMV_FMT_NVFP4) {
         const size_t smem = qg::Smem::total<QGEMV_FMT_NVFP4>();
         err = res ? launch(h, qg::gemv_kernel<QGEMV_FMT_NVFP4, true>, grid, block, smem, stream, P)
@@ -156,7 +172,11 @@ int qgemv_init(const qgemv_config* cfg, qgemv_handle** out) {
     if (cudaFuncSetAttribute(qg::gemv_kernel<QGEMV_FMT_NVFP4, true>, dyn, qg::Smem::total<QGEMV_FMT_NVFP4>()) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_kernel<QGEMV_FMT_NVFP4, false>, dyn, qg::Smem::total<QGEMV_FMT_NVFP4>()) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_kernel<QGEMV_FMT_FP8, true>, dyn, qg::Smem::total<QGEMV_FMT_FP8>()) != cudaSuccess ||
-        cudaFuncSetAttribute(qg::gemv_kernel<QGEMV_FMT_FP8, false>, dyn, qg::Smem::total<QGEMV_FMT_FP8>()) != cudaSuccess) {
+        cudaFuncSetAttribute(qg::gemv_kernel<QGEMV_FMT_FP8, false>, dyn, qg::Smem::total<QGEMV_FMT_FP8>()) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_stream_kernel<QGEMV_FMT_NVFP4>, dyn, qg::SSmem::total<QGEMV_FMT_NVFP4>()) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_stream_kernel<QGEMV_FMT_FP8>, dyn, qg::SSmem::total<QGEMV_FMT_FP8>()) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_NVFP4>, dyn, qg::SSmem::total<QGEMV_FMT_NVFP4>()) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8>, dyn, qg::SSmem::total<QGEMV_FMT_FP8>()) != cudaSuccess) {
         cudaFree(h->status_dev);
         delete h;
         return QGEMV_ERR_CUDA;

@@ -473,6 +473,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams P) {
     }
     __syncthreads();
     pdl_launch_dependents();
+    if (P.debug & 16) return;
 
     // problem count: 1 for a dense GEMV, read from the router prep output for MoE
     int nprob = 1;
@@ -493,6 +494,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams P) {
         constexpr int kWarps = kConsumerWarps + kConverterWarps;
         unsigned int* rowmax = reinterpret_cast<unsigned int*>(smem_raw + Smem::kXExp) + 64;  // 8 words
         int* rowexp = reinterpret_cast<int*>(smem_raw + Smem::kXExp);                           // 8 words
+        if (P.debug & 32) return;
         RowRegs r0, r1;
         const int n_pairs = n_phases * Bl;
         const int i0 = wid, i1 = wid + kWarps;
@@ -507,6 +509,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams P) {
                                         min(P.units, (f_1 + 1) * QG_PHASE_UNITS), lane);
             if (lane == 0) atomicMax(rowmax + b_1, m);
         }
+        if (P.debug & 32) return;
         named_bar_sync(2, 32 * kWarps);
         if (i0 < n_pairs)
             store_row(r0, row_exponent(rowmax[b_0]), f_0, f_0 * QG_PHASE_UNITS,
@@ -546,6 +549,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams P) {
                 ++rcnt;
                 v.x *= ts, v.y *= ts, v.z *= ts, v.w *= ts;
                 const int32_t panel = int32_t(it.vp + pl);  // dense: virtual panel == panel
+                if (P.debug & 64) continue;
                 if (!it.partial) {
                     store_panel<FMT>(P, v, lane, panel, P.B, nullptr, P.chan_scale);
                 } else {
