@@ -42,7 +42,7 @@ def measured_peak_gbs():
 class ClockSampler:
     """Samples SM clocks and throttle reasons through NVML (read-only) while the timed region runs."""
 
-    def __init__(self, index: int, period_s: float = 0.05):
+    def __init__(self, index: int, period_s: float = 0.005):
         self.index, self.period = index, period_s
         self.sm, self.reasons, self.max_mhz = [], set(), None
         self._stop = threading.Event()
@@ -278,7 +278,7 @@ def main():
         line = {
             "metric": METRIC, "value": round(gbs, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": warmup, "ms_per_step": round(ms / args.steps, 5), "higher_is_better": True,
-            "scaling": "weak" if world == 1 else "strong", "vs_baseline": None, "dtype": "f16xf16->f32",
+            "scaling": "weak" if world == 1 else "strong", "vs_baseline": None, "dtype": "f16 (fp32 accumulate)",
             "data": "synthetic",
             "config": {
                 "workload": f"{model['name']}-shaped decode layer stack, NVFP4 weights, batch {args.batch}, "
@@ -291,7 +291,7 @@ def main():
             },
             "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4), "traffic": None, "peak_kind": peak_kind,
-                         "kernel": "gemv_kernel<NVFP4>", "bytes_per_launch": int(per_launch_bytes),
+                         "kernel": "gemv_stream_wp_kernel<NVFP4>", "bytes_per_launch": int(per_launch_bytes),
                          "us_per_launch": round(per_launch_us, 3)},
             "e2e": {"value": round(gbs_host, 2), "unit": UNIT, "h2d_bytes_per_step": stack.h2d_bytes,
                     "d2h_bytes_per_step": stack.d2h_bytes, "ms_per_step": round(ms_host / args.steps, 5)},

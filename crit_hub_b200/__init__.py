@@ -77,6 +77,7 @@ def _load() -> C.CDLL:
     vp, i32, i64, sz = C.c_void_p, C.c_int, C.c_int64, C.c_size_t
     L.qgemv_status_string.restype = C.c_char_p
     L.qgemv_status_string.argtypes = [i32]
+    L.qgemv_last_cuda_error.restype = C.c_char_p
     L.qgemv_init.argtypes = [C.POINTER(_Config), C.POINTER(vp)]
     L.qgemv_destroy.argtypes = [vp]
     L.qgemv_sm_count.argtypes = [vp]
@@ -106,6 +107,8 @@ def status_string(status: int) -> str:
 
 def _check(status: int, what: str) -> None:
     if status != 0:
+        if status == ERR_CUDA:
+            what = f"{what} [{_load().qgemv_last_cuda_error().decode()}]"
         raise QgemvError(status, what)
 
 

@@ -40,10 +40,15 @@ struct qgemv_weight {
 
 namespace {
 
+thread_local cudaError_t g_last_cuda_error = cudaSuccess;
+
 #define QG_CUDA(expr)                                   \
     do {                                                \
         cudaError_t err__ = (expr);                     \
-        if (err__ != cudaSuccess) return QGEMV_ERR_CUDA; \
+        if (err__ != cudaSuccess) {                      \
+            g_last_cuda_error = err__;                   \
+            return QGEMV_ERR_CUDA;                       \
+        }                                                \
     } while (0)
 
 constexpr int kMaxMoeSlots = 4096;
@@ -66,7 +71,9 @@ cudaError_t launch(const qgemv_handle* h, void (*kernel)(KArgs...), dim3 grid, d
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = h->cfg.use_pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+    const cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+    if (err != cudaSuccess) g_last_cuda_error = err;
+    return err;
 }
 
 int gemv_grid(const qgemv_handle* h) {
@@ -104,12 +111,16 @@ int launch_gemv(const qgemv_handle* h, const qgemv_weight* w, const qg::GemvPara
         const bool whole = w->n_panels >= int64_t(grid.x) && !(h->cfg.debug & 512);
         if (w->fmt == QGEMV_FMT_NVFP4) {
             const size_t smem = qg::SSmem::total<QGEMV_FMT_NVFP4>();
-            err = whole ? launch(h, qg::gemv_stream_wp_kernel<QGEMV_FMT_NVFP4>, grid, sblock, smem, stream, P)
-                        : launch(h, qg::gemv_stream_kernel<QGEMV_FMT_NVFP4>, grid, sblock, smem, stream, P);
+            const bool full = w->units % qg::StreamTraits<QGEMV_FMT_NVFP4>::kChunkUnits == 0;
+            err = !whole ? launch(h, qg::gemv_stream_kernel<QGEMV_FMT_NVFP4>, grid, sblock, smem, stream, P)
+                  : full ? launch(h, qg::gemv_stream_wp_kernel<QGEMV_FMT_NVFP4, true, 1>, grid, sblock, smem, stream, P)
+                         : launch(h, qg::gemv_stream_wp_kernel<QGEMV_FMT_NVFP4, false, 1>, grid, sblock, smem, stream, P);
         } else {
             const size_t smem = qg::SSmem::total<QGEMV_FMT_FP8>();
-            err = whole ? launch(h, qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8>, grid, sblock, smem, stream, P)
-                        : launch(h, qg::gemv_stream_kernel<QGEMV_FMT_FP8>, grid, sblock, smem, stream, P);
+            const bool full = w->units % qg::StreamTraits<QGEMV_FMT_FP8>::kChunkUnits == 0;
+            err = !whole ? launch(h, qg::gemv_stream_kernel<QGEMV_FMT_FP8>, grid, sblock, smem, stream, P)
+                  : full ? launch(h, qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8, true, 1>, grid, sblock, smem, stream, P)
+                         : launch(h, qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8, false, 1>, grid, sblock, smem, stream, P);
         }
         return err == cudaSuccess ? QGEMV_OK : QGEMV_ERR_CUDA;
     }
@@ -129,6 +140,8 @@ int launch_gemv(const qgemv_handle* h, const qgemv_weight* w, const qg::GemvPara
 }  // namespace
 
 extern "C" {
+
+const char* qgemv_last_cuda_error(void) { return cudaGetErrorString(g_last_cuda_error); }
 
 const char* qgemv_status_string(int status) {
     switch (status) {
@@ -175,8 +188,10 @@ int qgemv_init(const qgemv_config* cfg, qgemv_handle** out) {
         cudaFuncSetAttribute(qg::gemv_kernel<QGEMV_FMT_FP8, false>, dyn, qg::Smem::total<QGEMV_FMT_FP8>()) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_stream_kernel<QGEMV_FMT_NVFP4>, dyn, qg::SSmem::total<QGEMV_FMT_NVFP4>()) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_stream_kernel<QGEMV_FMT_FP8>, dyn, qg::SSmem::total<QGEMV_FMT_FP8>()) != cudaSuccess ||
-        cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_NVFP4>, dyn, qg::SSmem::total<QGEMV_FMT_NVFP4>()) != cudaSuccess ||
-        cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8>, dyn, qg::SSmem::total<QGEMV_FMT_FP8>()) != cudaSuccess) {
+        cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_NVFP4, true, 1>, dyn, qg::SSmem::total<QGEMV_FMT_NVFP4>()) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_NVFP4, false, 1>, dyn, qg::SSmem::total<QGEMV_FMT_NVFP4>()) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8, true, 1>, dyn, qg::SSmem::total<QGEMV_FMT_FP8>()) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8, false, 1>, dyn, qg::SSmem::total<QGEMV_FMT_FP8>()) != cudaSuccess) {
         cudaFree(h->status_dev);
         delete h;
         return QGEMV_ERR_CUDA;

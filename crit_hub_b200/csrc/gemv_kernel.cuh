@@ -23,6 +23,7 @@
 // on timing; partial panels are written to per-CTA workspace slots and summed in a fixed order
 // by whichever CTA arrives last.
 #pragma once
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 

@@ -46,13 +46,15 @@ struct SSmem {
     static constexpr int kRowMax = 544;       // 8 words
     static constexpr int kRowExp = 576;       // 8 words
     static constexpr int kAbort = 608;
+    static constexpr int kZero = 640;         // 16 zero bytes
     static constexpr int kXBuf = 1024;
     static constexpr int kRed = kXBuf + kSXBufBytes;                   // kSRedSlots * kSWarps * 512
     static constexpr int kRing0 = kRed + kSRedSlots * kSWarps * 512;
     template <int FMT>
     static constexpr int total() {
-        return kRing0 + kSWarps * StreamTraits<FMT>::kRing * StreamTraits<FMT>::kChunkUnits *
-                            FmtTraits<FMT>::kUnitBytes;
+        constexpr int split_ring = StreamTraits<FMT>::kRing;
+        constexpr int ring_slots = split_ring > 4 ? split_ring : 4;  // whole-panel kernel: 4 chunk slots
+        return kRing0 + kSWarps * ring_slots * StreamTraits<FMT>::kChunkUnits * FmtTraits<FMT>::kUnitBytes;
     }
 };
 
@@ -207,7 +209,7 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_kernel(const GemvPar
         uint32_t rcnt = 0;
         for (int p = p_first; p <= p_last; ++p, ++rcnt) {
             const int rs = rcnt % kSRedSlots;
-            if (!mbar_wait(sbase + SSmem::kBarRedFull + 8 * rs, (rcnt / kSRedSlots) & 1, P.spin_limit)) {
+            if (!mbar_wait(sbase + SSmem::kBarRedFull + 8 * rs, (rcnt / kSRedSlots) & 1, P.spin_limit, 200u)) {
                 if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 6, int(rcnt));
                 *abort_flag = 1;
                 return;
@@ -306,13 +308,11 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_kernel(const GemvPar
             }
             ++consumed;
             cons_cur.advance();
-            // the slot is free again: order this warp's reads before the next asynchronous write
+            // the slot is free again: all loads of this chunk have delivered their data (see the
+            // whole-panel kernel), so the next asynchronous write needs no cross-proxy fence
             __syncwarp();
             if (issue_cur.valid()) {
-                if (lane == 0) {
-                    fence_proxy_async_smem();
-                    issue_one();
-                }
+                if (lane == 0) issue_one();
                 ++issued;
                 issue_cur.advance();
             }
@@ -329,8 +329,7 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_kernel(const GemvPar
         }
         sts128f(red + rs * kSWarps * 512, (cA[0] + cB[0]) * fs0, (cA[1] + cB[1]) * fs1, (cA[2] + cB[2]) * fs0,
                 (cA[3] + cB[3]) * fs1);
-        __threadfence_block();
-        __syncwarp();
+        __syncwarp();  // orders the lanes' stores before lane 0's releasing arrive
         if (lane == 0) mbar_arrive(sbase + SSmem::kBarRedFull + 8 * rs);
     }
     // never leave with copies in flight: wait (bounded) for every copy this warp still owns
@@ -341,15 +340,18 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_kernel(const GemvPar
 }
 
 // Whole-panel variant: every CTA owns whole panels (no panel is split between CTAs, so there is
-// no cross-CTA fix-up), every warp has the same number of chunks in every panel, and the issue
-// cursor is a pair of counters.  Chosen by the host when there is at least one panel per CTA.
-template <int FMT>
+// no cross-CTA fix-up).  The K extent is cut into chunks of kChunkUnits units and warp w owns
+// chunks [w*NC/16, (w+1)*NC/16) of every panel, so every warp sees the same chunk sequence in every
+// panel and the loop bookkeeping is a handful of running counters.  Chosen by the host when there
+// is at least one panel per CTA.  FULL: units is a multiple of kChunkUnits (no ragged last chunk).
+template <int FMT, bool FULL, int PPI>
 __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_wp_kernel(const GemvParams P) {
     using ST = StreamTraits<FMT>;
     constexpr int kUnitBytes = FmtTraits<FMT>::kUnitBytes;
     constexpr int CH = ST::kChunkUnits;
     constexpr int kRing = ST::kRing;
     constexpr int kSlotBytes = CH * kUnitBytes;
+    constexpr int kWpRing = 4 / PPI;  // ring slots per warp; a slot holds one chunk of PPI panels
 
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const uint32_t sbase = smem_u32(smem_raw);
@@ -358,13 +360,15 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_wp_kernel(const Gemv
     const int units = P.units;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < kSWarps * kRing; ++i) mbar_init(sbase + SSmem::kBarFull + 8 * i, 1);
+        for (int i = 0; i < kSWarps * kWpRing; ++i) mbar_init(sbase + SSmem::kBarFull + 8 * i, 1);
         for (int i = 0; i < kSRedSlots; ++i) {
             mbar_init(sbase + SSmem::kBarRedFull + 8 * i, kSWarps);
             mbar_init(sbase + SSmem::kBarRedEmpty + 8 * i, 1);
         }
         for (int b = 0; b < 8; ++b) reinterpret_cast<volatile unsigned int*>(smem_raw + SSmem::kRowMax)[b] = 0u;
         *reinterpret_cast<volatile int*>(smem_raw + SSmem::kAbort) = 0;
+        // 16 zero bytes: the activation "fragment" of lanes whose batch column does not exist
+        for (int i = 0; i < 4; ++i) reinterpret_cast<volatile unsigned int*>(smem_raw + SSmem::kZero)[i] = 0u;
         mbar_fence_init();
     }
     __syncthreads();
@@ -383,7 +387,7 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_wp_kernel(const Gemv
         const uint32_t red = sbase + SSmem::kRed + lane * 16;
         uint32_t rs = 0, rpar = 0;
         for (int p = p0; p < p1; ++p) {
-            if (!mbar_wait(sbase + SSmem::kBarRedFull + 8 * rs, rpar, P.spin_limit)) {
+            if (!mbar_wait(sbase + SSmem::kBarRedFull + 8 * rs, rpar, P.spin_limit, 200u)) {
                 if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 6, p);
                 *abort_flag = 1;
                 return;
@@ -407,41 +411,53 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_wp_kernel(const Gemv
     }
 
     // ================= consumer warps =================
+    // Each iteration handles one chunk of this warp's K slice for TWO consecutive panels: the
+    // activation fragments and the loop bookkeeping are shared by both, and four independent
+    // accumulator chains are in flight.
     const int w = warp;
     const int g = lane >> 2, t = lane & 3;
-    const int S = (units + kSWarps - 1) / kSWarps;
-    const int s_lo = min(units, w * S), s_hi = min(units, (w + 1) * S);
-    const int nu = s_hi - s_lo;
-    const int cpp = (nu + CH - 1) / CH;  // chunks per panel of this warp (same for every panel)
-    const uint32_t ring = sbase + SSmem::kRing0 + w * (kRing * kSlotBytes);
-    const uint32_t bars = sbase + SSmem::kBarFull + 8 * (w * kRing);
+    const int n_chunks = (units + CH - 1) / CH;
+    const int ck_lo = (w * n_chunks) / kSWarps, ck_hi = ((w + 1) * n_chunks) / kSWarps;
+    const int nck = ck_hi - ck_lo;  // chunks of this warp in every panel
+    constexpr int kPairBytes = PPI * kSlotBytes;
+    const uint32_t ring = sbase + SSmem::kRing0 + w * (kWpRing * kPairBytes);
+    const uint32_t bars = sbase + SSmem::kBarFull + 8 * (w * kWpRing);
     const uint64_t pol = policy_evict_first();
     const bool drop = (P.debug & 2) != 0;  // host-set fault injection: never issue a copy
 
-    // issue cursor: (panel ip, chunk ic, ring slot islot); lane 0 issues
-    int ip = p0, ic = 0, islot = 0, in_flight = 0;
-    const uint64_t panel_bytes = uint64_t(units) * kUnitBytes;
+    // issue cursor: running byte offset of panel a's chunk, chunk counter, ring slot
+    const uint32_t panel_bytes = uint32_t(units) * kUnitBytes;  // a packed matrix is below 4 GB
+    const int n_pairs = (p1 - p0 + PPI - 1) / PPI;
+    uint32_t ioff = uint32_t(p0) * panel_bytes + uint32_t(ck_lo) * kSlotBytes;
+    const uint32_t ioff_next_pair = uint32_t(PPI) * panel_bytes - uint32_t(nck) * kSlotBytes;
+    int ic = 0, islot = 0, ipair = 0;
+    int to_issue = nck * n_pairs, in_flight = 0;
     auto issue_one = [&]() {
-        const int c0 = s_lo + ic * CH;
-        const uint32_t bytes = uint32_t(min(CH, s_hi - c0)) * kUnitBytes;
-        const uint64_t off = uint64_t(ip) * panel_bytes + uint64_t(c0) * kUnitBytes;
-        if (lane == 0) {
-            if ((P.debug & 1) && off + bytes > P.payload_bytes) {
-                report(P.status, QGEMV_ERR_BOUNDS, 2, ip);
-            } else if (!drop) {
-                mbar_arrive_expect_tx(bars + 8 * islot, bytes);
-                bulk_g2s(ring + islot * kSlotBytes, P.payload + off, bytes, bars + 8 * islot, pol);
+        if (lane == 0 && !drop) {
+            uint32_t bytes = kSlotBytes;
+            if (!FULL) bytes = uint32_t(min(CH, units - (ck_lo + ic) * CH)) * kUnitBytes;
+            const bool two = PPI == 2 && p0 + 2 * ipair + 1 < p1;
+            if ((P.debug & 1) && uint64_t(ioff) + (two ? panel_bytes : 0u) + bytes > P.payload_bytes) {
+                report(P.status, QGEMV_ERR_BOUNDS, 2, ipair);
+            } else {
+                const uint32_t bar = bars + 8 * islot;
+                const uint32_t dst = ring + islot * kPairBytes;
+                mbar_arrive_expect_tx(bar, two ? 2u * bytes : bytes);
+                bulk_g2s(dst, P.payload + ioff, bytes, bar, pol);
+                if (two) bulk_g2s(dst + kSlotBytes, P.payload + ioff + panel_bytes, bytes, bar, pol);
             }
         }
-        if (++ic == cpp) {
+        ioff += kSlotBytes;
+        if (++ic == nck) {
             ic = 0;
-            ++ip;
+            ++ipair;
+            ioff += ioff_next_pair;
         }
-        if (++islot == kRing) islot = 0;
+        if (++islot == kWpRing) islot = 0;
+        --to_issue;
         ++in_flight;
     };
-    if (cpp > 0)
-        for (int i = 0; i < kRing && ip < p1; ++i) issue_one();
+    for (int i = 0; i < kWpRing && to_issue > 0; ++i) issue_one();
 
     // weights never depend on the preceding kernel; activations do
     pdl_wait();
@@ -449,98 +465,109 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_wp_kernel(const Gemv
     const int* rowexp = reinterpret_cast<const int*>(smem_raw + SSmem::kRowExp);
     const float fs0 = pow2i(rowexp[2 * t]), fs1 = pow2i(rowexp[2 * t + 1]);
 
+    // Activation fragments of (unit u, block pair pp): 16 bytes at xbase + u*xunit + pp*xpair.  Lanes
+    // whose batch column does not exist read sixteen zero bytes with zero strides: no branches.
     const bool xlane = g < Bl;
-    const uint32_t xpair = uint32_t(Bl) * 64u;
-    const uint32_t xlane_base = sbase + SSmem::kXBuf + g * 64 + t * 16;
+    const uint32_t xpair = xlane ? uint32_t(Bl) * 64u : 0u;
+    const uint32_t xunit = 2u * xpair;
+    const uint32_t xbase = xlane ? sbase + SSmem::kXBuf + g * 64 + t * 16 : sbase + SSmem::kZero;
     // one chunk per panel: the activation fragments of the slice never change -- keep them in registers
-    const bool bf_fixed = (cpp == 1);
+    const bool bf_fixed = (nck == 1) && FULL;
     uint32_t bfr[CH][8];
 #pragma unroll
     for (int j = 0; j < CH; ++j) {
-        if (bf_fixed && j < nu) {
-            load_bfrag(bfr[j], xlane, xlane_base + uint32_t(s_lo + j) * 2u * xpair, xpair);
-        } else {
-#pragma unroll
-            for (int z = 0; z < 8; ++z) bfr[j][z] = 0u;
-        }
+        const uint32_t xa = xbase + uint32_t(ck_lo * CH + j) * xunit;
+        const uint4 x0 = lds128(bf_fixed ? xa : sbase + SSmem::kZero);
+        const uint4 x1 = lds128(bf_fixed ? xa + xpair : sbase + SSmem::kZero);
+        bfr[j][0] = x0.x, bfr[j][1] = x0.y, bfr[j][2] = x0.z, bfr[j][3] = x0.w;
+        bfr[j][4] = x1.x, bfr[j][5] = x1.y, bfr[j][6] = x1.z, bfr[j][7] = x1.w;
     }
     const uint32_t red = sbase + SSmem::kRed + w * 512 + lane * 16;
     uint32_t rs = 0, ruse = 0;
     int cslot = 0;
     uint32_t cpar = 0;
-
-    for (int p = p0; p < p1; ++p) {
-        float cA[4] = {0.f, 0.f, 0.f, 0.f}, cB[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int c = 0; c < cpp; ++c) {
-            if (!mbar_wait(bars + 8 * cslot, cpar, P.spin_limit)) {
-                if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 5, p);
-                *abort_flag = 1;
-                goto drain;
-            }
-            {
-                const int c0 = s_lo + c * CH;
-                const int n = min(CH, s_hi - c0);
-                const uint32_t st = ring + cslot * kSlotBytes;
-                if (bf_fixed) {
-#pragma unroll
-                    for (int j = 0; j < CH; j += 2) {
-                        if (j + 1 < n) {
-                            consume_two<FMT>(cA, cB, st + j * kUnitBytes, st + (j + 1) * kUnitBytes, lane, bfr[j],
-                                             bfr[j + 1]);
-                        } else if (j < n) {
-                            consume_unit<FMT>(cA, st + j * kUnitBytes, lane, bfr[j]);
-                        }
-                    }
-                } else {
-                    const uint32_t xu = xlane_base + uint32_t(c0) * 2u * xpair;
-                    uint32_t bfA[8], bfB[8];
-#pragma unroll
-                    for (int j = 0; j < CH; j += 2) {
-                        if (j + 1 < n) {
-                            load_bfrag(bfA, xlane, xu + j * 2 * xpair, xpair);
-                            load_bfrag(bfB, xlane, xu + (j + 1) * 2 * xpair, xpair);
-                            consume_two<FMT>(cA, cB, st + j * kUnitBytes, st + (j + 1) * kUnitBytes, lane, bfA, bfB);
-                        } else if (j < n) {
-                            load_bfrag(bfA, xlane, xu + j * 2 * xpair, xpair);
-                            consume_unit<FMT>(cA, st + j * kUnitBytes, lane, bfA);
-                        }
-                    }
-                }
-            }
-            --in_flight;
-            if (++cslot == kRing) {
-                cslot = 0;
-                cpar ^= 1u;
-            }
-            // the slot is free again: order this warp's reads before the next asynchronous write
-            __syncwarp();
-            if (ip < p1) {
-                if (lane == 0) fence_proxy_async_smem();
-                issue_one();
-            }
-        }
-        // hand this warp's K slice of the panel to the epilogue warp (zeros if it has no units)
+    // hands one panel's K slice of this warp to the epilogue warp; false when the wait ran out
+    auto hand_over = [&](const float (&cA)[4], const float (&cB)[4], int p) -> bool {
         if (ruse > 0 && !mbar_wait(sbase + SSmem::kBarRedEmpty + 8 * rs, (ruse - 1) & 1, P.spin_limit)) {
             if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 7, p);
             *abort_flag = 1;
-            goto drain;
+            return false;
         }
         sts128f(red + rs * kSWarps * 512, (cA[0] + cB[0]) * fs0, (cA[1] + cB[1]) * fs1, (cA[2] + cB[2]) * fs0,
                 (cA[3] + cB[3]) * fs1);
-        __threadfence_block();
-        __syncwarp();
+        __syncwarp();  // orders the lanes' stores before lane 0's releasing arrive
         if (lane == 0) mbar_arrive(sbase + SSmem::kBarRedFull + 8 * rs);
         if (++rs == kSRedSlots) {
             rs = 0;
             ++ruse;
         }
+        return true;
+    };
+
+    for (int pr = 0; pr < n_pairs; ++pr) {
+        const int pa = p0 + PPI * pr;
+        const bool two = PPI == 2 && pa + 1 < p1;
+        float cA0[4] = {0.f, 0.f, 0.f, 0.f}, cB0[4] = {0.f, 0.f, 0.f, 0.f};
+        float cA1[4] = {0.f, 0.f, 0.f, 0.f}, cB1[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int c = 0; c < nck; ++c) {
+            if (!mbar_wait(bars + 8 * cslot, cpar, P.spin_limit)) {
+                if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 5, pa);
+                *abort_flag = 1;
+                goto drain;
+            }
+            {
+                const uint32_t st = ring + cslot * kPairBytes;
+                if (bf_fixed && two) {
+#pragma unroll
+                    for (int j = 0; j < CH; j += 2) {
+                        consume_two<FMT>(cA0, cB0, st + j * kUnitBytes, st + (j + 1) * kUnitBytes, lane, bfr[j],
+                                         bfr[j + 1]);
+                        consume_two<FMT>(cA1, cB1, st + kSlotBytes + j * kUnitBytes,
+                                         st + kSlotBytes + (j + 1) * kUnitBytes, lane, bfr[j], bfr[j + 1]);
+                    }
+                } else {
+                    const uint32_t xu = xbase + uint32_t((ck_lo + c) * CH) * xunit;
+                    const int n = FULL ? CH : min(CH, units - (ck_lo + c) * CH);
+#pragma unroll
+                    for (int j = 0; j < CH; j += 2) {
+                        uint32_t bfA[8], bfB[8];
+                        if (FULL || j + 1 < n) {
+                            load_bfrag(bfA, true, xu + j * xunit, xpair);
+                            load_bfrag(bfB, true, xu + (j + 1) * xunit, xpair);
+                            consume_two<FMT>(cA0, cB0, st + j * kUnitBytes, st + (j + 1) * kUnitBytes, lane, bfA, bfB);
+                            if (two)
+                                consume_two<FMT>(cA1, cB1, st + kSlotBytes + j * kUnitBytes,
+                                                 st + kSlotBytes + (j + 1) * kUnitBytes, lane, bfA, bfB);
+                        } else if (j < n) {
+                            load_bfrag(bfA, true, xu + j * xunit, xpair);
+                            consume_unit<FMT>(cA0, st + j * kUnitBytes, lane, bfA);
+                            if (two) consume_unit<FMT>(cA1, st + kSlotBytes + j * kUnitBytes, lane, bfA);
+                        }
+                    }
+                }
+            }
+            --in_flight;
+            if (++cslot == kWpRing) {
+                cslot = 0;
+                cpar ^= 1u;
+            }
+            // The slot is free again.  Every shared-memory load of this chunk has already delivered
+            // its data (the MMAs above consumed it), so once the warp has converged the next
+            // asynchronous write cannot pass a pending read: no cross-proxy fence is needed for this
+            // read-then-overwrite order.
+            __syncwarp();
+            if (to_issue > 0) issue_one();
+        }
+        // hand this warp's K slice of the panels to the epilogue warp (zeros if it has no chunks)
+        if (!hand_over(cA0, cB0, pa)) goto drain;
+        if (two && !hand_over(cA1, cB1, pa + 1)) goto drain;
     }
 drain:
     // never leave with copies in flight: wait (bounded) for every copy this warp still owns
     if (!drop) {
         while (in_flight > 0) {
             (void)mbar_wait(bars + 8 * cslot, cpar, int64_t(1) << 20);
-            if (++cslot == kRing) {
+            if (++cslot == kWpRing) {
                 cslot = 0;
                 cpar ^= 1u;
             }

@@ -41,11 +41,15 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-// Bounded wait: gives up after `spin_limit` polls or two seconds, whichever comes first.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int64_t spin_limit) {
+// Bounded wait: gives up after `spin_limit` polls or two seconds, whichever comes first.  A warp
+// that keeps polling competes for issue slots with the warps that have work, so every failed poll
+// is followed by a short sleep (`sleep_ns`; longer for waiters that are off the critical path).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int64_t spin_limit,
+                                          uint32_t sleep_ns = 32u) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = globaltimer_ns();
     for (int64_t i = 0; i < spin_limit; ++i) {
+        __nanosleep(sleep_ns);
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 63) == 63 && globaltimer_ns() - t0 > 2000000000ull) return false;
     }

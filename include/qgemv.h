@@ -91,6 +91,8 @@ typedef struct qgemv_dev_status {
 int qgemv_init(const qgemv_config* cfg, qgemv_handle** out);
 int qgemv_destroy(qgemv_handle* h);
 const char* qgemv_status_string(int status);
+/* Text of the last CUDA runtime error seen by the calling thread (after a QGEMV_ERR_CUDA). */
+const char* qgemv_last_cuda_error(void);
 /* Number of SMs of the handle's device (the CTA count the kernels are scheduled over). */
 int qgemv_sm_count(const qgemv_handle* h);
 
