@@ -93,6 +93,7 @@ def _load() -> C.CDLL:
     L.qgemv_weight_bytes.restype = i64
     L.qgemv_weight_bytes.argtypes = [vp]
     L.qgemv_gemv.argtypes = [vp, vp, vp, i32, vp, i32, vp]
+    L.qgemv_gemv_noalloc.argtypes = [vp, vp, vp, i32, vp, i32, vp]
     L.qgemv_moe_gemv.argtypes = [vp, vp, vp, vp, i32, i32, i32, vp, i32, vp]
     L.qgemv_moe_combine.argtypes = [vp, vp, i32, vp, i32, i32, i64, vp, i32, vp]
     L.qgemv_dequant_f32.argtypes = [vp, vp, i32, vp, vp]
@@ -252,3 +253,12 @@ class QGemv:
         st = _DevStatus()
         _check(_load().qgemv_last_device_status(self._ptr, stream, C.byref(st)), "device_status")
         return DeviceStatus(st.code, st.where, st.block, st.extra)
+
+
+def gemv_noalloc(dev_blob_ptr: int, host_blob: np.ndarray, x_ptr: int, B: int, y_ptr: int,
+                 y_dtype: int = OUT_BF16, stream: int = 0) -> None:
+    """Allocation-free GEMV: `dev_blob_ptr` is the caller's device copy of the packed blob and
+    `host_blob` the same blob (at least its first 256 bytes) in host memory.  Needs no handle; the
+    kernel's scratch is a static array inside the library (see include/qgemv.h for the limits)."""
+    _check(_load().qgemv_gemv_noalloc(dev_blob_ptr, _np_ptr(host_blob), x_ptr, B, y_ptr, y_dtype, stream),
+           "gemv_noalloc")

@@ -4,6 +4,7 @@
 
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 #include <new>
 #include <vector>
 
@@ -373,6 +374,122 @@ int qgemv_last_device_status(qgemv_handle* h, void* stream, qgemv_dev_status* ou
     out->block = v[2];
     out->extra = v[3];
     if (v[0] != 0) QG_CUDA(cudaMemset(h->status_dev, 0, sizeof v));
+    return QGEMV_OK;
+}
+
+
+// ---- allocation-free GEMV ----------------------------------------------------------------------
+// Some callers may not allocate device memory at the moment they need a projection: code running
+// inside a memory pool that owns the whole device, a plugin that was handed its buffers by a host
+// framework and must not touch the allocator, or a latency-critical path where a cudaMalloc would
+// synchronise the device.  qgemv_gemv_noalloc serves them: weights, activations and outputs are the
+// caller's buffers, and the kernel's own scratch (the partial-sum slots and arrival counters of
+// panels that are split between CTAs, the device status word and the tensor scale) lives in the
+// file-scope array below, which every GPU that loads this library holds until the process exits.
+namespace {
+constexpr int kNoAllocMaxCtas = 256;        // CTAs the scratch has partial-sum slots for
+constexpr int kNoAllocMaxPanels = 16384;    // 16-row panels (N <= 262144) it has counters for
+constexpr size_t kNoAllocWsBytes = size_t(2) * kNoAllocMaxCtas * 512;       // 256 KiB
+constexpr size_t kNoAllocCounterBytes = size_t(kNoAllocMaxPanels) * 4;      // 64 KiB
+constexpr size_t kNoAllocMiscBytes = 256;                                   // status word, tensor scale
+constexpr size_t kNoAllocBytes = kNoAllocWsBytes + kNoAllocCounterBytes + kNoAllocMiscBytes;
+constexpr int kNoAllocMaxDevices = 64;
+
+struct NoAllocDevice {
+    bool ready = false;
+    unsigned char* scratch = nullptr;  // device address of g_noalloc_scratch on that device
+    int sm_count = 0;
+};
+NoAllocDevice g_noalloc_dev[kNoAllocMaxDevices];
+std::mutex g_noalloc_mutex;
+}  // namespace
+
+// In host code this name is only a stand-in for the symbol: the device address comes from
+// cudaGetSymbolAddress, once per device, below.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+
+int qgemv_gemv_noalloc(const void* dev_blob, const void* host_header, const void* x_bf16, int B, void* y,
+                       int y_dtype, void* stream) {
+    if (!dev_blob || !host_header || !x_bf16 || !y) return QGEMV_ERR_INVALID_ARG;
+    if (B < 1 || B > QGEMV_MAX_BATCH) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+    if (y_dtype != QGEMV_OUT_BF16 && y_dtype != QGEMV_OUT_F32) return QGEMV_ERR_INVALID_ARG;
+    if ((reinterpret_cast<uintptr_t>(x_bf16) & 15u) != 0 || (reinterpret_cast<uintptr_t>(dev_blob) & 15u) != 0)
+        return QGEMV_ERR_INVALID_ARG;
+    qg_blob_header hd;
+    std::memcpy(&hd, host_header, sizeof hd);
+    if (hd.magic != QG_BLOB_MAGIC || hd.version != QG_BLOB_VERSION || hd.header_bytes != QG_HEADER_BYTES)
+        return QGEMV_ERR_BAD_BLOB;
+    if (hd.fmt != QGEMV_FMT_NVFP4 && hd.fmt != QGEMV_FMT_FP8) return QGEMV_ERR_BAD_BLOB;
+    if (hd.N <= 0 || hd.K <= 0 || hd.n_panels != (hd.N + 15) / 16 || hd.units_per_panel != (hd.K + 63) / 64)
+        return QGEMV_ERR_BAD_BLOB;
+    // limits of the static scratch and of the schedule that uses it
+    if (hd.n_panels > kNoAllocMaxPanels) return QGEMV_ERR_UNSUPPORTED_SHAPE;  // N above 262144 rows
+    if (!qg::use_stream_path(true, B, hd.units_per_panel)) return QGEMV_ERR_UNSUPPORTED_SHAPE;  // K * B above 32768
+
+    int dev = 0;
+    QG_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kNoAllocMaxDevices) return QGEMV_ERR_INVALID_ARG;
+    NoAllocDevice& nd = g_noalloc_dev[dev];
+    {
+        // First call on this device: resolve the scratch symbol and opt the kernels into their
+        // shared-memory size.  This is set-up work, so it should happen before any stream capture.
+        std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+        if (!nd.ready) {
+            cudaDeviceProp prop;
+            QG_CUDA(cudaGetDeviceProperties(&prop, dev));
+            if (prop.major != 10) return QGEMV_ERR_NO_DEVICE;
+            void* ptr = nullptr;
+            QG_CUDA(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+            const cudaFuncAttribute dyn = cudaFuncAttributeMaxDynamicSharedMemorySize;
+            QG_CUDA(cudaFuncSetAttribute(qg::gemv_stream_kernel<QGEMV_FMT_NVFP4>, dyn, qg::SSmem::total<QGEMV_FMT_NVFP4>()));
+            QG_CUDA(cudaFuncSetAttribute(qg::gemv_stream_kernel<QGEMV_FMT_FP8>, dyn, qg::SSmem::total<QGEMV_FMT_FP8>()));
+            nd.scratch = static_cast<unsigned char*>(ptr);
+            nd.sm_count = prop.multiProcessorCount;
+            nd.ready = true;
+        }
+    }
+    if (nd.sm_count > kNoAllocMaxCtas) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    unsigned char* ws = nd.scratch;
+    unsigned char* counters = ws + kNoAllocWsBytes;
+    unsigned char* misc = counters + kNoAllocCounterBytes;  // [0,16): status, [16,20): tensor scale
+    // The array keeps the previous call's contents: counters and status must start at zero.
+    QG_CUDA(cudaMemsetAsync(counters, 0, size_t(hd.n_panels) * 4, s));
+    QG_CUDA(cudaMemsetAsync(misc, 0, 16, s));
+    const float ts = hd.tensor_scale;
+    QG_CUDA(cudaMemcpyAsync(misc + 16, &ts, 4, cudaMemcpyHostToDevice, s));
+
+    qg::GemvParams P;
+    std::memset(&P, 0, sizeof P);
+    const uint8_t* blob = static_cast<const uint8_t*>(dev_blob);
+    P.payload = blob + QG_HEADER_BYTES + hd.aux_bytes;
+    P.stack_stride = 0;
+    P.chan_scale = reinterpret_cast<const float*>(blob + QG_HEADER_BYTES);
+    P.chan_stride = 0;
+    P.tensor_scale = reinterpret_cast<const float*>(misc + 16);
+    P.x = static_cast<const uint16_t*>(x_bf16);
+    P.y = y;
+    P.ws = reinterpret_cast<float*>(ws);
+    P.counters = reinterpret_cast<int32_t*>(counters);
+    P.status = reinterpret_cast<int32_t*>(misc);
+    P.prob = nullptr;
+    P.spin_limit = int64_t(1) << 26;
+    P.N = int32_t(hd.N);
+    P.K = int32_t(hd.K);
+    P.n_panels = int32_t(hd.n_panels);
+    P.units = int32_t(hd.units_per_panel);
+    P.B = B;
+    P.y_dtype = y_dtype;
+    P.debug = 0;
+    P.payload_bytes = hd.payload_bytes;
+    const dim3 grid(nd.sm_count), block(qg::kSThreads);
+    if (hd.fmt == QGEMV_FMT_NVFP4) {
+        qg::gemv_stream_kernel<QGEMV_FMT_NVFP4><<<grid, block, qg::SSmem::total<QGEMV_FMT_NVFP4>(), s>>>(P);
+    } else {
+        qg::gemv_stream_kernel<QGEMV_FMT_FP8><<<grid, block, qg::SSmem::total<QGEMV_FMT_FP8>(), s>>>(P);
+    }
+    QG_CUDA(cudaGetLastError());
     return QGEMV_OK;
 }
 

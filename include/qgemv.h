@@ -138,6 +138,27 @@ int64_t qgemv_weight_bytes(const qgemv_weight* w);
 int qgemv_gemv(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, int B, void* y,
                int y_dtype, void* stream);
 
+/* ---- allocation-free GEMV --------------------------------------------------------------------
+ * No counterpart in the crit-hub registry; added for callers that cannot allocate device memory
+ * when they need a projection: code living inside a memory pool that owns the whole GPU, plugins
+ * that must only use the buffers their host framework hands them, and latency-critical paths
+ * where a cudaMalloc would stall the device.  This call allocates nothing (no cudaMalloc, no
+ * cudaFree, no handle): the weights are a packed blob the CALLER copied to device memory
+ * (`dev_blob`, 16-byte aligned, laid out by qgemv_pack_host), `host_header` is the first 256 bytes
+ * of that blob in host memory, x and y are the caller's device buffers as for qgemv_gemv.
+ * The kernel's scratch (partial sums and arrival counters of panels split between CTAs, a status
+ * word, the tensor scale) is a 320 KiB array compiled into the library; every GPU that loads
+ * the library holds it until the process exits.
+ * Limits (QGEMV_ERR_UNSUPPORTED_SHAPE beyond them): N <= 262144 rows, K * B <= 32768, B <= 8,
+ * at most 256 SMs.
+ * The first call on a device resolves the array's device address and sets kernel attributes;
+ * make that first call before any stream capture.  All calls share the one array, and it keeps
+ * the previous call's contents: the call clears what must start at zero on `stream`, so calls
+ * that overlap on the GPU (different streams, or concurrent threads) race -- serialise them.
+ * Results equal qgemv_gemv's up to the summation order of the K split. */
+int qgemv_gemv_noalloc(const void* dev_blob, const void* host_header, const void* x_bf16, int B, void* y,
+                       int y_dtype, void* stream);
+
 /* ---- MoE grouped GEMV ---------------------------------------------------------------------------
  * One launch walks the router's top-k lists.  For every token t and slot j:
  *   out[t*topk + j][:] = W[expert_ids[t][j]] . x[row][:],
