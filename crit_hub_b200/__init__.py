@@ -93,6 +93,7 @@ def _load() -> C.CDLL:
     L.qgemv_weight_bytes.restype = i64
     L.qgemv_weight_bytes.argtypes = [vp]
     L.qgemv_gemv.argtypes = [vp, vp, vp, i32, vp, i32, vp]
+    L.qgemv_gemv_prefetch.argtypes = [vp, vp, vp, i32, vp, i32, vp, vp]
     L.qgemv_gemv_noalloc.argtypes = [vp, vp, vp, i32, vp, i32, vp]
     L.qgemv_moe_gemv.argtypes = [vp, vp, vp, vp, i32, i32, i32, vp, i32, vp]
     L.qgemv_moe_combine.argtypes = [vp, vp, i32, vp, i32, i32, i64, vp, i32, vp]
@@ -233,8 +234,14 @@ class QGemv:
                "load_stacked")
         return Weight(self, w.value, fmt, N, K, blobs.shape[0])
 
-    def gemv(self, w: Weight, x_ptr: int, B: int, y_ptr: int, y_dtype: int = OUT_BF16, stream: int = 0) -> None:
-        _check(_load().qgemv_gemv(self._ptr, w._ptr, x_ptr, B, y_ptr, y_dtype, stream), "gemv")
+    def gemv(self, w: Weight, x_ptr: int, B: int, y_ptr: int, y_dtype: int = OUT_BF16, stream: int = 0,
+             next_weight: Weight | None = None) -> None:
+        """y = W x.  `next_weight`: the matrix the caller multiplies by next; it is prefetched into L2."""
+        if next_weight is None:
+            _check(_load().qgemv_gemv(self._ptr, w._ptr, x_ptr, B, y_ptr, y_dtype, stream), "gemv")
+        else:
+            _check(_load().qgemv_gemv_prefetch(self._ptr, w._ptr, x_ptr, B, y_ptr, y_dtype, next_weight._ptr,
+                                               stream), "gemv")
 
     def moe_gemv(self, experts: Weight, expert_ids_ptr: int, x_ptr: int, T: int, topk: int,
                  per_slot_input: bool, out_ptr: int, out_dtype: int = OUT_F32, stream: int = 0) -> None:

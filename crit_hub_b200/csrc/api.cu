@@ -294,6 +294,11 @@ int64_t qgemv_weight_bytes(const qgemv_weight* w) {
 
 int qgemv_gemv(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, int B, void* y,
                int y_dtype, void* stream) {
+    return qgemv_gemv_prefetch(h, w, x_bf16, B, y, y_dtype, nullptr, stream);
+}
+
+int qgemv_gemv_prefetch(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, int B, void* y,
+                        int y_dtype, const qgemv_weight* next, void* stream) {
     if (!h || !w || !x_bf16 || !y) return QGEMV_ERR_INVALID_ARG;
     if (B < 1 || B > QGEMV_MAX_BATCH) return QGEMV_ERR_UNSUPPORTED_SHAPE;
     if (y_dtype != QGEMV_OUT_BF16 && y_dtype != QGEMV_OUT_F32) return QGEMV_ERR_INVALID_ARG;
@@ -304,6 +309,10 @@ int qgemv_gemv(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, int B
     P.B = B;
     P.y_dtype = y_dtype;
     P.prob = nullptr;
+    if (next) {
+        P.pf_base = next->dev_blob + QG_HEADER_BYTES + next->aux_bytes;
+        P.pf_bytes = next->payload_bytes;
+    }
     return launch_gemv(h, w, P, static_cast<cudaStream_t>(stream));
 }
 

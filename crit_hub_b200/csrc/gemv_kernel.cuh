@@ -78,6 +78,8 @@ struct GemvParams {
     int32_t y_dtype;
     int32_t debug;
     uint64_t payload_bytes;     // per stacked weight, for debug bounds checks
+    const uint8_t* pf_base;     // optional: payload of the weight the caller will use next
+    uint64_t pf_bytes;          // bytes of it to pull into L2 while this GEMV runs (0 = none)
 };
 
 struct Smem {

@@ -41,12 +41,12 @@ struct StreamTraits<QGEMV_FMT_FP8> {
 
 struct SSmem {
     static constexpr int kBarFull = 0;        // kSWarps * 4 * 8 = 512 bytes
-    static constexpr int kBarRedFull = 512;   // kSRedSlots * 8
-    static constexpr int kBarRedEmpty = 528;  // kSRedSlots * 8
-    static constexpr int kRowMax = 544;       // 8 words
-    static constexpr int kRowExp = 576;       // 8 words
-    static constexpr int kAbort = 608;
-    static constexpr int kZero = 640;         // 16 zero bytes
+    static constexpr int kBarRedFull = 512;   // 4 groups * kSRedSlots * 8
+    static constexpr int kBarRedEmpty = 576;  // 4 groups * kSRedSlots * 8
+    static constexpr int kRowMax = 640;       // 8 words
+    static constexpr int kRowExp = 672;       // 8 words
+    static constexpr int kAbort = 704;
+    static constexpr int kZero = 720;         // 16 zero bytes
     static constexpr int kXBuf = 1024;
     static constexpr int kRed = kXBuf + kSXBufBytes;                   // kSRedSlots * kSWarps * 512
     static constexpr int kRing0 = kRed + kSRedSlots * kSWarps * 512;
@@ -358,11 +358,21 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_wp_kernel(const Gemv
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int Bl = P.B;
     const int units = P.units;
+    const int grid = P.n_panels < int(gridDim.x) ? P.n_panels : int(gridDim.x);
+    const int cta = blockIdx.x;
+    const int p0 = cta < grid ? int((int64_t(cta) * P.n_panels) / grid) : 0;
+    const int p1 = cta < grid ? int((int64_t(cta + 1) * P.n_panels) / grid) : 0;
+    // Warp groups: the sixteen consumer warps form G groups of GS warps; a group works on every
+    // G-th panel of the CTA and splits K between its GS warps.  Many panels per CTA -> small groups
+    // (a warp stays longer on one panel, fewer hand-overs); few panels -> all sixteen warps split K.
+    const int npc = p1 - p0;
+    const int GS = npc >= 8 ? 4 : (npc >= 4 ? 8 : 16);
+    const int G = kSWarps / GS;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < kSWarps * kWpRing; ++i) mbar_init(sbase + SSmem::kBarFull + 8 * i, 1);
-        for (int i = 0; i < kSRedSlots; ++i) {
-            mbar_init(sbase + SSmem::kBarRedFull + 8 * i, kSWarps);
+        for (int i = 0; i < 4 * kSRedSlots; ++i) {  // up to four warp groups, two hand-over slots each
+            mbar_init(sbase + SSmem::kBarRedFull + 8 * i, uint32_t(GS));
             mbar_init(sbase + SSmem::kBarRedEmpty + 8 * i, 1);
         }
         for (int b = 0; b < 8; ++b) reinterpret_cast<volatile unsigned int*>(smem_raw + SSmem::kRowMax)[b] = 0u;
@@ -374,10 +384,7 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_wp_kernel(const Gemv
     __syncthreads();
     pdl_launch_dependents();
 
-    const int grid = P.n_panels < int(gridDim.x) ? P.n_panels : int(gridDim.x);
-    const int cta = blockIdx.x;
     if (cta >= grid) return;
-    const int p0 = int((int64_t(cta) * P.n_panels) / grid), p1 = int((int64_t(cta + 1) * P.n_panels) / grid);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + SSmem::kAbort);
 
     if (warp == kSEpilogueWarp) {
@@ -385,26 +392,43 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_wp_kernel(const Gemv
         pdl_wait();  // the output buffer may still be in use by the preceding kernel
         const float ts = (FMT == QGEMV_FMT_NVFP4) ? P.tensor_scale[0] : 1.0f;
         const uint32_t red = sbase + SSmem::kRed + lane * 16;
-        uint32_t rs = 0, rpar = 0;
-        for (int p = p0; p < p1; ++p) {
-            if (!mbar_wait(sbase + SSmem::kBarRedFull + 8 * rs, rpar, P.spin_limit, 200u)) {
+        // Optional L2 prefetch of the weight the caller uses next: this CTA's share, issued in
+        // pieces as its own panels complete, so it trails this GEMV's demand loads instead of
+        // competing with them.  Weights are immutable, so prefetching them early is always safe.
+        uint64_t pf_pos = 0, pf_end = 0, pf_step = 0;
+        if (P.pf_bytes != 0) {
+            pf_pos = ((uint64_t(cta) * P.pf_bytes) / grid) & ~uint64_t(127);
+            pf_end = cta + 1 == grid ? (P.pf_bytes & ~uint64_t(15)) : (((uint64_t(cta + 1) * P.pf_bytes) / grid) & ~uint64_t(127));
+            pf_step = ((pf_end - pf_pos) / uint64_t(npc) + 127) & ~uint64_t(127);
+        }
+        for (int i = 0; i < npc; ++i) {
+            const int p = p0 + i;
+            const int gidx = i % G, use = i / G;
+            const int rs = use % kSRedSlots;
+            const uint32_t rpar = uint32_t(use / kSRedSlots) & 1u;
+            const int bi = gidx * kSRedSlots + rs;
+            if (!mbar_wait(sbase + SSmem::kBarRedFull + 8 * bi, rpar, P.spin_limit, 200u)) {
                 if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 6, p);
                 *abort_flag = 1;
                 return;
             }
-            float4 v = lds128f(red + (rs * kSWarps) * 512);
-#pragma unroll
-            for (int ww = 1; ww < kSWarps; ++ww) {
-                const float4 q = lds128f(red + (rs * kSWarps + ww) * 512);
+            const uint32_t slot = red + uint32_t(bi * GS) * 512u;
+            float4 v = lds128f(slot);
+            for (int ww = 1; ww < GS; ++ww) {
+                const float4 q = lds128f(slot + ww * 512);
                 v.x += q.x, v.y += q.y, v.z += q.z, v.w += q.w;
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(sbase + SSmem::kBarRedEmpty + 8 * rs);
+            if (lane == 0) mbar_arrive(sbase + SSmem::kBarRedEmpty + 8 * bi);
             v.x *= ts, v.y *= ts, v.z *= ts, v.w *= ts;
             store_panel<FMT>(P, v, lane, p, Bl, nullptr, P.chan_scale);
-            if (++rs == kSRedSlots) {
-                rs = 0;
-                rpar ^= 1u;
+            if (pf_pos < pf_end && lane == 0) {
+                const uint64_t stop = (i + 1 == npc || pf_pos + pf_step > pf_end) ? pf_end : pf_pos + pf_step;
+                while (pf_pos < stop) {
+                    const uint32_t n = uint32_t(stop - pf_pos < 32768 ? stop - pf_pos : 32768);
+                    bulk_prefetch_l2(P.pf_base + pf_pos, n);
+                    pf_pos += n;
+                }
             }
         }
         return;
@@ -417,7 +441,8 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_wp_kernel(const Gemv
     const int w = warp;
     const int g = lane >> 2, t = lane & 3;
     const int n_chunks = (units + CH - 1) / CH;
-    const int ck_lo = (w * n_chunks) / kSWarps, ck_hi = ((w + 1) * n_chunks) / kSWarps;
+    const int gidx = w / GS, ws = w - gidx * GS;  // group and K-slice index inside the group
+    const int ck_lo = (ws * n_chunks) / GS, ck_hi = ((ws + 1) * n_chunks) / GS;
     const int nck = ck_hi - ck_lo;  // chunks of this warp in every panel
     constexpr int kPairBytes = PPI * kSlotBytes;
     const uint32_t ring = sbase + SSmem::kRing0 + w * (kWpRing * kPairBytes);
@@ -427,24 +452,25 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_wp_kernel(const Gemv
 
     // issue cursor: running byte offset of panel a's chunk, chunk counter, ring slot
     const uint32_t panel_bytes = uint32_t(units) * kUnitBytes;  // a packed matrix is below 4 GB
-    const int n_pairs = (p1 - p0 + PPI - 1) / PPI;
-    uint32_t ioff = uint32_t(p0) * panel_bytes + uint32_t(ck_lo) * kSlotBytes;
-    const uint32_t ioff_next_pair = uint32_t(PPI) * panel_bytes - uint32_t(nck) * kSlotBytes;
+    const int np_g = npc > gidx ? (npc - gidx + G - 1) / G : 0;  // panels of this group
+    const int n_pairs = (np_g + PPI - 1) / PPI;
+    uint32_t ioff = uint32_t(p0 + gidx) * panel_bytes + uint32_t(ck_lo) * kSlotBytes;
+    const uint32_t ioff_next_pair = uint32_t(PPI * G) * panel_bytes - uint32_t(nck) * kSlotBytes;
     int ic = 0, islot = 0, ipair = 0;
     int to_issue = nck * n_pairs, in_flight = 0;
     auto issue_one = [&]() {
         if (lane == 0 && !drop) {
             uint32_t bytes = kSlotBytes;
             if (!FULL) bytes = uint32_t(min(CH, units - (ck_lo + ic) * CH)) * kUnitBytes;
-            const bool two = PPI == 2 && p0 + 2 * ipair + 1 < p1;
-            if ((P.debug & 1) && uint64_t(ioff) + (two ? panel_bytes : 0u) + bytes > P.payload_bytes) {
+            const bool two = PPI == 2 && 2 * ipair + 1 < np_g;
+            if ((P.debug & 1) && uint64_t(ioff) + (two ? uint64_t(G) * panel_bytes : 0u) + bytes > P.payload_bytes) {
                 report(P.status, QGEMV_ERR_BOUNDS, 2, ipair);
             } else {
                 const uint32_t bar = bars + 8 * islot;
                 const uint32_t dst = ring + islot * kPairBytes;
                 mbar_arrive_expect_tx(bar, two ? 2u * bytes : bytes);
                 bulk_g2s(dst, P.payload + ioff, bytes, bar, pol);
-                if (two) bulk_g2s(dst + kSlotBytes, P.payload + ioff + panel_bytes, bytes, bar, pol);
+                if (two) bulk_g2s(dst + kSlotBytes, P.payload + ioff + uint32_t(G) * panel_bytes, bytes, bar, pol);
             }
         }
         ioff += kSlotBytes;
@@ -482,21 +508,23 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_wp_kernel(const Gemv
         bfr[j][0] = x0.x, bfr[j][1] = x0.y, bfr[j][2] = x0.z, bfr[j][3] = x0.w;
         bfr[j][4] = x1.x, bfr[j][5] = x1.y, bfr[j][6] = x1.z, bfr[j][7] = x1.w;
     }
-    const uint32_t red = sbase + SSmem::kRed + w * 512 + lane * 16;
+    const uint32_t red = sbase + SSmem::kRed + uint32_t(gidx * kSRedSlots * GS + ws) * 512u + lane * 16;
+    const uint32_t red_bars = 8u * uint32_t(gidx * kSRedSlots);
     uint32_t rs = 0, ruse = 0;
     int cslot = 0;
     uint32_t cpar = 0;
     // hands one panel's K slice of this warp to the epilogue warp; false when the wait ran out
     auto hand_over = [&](const float (&cA)[4], const float (&cB)[4], int p) -> bool {
-        if (ruse > 0 && !mbar_wait(sbase + SSmem::kBarRedEmpty + 8 * rs, (ruse - 1) & 1, P.spin_limit)) {
+        if (ruse > 0 &&
+            !mbar_wait(sbase + SSmem::kBarRedEmpty + red_bars + 8 * rs, (ruse - 1) & 1, P.spin_limit)) {
             if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 7, p);
             *abort_flag = 1;
             return false;
         }
-        sts128f(red + rs * kSWarps * 512, (cA[0] + cB[0]) * fs0, (cA[1] + cB[1]) * fs1, (cA[2] + cB[2]) * fs0,
+        sts128f(red + rs * uint32_t(GS) * 512u, (cA[0] + cB[0]) * fs0, (cA[1] + cB[1]) * fs1, (cA[2] + cB[2]) * fs0,
                 (cA[3] + cB[3]) * fs1);
         __syncwarp();  // orders the lanes' stores before lane 0's releasing arrive
-        if (lane == 0) mbar_arrive(sbase + SSmem::kBarRedFull + 8 * rs);
+        if (lane == 0) mbar_arrive(sbase + SSmem::kBarRedFull + red_bars + 8 * rs);
         if (++rs == kSRedSlots) {
             rs = 0;
             ++ruse;
@@ -505,8 +533,8 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_wp_kernel(const Gemv
     };
 
     for (int pr = 0; pr < n_pairs; ++pr) {
-        const int pa = p0 + PPI * pr;
-        const bool two = PPI == 2 && pa + 1 < p1;
+        const int pa = p0 + gidx + PPI * pr * G;
+        const bool two = PPI == 2 && PPI * pr + 1 < np_g;
         float cA0[4] = {0.f, 0.f, 0.f, 0.f}, cB0[4] = {0.f, 0.f, 0.f, 0.f};
         float cA1[4] = {0.f, 0.f, 0.f, 0.f}, cB1[4] = {0.f, 0.f, 0.f, 0.f};
         for (int c = 0; c < nck; ++c) {
@@ -560,7 +588,7 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_wp_kernel(const Gemv
         }
         // hand this warp's K slice of the panels to the epilogue warp (zeros if it has no chunks)
         if (!hand_over(cA0, cB0, pa)) goto drain;
-        if (two && !hand_over(cA1, cB1, pa + 1)) goto drain;
+        if (two && !hand_over(cA1, cB1, pa + G)) goto drain;
     }
 drain:
     // never leave with copies in flight: wait (bounded) for every copy this warp still owns

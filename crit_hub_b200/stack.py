@@ -31,8 +31,9 @@ class LayerStack:
     """Owns an activation arena [sum B*K] bf16 and an output arena [sum B*N]; one GEMV per weight."""
 
     def __init__(self, handle: QGemv, weights: list[Weight], batch: int, out_dtype: int = OUT_BF16,
-                 device: int = 0):
+                 device: int = 0, prefetch_next: bool = True):
         self.handle, self.batch, self.out_dtype = handle, batch, out_dtype
+        self.prefetch_next = prefetch_next  # name the following matrix in every call (L2 prefetch)
         self.device = torch.device("cuda", device)
         self.calls: list[_Call] = []
         x_total = y_total = 0
@@ -74,9 +75,11 @@ class LayerStack:
     def _enqueue(self, stream_handle: int) -> None:
         xe, ye = self.x_dev.element_size(), self.y_dev.element_size()
         xb, yb = self.x_dev.data_ptr(), self.y_dev.data_ptr()
-        for c in self.calls:
+        n = len(self.calls)
+        for i, c in enumerate(self.calls):
+            nxt = self.calls[(i + 1) % n].weight if self.prefetch_next and n > 1 else None
             self.handle.gemv(c.weight, xb + c.x_off * xe, self.batch, yb + c.y_off * ye, self.out_dtype,
-                             stream_handle)
+                             stream_handle, next_weight=nxt)
 
     def capture(self) -> None:
         """Run once eagerly (loads modules, warms caches), then capture the stack into a graph."""

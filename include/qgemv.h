@@ -137,6 +137,12 @@ int64_t qgemv_weight_bytes(const qgemv_weight* w);
  * along K", tools/fixtures/engines/crit-labs/mtp-adaptive-width/card.yaml:77). */
 int qgemv_gemv(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, int B, void* y,
                int y_dtype, void* stream);
+/* Same GEMV; additionally pulls the packed weight `next` (nullable) into L2 while this GEMV runs.
+ * An engine knows the order of its projections ("one CUDA graph per round",
+ * tools/fixtures/engines/crit-labs/mtp4-nvfp4-mma/card.yaml:75): naming the next matrix keeps HBM
+ * busy across the launch boundary.  Weights are immutable, so the hint never changes a result. */
+int qgemv_gemv_prefetch(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, int B, void* y,
+                        int y_dtype, const qgemv_weight* next, void* stream);
 
 /* ---- allocation-free GEMV --------------------------------------------------------------------
  * No counterpart in the crit-hub registry; added for callers that cannot allocate device memory
