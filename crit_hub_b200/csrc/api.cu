@@ -12,6 +12,7 @@
 #include "aux_kernels.cuh"
 #include "gemv_kernel.cuh"
 #include "gemv_stream.cuh"
+#include "moe_stream.cuh"
 #include "qgemv_layout.h"
 
 extern "C" int qgemv_blob_verify(const void* blob, size_t bytes);
@@ -189,6 +190,8 @@ int qgemv_init(const qgemv_config* cfg, qgemv_handle** out) {
         cudaFuncSetAttribute(qg::gemv_kernel<QGEMV_FMT_FP8, false>, dyn, qg::Smem::total<QGEMV_FMT_FP8>()) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_stream_kernel<QGEMV_FMT_NVFP4>, dyn, qg::SSmem::total<QGEMV_FMT_NVFP4>()) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_stream_kernel<QGEMV_FMT_FP8>, dyn, qg::SSmem::total<QGEMV_FMT_FP8>()) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::moe_stream_kernel<QGEMV_FMT_NVFP4>, dyn, qg::SSmem::total<QGEMV_FMT_NVFP4>()) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::moe_stream_kernel<QGEMV_FMT_FP8>, dyn, qg::SSmem::total<QGEMV_FMT_FP8>()) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_NVFP4, true, 1>, dyn, qg::SSmem::total<QGEMV_FMT_NVFP4>()) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_NVFP4, false, 1>, dyn, qg::SSmem::total<QGEMV_FMT_NVFP4>()) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8, true, 1>, dyn, qg::SSmem::total<QGEMV_FMT_FP8>()) != cudaSuccess ||
@@ -325,9 +328,9 @@ int qgemv_moe_gemv(qgemv_handle* h, const qgemv_weight* experts, const int32_t* 
     if (out_dtype != QGEMV_OUT_BF16 && out_dtype != QGEMV_OUT_F32) return QGEMV_ERR_INVALID_ARG;
     if ((reinterpret_cast<uintptr_t>(x_bf16) & 15u) != 0) return QGEMV_ERR_INVALID_ARG;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const int threads = experts->n_stack < 1024 ? ((experts->n_stack + 31) / 32) * 32 : 1024;
+    const int threads = 1024;  // 32 warps, one expert per warp at a time
     cudaError_t err = launch(h, qg::moe_prep_kernel, dim3(1), dim3(threads),
-                             size_t(experts->n_stack) * 8, s, expert_ids, T, topk, experts->n_stack,
+                             size_t(experts->n_stack) * 8 + size_t(T) * topk * 4 + 16, s, expert_ids, T, topk, experts->n_stack,
                              per_slot_input, experts->max_prob, experts->prob, h->status_dev);
     if (err != cudaSuccess) return QGEMV_ERR_CUDA;
     qg::GemvParams P = base_params(h, experts);
@@ -336,6 +339,13 @@ int qgemv_moe_gemv(qgemv_handle* h, const qgemv_weight* experts, const int32_t* 
     P.B = 0;
     P.y_dtype = out_dtype;
     P.prob = experts->prob;
+    if (qg::use_moe_stream_path(experts->units) && !(h->cfg.debug & 256)) {
+        const dim3 grid(gemv_grid(h)), block(qg::kSThreads);
+        err = experts->fmt == QGEMV_FMT_NVFP4
+                  ? launch(h, qg::moe_stream_kernel<QGEMV_FMT_NVFP4>, grid, block, qg::SSmem::total<QGEMV_FMT_NVFP4>(), s, P)
+                  : launch(h, qg::moe_stream_kernel<QGEMV_FMT_FP8>, grid, block, qg::SSmem::total<QGEMV_FMT_FP8>(), s, P);
+        return err == cudaSuccess ? QGEMV_OK : QGEMV_ERR_CUDA;
+    }
     return launch_gemv(h, experts, P, s);
 }
 

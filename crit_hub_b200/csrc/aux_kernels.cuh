@@ -76,61 +76,93 @@ __global__ void dequant_kernel(const uint8_t* payload, const float* chan, float 
 // Router walk: groups the (token, slot) pairs of expert_ids [T][topk] by expert, in ascending
 // (t, j) order, and cuts each group into problems of at most eight activation rows.
 // prob[0] = problem count; problem i = {expert, nrows, xrow[8], orow[8], 0, 0}.
-// One CTA, one thread per expert (strided), so the table is deterministic.
+// One CTA; a warp per expert (strided) scans the list 32 entries at a time with ballots, so the
+// order inside every problem is the list order and the table is deterministic.
 __global__ void moe_prep_kernel(const int32_t* expert_ids, int T, int topk, int n_experts,
                                 int per_slot_input, int max_prob, int32_t* prob, int32_t* status) {
-    extern __shared__ int sh[];  // counts[n_experts], base[n_experts]
-    int* counts = sh;
-    int* base = sh + n_experts;
+    extern __shared__ int sh[];  // ids[T*topk], counts[n_experts], base[n_experts], flags[2]
+    const int total = T * topk;
+    int* ids = sh;
+    int* counts = sh + total;
+    int* base = counts + n_experts;
+    int* flags = base + n_experts;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     pdl_launch_dependents();
     pdl_wait();
-    const int total = T * topk;
-    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
+    if (threadIdx.x == 0) flags[0] = 0, flags[1] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < total; i += blockDim.x) {  // one coalesced read of the router output
+        const int e = __ldcg(expert_ids + i);
+        ids[i] = e;
+        if (e < 0 || e >= n_experts) flags[0] = 1;
+    }
+    __syncthreads();
+    for (int e = warp; e < n_experts; e += nwarps) {
         int c = 0;
-        for (int i = 0; i < total; ++i) c += (__ldcg(expert_ids + i) == e);
-        counts[e] = c;
+        for (int i0 = 0; i0 < total; i0 += 32) {
+            const int i = i0 + lane;
+            c += __popc(__ballot_sync(0xFFFFFFFFu, i < total && ids[i] == e));
+        }
+        if (lane == 0) counts[e] = c;
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        int acc = 0;
-        for (int e = 0; e < n_experts; ++e) {
-            base[e] = acc;
-            acc += (counts[e] + 7) / 8;
-        }
-        if (acc > max_prob) {
-            report(status, QGEMV_ERR_BOUNDS, 20, acc);
-            acc = 0;
-        }
-        prob[0] = acc;
-        int bad = 0;
-        for (int i = 0; i < total; ++i) {
-            const int e = __ldcg(expert_ids + i);
-            bad |= (e < 0 || e >= n_experts);
-        }
-        if (bad) {
-            report(status, QGEMV_ERR_BOUNDS, 21, 0);
-            prob[0] = 0;
-        }
-    }
-    __syncthreads();
-    if (prob[0] == 0) return;
-    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
-        if (counts[e] == 0) continue;
-        int seen = 0;
-        for (int i = 0; i < total; ++i) {
-            if (__ldcg(expert_ids + i) != e) continue;
-            int32_t* p = prob + 1 + (base[e] + seen / 8) * kProbInts;
-            const int r = seen & 7;
-            if (r == 0) {
-                p[0] = e;
-                const int left = counts[e] - seen;
-                p[1] = left < 8 ? left : 8;
-                for (int z = 0; z < 8; ++z) p[2 + z] = 0, p[10 + z] = 0;
-                p[18] = p[19] = 0;
+    if (warp == 0) {  // exclusive prefix of the per-expert problem counts
+        int carry = 0;
+        for (int e0 = 0; e0 < n_experts; e0 += 32) {
+            const int e = e0 + lane;
+            const int np = e < n_experts ? (counts[e] + 7) / 8 : 0;
+            int incl = np;
+            for (int d = 1; d < 32; d <<= 1) {
+                const int v = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+                if (lane >= d) incl += v;
             }
-            p[2 + r] = per_slot_input ? i : i / topk;
-            p[10 + r] = i;
-            ++seen;
+            if (e < n_experts) base[e] = carry + incl - np;
+            carry += __shfl_sync(0xFFFFFFFFu, incl, 31);
+        }
+        if (lane == 0) {
+            int acc = carry;
+            if (flags[0]) {
+                report(status, QGEMV_ERR_BOUNDS, 21, 0);
+                acc = 0;
+            } else if (acc > max_prob) {
+                report(status, QGEMV_ERR_BOUNDS, 20, acc);
+                acc = 0;
+            }
+            prob[0] = acc;
+            flags[1] = acc;
+        }
+    }
+    __syncthreads();
+    if (flags[1] == 0) return;
+    for (int e = warp; e < n_experts; e += nwarps) {
+        const int cnt = counts[e];
+        if (cnt == 0) continue;
+        int seen = 0;
+        for (int i0 = 0; i0 < total; i0 += 32) {
+            const int i = i0 + lane;
+            const bool hit = i < total && ids[i] == e;
+            const unsigned m = __ballot_sync(0xFFFFFFFFu, hit);
+            if (hit) {
+                const int k = seen + __popc(m & ((1u << lane) - 1u));  // rank of this entry in the expert's list
+                int32_t* p = prob + 1 + (base[e] + (k >> 3)) * kProbInts;
+                const int r = k & 7;
+                if (r == 0) {
+                    p[0] = e;
+                    const int left = cnt - k;
+                    p[1] = left < 8 ? left : 8;
+                    p[18] = p[19] = 0;
+                }
+                p[2 + r] = per_slot_input ? i : i / topk;
+                p[10 + r] = i;
+            }
+            seen += __popc(m);
+        }
+        // unused row slots of the last problem of this expert
+        const int tail = cnt & 7;
+        if (tail != 0 && lane >= tail && lane < 8) {
+            int32_t* p = prob + 1 + (base[e] + (cnt >> 3)) * kProbInts;
+            p[2 + lane] = 0;
+            p[10 + lane] = 0;
         }
     }
 }
