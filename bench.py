@@ -97,7 +97,12 @@ class ClockSampler:
 
 
 def build_stack(model, batch, rank, world, dev_index):
+    """The rank's share of the layer stack.  Tensor parallel: QKV and gate/up are column-parallel
+    (this rank holds N/world output rows), o and down are row-parallel (K/world input columns; their
+    outputs are partial sums that are all-reduced right after the GEMV, inside the captured graph).
+    Each rank synthesises its own shard directly (seeded by layer, matrix and rank)."""
     import torch
+    import torch.distributed as dist
 
     import crit_hub_b200 as qg
     from crit_hub_b200.stack import LayerStack, llama_layer_shapes, synth_nvfp4
@@ -106,21 +111,41 @@ def build_stack(model, batch, rank, world, dev_index):
     handle = qg.QGemv(device=dev_index, use_pdl=True)
     shapes = llama_layer_shapes(model["hidden"], model["q_heads"], model["kv_heads"], model["head_dim"],
                                 model["inter"])
-    weights, total_bytes = [], 0
+    weights, total_bytes, row_parallel = [], 0, []
     for layer in range(model["layers"]):
         for mi, (name, N, K) in enumerate(shapes):
-            codes, scales = synth_nvfp4(N, K, 1000 * layer + mi, device)
-            shard = None
             if world > 1:
-                if name in ("qkv", "gate_up"):   # column-parallel: split output rows
-                    shard = qg.Shard(rank * N // world, (rank + 1) * N // world, 0, K)
-                else:                             # row-parallel: split K
-                    shard = qg.Shard(0, N, rank * K // world, (rank + 1) * K // world)
-            blob = qg.pack(qg.FMT_NVFP4, codes, scales, 1.0, shard=shard)
-            w = handle.load(blob)
+                if name in ("qkv", "gate_up"):
+                    N = N // world
+                else:
+                    K = K // world
+            codes, scales = synth_nvfp4(N, K, (1000 * layer + mi) * 16 + rank, device)
+            w = handle.load(qg.pack(qg.FMT_NVFP4, codes, scales, 1.0))
             weights.append(w)
+            row_parallel.append(world > 1 and name in ("o", "down"))
             total_bytes += w.weight_bytes
-    stack = LayerStack(handle, weights, batch, qg.OUT_BF16, device=dev_index)
+
+    stack_ref = []
+    if world > 1:
+        # exchange buffers for the peer-memory all-reduce: gather every rank's CUDA IPC handle
+        hidden_elems = batch * model["hidden"]
+        mine = torch.from_numpy(handle.tp_create(rank, world, hidden_elems)).to(device)
+        gathered = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(gathered, mine)
+        torch.cuda.synchronize()
+        handle.tp_connect(torch.stack(gathered).cpu().numpy())
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    def after_call(i):
+        if row_parallel[i]:
+            st = stack_ref[0]
+            out = st.output(i)
+            handle.tp_allreduce(out.data_ptr(), qg.OUT_BF16, out.numel(), torch.cuda.current_stream().cuda_stream)
+
+    stack = LayerStack(handle, weights, batch, qg.OUT_BF16, device=dev_index,
+                       after_call=after_call if world > 1 else None)
+    stack_ref.append(stack)
     g = torch.Generator()
     g.manual_seed(7 + rank)
     stack.set_inputs([torch.randn((batch, w.K), generator=g).to(torch.bfloat16) for w in weights])
@@ -204,23 +229,27 @@ def main():
     if args.layers > 0:
         model["layers"] = args.layers
 
+    def note(msg):
+        if os.environ.get("QGEMV_BENCH_VERBOSE"):
+            print(f"[rank {rank}] {msg}", file=sys.stderr, flush=True)
+
+    note("building the stack")
     handle, stack, rank_bytes = build_stack(model, args.batch, rank, world, local)
+    note("capturing")
     stack.capture()
+    note("captured")
     st = handle.device_status(stack.stream.cuda_stream)
     if st.code != 0:
         raise SystemExit(f"kernel reported {st}")
 
     def barrier():
-        if world > 1:
-            dist.barrier()
+        # every NCCL operation of this process runs on the stack's stream: collectives of one
+        # communicator must be issued in the same order on every rank
         torch.cuda.synchronize()
-
-    def all_reduce_partials():
-        # row-parallel o_proj / down outputs are partial sums: one all-reduce per block
         if world > 1:
-            for i, c in enumerate(stack.calls):
-                if i % 4 in (1, 3):
-                    dist.all_reduce(stack.output(i))
+            with torch.cuda.stream(stack.stream):
+                dist.barrier()
+        torch.cuda.synchronize()
 
     def timed(fn, n):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -234,22 +263,22 @@ def main():
         barrier()
         ms = e0.elapsed_time(e1)
         if world > 1:
-            t = torch.tensor([ms], device="cuda")
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            with torch.cuda.stream(stack.stream):
+                t = torch.tensor([ms], device="cuda")
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            torch.cuda.synchronize()
             ms = float(t.item())
         return ms
 
     def dev_step():
         stack.step()
-        if world > 1:
-            with torch.cuda.stream(stack.stream):
-                all_reduce_partials()
 
     def host_step():
         stack.step_host()
 
     for _ in range(warmup):
         dev_step()
+    note("warm-up done")
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -264,16 +293,19 @@ def main():
 
     total_bytes = rank_bytes
     if world > 1:
-        t = torch.tensor([float(rank_bytes)], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t)
+        with torch.cuda.stream(stack.stream):
+            t = torch.tensor([float(rank_bytes)], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t)
+        torch.cuda.synchronize()
         total_bytes = float(t.item())
     if rank == 0:
         peak, peak_kind = measured_peak_gbs()
         gbs = total_bytes * args.steps / (ms * 1e-3) / 1e9
         gbs_host = total_bytes * args.steps / (ms_host * 1e-3) / 1e9
-        launches = stack.launches_per_step * args.steps
+        n_allreduce = sum(1 for i in range(stack.launches_per_step) if world > 1 and i % 4 in (1, 3))
+        launches = (stack.launches_per_step + n_allreduce) * args.steps
         per_launch_bytes = rank_bytes / stack.launches_per_step
-        per_launch_us = ms * 1e3 / launches
+        per_launch_us = ms * 1e3 / (stack.launches_per_step * args.steps)
         achieved = per_launch_bytes / (per_launch_us * 1e-6) / 1e9
         line = {
             "metric": METRIC, "value": round(gbs, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -284,6 +316,7 @@ def main():
                 "workload": f"{model['name']}-shaped decode layer stack, NVFP4 weights, batch {args.batch}, "
                             f"{model['layers']} layers x (qkv, o, gate_up, down)",
                 "batch": args.batch, "layers": model["layers"], "tp": world,
+                "exchange": "none" if world == 1 else "peer-memory push all-reduce after o and down (tp_allreduce_kernel), in the graph",
                 "weight_bytes_per_step": int(total_bytes),
                 "us_per_layer": round(ms * 1e3 / args.steps / model["layers"], 3),
                 "cache": "weights per step exceed L2 (126 MB); every replay streams from HBM",

@@ -94,6 +94,9 @@ def _load() -> C.CDLL:
     L.qgemv_weight_bytes.argtypes = [vp]
     L.qgemv_gemv.argtypes = [vp, vp, vp, i32, vp, i32, vp]
     L.qgemv_gemv_prefetch.argtypes = [vp, vp, vp, i32, vp, i32, vp, vp]
+    L.qgemv_tp_create.argtypes = [vp, i32, i32, i64, vp]
+    L.qgemv_tp_connect.argtypes = [vp, vp]
+    L.qgemv_tp_allreduce.argtypes = [vp, vp, i32, i64, vp]
     L.qgemv_gemv_noalloc.argtypes = [vp, vp, vp, i32, vp, i32, vp]
     L.qgemv_moe_gemv.argtypes = [vp, vp, vp, vp, i32, i32, i32, vp, i32, vp]
     L.qgemv_moe_combine.argtypes = [vp, vp, i32, vp, i32, i32, i64, vp, i32, vp]
@@ -255,6 +258,21 @@ class QGemv:
 
     def dequant_f32(self, w: Weight, out_ptr: int, which: int = 0, stream: int = 0) -> None:
         _check(_load().qgemv_dequant_f32(self._ptr, w._ptr, which, out_ptr, stream), "dequant_f32")
+
+    # ---- tensor parallel --------------------------------------------------------------------------
+    def tp_create(self, rank: int, world: int, max_elems: int) -> np.ndarray:
+        """Allocates this rank's exchange buffer; returns its 64-byte CUDA IPC handle."""
+        out = np.zeros(64, dtype=np.uint8)
+        _check(_load().qgemv_tp_create(self._ptr, rank, world, max_elems, _np_ptr(out)), "tp_create")
+        return out
+
+    def tp_connect(self, all_handles: np.ndarray) -> None:
+        """all_handles: u8 [world][64], the handles of every rank in rank order."""
+        _check(_load().qgemv_tp_connect(self._ptr, _np_ptr(np.ascontiguousarray(all_handles, dtype=np.uint8))),
+               "tp_connect")
+
+    def tp_allreduce(self, y_ptr: int, y_dtype: int, n: int, stream: int = 0) -> None:
+        _check(_load().qgemv_tp_allreduce(self._ptr, y_ptr, y_dtype, n, stream), "tp_allreduce")
 
     def device_status(self, stream: int = 0) -> DeviceStatus:
         st = _DevStatus()

@@ -13,6 +13,7 @@
 #include "gemv_kernel.cuh"
 #include "gemv_stream.cuh"
 #include "moe_stream.cuh"
+#include "tp_allreduce.cuh"
 #include "qgemv_layout.h"
 
 extern "C" int qgemv_blob_verify(const void* blob, size_t bytes);
@@ -21,6 +22,12 @@ struct qgemv_handle {
     qgemv_config cfg;
     int sm_count;
     int32_t* status_dev;
+    // tensor-parallel exchange (qgemv_tp_*)
+    int tp_rank, tp_world;
+    int64_t tp_max_elems;
+    uint8_t* tp_local;                     // this rank's exchange buffer
+    uint8_t* tp_peer[qg::kTpMaxWorld];     // every rank's buffer as mapped here (tp_peer[rank] == tp_local)
+    uint32_t* tp_epochs;
 };
 
 struct qgemv_weight {
@@ -178,6 +185,9 @@ int qgemv_init(const qgemv_config* cfg, qgemv_handle** out) {
     h->cfg = *cfg;
     h->sm_count = prop.multiProcessorCount;
     h->status_dev = nullptr;
+    h->tp_rank = 0, h->tp_world = 0, h->tp_max_elems = 0;
+    h->tp_local = nullptr, h->tp_epochs = nullptr;
+    for (int i = 0; i < qg::kTpMaxWorld; ++i) h->tp_peer[i] = nullptr;
     if (cudaMalloc(&h->status_dev, 4 * sizeof(int32_t)) != cudaSuccess ||
         cudaMemset(h->status_dev, 0, 4 * sizeof(int32_t)) != cudaSuccess) {
         delete h;
@@ -207,6 +217,10 @@ int qgemv_init(const qgemv_config* cfg, qgemv_handle** out) {
 int qgemv_destroy(qgemv_handle* h) {
     if (!h) return QGEMV_ERR_INVALID_ARG;
     cudaSetDevice(h->cfg.device);
+    for (int i = 0; i < h->tp_world; ++i)
+        if (i != h->tp_rank && h->tp_peer[i]) cudaIpcCloseMemHandle(h->tp_peer[i]);
+    cudaFree(h->tp_local);
+    cudaFree(h->tp_epochs);
     cudaFree(h->status_dev);
     delete h;
     return QGEMV_OK;
@@ -396,6 +410,69 @@ int qgemv_last_device_status(qgemv_handle* h, void* stream, qgemv_dev_status* ou
     return QGEMV_OK;
 }
 
+
+// ---- tensor-parallel exchange over peer memory ------------------------------------------------
+int qgemv_tp_create(qgemv_handle* h, int rank, int world, int64_t max_elems, void* ipc_handle_out) {
+    if (!h || !ipc_handle_out || world < 1 || world > qg::kTpMaxWorld || rank < 0 || rank >= world)
+        return QGEMV_ERR_INVALID_ARG;
+    if (max_elems < 4 || h->tp_local) return QGEMV_ERR_INVALID_ARG;
+    QG_CUDA(cudaSetDevice(h->cfg.device));
+    max_elems = (max_elems + 3) / 4 * 4;
+    const size_t bytes = qg::tp_buffer_bytes(world, max_elems);
+    QG_CUDA(cudaMalloc(&h->tp_local, bytes));
+    QG_CUDA(cudaMemset(h->tp_local, 0, bytes));
+    QG_CUDA(cudaMalloc(&h->tp_epochs, qg::kTpCtas * 4));
+    QG_CUDA(cudaMemset(h->tp_epochs, 0, qg::kTpCtas * 4));
+    QG_CUDA(cudaDeviceSynchronize());
+    cudaIpcMemHandle_t mh;
+    QG_CUDA(cudaIpcGetMemHandle(&mh, h->tp_local));
+    static_assert(sizeof(cudaIpcMemHandle_t) == QGEMV_IPC_HANDLE_BYTES, "IPC handle size");
+    std::memcpy(ipc_handle_out, &mh, sizeof mh);
+    h->tp_rank = rank;
+    h->tp_world = world;
+    h->tp_max_elems = max_elems;
+    h->tp_peer[rank] = h->tp_local;
+    return QGEMV_OK;
+}
+
+int qgemv_tp_connect(qgemv_handle* h, const void* all_handles) {
+    if (!h || !all_handles || !h->tp_local) return QGEMV_ERR_INVALID_ARG;
+    QG_CUDA(cudaSetDevice(h->cfg.device));
+    const uint8_t* src = static_cast<const uint8_t*>(all_handles);
+    for (int r = 0; r < h->tp_world; ++r) {
+        if (r == h->tp_rank) continue;
+        cudaIpcMemHandle_t mh;
+        std::memcpy(&mh, src + size_t(r) * QGEMV_IPC_HANDLE_BYTES, sizeof mh);
+        void* p = nullptr;
+        QG_CUDA(cudaIpcOpenMemHandle(&p, mh, cudaIpcMemLazyEnablePeerAccess));
+        h->tp_peer[r] = static_cast<uint8_t*>(p);
+    }
+    return QGEMV_OK;
+}
+
+int qgemv_tp_allreduce(qgemv_handle* h, void* y, int y_dtype, int64_t n, void* stream) {
+    if (!h || !y || n < 1) return QGEMV_ERR_INVALID_ARG;
+    if (!h->tp_local) return QGEMV_ERR_INVALID_ARG;
+    if (n > h->tp_max_elems) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+    if (y_dtype != QGEMV_OUT_BF16 && y_dtype != QGEMV_OUT_F32) return QGEMV_ERR_INVALID_ARG;
+    for (int r = 0; r < h->tp_world; ++r)
+        if (!h->tp_peer[r]) return QGEMV_ERR_INVALID_ARG;  // qgemv_tp_connect has not run
+    qg::TpParams P;
+    std::memset(&P, 0, sizeof P);
+    for (int r = 0; r < h->tp_world; ++r) P.buf[r] = h->tp_peer[r];
+    P.rank = h->tp_rank;
+    P.world = h->tp_world;
+    P.max_elems = h->tp_max_elems;
+    P.y = y;
+    P.y_dtype = y_dtype;
+    P.n = n;
+    P.epochs = h->tp_epochs;
+    P.status = h->status_dev;
+    P.spin_limit = default_spin(h);
+    const cudaError_t err = launch(h, qg::tp_allreduce_kernel, dim3(qg::kTpCtas), dim3(qg::kTpThreads), 0,
+                                   static_cast<cudaStream_t>(stream), P);
+    return err == cudaSuccess ? QGEMV_OK : QGEMV_ERR_CUDA;
+}
 
 // ---- allocation-free GEMV ----------------------------------------------------------------------
 // Some callers may not allocate device memory at the moment they need a projection: code running

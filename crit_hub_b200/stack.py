@@ -31,8 +31,11 @@ class LayerStack:
     """Owns an activation arena [sum B*K] bf16 and an output arena [sum B*N]; one GEMV per weight."""
 
     def __init__(self, handle: QGemv, weights: list[Weight], batch: int, out_dtype: int = OUT_BF16,
-                 device: int = 0, prefetch_next: bool = True):
+                 device: int = 0, prefetch_next: bool = True, after_call=None):
         self.handle, self.batch, self.out_dtype = handle, batch, out_dtype
+        # after_call(i): optional hook enqueued on the same stream right after GEMV i (and captured
+        # with it), e.g. the all-reduce of a row-parallel projection's partial outputs
+        self.after_call = after_call
         self.prefetch_next = prefetch_next  # name the following matrix in every call (L2 prefetch)
         self.device = torch.device("cuda", device)
         self.calls: list[_Call] = []
@@ -80,6 +83,8 @@ class LayerStack:
             nxt = self.calls[(i + 1) % n].weight if self.prefetch_next and n > 1 else None
             self.handle.gemv(c.weight, xb + c.x_off * xe, self.batch, yb + c.y_off * ye, self.out_dtype,
                              stream_handle, next_weight=nxt)
+            if self.after_call is not None:
+                self.after_call(i)
 
     def capture(self) -> None:
         """Run once eagerly (loads modules, warms caches), then capture the stack into a graph."""

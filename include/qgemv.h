@@ -144,6 +144,22 @@ int qgemv_gemv(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, int B
 int qgemv_gemv_prefetch(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, int B, void* y,
                         int y_dtype, const qgemv_weight* next, void* stream);
 
+/* ---- tensor-parallel exchange -------------------------------------------------------------------
+ * Not in the registry (every listed engine runs on one GPU, engines/crit-labs/mtp5-nvfp4-drafts/
+ * card.yaml:100); needed for the row-parallel projections (o, down) of a model sharded over the
+ * GPUs of one node.  One process per GPU.  qgemv_tp_create allocates this rank's exchange buffer
+ * and returns its CUDA IPC handle (QGEMV_IPC_HANDLE_BYTES); the caller gathers the handles of all
+ * ranks (any transport) and passes the concatenation, rank order, to qgemv_tp_connect.
+ * qgemv_tp_allreduce then sums a vector of n <= max_elems elements over the ranks in place
+ * (fp32 accumulation in rank order: every rank gets the same bits): every rank pushes its partial
+ * into its slot of every rank's buffer over NVLink, flags it, waits -- bounded -- for the flags
+ * in its own buffer and reduces locally.  Asynchronous on `stream`, graph-capturable; all ranks
+ * must issue the same sequence of calls. */
+#define QGEMV_IPC_HANDLE_BYTES 64
+int qgemv_tp_create(qgemv_handle* h, int rank, int world, int64_t max_elems, void* ipc_handle_out);
+int qgemv_tp_connect(qgemv_handle* h, const void* all_handles);
+int qgemv_tp_allreduce(qgemv_handle* h, void* y, int y_dtype, int64_t n, void* stream);
+
 /* ---- allocation-free GEMV --------------------------------------------------------------------
  * No counterpart in the crit-hub registry; added for callers that cannot allocate device memory
  * when they need a projection: code living inside a memory pool that owns the whole GPU, plugins

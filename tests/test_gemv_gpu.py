@@ -268,3 +268,85 @@ def test_moe_gemv(qg, handle, T, per_slot):
     yref = np.einsum("tj,tjn->tn", wts.astype(np.float64), ref.reshape(T, topk, N))
     assert O.rel_l2(y.cpu().numpy(), yref) < TOL_F32
     w.unload()
+
+
+# ---- tensor-parallel exchange ----------------------------------------------------------------------
+def test_tp_allreduce_single_rank(qg):
+    """World of one: the exchange degenerates to push-to-self, flag, reduce; replaying it checks
+    the device-side epochs and the two parities."""
+    import torch
+    h = qg.QGemv(device=0)
+    handle_bytes = h.tp_create(0, 1, 4096)
+    h.tp_connect(handle_bytes.reshape(1, 64))
+    y = torch.randn(1000, device="cuda", dtype=torch.float32)
+    ref = y.clone()
+    for _ in range(5):
+        h.tp_allreduce(y.data_ptr(), qg.OUT_F32, y.numel())
+    torch.cuda.synchronize()
+    assert h.device_status().code == 0
+    assert torch.equal(y, ref)
+    yb = torch.randn(777, device="cuda").bfloat16()
+    refb = yb.clone()
+    h.tp_allreduce(yb.data_ptr(), qg.OUT_BF16, yb.numel())
+    torch.cuda.synchronize()
+    assert torch.equal(yb, refb)
+    with pytest.raises(qg.QgemvError):
+        h.tp_allreduce(y.data_ptr(), qg.OUT_F32, 5000)  # above max_elems
+    h.close()
+
+
+def _tp_worker(rank, world, port, q):
+    import os
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    import crit_hub_b200 as qg
+    from oracle import oracle as O
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        N, K, B = 512, 4096, 2
+        codes, scales, ts = O.make_nvfp4(N, K, seed=9)
+        x = O.make_x(B, K, seed=9)
+        h = qg.QGemv(device=rank)
+        mine = torch.from_numpy(h.tp_create(rank, world, B * N))
+        gathered = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(gathered, mine)
+        h.tp_connect(torch.stack(gathered).numpy())
+        dist.barrier()
+        # row-parallel shard: this rank owns K/world input columns
+        k0, k1 = rank * K // world, (rank + 1) * K // world
+        w = h.load(qg.pack(qg.FMT_NVFP4, codes, scales, ts, shard=qg.Shard(0, N, k0, k1)))
+        xd = torch.from_numpy(np.ascontiguousarray(x[:, k0:k1]).view(np.int16)).cuda()
+        y = torch.empty((B, N), dtype=torch.float32, device="cuda")
+        for _ in range(3):
+            h.gemv(w, xd.data_ptr(), B, y.data_ptr(), qg.OUT_F32)
+            h.tp_allreduce(y.data_ptr(), qg.OUT_F32, y.numel())
+        torch.cuda.synchronize()
+        st = h.device_status()
+        err = O.rel_l2(y.cpu().numpy(), O.gemv_nvfp4_f64(codes, scales, ts, x))
+        q.put((rank, st.code, err, y.cpu().numpy().tobytes()))
+        dist.barrier()  # leave only between steps, nothing in flight
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tp_allreduce_two_gpus(qg):
+    """Row-parallel GEMV on two GPUs + peer-memory all-reduce equals the unsharded oracle, and
+    both ranks hold the same bits."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_tp_worker, args=(r, 2, 29533, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=60)
+    assert all(r[1] == 0 for r in res)
+    assert all(r[2] < TOL_F32 for r in res)
+    assert res[0][3] == res[1][3]
