@@ -19,6 +19,7 @@ FMT_NVFP4 = 1
 FMT_FP8 = 2
 OUT_BF16 = 0
 OUT_F32 = 1
+ACT_A16_EXACT = 0
 MAX_BATCH = 8
 
 ERR_INVALID_ARG = -1
@@ -94,6 +95,7 @@ def _load() -> C.CDLL:
     L.qgemv_weight_bytes.argtypes = [vp]
     L.qgemv_gemv.argtypes = [vp, vp, vp, i32, vp, i32, vp]
     L.qgemv_gemv_prefetch.argtypes = [vp, vp, vp, i32, vp, i32, vp, vp]
+    L.qgemv_gemm_skinny.argtypes = [vp, vp, vp, i32, vp, i32, i32, vp]
     L.qgemv_tp_create.argtypes = [vp, i32, i32, i64, vp]
     L.qgemv_tp_connect.argtypes = [vp, vp]
     L.qgemv_tp_allreduce.argtypes = [vp, vp, i32, i64, vp]
@@ -245,6 +247,12 @@ class QGemv:
         else:
             _check(_load().qgemv_gemv_prefetch(self._ptr, w._ptr, x_ptr, B, y_ptr, y_dtype, next_weight._ptr,
                                                stream), "gemv")
+
+    def gemm_skinny(self, w: Weight, x_ptr: int, M: int, y_ptr: int, y_dtype: int = OUT_BF16,
+                    act_mode: int = ACT_A16_EXACT, stream: int = 0) -> None:
+        """Y[M][N] = X[M][K] dequant(W)^T on the tcgen05 tensor cores, M = 16..256 (multiple of 16)."""
+        _check(_load().qgemv_gemm_skinny(self._ptr, w._ptr, x_ptr, M, y_ptr, y_dtype, act_mode, stream),
+               "gemm_skinny")
 
     def moe_gemv(self, experts: Weight, expert_ids_ptr: int, x_ptr: int, T: int, topk: int,
                  per_slot_input: bool, out_ptr: int, out_dtype: int = OUT_F32, stream: int = 0) -> None:

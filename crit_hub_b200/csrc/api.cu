@@ -12,6 +12,7 @@
 #include "aux_kernels.cuh"
 #include "gemv_kernel.cuh"
 #include "gemv_stream.cuh"
+#include "gemm_skinny.cuh"
 #include "moe_stream.cuh"
 #include "tp_allreduce.cuh"
 #include "qgemv_layout.h"
@@ -28,6 +29,9 @@ struct qgemv_handle {
     uint8_t* tp_local;                     // this rank's exchange buffer
     uint8_t* tp_peer[qg::kTpMaxWorld];     // every rank's buffer as mapped here (tp_peer[rank] == tp_local)
     uint32_t* tp_epochs;
+    // skinny GEMM: f16 activation tiles + per-row exponents, grown on demand
+    uint8_t* gs_ws;
+    size_t gs_ws_bytes;
 };
 
 struct qgemv_weight {
@@ -188,6 +192,7 @@ int qgemv_init(const qgemv_config* cfg, qgemv_handle** out) {
     h->tp_rank = 0, h->tp_world = 0, h->tp_max_elems = 0;
     h->tp_local = nullptr, h->tp_epochs = nullptr;
     for (int i = 0; i < qg::kTpMaxWorld; ++i) h->tp_peer[i] = nullptr;
+    h->gs_ws = nullptr, h->gs_ws_bytes = 0;
     if (cudaMalloc(&h->status_dev, 4 * sizeof(int32_t)) != cudaSuccess ||
         cudaMemset(h->status_dev, 0, 4 * sizeof(int32_t)) != cudaSuccess) {
         delete h;
@@ -205,7 +210,9 @@ int qgemv_init(const qgemv_config* cfg, qgemv_handle** out) {
         cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_NVFP4, true, 1>, dyn, qg::SSmem::total<QGEMV_FMT_NVFP4>()) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_NVFP4, false, 1>, dyn, qg::SSmem::total<QGEMV_FMT_NVFP4>()) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8, true, 1>, dyn, qg::SSmem::total<QGEMV_FMT_FP8>()) != cudaSuccess ||
-        cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8, false, 1>, dyn, qg::SSmem::total<QGEMV_FMT_FP8>()) != cudaSuccess) {
+        cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8, false, 1>, dyn, qg::SSmem::total<QGEMV_FMT_FP8>()) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemm_skinny_kernel<QGEMV_FMT_NVFP4>, dyn, qg::GsSmem::total(QG_NVFP4_UNIT_BYTES, qg::kGsMaxM)) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemm_skinny_kernel<QGEMV_FMT_FP8>, dyn, qg::GsSmem::total(QG_FP8_UNIT_BYTES, qg::kGsMaxM)) != cudaSuccess) {
         cudaFree(h->status_dev);
         delete h;
         return QGEMV_ERR_CUDA;
@@ -221,6 +228,7 @@ int qgemv_destroy(qgemv_handle* h) {
         if (i != h->tp_rank && h->tp_peer[i]) cudaIpcCloseMemHandle(h->tp_peer[i]);
     cudaFree(h->tp_local);
     cudaFree(h->tp_epochs);
+    cudaFree(h->gs_ws);
     cudaFree(h->status_dev);
     delete h;
     return QGEMV_OK;
@@ -331,6 +339,57 @@ int qgemv_gemv_prefetch(qgemv_handle* h, const qgemv_weight* w, const void* x_bf
         P.pf_bytes = next->payload_bytes;
     }
     return launch_gemv(h, w, P, static_cast<cudaStream_t>(stream));
+}
+
+int qgemv_gemm_skinny(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, int M, void* y,
+                      int y_dtype, int act_mode, void* stream) {
+    if (!h || !w || !x_bf16 || !y) return QGEMV_ERR_INVALID_ARG;
+    if (act_mode != QGEMV_ACT_A16_EXACT) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+    if (y_dtype != QGEMV_OUT_BF16 && y_dtype != QGEMV_OUT_F32) return QGEMV_ERR_INVALID_ARG;
+    if ((reinterpret_cast<uintptr_t>(x_bf16) & 15u) != 0) return QGEMV_ERR_INVALID_ARG;
+    if (M < 16 || M > qg::kGsMaxM || M % 16 != 0) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+    if (w->n_stack != 1 || w->N % 128 != 0 || w->K % 64 != 0) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    QG_CUDA(cudaSetDevice(h->cfg.device));
+    const size_t xt_bytes = size_t(M) * size_t(w->K) * 2;
+    const size_t need = xt_bytes + size_t(qg::kGsMaxM) * 4;
+    if (need > h->gs_ws_bytes) {
+        // growing the activation scratch synchronises; it happens on the first call of a new
+        // largest (M, K) only and must not fall inside a stream capture
+        QG_CUDA(cudaDeviceSynchronize());
+        cudaFree(h->gs_ws);
+        h->gs_ws = nullptr, h->gs_ws_bytes = 0;
+        QG_CUDA(cudaMalloc(&h->gs_ws, need));
+        h->gs_ws_bytes = need;
+    }
+    uint8_t* xt = h->gs_ws;
+    int32_t* xexp = reinterpret_cast<int32_t*>(h->gs_ws + (h->gs_ws_bytes - size_t(qg::kGsMaxM) * 4));
+    if (launch(h, qg::x_prep_kernel, dim3(M), dim3(256), 0, st, static_cast<const uint16_t*>(x_bf16), M,
+               int(w->K), xt, xexp) != cudaSuccess)
+        return QGEMV_ERR_CUDA;
+    qg::GsParams P;
+    std::memset(&P, 0, sizeof P);
+    P.payload = w->dev_blob + QG_HEADER_BYTES + w->aux_bytes;
+    P.chan_scale = reinterpret_cast<const float*>(w->dev_blob + QG_HEADER_BYTES);
+    P.tensor_scale = w->host_tensor_scale[0];
+    P.xt = xt;
+    P.xexp = xexp;
+    P.y = y;
+    P.y_dtype = y_dtype;
+    P.N = int32_t(w->N), P.K = int32_t(w->K), P.M = M;
+    P.units = int32_t(w->units);
+    P.status = h->status_dev;
+    P.spin_limit = default_spin(h);
+    P.debug = h->cfg.debug;
+    const dim3 grid(unsigned(w->N / 128)), block(qg::kGsThreads);
+    cudaError_t err;
+    if (w->fmt == QGEMV_FMT_NVFP4)
+        err = launch(h, qg::gemm_skinny_kernel<QGEMV_FMT_NVFP4>, grid, block,
+                     size_t(qg::GsSmem::total(QG_NVFP4_UNIT_BYTES, M)), st, P);
+    else
+        err = launch(h, qg::gemm_skinny_kernel<QGEMV_FMT_FP8>, grid, block,
+                     size_t(qg::GsSmem::total(QG_FP8_UNIT_BYTES, M)), st, P);
+    return err == cudaSuccess ? QGEMV_OK : QGEMV_ERR_CUDA;
 }
 
 int qgemv_moe_gemv(qgemv_handle* h, const qgemv_weight* experts, const int32_t* expert_ids,

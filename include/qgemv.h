@@ -181,6 +181,27 @@ int qgemv_tp_allreduce(qgemv_handle* h, void* y, int y_dtype, int64_t n, void* s
 int qgemv_gemv_noalloc(const void* dev_blob, const void* host_header, const void* x_bf16, int B, void* y,
                        int y_dtype, void* stream);
 
+/* ---- skinny GEMM / short prefill -------------------------------------------------------------------
+ * Y[M][N] = X[M][K] . dequant(W)^T for M = 16 .. 256 tokens (a multiple of 16) on the tcgen05
+ * tensor cores with fp32 accumulators in tensor memory.  Replaces the engines' prompt GEMM
+ * ("pinned-gemm ... about 40% of the GPU's FP4 rate",
+ * engines/crit-labs/mtp5-nvfp4-drafts/card.yaml:77,95; cuBLASLt NVFP4 / torch._scaled_mm FP8
+ * prefill GEMMs, tools/fixtures/engines/crit-labs/mtp4-nvfp4-mma/card.yaml:77).
+ * x: device bf16 [M][K], 16-byte aligned; y: device [M][N] bf16 or fp32.
+ * act_mode QGEMV_ACT_A16_EXACT: weights are dequantised exactly to f16 tiles, activations stay
+ * 16-bit (bf16 -> f16 with an exact per-row power-of-two scale), kind::f16 MMA: same 2e-3 bound
+ * as the GEMV.  The block-scaled FP4 / FP8-activation modes quantise the activations and are a
+ * different operator; they return QGEMV_ERR_UNSUPPORTED_SHAPE.
+ * Shapes: single (unstacked) weight, N a multiple of 128, K a multiple of 64.
+ * The call keeps an internal f16 copy of the activations (M*K*2 bytes); the first call with a
+ * new largest M*K grows it with cudaMalloc after a device synchronise -- make that call outside
+ * stream capture.  Two launches per call (activation preparation, GEMM). */
+#define QGEMV_ACT_A16_EXACT 0
+#define QGEMV_ACT_A4_BLOCKSCALED 1
+#define QGEMV_ACT_A8 2
+int qgemv_gemm_skinny(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, int M, void* y,
+                      int y_dtype, int act_mode, void* stream);
+
 /* ---- MoE grouped GEMV ---------------------------------------------------------------------------
  * One launch walks the router's top-k lists.  For every token t and slot j:
  *   out[t*topk + j][:] = W[expert_ids[t][j]] . x[row][:],
