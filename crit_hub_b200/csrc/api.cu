@@ -2,6 +2,7 @@
 // Host code only decides shapes and launch attributes; there is no CPU compute path.
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
@@ -65,6 +66,7 @@ thread_local cudaError_t g_last_cuda_error = cudaSuccess;
     } while (0)
 
 constexpr int kMaxMoeSlots = 4096;
+constexpr int kGsMaxTiles = 4096;  // skinny GEMM: 128-row tiles a handle keeps counters for
 
 int64_t default_spin(const qgemv_handle* h) {
     return h->cfg.spin_limit > 0 ? h->cfg.spin_limit : (int64_t(1) << 26);
@@ -211,8 +213,8 @@ int qgemv_init(const qgemv_config* cfg, qgemv_handle** out) {
         cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_NVFP4, false, 1>, dyn, qg::SSmem::total<QGEMV_FMT_NVFP4>()) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8, true, 1>, dyn, qg::SSmem::total<QGEMV_FMT_FP8>()) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8, false, 1>, dyn, qg::SSmem::total<QGEMV_FMT_FP8>()) != cudaSuccess ||
-        cudaFuncSetAttribute(qg::gemm_skinny_kernel<QGEMV_FMT_NVFP4>, dyn, qg::GsSmem::total(QG_NVFP4_UNIT_BYTES, qg::kGsMaxM)) != cudaSuccess ||
-        cudaFuncSetAttribute(qg::gemm_skinny_kernel<QGEMV_FMT_FP8>, dyn, qg::GsSmem::total(QG_FP8_UNIT_BYTES, qg::kGsMaxM)) != cudaSuccess) {
+        cudaFuncSetAttribute(qg::gemm_skinny_kernel<QGEMV_FMT_NVFP4>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemm_skinny_kernel<QGEMV_FMT_FP8>, dyn, qg::kGsSmemBudget) != cudaSuccess) {
         cudaFree(h->status_dev);
         delete h;
         return QGEMV_ERR_CUDA;
@@ -351,22 +353,35 @@ int qgemv_gemm_skinny(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16
     if (w->n_stack != 1 || w->N % 128 != 0 || w->K % 64 != 0) return QGEMV_ERR_UNSUPPORTED_SHAPE;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     QG_CUDA(cudaSetDevice(h->cfg.device));
-    const size_t xt_bytes = size_t(M) * size_t(w->K) * 2;
-    const size_t need = xt_bytes + size_t(qg::kGsMaxM) * 4;
+    const int tiles = int(w->N / 128);
+    if (tiles > kGsMaxTiles) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+    const int run_log2 = w->units % 4 == 0 ? 2 : (w->units % 2 == 0 ? 1 : 0);
+    const int64_t total = int64_t(tiles) * (w->units >> run_log2);  // work items: runs of units
+    const int grid = int(std::min<int64_t>(gemv_grid(h), total));
+    // scratch: [tile counters, fixed place][row exponents][f16 activation tiles][partial tiles]
+    const size_t cnt_bytes = size_t(kGsMaxTiles) * 16 * sizeof(int32_t);
+    const size_t exp_bytes = size_t(qg::kGsMaxM) * 4;
+    const size_t xt_bytes = ((size_t(M) * size_t(w->K) * 2 + 255) / 256) * 256;
+    const size_t ws_bytes = size_t(2) * grid * size_t(M) * 128 * sizeof(float);
+    const size_t need = cnt_bytes + exp_bytes + xt_bytes + ws_bytes;
     if (need > h->gs_ws_bytes) {
-        // growing the activation scratch synchronises; it happens on the first call of a new
-        // largest (M, K) only and must not fall inside a stream capture
+        // growing the scratch synchronises; it happens on the first call of a new largest shape
+        // only and must not fall inside a stream capture
         QG_CUDA(cudaDeviceSynchronize());
         cudaFree(h->gs_ws);
         h->gs_ws = nullptr, h->gs_ws_bytes = 0;
         QG_CUDA(cudaMalloc(&h->gs_ws, need));
+        QG_CUDA(cudaMemset(h->gs_ws, 0, cnt_bytes));
         h->gs_ws_bytes = need;
     }
-    uint8_t* xt = h->gs_ws;
-    int32_t* xexp = reinterpret_cast<int32_t*>(h->gs_ws + (h->gs_ws_bytes - size_t(qg::kGsMaxM) * 4));
-    if (launch(h, qg::x_prep_kernel, dim3(M), dim3(256), 0, st, static_cast<const uint16_t*>(x_bf16), M,
-               int(w->K), xt, xexp) != cudaSuccess)
+    int32_t* counters = reinterpret_cast<int32_t*>(h->gs_ws);
+    int32_t* xexp = reinterpret_cast<int32_t*>(h->gs_ws + cnt_bytes);
+    uint8_t* xt = h->gs_ws + cnt_bytes + exp_bytes;
+    float* ws = reinterpret_cast<float*>(xt + xt_bytes);
+    if (launch(h, qg::x_prep_kernel, dim3(M), dim3(qg::kXPrepThreads), 0, st,
+               static_cast<const uint16_t*>(x_bf16), M, int(w->K), xt, xexp) != cudaSuccess)
         return QGEMV_ERR_CUDA;
+    const int unit_bytes = w->fmt == QGEMV_FMT_NVFP4 ? QG_NVFP4_UNIT_BYTES : QG_FP8_UNIT_BYTES;
     qg::GsParams P;
     std::memset(&P, 0, sizeof P);
     P.payload = w->dev_blob + QG_HEADER_BYTES + w->aux_bytes;
@@ -375,20 +390,22 @@ int qgemv_gemm_skinny(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16
     P.xt = xt;
     P.xexp = xexp;
     P.y = y;
+    P.ws = ws;
+    P.counters = counters;
     P.y_dtype = y_dtype;
     P.N = int32_t(w->N), P.K = int32_t(w->K), P.M = M;
     P.units = int32_t(w->units);
+    P.tiles = tiles;
+    P.x_stages = qg::GsSmem::x_stages(unit_bytes, M);
+    P.run_log2 = run_log2;
     P.status = h->status_dev;
     P.spin_limit = default_spin(h);
     P.debug = h->cfg.debug;
-    const dim3 grid(unsigned(w->N / 128)), block(qg::kGsThreads);
-    cudaError_t err;
-    if (w->fmt == QGEMV_FMT_NVFP4)
-        err = launch(h, qg::gemm_skinny_kernel<QGEMV_FMT_NVFP4>, grid, block,
-                     size_t(qg::GsSmem::total(QG_NVFP4_UNIT_BYTES, M)), st, P);
-    else
-        err = launch(h, qg::gemm_skinny_kernel<QGEMV_FMT_FP8>, grid, block,
-                     size_t(qg::GsSmem::total(QG_FP8_UNIT_BYTES, M)), st, P);
+    const size_t smem = size_t(qg::GsSmem::total(unit_bytes, M));
+    const dim3 g(static_cast<unsigned>(grid)), block(qg::kGsThreads);
+    const cudaError_t err = w->fmt == QGEMV_FMT_NVFP4
+                                ? launch(h, qg::gemm_skinny_kernel<QGEMV_FMT_NVFP4>, g, block, smem, st, P)
+                                : launch(h, qg::gemm_skinny_kernel<QGEMV_FMT_FP8>, g, block, smem, st, P);
     return err == cudaSuccess ? QGEMV_OK : QGEMV_ERR_CUDA;
 }
 

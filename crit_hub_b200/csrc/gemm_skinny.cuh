@@ -1,23 +1,38 @@
-// Skinny GEMM / short prefill on the 5th-generation tensor cores (tcgen05, TMEM accumulators):
+// Skinny GEMM / short prefill on the 5th-generation tensor cores (tcgen05, TMEM):
 //     Y[M][N] = X[M][K] * dequant(W)^T,   M = 16 .. 256 tokens (multiple of 16).
 //
-// "W4A16-exact" variant: the packed NVFP4 / FP8 weights are dequantised to f16 tiles in shared
-// memory (the f16 value of code * block scale is exact) and multiplied with f16 activations by
-// tcgen05.mma kind::f16 with fp32 accumulators in tensor memory.  Activations are converted
-// bf16 -> f16 once per call by x_prep_kernel, scaled per token row by a power of two exactly as
-// in the GEMV kernels, and laid out in the MMA's canonical K-major tile order so that one bulk
-// copy brings a whole [M x 64] tile.  (The block-scaled kinds, mxf4nvf4 / f8f6f4, need FP4 / FP8
-// activations and cannot meet a 2e-3 bound against unquantised activations; they are a different
-// operator and are not what this kernel computes.)
+// "W4A16-exact" variant: the packed NVFP4 / FP8 weights are dequantised to f16 (the f16 value of
+// code * block scale is exact) and multiplied with f16 activations by tcgen05.mma kind::f16 with
+// fp32 accumulators in tensor memory.  Activations are converted bf16 -> f16 once per call by
+// x_prep_kernel, scaled per token row by a power of two exactly as in the GEMV kernels.  (The
+// block-scaled kinds, mxf4nvf4 / f8f6f4, need FP4 / FP8 activations and cannot meet a 2e-3 bound
+// against unquantised activations; they are a different operator.)
 //
-// One CTA per 128 weight rows (8 panels); MMA shape M=128 (weight rows) x N=M_tokens x K=16, four
-// MMAs per 64-wide K step.  Warp roles:
-//   warps 0-3  dequantise the 8 panels of a stage into the canonical A tile (no swizzle: core
-//              matrices of 8 rows x 16 bytes), then fence the async proxy and signal; at the end
-//              they read the accumulator from TMEM (each warp its 32 lanes) and store Y
-//   warp 4     one thread issues the bulk (TMA) copies: 8 x 576 (or 1024) bytes of packed weights
-//              and one activation tile per stage
-//   warp 5     allocates TMEM; one thread issues tcgen05.mma and commits to the stage's mbarrier
+// MMA shape: M = 128 weight rows (8 panels) x N = M_tokens x K = 16; a unit (64 K) is four MMAs.
+//   A operand (weights)  lives in TENSOR MEMORY: the packed unit is ordered as mma.m16n8k16
+//       fragments, and the register quadruple of one fragment is exactly what
+//       tcgen05.st.16x256b wants for a 16-row x 16-k slab, so a dequantising warp converts
+//       (cvt + one f16x2 multiply per register) and stores a whole unit with one tcgen05.st.x4:
+//       no shuffles, no shared-memory round trip.  The slab's k order is the packed layout's
+//       permutation (slot s = 4t + 2r + h); x_prep_kernel writes the activations in the same order.
+//   B operand (activations) is read from shared memory through a K-major no-swizzle descriptor
+//       (core matrix = 8 token rows x 16 bytes); x_prep_kernel lays the tiles out in that order
+//       so one bulk copy brings a whole [M x 64] tile.
+//   D (fp32) occupies TMEM columns [0, M); the A ring occupies six 32-column stages at the end of the allocation.
+//
+// Work split: the linear space (row tile, unit) is cut evenly over the CTAs (one per SM); a CTA's
+// range is a sequence of segments, each a K range of one row tile.  A segment that covers its
+// whole tile stores Y directly; otherwise the fp32 partial goes to a workspace slot and the last
+// contributor of the tile (atomic counter) adds all parts in CTA order -- deterministic.
+//
+// Warp roles (15 warps):
+//   0-11 three dequantising warpgroups; group q = warp / 4 takes the CTA's steps i = q (mod 3), so the
+//        latency of one step's conversion, tcgen05.st and barrier round trips overlaps the other
+//        groups' steps.  Warp w handles panels 2(w%4), 2(w%4)+1 = TMEM lanes 32(w%4)..+31 (the lane
+//        quarter a warp may access), and in the epilogue the same lanes of every third 8-column chunk
+//   12   one thread issues the bulk copies of packed weights (ring of 8 stages)
+//   13   allocates TMEM; one thread issues tcgen05.mma and the commits that free ring stages
+//   14   one thread issues the bulk copies of activation tiles (ring sized to what is left)
 // Every wait is bounded; TMEM is always released before the CTA exits.
 #pragma once
 #include <cuda_bf16.h>
@@ -27,41 +42,60 @@
 
 namespace qg {
 
-constexpr int kGsStages = 3;
-constexpr int kGsThreads = 192;          // 6 warps
-constexpr int kGsATileBytes = 128 * 128; // 128 rows x 64 f16
+constexpr int kGsGroups = 3;     // dequantising warpgroups; group q takes the CTA's steps i = q (mod 3)
+constexpr int kGsDqWarps = 4 * kGsGroups;
+constexpr int kGsWarpP = kGsDqWarps, kGsWarpMma = kGsDqWarps + 1, kGsWarpX = kGsDqWarps + 2;
+constexpr int kGsThreads = 32 * (kGsDqWarps + 3);
 constexpr int kGsMaxM = 256;
+constexpr int kGsRunMax = 4;     // units of one panel fetched by one bulk copy (a run)
+constexpr int kGsPStagesMax = 4; // packed-weight ring: stages of 8 panels x one run
+constexpr int kGsAStages = 6;    // dequantised-weight ring in TMEM (32 columns each)
+constexpr int kGsXStagesMax = 8;
+constexpr int kGsSmemBudget = 227 * 1024;
 
 struct GsParams {
     const uint8_t* payload;   // packed weight
     const float* chan_scale;  // FP8 channel scales
     float tensor_scale;
-    const uint8_t* xt;        // f16 activation tiles: [units][M/8][8 k-chunks][8 rows][8 elems]
+    const uint8_t* xt;        // f16 activation tiles: [units][M/8][8 chunks][8 rows][8 slots]
     const int32_t* xexp;      // per token row: exponent E (x was scaled by 2^-E)
     void* y;                  // [M][N]
+    float* ws;                // partial tiles: slot (2*cta + which) of [M][128] fp32
+    int32_t* counters;        // per row tile, zero between launches
     int32_t y_dtype;
     int32_t N, K, M;
     int32_t units;            // K / 64
+    int32_t tiles;            // N / 128
+    int32_t x_stages;
+    int32_t run_log2;         // log2(units per run): 2, 1 or 0, the largest that divides K / 64
     int32_t* status;
     int64_t spin_limit;
     int32_t debug;
 };
 
 struct GsSmem {
-    static constexpr int kBarFull = 0;     // kGsStages
-    static constexpr int kBarAReady = 32;  // kGsStages
-    static constexpr int kBarEmpty = 64;   // kGsStages
-    static constexpr int kBarDone = 96;
-    static constexpr int kTmemPtr = 104;
-    static constexpr int kAbort = 108;
-    static constexpr int kStage0 = 1024;
-    // stage: [packed weights 8 panels][activation tile M*128][A tile 16 KB]
-    __host__ __device__ static constexpr int packed_bytes(int unit_bytes) { return 8 * unit_bytes; }
-    __host__ __device__ static constexpr int stage_bytes(int unit_bytes, int M) {
-        return ((packed_bytes(unit_bytes) + 1023) / 1024) * 1024 + M * 128 + kGsATileBytes;
+    static constexpr int kBarPFull = 0;      // kGsPStagesMax
+    static constexpr int kBarPEmpty = 64;    // kGsPStagesMax
+    static constexpr int kBarXFull = 128;    // kGsXStagesMax
+    static constexpr int kBarXEmpty = 192;   // kGsXStagesMax
+    static constexpr int kBarAReady = 256;   // kGsAStages
+    static constexpr int kBarAEmpty = 304;   // kGsAStages
+    static constexpr int kBarDone = 352;
+    static constexpr int kBarDFree = 360;
+    static constexpr int kTmemPtr = 368;
+    static constexpr int kAbort = 372;
+    static constexpr int kBarDrain = 376;
+    static constexpr int kRing0 = 1024;
+    __host__ __device__ static constexpr int packed_stage(int unit_bytes) { return 8 * kGsRunMax * unit_bytes; }
+    // four stages of NVFP4 runs (72 KB), three of FP8 (96 KB)
+    __host__ __device__ static constexpr int p_stages(int unit_bytes) { return unit_bytes > 600 ? 3 : kGsPStagesMax; }
+    __host__ __device__ static constexpr int x_off(int unit_bytes) { return kRing0 + p_stages(unit_bytes) * packed_stage(unit_bytes); }
+    __host__ __device__ static int x_stages(int unit_bytes, int M) {
+        const int n = (kGsSmemBudget - x_off(unit_bytes)) / (M * 128);
+        return n > kGsXStagesMax ? kGsXStagesMax : n;
     }
-    __host__ __device__ static constexpr int total(int unit_bytes, int M) {
-        return kStage0 + kGsStages * stage_bytes(unit_bytes, M);
+    __host__ __device__ static int total(int unit_bytes, int M) {
+        return x_off(unit_bytes) + x_stages(unit_bytes, M) * M * 128;
     }
 };
 
@@ -79,12 +113,13 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                           uint32_t accumulate) {
+// D[tmem] (+)= A[tmem] * B[smem descriptor]
+__device__ __forceinline__ void tc_mma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                              uint32_t accumulate) {
     asm volatile(
         "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_d),
-        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&v)[8]) {
@@ -94,24 +129,39 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&v)[8]) {
                  : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+// 16 lanes x 32 columns: slab j (columns 8j..8j+7) takes registers 4j..4j+3 of every thread;
+// thread (g, t) supplies lane g: columns 2t, 2t+1 (registers 0, 1) and lane g+8 (registers 2, 3).
+__device__ __forceinline__ void tmem_st_16x256b_x4(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.16x256b.x4.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // K-major, no swizzle: core matrix = 8 rows x 16 bytes (128 contiguous bytes); the next 16-byte K
 // chunk is LBO bytes away, the next 8-row group SBO bytes away.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
     return uint64_t((addr >> 4) & 0x3FFFu) | (uint64_t((lbo >> 4) & 0x3FFFu) << 16) |
            (uint64_t((sbo >> 4) & 0x3FFFu) << 32) | (uint64_t(1) << 46);
 }
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
-    uint32_t d;
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
-    return d;
+
+// Position (0..63) inside a unit's MMA k order of logical element k (0..63): slab j = tile T of
+// the packed layout, slot s = 4t + 2r + h inside the slab.
+__host__ __device__ __forceinline__ int gs_kslot(int k) {
+    const int kb = k >> 4, e = k & 15;
+    const int pr = kb >> 1, h = kb & 1, t = e >> 2, sub = (e >> 1) & 1, r = e & 1;
+    return 16 * (2 * pr + sub) + 4 * t + 2 * r + h;
 }
 
 // Activation preparation: one CTA per token row.  bf16 -> f16 scaled by 2^-E (row maximum into
-// [2^14, 2^15)), written in tile order: element (m, k) of unit u = k / 64 goes to
-//   xt + u * (M*128) + (m/8)*1024 + ((k%64)/8)*128 + (m%8)*16 + (k%8)*2.
-__global__ void x_prep_kernel(const uint16_t* x, int M, int K, uint8_t* xt, int32_t* xexp) {
+// [2^14, 2^15)), written in tile order: element (m, k), unit u = k / 64, position p = gs_kslot(k % 64):
+//   xt + u * (M*128) + (m/8)*1024 + (p/8)*128 + (m%8)*16 + (p%8)*2.
+constexpr int kXPrepThreads = 256;
+__global__ void __launch_bounds__(kXPrepThreads) x_prep_kernel(const uint16_t* x, int M, int K, uint8_t* xt,
+                                                               int32_t* xexp) {
     __shared__ unsigned int smax;
+    __shared__ __align__(16) uint16_t seg[kXPrepThreads * 8];  // 2048 elements = 32 units
     pdl_launch_dependents();
     pdl_wait();
     const int m = blockIdx.x;
@@ -119,8 +169,8 @@ __global__ void x_prep_kernel(const uint16_t* x, int M, int K, uint8_t* xt, int3
     __syncthreads();
     const uint16_t* xr = x + int64_t(m) * K;
     unsigned int mx = 0;
-    for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
-        const uint4 v = __ldcg(reinterpret_cast<const uint4*>(xr + k));
+    for (int k = threadIdx.x * 8; k < K; k += kXPrepThreads * 8) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(xr + k));
         const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int z = 0; z < 4; ++z) {
@@ -135,193 +185,307 @@ __global__ void x_prep_kernel(const uint16_t* x, int M, int K, uint8_t* xt, int3
     if (threadIdx.x == 0) xexp[m] = E;
     const float sf = pow2i(-E);
     const size_t tile_bytes = size_t(M) * 128;
-    for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
-        const uint4 v = __ldcg(reinterpret_cast<const uint4*>(xr + k));
-        uint4 o;
-        o.x = pack_f16x2(__uint_as_float(v.x << 16) * sf, __uint_as_float(v.x & 0xFFFF0000u) * sf);
-        o.y = pack_f16x2(__uint_as_float(v.y << 16) * sf, __uint_as_float(v.y & 0xFFFF0000u) * sf);
-        o.z = pack_f16x2(__uint_as_float(v.z << 16) * sf, __uint_as_float(v.z & 0xFFFF0000u) * sf);
-        o.w = pack_f16x2(__uint_as_float(v.w << 16) * sf, __uint_as_float(v.w & 0xFFFF0000u) * sf);
-        const int u = k >> 6, kc = (k & 63) >> 3;
-        *reinterpret_cast<uint4*>(xt + size_t(u) * tile_bytes + size_t(m >> 3) * 1024 + kc * 128 + (m & 7) * 16) = o;
+    uint8_t* dst_row = xt + size_t(m >> 3) * 1024 + (m & 7) * 16;
+    for (int k0 = 0; k0 < K; k0 += kXPrepThreads * 8) {
+        const int k = k0 + threadIdx.x * 8;
+        if (k < K) {
+            const uint4 v = __ldg(reinterpret_cast<const uint4*>(xr + k));
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+            const int ubase = (threadIdx.x >> 3) * 64, kin = (threadIdx.x & 7) * 8;
+#pragma unroll
+            for (int z = 0; z < 4; ++z) {
+                const uint32_t f = pack_f16x2(__uint_as_float(w[z] << 16) * sf, __uint_as_float(w[z] & 0xFFFF0000u) * sf);
+                seg[ubase + gs_kslot(kin + 2 * z)] = uint16_t(f & 0xFFFFu);
+                seg[ubase + gs_kslot(kin + 2 * z + 1)] = uint16_t(f >> 16);
+            }
+        }
+        __syncthreads();
+        if (k < K) {
+            const uint4 o = *reinterpret_cast<const uint4*>(seg + threadIdx.x * 8);
+            const int u = k >> 6, chunk = (k & 63) >> 3;
+            *reinterpret_cast<uint4*>(dst_row + size_t(u) * tile_bytes + chunk * 128) = o;
+        }
+        __syncthreads();
     }
 }
 
-// Dequantises one packed unit of one panel (lane-ordered MMA-fragment layout) into the canonical
-// A tile: this lane's rows g and g+8 of the panel, four 4-element runs per row.
+// Dequantises one packed unit (lane-ordered MMA-fragment layout) and stores it as four 16x16
+// slabs into 16 TMEM lanes x 32 columns at `taddr`.
 template <int FMT>
-__device__ __forceinline__ void dequant_unit_to_tile(uint32_t unit, uint32_t a_tile, int panel, int lane) {
-    const int g = lane >> 2, t = lane & 3;
-    uint32_t a[4][4];  // [tile T][register jb]: f16x2 = (block 2*pr, block 2*pr+1)
+__device__ __forceinline__ void dequant_unit_to_tmem(uint32_t unit, uint32_t taddr, int lane) {
+    uint32_t a[16];  // [slab T][register]: order (row g, r=0), (row g, r=1), (row g+8, r=0), (row g+8, r=1)
     if (FMT == QGEMV_FMT_NVFP4) {
         const uint4 cw = lds128(unit + lane * 16);
-        const uint2 sw = lds64(unit + 512 + g * 8);
+        const uint2 sw = lds64(unit + 512 + (lane >> 2) * 8);
         uint32_t sg[2], sh[2];
-        cvt_e4m3x4(sw.x, sg[0], sg[1]);
-        cvt_e4m3x4(sw.y, sh[0], sh[1]);
+        cvt_e4m3x4(sw.x, sg[0], sg[1]);  // row g:   (blk0, blk1), (blk2, blk3)
+        cvt_e4m3x4(sw.y, sh[0], sh[1]);  // row g+8
         const uint32_t w[4] = {cw.x, cw.y, cw.z, cw.w};
 #pragma unroll
         for (int T = 0; T < 4; ++T) {
-            cvt_e2m1x8(w[T], a[T][0], a[T][1], a[T][2], a[T][3]);
-            a[T][0] = hmul2(a[T][0], sg[T >> 1]);
-            a[T][2] = hmul2(a[T][2], sg[T >> 1]);
-            a[T][1] = hmul2(a[T][1], sh[T >> 1]);
-            a[T][3] = hmul2(a[T][3], sh[T >> 1]);
+            uint32_t b0, b1, b2, b3;  // bytes jb = rowhi + 2r
+            cvt_e2m1x8(w[T], b0, b1, b2, b3);
+            a[4 * T + 0] = hmul2(b0, sg[T >> 1]);
+            a[4 * T + 1] = hmul2(b2, sg[T >> 1]);
+            a[4 * T + 2] = hmul2(b1, sh[T >> 1]);
+            a[4 * T + 3] = hmul2(b3, sh[T >> 1]);
         }
     } else {
         const uint4 v0 = lds128(unit + lane * 16);
         const uint4 v1 = lds128(unit + 512 + lane * 16);
-        cvt_e4m3x4(v0.x, a[0][0], a[0][1]);
-        cvt_e4m3x4(v0.y, a[0][2], a[0][3]);
-        cvt_e4m3x4(v0.z, a[1][0], a[1][1]);
-        cvt_e4m3x4(v0.w, a[1][2], a[1][3]);
-        cvt_e4m3x4(v1.x, a[2][0], a[2][1]);
-        cvt_e4m3x4(v1.y, a[2][2], a[2][3]);
-        cvt_e4m3x4(v1.z, a[3][0], a[3][1]);
-        cvt_e4m3x4(v1.w, a[3][2], a[3][3]);
-    }
-    // element (row = g + 8*rowhi, block kb = 2*pr + h, e = 4*t + 2*sub + r) is half h of a[2*pr+sub][rowhi + 2*r]
+        const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
 #pragma unroll
-    for (int rowhi = 0; rowhi < 2; ++rowhi) {
-        const uint32_t row_base = a_tile + uint32_t(2 * panel + rowhi) * 1024u + uint32_t(g) * 16u + uint32_t(t & 1) * 8u;
-#pragma unroll
-        for (int pr = 0; pr < 2; ++pr) {
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const uint32_t sel = h ? 0x7632u : 0x5410u;
-                const uint32_t lo = prmt(a[2 * pr][rowhi], a[2 * pr][rowhi + 2], sel);          // e = 4t, 4t+1
-                const uint32_t hi = prmt(a[2 * pr + 1][rowhi], a[2 * pr + 1][rowhi + 2], sel);  // e = 4t+2, 4t+3
-                const int kc = 2 * (2 * pr + h) + (t >> 1);  // 16-byte K chunk inside the 64-wide step
-                asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(row_base + uint32_t(kc) * 128u), "r"(lo), "r"(hi)
-                             : "memory");
-            }
+        for (int T = 0; T < 4; ++T) {
+            uint32_t b0, b1, b2, b3;
+            cvt_e4m3x4(w[2 * T], b0, b1);
+            cvt_e4m3x4(w[2 * T + 1], b2, b3);
+            a[4 * T + 0] = b0, a[4 * T + 1] = b2, a[4 * T + 2] = b1, a[4 * T + 3] = b3;
         }
     }
+    tmem_st_16x256b_x4(taddr, a);
+}
+
+// One segment of a CTA's range: units [u0, u1) of row tile `tile`.
+struct GsSeg {
+    int32_t tile, u0, u1;
+};
+struct GsWalker {
+    int32_t pos, end, units;
+    __device__ __forceinline__ void init(int32_t total, int32_t units_, int cta, int grid) {
+        units = units_;
+        pos = int32_t((int64_t(cta) * total) / grid);
+        end = int32_t((int64_t(cta + 1) * total) / grid);
+    }
+    __device__ __forceinline__ bool next(GsSeg& s) {
+        if (pos >= end) return false;
+        s.tile = pos / units;
+        s.u0 = pos - s.tile * units;
+        const int32_t left = end - pos;
+        s.u1 = s.u0 + left < units ? s.u0 + left : units;
+        pos += s.u1 - s.u0;
+        return true;
+    }
+};
+// Workspace slot of the part of row tile `tile` that CTA c computes: its first segment uses slot
+// 2c, its last one slot 2c + 1 (segments in between are whole tiles and need none).
+__device__ __forceinline__ int32_t gs_slot(int32_t c, int32_t tile, int32_t units, int32_t total, int grid) {
+    const int32_t a = int32_t((int64_t(c) * total) / grid);
+    return 2 * c + (a / units == tile ? 0 : 1);
 }
 
 template <int FMT>
 __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsParams P) {
     constexpr int kUnitBytes = FmtTraits<FMT>::kUnitBytes;
+    constexpr int kPStage = GsSmem::packed_stage(kUnitBytes);
     extern __shared__ __align__(128) unsigned char gs_smem[];
     const uint32_t sbase = smem_u32(gs_smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int kPStages = GsSmem::p_stages(kUnitBytes);
     const int M = P.M;
-    const int stage_bytes = GsSmem::stage_bytes(kUnitBytes, M);
-    const int x_off = ((GsSmem::packed_bytes(kUnitBytes) + 1023) / 1024) * 1024;
-    const int a_off = x_off + M * 128;
+    const int grid = gridDim.x, cta = blockIdx.x;
+    // the work space is counted in runs (1 << rl units of one row tile): `units` and `total` below are runs
+    const int rl = P.run_log2, run = 1 << rl;
+    const int units = P.units >> rl;
+    const int32_t total = P.tiles * units;
+    const uint32_t x_bytes = uint32_t(M) * 128u;
+    const uint32_t xring = sbase + GsSmem::x_off(kUnitBytes);
+    const int x_stages = P.x_stages;
     uint32_t ncols = 32;
-    while (int(ncols) < M) ncols <<= 1;
+    while (int(ncols) < M + 32 * kGsAStages) ncols <<= 1;
+    const uint32_t acol0 = ncols - 32 * kGsAStages;  // A ring: the last columns of the allocation
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gs_smem + GsSmem::kAbort);
     volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(gs_smem + GsSmem::kTmemPtr);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kGsStages; ++s) {
-            mbar_init(sbase + GsSmem::kBarFull + 8 * s, 1);
+        for (int s = 0; s < kPStages; ++s) {
+            mbar_init(sbase + GsSmem::kBarPFull + 8 * s, 1);
+            mbar_init(sbase + GsSmem::kBarPEmpty + 8 * s, 4u << rl);  // four warps per unit of the run
+        }
+        for (int s = 0; s < kGsXStagesMax; ++s) {
+            mbar_init(sbase + GsSmem::kBarXFull + 8 * s, 1);
+            mbar_init(sbase + GsSmem::kBarXEmpty + 8 * s, 1);
+        }
+        for (int s = 0; s < kGsAStages; ++s) {
             mbar_init(sbase + GsSmem::kBarAReady + 8 * s, 4);
-            mbar_init(sbase + GsSmem::kBarEmpty + 8 * s, 1);
+            mbar_init(sbase + GsSmem::kBarAEmpty + 8 * s, 1);
         }
         mbar_init(sbase + GsSmem::kBarDone, 1);
+        mbar_init(sbase + GsSmem::kBarDFree, kGsDqWarps);
+        mbar_init(sbase + GsSmem::kBarDrain, 1);
         *abort_flag = 0;
         mbar_fence_init();
     }
-    if (warp == 5) tmem_alloc(sbase + GsSmem::kTmemPtr, ncols);
+    if (warp == kGsWarpMma) {
+        __syncwarp();
+        tmem_alloc(sbase + GsSmem::kTmemPtr, ncols);
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_ptr;
     pdl_launch_dependents();
-    const int n0 = blockIdx.x * 128;  // first weight row of this CTA
-    const int panel0 = n0 / 16;
-    const int units = P.units;
 
-    if (warp == 4) {
-        // ================= producer =================
+    if (warp == kGsWarpP) {
+        // ================= packed-weight producer =================
         if (lane == 0 && !(P.debug & 2)) {
             const uint64_t pol = policy_evict_first();
-            pdl_wait();  // the activation tiles come from x_prep_kernel
-            const uint32_t x_bytes = uint32_t(M) * 128u;
-            for (int u = 0; u < units; ++u) {
-                const int s = u % kGsStages;
-                const uint32_t use = uint32_t(u / kGsStages);
-                if (use > 0 && !mbar_wait(sbase + GsSmem::kBarEmpty + 8 * s, (use - 1) & 1, P.spin_limit)) {
-                    report(P.status, QGEMV_ERR_TIMEOUT, 41, u);
+            int32_t pos = int32_t((int64_t(cta) * total) / grid);
+            const int32_t end = int32_t((int64_t(cta + 1) * total) / grid);
+            int32_t tile = pos / units, u = pos - tile * units;
+            int s = 0;
+            uint32_t use = 0;
+            for (; pos < end; ++pos) {
+                if (use > 0 && !mbar_wait(sbase + GsSmem::kBarPEmpty + 8 * s, (use - 1) & 1, P.spin_limit)) {
+                    report(P.status, QGEMV_ERR_TIMEOUT, 41, pos);
                     *abort_flag = 1;
                     break;
                 }
-                const uint32_t bar = sbase + GsSmem::kBarFull + 8 * s;
-                const uint32_t st = sbase + GsSmem::kStage0 + s * stage_bytes;
-                mbar_arrive_expect_tx(bar, 8u * kUnitBytes + x_bytes);
+                const uint32_t bar = sbase + GsSmem::kBarPFull + 8 * s;
+                const uint32_t st = sbase + GsSmem::kRing0 + s * kPStage;
+                const uint32_t run_bytes = uint32_t(kUnitBytes) << rl;
+                mbar_arrive_expect_tx(bar, 8u * run_bytes);
+                const uint8_t* src = P.payload + (uint64_t(tile) * 8 * P.units + (uint64_t(u) << rl)) * kUnitBytes;
+#pragma unroll
                 for (int p = 0; p < 8; ++p)
-                    bulk_g2s(st + p * kUnitBytes,
-                             P.payload + (uint64_t(panel0 + p) * units + u) * kUnitBytes, kUnitBytes, bar, pol);
-                bulk_g2s(st + x_off, P.xt + uint64_t(u) * x_bytes, x_bytes, bar, pol);
+                    bulk_g2s(st + p * run_bytes, src + uint64_t(p) * P.units * kUnitBytes, run_bytes, bar, pol);
+                if (++u == units) u = 0, ++tile;
+                if (++s == kPStages) s = 0, ++use;
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == kGsWarpX) {
+        // ================= activation-tile producer =================
+        if (lane == 0) {
+            pdl_wait();  // the tiles come from x_prep_kernel
+            int32_t pos = int32_t((int64_t(cta) * total) / grid) << rl;  // in units from here on
+            const int32_t end = int32_t((int64_t(cta + 1) * total) / grid) << rl;
+            int32_t u = pos % P.units;
+            int s = 0;
+            uint32_t use = 0;
+            for (; pos < end; ++pos) {
+                if (use > 0 && !mbar_wait(sbase + GsSmem::kBarXEmpty + 8 * s, (use - 1) & 1, P.spin_limit)) {
+                    report(P.status, QGEMV_ERR_TIMEOUT, 46, pos);
+                    *abort_flag = 1;
+                    break;
+                }
+                const uint32_t bar = sbase + GsSmem::kBarXFull + 8 * s;
+                mbar_arrive_expect_tx(bar, x_bytes);
+                bulk_g2s_plain(xring + s * x_bytes, P.xt + uint64_t(u) * x_bytes, x_bytes, bar);
+                if (++u == P.units) u = 0;
+                if (++s == x_stages) s = 0, ++use;
+            }
+        }
+    } else if (warp == kGsWarpMma) {
         // ================= MMA issuer =================
         if (lane == 0) {
             const uint32_t idesc = (1u << 4) | (uint32_t(M >> 3) << 17) | (uint32_t(128 >> 4) << 24);
+            GsWalker wk;
+            wk.init(total, units, cta, grid);
+            GsSeg sg;
+            int sa = 0, sx = 0;
+            uint32_t usea = 0, usex = 0, nseg = 0;
             bool ok = true;
-            for (int u = 0; u < units && ok; ++u) {
-                const int s = u % kGsStages;
-                if (!mbar_wait(sbase + GsSmem::kBarAReady + 8 * s, uint32_t(u / kGsStages) & 1, P.spin_limit)) {
-                    report(P.status, QGEMV_ERR_TIMEOUT, 42, u);
+            while (ok && wk.next(sg)) {
+                // the accumulator is free once the epilogue of the previous segment has read it
+                if (nseg > 0 && !mbar_wait(sbase + GsSmem::kBarDFree, (nseg - 1) & 1, P.spin_limit)) {
+                    report(P.status, QGEMV_ERR_TIMEOUT, 47, int(nseg));
+                    *abort_flag = 1;
+                    ok = false;
+                    break;
+                }
+                const int ua = sg.u0 << rl, ub = sg.u1 << rl;
+                for (int u = ua; u < ub; ++u) {
+                    if (!mbar_wait(sbase + GsSmem::kBarAReady + 8 * sa, usea & 1, P.spin_limit) ||
+                        !mbar_wait(sbase + GsSmem::kBarXFull + 8 * sx, usex & 1, P.spin_limit)) {
+                        report(P.status, QGEMV_ERR_TIMEOUT, 42, u);
+                        *abort_flag = 1;
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t xs = xring + sx * x_bytes;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {  // four K=16 slabs: 8 TMEM columns / two 16-byte chunks each
+                        const uint64_t db = smem_desc(xs + j * 256, 128, 1024);
+                        tc_mma_f16_ts(tmem_base, tmem_base + acol0 + 32 * sa + 8 * j, db, idesc,
+                                      (u > ua || j > 0) ? 1u : 0u);
+                    }
+                    tc_commit(sbase + GsSmem::kBarAEmpty + 8 * sa);  // stages reusable once these MMAs retire
+                    tc_commit(sbase + GsSmem::kBarXEmpty + 8 * sx);
+                    if (++sa == kGsAStages) sa = 0, ++usea;
+                    if (++sx == x_stages) sx = 0, ++usex;
+                }
+                tc_commit(sbase + GsSmem::kBarDone);
+                ++nseg;
+            }
+        }
+    } else {
+        // ================= dequantisation warps; epilogue of each segment =================
+        const int q = warp >> 2, wq = warp & 3;  // group, TMEM lane quarter
+        GsWalker wk;
+        wk.init(total, units, cta, grid);
+        GsSeg sg;
+        // this group's next step, as an index into the CTA's range, and its ring positions
+        int32_t inext = q;
+        int sa = q % kGsAStages;
+        uint32_t usea = 0, nseg = 0;
+        int32_t seg_i0 = 0;  // index of the segment's first step
+        bool ok = true;
+        bool waited_x = false;
+        const uint32_t lane_base = uint32_t(32 * wq) << 16;
+        while (ok && wk.next(sg)) {
+            const int32_t seg_i1 = seg_i0 + ((sg.u1 - sg.u0) << rl);
+            for (; inext < seg_i1; inext += kGsGroups) {
+                // the TMEM stage is free once the MMAs of its previous use retired
+                const int32_t ri = inext >> rl;  // run index in the CTA's range -> packed ring position
+                const int sp = ri % kPStages;
+                const uint32_t usep = uint32_t(ri / kPStages);
+                bool w_ok = usea == 0 || mbar_wait(sbase + GsSmem::kBarAEmpty + 8 * sa, (usea - 1) & 1, P.spin_limit);
+                w_ok = w_ok && mbar_wait(sbase + GsSmem::kBarPFull + 8 * sp, usep & 1, P.spin_limit);
+                if (!__all_sync(0xFFFFFFFFu, w_ok)) {
+                    if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 44, inext);
                     *abort_flag = 1;
                     ok = false;
                     break;
                 }
                 tc_fence_after();
-                const uint32_t st = sbase + GsSmem::kStage0 + s * stage_bytes;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {  // four K=16 steps: two 16-byte chunks each
-                    const uint64_t da = smem_desc(st + a_off + j * 256, 128, 1024);
-                    const uint64_t db = smem_desc(st + x_off + j * 256, 128, 1024);
-                    tc_mma_f16(tmem_base, da, db, idesc, (u > 0 || j > 0) ? 1u : 0u);
+                // stage layout: [panel][unit of the run]
+                const uint32_t st = sbase + GsSmem::kRing0 + sp * kPStage +
+                                    uint32_t(((2 * wq) << rl) + (inext & (run - 1))) * kUnitBytes;
+                const uint32_t ta = tmem_base + lane_base + acol0 + 32 * sa;
+                dequant_unit_to_tmem<FMT>(st, ta, lane);
+                dequant_unit_to_tmem<FMT>(st + (uint32_t(kUnitBytes) << rl), ta + (16u << 16), lane);
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(sbase + GsSmem::kBarAReady + 8 * sa);
+                    mbar_arrive(sbase + GsSmem::kBarPEmpty + 8 * sp);
                 }
-                tc_commit(sbase + GsSmem::kBarEmpty + 8 * s);  // stage reusable once these MMAs retire
+                sa += kGsGroups;
+                if (sa >= kGsAStages) sa -= kGsAStages, ++usea;
             }
-            tc_commit(sbase + GsSmem::kBarDone);
-        }
-    } else {
-        // ================= dequantisation warps, then epilogue =================
-        bool ok = true;
-        for (int u = 0; u < units && ok; ++u) {
-            const int s = u % kGsStages;
-            const uint32_t use = uint32_t(u / kGsStages);
-            // the A tile of this stage is free once the MMAs of its previous use retired
-            if (use > 0 && !mbar_wait(sbase + GsSmem::kBarEmpty + 8 * s, (use - 1) & 1, P.spin_limit)) {
-                if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 43, u);
+            seg_i0 = seg_i1;
+            if (!ok) break;
+            // ---- epilogue: this warp owns TMEM lanes [32w, 32w+32) = rows n0 + 32w + lane ----
+            if (!__all_sync(0xFFFFFFFFu, mbar_wait(sbase + GsSmem::kBarDone, nseg & 1, P.spin_limit))) {
+                if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 45, int(nseg));
                 *abort_flag = 1;
                 ok = false;
                 break;
             }
-            if (!mbar_wait(sbase + GsSmem::kBarFull + 8 * s, use & 1, P.spin_limit)) {
-                if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 44, u);
-                *abort_flag = 1;
-                ok = false;
-                break;
-            }
-            const uint32_t st = sbase + GsSmem::kStage0 + s * stage_bytes;
-            dequant_unit_to_tile<FMT>(st + (2 * warp) * kUnitBytes, st + a_off, 2 * warp, lane);
-            dequant_unit_to_tile<FMT>(st + (2 * warp + 1) * kUnitBytes, st + a_off, 2 * warp + 1, lane);
-            fence_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
-            __syncwarp();
-            if (lane == 0) mbar_arrive(sbase + GsSmem::kBarAReady + 8 * s);
-        }
-        // ---- epilogue: warp w reads TMEM lanes [32w, 32w+32) = weight rows n0 + 32w + lane ----
-        ok = __all_sync(0xFFFFFFFFu, ok);
-        const bool done = ok && __all_sync(0xFFFFFFFFu, mbar_wait(sbase + GsSmem::kBarDone, 0, P.spin_limit));
-        if (done) {
             tc_fence_after();
-            const int n = n0 + 32 * warp + lane;
-            float rs = (FMT == QGEMV_FMT_NVFP4) ? P.tensor_scale : P.chan_scale[n];
-            for (int c = 0; c < M; c += 8) {
-                uint32_t v[8];
-                tmem_ld8(tmem_base + (uint32_t(32 * warp) << 16) + uint32_t(c), v);
+            if (!waited_x) {
+                pdl_wait();  // the row exponents come from x_prep_kernel
+                waited_x = true;
+            }
+            const int row = 32 * wq + lane;
+            const int n = sg.tile * 128 + row;
+            const float rs = (FMT == QGEMV_FMT_NVFP4) ? P.tensor_scale : __ldg(P.chan_scale + n);
+            auto store_cols = [&](int c, const float (&v)[8]) {
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const int m = c + i;
-                    const float val = __uint_as_float(v[i]) * rs * pow2i(__ldg(P.xexp + m));
+                    const float val = v[i] * rs * pow2i(__ldg(P.xexp + m));
                     const int64_t idx = int64_t(m) * P.N + n;
                     if (P.y_dtype == QGEMV_OUT_F32) {
                         static_cast<float*>(P.y)[idx] = val;
@@ -329,19 +493,73 @@ __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsPara
                         static_cast<__nv_bfloat16*>(P.y)[idx] = __float2bfloat16_rn(val);
                     }
                 }
+            };
+            if (sg.u0 == 0 && sg.u1 == units) {  // (runs) the segment is the whole tile
+                for (int c = 8 * q; c < M; c += 8 * kGsGroups) {
+                    uint32_t r[8];
+                    tmem_ld8(tmem_base + lane_base + uint32_t(c), r);
+                    float v[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+                    store_cols(c, v);
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(sbase + GsSmem::kBarDFree);
+            } else {
+                // partial: park the fp32 sums, then the last contributor of (tile, lane quarter)
+                // adds all parts in CTA order
+                float* slot = P.ws + size_t(gs_slot(cta, sg.tile, units, total, grid)) * size_t(M) * 128;
+                for (int c = 8 * q; c < M; c += 8 * kGsGroups) {
+                    uint32_t r[8];
+                    tmem_ld8(tmem_base + lane_base + uint32_t(c), r);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) __stcg(slot + (c + i) * 128 + row, __uint_as_float(r[i]));
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(sbase + GsSmem::kBarDFree);  // the next segment may start
+                __threadfence();
+                __syncwarp();
+                const int32_t c_lo = int32_t(cta_of(int64_t(sg.tile) * units, total, grid));
+                const int32_t c_hi = int32_t(cta_of(int64_t(sg.tile + 1) * units - 1, total, grid));
+                int old = 0;
+                if (lane == 0) old = atomicAdd(P.counters + sg.tile * 16 + warp, 1);
+                old = __shfl_sync(0xFFFFFFFFu, old, 0);
+                if (old == c_hi - c_lo) {
+                    __threadfence();
+                    for (int c = 8 * q; c < M; c += 8 * kGsGroups) {
+                        float v[8];
+                        for (int32_t cc = c_lo; cc <= c_hi; ++cc) {
+                            const float* sl = P.ws + size_t(gs_slot(cc, sg.tile, units, total, grid)) * size_t(M) * 128;
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const float q = __ldcg(sl + (c + i) * 128 + row);
+                                v[i] = cc == c_lo ? q : v[i] + q;
+                            }
+                        }
+                        store_cols(c, v);
+                    }
+                    __syncwarp();
+                    if (lane == 0) P.counters[sg.tile * 16 + warp] = 0;
+                }
             }
-            tc_fence_before();
-        } else if (ok) {
-            if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 45, 0);
-            *abort_flag = 1;
+            ++nseg;
         }
     }
     // ---- release TMEM (always), after every role is done with it ----
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == kGsWarpMma) {
         __syncwarp();
-        if (*abort_flag) (void)mbar_wait(sbase + GsSmem::kBarDone, 0, int64_t(1) << 16);  // let issued MMAs retire
+        if (*abort_flag) {
+            // let whatever MMAs were issued retire before the columns are handed back (bounded)
+            if (lane == 0) {
+                tc_commit(sbase + GsSmem::kBarDrain);
+                (void)mbar_wait(sbase + GsSmem::kBarDrain, 0, int64_t(1) << 16);
+            }
+            __syncwarp();
+        }
         tc_fence_after();
         tmem_dealloc(tmem_base, ncols);
     }

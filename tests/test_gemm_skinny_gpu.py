@@ -138,7 +138,7 @@ def test_skinny_bounded_wait(qg):
     h.gemm_skinny(w, xd.data_ptr(), 32, yd.data_ptr(), qg.OUT_F32)
     torch.cuda.synchronize()
     st = h.device_status()
-    assert st.code == qg.ERR_TIMEOUT and st.where in (42, 44)
+    assert st.code == qg.ERR_TIMEOUT and st.where in (42, 44, 45, 46)
     w.unload()
     h.close()
     h2 = qg.QGemv()
