@@ -396,12 +396,13 @@ int qgemv_gemm_skinny(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16
     P.N = int32_t(w->N), P.K = int32_t(w->K), P.M = M;
     P.units = int32_t(w->units);
     P.tiles = tiles;
-    P.x_stages = qg::GsSmem::x_stages(unit_bytes, M);
     P.run_log2 = run_log2;
+    P.xg_log2 = qg::GsSmem::xg_log2(unit_bytes, M, run_log2);
+    P.x_stages = qg::GsSmem::x_stages(unit_bytes, M, P.xg_log2);
     P.status = h->status_dev;
     P.spin_limit = default_spin(h);
     P.debug = h->cfg.debug;
-    const size_t smem = size_t(qg::GsSmem::total(unit_bytes, M));
+    const size_t smem = size_t(qg::GsSmem::total(unit_bytes, M, P.xg_log2));
     const dim3 g(static_cast<unsigned>(grid)), block(qg::kGsThreads);
     const cudaError_t err = w->fmt == QGEMV_FMT_NVFP4
                                 ? launch(h, qg::gemm_skinny_kernel<QGEMV_FMT_NVFP4>, g, block, smem, st, P)

@@ -18,21 +18,29 @@
 //   B operand (activations) is read from shared memory through a K-major no-swizzle descriptor
 //       (core matrix = 8 token rows x 16 bytes); x_prep_kernel lays the tiles out in that order
 //       so one bulk copy brings a whole [M x 64] tile.
-//   D (fp32) occupies TMEM columns [0, M); the A ring occupies six 32-column stages at the end of the allocation.
+//   D (fp32) occupies TMEM columns [0, M); the A ring (two or three stages of one run = up to four
+//       units, 32 columns per unit) sits at the end of the allocation.
 //
-// Work split: the linear space (row tile, unit) is cut evenly over the CTAs (one per SM); a CTA's
+// Pipeline grain: a RUN = up to four consecutive units of one row tile.  One bulk copy per panel
+// fetches a run of packed weights; the MMA issuer waits once per run for the dequantised weights and
+// once per activation stage (1, 2 or 4 units, whatever leaves >= 3-4 stages in shared memory), so
+// its per-unit path is four tcgen05.mma and nothing else -- measured here, a wait + fence + commit
+// per unit costs ~300 cycles of the issuing thread, more than the MMAs of a narrow tile.
+//
+// Work split: the linear space (row tile, run) is cut evenly over the CTAs (one per SM); a CTA's
 // range is a sequence of segments, each a K range of one row tile.  A segment that covers its
 // whole tile stores Y directly; otherwise the fp32 partial goes to a workspace slot and the last
 // contributor of the tile (atomic counter) adds all parts in CTA order -- deterministic.
 //
 // Warp roles (15 warps):
-//   0-11 three dequantising warpgroups; group q = warp / 4 takes the CTA's steps i = q (mod 3), so the
-//        latency of one step's conversion, tcgen05.st and barrier round trips overlaps the other
-//        groups' steps.  Warp w handles panels 2(w%4), 2(w%4)+1 = TMEM lanes 32(w%4)..+31 (the lane
+//   0-11 three dequantising warpgroups; group q = warp / 4 takes the CTA's units i = q (mod 3), so the
+//        latency of one unit's conversion, tcgen05.st and barrier round trips overlaps the other
+//        groups' units.  Warp w handles panels 2(w%4), 2(w%4)+1 = TMEM lanes 32(w%4)..+31 (the lane
 //        quarter a warp may access), and in the epilogue the same lanes of every third 8-column chunk
-//   12   one thread issues the bulk copies of packed weights (ring of 8 stages)
-//   13   allocates TMEM; one thread issues tcgen05.mma and the commits that free ring stages
-//   14   one thread issues the bulk copies of activation tiles (ring sized to what is left)
+//   12   one thread issues the bulk copies of packed weights (ring of 3-4 runs)
+//   13   allocates TMEM; the warp walks the runs together, one elected lane issues tcgen05.mma and
+//        the commits that free ring stages
+//   14   one thread issues the bulk copies of activation tiles (L2 evict-last: every CTA re-reads them)
 // Every wait is bounded; TMEM is always released before the CTA exits.
 #pragma once
 #include <cuda_bf16.h>
@@ -47,10 +55,10 @@ constexpr int kGsDqWarps = 4 * kGsGroups;
 constexpr int kGsWarpP = kGsDqWarps, kGsWarpMma = kGsDqWarps + 1, kGsWarpX = kGsDqWarps + 2;
 constexpr int kGsThreads = 32 * (kGsDqWarps + 3);
 constexpr int kGsMaxM = 256;
-constexpr int kGsRunMax = 4;     // units of one panel fetched by one bulk copy (a run)
+constexpr int kGsRunMax = 4;     // units of one panel fetched by one bulk copy (a run); also the pipeline's grain
 constexpr int kGsPStagesMax = 4; // packed-weight ring: stages of 8 panels x one run
-constexpr int kGsAStages = 6;    // dequantised-weight ring in TMEM (32 columns each)
-constexpr int kGsXStagesMax = 8;
+constexpr int kGsAStagesMax = 3; // dequantised-weight ring in TMEM: stages of one run (32 columns per unit)
+constexpr int kGsXStagesMax = 16;
 constexpr int kGsSmemBudget = 227 * 1024;
 
 struct GsParams {
@@ -68,6 +76,7 @@ struct GsParams {
     int32_t tiles;            // N / 128
     int32_t x_stages;
     int32_t run_log2;         // log2(units per run): 2, 1 or 0, the largest that divides K / 64
+    int32_t xg_log2;          // log2(units per activation-ring stage), <= run_log2
     int32_t* status;
     int64_t spin_limit;
     int32_t debug;
@@ -75,27 +84,35 @@ struct GsParams {
 
 struct GsSmem {
     static constexpr int kBarPFull = 0;      // kGsPStagesMax
-    static constexpr int kBarPEmpty = 64;    // kGsPStagesMax
-    static constexpr int kBarXFull = 128;    // kGsXStagesMax
+    static constexpr int kBarPEmpty = 32;    // kGsPStagesMax
+    static constexpr int kBarXFull = 64;     // kGsXStagesMax
     static constexpr int kBarXEmpty = 192;   // kGsXStagesMax
-    static constexpr int kBarAReady = 256;   // kGsAStages
-    static constexpr int kBarAEmpty = 304;   // kGsAStages
-    static constexpr int kBarDone = 352;
-    static constexpr int kBarDFree = 360;
-    static constexpr int kTmemPtr = 368;
-    static constexpr int kAbort = 372;
-    static constexpr int kBarDrain = 376;
+    static constexpr int kBarAReady = 320;   // kGsAStagesMax
+    static constexpr int kBarAEmpty = 344;   // kGsAStagesMax
+    static constexpr int kBarDone = 368;
+    static constexpr int kBarDFree = 376;
+    static constexpr int kTmemPtr = 384;
+    static constexpr int kAbort = 388;
+    static constexpr int kBarDrain = 392;
     static constexpr int kRing0 = 1024;
     __host__ __device__ static constexpr int packed_stage(int unit_bytes) { return 8 * kGsRunMax * unit_bytes; }
     // four stages of NVFP4 runs (72 KB), three of FP8 (96 KB)
     __host__ __device__ static constexpr int p_stages(int unit_bytes) { return unit_bytes > 600 ? 3 : kGsPStagesMax; }
     __host__ __device__ static constexpr int x_off(int unit_bytes) { return kRing0 + p_stages(unit_bytes) * packed_stage(unit_bytes); }
-    __host__ __device__ static int x_stages(int unit_bytes, int M) {
-        const int n = (kGsSmemBudget - x_off(unit_bytes)) / (M * 128);
+    // activation ring: stages of (1 << xg_log2) units, as many as fit behind the packed ring
+    __host__ __device__ static int x_stages(int unit_bytes, int M, int xg_log2) {
+        const int n = (kGsSmemBudget - x_off(unit_bytes)) / ((M * 128) << xg_log2);
         return n > kGsXStagesMax ? kGsXStagesMax : n;
     }
-    __host__ __device__ static int total(int unit_bytes, int M) {
-        return x_off(unit_bytes) + x_stages(unit_bytes, M) * M * 128;
+    // largest stage grain (<= the run) that still leaves four stages, else three
+    __host__ __device__ static int xg_log2(int unit_bytes, int M, int run_log2) {
+        for (int want = 4; want >= 3; --want)
+            for (int g = run_log2; g >= 0; --g)
+                if (x_stages(unit_bytes, M, g) >= want) return g;
+        return 0;
+    }
+    __host__ __device__ static int total(int unit_bytes, int M, int xg_log2) {
+        return x_off(unit_bytes) + x_stages(unit_bytes, M, xg_log2) * ((M * 128) << xg_log2);
     }
 };
 
@@ -137,6 +154,11 @@ __device__ __forceinline__ void tmem_st_16x256b_x4(uint32_t taddr, const uint32_
         "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
         "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
+}
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n .reg .pred P;\n elect.sync _|P, 0xFFFFFFFF;\n selp.u32 %0, 1, 0, P;\n}" : "=r"(pred));
+    return pred != 0;
 }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // K-major, no swizzle: core matrix = 8 rows x 16 bytes (128 contiguous bytes); the next 16-byte K
@@ -277,22 +299,29 @@ template <int FMT>
 __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsParams P) {
     constexpr int kUnitBytes = FmtTraits<FMT>::kUnitBytes;
     constexpr int kPStage = GsSmem::packed_stage(kUnitBytes);
+    constexpr int kPStages = GsSmem::p_stages(kUnitBytes);
     extern __shared__ __align__(128) unsigned char gs_smem[];
     const uint32_t sbase = smem_u32(gs_smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    constexpr int kPStages = GsSmem::p_stages(kUnitBytes);
     const int M = P.M;
     const int grid = gridDim.x, cta = blockIdx.x;
-    // the work space is counted in runs (1 << rl units of one row tile): `units` and `total` below are runs
+    // the work space is counted in runs (1 << rl units of one row tile): `runs` per tile, `total` runs
     const int rl = P.run_log2, run = 1 << rl;
-    const int units = P.units >> rl;
-    const int32_t total = P.tiles * units;
-    const uint32_t x_bytes = uint32_t(M) * 128u;
+    const int xgl = P.xg_log2, xg = 1 << xgl;
+    const int runs = P.units >> rl;
+    const int32_t total = P.tiles * runs;
+    const int32_t r_begin = int32_t((int64_t(cta) * total) / grid);
+    const int32_t r_end = int32_t((int64_t(cta + 1) * total) / grid);
+    const uint32_t x_bytes = uint32_t(M) * 128u;       // one unit of activations
+    const uint32_t xs_bytes = x_bytes << xgl;          // one stage of the activation ring
     const uint32_t xring = sbase + GsSmem::x_off(kUnitBytes);
     const int x_stages = P.x_stages;
+    // TMEM: D in columns [0, M); behind it the A ring, kA stages of one run (32 columns per unit)
+    const uint32_t a_cols = 32u << rl;
+    const int kA = (M + 3 * int(a_cols) <= 512) ? 3 : 2;
     uint32_t ncols = 32;
-    while (int(ncols) < M + 32 * kGsAStages) ncols <<= 1;
-    const uint32_t acol0 = ncols - 32 * kGsAStages;  // A ring: the last columns of the allocation
+    while (ncols < uint32_t(M) + kA * a_cols) ncols <<= 1;
+    const uint32_t acol0 = ncols - kA * a_cols;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gs_smem + GsSmem::kAbort);
     volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(gs_smem + GsSmem::kTmemPtr);
 
@@ -305,8 +334,8 @@ __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsPara
             mbar_init(sbase + GsSmem::kBarXFull + 8 * s, 1);
             mbar_init(sbase + GsSmem::kBarXEmpty + 8 * s, 1);
         }
-        for (int s = 0; s < kGsAStages; ++s) {
-            mbar_init(sbase + GsSmem::kBarAReady + 8 * s, 4);
+        for (int s = 0; s < kGsAStagesMax; ++s) {
+            mbar_init(sbase + GsSmem::kBarAReady + 8 * s, 4u << rl);
             mbar_init(sbase + GsSmem::kBarAEmpty + 8 * s, 1);
         }
         mbar_init(sbase + GsSmem::kBarDone, 1);
@@ -326,15 +355,14 @@ __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsPara
     pdl_launch_dependents();
 
     if (warp == kGsWarpP) {
-        // ================= packed-weight producer =================
+        // ================= packed-weight producer: one stage = 8 panels x one run =================
         if (lane == 0 && !(P.debug & 2)) {
             const uint64_t pol = policy_evict_first();
-            int32_t pos = int32_t((int64_t(cta) * total) / grid);
-            const int32_t end = int32_t((int64_t(cta + 1) * total) / grid);
-            int32_t tile = pos / units, u = pos - tile * units;
+            int32_t tile = r_begin / runs, u = r_begin - tile * runs;
+            const uint32_t run_bytes = uint32_t(kUnitBytes) << rl;
             int s = 0;
             uint32_t use = 0;
-            for (; pos < end; ++pos) {
+            for (int32_t pos = r_begin; pos < r_end; ++pos) {
                 if (use > 0 && !mbar_wait(sbase + GsSmem::kBarPEmpty + 8 * s, (use - 1) & 1, P.spin_limit)) {
                     report(P.status, QGEMV_ERR_TIMEOUT, 41, pos);
                     *abort_flag = 1;
@@ -342,103 +370,115 @@ __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsPara
                 }
                 const uint32_t bar = sbase + GsSmem::kBarPFull + 8 * s;
                 const uint32_t st = sbase + GsSmem::kRing0 + s * kPStage;
-                const uint32_t run_bytes = uint32_t(kUnitBytes) << rl;
                 mbar_arrive_expect_tx(bar, 8u * run_bytes);
                 const uint8_t* src = P.payload + (uint64_t(tile) * 8 * P.units + (uint64_t(u) << rl)) * kUnitBytes;
 #pragma unroll
                 for (int p = 0; p < 8; ++p)
                     bulk_g2s(st + p * run_bytes, src + uint64_t(p) * P.units * kUnitBytes, run_bytes, bar, pol);
-                if (++u == units) u = 0, ++tile;
+                if (++u == runs) u = 0, ++tile;
                 if (++s == kPStages) s = 0, ++use;
             }
         }
     } else if (warp == kGsWarpX) {
-        // ================= activation-tile producer =================
+        // ================= activation-tile producer: one stage = xg units, one bulk copy =================
         if (lane == 0) {
             pdl_wait();  // the tiles come from x_prep_kernel
-            int32_t pos = int32_t((int64_t(cta) * total) / grid) << rl;  // in units from here on
-            const int32_t end = int32_t((int64_t(cta + 1) * total) / grid) << rl;
-            int32_t u = pos % P.units;
+            const uint64_t keep = policy_evict_last();  // every CTA re-reads the tiles: hold them in L2
+            const int32_t c_begin = r_begin << (rl - xgl), c_end = r_end << (rl - xgl);  // in stages
+            const int32_t cpt = P.units >> xgl;                                         // stages per tile
+            int32_t c = c_begin % cpt;
             int s = 0;
             uint32_t use = 0;
-            for (; pos < end; ++pos) {
+            for (int32_t pos = c_begin; pos < c_end; ++pos) {
                 if (use > 0 && !mbar_wait(sbase + GsSmem::kBarXEmpty + 8 * s, (use - 1) & 1, P.spin_limit)) {
                     report(P.status, QGEMV_ERR_TIMEOUT, 46, pos);
                     *abort_flag = 1;
                     break;
                 }
                 const uint32_t bar = sbase + GsSmem::kBarXFull + 8 * s;
-                mbar_arrive_expect_tx(bar, x_bytes);
-                bulk_g2s_plain(xring + s * x_bytes, P.xt + uint64_t(u) * x_bytes, x_bytes, bar);
-                if (++u == P.units) u = 0;
+                mbar_arrive_expect_tx(bar, xs_bytes);
+                bulk_g2s(xring + s * xs_bytes, P.xt + uint64_t(c) * xs_bytes, xs_bytes, bar, keep);
+                if (++c == cpt) c = 0;
                 if (++s == x_stages) s = 0, ++use;
             }
         }
     } else if (warp == kGsWarpMma) {
-        // ================= MMA issuer =================
-        if (lane == 0) {
-            const uint32_t idesc = (1u << 4) | (uint32_t(M >> 3) << 17) | (uint32_t(128 >> 4) << 24);
-            GsWalker wk;
-            wk.init(total, units, cta, grid);
-            GsSeg sg;
-            int sa = 0, sx = 0;
-            uint32_t usea = 0, usex = 0, nseg = 0;
-            bool ok = true;
-            while (ok && wk.next(sg)) {
-                // the accumulator is free once the epilogue of the previous segment has read it
-                if (nseg > 0 && !mbar_wait(sbase + GsSmem::kBarDFree, (nseg - 1) & 1, P.spin_limit)) {
-                    report(P.status, QGEMV_ERR_TIMEOUT, 47, int(nseg));
+        // ===== MMA issuer: the warp runs the loop together, one elected lane issues.  Barriers are
+        // waited once per run (A) and once per activation stage, so the per-unit path is four MMAs =====
+        const bool issuer = elect_one();
+        const uint32_t idesc = (1u << 4) | (uint32_t(M >> 3) << 17) | (uint32_t(128 >> 4) << 24);
+        GsWalker wk;
+        wk.init(total, runs, cta, grid);
+        GsSeg sg;
+        int sa = 0, sx = 0;
+        uint32_t usea = 0, usex = 0, nseg = 0;
+        int32_t istep = 0;  // unit index inside the CTA's range
+        bool ok = true;
+        while (ok && wk.next(sg)) {
+            // the accumulator is free once the epilogue of the previous segment has read it
+            if (nseg > 0 && !mbar_wait(sbase + GsSmem::kBarDFree, (nseg - 1) & 1, P.spin_limit)) {
+                if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 47, int(nseg));
+                *abort_flag = 1;
+                ok = false;
+                break;
+            }
+            bool first = true;
+            for (int32_t rr = sg.u0; rr < sg.u1 && ok; ++rr) {
+                if (!mbar_wait(sbase + GsSmem::kBarAReady + 8 * sa, usea & 1, P.spin_limit)) {
+                    if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 42, rr);
                     *abort_flag = 1;
                     ok = false;
                     break;
                 }
-                const int ua = sg.u0 << rl, ub = sg.u1 << rl;
-                for (int u = ua; u < ub; ++u) {
-                    if (!mbar_wait(sbase + GsSmem::kBarAReady + 8 * sa, usea & 1, P.spin_limit) ||
-                        !mbar_wait(sbase + GsSmem::kBarXFull + 8 * sx, usex & 1, P.spin_limit)) {
-                        report(P.status, QGEMV_ERR_TIMEOUT, 42, u);
+                tc_fence_after();
+                for (int s = 0; s < run; ++s, ++istep) {
+                    const int xi = istep & (xg - 1);
+                    if (xi == 0 && !mbar_wait(sbase + GsSmem::kBarXFull + 8 * sx, usex & 1, P.spin_limit)) {
+                        if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 48, rr);
                         *abort_flag = 1;
                         ok = false;
                         break;
                     }
-                    tc_fence_after();
-                    const uint32_t xs = xring + sx * x_bytes;
+                    if (issuer) {
+                        const uint32_t xs = xring + sx * xs_bytes + xi * x_bytes;
+                        const uint32_t ta = tmem_base + acol0 + sa * a_cols + 32 * s;
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {  // four K=16 slabs: 8 TMEM columns / two 16-byte chunks each
-                        const uint64_t db = smem_desc(xs + j * 256, 128, 1024);
-                        tc_mma_f16_ts(tmem_base, tmem_base + acol0 + 32 * sa + 8 * j, db, idesc,
-                                      (u > ua || j > 0) ? 1u : 0u);
+                        for (int j = 0; j < 4; ++j) {  // four K=16 slabs: 8 TMEM columns / two 16-byte chunks each
+                            tc_mma_f16_ts(tmem_base, ta + 8 * j, smem_desc(xs + j * 256, 128, 1024), idesc,
+                                          (first && j == 0) ? 0u : 1u);
+                        }
+                        if (xi == xg - 1) tc_commit(sbase + GsSmem::kBarXEmpty + 8 * sx);  // stage reusable once these retire
                     }
-                    tc_commit(sbase + GsSmem::kBarAEmpty + 8 * sa);  // stages reusable once these MMAs retire
-                    tc_commit(sbase + GsSmem::kBarXEmpty + 8 * sx);
-                    if (++sa == kGsAStages) sa = 0, ++usea;
-                    if (++sx == x_stages) sx = 0, ++usex;
+                    first = false;
+                    if (xi == xg - 1 && ++sx == x_stages) sx = 0, ++usex;
                 }
-                tc_commit(sbase + GsSmem::kBarDone);
-                ++nseg;
+                if (issuer && ok) tc_commit(sbase + GsSmem::kBarAEmpty + 8 * sa);
+                __syncwarp();
+                if (++sa == kA) sa = 0, ++usea;
             }
+            if (issuer) tc_commit(sbase + GsSmem::kBarDone);
+            __syncwarp();
+            ++nseg;
         }
     } else {
         // ================= dequantisation warps; epilogue of each segment =================
         const int q = warp >> 2, wq = warp & 3;  // group, TMEM lane quarter
         GsWalker wk;
-        wk.init(total, units, cta, grid);
+        wk.init(total, runs, cta, grid);
         GsSeg sg;
-        // this group's next step, as an index into the CTA's range, and its ring positions
-        int32_t inext = q;
-        int sa = q % kGsAStages;
-        uint32_t usea = 0, nseg = 0;
-        int32_t seg_i0 = 0;  // index of the segment's first step
+        int32_t inext = q;   // this group's next unit, as an index into the CTA's range
+        int32_t seg_i0 = 0;  // index of the segment's first unit
+        uint32_t nseg = 0;
         bool ok = true;
         bool waited_x = false;
         const uint32_t lane_base = uint32_t(32 * wq) << 16;
         while (ok && wk.next(sg)) {
             const int32_t seg_i1 = seg_i0 + ((sg.u1 - sg.u0) << rl);
             for (; inext < seg_i1; inext += kGsGroups) {
-                // the TMEM stage is free once the MMAs of its previous use retired
-                const int32_t ri = inext >> rl;  // run index in the CTA's range -> packed ring position
-                const int sp = ri % kPStages;
-                const uint32_t usep = uint32_t(ri / kPStages);
+                const int32_t ri = inext >> rl;  // run index in the CTA's range -> ring positions
+                const int sp = ri % kPStages, sa = ri % kA;
+                const uint32_t usep = uint32_t(ri / kPStages), usea = uint32_t(ri / kA);
+                // the TMEM stage is free once the MMAs of the run that used it last retired
                 bool w_ok = usea == 0 || mbar_wait(sbase + GsSmem::kBarAEmpty + 8 * sa, (usea - 1) & 1, P.spin_limit);
                 w_ok = w_ok && mbar_wait(sbase + GsSmem::kBarPFull + 8 * sp, usep & 1, P.spin_limit);
                 if (!__all_sync(0xFFFFFFFFu, w_ok)) {
@@ -448,10 +488,10 @@ __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsPara
                     break;
                 }
                 tc_fence_after();
-                // stage layout: [panel][unit of the run]
-                const uint32_t st = sbase + GsSmem::kRing0 + sp * kPStage +
-                                    uint32_t(((2 * wq) << rl) + (inext & (run - 1))) * kUnitBytes;
-                const uint32_t ta = tmem_base + lane_base + acol0 + 32 * sa;
+                const int ui = inext & (run - 1);
+                // packed stage layout: [panel][unit of the run]
+                const uint32_t st = sbase + GsSmem::kRing0 + sp * kPStage + uint32_t(((2 * wq) << rl) + ui) * kUnitBytes;
+                const uint32_t ta = tmem_base + lane_base + acol0 + sa * a_cols + 32 * ui;
                 dequant_unit_to_tmem<FMT>(st, ta, lane);
                 dequant_unit_to_tmem<FMT>(st + (uint32_t(kUnitBytes) << rl), ta + (16u << 16), lane);
                 tmem_wait_st();
@@ -461,12 +501,10 @@ __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsPara
                     mbar_arrive(sbase + GsSmem::kBarAReady + 8 * sa);
                     mbar_arrive(sbase + GsSmem::kBarPEmpty + 8 * sp);
                 }
-                sa += kGsGroups;
-                if (sa >= kGsAStages) sa -= kGsAStages, ++usea;
             }
             seg_i0 = seg_i1;
             if (!ok) break;
-            // ---- epilogue: this warp owns TMEM lanes [32w, 32w+32) = rows n0 + 32w + lane ----
+            // ---- epilogue: this warp owns TMEM lanes [32wq, 32wq+32) and every third 8-column chunk ----
             if (!__all_sync(0xFFFFFFFFu, mbar_wait(sbase + GsSmem::kBarDone, nseg & 1, P.spin_limit))) {
                 if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 45, int(nseg));
                 *abort_flag = 1;
@@ -494,7 +532,7 @@ __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsPara
                     }
                 }
             };
-            if (sg.u0 == 0 && sg.u1 == units) {  // (runs) the segment is the whole tile
+            if (sg.u0 == 0 && sg.u1 == runs) {  // the segment is the whole tile
                 for (int c = 8 * q; c < M; c += 8 * kGsGroups) {
                     uint32_t r[8];
                     tmem_ld8(tmem_base + lane_base + uint32_t(c), r);
@@ -507,9 +545,9 @@ __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsPara
                 __syncwarp();
                 if (lane == 0) mbar_arrive(sbase + GsSmem::kBarDFree);
             } else {
-                // partial: park the fp32 sums, then the last contributor of (tile, lane quarter)
-                // adds all parts in CTA order
-                float* slot = P.ws + size_t(gs_slot(cta, sg.tile, units, total, grid)) * size_t(M) * 128;
+                // partial: park the fp32 sums, then the last contributor of (tile, warp) adds all
+                // parts in CTA order
+                float* slot = P.ws + size_t(gs_slot(cta, sg.tile, runs, total, grid)) * size_t(M) * 128;
                 for (int c = 8 * q; c < M; c += 8 * kGsGroups) {
                     uint32_t r[8];
                     tmem_ld8(tmem_base + lane_base + uint32_t(c), r);
@@ -521,8 +559,8 @@ __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsPara
                 if (lane == 0) mbar_arrive(sbase + GsSmem::kBarDFree);  // the next segment may start
                 __threadfence();
                 __syncwarp();
-                const int32_t c_lo = int32_t(cta_of(int64_t(sg.tile) * units, total, grid));
-                const int32_t c_hi = int32_t(cta_of(int64_t(sg.tile + 1) * units - 1, total, grid));
+                const int32_t c_lo = int32_t(cta_of(int64_t(sg.tile) * runs, total, grid));
+                const int32_t c_hi = int32_t(cta_of(int64_t(sg.tile + 1) * runs - 1, total, grid));
                 int old = 0;
                 if (lane == 0) old = atomicAdd(P.counters + sg.tile * 16 + warp, 1);
                 old = __shfl_sync(0xFFFFFFFFu, old, 0);
@@ -531,11 +569,11 @@ __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsPara
                     for (int c = 8 * q; c < M; c += 8 * kGsGroups) {
                         float v[8];
                         for (int32_t cc = c_lo; cc <= c_hi; ++cc) {
-                            const float* sl = P.ws + size_t(gs_slot(cc, sg.tile, units, total, grid)) * size_t(M) * 128;
+                            const float* sl = P.ws + size_t(gs_slot(cc, sg.tile, runs, total, grid)) * size_t(M) * 128;
 #pragma unroll
                             for (int i = 0; i < 8; ++i) {
-                                const float q = __ldcg(sl + (c + i) * 128 + row);
-                                v[i] = cc == c_lo ? q : v[i] + q;
+                                const float qv = __ldcg(sl + (c + i) * 128 + row);
+                                v[i] = cc == c_lo ? qv : v[i] + qv;
                             }
                         }
                         store_cols(c, v);

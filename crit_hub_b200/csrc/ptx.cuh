@@ -36,6 +36,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uin
         : "memory");
     return ok != 0;
 }
+// Non-blocking probe: a few cycles when the phase has already completed.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        " selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ uint64_t globaltimer_ns() {
     uint64_t t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -46,7 +57,7 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 // is followed by a short sleep (`sleep_ns`; longer for waiters that are off the critical path).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int64_t spin_limit,
                                           uint32_t sleep_ns = 32u) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_test_wait(bar, parity) || mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = globaltimer_ns();
     for (int64_t i = 0; i < spin_limit; ++i) {
         __nanosleep(sleep_ns);
@@ -60,6 +71,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int64_t
 __device__ __forceinline__ uint64_t policy_evict_first() {
     uint64_t pol;
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ uint64_t policy_evict_last() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
     return pol;
 }
 __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uint32_t bytes,
