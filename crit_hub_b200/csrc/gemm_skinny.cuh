@@ -33,9 +33,9 @@
 // contributor of the tile (atomic counter) adds all parts in CTA order -- deterministic.
 //
 // Warp roles (15 warps):
-//   0-11 three dequantising warpgroups; group q = warp / 4 takes the CTA's units i = q (mod 3), so the
-//        latency of one unit's conversion, tcgen05.st and barrier round trips overlaps the other
-//        groups' units.  Warp w handles panels 2(w%4), 2(w%4)+1 = TMEM lanes 32(w%4)..+31 (the lane
+//   0-11 three dequantising warpgroups; group q = warp / 4 takes the CTA's runs r = q (mod 3), so the
+//        latency of one run's conversion, tcgen05.st and barrier round trips overlaps the other
+//        groups' runs.  Warp w handles panels 2(w%4), 2(w%4)+1 = TMEM lanes 32(w%4)..+31 (the lane
 //        quarter a warp may access), and in the epilogue the same lanes of every third 8-column chunk
 //   12   one thread issues the bulk copies of packed weights (ring of 3-4 runs)
 //   13   allocates TMEM; the warp walks the runs together, one elected lane issues tcgen05.mma and
@@ -50,7 +50,7 @@
 
 namespace qg {
 
-constexpr int kGsGroups = 3;     // dequantising warpgroups; group q takes the CTA's steps i = q (mod 3)
+constexpr int kGsGroups = 3;     // dequantising warpgroups; group q takes the CTA's runs r = q (mod 3)
 constexpr int kGsDqWarps = 4 * kGsGroups;
 constexpr int kGsWarpP = kGsDqWarps, kGsWarpMma = kGsDqWarps + 1, kGsWarpX = kGsDqWarps + 2;
 constexpr int kGsThreads = 32 * (kGsDqWarps + 3);
@@ -328,14 +328,14 @@ __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsPara
     if (threadIdx.x == 0) {
         for (int s = 0; s < kPStages; ++s) {
             mbar_init(sbase + GsSmem::kBarPFull + 8 * s, 1);
-            mbar_init(sbase + GsSmem::kBarPEmpty + 8 * s, 4u << rl);  // four warps per unit of the run
+            mbar_init(sbase + GsSmem::kBarPEmpty + 8 * s, 4);  // the four warps of the group that converts the run
         }
         for (int s = 0; s < kGsXStagesMax; ++s) {
             mbar_init(sbase + GsSmem::kBarXFull + 8 * s, 1);
             mbar_init(sbase + GsSmem::kBarXEmpty + 8 * s, 1);
         }
         for (int s = 0; s < kGsAStagesMax; ++s) {
-            mbar_init(sbase + GsSmem::kBarAReady + 8 * s, 4u << rl);
+            mbar_init(sbase + GsSmem::kBarAReady + 8 * s, 4);
             mbar_init(sbase + GsSmem::kBarAEmpty + 8 * s, 1);
         }
         mbar_init(sbase + GsSmem::kBarDone, 1);
@@ -466,34 +466,38 @@ __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsPara
         GsWalker wk;
         wk.init(total, runs, cta, grid);
         GsSeg sg;
-        int32_t inext = q;   // this group's next unit, as an index into the CTA's range
-        int32_t seg_i0 = 0;  // index of the segment's first unit
+        // Each TMEM stage must always be refilled by the same group (a parity wait may not run more than
+        // one phase ahead of the barrier), so with two stages only two groups convert; all three
+        // share the epilogue.
+        const int ng = kA < kGsGroups ? kA : kGsGroups;
+        int32_t rnext = q < ng ? q : 0x7FFFFFF0;  // this group's next run, as an index into the CTA's range
+        int32_t seg_r0 = 0;  // index of the segment's first run
         uint32_t nseg = 0;
         bool ok = true;
         bool waited_x = false;
         const uint32_t lane_base = uint32_t(32 * wq) << 16;
         while (ok && wk.next(sg)) {
-            const int32_t seg_i1 = seg_i0 + ((sg.u1 - sg.u0) << rl);
-            for (; inext < seg_i1; inext += kGsGroups) {
-                const int32_t ri = inext >> rl;  // run index in the CTA's range -> ring positions
-                const int sp = ri % kPStages, sa = ri % kA;
-                const uint32_t usep = uint32_t(ri / kPStages), usea = uint32_t(ri / kA);
+            const int32_t seg_r1 = seg_r0 + (sg.u1 - sg.u0);
+            for (; rnext < seg_r1; rnext += ng) {
+                const int sp = rnext % kPStages, sa = rnext % kA;
+                const uint32_t usep = uint32_t(rnext / kPStages), usea = uint32_t(rnext / kA);
                 // the TMEM stage is free once the MMAs of the run that used it last retired
                 bool w_ok = usea == 0 || mbar_wait(sbase + GsSmem::kBarAEmpty + 8 * sa, (usea - 1) & 1, P.spin_limit);
                 w_ok = w_ok && mbar_wait(sbase + GsSmem::kBarPFull + 8 * sp, usep & 1, P.spin_limit);
                 if (!__all_sync(0xFFFFFFFFu, w_ok)) {
-                    if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 44, inext);
+                    if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 44, rnext);
                     *abort_flag = 1;
                     ok = false;
                     break;
                 }
                 tc_fence_after();
-                const int ui = inext & (run - 1);
-                // packed stage layout: [panel][unit of the run]
-                const uint32_t st = sbase + GsSmem::kRing0 + sp * kPStage + uint32_t(((2 * wq) << rl) + ui) * kUnitBytes;
-                const uint32_t ta = tmem_base + lane_base + acol0 + sa * a_cols + 32 * ui;
-                dequant_unit_to_tmem<FMT>(st, ta, lane);
-                dequant_unit_to_tmem<FMT>(st + (uint32_t(kUnitBytes) << rl), ta + (16u << 16), lane);
+                // packed stage layout: [panel][unit of the run]; this warp: panels 2wq, 2wq+1
+                const uint32_t st = sbase + GsSmem::kRing0 + sp * kPStage + uint32_t((2 * wq) << rl) * kUnitBytes;
+                const uint32_t ta = tmem_base + lane_base + acol0 + sa * a_cols;
+                for (int ui = 0; ui < run; ++ui) {
+                    dequant_unit_to_tmem<FMT>(st + ui * kUnitBytes, ta + 32 * ui, lane);
+                    dequant_unit_to_tmem<FMT>(st + (uint32_t(kUnitBytes) << rl) + ui * kUnitBytes, ta + 32 * ui + (16u << 16), lane);
+                }
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
@@ -502,7 +506,7 @@ __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsPara
                     mbar_arrive(sbase + GsSmem::kBarPEmpty + 8 * sp);
                 }
             }
-            seg_i0 = seg_i1;
+            seg_r0 = seg_r1;
             if (!ok) break;
             // ---- epilogue: this warp owns TMEM lanes [32wq, 32wq+32) and every third 8-column chunk ----
             if (!__all_sync(0xFFFFFFFFu, mbar_wait(sbase + GsSmem::kBarDone, nseg & 1, P.spin_limit))) {
