@@ -38,8 +38,8 @@
 //        groups' runs.  Warp w handles panels 2(w%4), 2(w%4)+1 = TMEM lanes 32(w%4)..+31 (the lane
 //        quarter a warp may access), and in the epilogue the same lanes of every third 8-column chunk
 //   12   one thread issues the bulk copies of packed weights (ring of 3-4 runs)
-//   13   allocates TMEM; the warp walks the runs together, one elected lane issues tcgen05.mma and
-//        the commits that free ring stages
+//   13   allocates TMEM; one elected lane walks the runs, issues tcgen05.mma and the commits that free
+//        ring stages
 //   14   one thread issues the bulk copies of activation tiles (L2 evict-last: every CTA re-reads them)
 // Every wait is bounded; TMEM is always released before the CTA exits.
 #pragma once
@@ -403,63 +403,64 @@ __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsPara
             }
         }
     } else if (warp == kGsWarpMma) {
-        // ===== MMA issuer: the warp runs the loop together, one elected lane issues.  Barriers are
-        // waited once per run (A) and once per activation stage, so the per-unit path is four MMAs =====
-        const bool issuer = elect_one();
-        const uint32_t idesc = (1u << 4) | (uint32_t(M >> 3) << 17) | (uint32_t(128 >> 4) << 24);
-        GsWalker wk;
-        wk.init(total, runs, cta, grid);
-        GsSeg sg;
-        int sa = 0, sx = 0;
-        uint32_t usea = 0, usex = 0, nseg = 0;
-        int32_t istep = 0;  // unit index inside the CTA's range
-        bool ok = true;
-        while (ok && wk.next(sg)) {
-            // the accumulator is free once the epilogue of the previous segment has read it
-            if (nseg > 0 && !mbar_wait(sbase + GsSmem::kBarDFree, (nseg - 1) & 1, P.spin_limit)) {
-                if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 47, int(nseg));
-                *abort_flag = 1;
-                ok = false;
-                break;
-            }
-            bool first = true;
-            for (int32_t rr = sg.u0; rr < sg.u1 && ok; ++rr) {
-                if (!mbar_wait(sbase + GsSmem::kBarAReady + 8 * sa, usea & 1, P.spin_limit)) {
-                    if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 42, rr);
+        // ===== MMA issuer: one elected lane runs the whole loop (entering a one-lane region per unit
+        // costs more than the four MMAs of a narrow tile).  Barriers are waited once per run (A) and
+        // once per activation stage, so the per-unit path is four tcgen05.mma =====
+        if (elect_one()) {
+            const uint32_t idesc = (1u << 4) | (uint32_t(M >> 3) << 17) | (uint32_t(128 >> 4) << 24);
+            GsWalker wk;
+            wk.init(total, runs, cta, grid);
+            GsSeg sg;
+            int sa = 0, sx = 0;
+            uint32_t usea = 0, usex = 0, nseg = 0;
+            int32_t istep = 0;  // unit index inside the CTA's range
+            bool ok = true;
+            while (ok && wk.next(sg)) {
+                // the accumulator is free once the epilogue of the previous segment has read it
+                if (nseg > 0 && !mbar_wait(sbase + GsSmem::kBarDFree, (nseg - 1) & 1, P.spin_limit)) {
+                    report(P.status, QGEMV_ERR_TIMEOUT, 47, int(nseg));
                     *abort_flag = 1;
                     ok = false;
                     break;
                 }
-                tc_fence_after();
-                for (int s = 0; s < run; ++s, ++istep) {
-                    const int xi = istep & (xg - 1);
-                    if (xi == 0 && !mbar_wait(sbase + GsSmem::kBarXFull + 8 * sx, usex & 1, P.spin_limit)) {
-                        if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 48, rr);
+                uint32_t acc = 0;  // the segment's first MMA overwrites D
+                for (int32_t rr = sg.u0; rr < sg.u1 && ok; ++rr) {
+                    if (!mbar_wait(sbase + GsSmem::kBarAReady + 8 * sa, usea & 1, P.spin_limit)) {
+                        report(P.status, QGEMV_ERR_TIMEOUT, 42, rr);
                         *abort_flag = 1;
                         ok = false;
                         break;
                     }
-                    if (issuer) {
-                        const uint32_t xs = xring + sx * xs_bytes + xi * x_bytes;
-                        const uint32_t ta = tmem_base + acol0 + sa * a_cols + 32 * s;
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {  // four K=16 slabs: 8 TMEM columns / two 16-byte chunks each
-                            tc_mma_f16_ts(tmem_base, ta + 8 * j, smem_desc(xs + j * 256, 128, 1024), idesc,
-                                          (first && j == 0) ? 0u : 1u);
+                    tc_fence_after();
+                    const uint32_t ta_run = tmem_base + acol0 + sa * a_cols;
+                    for (int s = 0; s < run; ++s, ++istep) {
+                        const int xi = istep & (xg - 1);
+                        if (xi == 0 && !mbar_wait(sbase + GsSmem::kBarXFull + 8 * sx, usex & 1, P.spin_limit)) {
+                            report(P.status, QGEMV_ERR_TIMEOUT, 48, rr);
+                            *abort_flag = 1;
+                            ok = false;
+                            break;
                         }
-                        if (xi == xg - 1) tc_commit(sbase + GsSmem::kBarXEmpty + 8 * sx);  // stage reusable once these retire
+                        const uint64_t db = smem_desc(xring + sx * xs_bytes + xi * x_bytes, 128, 1024);
+                        const uint32_t ta = ta_run + 32 * s;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {  // four K=16 slabs: 8 TMEM columns / two 16-byte chunks (+16 in the descriptor) each
+                            tc_mma_f16_ts(tmem_base, ta + 8 * j, db + uint64_t(16 * j), idesc, acc);
+                            acc = 1;
+                        }
+                        if (xi == xg - 1) {
+                            tc_commit(sbase + GsSmem::kBarXEmpty + 8 * sx);  // stage reusable once these retire
+                            if (++sx == x_stages) sx = 0, ++usex;
+                        }
                     }
-                    first = false;
-                    if (xi == xg - 1 && ++sx == x_stages) sx = 0, ++usex;
+                    if (ok) tc_commit(sbase + GsSmem::kBarAEmpty + 8 * sa);
+                    if (++sa == kA) sa = 0, ++usea;
                 }
-                if (issuer && ok) tc_commit(sbase + GsSmem::kBarAEmpty + 8 * sa);
-                __syncwarp();
-                if (++sa == kA) sa = 0, ++usea;
+                tc_commit(sbase + GsSmem::kBarDone);
+                ++nseg;
             }
-            if (issuer) tc_commit(sbase + GsSmem::kBarDone);
-            __syncwarp();
-            ++nseg;
         }
+        __syncwarp();
     } else {
         // ================= dequantisation warps; epilogue of each segment =================
         const int q = warp >> 2, wq = warp & 3;  // group, TMEM lane quarter
