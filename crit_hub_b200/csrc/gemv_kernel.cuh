@@ -476,7 +476,6 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams P) {
     }
     __syncthreads();
     pdl_launch_dependents();
-    if (P.debug & 16) return;
 
     // problem count: 1 for a dense GEMV, read from the router prep output for MoE
     int nprob = 1;
@@ -497,7 +496,6 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams P) {
         constexpr int kWarps = kConsumerWarps + kConverterWarps;
         unsigned int* rowmax = reinterpret_cast<unsigned int*>(smem_raw + Smem::kXExp) + 64;  // 8 words
         int* rowexp = reinterpret_cast<int*>(smem_raw + Smem::kXExp);                           // 8 words
-        if (P.debug & 32) return;
         RowRegs r0, r1;
         const int n_pairs = n_phases * Bl;
         const int i0 = wid, i1 = wid + kWarps;
@@ -512,7 +510,6 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams P) {
                                         min(P.units, (f_1 + 1) * QG_PHASE_UNITS), lane);
             if (lane == 0) atomicMax(rowmax + b_1, m);
         }
-        if (P.debug & 32) return;
         named_bar_sync(2, 32 * kWarps);
         if (i0 < n_pairs)
             store_row(r0, row_exponent(rowmax[b_0]), f_0, f_0 * QG_PHASE_UNITS,
@@ -552,7 +549,6 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams P) {
                 ++rcnt;
                 v.x *= ts, v.y *= ts, v.z *= ts, v.w *= ts;
                 const int32_t panel = int32_t(it.vp + pl);  // dense: virtual panel == panel
-                if (P.debug & 64) continue;
                 if (!it.partial) {
                     store_panel<FMT>(P, v, lane, panel, P.B, nullptr, P.chan_scale);
                 } else {
@@ -566,7 +562,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams P) {
         // ================= producer: stream weight blocks =================
         // debug bit 1 is a host-set fault injection: the producer issues no copy at all, so the
         // consumers' first wait must run out and report instead of hanging
-        if (lane == 0 && !(P.debug & (2 | 8))) {
+        if (lane == 0 && !(P.debug & 2)) {
             const uint64_t pol = policy_evict_first();
             ItemWalker wk;
             wk.init(total, P.units, P.n_panels, cta, grid);
@@ -715,14 +711,13 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams P) {
                         bfB[0] = x2.x, bfB[1] = x2.y, bfB[2] = x2.z, bfB[3] = x2.w;
                         bfB[4] = x3.x, bfB[5] = x3.y, bfB[6] = x3.z, bfB[7] = x3.w;
                     }
-                    if (!(P.debug & 8) && !mbar_wait(sbase + Smem::kBarFull + 8 * s, par, P.spin_limit)) {
+                    if (!mbar_wait(sbase + Smem::kBarFull + 8 * s, par, P.spin_limit)) {
                         if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 5, s);
                         *abort_flag = 1;
                         return;
                     }
                     const uint32_t st = sbase + Smem::kStage0 + s * kStageBytes + (uA - ua) * kUnitBytes;
-                    if (P.debug & 4) {
-                    } else if (haveA && haveB) {
+                    if (haveA && haveB) {
                         consume_two<FMT>(cA, cB, st, st + kUnitBytes, lane, bfA, bfB);
                     } else if (haveA) {
                         consume_unit<FMT>(cA, st, lane, bfA);
@@ -730,7 +725,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams P) {
                         consume_unit<FMT>(cB, st + kUnitBytes, lane, bfB);
                     }
                     __syncwarp();
-                    if (!(P.debug & 8) && lane == 0) mbar_arrive(sbase + Smem::kBarEmpty + 8 * s);
+                    if (lane == 0) mbar_arrive(sbase + Smem::kBarEmpty + 8 * s);
                     if (++s == kStages) {
                         s = 0;
                         par ^= 1u;

@@ -69,7 +69,11 @@ typedef struct qgemv_config {
     int32_t debug;         /* bit 0: kernels bounds-check every staged address and report through
                               the device status word instead of touching memory;
                               bit 1: fault injection for tests -- the weight copies are never
-                              issued, so the bounded waits must run out and report */
+                              issued, so the bounded waits must run out and report;
+                              bit 8: schedule override for tests -- dense GEMV and MoE use the
+                              general CTA-wide ring kernel instead of the per-warp streaming one;
+                              bit 9: schedule override for tests -- the streaming kernel always
+                              splits K across CTAs (partial sums + fixed-order fix-up) */
     int64_t spin_limit;    /* poll budget of every in-kernel wait; 0 = default */
 } qgemv_config;
 

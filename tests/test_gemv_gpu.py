@@ -99,6 +99,29 @@ def test_gemv_nvfp4_shapes(qg, handle, N, K, B):
     w.unload()
 
 
+@pytest.mark.parametrize("bits", [256, 512])
+@pytest.mark.parametrize("fmt", ["nvfp4", "fp8"])
+def test_gemv_schedule_overrides(qg, bits, fmt):
+    """The general ring kernel (bit 8) and the always-split streaming kernel (bit 9) on shapes the
+    default schedule would give to the whole-panel kernel: same oracle, same tolerance."""
+    h = qg.QGemv(debug_bits=bits, debug=True)
+    for (N, K, B) in [(4096, 4096, 1), (6144, 2048, 3), (1000, 2112, 8)]:
+        x = O.make_x(B, K, seed=N + B)
+        if fmt == "nvfp4":
+            codes, scales, ts = O.make_nvfp4(N, K, seed=N + K, ts=0.5)
+            w = h.load(qg.pack(qg.FMT_NVFP4, codes, scales, ts))
+            ref = O.gemv_nvfp4_f64(codes, scales, ts, x)
+        else:
+            codes, scales = O.make_fp8(N, K, seed=N + K)
+            w = h.load(qg.pack(qg.FMT_FP8, codes, scales))
+            ref = O.gemv_fp8_f64(codes, scales, x)
+        y = U.run_gemv(qg, h, w, x, h=h)
+        U.status_ok(h)
+        assert O.rel_l2(y, ref) < TOL_F32, (N, K, B)
+        w.unload()
+    h.close()
+
+
 @pytest.mark.parametrize("N,K,B", [(64, 128, 1), (4096, 4096, 4), (500, 1344, 8), (28672, 4096, 1)])
 def test_gemv_fp8_shapes(qg, handle, N, K, B):
     codes, scales = O.make_fp8(N, K, seed=N + K)
