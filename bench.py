@@ -1,6 +1,7 @@
 """Benchmark of the NVFP4 decode GEMV path: weight GB/s over a Llama-shaped layer stack.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl ours|reference]
+    python bench.py --workload prefill [--tokens M]      (secondary: tcgen05 skinny GEMM, one GPU)
 
 A "step" is one pass of the hot path over the whole layer stack (four weight-streaming GEMVs per
 layer) at decode batch B, replayed as one CUDA graph.  `value` = algorithmic weight bytes of all
@@ -199,6 +200,119 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def measured_peak_tflops():
+    """Measured dense bf16 burst peak of this pool's B200s (TFLOP/s), else the stated fallback."""
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["bf16_tflops"]), "measured"
+    except (OSError, KeyError, ValueError):
+        return 1590.0, "fallback"
+
+
+def run_prefill(args):
+    """Secondary workload: the tcgen05 skinny GEMM over the four projections of one
+    Llama-3-70B-shaped layer (481 MB of NVFP4 weights, larger than L2) at --tokens rows.
+    One step = the four GEMMs; value = 2*M*N*K flops of the layer / device time."""
+    import numpy as np
+    import torch
+
+    import crit_hub_b200 as qg
+    from crit_hub_b200.stack import llama_layer_shapes, synth_nvfp4
+
+    if int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        raise SystemExit("--workload prefill is a single-GPU workload")
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    M = args.tokens
+    model = LLAMA_70B
+    h = qg.QGemv(device=0, use_pdl=True)
+    shapes = llama_layer_shapes(model["hidden"], model["q_heads"], model["kv_heads"], model["head_dim"], model["inter"])
+    ws, xs, ys, xh, yh = [], [], [], [], []
+    g = torch.Generator()
+    g.manual_seed(11)
+    for mi, (name, N, K) in enumerate(shapes):
+        codes, scales = synth_nvfp4(N, K, 77 + mi, dev)
+        ws.append(h.load(qg.pack(qg.FMT_NVFP4, codes, scales, 1.0)))
+        xh.append(torch.randn((M, K), generator=g).to(torch.bfloat16).pin_memory())
+        xs.append(xh[-1].to(dev))
+        ys.append(torch.empty((M, N), dtype=torch.bfloat16, device=dev))
+        yh.append(torch.empty((M, N), dtype=torch.bfloat16).pin_memory())
+    flops = sum(2.0 * M * w.N * w.K for w in ws)
+    wbytes = sum(w.weight_bytes for w in ws)
+    stream = torch.cuda.Stream(device=dev)
+
+    def dev_step():
+        for w, x, y in zip(ws, xs, ys):
+            h.gemm_skinny(w, x.data_ptr(), M, y.data_ptr(), qg.OUT_BF16, stream=stream.cuda_stream)
+
+    def host_step():
+        with torch.cuda.stream(stream):
+            for x, xp in zip(xs, xh):
+                x.copy_(xp, non_blocking=True)
+        dev_step()
+        with torch.cuda.stream(stream):
+            for y, yp in zip(ys, yh):
+                yp.copy_(y, non_blocking=True)
+        stream.synchronize()
+
+    def timed(fn, n):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        with torch.cuda.stream(stream):
+            e0.record()
+        for _ in range(n):
+            fn()
+        with torch.cuda.stream(stream):
+            e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1)
+
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
+        dev_step()
+    sampler = ClockSampler(0)
+    sampler.start()
+    ms = timed(dev_step, args.steps)
+    clocks = sampler.stop()
+    host_step()
+    ms_host = timed(host_step, args.steps)
+    st = h.device_status(stream.cuda_stream)
+    if st.code != 0:
+        raise SystemExit(f"kernel reported {st}")
+    tf = flops * args.steps / (ms * 1e-3) / 1e12
+    tf_host = flops * args.steps / (ms_host * 1e-3) / 1e12
+    peak, kind = measured_peak_tflops()
+    line = {
+        "metric": "nvfp4_prefill_gemm_tflops", "value": round(tf, 1), "unit": "TFLOP/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": warmup, "ms_per_step": round(ms / args.steps, 5), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16 (fp32 accumulate in tensor memory)", "data": "synthetic",
+        "config": {"workload": f"llama-3-70b-shaped layer (qkv, o, gate_up, down), NVFP4 weights, {M} tokens, "
+                               "W4A16-exact tcgen05 skinny GEMM", "tokens": M, "flops_per_step": flops,
+                   "weight_bytes_per_step": wbytes, "tokens_per_s_one_layer": round(M / (ms / args.steps * 1e-3), 1),
+                   "cache": "weights per step (481 MB) exceed L2 (126 MB)"},
+        "roofline": {"bound": "tensor", "achieved": round(tf, 1), "peak": peak, "unit": "TFLOP/s",
+                     "frac": round(tf / peak, 4), "traffic": None, "peak_kind": kind + " bf16 burst",
+                     "kernel": "gemm_skinny_kernel<NVFP4>", "flops_per_launch": flops / 4,
+                     "us_per_launch": round(ms * 1e3 / (4 * args.steps), 2)},
+        "e2e": {"value": round(tf_host, 1), "unit": "TFLOP/s",
+                "h2d_bytes_per_step": sum(x.numel() * 2 for x in xh), "d2h_bytes_per_step": sum(y.numel() * 2 for y in yh),
+                "ms_per_step": round(ms_host / args.steps, 5)},
+        "gpu_launches": 8 * args.steps, "clocks": clocks,
+    }
+    if not args.no_cpu_baseline:
+        from oracle import oracle as O
+        codes, scales, ts = O.make_nvfp4(4096, 4096, seed=3)
+        x = O.make_x(min(M, 128), 4096, seed=3)
+        O.gemv_nvfp4_fast(codes, scales, ts, x)
+        t0 = time.perf_counter()
+        _, threads = O.gemv_nvfp4_fast(codes, scales, ts, x)
+        sec = time.perf_counter() - t0
+        line["cpu_baseline"] = {"value": round(2.0 * x.shape[0] * 4096 * 4096 / sec / 1e12, 5), "unit": "TFLOP/s",
+                                "cores": threads, "kind": "port",
+                                "sample": f"4096x4096 NVFP4 matrix, {x.shape[0]} tokens, one pass of the fp32 OpenMP port"}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -208,9 +322,15 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (profiling small cases)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
+                    help="decode: the headline GEMV layer stack; prefill: the skinny GEMM over one 70B-shaped layer")
+    ap.add_argument("--tokens", type=int, default=256, help="rows of the prefill workload (16..256, multiple of 16)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+        return
+    if args.workload == "prefill":
+        run_prefill(args)
         return
 
     import torch
