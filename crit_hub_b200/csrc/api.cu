@@ -50,6 +50,7 @@ struct qgemv_weight {
     int32_t* prob;           // MoE problem table (stacked weights only)
     int max_prob;
     float* host_tensor_scale; // [n_stack], host copy
+    float* acc;               // fp32 [QGEMV_MAX_BATCH][N] running sums of K-chunked calls (null: never chunked)
 };
 
 namespace {
@@ -112,6 +113,10 @@ qg::GemvParams base_params(const qgemv_handle* h, const qgemv_weight* w) {
     P.n_panels = int32_t(w->n_panels);
     P.units = int32_t(w->units);
     P.debug = h->cfg.debug;
+    P.unit_stride = int32_t(w->units);
+    P.x_stride = int32_t(w->K);
+    P.acc_mode = 0;
+    P.acc = w->acc;
     P.payload_bytes = w->payload_bytes;
     return P;
 }
@@ -120,19 +125,19 @@ int launch_gemv(const qgemv_handle* h, const qgemv_weight* w, const qg::GemvPara
                 cudaStream_t stream) {
     const dim3 grid(gemv_grid(h)), block(qg::kThreads);
     cudaError_t err;
-    if (qg::use_stream_path(P.prob == nullptr, P.B, w->units) && !(h->cfg.debug & 256)) {
+    if (qg::use_stream_path(P.prob == nullptr, P.B, P.units) && !(h->cfg.debug & 256)) {
         const dim3 sblock(qg::kSThreads);
         // whole panels per CTA (no cross-CTA fix-up) once every CTA gets at least one panel
         const bool whole = w->n_panels >= int64_t(grid.x) && !(h->cfg.debug & 512);
         if (w->fmt == QGEMV_FMT_NVFP4) {
             const size_t smem = qg::SSmem::total<QGEMV_FMT_NVFP4>();
-            const bool full = w->units % qg::StreamTraits<QGEMV_FMT_NVFP4>::kChunkUnits == 0;
+            const bool full = P.units % qg::StreamTraits<QGEMV_FMT_NVFP4>::kChunkUnits == 0;
             err = !whole ? launch(h, qg::gemv_stream_kernel<QGEMV_FMT_NVFP4>, grid, sblock, smem, stream, P)
                   : full ? launch(h, qg::gemv_stream_wp_kernel<QGEMV_FMT_NVFP4, true, 1>, grid, sblock, smem, stream, P)
                          : launch(h, qg::gemv_stream_wp_kernel<QGEMV_FMT_NVFP4, false, 1>, grid, sblock, smem, stream, P);
         } else {
             const size_t smem = qg::SSmem::total<QGEMV_FMT_FP8>();
-            const bool full = w->units % qg::StreamTraits<QGEMV_FMT_FP8>::kChunkUnits == 0;
+            const bool full = P.units % qg::StreamTraits<QGEMV_FMT_FP8>::kChunkUnits == 0;
             err = !whole ? launch(h, qg::gemv_stream_kernel<QGEMV_FMT_FP8>, grid, sblock, smem, stream, P)
                   : full ? launch(h, qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8, true, 1>, grid, sblock, smem, stream, P)
                          : launch(h, qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8, false, 1>, grid, sblock, smem, stream, P);
@@ -280,6 +285,10 @@ int qgemv_load_stacked(qgemv_handle* h, const void* host_blobs, size_t bytes_eac
               cudaMalloc(&w->dev_tensor_scale, size_t(n_stacked) * 4) == cudaSuccess &&
               cudaMalloc(&w->ws, ws_bytes) == cudaSuccess &&
               cudaMalloc(&w->counters, n_counters * 4) == cudaSuccess;
+    // dense matrices whose activations cannot be staged at once at batch 8 are multiplied in K chunks
+    // and need the running fp32 sums
+    if (ok && n_stacked == 1 && w->units * QGEMV_MAX_BATCH > qg::kSMaxUnitsTimesBatch)
+        ok = cudaMalloc(&w->acc, size_t(QGEMV_MAX_BATCH) * size_t(w->n_panels) * 16 * sizeof(float)) == cudaSuccess;
     if (ok && n_stacked > 1)
         ok = cudaMalloc(&w->prob, (size_t(w->max_prob) * qg::kProbInts + 1) * 4) == cudaSuccess;
     ok = ok && cudaMemcpy(w->dev_blob, src, size_t(n_stacked) * bytes_each, cudaMemcpyHostToDevice) == cudaSuccess &&
@@ -308,6 +317,7 @@ int qgemv_unload(qgemv_handle* h, qgemv_weight* w) {
     cudaFree(w->ws);
     cudaFree(w->counters);
     cudaFree(w->prob);
+    cudaFree(w->acc);
     delete[] w->host_tensor_scale;
     delete w;
     return QGEMV_OK;
@@ -336,10 +346,34 @@ int qgemv_gemv_prefetch(qgemv_handle* h, const qgemv_weight* w, const void* x_bf
     P.B = B;
     P.y_dtype = y_dtype;
     P.prob = nullptr;
-    if (next) {
-        P.pf_base = next->dev_blob + QG_HEADER_BYTES + next->aux_bytes;
-        P.pf_bytes = next->payload_bytes;
+    const uint8_t* pf_base = next ? next->dev_blob + QG_HEADER_BYTES + next->aux_bytes : nullptr;
+    const uint64_t pf_bytes = next ? next->payload_bytes : 0;
+    // Activations too large to stage at once (units * B > 512) on a matrix with at least a panel per
+    // CTA: multiply in K chunks, one launch of the whole-panel streaming kernel each, summed in
+    // stream order through the weight's fp32 scratch.  The chunk length depends on B, so here a
+    // row's result matches other batch sizes to fp32 rounding, not bit for bit.
+    const int unit_bytes = w->fmt == QGEMV_FMT_NVFP4 ? QG_NVFP4_UNIT_BYTES : QG_FP8_UNIT_BYTES;
+    if (!qg::use_stream_path(true, B, w->units) && w->acc && w->n_panels >= gemv_grid(h) &&
+        !(h->cfg.debug & (256 | 512))) {
+        const int64_t cu = (qg::kSMaxUnitsTimesBatch / B) / QG_PHASE_UNITS * QG_PHASE_UNITS;  // units per chunk
+        const int64_t n_chunks = (w->units + cu - 1) / cu;
+        for (int64_t c = 0; c < n_chunks; ++c) {
+            qg::GemvParams Pc = P;
+            const int64_t u0 = c * cu, u1 = std::min<int64_t>(w->units, u0 + cu);
+            Pc.payload = P.payload + uint64_t(u0) * unit_bytes;
+            Pc.payload_bytes = w->payload_bytes - uint64_t(u0) * unit_bytes;
+            Pc.x = P.x + u0 * QG_UNIT_K;
+            Pc.units = int32_t(u1 - u0);
+            Pc.K = int32_t(std::min<int64_t>(w->K - u0 * QG_UNIT_K, (u1 - u0) * QG_UNIT_K));
+            Pc.acc_mode = c == 0 ? 1 : (c + 1 == n_chunks ? 3 : 2);
+            if (c + 1 == n_chunks) Pc.pf_base = pf_base, Pc.pf_bytes = pf_bytes;
+            const int rc = launch_gemv(h, w, Pc, static_cast<cudaStream_t>(stream));
+            if (rc != QGEMV_OK) return rc;
+        }
+        return QGEMV_OK;
     }
+    P.pf_base = pf_base;
+    P.pf_bytes = pf_bytes;
     return launch_gemv(h, w, P, static_cast<cudaStream_t>(stream));
 }
 
@@ -652,6 +686,8 @@ int qgemv_gemv_noalloc(const void* dev_blob, const void* host_header, const void
     P.K = int32_t(hd.K);
     P.n_panels = int32_t(hd.n_panels);
     P.units = int32_t(hd.units_per_panel);
+    P.unit_stride = P.units;
+    P.x_stride = P.K;
     P.B = B;
     P.y_dtype = y_dtype;
     P.debug = 0;

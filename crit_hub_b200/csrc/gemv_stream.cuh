@@ -146,11 +146,11 @@ __device__ __forceinline__ void stream_convert_x(const GemvParams& P, unsigned c
     const int f_0 = i0 / Bl, b_0 = i0 - f_0 * Bl, f_1 = i1 / Bl, b_1 = i1 - f_1 * Bl;
     const int e_0 = min(units, (f_0 + 1) * QG_PHASE_UNITS), e_1 = min(units, (f_1 + 1) * QG_PHASE_UNITS);
     if (i0 < n_pairs) {
-        const uint32_t m = load_row(r0, P.x + int64_t(b_0) * P.K, P.K, f_0, f_0 * QG_PHASE_UNITS, e_0, lane);
+        const uint32_t m = load_row(r0, P.x + int64_t(b_0) * P.x_stride, P.K, f_0, f_0 * QG_PHASE_UNITS, e_0, lane);
         if (lane == 0) atomicMax(rowmax + b_0, m);
     }
     if (i1 < n_pairs) {
-        const uint32_t m = load_row(r1, P.x + int64_t(b_1) * P.K, P.K, f_1, f_1 * QG_PHASE_UNITS, e_1, lane);
+        const uint32_t m = load_row(r1, P.x + int64_t(b_1) * P.x_stride, P.K, f_1, f_1 * QG_PHASE_UNITS, e_1, lane);
         if (lane == 0) atomicMax(rowmax + b_1, m);
     }
     named_bar_sync(1, 32 * kSWarps);
@@ -451,7 +451,7 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_wp_kernel(const Gemv
     const bool drop = (P.debug & 2) != 0;  // host-set fault injection: never issue a copy
 
     // issue cursor: running byte offset of panel a's chunk, chunk counter, ring slot
-    const uint32_t panel_bytes = uint32_t(units) * kUnitBytes;  // a packed matrix is below 4 GB
+    const uint32_t panel_bytes = uint32_t(P.unit_stride) * kUnitBytes;  // a packed matrix is below 4 GB
     const int np_g = npc > gidx ? (npc - gidx + G - 1) / G : 0;  // panels of this group
     const int n_pairs = (np_g + PPI - 1) / PPI;
     uint32_t ioff = uint32_t(p0 + gidx) * panel_bytes + uint32_t(ck_lo) * kSlotBytes;

@@ -99,6 +99,35 @@ def test_gemv_nvfp4_shapes(qg, handle, N, K, B):
     w.unload()
 
 
+@pytest.mark.parametrize("N,K,B", [(4096, 14336, 8), (4096, 14336, 3), (8192, 8192, 5), (8192, 28672, 8),
+                                   (3000, 9280, 7), (2400, 4160, 8)])
+def test_gemv_k_chunked(qg, handle, N, K, B):
+    """Activations too large to stage at once: the call becomes several launches over K chunks whose
+    panel sums run through an fp32 scratch; bf16 output is rounded once, at the last chunk."""
+    codes, scales, ts = O.make_nvfp4(N, K, seed=N + K + B, ts=0.9)
+    x = O.make_x(B, K, seed=B * 7 + 1)
+    ref = O.gemv_nvfp4_f64(codes, scales, ts, x)
+    w = handle.load(qg.pack(qg.FMT_NVFP4, codes, scales, ts))
+    y32 = U.run_gemv(qg, handle, w, x)
+    y16 = U.run_gemv(qg, handle, w, x, out_f32=False)
+    U.status_ok(handle)
+    assert O.rel_l2(y32, ref) < TOL_F32
+    assert np.array_equal(y16, O.bf16_encode(y32))
+    assert np.array_equal(U.bits(y32), U.bits(U.run_gemv(qg, handle, w, x)))  # deterministic
+    w.unload()
+
+
+def test_gemv_k_chunked_fp8(qg, handle):
+    N, K, B = 4096, 8192, 8
+    codes, scales = O.make_fp8(N, K, seed=5)
+    x = O.make_x(B, K, seed=6)
+    w = handle.load(qg.pack(qg.FMT_FP8, codes, scales))
+    y = U.run_gemv(qg, handle, w, x)
+    U.status_ok(handle)
+    assert O.rel_l2(y, O.gemv_fp8_f64(codes, scales, x)) < TOL_F32
+    w.unload()
+
+
 @pytest.mark.parametrize("bits", [256, 512])
 @pytest.mark.parametrize("fmt", ["nvfp4", "fp8"])
 def test_gemv_schedule_overrides(qg, bits, fmt):
