@@ -394,7 +394,7 @@ int qgemv_gemm_skinny(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16
     const int grid = int(std::min<int64_t>(gemv_grid(h), total));
     // scratch: [tile counters, fixed place][row exponents][f16 activation tiles][partial tiles]
     const size_t cnt_bytes = size_t(kGsMaxTiles) * 16 * sizeof(int32_t);
-    const size_t exp_bytes = size_t(qg::kGsMaxM) * 4;
+    const size_t exp_bytes = size_t(qg::kGsMaxM) * 8;  // row exponents, then row maxima (zero between calls)
     const size_t xt_bytes = ((size_t(M) * size_t(w->K) * 2 + 255) / 256) * 256;
     const size_t ws_bytes = size_t(2) * grid * size_t(M) * 128 * sizeof(float);
     const size_t need = cnt_bytes + exp_bytes + xt_bytes + ws_bytes;
@@ -405,15 +405,19 @@ int qgemv_gemm_skinny(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16
         cudaFree(h->gs_ws);
         h->gs_ws = nullptr, h->gs_ws_bytes = 0;
         QG_CUDA(cudaMalloc(&h->gs_ws, need));
-        QG_CUDA(cudaMemset(h->gs_ws, 0, cnt_bytes));
+        QG_CUDA(cudaMemset(h->gs_ws, 0, cnt_bytes + exp_bytes));
         h->gs_ws_bytes = need;
     }
     int32_t* counters = reinterpret_cast<int32_t*>(h->gs_ws);
     int32_t* xexp = reinterpret_cast<int32_t*>(h->gs_ws + cnt_bytes);
     uint8_t* xt = h->gs_ws + cnt_bytes + exp_bytes;
     float* ws = reinterpret_cast<float*>(xt + xt_bytes);
-    if (launch(h, qg::x_prep_kernel, dim3(M), dim3(qg::kXPrepThreads), 0, st,
-               static_cast<const uint16_t*>(x_bf16), M, int(w->K), xt, xexp) != cudaSuccess)
+    unsigned int* rowmax = reinterpret_cast<unsigned int*>(xexp + qg::kGsMaxM);
+    const dim3 pgrid(unsigned((w->K + qg::kXPrepThreads * 8 - 1) / (qg::kXPrepThreads * 8)), unsigned(M));
+    if (launch(h, qg::x_rowmax_kernel, pgrid, dim3(qg::kXPrepThreads), 0, st, static_cast<const uint16_t*>(x_bf16),
+               int(w->K), rowmax) != cudaSuccess ||
+        launch(h, qg::x_prep_kernel, pgrid, dim3(qg::kXPrepThreads), 0, st, static_cast<const uint16_t*>(x_bf16), M,
+               int(w->K), static_cast<const unsigned int*>(rowmax), xt, xexp) != cudaSuccess)
         return QGEMV_ERR_CUDA;
     const int unit_bytes = w->fmt == QGEMV_FMT_NVFP4 ? QG_NVFP4_UNIT_BYTES : QG_FP8_UNIT_BYTES;
     qg::GsParams P;
@@ -423,6 +427,7 @@ int qgemv_gemm_skinny(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16
     P.tensor_scale = w->host_tensor_scale[0];
     P.xt = xt;
     P.xexp = xexp;
+    P.rowmax = rowmax;
     P.y = y;
     P.ws = ws;
     P.counters = counters;

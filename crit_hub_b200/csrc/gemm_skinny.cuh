@@ -67,6 +67,7 @@ struct GsParams {
     float tensor_scale;
     const uint8_t* xt;        // f16 activation tiles: [units][M/8][8 chunks][8 rows][8 slots]
     const int32_t* xexp;      // per token row: exponent E (x was scaled by 2^-E)
+    unsigned int* rowmax;     // x_rowmax_kernel's scratch; cleared here for the next call
     void* y;                  // [M][N]
     float* ws;                // partial tiles: slot (2*cta + which) of [M][128] fp32
     int32_t* counters;        // per row tile, zero between launches
@@ -176,23 +177,21 @@ __host__ __device__ __forceinline__ int gs_kslot(int k) {
     return 16 * (2 * pr + sub) + 4 * t + 2 * r + h;
 }
 
-// Activation preparation: one CTA per token row.  bf16 -> f16 scaled by 2^-E (row maximum into
-// [2^14, 2^15)), written in tile order: element (m, k), unit u = k / 64, position p = gs_kslot(k % 64):
+// Activation preparation, two small kernels over a grid of (2048-element segment, token row):
+// x_rowmax_kernel finds every row's largest |bf16| bit pattern (atomicMax into rowmax[], which is
+// zero between calls: the GEMM kernel clears it once it no longer needs it); x_prep_kernel
+// converts bf16 -> f16 scaled by 2^-E (row maximum into [2^14, 2^15)) and writes tile order:
+// element (m, k), unit u = k / 64, position p = gs_kslot(k % 64) goes to
 //   xt + u * (M*128) + (m/8)*1024 + (p/8)*128 + (m%8)*16 + (p%8)*2.
 constexpr int kXPrepThreads = 256;
-__global__ void __launch_bounds__(kXPrepThreads) x_prep_kernel(const uint16_t* x, int M, int K, uint8_t* xt,
-                                                               int32_t* xexp) {
-    __shared__ unsigned int smax;
-    __shared__ __align__(16) uint16_t seg[kXPrepThreads * 8];  // 2048 elements = 32 units
+__global__ void __launch_bounds__(kXPrepThreads) x_rowmax_kernel(const uint16_t* x, int K, unsigned int* rowmax) {
     pdl_launch_dependents();
     pdl_wait();
-    const int m = blockIdx.x;
-    if (threadIdx.x == 0) smax = 0u;
-    __syncthreads();
-    const uint16_t* xr = x + int64_t(m) * K;
+    const int m = blockIdx.y;
+    const int k = (blockIdx.x * kXPrepThreads + threadIdx.x) * 8;
     unsigned int mx = 0;
-    for (int k = threadIdx.x * 8; k < K; k += kXPrepThreads * 8) {
-        const uint4 v = __ldg(reinterpret_cast<const uint4*>(xr + k));
+    if (k < K) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(x + int64_t(m) * K + k));
         const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int z = 0; z < 4; ++z) {
@@ -201,33 +200,39 @@ __global__ void __launch_bounds__(kXPrepThreads) x_prep_kernel(const uint16_t* x
         }
     }
     mx = __reduce_max_sync(0xFFFFFFFFu, mx);
-    if ((threadIdx.x & 31) == 0) atomicMax(&smax, mx);
+    __shared__ unsigned int smax;
+    if (threadIdx.x == 0) smax = 0u;
     __syncthreads();
-    const int E = row_exponent(smax);
-    if (threadIdx.x == 0) xexp[m] = E;
+    if ((threadIdx.x & 31) == 0 && mx != 0) atomicMax(&smax, mx);
+    __syncthreads();
+    if (threadIdx.x == 0 && smax != 0) atomicMax(rowmax + m, smax);
+}
+__global__ void __launch_bounds__(kXPrepThreads) x_prep_kernel(const uint16_t* x, int M, int K, const unsigned int* rowmax,
+                                                               uint8_t* xt, int32_t* xexp) {
+    __shared__ __align__(16) uint16_t seg[kXPrepThreads * 8];  // 2048 elements = 32 units
+    pdl_launch_dependents();
+    pdl_wait();
+    const int m = blockIdx.y;
+    const int E = row_exponent(__ldcg(rowmax + m));
+    if (blockIdx.x == 0 && threadIdx.x == 0) xexp[m] = E;
     const float sf = pow2i(-E);
-    const size_t tile_bytes = size_t(M) * 128;
-    uint8_t* dst_row = xt + size_t(m >> 3) * 1024 + (m & 7) * 16;
-    for (int k0 = 0; k0 < K; k0 += kXPrepThreads * 8) {
-        const int k = k0 + threadIdx.x * 8;
-        if (k < K) {
-            const uint4 v = __ldg(reinterpret_cast<const uint4*>(xr + k));
-            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-            const int ubase = (threadIdx.x >> 3) * 64, kin = (threadIdx.x & 7) * 8;
+    const int k = (blockIdx.x * kXPrepThreads + threadIdx.x) * 8;
+    if (k < K) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(x + int64_t(m) * K + k));
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        const int ubase = (threadIdx.x >> 3) * 64, kin = (threadIdx.x & 7) * 8;
 #pragma unroll
-            for (int z = 0; z < 4; ++z) {
-                const uint32_t f = pack_f16x2(__uint_as_float(w[z] << 16) * sf, __uint_as_float(w[z] & 0xFFFF0000u) * sf);
-                seg[ubase + gs_kslot(kin + 2 * z)] = uint16_t(f & 0xFFFFu);
-                seg[ubase + gs_kslot(kin + 2 * z + 1)] = uint16_t(f >> 16);
-            }
+        for (int z = 0; z < 4; ++z) {
+            const uint32_t f = pack_f16x2(__uint_as_float(w[z] << 16) * sf, __uint_as_float(w[z] & 0xFFFF0000u) * sf);
+            seg[ubase + gs_kslot(kin + 2 * z)] = uint16_t(f & 0xFFFFu);
+            seg[ubase + gs_kslot(kin + 2 * z + 1)] = uint16_t(f >> 16);
         }
-        __syncthreads();
-        if (k < K) {
-            const uint4 o = *reinterpret_cast<const uint4*>(seg + threadIdx.x * 8);
-            const int u = k >> 6, chunk = (k & 63) >> 3;
-            *reinterpret_cast<uint4*>(dst_row + size_t(u) * tile_bytes + chunk * 128) = o;
-        }
-        __syncthreads();
+    }
+    __syncthreads();
+    if (k < K) {
+        const uint4 o = *reinterpret_cast<const uint4*>(seg + threadIdx.x * 8);
+        const int u = k >> 6, chunk = (k & 63) >> 3;
+        *reinterpret_cast<uint4*>(xt + size_t(u) * (size_t(M) * 128) + size_t(m >> 3) * 1024 + (m & 7) * 16 + chunk * 128) = o;
     }
 }
 
@@ -383,6 +388,8 @@ __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsPara
         // ================= activation-tile producer: one stage = xg units, one bulk copy =================
         if (lane == 0) {
             pdl_wait();  // the tiles come from x_prep_kernel
+            if (cta == 0)
+                for (int m = 0; m < M; ++m) P.rowmax[m] = 0u;  // x_prep_kernel has finished with it
             const uint64_t keep = policy_evict_last();  // every CTA re-reads the tiles: hold them in L2
             const int32_t c_begin = r_begin << (rl - xgl), c_end = r_end << (rl - xgl);  // in stages
             const int32_t cpt = P.units >> xgl;                                         // stages per tile

@@ -199,7 +199,7 @@ int qgemv_gemv_noalloc(const void* dev_blob, const void* host_header, const void
  * Shapes: single (unstacked) weight, N a multiple of 128, K a multiple of 64.
  * The call keeps an internal f16 copy of the activations (M*K*2 bytes); the first call with a
  * new largest M*K grows it with cudaMalloc after a device synchronise -- make that call outside
- * stream capture.  Two launches per call (activation preparation, GEMM). */
+ * stream capture.  Three launches per call (activation row maxima, activation conversion, GEMM). */
 #define QGEMV_ACT_A16_EXACT 0
 #define QGEMV_ACT_A4_BLOCKSCALED 1
 #define QGEMV_ACT_A8 2
