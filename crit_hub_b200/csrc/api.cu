@@ -436,8 +436,9 @@ int qgemv_gemm_skinny(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16
     P.units = int32_t(w->units);
     P.tiles = tiles;
     P.run_log2 = run_log2;
-    P.xg_log2 = qg::GsSmem::xg_log2(unit_bytes, M, run_log2);
+    P.xg_log2 = qg::GsSmem::xg_log2(M, run_log2);
     P.x_stages = qg::GsSmem::x_stages(unit_bytes, M, P.xg_log2);
+    P.p_stages = qg::GsSmem::p_stages(unit_bytes, M, P.xg_log2);
     P.status = h->status_dev;
     P.spin_limit = default_spin(h);
     P.debug = h->cfg.debug;

@@ -56,7 +56,7 @@ constexpr int kGsWarpP = kGsDqWarps, kGsWarpMma = kGsDqWarps + 1, kGsWarpX = kGs
 constexpr int kGsThreads = 32 * (kGsDqWarps + 3);
 constexpr int kGsMaxM = 256;
 constexpr int kGsRunMax = 4;     // units of one panel fetched by one bulk copy (a run); also the pipeline's grain
-constexpr int kGsPStagesMax = 4; // packed-weight ring: stages of 8 panels x one run
+constexpr int kGsPStagesMax = 10; // packed-weight ring: stages of 8 panels x one run
 constexpr int kGsAStagesMax = 3; // dequantised-weight ring in TMEM: stages of one run (32 columns per unit)
 constexpr int kGsXStagesMax = 16;
 constexpr int kGsSmemBudget = 227 * 1024;
@@ -76,6 +76,7 @@ struct GsParams {
     int32_t units;            // K / 64
     int32_t tiles;            // N / 128
     int32_t x_stages;
+    int32_t p_stages;
     int32_t run_log2;         // log2(units per run): 2, 1 or 0, the largest that divides K / 64
     int32_t xg_log2;          // log2(units per activation-ring stage), <= run_log2
     int32_t* status;
@@ -85,35 +86,46 @@ struct GsParams {
 
 struct GsSmem {
     static constexpr int kBarPFull = 0;      // kGsPStagesMax
-    static constexpr int kBarPEmpty = 32;    // kGsPStagesMax
-    static constexpr int kBarXFull = 64;     // kGsXStagesMax
-    static constexpr int kBarXEmpty = 192;   // kGsXStagesMax
-    static constexpr int kBarAReady = 320;   // kGsAStagesMax
-    static constexpr int kBarAEmpty = 344;   // kGsAStagesMax
-    static constexpr int kBarDone = 368;
-    static constexpr int kBarDFree = 376;
-    static constexpr int kTmemPtr = 384;
-    static constexpr int kAbort = 388;
-    static constexpr int kBarDrain = 392;
+    static constexpr int kBarPEmpty = 80;    // kGsPStagesMax
+    static constexpr int kBarXFull = 160;    // kGsXStagesMax
+    static constexpr int kBarXEmpty = 288;   // kGsXStagesMax
+    static constexpr int kBarAReady = 416;   // kGsAStagesMax
+    static constexpr int kBarAEmpty = 440;   // kGsAStagesMax
+    static constexpr int kBarDone = 464;
+    static constexpr int kBarDFree = 472;
+    static constexpr int kTmemPtr = 480;
+    static constexpr int kAbort = 484;
+    static constexpr int kBarDrain = 488;
     static constexpr int kRing0 = 1024;
+    // Layout: [barriers][activation ring: x_stages x (M*128 << xg_log2)][packed ring: p_stages x
+    // packed_stage].  Both rings sit between a producer and the MMAs with a memory latency of a few
+    // thousand cycles in the loop, so what matters is how many RUNS each holds: the budget is split
+    // so that the two depths (in runs) are about equal.
     __host__ __device__ static constexpr int packed_stage(int unit_bytes) { return 8 * kGsRunMax * unit_bytes; }
-    // four stages of NVFP4 runs (72 KB), three of FP8 (96 KB)
-    __host__ __device__ static constexpr int p_stages(int unit_bytes) { return unit_bytes > 600 ? 3 : kGsPStagesMax; }
-    __host__ __device__ static constexpr int x_off(int unit_bytes) { return kRing0 + p_stages(unit_bytes) * packed_stage(unit_bytes); }
-    // activation ring: stages of (1 << xg_log2) units, as many as fit behind the packed ring
-    __host__ __device__ static int x_stages(int unit_bytes, int M, int xg_log2) {
-        const int n = (kGsSmemBudget - x_off(unit_bytes)) / ((M * 128) << xg_log2);
-        return n > kGsXStagesMax ? kGsXStagesMax : n;
+    // activation stage grain: the largest (<= the run) whose stage is at most 32 KB
+    __host__ __device__ static int xg_log2(int M, int run_log2) {
+        int g = run_log2;
+        while (g > 0 && ((M * 128) << g) > 32768) --g;
+        return g;
     }
-    // largest stage grain (<= the run) that still leaves four stages, else three
-    __host__ __device__ static int xg_log2(int unit_bytes, int M, int run_log2) {
-        for (int want = 4; want >= 3; --want)
-            for (int g = run_log2; g >= 0; --g)
-                if (x_stages(unit_bytes, M, g) >= want) return g;
-        return 0;
+    __host__ __device__ static int x_stages(int unit_bytes, int M, int xg_log2) {
+        const int budget = kGsSmemBudget - kRing0;
+        const int per_run = M * 128 * kGsRunMax + packed_stage(unit_bytes);
+        int n = (budget / per_run) * kGsRunMax + ((budget % per_run) * kGsRunMax) / per_run;  // depth in units
+        n >>= xg_log2;                                                                       // in stages
+        const int keep_p = (budget - 3 * packed_stage(unit_bytes)) / ((M * 128) << xg_log2);  // leave >= 3 packed stages
+        n = n > keep_p ? keep_p : n;
+        return n > kGsXStagesMax ? kGsXStagesMax : (n < 2 ? 2 : n);
+    }
+    __host__ __device__ static int p_off(int unit_bytes, int M, int xg_log2) {
+        return kRing0 + x_stages(unit_bytes, M, xg_log2) * ((M * 128) << xg_log2);
+    }
+    __host__ __device__ static int p_stages(int unit_bytes, int M, int xg_log2) {
+        const int n = (kGsSmemBudget - p_off(unit_bytes, M, xg_log2)) / packed_stage(unit_bytes);
+        return n > kGsPStagesMax ? kGsPStagesMax : n;
     }
     __host__ __device__ static int total(int unit_bytes, int M, int xg_log2) {
-        return x_off(unit_bytes) + x_stages(unit_bytes, M, xg_log2) * ((M * 128) << xg_log2);
+        return p_off(unit_bytes, M, xg_log2) + p_stages(unit_bytes, M, xg_log2) * packed_stage(unit_bytes);
     }
 };
 
@@ -304,7 +316,6 @@ template <int FMT>
 __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsParams P) {
     constexpr int kUnitBytes = FmtTraits<FMT>::kUnitBytes;
     constexpr int kPStage = GsSmem::packed_stage(kUnitBytes);
-    constexpr int kPStages = GsSmem::p_stages(kUnitBytes);
     extern __shared__ __align__(128) unsigned char gs_smem[];
     const uint32_t sbase = smem_u32(gs_smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -319,8 +330,9 @@ __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsPara
     const int32_t r_end = int32_t((int64_t(cta + 1) * total) / grid);
     const uint32_t x_bytes = uint32_t(M) * 128u;       // one unit of activations
     const uint32_t xs_bytes = x_bytes << xgl;          // one stage of the activation ring
-    const uint32_t xring = sbase + GsSmem::x_off(kUnitBytes);
-    const int x_stages = P.x_stages;
+    const uint32_t xring = sbase + GsSmem::kRing0;
+    const int x_stages = P.x_stages, kPStages = P.p_stages;
+    const uint32_t pring = xring + uint32_t(x_stages) * xs_bytes;
     // TMEM: D in columns [0, M); behind it the A ring, kA stages of one run (32 columns per unit)
     const uint32_t a_cols = 32u << rl;
     const int kA = (M + 3 * int(a_cols) <= 512) ? 3 : 2;
@@ -331,7 +343,7 @@ __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsPara
     volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(gs_smem + GsSmem::kTmemPtr);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kPStages; ++s) {
+        for (int s = 0; s < kGsPStagesMax; ++s) {
             mbar_init(sbase + GsSmem::kBarPFull + 8 * s, 1);
             mbar_init(sbase + GsSmem::kBarPEmpty + 8 * s, 4);  // the four warps of the group that converts the run
         }
@@ -374,7 +386,7 @@ __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsPara
                     break;
                 }
                 const uint32_t bar = sbase + GsSmem::kBarPFull + 8 * s;
-                const uint32_t st = sbase + GsSmem::kRing0 + s * kPStage;
+                const uint32_t st = pring + s * kPStage;
                 mbar_arrive_expect_tx(bar, 8u * run_bytes);
                 const uint8_t* src = P.payload + (uint64_t(tile) * 8 * P.units + (uint64_t(u) << rl)) * kUnitBytes;
 #pragma unroll
@@ -500,7 +512,7 @@ __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsPara
                 }
                 tc_fence_after();
                 // packed stage layout: [panel][unit of the run]; this warp: panels 2wq, 2wq+1
-                const uint32_t st = sbase + GsSmem::kRing0 + sp * kPStage + uint32_t((2 * wq) << rl) * kUnitBytes;
+                const uint32_t st = pring + sp * kPStage + uint32_t((2 * wq) << rl) * kUnitBytes;
                 const uint32_t ta = tmem_base + lane_base + acol0 + sa * a_cols;
                 for (int ui = 0; ui < run; ++ui) {
                     dequant_unit_to_tmem<FMT>(st + ui * kUnitBytes, ta + 32 * ui, lane);
