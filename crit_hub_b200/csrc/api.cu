@@ -33,6 +33,8 @@ struct qgemv_handle {
     // skinny GEMM: f16 activation tiles + per-row exponents, grown on demand
     uint8_t* gs_ws;
     size_t gs_ws_bytes;
+    // K-chunked GEMV: fp32 partial results [chunk][B][N], fixed size, allocated with the handle
+    float* chunk_ws;
 };
 
 struct qgemv_weight {
@@ -50,7 +52,6 @@ struct qgemv_weight {
     int32_t* prob;           // MoE problem table (stacked weights only)
     int max_prob;
     float* host_tensor_scale; // [n_stack], host copy
-    float* acc;               // fp32 [QGEMV_MAX_BATCH][N] running sums of K-chunked calls (null: never chunked)
 };
 
 namespace {
@@ -67,6 +68,7 @@ thread_local cudaError_t g_last_cuda_error = cudaSuccess;
     } while (0)
 
 constexpr int kMaxMoeSlots = 4096;
+constexpr size_t kChunkWsBytes = size_t(16) << 20;  // partial results of a K-chunked GEMV
 constexpr int kGsMaxTiles = 4096;  // skinny GEMM: 128-row tiles a handle keeps counters for
 
 int64_t default_spin(const qgemv_handle* h) {
@@ -115,8 +117,6 @@ qg::GemvParams base_params(const qgemv_handle* h, const qgemv_weight* w) {
     P.debug = h->cfg.debug;
     P.unit_stride = int32_t(w->units);
     P.x_stride = int32_t(w->K);
-    P.acc_mode = 0;
-    P.acc = w->acc;
     P.payload_bytes = w->payload_bytes;
     return P;
 }
@@ -200,7 +200,9 @@ int qgemv_init(const qgemv_config* cfg, qgemv_handle** out) {
     h->tp_local = nullptr, h->tp_epochs = nullptr;
     for (int i = 0; i < qg::kTpMaxWorld; ++i) h->tp_peer[i] = nullptr;
     h->gs_ws = nullptr, h->gs_ws_bytes = 0;
-    if (cudaMalloc(&h->status_dev, 4 * sizeof(int32_t)) != cudaSuccess ||
+    h->chunk_ws = nullptr;
+    if (cudaMalloc(&h->chunk_ws, kChunkWsBytes) != cudaSuccess ||
+        cudaMalloc(&h->status_dev, 4 * sizeof(int32_t)) != cudaSuccess ||
         cudaMemset(h->status_dev, 0, 4 * sizeof(int32_t)) != cudaSuccess) {
         delete h;
         return QGEMV_ERR_CUDA;
@@ -236,6 +238,7 @@ int qgemv_destroy(qgemv_handle* h) {
     cudaFree(h->tp_local);
     cudaFree(h->tp_epochs);
     cudaFree(h->gs_ws);
+    cudaFree(h->chunk_ws);
     cudaFree(h->status_dev);
     delete h;
     return QGEMV_OK;
@@ -285,10 +288,6 @@ int qgemv_load_stacked(qgemv_handle* h, const void* host_blobs, size_t bytes_eac
               cudaMalloc(&w->dev_tensor_scale, size_t(n_stacked) * 4) == cudaSuccess &&
               cudaMalloc(&w->ws, ws_bytes) == cudaSuccess &&
               cudaMalloc(&w->counters, n_counters * 4) == cudaSuccess;
-    // dense matrices whose activations cannot be staged at once at batch 8 are multiplied in K chunks
-    // and need the running fp32 sums
-    if (ok && n_stacked == 1 && w->units * QGEMV_MAX_BATCH > qg::kSMaxUnitsTimesBatch)
-        ok = cudaMalloc(&w->acc, size_t(QGEMV_MAX_BATCH) * size_t(w->n_panels) * 16 * sizeof(float)) == cudaSuccess;
     if (ok && n_stacked > 1)
         ok = cudaMalloc(&w->prob, (size_t(w->max_prob) * qg::kProbInts + 1) * 4) == cudaSuccess;
     ok = ok && cudaMemcpy(w->dev_blob, src, size_t(n_stacked) * bytes_each, cudaMemcpyHostToDevice) == cudaSuccess &&
@@ -317,7 +316,6 @@ int qgemv_unload(qgemv_handle* h, qgemv_weight* w) {
     cudaFree(w->ws);
     cudaFree(w->counters);
     cudaFree(w->prob);
-    cudaFree(w->acc);
     delete[] w->host_tensor_scale;
     delete w;
     return QGEMV_OK;
@@ -349,28 +347,36 @@ int qgemv_gemv_prefetch(qgemv_handle* h, const qgemv_weight* w, const void* x_bf
     const uint8_t* pf_base = next ? next->dev_blob + QG_HEADER_BYTES + next->aux_bytes : nullptr;
     const uint64_t pf_bytes = next ? next->payload_bytes : 0;
     // Activations too large to stage at once (units * B > 512) on a matrix with at least a panel per
-    // CTA: multiply in K chunks, one launch of the whole-panel streaming kernel each, summed in
-    // stream order through the weight's fp32 scratch.  The chunk length depends on B, so here a
-    // row's result matches other batch sizes to fp32 rounding, not bit for bit.
+    // CTA: multiply in K chunks, one launch of the whole-panel streaming kernel each into its own
+    // fp32 slice of the handle's scratch, then add the slices in chunk order and round once.  The
+    // chunk length depends on B, so here a row's result matches other batch sizes to fp32 rounding,
+    // not bit for bit.  Calls that share a handle share the scratch: keep them on one stream.
     const int unit_bytes = w->fmt == QGEMV_FMT_NVFP4 ? QG_NVFP4_UNIT_BYTES : QG_FP8_UNIT_BYTES;
-    if (!qg::use_stream_path(true, B, w->units) && w->acc && w->n_panels >= gemv_grid(h) &&
+    if (!qg::use_stream_path(true, B, w->units) && w->n_stack == 1 && w->n_panels >= gemv_grid(h) &&
         !(h->cfg.debug & (256 | 512))) {
         const int64_t cu = (qg::kSMaxUnitsTimesBatch / B) / QG_PHASE_UNITS * QG_PHASE_UNITS;  // units per chunk
         const int64_t n_chunks = (w->units + cu - 1) / cu;
-        for (int64_t c = 0; c < n_chunks; ++c) {
-            qg::GemvParams Pc = P;
-            const int64_t u0 = c * cu, u1 = std::min<int64_t>(w->units, u0 + cu);
-            Pc.payload = P.payload + uint64_t(u0) * unit_bytes;
-            Pc.payload_bytes = w->payload_bytes - uint64_t(u0) * unit_bytes;
-            Pc.x = P.x + u0 * QG_UNIT_K;
-            Pc.units = int32_t(u1 - u0);
-            Pc.K = int32_t(std::min<int64_t>(w->K - u0 * QG_UNIT_K, (u1 - u0) * QG_UNIT_K));
-            Pc.acc_mode = c == 0 ? 1 : (c + 1 == n_chunks ? 3 : 2);
-            if (c + 1 == n_chunks) Pc.pf_base = pf_base, Pc.pf_bytes = pf_bytes;
-            const int rc = launch_gemv(h, w, Pc, static_cast<cudaStream_t>(stream));
-            if (rc != QGEMV_OK) return rc;
+        const int64_t slice = int64_t(B) * w->N;
+        if (size_t(n_chunks * slice) * sizeof(float) <= kChunkWsBytes) {
+            cudaStream_t st = static_cast<cudaStream_t>(stream);
+            for (int64_t c = 0; c < n_chunks; ++c) {
+                qg::GemvParams Pc = P;
+                const int64_t u0 = c * cu, u1 = std::min<int64_t>(w->units, u0 + cu);
+                Pc.payload = P.payload + uint64_t(u0) * unit_bytes;
+                Pc.payload_bytes = w->payload_bytes - uint64_t(u0) * unit_bytes;
+                Pc.x = P.x + u0 * QG_UNIT_K;
+                Pc.units = int32_t(u1 - u0);
+                Pc.K = int32_t(std::min<int64_t>(w->K - u0 * QG_UNIT_K, (u1 - u0) * QG_UNIT_K));
+                Pc.y = h->chunk_ws + c * slice;
+                Pc.y_dtype = QGEMV_OUT_F32;
+                if (c + 1 == n_chunks) Pc.pf_base = pf_base, Pc.pf_bytes = pf_bytes;
+                const int rc = launch_gemv(h, w, Pc, st);
+                if (rc != QGEMV_OK) return rc;
+            }
+            const cudaError_t err = launch(h, qg::chunk_sum_kernel, dim3(unsigned((slice + 255) / 256)), dim3(256), 0, st,
+                                           static_cast<const float*>(h->chunk_ws), int(n_chunks), slice, y, y_dtype);
+            return err == cudaSuccess ? QGEMV_OK : QGEMV_ERR_CUDA;
         }
-        return QGEMV_OK;
     }
     P.pf_base = pf_base;
     P.pf_bytes = pf_bytes;

@@ -190,4 +190,19 @@ __global__ void moe_combine_kernel(const void* slot_out, int slot_dtype, const f
     }
 }
 
+// K-chunked GEMV: y = sum over chunks (in chunk order) of the fp32 partial results, rounded once.
+__global__ void chunk_sum_kernel(const float* parts, int n_chunks, int64_t n, void* y, int y_dtype) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float v = __ldcg(parts + i);
+    for (int c = 1; c < n_chunks; ++c) v += __ldcg(parts + int64_t(c) * n + i);
+    if (y_dtype == QGEMV_OUT_F32) {
+        static_cast<float*>(y)[i] = v;
+    } else {
+        static_cast<__nv_bfloat16*>(y)[i] = __float2bfloat16_rn(v);
+    }
+}
+
 }  // namespace qg

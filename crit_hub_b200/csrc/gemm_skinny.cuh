@@ -380,7 +380,7 @@ __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsPara
             int s = 0;
             uint32_t use = 0;
             for (int32_t pos = r_begin; pos < r_end; ++pos) {
-                if (use > 0 && !mbar_wait(sbase + GsSmem::kBarPEmpty + 8 * s, (use - 1) & 1, P.spin_limit)) {
+                if (use > 0 && !mbar_wait_probe(sbase + GsSmem::kBarPEmpty + 8 * s, (use - 1) & 1, P.spin_limit)) {
                     report(P.status, QGEMV_ERR_TIMEOUT, 41, pos);
                     *abort_flag = 1;
                     break;
@@ -409,7 +409,7 @@ __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsPara
             int s = 0;
             uint32_t use = 0;
             for (int32_t pos = c_begin; pos < c_end; ++pos) {
-                if (use > 0 && !mbar_wait(sbase + GsSmem::kBarXEmpty + 8 * s, (use - 1) & 1, P.spin_limit)) {
+                if (use > 0 && !mbar_wait_probe(sbase + GsSmem::kBarXEmpty + 8 * s, (use - 1) & 1, P.spin_limit)) {
                     report(P.status, QGEMV_ERR_TIMEOUT, 46, pos);
                     *abort_flag = 1;
                     break;
@@ -436,7 +436,7 @@ __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsPara
             bool ok = true;
             while (ok && wk.next(sg)) {
                 // the accumulator is free once the epilogue of the previous segment has read it
-                if (nseg > 0 && !mbar_wait(sbase + GsSmem::kBarDFree, (nseg - 1) & 1, P.spin_limit)) {
+                if (nseg > 0 && !mbar_wait_probe(sbase + GsSmem::kBarDFree, (nseg - 1) & 1, P.spin_limit)) {
                     report(P.status, QGEMV_ERR_TIMEOUT, 47, int(nseg));
                     *abort_flag = 1;
                     ok = false;
@@ -444,7 +444,7 @@ __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsPara
                 }
                 uint32_t acc = 0;  // the segment's first MMA overwrites D
                 for (int32_t rr = sg.u0; rr < sg.u1 && ok; ++rr) {
-                    if (!mbar_wait(sbase + GsSmem::kBarAReady + 8 * sa, usea & 1, P.spin_limit)) {
+                    if (!mbar_wait_probe(sbase + GsSmem::kBarAReady + 8 * sa, usea & 1, P.spin_limit)) {
                         report(P.status, QGEMV_ERR_TIMEOUT, 42, rr);
                         *abort_flag = 1;
                         ok = false;
@@ -454,7 +454,7 @@ __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsPara
                     const uint32_t ta_run = tmem_base + acol0 + sa * a_cols;
                     for (int s = 0; s < run; ++s, ++istep) {
                         const int xi = istep & (xg - 1);
-                        if (xi == 0 && !mbar_wait(sbase + GsSmem::kBarXFull + 8 * sx, usex & 1, P.spin_limit)) {
+                        if (xi == 0 && !mbar_wait_probe(sbase + GsSmem::kBarXFull + 8 * sx, usex & 1, P.spin_limit)) {
                             report(P.status, QGEMV_ERR_TIMEOUT, 48, rr);
                             *abort_flag = 1;
                             ok = false;
@@ -502,8 +502,8 @@ __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsPara
                 const int sp = rnext % kPStages, sa = rnext % kA;
                 const uint32_t usep = uint32_t(rnext / kPStages), usea = uint32_t(rnext / kA);
                 // the TMEM stage is free once the MMAs of the run that used it last retired
-                bool w_ok = usea == 0 || mbar_wait(sbase + GsSmem::kBarAEmpty + 8 * sa, (usea - 1) & 1, P.spin_limit);
-                w_ok = w_ok && mbar_wait(sbase + GsSmem::kBarPFull + 8 * sp, usep & 1, P.spin_limit);
+                bool w_ok = usea == 0 || mbar_wait_probe(sbase + GsSmem::kBarAEmpty + 8 * sa, (usea - 1) & 1, P.spin_limit);
+                w_ok = w_ok && mbar_wait_probe(sbase + GsSmem::kBarPFull + 8 * sp, usep & 1, P.spin_limit);
                 if (!__all_sync(0xFFFFFFFFu, w_ok)) {
                     if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 44, rnext);
                     *abort_flag = 1;
@@ -529,7 +529,7 @@ __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsPara
             seg_r0 = seg_r1;
             if (!ok) break;
             // ---- epilogue: this warp owns TMEM lanes [32wq, 32wq+32) and every third 8-column chunk ----
-            if (!__all_sync(0xFFFFFFFFu, mbar_wait(sbase + GsSmem::kBarDone, nseg & 1, P.spin_limit))) {
+            if (!__all_sync(0xFFFFFFFFu, mbar_wait_probe(sbase + GsSmem::kBarDone, nseg & 1, P.spin_limit))) {
                 if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 45, int(nseg));
                 *abort_flag = 1;
                 ok = false;
@@ -618,7 +618,7 @@ __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsPara
             // let whatever MMAs were issued retire before the columns are handed back (bounded)
             if (lane == 0) {
                 tc_commit(sbase + GsSmem::kBarDrain);
-                (void)mbar_wait(sbase + GsSmem::kBarDrain, 0, int64_t(1) << 16);
+                (void)mbar_wait_probe(sbase + GsSmem::kBarDrain, 0, int64_t(1) << 16);
             }
             __syncwarp();
         }

@@ -78,11 +78,9 @@ struct GemvParams {
     int32_t y_dtype;
     int32_t debug;
     // K-chunked calls (dense, activations too large to stage at once): the launch covers `units`
-    // units of every panel starting at `payload`; panels are `unit_stride` units apart, activation
-    // rows `x_stride` elements apart, and the panel sums go through the fp32 scratch `acc`
-    // ([B][N]): acc_mode 0 none, 1 first chunk (write acc), 2 middle (acc += sum), 3 last (y = acc + sum)
-    int32_t unit_stride, x_stride, acc_mode;
-    float* acc;
+    // units of every panel starting at `payload`; panels are `unit_stride` units apart and
+    // activation rows `x_stride` elements apart
+    int32_t unit_stride, x_stride;
     uint64_t payload_bytes;     // per stacked weight, for debug bounds checks
     const uint8_t* pf_base;     // optional: payload of the weight the caller will use next
     uint64_t pf_bytes;          // bytes of it to pull into L2 while this GEMV runs (0 = none)
@@ -325,14 +323,7 @@ __device__ __forceinline__ void store_panel(const GemvParams& P, float4 v, int l
         const int n = (i & 2) ? n1 : n0;
         if (col < nrows && n < P.N) {
             const int64_t idx = int64_t(pr ? __ldcg(pr + 10 + col) : col) * P.N + n;
-            float val = vals[i];
-            if (P.acc_mode != 0) {  // K-chunked call: chunks are separate launches in stream order
-                if (P.acc_mode != 1) val += __ldcg(P.acc + idx);
-                if (P.acc_mode != 3) {
-                    __stcg(P.acc + idx, val);
-                    continue;
-                }
-            }
+            const float val = vals[i];
             if (P.y_dtype == QGEMV_OUT_F32) {
                 static_cast<float*>(P.y)[idx] = val;
             } else {

@@ -57,7 +57,7 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 // is followed by a short sleep (`sleep_ns`; longer for waiters that are off the critical path).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int64_t spin_limit,
                                           uint32_t sleep_ns = 32u) {
-    if (mbar_test_wait(bar, parity) || mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = globaltimer_ns();
     for (int64_t i = 0; i < spin_limit; ++i) {
         __nanosleep(sleep_ns);
@@ -65,6 +65,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int64_t
         if ((i & 63) == 63 && globaltimer_ns() - t0 > 2000000000ull) return false;
     }
     return false;
+}
+
+// The same for waiters that usually find the phase already complete: the non-blocking probe
+// costs 14 cycles against 46 for try_wait with its suspend hint.
+__device__ __forceinline__ bool mbar_wait_probe(uint32_t bar, uint32_t parity, int64_t spin_limit,
+                                                uint32_t sleep_ns = 32u) {
+    return mbar_test_wait(bar, parity) || mbar_wait(bar, parity, spin_limit, sleep_ns);
 }
 
 // ---- bulk async copy global -> shared (TMA, no tensor map, no multicast) -----------------------
