@@ -31,7 +31,7 @@ class LayerStack:
     """Owns an activation arena [sum B*K] bf16 and an output arena [sum B*N]; one GEMV per weight."""
 
     def __init__(self, handle: QGemv, weights: list[Weight], batch: int, out_dtype: int = OUT_BF16,
-                 device: int = 0, prefetch_next: bool = True, after_call=None):
+                 device: int = 0, prefetch_next: bool = False, after_call=None):
         self.handle, self.batch, self.out_dtype = handle, batch, out_dtype
         # after_call(i): optional hook enqueued on the same stream right after GEMV i (and captured
         # with it), e.g. the all-reduce of a row-parallel projection's partial outputs
