@@ -373,25 +373,27 @@ __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsPara
 
     if (warp == kGsWarpP) {
         // ================= packed-weight producer: one stage = 8 panels x one run =================
-        if (lane == 0 && !(P.debug & 2)) {
+        // Eight lanes issue the eight panels' copies with one instruction each turn (a single thread
+        // issuing them back to back spends longer per run than the copies take to arrive).
+        if (lane < 8 && !(P.debug & 2)) {
             const uint64_t pol = policy_evict_first();
             int32_t tile = r_begin / runs, u = r_begin - tile * runs;
             const uint32_t run_bytes = uint32_t(kUnitBytes) << rl;
             int s = 0;
             uint32_t use = 0;
             for (int32_t pos = r_begin; pos < r_end; ++pos) {
-                if (use > 0 && !mbar_wait_probe(sbase + GsSmem::kBarPEmpty + 8 * s, (use - 1) & 1, P.spin_limit)) {
-                    report(P.status, QGEMV_ERR_TIMEOUT, 41, pos);
+                bool ok = use == 0 || mbar_wait_probe(sbase + GsSmem::kBarPEmpty + 8 * s, (use - 1) & 1, P.spin_limit);
+                if (!__all_sync(0xFFu, ok)) {
+                    if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 41, pos);
                     *abort_flag = 1;
                     break;
                 }
                 const uint32_t bar = sbase + GsSmem::kBarPFull + 8 * s;
                 const uint32_t st = pring + s * kPStage;
-                mbar_arrive_expect_tx(bar, 8u * run_bytes);
+                if (lane == 0) mbar_arrive_expect_tx(bar, 8u * run_bytes);
+                __syncwarp(0xFFu);
                 const uint8_t* src = P.payload + (uint64_t(tile) * 8 * P.units + (uint64_t(u) << rl)) * kUnitBytes;
-#pragma unroll
-                for (int p = 0; p < 8; ++p)
-                    bulk_g2s(st + p * run_bytes, src + uint64_t(p) * P.units * kUnitBytes, run_bytes, bar, pol);
+                bulk_g2s(st + lane * run_bytes, src + uint64_t(lane) * P.units * kUnitBytes, run_bytes, bar, pol);
                 if (++u == runs) u = 0, ++tile;
                 if (++s == kPStages) s = 0, ++use;
             }
