@@ -32,6 +32,13 @@ ERR_BOUNDS = -7
 ERR_NO_DEVICE = -8
 
 
+class SkinnyPlan(C.Structure):
+    """qgemv_skinny_plan: how qgemv_gemm_skinny would run a shape."""
+    _fields_ = [("run_units", C.c_int32), ("x_stage_units", C.c_int32), ("x_stages", C.c_int32),
+                ("p_stages", C.c_int32), ("a_stages", C.c_int32), ("tmem_columns", C.c_int32),
+                ("smem_bytes", C.c_int32), ("ctas", C.c_int32), ("scratch_bytes", C.c_int64)]
+
+
 class QgemvError(RuntimeError):
     def __init__(self, status: int, what: str):
         super().__init__(f"{what}: {status_string(status)} ({status})")
@@ -96,6 +103,7 @@ def _load() -> C.CDLL:
     L.qgemv_gemv.argtypes = [vp, vp, vp, i32, vp, i32, vp]
     L.qgemv_gemv_prefetch.argtypes = [vp, vp, vp, i32, vp, i32, vp, vp]
     L.qgemv_gemm_skinny.argtypes = [vp, vp, vp, i32, vp, i32, i32, vp]
+    L.qgemv_gemm_skinny_plan.argtypes = [i32, i64, i64, i32, i32, C.POINTER(SkinnyPlan)]
     L.qgemv_tp_create.argtypes = [vp, i32, i32, i64, vp]
     L.qgemv_tp_connect.argtypes = [vp, vp]
     L.qgemv_tp_allreduce.argtypes = [vp, vp, i32, i64, vp]
@@ -295,3 +303,10 @@ def gemv_noalloc(dev_blob_ptr: int, host_blob: np.ndarray, x_ptr: int, B: int, y
     kernel's scratch is a static array inside the library (see include/qgemv.h for the limits)."""
     _check(_load().qgemv_gemv_noalloc(dev_blob_ptr, _np_ptr(host_blob), x_ptr, B, y_ptr, y_dtype, stream),
            "gemv_noalloc")
+
+
+def gemm_skinny_plan(fmt: int, N: int, K: int, M: int, sm_count: int = 148) -> SkinnyPlan:
+    """Pure host arithmetic: ring depths, tensor- and shared-memory use of a skinny GEMM shape."""
+    plan = SkinnyPlan()
+    _check(_load().qgemv_gemm_skinny_plan(fmt, N, K, M, sm_count, C.byref(plan)), "gemm_skinny_plan")
+    return plan

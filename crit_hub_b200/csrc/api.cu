@@ -335,9 +335,19 @@ int qgemv_gemv(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, int B
 int qgemv_gemv_prefetch(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, int B, void* y,
                         int y_dtype, const qgemv_weight* next, void* stream) {
     if (!h || !w || !x_bf16 || !y) return QGEMV_ERR_INVALID_ARG;
-    if (B < 1 || B > QGEMV_MAX_BATCH) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+    if (B < 1 || B > QGEMV_MAX_ROWS) return QGEMV_ERR_UNSUPPORTED_SHAPE;
     if (y_dtype != QGEMV_OUT_BF16 && y_dtype != QGEMV_OUT_F32) return QGEMV_ERR_INVALID_ARG;
     if ((reinterpret_cast<uintptr_t>(x_bf16) & 15u) != 0) return QGEMV_ERR_INVALID_ARG;
+    if (B > QGEMV_MAX_BATCH) {
+        // two launches: rows 0..7, then the rest (the second one names the next matrix)
+        if ((w->K * 2 * QGEMV_MAX_BATCH) % 16 != 0) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+        const int rc = qgemv_gemv_prefetch(h, w, x_bf16, QGEMV_MAX_BATCH, y, y_dtype, nullptr, stream);
+        if (rc != QGEMV_OK) return rc;
+        const size_t ye = y_dtype == QGEMV_OUT_F32 ? 4 : 2;
+        return qgemv_gemv_prefetch(h, w, static_cast<const uint16_t*>(x_bf16) + int64_t(QGEMV_MAX_BATCH) * w->K,
+                                   B - QGEMV_MAX_BATCH, static_cast<uint8_t*>(y) + size_t(QGEMV_MAX_BATCH) * w->N * ye,
+                                   y_dtype, next, stream);
+    }
     qg::GemvParams P = base_params(h, w);
     P.x = static_cast<const uint16_t*>(x_bf16);
     P.y = y;
@@ -381,6 +391,29 @@ int qgemv_gemv_prefetch(qgemv_handle* h, const qgemv_weight* w, const void* x_bf
     P.pf_base = pf_base;
     P.pf_bytes = pf_bytes;
     return launch_gemv(h, w, P, static_cast<cudaStream_t>(stream));
+}
+
+int qgemv_gemm_skinny_plan(int fmt, int64_t N, int64_t K, int M, int sm_count, qgemv_skinny_plan* out) {
+    if (!out || (fmt != QGEMV_FMT_NVFP4 && fmt != QGEMV_FMT_FP8) || sm_count < 1) return QGEMV_ERR_INVALID_ARG;
+    if (M < 16 || M > qg::kGsMaxM || M % 16 != 0 || N < 128 || N % 128 != 0 || K < 64 || K % 64 != 0 ||
+        N / 128 > kGsMaxTiles)
+        return QGEMV_ERR_UNSUPPORTED_SHAPE;
+    const int unit_bytes = fmt == QGEMV_FMT_NVFP4 ? QG_NVFP4_UNIT_BYTES : QG_FP8_UNIT_BYTES;
+    const int64_t units = K / 64, tiles = N / 128;
+    const int rl = units % 4 == 0 ? 2 : (units % 2 == 0 ? 1 : 0);
+    const int xgl = qg::GsSmem::xg_log2(M, rl);
+    const int64_t total = tiles * (units >> rl);
+    out->run_units = 1 << rl;
+    out->x_stage_units = 1 << xgl;
+    out->x_stages = qg::GsSmem::x_stages(unit_bytes, M, xgl);
+    out->p_stages = qg::GsSmem::p_stages(unit_bytes, M, xgl);
+    out->a_stages = qg::GsSmem::a_stages(M, rl);
+    out->tmem_columns = qg::GsSmem::tmem_columns(M, rl);
+    out->smem_bytes = qg::GsSmem::total(unit_bytes, M, xgl);
+    out->ctas = int32_t(std::min<int64_t>(sm_count, total));
+    out->scratch_bytes = int64_t(kGsMaxTiles) * 16 * 4 + int64_t(qg::kGsMaxM) * 8 + ((int64_t(M) * K * 2 + 255) / 256) * 256 +
+                         int64_t(2) * out->ctas * M * 128 * 4;
+    return QGEMV_OK;
 }
 
 int qgemv_gemm_skinny(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, int M, void* y,

@@ -127,6 +127,14 @@ struct GsSmem {
     __host__ __device__ static int total(int unit_bytes, int M, int xg_log2) {
         return p_off(unit_bytes, M, xg_log2) + p_stages(unit_bytes, M, xg_log2) * packed_stage(unit_bytes);
     }
+    // Tensor memory: D in columns [0, M); behind it the A ring, three stages of one run (32 columns
+    // per unit) when they fit 512 columns, else two; the allocation is the next power of two.
+    __host__ __device__ static int a_stages(int M, int run_log2) { return M + 3 * (32 << run_log2) <= 512 ? 3 : 2; }
+    __host__ __device__ static int tmem_columns(int M, int run_log2) {
+        int n = 32;
+        while (n < M + a_stages(M, run_log2) * (32 << run_log2)) n <<= 1;
+        return n;
+    }
 };
 
 // ---- tcgen05 wrappers ----------------------------------------------------------------------------
@@ -335,9 +343,8 @@ __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsPara
     const uint32_t pring = xring + uint32_t(x_stages) * xs_bytes;
     // TMEM: D in columns [0, M); behind it the A ring, kA stages of one run (32 columns per unit)
     const uint32_t a_cols = 32u << rl;
-    const int kA = (M + 3 * int(a_cols) <= 512) ? 3 : 2;
-    uint32_t ncols = 32;
-    while (ncols < uint32_t(M) + kA * a_cols) ncols <<= 1;
+    const int kA = GsSmem::a_stages(M, rl);
+    const uint32_t ncols = uint32_t(GsSmem::tmem_columns(M, rl));
     const uint32_t acol0 = ncols - kA * a_cols;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gs_smem + GsSmem::kAbort);
     volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(gs_smem + GsSmem::kTmemPtr);

@@ -56,7 +56,8 @@ enum {
 
 enum { QGEMV_OUT_BF16 = 0, QGEMV_OUT_F32 = 1 };
 
-#define QGEMV_MAX_BATCH 8 /* activation rows per gemv call (decode batch / draft width) */
+#define QGEMV_MAX_BATCH 8 /* activation rows per kernel launch (decode batch / draft width) */
+#define QGEMV_MAX_ROWS 16 /* activation rows per gemv call: 9..16 run as two launches (LM head at batch 16) */
 
 typedef struct qgemv_handle qgemv_handle;
 typedef struct qgemv_weight qgemv_weight;
@@ -130,7 +131,7 @@ int qgemv_unload(qgemv_handle* h, qgemv_weight* w);
 /* Algorithmic weight bytes of one matrix: N*K*0.5625 + 4 (NVFP4) or N*K + 4*N (FP8). */
 int64_t qgemv_weight_bytes(const qgemv_weight* w);
 
-/* ---- decode GEMV, batch 1..8 -------------------------------------------------------------------
+/* ---- decode GEMV, batch 1..8 (up to 16 rows per call as two launches) -------------------------
  * y[b][n] = sum_k dequant(W)[n][k] * x[b][k], fp32 accumulation, output bf16 or fp32.
  * x: device bf16 [B][K] row-major; y: device [B][N] row-major.
  * The decode rows / decode-gemv of engines/crit-labs/mtp5-nvfp4-drafts/card.yaml:77 and the
@@ -138,7 +139,11 @@ int64_t qgemv_weight_bytes(const qgemv_weight* w);
  * ("hardware E2M1 conversion into mma.m16n8k16 ... one instruction stream for every column
  * count").  As there, row b of the result does not depend on B, and the split along K is fixed
  * by the shape and the CTA count, never by timing ("column invariant with a deterministic split
- * along K", tools/fixtures/engines/crit-labs/mtp-adaptive-width/card.yaml:77). */
+ * along K", tools/fixtures/engines/crit-labs/mtp-adaptive-width/card.yaml:77).  Exception: where
+ * K * B exceeds 32768 elements the call is split along K in chunks whose length depends on B, and
+ * a row then matches other batch sizes to fp32 rounding only.  B = 9..16 (the output head at batch
+ * 16, engines/crit-labs/mtp5-nvfp4-drafts/card.yaml:77) streams the matrix twice: rows 0..7, then
+ * the rest. */
 int qgemv_gemv(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, int B, void* y,
                int y_dtype, void* stream);
 /* Same GEMV; additionally pulls the packed weight `next` (nullable) into L2 while this GEMV runs.
@@ -205,6 +210,21 @@ int qgemv_gemv_noalloc(const void* dev_blob, const void* host_header, const void
 #define QGEMV_ACT_A8 2
 int qgemv_gemm_skinny(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, int M, void* y,
                       int y_dtype, int act_mode, void* stream);
+/* How qgemv_gemm_skinny would run a shape: pipeline grain, ring depths, tensor-memory and shared-
+ * memory use, CTA count and scratch bytes.  Pure host arithmetic (no device needed); returns
+ * QGEMV_ERR_UNSUPPORTED_SHAPE for shapes the GEMM refuses.  No counterpart in the reference. */
+typedef struct qgemv_skinny_plan {
+    int32_t run_units;      /* K units (of 64) per pipeline run: 4, 2 or 1 */
+    int32_t x_stage_units;  /* K units per activation-ring stage */
+    int32_t x_stages;       /* activation-ring stages in shared memory */
+    int32_t p_stages;       /* packed-weight ring stages (8 panels x one run each) */
+    int32_t a_stages;       /* dequantised-weight stages in tensor memory */
+    int32_t tmem_columns;   /* tensor-memory columns allocated per CTA (power of two <= 512) */
+    int32_t smem_bytes;     /* dynamic shared memory per CTA */
+    int32_t ctas;           /* CTAs launched */
+    int64_t scratch_bytes;  /* internal scratch the call needs (activation tiles, partial tiles, counters) */
+} qgemv_skinny_plan;
+int qgemv_gemm_skinny_plan(int fmt, int64_t N, int64_t K, int M, int sm_count, qgemv_skinny_plan* out);
 
 /* ---- MoE grouped GEMV ---------------------------------------------------------------------------
  * One launch walks the router's top-k lists.  For every token t and slot j:

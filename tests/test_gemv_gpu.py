@@ -227,13 +227,27 @@ def test_activation_ranges(qg, handle):
     w.unload()
 
 
+def test_lm_head_batch_16(qg, handle):
+    """Rows 9..16 of one call run as a second launch: FP8 head with fp32 logits, 16 rows."""
+    N, K, B = 4000, 1024, 16
+    codes, scales = O.make_fp8(N, K, seed=8)
+    x = O.make_x(B, K, seed=9)
+    w = handle.load(qg.pack(qg.FMT_FP8, codes, scales))
+    y = U.run_gemv(qg, handle, w, x)
+    U.status_ok(handle)
+    assert O.rel_l2(y, O.gemv_fp8_f64(codes, scales, x)) < TOL_F32
+    y11 = U.run_gemv(qg, handle, w, x[:11])
+    assert np.array_equal(U.bits(y[:11]), U.bits(y11))
+    w.unload()
+
+
 def test_bad_arguments(qg, handle):
     codes, scales, ts = O.make_nvfp4(16, 64, seed=1)
     w = handle.load(qg.pack(qg.FMT_NVFP4, codes, scales, ts))
     import torch
-    x = torch.zeros(9 * 64, dtype=torch.bfloat16, device="cuda")
-    y = torch.zeros(9 * 16, dtype=torch.float32, device="cuda")
-    for B in (0, 9, -1):
+    x = torch.zeros(17 * 64, dtype=torch.bfloat16, device="cuda")
+    y = torch.zeros(17 * 16, dtype=torch.float32, device="cuda")
+    for B in (0, 17, -1):
         with pytest.raises(qg.QgemvError) as e:
             handle.gemv(w, x.data_ptr(), B, y.data_ptr(), qg.OUT_F32)
         assert e.value.status == qg.ERR_UNSUPPORTED_SHAPE
