@@ -30,6 +30,8 @@ def test_cta_count_and_scratch(qg):
     assert p.ctas == 1 and p.run_units == 1
     p = qg.gemm_skinny_plan(qg.FMT_NVFP4, 57344, 8192, 256)
     assert p.ctas == 148 and p.run_units == 4 and p.a_stages == 2 and p.tmem_columns == 512
+    assert qg.gemm_skinny_plan(qg.FMT_NVFP4, 8192, 8192, 256).ctas == 128    # 64 tiles x 2 K parts
+    assert qg.gemm_skinny_plan(qg.FMT_NVFP4, 10240, 8192, 256).ctas == 80   # 80 tiles, one CTA each
     assert p.scratch_bytes >= 256 * 8192 * 2 + 2 * 148 * 256 * 128 * 4
     p = qg.gemm_skinny_plan(qg.FMT_NVFP4, 57344, 8192, 128)
     assert p.a_stages == 3 and p.tmem_columns == 512
