@@ -26,7 +26,7 @@ def run_skinny(qg, handle, w, x_bf16, out_f32=True):
 
 
 @pytest.mark.parametrize("N,K,M", [(128, 64, 16), (128, 256, 16), (256, 512, 64), (384, 1088, 48),
-                                   (1024, 4096, 128), (256, 2048, 256), (2048, 8192, 32)])
+                                   (1024, 4096, 128), (256, 2048, 256), (2048, 8192, 32), (128, 36864, 16)])
 def test_skinny_nvfp4(qg, handle, N, K, M):
     codes, scales, ts = O.make_nvfp4(N, K, seed=N + K + M, ts=0.75)
     x = O.make_x(M, K, seed=M + K)
