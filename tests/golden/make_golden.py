@@ -62,5 +62,36 @@ def main() -> None:
     print("wrote", os.path.join(HERE, "qgemv_golden.npz"))
 
 
+def main_skinny() -> None:
+    """Seeded skinny-GEMM cases (several token rows, N a multiple of 128) with fp64 results, from the
+    third-party codecs only; a file of its own so that the GEMV vectors above stay byte-identical."""
+    e2m1 = np.arange(16, dtype=np.uint8).view(ml_dtypes.float4_e2m1fn).astype(np.float64)
+    e4m3 = np.arange(256, dtype=np.uint8).view(ml_dtypes.float8_e4m3fn).astype(np.float64)
+    rng = np.random.Generator(np.random.Philox(20250319))
+    out = {}
+    for tag, (N, K, M) in {"a": (128, 192, 16), "b": (256, 256, 32)}.items():
+        codes = rng.integers(0, 256, size=(N, K // 2), dtype=np.uint8)
+        sc = np.abs(rng.standard_normal((N, K // 16)).astype(np.float32)) * np.float32(0.05)
+        scales = sc.astype(ml_dtypes.float8_e4m3fn).view(np.uint8)
+        ts = np.float32(1.375)
+        x = (rng.standard_normal((M, K)) * rng.choice([0.01, 1.0, 300.0], size=(M, 1))).astype(np.float32).astype(ml_dtypes.bfloat16)
+        nib = np.empty((N, K), dtype=np.uint8)
+        nib[:, 0::2] = codes & 15
+        nib[:, 1::2] = codes >> 4
+        w = (e2m1[nib] * e4m3[np.repeat(scales, 16, axis=1)]).astype(np.float32) * ts  # the dequantisation rule
+        out.update({f"{tag}_codes": codes, f"{tag}_scales": scales, f"{tag}_ts": ts, f"{tag}_x": x.view(np.uint16),
+                    f"{tag}_y": x.astype(np.float64) @ w.astype(np.float64).T})
+    N, K, M = 128, 128, 16
+    fcodes = rng.integers(0, 254, size=(N, K), dtype=np.uint8)
+    fcodes = np.where(fcodes >= 127, fcodes + 1, fcodes).astype(np.uint8)
+    fs = (np.abs(rng.standard_normal(N)) * 0.02).astype(np.float32)
+    fx = rng.standard_normal((M, K)).astype(np.float32).astype(ml_dtypes.bfloat16)
+    fw = (e4m3[fcodes].astype(np.float32) * fs[:, None]).astype(np.float32)
+    out.update({"f_codes": fcodes, "f_scales": fs, "f_x": fx.view(np.uint16), "f_y": fx.astype(np.float64) @ fw.astype(np.float64).T})
+    np.savez_compressed(os.path.join(HERE, "skinny_golden.npz"), **out)
+    print("wrote", os.path.join(HERE, "skinny_golden.npz"))
+
+
 if __name__ == "__main__":
     main()
+    main_skinny()

@@ -43,6 +43,22 @@ def test_skinny_nvfp4(qg, handle, N, K, M):
     w.unload()
 
 
+def test_skinny_golden_fixture(qg, handle):
+    """Against the committed vectors made from third-party codecs, not from the oracle."""
+    import os
+    S = np.load(os.path.join(os.path.dirname(__file__), "golden", "skinny_golden.npz"))
+    for t in "ab":
+        w = handle.load(qg.pack(qg.FMT_NVFP4, S[f"{t}_codes"], S[f"{t}_scales"], float(S[f"{t}_ts"])))
+        y = run_skinny(qg, handle, w, S[f"{t}_x"])
+        U.status_ok(handle)
+        assert O.rel_l2(y, S[f"{t}_y"]) < TOL_F32
+        w.unload()
+    w = handle.load(qg.pack(qg.FMT_FP8, S["f_codes"], S["f_scales"]))
+    y = run_skinny(qg, handle, w, S["f_x"])
+    assert O.rel_l2(y, S["f_y"]) < TOL_F32
+    w.unload()
+
+
 @pytest.mark.parametrize("N,K,M", [(128, 128, 16), (512, 1024, 80), (256, 4096, 256)])
 def test_skinny_fp8(qg, handle, N, K, M):
     codes, scales = O.make_fp8(N, K, seed=N + K)

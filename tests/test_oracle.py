@@ -121,3 +121,13 @@ def test_moe_oracle_consistent():
             e = ids[t, j]
             ref = O.gemv_nvfp4_f64(codes[e], scales[e], float(ts[e]), x[t:t + 1])
             assert np.array_equal(out[t * topk + j], ref[0])
+
+
+def test_oracle_matches_skinny_golden():
+    """Several token rows against vectors made from the third-party codecs (tests/golden/make_golden.py)."""
+    import os
+    S = np.load(os.path.join(os.path.dirname(__file__), "golden", "skinny_golden.npz"))
+    for t in "ab":
+        y = O.gemv_nvfp4_f64(S[f"{t}_codes"], S[f"{t}_scales"], float(S[f"{t}_ts"]), S[f"{t}_x"])
+        assert O.rel_l2(y, S[f"{t}_y"]) < 1e-12
+    assert O.rel_l2(O.gemv_fp8_f64(S["f_codes"], S["f_scales"], S["f_x"]), S["f_y"]) < 1e-12
