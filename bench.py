@@ -2,6 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl ours|reference]
     python bench.py --workload prefill [--tokens M]      (secondary: tcgen05 skinny GEMM, one GPU)
+    python bench.py --workload lmhead [--batch B]        (secondary: FP8 output head, one GPU)
 
 A "step" is one pass of the hot path over the whole layer stack (four weight-streaming GEMVs per
 layer) at decode batch B, replayed as one CUDA graph.  `value` = algorithmic weight bytes of all
@@ -315,6 +316,77 @@ def run_prefill(args):
     print(json.dumps(line), flush=True)
 
 
+def run_lmhead(args):
+    """Secondary workload: the FP8-E4M3 output head (128256 x 4096, per-channel scales, fp32 logits)
+    at decode batch --batch; two copies of the matrix alternate so every launch streams from HBM."""
+    import torch
+
+    import crit_hub_b200 as qg
+    from crit_hub_b200.stack import LayerStack, synth_fp8
+
+    if int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        raise SystemExit("--workload lmhead is a single-GPU workload")
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    N, K, B = 128256, 4096, args.batch
+    h = qg.QGemv(device=0, use_pdl=True)
+    ws = []
+    for i in range(2):
+        codes, scales = synth_fp8(N, K, 5 + i, dev)
+        ws.append(h.load(qg.pack(qg.FMT_FP8, codes, scales)))
+    stack = LayerStack(h, ws, B, qg.OUT_F32)
+    g = torch.Generator()
+    g.manual_seed(3)
+    stack.set_inputs([torch.randn((B, K), generator=g).to(torch.bfloat16) for _ in ws])
+    stack.capture()
+
+    def timed(fn, n):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        with torch.cuda.stream(stack.stream):
+            e0.record()
+        for _ in range(n):
+            fn()
+        with torch.cuda.stream(stack.stream):
+            e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1)
+
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
+        stack.step()
+    sampler = ClockSampler(0)
+    sampler.start()
+    ms = timed(stack.step, args.steps)
+    clocks = sampler.stop()
+    stack.step_host()
+    ms_host = timed(stack.step_host, args.steps)
+    st = h.device_status(stack.stream.cuda_stream)
+    if st.code != 0:
+        raise SystemExit(f"kernel reported {st}")
+    wbytes = sum(w.weight_bytes for w in ws)
+    gbs = wbytes * args.steps / (ms * 1e-3) / 1e9
+    peak, kind = measured_peak_gbs()
+    line = {
+        "metric": "fp8_lm_head_gemv_weight_gbps", "value": round(gbs, 2), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+        "warmup": warmup, "ms_per_step": round(ms / args.steps, 5), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16 (fp32 accumulate)", "data": "synthetic",
+        "config": {"workload": f"FP8-E4M3 output head 128256 x 4096, per-channel scales, fp32 logits, batch {B}; two copies alternate",
+                   "batch": B, "weight_bytes_per_step": wbytes, "us_per_launch": round(ms * 1e3 / (2 * args.steps), 2),
+                   "cache": "each copy (525 MB) exceeds L2 (126 MB)"},
+        "roofline": {"bound": "hbm", "achieved": round(gbs, 2), "peak": peak, "unit": UNIT, "frac": round(gbs / peak, 4),
+                     "traffic": int(1.0069 * (wbytes // 2)),
+                     "traffic_source": "ncu capture of one launch: DRAM read+write 529.4 MB for 525.85 MB of weights",
+                     "peak_kind": kind, "kernel": "gemv_stream_wp_kernel<FP8>",
+                     "bytes_per_launch": wbytes // 2, "us_per_launch": round(ms * 1e3 / (2 * args.steps), 2)},
+        "e2e": {"value": round(wbytes * args.steps / (ms_host * 1e-3) / 1e9, 2), "unit": UNIT,
+                "h2d_bytes_per_step": stack.h2d_bytes, "d2h_bytes_per_step": stack.d2h_bytes,
+                "ms_per_step": round(ms_host / args.steps, 5)},
+        "gpu_launches": 2 * args.steps, "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -324,8 +396,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (profiling small cases)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
-                    help="decode: the headline GEMV layer stack; prefill: the skinny GEMM over one 70B-shaped layer")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "lmhead"],
+                    help="decode: the headline GEMV layer stack; prefill: the skinny GEMM over one 70B-shaped layer; "
+                         "lmhead: the FP8 output head")
     ap.add_argument("--tokens", type=int, default=256, help="rows of the prefill workload (16..256, multiple of 16)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -333,6 +406,9 @@ def main():
         return
     if args.workload == "prefill":
         run_prefill(args)
+        return
+    if args.workload == "lmhead":
+        run_lmhead(args)
         return
 
     import torch
