@@ -36,7 +36,7 @@
 //   0-11 three dequantising warpgroups; group q = warp / 4 takes the CTA's runs r = q (mod 3), so the
 //        latency of one run's conversion, tcgen05.st and barrier round trips overlaps the other
 //        groups' runs.  Warp w handles panels 2(w%4), 2(w%4)+1 = TMEM lanes 32(w%4)..+31 (the lane
-//        quarter a warp may access), and in the epilogue the same lanes of every third 8-column chunk
+//        quarter a warp may access), and in the epilogue the same lanes of every third 16-column chunk
 //   12   one thread issues the bulk copies of packed weights (ring of 3-4 runs)
 //   13   allocates TMEM; one elected lane walks the runs, issues tcgen05.mma and the commits that free
 //        ring stages
@@ -165,6 +165,15 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&v)[8]) {
                  : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
                  : "r"(taddr)
                  : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr)
+        : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 // 16 lanes x 32 columns: slab j (columns 8j..8j+7) takes registers 4j..4j+3 of every thread;
@@ -537,7 +546,7 @@ __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsPara
             }
             seg_r0 = seg_r1;
             if (!ok) break;
-            // ---- epilogue: this warp owns TMEM lanes [32wq, 32wq+32) and every third 8-column chunk ----
+            // ---- epilogue: this warp owns TMEM lanes [32wq, 32wq+32) and every third 16-column chunk ----
             if (!__all_sync(0xFFFFFFFFu, mbar_wait_probe(sbase + GsSmem::kBarDone, nseg & 1, P.spin_limit))) {
                 if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 45, int(nseg));
                 *abort_flag = 1;
@@ -552,9 +561,9 @@ __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsPara
             const int row = 32 * wq + lane;
             const int n = sg.tile * 128 + row;
             const float rs = (FMT == QGEMV_FMT_NVFP4) ? P.tensor_scale : __ldg(P.chan_scale + n);
-            auto store_cols = [&](int c, const float (&v)[8]) {
+            auto store_cols = [&](int c, const float (&v)[16]) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
+                for (int i = 0; i < 16; ++i) {
                     const int m = c + i;
                     const float val = v[i] * rs * pow2i(__ldg(P.xexp + m));
                     const int64_t idx = int64_t(m) * P.N + n;
@@ -566,12 +575,12 @@ __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsPara
                 }
             };
             if (sg.u0 == 0 && sg.u1 == runs) {  // the segment is the whole tile
-                for (int c = 8 * q; c < M; c += 8 * kGsGroups) {
-                    uint32_t r[8];
-                    tmem_ld8(tmem_base + lane_base + uint32_t(c), r);
-                    float v[8];
+                for (int c = 16 * q; c < M; c += 16 * kGsGroups) {
+                    uint32_t r[16];
+                    tmem_ld16(tmem_base + lane_base + uint32_t(c), r);
+                    float v[16];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+                    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
                     store_cols(c, v);
                 }
                 tc_fence_before();
@@ -581,11 +590,11 @@ __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsPara
                 // partial: park the fp32 sums, then the last contributor of (tile, warp) adds all
                 // parts in CTA order
                 float* slot = P.ws + size_t(gs_slot(cta, sg.tile, runs, total, grid)) * size_t(M) * 128;
-                for (int c = 8 * q; c < M; c += 8 * kGsGroups) {
-                    uint32_t r[8];
-                    tmem_ld8(tmem_base + lane_base + uint32_t(c), r);
+                for (int c = 16 * q; c < M; c += 16 * kGsGroups) {
+                    uint32_t r[16];
+                    tmem_ld16(tmem_base + lane_base + uint32_t(c), r);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) __stcg(slot + (c + i) * 128 + row, __uint_as_float(r[i]));
+                    for (int i = 0; i < 16; ++i) __stcg(slot + (c + i) * 128 + row, __uint_as_float(r[i]));
                 }
                 tc_fence_before();
                 __syncwarp();
@@ -599,12 +608,12 @@ __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsPara
                 old = __shfl_sync(0xFFFFFFFFu, old, 0);
                 if (old == c_hi - c_lo) {
                     __threadfence();
-                    for (int c = 8 * q; c < M; c += 8 * kGsGroups) {
-                        float v[8];
+                    for (int c = 16 * q; c < M; c += 16 * kGsGroups) {
+                        float v[16];
                         for (int32_t cc = c_lo; cc <= c_hi; ++cc) {
                             const float* sl = P.ws + size_t(gs_slot(cc, sg.tile, runs, total, grid)) * size_t(M) * 128;
 #pragma unroll
-                            for (int i = 0; i < 8; ++i) {
+                            for (int i = 0; i < 16; ++i) {
                                 const float qv = __ldcg(sl + (c + i) * 128 + row);
                                 v[i] = cc == c_lo ? qv : v[i] + qv;
                             }
