@@ -514,35 +514,45 @@ __global__ void __launch_bounds__(kGsThreads, 1) gemm_skinny_kernel(const GsPara
         bool ok = true;
         bool waited_x = false;
         const uint32_t lane_base = uint32_t(32 * wq) << 16;
+        const int32_t n_local = r_end - r_begin;  // runs of this CTA
+        // converts run r of the CTA's range into its TMEM stage; false when a wait ran out
+        auto convert_run = [&](int32_t r) -> bool {
+            const int sp = r % kPStages, sa = r % kA;
+            const uint32_t usep = uint32_t(r / kPStages), usea = uint32_t(r / kA);
+            // the TMEM stage is free once the MMAs of the run that used it last retired
+            bool w_ok = usea == 0 || mbar_wait_probe(sbase + GsSmem::kBarAEmpty + 8 * sa, (usea - 1) & 1, P.spin_limit);
+            w_ok = w_ok && mbar_wait_probe(sbase + GsSmem::kBarPFull + 8 * sp, usep & 1, P.spin_limit);
+            if (!__all_sync(0xFFFFFFFFu, w_ok)) {
+                if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 44, r);
+                *abort_flag = 1;
+                return false;
+            }
+            tc_fence_after();
+            // packed stage layout: [panel][unit of the run]; this warp: panels 2wq, 2wq+1
+            const uint32_t st = pring + sp * kPStage + uint32_t((2 * wq) << rl) * kUnitBytes;
+            const uint32_t ta = tmem_base + lane_base + acol0 + sa * a_cols;
+            for (int ui = 0; ui < run; ++ui) {
+                dequant_unit_to_tmem<FMT>(st + ui * kUnitBytes, ta + 32 * ui, lane);
+                dequant_unit_to_tmem<FMT>(st + (uint32_t(kUnitBytes) << rl) + ui * kUnitBytes, ta + 32 * ui + (16u << 16), lane);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(sbase + GsSmem::kBarAReady + 8 * sa);
+                mbar_arrive(sbase + GsSmem::kBarPEmpty + 8 * sp);
+            }
+            return true;
+        };
         while (ok && wk.next(sg)) {
             const int32_t seg_r1 = seg_r0 + (sg.u1 - sg.u0);
-            for (; rnext < seg_r1; rnext += ng) {
-                const int sp = rnext % kPStages, sa = rnext % kA;
-                const uint32_t usep = uint32_t(rnext / kPStages), usea = uint32_t(rnext / kA);
-                // the TMEM stage is free once the MMAs of the run that used it last retired
-                bool w_ok = usea == 0 || mbar_wait_probe(sbase + GsSmem::kBarAEmpty + 8 * sa, (usea - 1) & 1, P.spin_limit);
-                w_ok = w_ok && mbar_wait_probe(sbase + GsSmem::kBarPFull + 8 * sp, usep & 1, P.spin_limit);
-                if (!__all_sync(0xFFFFFFFFu, w_ok)) {
-                    if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 44, rnext);
-                    *abort_flag = 1;
-                    ok = false;
-                    break;
-                }
-                tc_fence_after();
-                // packed stage layout: [panel][unit of the run]; this warp: panels 2wq, 2wq+1
-                const uint32_t st = pring + sp * kPStage + uint32_t((2 * wq) << rl) * kUnitBytes;
-                const uint32_t ta = tmem_base + lane_base + acol0 + sa * a_cols;
-                for (int ui = 0; ui < run; ++ui) {
-                    dequant_unit_to_tmem<FMT>(st + ui * kUnitBytes, ta + 32 * ui, lane);
-                    dequant_unit_to_tmem<FMT>(st + (uint32_t(kUnitBytes) << rl) + ui * kUnitBytes, ta + 32 * ui + (16u << 16), lane);
-                }
-                tmem_wait_st();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(sbase + GsSmem::kBarAReady + 8 * sa);
-                    mbar_arrive(sbase + GsSmem::kBarPEmpty + 8 * sp);
-                }
+            for (; rnext < seg_r1 && ok; rnext += ng) ok = convert_run(rnext);
+            // While this segment's last MMAs drain, convert this group's first run of the NEXT segment:
+            // its TMEM stage was last used by a run of this segment or earlier (rnext - kA < seg_r1), so
+            // the wait above needs nothing that comes after the epilogue below.
+            if (ok && rnext < n_local && rnext - kA < seg_r1) {
+                ok = convert_run(rnext);
+                rnext += ng;
             }
             seg_r0 = seg_r1;
             if (!ok) break;
