@@ -369,19 +369,24 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_wp_kernel(const Gemv
     const int GS = npc >= 8 ? 4 : (npc >= 4 ? 8 : 16);
     const int G = kSWarps / GS;
 
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < kSWarps * kWpRing; ++i) mbar_init(sbase + SSmem::kBarFull + 8 * i, 1);
-        for (int i = 0; i < 4 * kSRedSlots; ++i) {  // up to four warp groups, two hand-over slots each
-            mbar_init(sbase + SSmem::kBarRedFull + 8 * i, uint32_t(GS));
-            mbar_init(sbase + SSmem::kBarRedEmpty + 8 * i, 1);
+    // Set-up is spread over the warps and the CTA-wide barrier comes late: a consumer warp's ring
+    // barriers are private to it, so it initialises them itself and starts its first weight copies
+    // before the CTA has synchronised at all.
+    if (warp == kSEpilogueWarp) {
+        if (lane < 4 * kSRedSlots) {  // up to four warp groups, two hand-over slots each
+            mbar_init(sbase + SSmem::kBarRedFull + 8 * lane, uint32_t(GS));
+            mbar_init(sbase + SSmem::kBarRedEmpty + 8 * lane, 1);
         }
-        for (int b = 0; b < 8; ++b) reinterpret_cast<volatile unsigned int*>(smem_raw + SSmem::kRowMax)[b] = 0u;
-        *reinterpret_cast<volatile int*>(smem_raw + SSmem::kAbort) = 0;
+        if (lane < 8) reinterpret_cast<volatile unsigned int*>(smem_raw + SSmem::kRowMax)[lane] = 0u;
         // 16 zero bytes: the activation "fragment" of lanes whose batch column does not exist
-        for (int i = 0; i < 4; ++i) reinterpret_cast<volatile unsigned int*>(smem_raw + SSmem::kZero)[i] = 0u;
+        if (lane < 4) reinterpret_cast<volatile unsigned int*>(smem_raw + SSmem::kZero)[lane] = 0u;
+        if (lane == 0) *reinterpret_cast<volatile int*>(smem_raw + SSmem::kAbort) = 0;
         mbar_fence_init();
+    } else {
+        if (lane < kWpRing) mbar_init(sbase + SSmem::kBarFull + 8 * (warp * kWpRing + lane), 1);
+        mbar_fence_init();
+        __syncwarp();
     }
-    __syncthreads();
     pdl_launch_dependents();
 
     if (cta >= grid) return;
@@ -389,7 +394,8 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_wp_kernel(const Gemv
 
     if (warp == kSEpilogueWarp) {
         // ================= epilogue: reduce the sixteen K slices of each panel, scale, store =================
-        pdl_wait();  // the output buffer may still be in use by the preceding kernel
+        __syncthreads();  // the CTA's one barrier: shared set-up is visible to everyone
+        pdl_wait();       // the output buffer may still be in use by the preceding kernel
         const float ts = (FMT == QGEMV_FMT_NVFP4) ? P.tensor_scale[0] : 1.0f;
         const uint32_t red = sbase + SSmem::kRed + lane * 16;
         // Optional L2 prefetch of the weight the caller uses next: this CTA's share, issued in
@@ -485,6 +491,7 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_wp_kernel(const Gemv
     };
     for (int i = 0; i < kWpRing && to_issue > 0; ++i) issue_one();
 
+    __syncthreads();  // the CTA's one barrier (the epilogue warp's set-up; see the top of the kernel)
     // weights never depend on the preceding kernel; activations do
     pdl_wait();
     stream_convert_x(P, smem_raw, sbase, w, lane);
