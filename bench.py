@@ -3,6 +3,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl ours|reference]
     python bench.py --workload prefill [--tokens M]      (secondary: tcgen05 skinny GEMM, one GPU)
     python bench.py --workload lmhead [--batch B]        (secondary: FP8 output head, one GPU)
+    python bench.py --workload moe [--tokens T]          (secondary: grouped MoE GEMV, one GPU)
 
 A "step" is one pass of the hot path over the whole layer stack (four weight-streaming GEMVs per
 layer) at decode batch B, replayed as one CUDA graph.  `value` = algorithmic weight bytes of all
@@ -387,6 +388,117 @@ def run_lmhead(args):
     print(json.dumps(line), flush=True)
 
 
+def run_moe(args):
+    """Secondary workload: the grouped MoE GEMV -- 128 experts, top-8, hidden 2048, expert width 768
+    (gate/up 1536 x 2048 and down 2048 x 768 per expert, NVFP4), --tokens tokens per step, four
+    layers of distinct experts in one CUDA graph.  value = bytes of the experts actually touched /
+    device time."""
+    import numpy as np
+    import torch
+
+    import crit_hub_b200 as qg
+    from crit_hub_b200.stack import synth_nvfp4
+
+    if int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        raise SystemExit("--workload moe is a single-GPU workload")
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    E, topk, hidden, inter, L = 128, 8, 2048, 768, 4
+    T = args.tokens if args.tokens <= 512 and args.tokens != 256 else 8
+    h = qg.QGemv(device=0, use_pdl=True)
+
+    def stacked(N, K, seed0):
+        blobs = []
+        for e in range(E):
+            c, s = synth_nvfp4(N, K, seed0 + e, dev)
+            blobs.append(qg.pack(qg.FMT_NVFP4, c, s, 1.0))
+        return np.stack(blobs)
+
+    gu = [h.load_stacked(stacked(2 * inter, hidden, 1000 * l)) for l in range(L)]
+    dn = [h.load_stacked(stacked(hidden, inter, 1000 * l + 500)) for l in range(L)]
+    per_expert = gu[0].weight_bytes + dn[0].weight_bytes
+    g = torch.Generator(device=dev)
+    g.manual_seed(T)
+    ids = torch.topk(torch.randn(T, E, device=dev, generator=g), topk, dim=-1).indices.to(torch.int32).contiguous()
+    distinct = int(torch.unique(ids).numel())
+    x_host = torch.randn(T, hidden).to(torch.bfloat16).pin_memory()
+    x = x_host.to(dev)
+    hbuf = torch.empty(T * topk, 2 * inter, device=dev, dtype=torch.bfloat16)
+    act = torch.randn(T * topk, inter, device=dev).to(torch.bfloat16)
+    out = torch.empty(T * topk, hidden, device=dev, dtype=torch.float32)
+    out_host = torch.empty(T * topk, hidden, dtype=torch.float32).pin_memory()
+    stream = torch.cuda.Stream()
+
+    def layers(st):
+        for l in range(L):
+            h.moe_gemv(gu[l], ids.data_ptr(), x.data_ptr(), T, topk, False, hbuf.data_ptr(), qg.OUT_BF16, st)
+            h.moe_gemv(dn[l], ids.data_ptr(), act.data_ptr(), T, topk, True, out.data_ptr(), qg.OUT_F32, st)
+
+    with torch.cuda.stream(stream):
+        layers(stream.cuda_stream)
+    stream.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        layers(torch.cuda.current_stream().cuda_stream)
+
+    def dev_step():
+        with torch.cuda.stream(stream):
+            graph.replay()
+
+    def host_step():
+        with torch.cuda.stream(stream):
+            x.copy_(x_host, non_blocking=True)
+            graph.replay()
+            out_host.copy_(out, non_blocking=True)
+        stream.synchronize()
+
+    def timed(fn, n):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        with torch.cuda.stream(stream):
+            e0.record()
+        for _ in range(n):
+            fn()
+        with torch.cuda.stream(stream):
+            e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1)
+
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
+        dev_step()
+    sampler = ClockSampler(0)
+    sampler.start()
+    ms = timed(dev_step, args.steps)
+    clocks = sampler.stop()
+    host_step()
+    ms_host = timed(host_step, args.steps)
+    st = h.device_status(stream.cuda_stream)
+    if st.code != 0:
+        raise SystemExit(f"kernel reported {st}")
+    nbytes = distinct * per_expert * L
+    gbs = nbytes * args.steps / (ms * 1e-3) / 1e9
+    peak, kind = measured_peak_gbs()
+    line = {
+        "metric": "nvfp4_moe_gemv_touched_weight_gbps", "value": round(gbs, 2), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+        "warmup": warmup, "ms_per_step": round(ms / args.steps, 5), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16 (fp32 accumulate)", "data": "synthetic",
+        "config": {"workload": f"MoE grouped GEMV: {E} experts, top-{topk}, hidden {hidden}, expert width {inter}, NVFP4, "
+                               f"{T} tokens, {L} layers (gate/up + down) in one CUDA graph",
+                   "tokens": T, "distinct_experts": distinct, "touched_weight_bytes_per_step": nbytes,
+                   "us_per_layer": round(ms * 1e3 / args.steps / L, 2),
+                   "cache": "four layers of distinct experts; at 1 token the touched experts (21 MB per layer) fit L2"},
+        "roofline": {"bound": "hbm", "achieved": round(gbs, 2), "peak": peak, "unit": UNIT, "frac": round(gbs / peak, 4),
+                     "traffic": None, "peak_kind": kind, "kernel": "moe_stream_kernel<NVFP4>",
+                     "bytes_per_launch": nbytes // (2 * L), "us_per_launch": round(ms * 1e3 / (2 * L * args.steps), 2)},
+        "e2e": {"value": round(nbytes * args.steps / (ms_host * 1e-3) / 1e9, 2), "unit": UNIT,
+                "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 4,
+                "ms_per_step": round(ms_host / args.steps, 5)},
+        "gpu_launches": 4 * L * args.steps, "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -396,9 +508,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (profiling small cases)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "lmhead"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "lmhead", "moe"],
                     help="decode: the headline GEMV layer stack; prefill: the skinny GEMM over one 70B-shaped layer; "
-                         "lmhead: the FP8 output head")
+                         "lmhead: the FP8 output head; moe: the grouped expert GEMV (--tokens 1/8/64)")
     ap.add_argument("--tokens", type=int, default=256, help="rows of the prefill workload (16..256, multiple of 16)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -409,6 +521,9 @@ def main():
         return
     if args.workload == "lmhead":
         run_lmhead(args)
+        return
+    if args.workload == "moe":
+        run_moe(args)
         return
 
     import torch
