@@ -214,8 +214,8 @@ int qgemv_init(const qgemv_config* cfg, qgemv_handle** out) {
         cudaFuncSetAttribute(qg::gemv_kernel<QGEMV_FMT_FP8, false>, dyn, qg::Smem::total<QGEMV_FMT_FP8>()) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_stream_kernel<QGEMV_FMT_NVFP4>, dyn, qg::SSmem::total<QGEMV_FMT_NVFP4>()) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_stream_kernel<QGEMV_FMT_FP8>, dyn, qg::SSmem::total<QGEMV_FMT_FP8>()) != cudaSuccess ||
-        cudaFuncSetAttribute(qg::moe_stream_kernel<QGEMV_FMT_NVFP4>, dyn, qg::SSmem::total<QGEMV_FMT_NVFP4>()) != cudaSuccess ||
-        cudaFuncSetAttribute(qg::moe_stream_kernel<QGEMV_FMT_FP8>, dyn, qg::SSmem::total<QGEMV_FMT_FP8>()) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::moe_stream_kernel<QGEMV_FMT_NVFP4>, dyn, qg::MSmem::total<QGEMV_FMT_NVFP4>()) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::moe_stream_kernel<QGEMV_FMT_FP8>, dyn, qg::MSmem::total<QGEMV_FMT_FP8>()) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_NVFP4, true, 1>, dyn, qg::SSmem::total<QGEMV_FMT_NVFP4>()) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_NVFP4, false, 1>, dyn, qg::SSmem::total<QGEMV_FMT_NVFP4>()) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8, true, 1>, dyn, qg::SSmem::total<QGEMV_FMT_FP8>()) != cudaSuccess ||
@@ -524,8 +524,8 @@ int qgemv_moe_gemv(qgemv_handle* h, const qgemv_weight* experts, const int32_t* 
     if (qg::use_moe_stream_path(experts->units) && !(h->cfg.debug & 256)) {
         const dim3 grid(gemv_grid(h)), block(qg::kSThreads);
         err = experts->fmt == QGEMV_FMT_NVFP4
-                  ? launch(h, qg::moe_stream_kernel<QGEMV_FMT_NVFP4>, grid, block, qg::SSmem::total<QGEMV_FMT_NVFP4>(), s, P)
-                  : launch(h, qg::moe_stream_kernel<QGEMV_FMT_FP8>, grid, block, qg::SSmem::total<QGEMV_FMT_FP8>(), s, P);
+                  ? launch(h, qg::moe_stream_kernel<QGEMV_FMT_NVFP4>, grid, block, qg::MSmem::total<QGEMV_FMT_NVFP4>(), s, P)
+                  : launch(h, qg::moe_stream_kernel<QGEMV_FMT_FP8>, grid, block, qg::MSmem::total<QGEMV_FMT_FP8>(), s, P);
         return err == cudaSuccess ? QGEMV_OK : QGEMV_ERR_CUDA;
     }
     return launch_gemv(h, experts, P, s);

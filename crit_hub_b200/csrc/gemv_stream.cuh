@@ -51,7 +51,7 @@ struct SSmem {
     static constexpr int kRed = kXBuf + kSXBufBytes;                   // kSRedSlots * kSWarps * 512
     static constexpr int kRing0 = kRed + kSRedSlots * kSWarps * 512;
     template <int FMT>
-    static constexpr int total() {
+    __host__ __device__ static constexpr int total() {
         constexpr int split_ring = StreamTraits<FMT>::kRing;
         constexpr int ring_slots = split_ring > 4 ? split_ring : 4;  // whole-panel kernel: 4 chunk slots
         return kRing0 + kSWarps * ring_slots * StreamTraits<FMT>::kChunkUnits * FmtTraits<FMT>::kUnitBytes;

@@ -17,6 +17,13 @@ namespace qg {
 struct MSmem {  // extra words inside the 1 KB header region of SSmem
     static constexpr int kRowMax16 = 768;  // 16 words
     static constexpr int kRowExp16 = 832;  // 16 words
+    // hand-over barriers of up to sixteen warp groups (two slots each) sit behind the rings
+    template <int FMT>
+    __host__ __device__ static constexpr int bar_red_full() { return SSmem::total<FMT>(); }
+    template <int FMT>
+    __host__ __device__ static constexpr int bar_red_empty() { return SSmem::total<FMT>() + 256; }
+    template <int FMT>
+    __host__ __device__ static constexpr int total() { return SSmem::total<FMT>() + 512; }
 };
 
 inline bool use_moe_stream_path(int64_t units) { return units <= 32; }
@@ -29,6 +36,7 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stream_kernel(const GemvPara
     constexpr int kSlotBytes = CH * kUnitBytes;
     constexpr int kWpRing = 4;
     constexpr int kProbXBytes = 32768;  // f16 fragments of one problem: 32 units x 8 rows x 128 B
+    constexpr int kBarRedFull = MSmem::bar_red_full<FMT>(), kBarRedEmpty = MSmem::bar_red_empty<FMT>();
 
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const uint32_t sbase = smem_u32(smem_raw);
@@ -45,15 +53,20 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stream_kernel(const GemvPara
     const int R = nprob > grid ? nprob : grid;        // ranges; each spans at most two problems
     const int npr = int((VP + R - 1) / R);            // panels per range (upper bound)
     const int n_chunks = (units + CH - 1) / CH;
-    int GS = npr >= 8 ? 4 : (npr >= 4 ? 8 : 16);
-    while (GS > 4 && GS > n_chunks) GS >>= 1;         // short K: fewer warps per panel, more groups
+    // Warps per panel: experts have short K (2048 and less), so a panel is only a few chunks; a warp
+    // should keep about four of them per panel (hand-overs to the epilogue warp cost as much as a
+    // chunk), which means one or two warps per panel and up to sixteen panels in flight per CTA --
+    // unless the range has too few panels to occupy that many groups.
+    int GS = 1;
+    while (GS < 16 && n_chunks / (2 * GS) >= 4) GS <<= 1;
+    while (GS < 16 && kSWarps / GS > npr) GS <<= 1;
     const int G = kSWarps / GS;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < kSWarps * kWpRing; ++i) mbar_init(sbase + SSmem::kBarFull + 8 * i, 1);
-        for (int i = 0; i < 4 * kSRedSlots; ++i) {
-            mbar_init(sbase + SSmem::kBarRedFull + 8 * i, uint32_t(GS));
-            mbar_init(sbase + SSmem::kBarRedEmpty + 8 * i, 1);
+        for (int i = 0; i < kSWarps * kSRedSlots; ++i) {
+            mbar_init(sbase + kBarRedFull + 8 * i, uint32_t(GS));
+            mbar_init(sbase + kBarRedEmpty + 8 * i, 1);
         }
         *reinterpret_cast<volatile int*>(smem_raw + SSmem::kAbort) = 0;
         mbar_fence_init();
@@ -64,7 +77,9 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stream_kernel(const GemvPara
     if (warp == kSEpilogueWarp) {
         // ================= epilogue =================
         const uint32_t red = sbase + SSmem::kRed + lane * 16;
-        int hand[4] = {0, 0, 0, 0};  // hand-overs seen so far, per group
+        int hand[kSWarps];  // hand-overs seen so far, per group
+#pragma unroll
+        for (int i = 0; i < kSWarps; ++i) hand[i] = 0;
         for (int r = cta; r < R; r += grid) {
             const int64_t p0 = (int64_t(r) * VP) / R, p1 = (int64_t(r + 1) * VP) / R;
             const int64_t q0 = p0 / P.n_panels;
@@ -72,6 +87,14 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stream_kernel(const GemvPara
             const int32_t* pr0 = P.prob + 1 + q0 * kProbInts;
             const int32_t* pr1 = (q0 + 1 < nprob) ? pr0 + kProbInts : pr0;
             const int ex0 = __ldcg(pr0), nr0 = __ldcg(pr0 + 1), ex1 = __ldcg(pr1), nr1 = __ldcg(pr1 + 1);
+            // everything the per-panel path needs from global memory, fetched once per range: this
+            // lane's two output rows of either problem, the experts' tensor scales
+            const int tq = lane & 3, gq = lane >> 2;
+            const int c0 = 2 * tq, c1 = c0 + 1;
+            const int orow00 = c0 < nr0 ? __ldcg(pr0 + 10 + c0) : 0, orow01 = c1 < nr0 ? __ldcg(pr0 + 10 + c1) : 0;
+            const int orow10 = c0 < nr1 ? __ldcg(pr1 + 10 + c0) : 0, orow11 = c1 < nr1 ? __ldcg(pr1 + 10 + c1) : 0;
+            const float ts0 = (FMT == QGEMV_FMT_NVFP4) ? __ldg(P.tensor_scale + ex0) : 1.0f;
+            const float ts1 = (FMT == QGEMV_FMT_NVFP4) ? __ldg(P.tensor_scale + ex1) : 1.0f;
             int sel = 0;
             int32_t panel = int32_t(p0 - q0 * P.n_panels);
             for (int64_t p = p0; p < p1; ++p) {
@@ -80,7 +103,7 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stream_kernel(const GemvPara
                 const int rs = use % kSRedSlots;
                 const uint32_t rpar = uint32_t(use / kSRedSlots) & 1u;
                 const int bi = gidx * kSRedSlots + rs;
-                if (!mbar_wait(sbase + SSmem::kBarRedFull + 8 * bi, rpar, P.spin_limit, 200u)) {
+                if (!mbar_wait(sbase + kBarRedFull + 8 * bi, rpar, P.spin_limit, 200u)) {
                     if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 6, int(p));
                     *abort_flag = 1;
                     return;
@@ -92,15 +115,31 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stream_kernel(const GemvPara
                     v.x += q.x, v.y += q.y, v.z += q.z, v.w += q.w;
                 }
                 __syncwarp();
-                if (lane == 0) mbar_arrive(sbase + SSmem::kBarRedEmpty + 8 * bi);
-                const int expert = sel ? ex1 : ex0;
-                if (FMT == QGEMV_FMT_NVFP4) {
-                    const float ts = P.tensor_scale[expert];
-                    v.x *= ts, v.y *= ts, v.z *= ts, v.w *= ts;
+                if (lane == 0) mbar_arrive(sbase + kBarRedEmpty + 8 * bi);
+                const float ts = sel ? ts1 : ts0;
+                v.x *= ts, v.y *= ts, v.z *= ts, v.w *= ts;
+                const int n0 = panel * 16 + gq, n1 = n0 + 8;
+                if (FMT == QGEMV_FMT_FP8) {
+                    const float* chan = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(P.chan_scale) +
+                                                                       uint64_t(sel ? ex1 : ex0) * P.chan_stride);
+                    const float s0 = __ldg(chan + n0), s1 = __ldg(chan + n1);  // padded to 16 rows per panel
+                    v.x *= s0, v.y *= s0, v.z *= s1, v.w *= s1;
                 }
-                const float* chan = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(P.chan_scale) +
-                                                                   uint64_t(expert) * P.chan_stride);
-                store_panel<FMT>(P, v, lane, panel, sel ? nr1 : nr0, sel ? pr1 : pr0, chan);
+                const int nrows = sel ? nr1 : nr0;
+                const int64_t ra = int64_t(sel ? orow10 : orow00) * P.N, rb = int64_t(sel ? orow11 : orow01) * P.N;
+                const float vals[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int n = (i & 2) ? n1 : n0;
+                    if (((i & 1) ? c1 : c0) < nrows && n < P.N) {
+                        const int64_t idx = ((i & 1) ? rb : ra) + n;
+                        if (P.y_dtype == QGEMV_OUT_F32) {
+                            static_cast<float*>(P.y)[idx] = vals[i];
+                        } else {
+                            static_cast<__nv_bfloat16*>(P.y)[idx] = __float2bfloat16_rn(vals[i]);
+                        }
+                    }
+                }
                 if (++panel == P.n_panels) {
                     panel = 0;
                     ++sel;
@@ -269,7 +308,7 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stream_kernel(const GemvPara
             }
             if (!ok) break;
             if (ruse > 0 &&
-                !mbar_wait(sbase + SSmem::kBarRedEmpty + red_bars + 8 * rs, (ruse - 1) & 1, P.spin_limit)) {
+                !mbar_wait(sbase + kBarRedEmpty + red_bars + 8 * rs, (ruse - 1) & 1, P.spin_limit)) {
                 if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 7, int(p));
                 *abort_flag = 1;
                 ok = false;
@@ -278,7 +317,7 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stream_kernel(const GemvPara
             sts128f(red + rs * uint32_t(GS) * 512u, (cA[0] + cB[0]) * fs0, (cA[1] + cB[1]) * fs1,
                     (cA[2] + cB[2]) * fs0, (cA[3] + cB[3]) * fs1);
             __syncwarp();
-            if (lane == 0) mbar_arrive(sbase + SSmem::kBarRedFull + red_bars + 8 * rs);
+            if (lane == 0) mbar_arrive(sbase + kBarRedFull + red_bars + 8 * rs);
             if (++rs == kSRedSlots) {
                 rs = 0;
                 ++ruse;
