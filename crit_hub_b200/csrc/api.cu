@@ -510,9 +510,9 @@ int qgemv_moe_gemv(qgemv_handle* h, const qgemv_weight* experts, const int32_t* 
     if (out_dtype != QGEMV_OUT_BF16 && out_dtype != QGEMV_OUT_F32) return QGEMV_ERR_INVALID_ARG;
     if ((reinterpret_cast<uintptr_t>(x_bf16) & 15u) != 0) return QGEMV_ERR_INVALID_ARG;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const int threads = 1024;  // 32 warps, one expert per warp at a time
+    const int threads = 1024;
     cudaError_t err = launch(h, qg::moe_prep_kernel, dim3(1), dim3(threads),
-                             size_t(experts->n_stack) * 8 + size_t(T) * topk * 4 + 16, s, expert_ids, T, topk, experts->n_stack,
+                             size_t(experts->n_stack) * 12 + size_t(T) * topk * 4 + 16, s, expert_ids, T, topk, experts->n_stack,
                              per_slot_input, experts->max_prob, experts->prob, h->status_dev);
     if (err != cudaSuccess) return QGEMV_ERR_CUDA;
     qg::GemvParams P = base_params(h, experts);

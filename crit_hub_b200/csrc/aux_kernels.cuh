@@ -76,20 +76,22 @@ __global__ void dequant_kernel(const uint8_t* payload, const float* chan, float 
 // Router walk: groups the (token, slot) pairs of expert_ids [T][topk] by expert, in ascending
 // (t, j) order, and cuts each group into problems of at most eight activation rows.
 // prob[0] = problem count; problem i = {expert, nrows, xrow[8], orow[8], 0, 0}.
-// One CTA; a warp per expert (strided) scans the list 32 entries at a time with ballots, so the
-// order inside every problem is the list order and the table is deterministic.
+// One CTA: counts by a shared-memory histogram, a warp prefix scan, then one warp walks the list in
+// order, so the order inside every problem is the list order and the table is deterministic.
 __global__ void moe_prep_kernel(const int32_t* expert_ids, int T, int topk, int n_experts,
                                 int per_slot_input, int max_prob, int32_t* prob, int32_t* status) {
-    extern __shared__ int sh[];  // ids[T*topk], counts[n_experts], base[n_experts], flags[2]
+    extern __shared__ int sh[];  // ids[T*topk], counts[n_experts], base[n_experts], seen[n_experts], flags[2]
     const int total = T * topk;
     int* ids = sh;
     int* counts = sh + total;
     int* base = counts + n_experts;
-    int* flags = base + n_experts;
+    int* seen = base + n_experts;
+    int* flags = seen + n_experts;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     pdl_launch_dependents();
     pdl_wait();
     if (threadIdx.x == 0) flags[0] = 0, flags[1] = 0;
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) counts[e] = 0, seen[e] = 0;
     __syncthreads();
     for (int i = threadIdx.x; i < total; i += blockDim.x) {  // one coalesced read of the router output
         const int e = __ldcg(expert_ids + i);
@@ -97,13 +99,10 @@ __global__ void moe_prep_kernel(const int32_t* expert_ids, int T, int topk, int 
         if (e < 0 || e >= n_experts) flags[0] = 1;
     }
     __syncthreads();
-    for (int e = warp; e < n_experts; e += nwarps) {
-        int c = 0;
-        for (int i0 = 0; i0 < total; i0 += 32) {
-            const int i = i0 + lane;
-            c += __popc(__ballot_sync(0xFFFFFFFFu, i < total && ids[i] == e));
-        }
-        if (lane == 0) counts[e] = c;
+    // per-expert entry counts: a shared-memory histogram (order does not matter for a count)
+    for (int i = threadIdx.x; i < total; i += blockDim.x) {
+        const int e = ids[i];
+        if (e >= 0 && e < n_experts) atomicAdd(&counts[e], 1);
     }
     __syncthreads();
     if (warp == 0) {  // exclusive prefix of the per-expert problem counts
@@ -134,16 +133,22 @@ __global__ void moe_prep_kernel(const int32_t* expert_ids, int T, int topk, int 
     }
     __syncthreads();
     if (flags[1] == 0) return;
-    for (int e = warp; e < n_experts; e += nwarps) {
-        const int cnt = counts[e];
-        if (cnt == 0) continue;
-        int seen = 0;
+    // Fill the table in list order: one warp walks the list 32 entries at a time; entries of a tile
+    // that name the same expert find each other with match_any, their rank in the expert's list is
+    // the running count `seen[e]` plus their position among the tile's matches.
+    if (warp == 0) {
         for (int i0 = 0; i0 < total; i0 += 32) {
             const int i = i0 + lane;
-            const bool hit = i < total && ids[i] == e;
-            const unsigned m = __ballot_sync(0xFFFFFFFFu, hit);
-            if (hit) {
-                const int k = seen + __popc(m & ((1u << lane) - 1u));  // rank of this entry in the expert's list
+            const bool valid = i < total;
+            const int e = valid ? ids[i] : -1 - lane;  // invalid lanes match nobody
+            const unsigned m = __match_any_sync(0xFFFFFFFFu, e);
+            int k = 0, cnt = 0;
+            if (valid) {
+                k = seen[e] + __popc(m & ((1u << lane) - 1u));  // rank of this entry in the expert's list
+                cnt = counts[e];
+            }
+            __syncwarp();
+            if (valid) {
                 int32_t* p = prob + 1 + (base[e] + (k >> 3)) * kProbInts;
                 const int r = k & 7;
                 if (r == 0) {
@@ -154,15 +159,12 @@ __global__ void moe_prep_kernel(const int32_t* expert_ids, int T, int topk, int 
                 }
                 p[2 + r] = per_slot_input ? i : i / topk;
                 p[10 + r] = i;
+                if (k == cnt - 1) {  // last entry of the expert: clear the unused row slots of its last problem
+                    for (int z = r + 1; z < 8; ++z) p[2 + z] = 0, p[10 + z] = 0;
+                }
+                if ((m & ((1u << lane) - 1u)) == 0) seen[e] += __popc(m);  // the tile's first match updates the count
             }
-            seen += __popc(m);
-        }
-        // unused row slots of the last problem of this expert
-        const int tail = cnt & 7;
-        if (tail != 0 && lane >= tail && lane < 8) {
-            int32_t* p = prob + 1 + (base[e] + (cnt >> 3)) * kProbInts;
-            p[2 + lane] = 0;
-            p[10 + lane] = 0;
+            __syncwarp();
         }
     }
 }
