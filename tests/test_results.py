@@ -60,7 +60,9 @@ def test_throughput_rules():
     assert R.check_throughput([]) != []
 
 
-REF_TOOLS = "/root/reference/tools"
+# the registry checkout, when it sits next to this repository (or where CRIT_HUB_TOOLS points)
+REF_TOOLS = os.environ.get("CRIT_HUB_TOOLS") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference", "tools")
 
 
 @pytest.mark.skipif(not os.path.isdir(REF_TOOLS), reason="the registry's own checker is not on this machine")
