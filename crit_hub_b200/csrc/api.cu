@@ -121,14 +121,22 @@ qg::GemvParams base_params(const qgemv_handle* h, const qgemv_weight* w) {
     return P;
 }
 
+// Whole panels per CTA as soon as a fair share of the SMs gets one: with fewer panels than CTAs
+// the idle SMs cost less than the K split's fix-up does (1280 x 8192, 80 panels: 4.9 us on 80 CTAs
+// against 8.9 us split over 148).  Below that the split kernel spreads the few panels over all SMs.
+bool wp_has_enough_panels(const qgemv_handle* h, const qgemv_weight* w) {
+    const int64_t g = gemv_grid(h);
+    return w->n_panels >= g || w->n_panels >= std::max<int64_t>(32, g / 4);
+}
+
 int launch_gemv(const qgemv_handle* h, const qgemv_weight* w, const qg::GemvParams& P,
                 cudaStream_t stream) {
     const dim3 grid(gemv_grid(h)), block(qg::kThreads);
     cudaError_t err;
     if (qg::use_stream_path(P.prob == nullptr, P.B, P.units) && !(h->cfg.debug & 256)) {
         const dim3 sblock(qg::kSThreads);
-        // whole panels per CTA (no cross-CTA fix-up) once every CTA gets at least one panel
-        const bool whole = w->n_panels >= int64_t(grid.x) && !(h->cfg.debug & 512);
+        // whole panels per CTA (no cross-CTA fix-up)
+        const bool whole = wp_has_enough_panels(h, w) && !(h->cfg.debug & 512);
         if (w->fmt == QGEMV_FMT_NVFP4) {
             const size_t smem = qg::SSmem::total<QGEMV_FMT_NVFP4>();
             const bool full = P.units % qg::StreamTraits<QGEMV_FMT_NVFP4>::kChunkUnits == 0;
@@ -362,7 +370,7 @@ int qgemv_gemv_prefetch(qgemv_handle* h, const qgemv_weight* w, const void* x_bf
     // chunk length depends on B, so here a row's result matches other batch sizes to fp32 rounding,
     // not bit for bit.  Calls that share a handle share the scratch: keep them on one stream.
     const int unit_bytes = w->fmt == QGEMV_FMT_NVFP4 ? QG_NVFP4_UNIT_BYTES : QG_FP8_UNIT_BYTES;
-    if (!qg::use_stream_path(true, B, w->units) && w->n_stack == 1 && w->n_panels >= gemv_grid(h) &&
+    if (!qg::use_stream_path(true, B, w->units) && w->n_stack == 1 && wp_has_enough_panels(h, w) &&
         !(h->cfg.debug & (256 | 512))) {
         const int64_t cu = (qg::kSMaxUnitsTimesBatch / B) / QG_PHASE_UNITS * QG_PHASE_UNITS;  // units per chunk
         const int64_t n_chunks = (w->units + cu - 1) / cu;
