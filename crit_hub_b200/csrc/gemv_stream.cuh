@@ -366,7 +366,9 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_wp_kernel(const Gemv
     // G-th panel of the CTA and splits K between its GS warps.  Many panels per CTA -> small groups
     // (a warp stays longer on one panel, fewer hand-overs); few panels -> all sixteen warps split K.
     const int npc = p1 - p0;
-    const int GS = npc >= 8 ? 4 : (npc >= 4 ? 8 : 16);
+    int GS = npc >= 8 ? 4 : (npc >= 4 ? 8 : 16);
+    // short K: a panel has fewer chunks than the group has warps -- smaller groups, more panels in flight
+    while (GS > 4 && GS > (units + CH - 1) / CH) GS >>= 1;
     const int G = kSWarps / GS;
 
     // Set-up is spread over the warps and the CTA-wide barrier comes late: a consumer warp's ring
