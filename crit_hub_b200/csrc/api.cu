@@ -140,13 +140,19 @@ int launch_gemv(const qgemv_handle* h, const qgemv_weight* w, const qg::GemvPara
         if (w->fmt == QGEMV_FMT_NVFP4) {
             const size_t smem = qg::SSmem::total<QGEMV_FMT_NVFP4>();
             const bool full = P.units % qg::StreamTraits<QGEMV_FMT_NVFP4>::kChunkUnits == 0;
+            const bool shortk = P.units < 16 * qg::StreamTraits<QGEMV_FMT_NVFP4>::kChunkUnits;
             err = !whole ? launch(h, qg::gemv_stream_kernel<QGEMV_FMT_NVFP4>, grid, sblock, smem, stream, P)
+                  : shortk ? (full ? launch(h, qg::gemv_stream_wp_kernel<QGEMV_FMT_NVFP4, true, 1, true>, grid, sblock, smem, stream, P)
+                                   : launch(h, qg::gemv_stream_wp_kernel<QGEMV_FMT_NVFP4, false, 1, true>, grid, sblock, smem, stream, P))
                   : full ? launch(h, qg::gemv_stream_wp_kernel<QGEMV_FMT_NVFP4, true, 1>, grid, sblock, smem, stream, P)
                          : launch(h, qg::gemv_stream_wp_kernel<QGEMV_FMT_NVFP4, false, 1>, grid, sblock, smem, stream, P);
         } else {
             const size_t smem = qg::SSmem::total<QGEMV_FMT_FP8>();
             const bool full = P.units % qg::StreamTraits<QGEMV_FMT_FP8>::kChunkUnits == 0;
+            const bool shortk = P.units < 16 * qg::StreamTraits<QGEMV_FMT_FP8>::kChunkUnits;
             err = !whole ? launch(h, qg::gemv_stream_kernel<QGEMV_FMT_FP8>, grid, sblock, smem, stream, P)
+                  : shortk ? (full ? launch(h, qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8, true, 1, true>, grid, sblock, smem, stream, P)
+                                   : launch(h, qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8, false, 1, true>, grid, sblock, smem, stream, P))
                   : full ? launch(h, qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8, true, 1>, grid, sblock, smem, stream, P)
                          : launch(h, qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8, false, 1>, grid, sblock, smem, stream, P);
         }
@@ -228,6 +234,10 @@ int qgemv_init(const qgemv_config* cfg, qgemv_handle** out) {
         cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_NVFP4, false, 1>, dyn, qg::SSmem::total<QGEMV_FMT_NVFP4>()) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8, true, 1>, dyn, qg::SSmem::total<QGEMV_FMT_FP8>()) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8, false, 1>, dyn, qg::SSmem::total<QGEMV_FMT_FP8>()) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_NVFP4, true, 1, true>, dyn, qg::SSmem::total<QGEMV_FMT_NVFP4>()) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_NVFP4, false, 1, true>, dyn, qg::SSmem::total<QGEMV_FMT_NVFP4>()) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8, true, 1, true>, dyn, qg::SSmem::total<QGEMV_FMT_FP8>()) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8, false, 1, true>, dyn, qg::SSmem::total<QGEMV_FMT_FP8>()) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemm_skinny_kernel<QGEMV_FMT_NVFP4>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemm_skinny_kernel<QGEMV_FMT_FP8>, dyn, qg::kGsSmemBudget) != cudaSuccess) {
         cudaFree(h->status_dev);

@@ -344,7 +344,13 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_kernel(const GemvPar
 // chunks [w*NC/16, (w+1)*NC/16) of every panel, so every warp sees the same chunk sequence in every
 // panel and the loop bookkeeping is a handful of running counters.  Chosen by the host when there
 // is at least one panel per CTA.  FULL: units is a multiple of kChunkUnits (no ragged last chunk).
-template <int FMT, bool FULL, int PPI>
+__device__ __forceinline__ int wp_short_group(int npc, int n_chunks) {
+    int gs = npc >= 8 ? 4 : (npc >= 4 ? 8 : 16);
+    while (gs > 4 && gs > n_chunks) gs >>= 1;
+    return gs;
+}
+
+template <int FMT, bool FULL, int PPI, bool SHORTK = false>
 __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_wp_kernel(const GemvParams P) {
     using ST = StreamTraits<FMT>;
     constexpr int kUnitBytes = FmtTraits<FMT>::kUnitBytes;
@@ -366,9 +372,9 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_wp_kernel(const Gemv
     // G-th panel of the CTA and splits K between its GS warps.  Many panels per CTA -> small groups
     // (a warp stays longer on one panel, fewer hand-overs); few panels -> all sixteen warps split K.
     const int npc = p1 - p0;
-    int GS = npc >= 8 ? 4 : (npc >= 4 ? 8 : 16);
-    // short K: a panel has fewer chunks than the group has warps -- smaller groups, more panels in flight
-    while (GS > 4 && GS > (units + CH - 1) / CH) GS >>= 1;
+    // SHORTK (a panel has fewer chunks than sixteen): groups no larger than the chunk count, so that
+    // no warp idles and more panels are in flight.  A separate instantiation: the common one keeps its code.
+    const int GS = SHORTK ? wp_short_group(npc, (units + CH - 1) / CH) : (npc >= 8 ? 4 : (npc >= 4 ? 8 : 16));
     const int G = kSWarps / GS;
 
     // Set-up is spread over the warps and the CTA-wide barrier comes late: a consumer warp's ring
