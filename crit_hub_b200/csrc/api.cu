@@ -68,7 +68,7 @@ thread_local cudaError_t g_last_cuda_error = cudaSuccess;
     } while (0)
 
 constexpr int kMaxMoeSlots = 4096;
-constexpr size_t kChunkWsBytes = size_t(16) << 20;  // partial results of a K-chunked GEMV
+constexpr size_t kChunkWsBytes = size_t(64) << 20;  // partial results of a K-chunked GEMV / MoE GEMV
 constexpr int kGsMaxTiles = 4096;  // skinny GEMM: 128-row tiles a handle keeps counters for
 
 int64_t default_spin(const qgemv_handle* h) {
@@ -539,14 +539,35 @@ int qgemv_moe_gemv(qgemv_handle* h, const qgemv_weight* experts, const int32_t* 
     P.B = 0;
     P.y_dtype = out_dtype;
     P.prob = experts->prob;
-    if (qg::use_moe_stream_path(experts->units) && !(h->cfg.debug & 256)) {
-        const dim3 grid(gemv_grid(h)), block(qg::kSThreads);
-        err = experts->fmt == QGEMV_FMT_NVFP4
-                  ? launch(h, qg::moe_stream_kernel<QGEMV_FMT_NVFP4>, grid, block, qg::MSmem::total<QGEMV_FMT_NVFP4>(), s, P)
-                  : launch(h, qg::moe_stream_kernel<QGEMV_FMT_FP8>, grid, block, qg::MSmem::total<QGEMV_FMT_FP8>(), s, P);
-        return err == cudaSuccess ? QGEMV_OK : QGEMV_ERR_CUDA;
+    const dim3 grid(gemv_grid(h)), block(qg::kSThreads);
+    auto launch_stream = [&](const qg::GemvParams& Q) {
+        return experts->fmt == QGEMV_FMT_NVFP4
+                   ? launch(h, qg::moe_stream_kernel<QGEMV_FMT_NVFP4>, grid, block, qg::MSmem::total<QGEMV_FMT_NVFP4>(), s, Q)
+                   : launch(h, qg::moe_stream_kernel<QGEMV_FMT_FP8>, grid, block, qg::MSmem::total<QGEMV_FMT_FP8>(), s, Q);
+    };
+    if (h->cfg.debug & 256) return launch_gemv(h, experts, P, s);
+    if (qg::use_moe_stream_path(experts->units)) return launch_stream(P) == cudaSuccess ? QGEMV_OK : QGEMV_ERR_CUDA;
+    // Experts with K > 2048: one launch of the streaming kernel per K chunk of 32 units, each into its
+    // own fp32 slice [T*topk][N] of the handle's scratch, then the slices are added in chunk order.
+    const int unit_bytes = experts->fmt == QGEMV_FMT_NVFP4 ? QG_NVFP4_UNIT_BYTES : QG_FP8_UNIT_BYTES;
+    const int64_t cu = 32, n_chunks = (experts->units + cu - 1) / cu;
+    const int64_t slice = int64_t(T) * topk * experts->N;
+    if (size_t(n_chunks * slice) * sizeof(float) > kChunkWsBytes) return launch_gemv(h, experts, P, s);
+    for (int64_t c = 0; c < n_chunks; ++c) {
+        qg::GemvParams Pc = P;
+        const int64_t u0 = c * cu, u1 = std::min<int64_t>(experts->units, u0 + cu);
+        Pc.payload = P.payload + uint64_t(u0) * unit_bytes;
+        Pc.payload_bytes = experts->payload_bytes - uint64_t(u0) * unit_bytes;
+        Pc.x = P.x + u0 * QG_UNIT_K;
+        Pc.units = int32_t(u1 - u0);
+        Pc.K = int32_t(std::min<int64_t>(experts->K - u0 * QG_UNIT_K, (u1 - u0) * QG_UNIT_K));
+        Pc.y = h->chunk_ws + c * slice;
+        Pc.y_dtype = QGEMV_OUT_F32;
+        if (launch_stream(Pc) != cudaSuccess) return QGEMV_ERR_CUDA;
     }
-    return launch_gemv(h, experts, P, s);
+    err = launch(h, qg::chunk_sum_kernel, dim3(unsigned((slice + 255) / 256)), dim3(256), 0, s,
+                 static_cast<const float*>(h->chunk_ws), int(n_chunks), slice, out, out_dtype);
+    return err == cudaSuccess ? QGEMV_OK : QGEMV_ERR_CUDA;
 }
 
 int qgemv_moe_combine(qgemv_handle* h, const void* slot_out, int slot_dtype, const float* expert_w,

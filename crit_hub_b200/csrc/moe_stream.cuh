@@ -8,7 +8,8 @@
 // scale per row, as in the dense kernels), then stream the range's panels exactly like the dense
 // whole-panel kernel: warp groups split K, private bulk-copy rings per warp, an epilogue warp that
 // sums the K slices in warp order and scatters the rows to out[orow].
-// Needs units <= 32 (K <= 2048) so that two problems' fragments (8 rows each) fit 64 KB.
+// Needs units <= 32 (K <= 2048) per launch so that two problems' fragments (8 rows each) fit 64 KB;
+// longer K is served as several launches over K chunks whose results are added afterwards.
 #pragma once
 #include "gemv_stream.cuh"
 
@@ -159,7 +160,7 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stream_kernel(const GemvPara
     const uint32_t bars = sbase + SSmem::kBarFull + 8 * (w * kWpRing);
     const uint64_t pol = policy_evict_first();
     const bool drop = (P.debug & 2) != 0;
-    const uint64_t panel_bytes = uint64_t(units) * kUnitBytes;
+    const uint64_t panel_bytes = uint64_t(P.unit_stride) * kUnitBytes;  // a K-chunked call covers `units` of them
     const int n_phases = (units + QG_PHASE_UNITS - 1) / QG_PHASE_UNITS;  // 1 or 2
     unsigned int* rowmax = reinterpret_cast<unsigned int*>(smem_raw + MSmem::kRowMax16);
     int* rowexp = reinterpret_cast<int*>(smem_raw + MSmem::kRowExp16);
@@ -244,7 +245,7 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stream_kernel(const GemvPara
                     if (b_[z] < __ldcg(pr + 1)) {
                         act[z] = true;
                         const int64_t row = __ldcg(pr + 2 + b_[z]);
-                        const uint32_t m = load_row(rr[z], P.x + row * int64_t(P.K), P.K, f_[z], f_[z] * QG_PHASE_UNITS,
+                        const uint32_t m = load_row(rr[z], P.x + row * int64_t(P.x_stride), P.K, f_[z], f_[z] * QG_PHASE_UNITS,
                                                     min(units, (f_[z] + 1) * QG_PHASE_UNITS), lane);
                         if (lane == 0) atomicMax(rowmax + sel_[z] * 8 + b_[z], m);
                     }

@@ -232,6 +232,8 @@ int qgemv_gemm_skinny_plan(int fmt, int64_t N, int64_t K, int M, int sm_count, q
  *   row = t (per_slot_input == 0, gate/up stage) or t*topk + j (per_slot_input == 1, down stage).
  * experts: a stacked weight from qgemv_load_stacked; expert_ids: device int32 [T][topk];
  * x: device bf16; out: device [T*topk][N] bf16 or fp32.  T*topk <= 4096.
+ * Experts with K > 2048 run as several launches over K chunks plus a sum (fp32 partial results in
+ * a scratch that belongs to the handle: keep calls that share a handle on one stream).
  * No listed engine publishes an MoE kernel; the shape is the registry's `host_expert_gbs`
  * probe slot (engines/crit-labs/mtp5-nvfp4-drafts/evidence/crit-eval.json:124). */
 int qgemv_moe_gemv(qgemv_handle* h, const qgemv_weight* experts, const int32_t* expert_ids,

@@ -336,6 +336,30 @@ def test_moe_gemv(qg, handle, T, per_slot):
     w.unload()
 
 
+def test_moe_gemv_long_k(qg, handle):
+    """Experts with K > 2048 run as K chunks of the streaming kernel, added in chunk order."""
+    import torch
+    E, topk, T, N, K = 16, 4, 8, 256, 4352
+    codes, scales, ts = _experts(E, N, K, seed=900)
+    blobs = np.stack([qg.pack(qg.FMT_NVFP4, codes[e], scales[e], float(ts[e])) for e in range(E)])
+    w = handle.load_stacked(blobs)
+    ids, _ = _route(T, E, topk, seed=5)
+    x = O.make_x(T, K, seed=6)
+    ref = O.moe_gemv_nvfp4_f64(codes, scales, ts, ids, x, per_slot_input=False)
+    xd = U.dev_u16(x)
+    idd = torch.from_numpy(ids).cuda()
+    for dt, tol in ((qg.OUT_F32, TOL_F32), (qg.OUT_BF16, TOL_BF16)):
+        tdt = torch.float32 if dt == qg.OUT_F32 else torch.bfloat16
+        out = torch.full((T * topk, N), float("nan"), dtype=tdt, device="cuda")
+        handle.moe_gemv(w, idd.data_ptr(), xd.data_ptr(), T, topk, False, out.data_ptr(), dt)
+        torch.cuda.synchronize()
+        U.status_ok(handle)
+        got = out.float().cpu().numpy()
+        assert not np.isnan(got).any()
+        assert O.rel_l2(got, ref) < tol
+    w.unload()
+
+
 # ---- tensor-parallel exchange ----------------------------------------------------------------------
 def test_tp_allreduce_single_rank(qg):
     """World of one: the exchange degenerates to push-to-self, flag, reduce; replaying it checks
