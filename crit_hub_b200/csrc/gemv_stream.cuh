@@ -421,6 +421,12 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_wp_kernel(const Gemv
             const int rs = use % kSRedSlots;
             const uint32_t rpar = uint32_t(use / kSRedSlots) & 1u;
             const int bi = gidx * kSRedSlots + rs;
+            // FP8: fetch the panel's two channel scales before the wait, so their latency hides in it
+            float cs0 = 1.0f, cs1 = 1.0f;
+            if (FMT == QGEMV_FMT_FP8) {
+                cs0 = __ldg(P.chan_scale + p * 16 + (lane >> 2));  // padded to 16 rows per panel
+                cs1 = __ldg(P.chan_scale + p * 16 + (lane >> 2) + 8);
+            }
             if (!mbar_wait(sbase + SSmem::kBarRedFull + 8 * bi, rpar, P.spin_limit, 200u)) {
                 if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 6, p);
                 *abort_flag = 1;
@@ -434,8 +440,13 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_wp_kernel(const Gemv
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(sbase + SSmem::kBarRedEmpty + 8 * bi);
-            v.x *= ts, v.y *= ts, v.z *= ts, v.w *= ts;
-            store_panel<FMT>(P, v, lane, p, Bl, nullptr, P.chan_scale);
+            if (FMT == QGEMV_FMT_FP8) {
+                v.x *= cs0, v.y *= cs0, v.z *= cs1, v.w *= cs1;
+                store_panel<QGEMV_FMT_NVFP4>(P, v, lane, p, Bl, nullptr, nullptr);  // scaled already
+            } else {
+                v.x *= ts, v.y *= ts, v.z *= ts, v.w *= ts;
+                store_panel<FMT>(P, v, lane, p, Bl, nullptr, P.chan_scale);
+            }
             if (pf_pos < pf_end && lane == 0) {
                 const uint64_t stop = (i + 1 == npc || pf_pos + pf_step > pf_end) ? pf_end : pf_pos + pf_step;
                 while (pf_pos < stop) {
