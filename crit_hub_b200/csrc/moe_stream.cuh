@@ -43,6 +43,9 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stream_kernel(const GemvPara
     const uint32_t sbase = smem_u32(smem_raw);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int units = P.units;
+    // ring barriers do not depend on the problem table: set them up (spread over the warps) while the
+    // preceding kernel may still be running
+    if (warp < kSWarps && lane < kWpRing) mbar_init(sbase + SSmem::kBarFull + 8 * (warp * kWpRing + lane), 1);
     pdl_launch_dependents();
     pdl_wait();  // the problem table and the activations come from preceding kernels
     const int nprob = __ldcg(P.prob);
@@ -63,15 +66,15 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stream_kernel(const GemvPara
     while (GS < 16 && kSWarps / GS > npr) GS <<= 1;
     const int G = kSWarps / GS;
 
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < kSWarps * kWpRing; ++i) mbar_init(sbase + SSmem::kBarFull + 8 * i, 1);
-        for (int i = 0; i < kSWarps * kSRedSlots; ++i) {
-            mbar_init(sbase + kBarRedFull + 8 * i, uint32_t(GS));
-            mbar_init(sbase + kBarRedEmpty + 8 * i, 1);
+    if (warp == kSEpilogueWarp) {
+        static_assert(kSWarps * kSRedSlots <= 32, "one hand-over barrier pair per lane");
+        if (lane < kSWarps * kSRedSlots) {
+            mbar_init(sbase + kBarRedFull + 8 * lane, uint32_t(GS));
+            mbar_init(sbase + kBarRedEmpty + 8 * lane, 1);
         }
-        *reinterpret_cast<volatile int*>(smem_raw + SSmem::kAbort) = 0;
-        mbar_fence_init();
+        if (lane == 0) *reinterpret_cast<volatile int*>(smem_raw + SSmem::kAbort) = 0;
     }
+    mbar_fence_init();
     __syncthreads();
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + SSmem::kAbort);
 
