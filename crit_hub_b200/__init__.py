@@ -108,6 +108,7 @@ def _load() -> C.CDLL:
     L.qgemv_tp_connect.argtypes = [vp, vp]
     L.qgemv_tp_allreduce.argtypes = [vp, vp, i32, i64, vp]
     L.qgemv_gemv_noalloc.argtypes = [vp, vp, vp, i32, vp, i32, vp]
+    L.qgemv_noalloc_last_status.argtypes = [vp, C.POINTER(_DevStatus)]
     L.qgemv_moe_gemv.argtypes = [vp, vp, vp, vp, i32, i32, i32, vp, i32, vp]
     L.qgemv_moe_combine.argtypes = [vp, vp, i32, vp, i32, i32, i64, vp, i32, vp]
     L.qgemv_dequant_f32.argtypes = [vp, vp, i32, vp, vp]
@@ -303,6 +304,14 @@ def gemv_noalloc(dev_blob_ptr: int, host_blob: np.ndarray, x_ptr: int, B: int, y
     kernel's scratch is a static array inside the library (see include/qgemv.h for the limits)."""
     _check(_load().qgemv_gemv_noalloc(dev_blob_ptr, _np_ptr(host_blob), x_ptr, B, y_ptr, y_dtype, stream),
            "gemv_noalloc")
+
+
+def noalloc_last_status(stream: int = 0) -> DeviceStatus:
+    """Synchronises `stream` and returns the status word of the last allocation-free GEMV on the
+    current device (all zero when none has run, or when it ended without a report)."""
+    st = _DevStatus()
+    _check(_load().qgemv_noalloc_last_status(stream, C.byref(st)), "noalloc_last_status")
+    return DeviceStatus(st.code, st.where, st.block, st.extra)
 
 
 def gemm_skinny_plan(fmt: int, N: int, K: int, M: int, sm_count: int = 148) -> SkinnyPlan:

@@ -218,7 +218,8 @@ int qgemv_init(const qgemv_config* cfg, qgemv_handle** out) {
     if (cudaMalloc(&h->chunk_ws, kChunkWsBytes) != cudaSuccess ||
         cudaMalloc(&h->status_dev, 4 * sizeof(int32_t)) != cudaSuccess ||
         cudaMemset(h->status_dev, 0, 4 * sizeof(int32_t)) != cudaSuccess) {
-        delete h;
+        g_last_cuda_error = cudaGetLastError();
+        qgemv_destroy(h);  // frees whatever was allocated
         return QGEMV_ERR_CUDA;
     }
     const cudaFuncAttribute dyn = cudaFuncAttributeMaxDynamicSharedMemorySize;
@@ -240,8 +241,8 @@ int qgemv_init(const qgemv_config* cfg, qgemv_handle** out) {
         cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8, false, 1, true>, dyn, qg::SSmem::total<QGEMV_FMT_FP8>()) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemm_skinny_kernel<QGEMV_FMT_NVFP4>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemm_skinny_kernel<QGEMV_FMT_FP8>, dyn, qg::kGsSmemBudget) != cudaSuccess) {
-        cudaFree(h->status_dev);
-        delete h;
+        g_last_cuda_error = cudaGetLastError();
+        qgemv_destroy(h);
         return QGEMV_ERR_CUDA;
     }
     *out = h;
@@ -626,13 +627,19 @@ int qgemv_tp_create(qgemv_handle* h, int rank, int world, int64_t max_elems, voi
     QG_CUDA(cudaSetDevice(h->cfg.device));
     max_elems = (max_elems + 3) / 4 * 4;
     const size_t bytes = qg::tp_buffer_bytes(world, max_elems);
-    QG_CUDA(cudaMalloc(&h->tp_local, bytes));
-    QG_CUDA(cudaMemset(h->tp_local, 0, bytes));
-    QG_CUDA(cudaMalloc(&h->tp_epochs, qg::kTpCtas * 4));
-    QG_CUDA(cudaMemset(h->tp_epochs, 0, qg::kTpCtas * 4));
-    QG_CUDA(cudaDeviceSynchronize());
     cudaIpcMemHandle_t mh;
-    QG_CUDA(cudaIpcGetMemHandle(&mh, h->tp_local));
+    const bool ok = cudaMalloc(&h->tp_local, bytes) == cudaSuccess && cudaMemset(h->tp_local, 0, bytes) == cudaSuccess &&
+                    cudaMalloc(&h->tp_epochs, qg::kTpCtas * 4) == cudaSuccess &&
+                    cudaMemset(h->tp_epochs, 0, qg::kTpCtas * 4) == cudaSuccess &&
+                    cudaDeviceSynchronize() == cudaSuccess && cudaIpcGetMemHandle(&mh, h->tp_local) == cudaSuccess;
+    if (!ok) {
+        // leave the handle as it was, so that the call can be retried
+        g_last_cuda_error = cudaGetLastError();
+        cudaFree(h->tp_local);
+        cudaFree(h->tp_epochs);
+        h->tp_local = nullptr, h->tp_epochs = nullptr;
+        return QGEMV_ERR_CUDA;
+    }
     static_assert(sizeof(cudaIpcMemHandle_t) == QGEMV_IPC_HANDLE_BYTES, "IPC handle size");
     std::memcpy(ipc_handle_out, &mh, sizeof mh);
     h->tp_rank = rank;
@@ -707,6 +714,14 @@ NoAllocDevice g_noalloc_dev[kNoAllocMaxDevices];
 std::mutex g_noalloc_mutex;
 }  // namespace
 
+// Clears the arrival counters and the status word and stores the tensor scale ([16, 20) of `misc`).
+static __global__ void noalloc_prepare_kernel(int32_t* counters, int32_t n_counters, int32_t* misc, float tensor_scale) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n_counters) counters[i] = 0;
+    if (i < 4) misc[i] = 0;
+    if (i == 4) reinterpret_cast<float*>(misc)[4] = tensor_scale;
+}
+
 // In host code this name is only a stand-in for the symbol: the device address comes from
 // cudaGetSymbolAddress, once per device, below.
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
@@ -723,11 +738,20 @@ int qgemv_gemv_noalloc(const void* dev_blob, const void* host_header, const void
     if (hd.magic != QG_BLOB_MAGIC || hd.version != QG_BLOB_VERSION || hd.header_bytes != QG_HEADER_BYTES)
         return QGEMV_ERR_BAD_BLOB;
     if (hd.fmt != QGEMV_FMT_NVFP4 && hd.fmt != QGEMV_FMT_FP8) return QGEMV_ERR_BAD_BLOB;
-    if (hd.N <= 0 || hd.K <= 0 || hd.n_panels != (hd.N + 15) / 16 || hd.units_per_panel != (hd.K + 63) / 64)
+    if (hd.N <= 0 || hd.K <= 0 || hd.K % 16 != 0 || hd.n_panels != (hd.N + 15) / 16 ||
+        hd.units_per_panel != (hd.K + 63) / 64)
         return QGEMV_ERR_BAD_BLOB;
     // limits of the static scratch and of the schedule that uses it
     if (hd.n_panels > kNoAllocMaxPanels) return QGEMV_ERR_UNSUPPORTED_SHAPE;  // N above 262144 rows
-    if (!qg::use_stream_path(true, B, hd.units_per_panel)) return QGEMV_ERR_UNSUPPORTED_SHAPE;  // K * B above 32768
+    // ceil(K / 1024) * B above 32: the activations cannot be staged at once
+    if (!qg::use_stream_path(true, B, hd.units_per_panel)) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+    // aux_bytes, payload_bytes and unit_bytes are functions of (fmt, N, K): a header that disagrees is
+    // stale or damaged, and its values would move the payload pointer
+    const uint32_t unit_bytes = hd.fmt == QGEMV_FMT_NVFP4 ? QG_NVFP4_UNIT_BYTES : QG_FP8_UNIT_BYTES;
+    const uint64_t aux_bytes = hd.fmt == QGEMV_FMT_FP8 ? (uint64_t(hd.n_panels) * 16 * 4 + 255) / 256 * 256 : 0;
+    const uint64_t payload_bytes = uint64_t(hd.n_panels) * uint64_t(hd.units_per_panel) * unit_bytes;
+    if (hd.unit_bytes != unit_bytes || hd.aux_bytes != aux_bytes || hd.payload_bytes != payload_bytes)
+        return QGEMV_ERR_BAD_BLOB;
 
     int dev = 0;
     QG_CUDA(cudaGetDevice(&dev));
@@ -757,16 +781,16 @@ int qgemv_gemv_noalloc(const void* dev_blob, const void* host_header, const void
     unsigned char* ws = nd.scratch;
     unsigned char* counters = ws + kNoAllocWsBytes;
     unsigned char* misc = counters + kNoAllocCounterBytes;  // [0,16): status, [16,20): tensor scale
-    // The array keeps the previous call's contents: counters and status must start at zero.
-    QG_CUDA(cudaMemsetAsync(counters, 0, size_t(hd.n_panels) * 4, s));
-    QG_CUDA(cudaMemsetAsync(misc, 0, 16, s));
-    const float ts = hd.tensor_scale;
-    QG_CUDA(cudaMemcpyAsync(misc + 16, &ts, 4, cudaMemcpyHostToDevice, s));
+    // The array keeps the previous call's contents: counters and status must start at zero.  One small
+    // kernel clears them and stores the tensor scale (passed by value: no host pointer outlives the call).
+    noalloc_prepare_kernel<<<dim3(unsigned((hd.n_panels + 255) / 256)), dim3(256), 0, s>>>(
+        reinterpret_cast<int32_t*>(counters), int32_t(hd.n_panels), reinterpret_cast<int32_t*>(misc), hd.tensor_scale);
+    QG_CUDA(cudaGetLastError());
 
     qg::GemvParams P;
     std::memset(&P, 0, sizeof P);
     const uint8_t* blob = static_cast<const uint8_t*>(dev_blob);
-    P.payload = blob + QG_HEADER_BYTES + hd.aux_bytes;
+    P.payload = blob + QG_HEADER_BYTES + aux_bytes;
     P.stack_stride = 0;
     P.chan_scale = reinterpret_cast<const float*>(blob + QG_HEADER_BYTES);
     P.chan_stride = 0;
@@ -787,7 +811,7 @@ int qgemv_gemv_noalloc(const void* dev_blob, const void* host_header, const void
     P.B = B;
     P.y_dtype = y_dtype;
     P.debug = 0;
-    P.payload_bytes = hd.payload_bytes;
+    P.payload_bytes = payload_bytes;
     const dim3 grid(nd.sm_count), block(qg::kSThreads);
     if (hd.fmt == QGEMV_FMT_NVFP4) {
         qg::gemv_stream_kernel<QGEMV_FMT_NVFP4><<<grid, block, qg::SSmem::total<QGEMV_FMT_NVFP4>(), s>>>(P);
@@ -795,6 +819,21 @@ int qgemv_gemv_noalloc(const void* dev_blob, const void* host_header, const void
         qg::gemv_stream_kernel<QGEMV_FMT_FP8><<<grid, block, qg::SSmem::total<QGEMV_FMT_FP8>(), s>>>(P);
     }
     QG_CUDA(cudaGetLastError());
+    return QGEMV_OK;
+}
+
+int qgemv_noalloc_last_status(void* stream, qgemv_dev_status* out) {
+    if (!out) return QGEMV_ERR_INVALID_ARG;
+    int dev = 0;
+    QG_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kNoAllocMaxDevices) return QGEMV_ERR_INVALID_ARG;
+    out->code = out->where = out->block = out->extra = 0;
+    const NoAllocDevice& nd = g_noalloc_dev[dev];
+    if (!nd.ready) return QGEMV_OK;  // no call has run on this device yet
+    QG_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    int32_t v[4];
+    QG_CUDA(cudaMemcpy(v, nd.scratch + kNoAllocWsBytes + kNoAllocCounterBytes, sizeof v, cudaMemcpyDeviceToHost));
+    out->code = v[0], out->where = v[1], out->block = v[2], out->extra = v[3];
     return QGEMV_OK;
 }
 

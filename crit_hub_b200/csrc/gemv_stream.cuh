@@ -58,8 +58,14 @@ struct SSmem {
     }
 };
 
+// The activation staging (stream_convert_x) converts at most two (phase, row) pairs per consumer
+// warp, a phase being 16 units, and lays a phase out as batch * 2048 bytes: the gate therefore
+// counts whole phases.  units * batch <= 512 alone would admit ragged K with 33..35 pairs
+// (e.g. 72 units at batch 7), more than the warps convert and than the buffer holds.
 inline bool use_stream_path(bool dense, int batch, int64_t units) {
-    return dense && batch >= 1 && units * batch <= kSMaxUnitsTimesBatch;
+    const int64_t n_phases = (units + QG_PHASE_UNITS - 1) / QG_PHASE_UNITS;
+    return dense && batch >= 1 && n_phases * batch <= 2 * kSWarps &&
+           n_phases * batch * (QG_PHASE_UNITS * 128) <= kSXBufBytes;
 }
 
 __device__ __forceinline__ void fence_proxy_async_smem() {

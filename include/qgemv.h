@@ -180,15 +180,21 @@ int qgemv_tp_allreduce(qgemv_handle* h, void* y, int y_dtype, int64_t n, void* s
  * The kernel's scratch (partial sums and arrival counters of panels split between CTAs, a status
  * word, the tensor scale) is a 320 KiB array compiled into the library; every GPU that loads
  * the library holds it until the process exits.
- * Limits (QGEMV_ERR_UNSUPPORTED_SHAPE beyond them): N <= 262144 rows, K * B <= 32768, B <= 8,
- * at most 256 SMs.
+ * Limits (QGEMV_ERR_UNSUPPORTED_SHAPE beyond them): N <= 262144 rows, ceil(K / 1024) * B <= 32
+ * (e.g. K <= 32768 at B = 1, K <= 4096 at B = 8), B <= 8, at most 256 SMs.  The header is checked
+ * against the sizes that follow from its format and shape (QGEMV_ERR_BAD_BLOB when they disagree).
  * The first call on a device resolves the array's device address and sets kernel attributes;
  * make that first call before any stream capture.  All calls share the one array, and it keeps
  * the previous call's contents: the call clears what must start at zero on `stream`, so calls
  * that overlap on the GPU (different streams, or concurrent threads) race -- serialise them.
- * Results equal qgemv_gemv's up to the summation order of the K split. */
+ * Results equal qgemv_gemv's up to the summation order of the K split.
+ * A bounded in-kernel wait that runs out leaves y unwritten and records itself in the array's status
+ * word, which qgemv_gemv_noalloc never reads back (it does not synchronise):
+ * qgemv_noalloc_last_status synchronises `stream` and copies out the status of the last call on the
+ * current device (all zero when none has run).  It allocates nothing either. */
 int qgemv_gemv_noalloc(const void* dev_blob, const void* host_header, const void* x_bf16, int B, void* y,
                        int y_dtype, void* stream);
+int qgemv_noalloc_last_status(void* stream, qgemv_dev_status* out);
 
 /* ---- skinny GEMM / short prefill -------------------------------------------------------------------
  * Y[M][N] = X[M][K] . dequant(W)^T for M = 16 .. 256 tokens (a multiple of 16) on the tcgen05

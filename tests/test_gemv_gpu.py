@@ -117,6 +117,39 @@ def test_gemv_k_chunked(qg, handle, N, K, B):
     w.unload()
 
 
+# Ragged K where units * B <= 512 but ceil(K / 1024) * B exceeds the 32 (phase, row) pairs the
+# activation staging of the streaming kernels holds, and the nearest shapes on the other side of
+# that edge.  Default schedule, the always-split streaming kernel (bit 9) and both formats.
+_EDGE = [(512, 4608, 7), (512, 4160, 7), (512, 5184, 6), (512, 5376, 6), (512, 6208, 5), (512, 6400, 5),
+         (256, 10304, 3), (256, 10752, 3),
+         (512, 4096, 7), (512, 4096, 8), (512, 5120, 6), (512, 6144, 5), (256, 10240, 3), (4096, 4608, 7)]
+
+
+@pytest.mark.parametrize("N,K,B", _EDGE)
+@pytest.mark.parametrize("bits", [0, 512])
+def test_gemv_activation_staging_edge(qg, handle, N, K, B, bits):
+    h = handle if bits == 0 else qg.QGemv(debug_bits=bits, debug=True)
+    x = O.make_x(B, K, seed=K + B)
+    codes, scales, ts = O.make_nvfp4(N, K, seed=N + K + B, ts=0.75)
+    w = h.load(qg.pack(qg.FMT_NVFP4, codes, scales, ts))
+    y = U.run_gemv(qg, h, w, x, h=h)
+    U.status_ok(h)
+    ref = O.gemv_nvfp4_f64(codes, scales, ts, x)
+    for b in range(B):  # per row: an unstaged row would hide in a whole-matrix norm
+        assert O.rel_l2(y[b], ref[b]) < TOL_F32, (b, N, K, B)
+    w.unload()
+    codes8, scales8 = O.make_fp8(N, K, seed=N + K + B)
+    w = h.load(qg.pack(qg.FMT_FP8, codes8, scales8))
+    y = U.run_gemv(qg, h, w, x, h=h)
+    U.status_ok(h)
+    ref = O.gemv_fp8_f64(codes8, scales8, x)
+    for b in range(B):
+        assert O.rel_l2(y[b], ref[b]) < TOL_F32, (b, N, K, B)
+    w.unload()
+    if bits:
+        h.close()
+
+
 def test_gemv_k_chunked_fp8(qg, handle):
     N, K, B = 4096, 8192, 8
     codes, scales = O.make_fp8(N, K, seed=5)

@@ -42,7 +42,31 @@ def test_noalloc_matches_regular_entry_point(qg, handle, N, K, B):
             first = got
         else:
             assert np.array_equal(U.bits(got), U.bits(first))
+        st = qg.noalloc_last_status()
+        assert st.code == 0, st
     w.unload()
+
+
+@pytest.mark.parametrize("N,K,B", [(512, 4608, 7), (512, 4160, 7), (512, 5184, 6), (512, 6208, 5), (256, 10304, 3)])
+def test_noalloc_ragged_k_edge(qg, N, K, B):
+    """Shapes with units * B <= 512 but more than 32 (phase, row) pairs: beyond what the activation
+    staging holds, so the entry point must refuse them instead of computing with unstaged rows."""
+    import torch
+    codes, scales, ts = O.make_nvfp4(N, K, seed=K + B)
+    blob = qg.pack(qg.FMT_NVFP4, codes, scales, ts)
+    dev_blob = torch.from_numpy(blob).cuda()
+    x = torch.zeros(B * K, dtype=torch.bfloat16, device="cuda")
+    y = torch.zeros(B * N, dtype=torch.float32, device="cuda")
+    with pytest.raises(qg.QgemvError) as e:
+        qg.gemv_noalloc(dev_blob.data_ptr(), blob, x.data_ptr(), B, y.data_ptr(), qg.OUT_F32)
+    assert e.value.status == qg.ERR_UNSUPPORTED_SHAPE
+    # one row fewer fits: results match the oracle
+    Bf = B - 1 if (K + 1023) // 1024 * (B - 1) <= 32 else 1
+    xf = O.make_x(Bf, K, seed=3)
+    yf = torch.full((Bf, N), float("nan"), dtype=torch.float32, device="cuda")
+    qg.gemv_noalloc(dev_blob.data_ptr(), blob, U.dev_u16(xf).data_ptr(), Bf, yf.data_ptr(), qg.OUT_F32)
+    torch.cuda.synchronize()
+    assert O.rel_l2(yf.cpu().numpy(), O.gemv_nvfp4_f64(codes, scales, ts, xf)) < TOL_F32
 
 
 def test_noalloc_fp8_and_bf16_output(qg, handle):
@@ -67,7 +91,7 @@ def test_noalloc_rejects_sizes_beyond_its_scratch(qg):
     dev_blob = torch.from_numpy(blob).cuda()
     x = torch.zeros(8 * 8192, dtype=torch.bfloat16, device="cuda")
     y = torch.zeros(8 * 16, dtype=torch.float32, device="cuda")
-    with pytest.raises(qg.QgemvError) as e:   # K * B = 65536 is above the 32768 limit
+    with pytest.raises(qg.QgemvError) as e:   # ceil(K / 1024) * B = 64 phases-times-rows, above 32
         qg.gemv_noalloc(dev_blob.data_ptr(), blob, x.data_ptr(), 8, y.data_ptr(), qg.OUT_F32)
     assert e.value.status == qg.ERR_UNSUPPORTED_SHAPE
     big = blob.copy()
@@ -81,3 +105,11 @@ def test_noalloc_rejects_sizes_beyond_its_scratch(qg):
     with pytest.raises(qg.QgemvError) as e:
         qg.gemv_noalloc(dev_blob.data_ptr(), bad, x.data_ptr(), 1, y.data_ptr(), qg.OUT_F32)
     assert e.value.status == qg.ERR_BAD_BLOB
+    # a header whose aux / payload sizes do not follow from its format and shape is refused
+    hd = np.frombuffer(blob[:256].tobytes(), dtype=np.uint8).copy()
+    for off in (64, 72):   # aux_bytes, payload_bytes
+        stale = blob.copy()
+        stale[off:off + 8] = np.frombuffer(np.uint64(int(np.frombuffer(hd[off:off + 8].tobytes(), dtype=np.uint64)[0]) + 576).tobytes(), dtype=np.uint8)
+        with pytest.raises(qg.QgemvError) as e:
+            qg.gemv_noalloc(dev_blob.data_ptr(), stale, x.data_ptr(), 1, y.data_ptr(), qg.OUT_F32)
+        assert e.value.status == qg.ERR_BAD_BLOB, off
