@@ -99,7 +99,7 @@ class ClockSampler:
         return out
 
 
-def build_stack(model, batch, rank, world, dev_index):
+def build_stack(model, batch, rank, world, dev_index, layout="tc"):
     """The rank's share of the layer stack.  Tensor parallel: QKV and gate/up are column-parallel
     (this rank holds N/world output rows), o and down are row-parallel (K/world input columns; their
     outputs are partial sums that are all-reduced right after the GEMV, inside the captured graph).
@@ -123,7 +123,7 @@ def build_stack(model, batch, rank, world, dev_index):
                 else:
                     K = K // world
             codes, scales = synth_nvfp4(N, K, (1000 * layer + mi) * 16 + rank, device)
-            w = handle.load(qg.pack(qg.FMT_NVFP4, codes, scales, 1.0))
+            w = handle.load(qg.pack(qg.FMT_NVFP4_TC if layout == "tc" else qg.FMT_NVFP4, codes, scales, 1.0))
             weights.append(w)
             row_parallel.append(world > 1 and name in ("o", "down"))
             total_bytes += w.weight_bytes
@@ -511,6 +511,9 @@ def main():
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "lmhead", "moe"],
                     help="decode: the headline GEMV layer stack; prefill: the skinny GEMM over one 70B-shaped layer; "
                          "lmhead: the FP8 output head; moe: the grouped expert GEMV (--tokens 1/8/64)")
+    ap.add_argument("--layout", default="lane", choices=["tc", "lane"],
+                    help="stored form of the NVFP4 weights: tc = tile order consumed as stored by the block-scaled "
+                         "tensor-core GEMV; lane = lane-ordered units for the CUDA-core GEMV")
     ap.add_argument("--tokens", type=int, default=256, help="rows of the prefill workload (16..256, multiple of 16)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -552,7 +555,7 @@ def main():
             print(f"[rank {rank}] {msg}", file=sys.stderr, flush=True)
 
     note("building the stack")
-    handle, stack, rank_bytes = build_stack(model, args.batch, rank, world, local)
+    handle, stack, rank_bytes = build_stack(model, args.batch, rank, world, local, args.layout)
     note("capturing")
     stack.capture()
     note("captured")

@@ -17,6 +17,7 @@ from . import _build
 
 FMT_NVFP4 = 1
 FMT_FP8 = 2
+FMT_NVFP4_TC = 3   # NVFP4 in the tile order the block-scaled tensor-core GEMV consumes as stored
 OUT_BF16 = 0
 OUT_F32 = 1
 ACT_A16_EXACT = 0
@@ -47,7 +48,8 @@ class QgemvError(RuntimeError):
 
 class _Config(C.Structure):
     _fields_ = [("device", C.c_int32), ("use_pdl", C.c_int32), ("grid_override", C.c_int32),
-                ("debug", C.c_int32), ("spin_limit", C.c_int64)]
+                ("debug", C.c_int32), ("spin_limit", C.c_int64), ("tc_stage_items", C.c_int32),
+                ("tc_smem_kb", C.c_int32)]
 
 
 class Shard(C.Structure):
@@ -145,7 +147,7 @@ def pack(fmt: int, codes: np.ndarray, scales: np.ndarray, tensor_scale: float = 
 
     NVFP4: codes u8 [N][K/2], scales u8 [N][K/16].  FP8: codes u8 [N][K], scales f32 [N].
     """
-    if fmt == FMT_NVFP4:
+    if fmt in (FMT_NVFP4, FMT_NVFP4_TC):
         N, K = scales.shape[0], scales.shape[1] * 16
         if codes.dtype != np.uint8 or scales.dtype != np.uint8 or codes.shape != (N, K // 2):
             raise ValueError("NVFP4 wants codes u8 [N][K/2] and scales u8 [N][K/16]")
@@ -179,7 +181,7 @@ def blob_verify(blob: np.ndarray) -> int:
 def unpack(blob: np.ndarray):
     """Inverse of pack(): returns (codes, scales, tensor_scale) of the sub-matrix in the blob."""
     fmt, N, K = blob_info(blob)
-    if fmt == FMT_NVFP4:
+    if fmt in (FMT_NVFP4, FMT_NVFP4_TC):
         codes = np.empty((N, K // 2), dtype=np.uint8)
         scales = np.empty((N, K // 16), dtype=np.uint8)
     else:
@@ -214,10 +216,12 @@ class QGemv:
     """One library handle on one device."""
 
     def __init__(self, device: int = 0, use_pdl: bool = True, grid_override: int = 0, debug: bool = False,
-                 spin_limit: int = 0, inject_drop_copies: bool = False, debug_bits: int = 0):
+                 spin_limit: int = 0, inject_drop_copies: bool = False, debug_bits: int = 0,
+                 tc_stage_items: int = 0, tc_smem_kb: int = 0):
         L = _load()
         cfg = _Config(device, 1 if use_pdl else 0, grid_override,
-                      (1 if debug else 0) | (2 if inject_drop_copies else 0) | debug_bits, spin_limit)
+                      (1 if debug else 0) | (2 if inject_drop_copies else 0) | debug_bits, spin_limit,
+                      tc_stage_items, tc_smem_kb)
         h = C.c_void_p()
         _check(L.qgemv_init(C.byref(cfg), C.byref(h)), "init")
         self._ptr = h.value

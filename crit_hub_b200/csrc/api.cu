@@ -14,6 +14,7 @@
 #include "gemv_kernel.cuh"
 #include "gemv_stream.cuh"
 #include "gemm_skinny.cuh"
+#include "gemv_tc.cuh"
 #include "moe_stream.cuh"
 #include "tp_allreduce.cuh"
 #include "qgemv_layout.h"
@@ -35,6 +36,9 @@ struct qgemv_handle {
     size_t gs_ws_bytes;
     // K-chunked GEMV: fp32 partial results [chunk][B][N], fixed size, allocated with the handle
     float* chunk_ws;
+    // tensor-core GEMV: partial slots (two per CTA, [8][128] fp32 each) and per-tile arrival counters
+    float* tc_ws;
+    int32_t* tc_counters;
 };
 
 struct qgemv_weight {
@@ -171,6 +175,87 @@ int launch_gemv(const qgemv_handle* h, const qgemv_weight* w, const qg::GemvPara
     return err == cudaSuccess ? QGEMV_OK : QGEMV_ERR_CUDA;
 }
 
+// ---- tensor-core GEMV (QGEMV_FMT_NVFP4_TC) -------------------------------------------------------
+// Shared-memory plan of one launch over `kt_len` items per tile: digit-plane slots for the items a
+// CTA can own, then as many ring stages as the cap allows.
+struct TcPlan {
+    int grid, npad, x_slots, ring, stage_items;
+    size_t smem;
+};
+bool tc_plan(const qgemv_handle* h, int64_t tiles, int64_t kt_len, int B, TcPlan* pl) {
+    const int64_t total = tiles * kt_len;
+    pl->grid = int(std::min<int64_t>(gemv_grid(h), total));
+    pl->npad = (8 * B + 15) / 16 * 16;
+    const int64_t per_cta = (total + pl->grid - 1) / pl->grid;
+    pl->x_slots = int(std::min<int64_t>(kt_len, per_cta));
+    pl->stage_items = h->cfg.tc_stage_items > 0 ? std::min(h->cfg.tc_stage_items, 8) : 4;
+    const int stage_bytes = pl->stage_items * qg::kTcItemBytes;
+    const int base = qg::TcSmem::ring_off(pl->x_slots, pl->npad);
+    // Prefer a footprint of about half an SM: the CTA of the next kernel in the stream is then
+    // resident beside this one and fills its ring while this one still streams.
+    const int want_cap = (h->cfg.tc_smem_kb > 0 ? std::min(h->cfg.tc_smem_kb, 227) : 112) * 1024;
+    int ring = (want_cap - base) / stage_bytes;
+    if (ring < 4) ring = (qg::kGsSmemBudget - base) / stage_bytes;  // large activations: the whole SM
+    if (ring > qg::kTcMaxRing) ring = qg::kTcMaxRing;
+    if (ring < 2) return false;
+    pl->ring = ring;
+    pl->smem = size_t(qg::TcSmem::total(pl->x_slots, pl->npad, ring, pl->stage_items));
+    return pl->smem <= size_t(qg::kGsSmemBudget);
+}
+
+int gemv_tc(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, int B, void* y, int y_dtype,
+            cudaStream_t stream) {
+    const int64_t tiles = w->n_panels / 8, kt_total = w->units;
+    // K window per launch: the whole K when the digit planes of a CTA's items fit beside a ring,
+    // otherwise chunks of items whose fp32 results are added in chunk order (as the K-chunked
+    // CUDA-core path does; the chunk length depends on B).
+    int64_t kt_chunk = kt_total;
+    TcPlan pl;
+    while (!tc_plan(h, tiles, kt_chunk, B, &pl)) {
+        if (kt_chunk <= 4) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+        kt_chunk = ((kt_chunk + 1) / 2 + 3) / 4 * 4;
+    }
+    const int64_t n_chunks = (kt_total + kt_chunk - 1) / kt_chunk;
+    const int64_t slice = int64_t(B) * w->N;
+    if (n_chunks > 1 && size_t(n_chunks * slice) * sizeof(float) > kChunkWsBytes) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+    for (int64_t c = 0; c < n_chunks; ++c) {
+        const int64_t k0 = c * kt_chunk, k1 = std::min(kt_total, k0 + kt_chunk);
+        if (k1 - k0 != kt_chunk && !tc_plan(h, tiles, k1 - k0, B, &pl)) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+        qg::TcParams P;
+        std::memset(&P, 0, sizeof P);
+        P.payload = w->dev_blob + QG_HEADER_BYTES + w->aux_bytes;
+        P.x = static_cast<const uint16_t*>(x_bf16) + k0 * 64;
+        P.y = n_chunks == 1 ? y : static_cast<void*>(h->chunk_ws + c * slice);
+        P.ws = h->tc_ws;
+        P.counters = h->tc_counters;
+        P.status = h->status_dev;
+        P.spin_limit = default_spin(h);
+        P.tensor_scale = w->host_tensor_scale[0];
+        P.N = int32_t(w->N);
+        P.K = int32_t(std::min<int64_t>(w->K - k0 * 64, (k1 - k0) * 64));
+        P.tiles = int32_t(tiles);
+        P.kt_total = int32_t(kt_total);
+        P.kt0 = int32_t(k0);
+        P.kt_len = int32_t(k1 - k0);
+        P.x_stride = int32_t(w->K);
+        P.B = B;
+        P.y_dtype = n_chunks == 1 ? y_dtype : QGEMV_OUT_F32;
+        P.debug = h->cfg.debug;
+        P.npad = pl.npad;
+        P.ring = pl.ring;
+        P.stage_items = pl.stage_items;
+        P.x_slots = pl.x_slots;
+        if (launch(h, qg::gemv_tc_kernel, dim3(unsigned(pl.grid)), dim3(qg::kTcThreads), pl.smem, stream, P) != cudaSuccess)
+            return QGEMV_ERR_CUDA;
+    }
+    if (n_chunks > 1) {
+        const cudaError_t err = launch(h, qg::chunk_sum_kernel, dim3(unsigned((slice + 255) / 256)), dim3(256), 0, stream,
+                                       static_cast<const float*>(h->chunk_ws), int(n_chunks), slice, y, y_dtype);
+        return err == cudaSuccess ? QGEMV_OK : QGEMV_ERR_CUDA;
+    }
+    return QGEMV_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -215,7 +300,12 @@ int qgemv_init(const qgemv_config* cfg, qgemv_handle** out) {
     for (int i = 0; i < qg::kTpMaxWorld; ++i) h->tp_peer[i] = nullptr;
     h->gs_ws = nullptr, h->gs_ws_bytes = 0;
     h->chunk_ws = nullptr;
-    if (cudaMalloc(&h->chunk_ws, kChunkWsBytes) != cudaSuccess ||
+    h->tc_ws = nullptr, h->tc_counters = nullptr;
+    const size_t tc_ws_bytes = size_t(2) * size_t(std::max(h->sm_count, cfg->grid_override)) * 1024 * sizeof(float);
+    if (cudaMalloc(&h->tc_ws, tc_ws_bytes) != cudaSuccess ||
+        cudaMalloc(&h->tc_counters, size_t(qg::kTcMaxTiles) * 4 * sizeof(int32_t)) != cudaSuccess ||
+        cudaMemset(h->tc_counters, 0, size_t(qg::kTcMaxTiles) * 4 * sizeof(int32_t)) != cudaSuccess ||
+        cudaMalloc(&h->chunk_ws, kChunkWsBytes) != cudaSuccess ||
         cudaMalloc(&h->status_dev, 4 * sizeof(int32_t)) != cudaSuccess ||
         cudaMemset(h->status_dev, 0, 4 * sizeof(int32_t)) != cudaSuccess) {
         g_last_cuda_error = cudaGetLastError();
@@ -239,6 +329,7 @@ int qgemv_init(const qgemv_config* cfg, qgemv_handle** out) {
         cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_NVFP4, false, 1, true>, dyn, qg::SSmem::total<QGEMV_FMT_NVFP4>()) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8, true, 1, true>, dyn, qg::SSmem::total<QGEMV_FMT_FP8>()) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8, false, 1, true>, dyn, qg::SSmem::total<QGEMV_FMT_FP8>()) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_tc_kernel, dyn, qg::kGsSmemBudget) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemm_skinny_kernel<QGEMV_FMT_NVFP4>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemm_skinny_kernel<QGEMV_FMT_FP8>, dyn, qg::kGsSmemBudget) != cudaSuccess) {
         g_last_cuda_error = cudaGetLastError();
@@ -258,6 +349,8 @@ int qgemv_destroy(qgemv_handle* h) {
     cudaFree(h->tp_epochs);
     cudaFree(h->gs_ws);
     cudaFree(h->chunk_ws);
+    cudaFree(h->tc_ws);
+    cudaFree(h->tc_counters);
     cudaFree(h->status_dev);
     delete h;
     return QGEMV_OK;
@@ -280,6 +373,9 @@ int qgemv_load_stacked(qgemv_handle* h, const void* host_blobs, size_t bytes_eac
         ts[size_t(i)] = hi->tensor_scale;
     }
     if (h0->N > INT32_MAX || h0->K > INT32_MAX || h0->n_panels * h0->units_per_panel > (int64_t(1) << 40))
+        return QGEMV_ERR_UNSUPPORTED_SHAPE;
+    if (h0->fmt == QGEMV_FMT_NVFP4_TC &&
+        (n_stacked != 1 || h0->n_panels / 8 > qg::kTcMaxTiles || h0->n_panels / 8 * h0->units_per_panel > INT32_MAX))
         return QGEMV_ERR_UNSUPPORTED_SHAPE;
     QG_CUDA(cudaSetDevice(h->cfg.device));
     qgemv_weight* w = new (std::nothrow) qgemv_weight;
@@ -342,7 +438,7 @@ int qgemv_unload(qgemv_handle* h, qgemv_weight* w) {
 
 int64_t qgemv_weight_bytes(const qgemv_weight* w) {
     if (!w) return QGEMV_ERR_INVALID_ARG;
-    if (w->fmt == QGEMV_FMT_NVFP4) return w->N * w->K / 2 + w->N * w->K / 16 + 4;
+    if (w->fmt != QGEMV_FMT_FP8) return w->N * w->K / 2 + w->N * w->K / 16 + 4;
     return w->N * w->K + 4 * w->N;
 }
 
@@ -357,6 +453,7 @@ int qgemv_gemv_prefetch(qgemv_handle* h, const qgemv_weight* w, const void* x_bf
     if (B < 1 || B > QGEMV_MAX_ROWS) return QGEMV_ERR_UNSUPPORTED_SHAPE;
     if (y_dtype != QGEMV_OUT_BF16 && y_dtype != QGEMV_OUT_F32) return QGEMV_ERR_INVALID_ARG;
     if ((reinterpret_cast<uintptr_t>(x_bf16) & 15u) != 0) return QGEMV_ERR_INVALID_ARG;
+    if (w->fmt == QGEMV_FMT_NVFP4_TC && B <= QGEMV_MAX_BATCH) return gemv_tc(h, w, x_bf16, B, y, y_dtype, static_cast<cudaStream_t>(stream));
     if (B > QGEMV_MAX_BATCH) {
         // two launches: rows 0..7, then the rest (the second one names the next matrix)
         if ((w->K * 2 * QGEMV_MAX_BATCH) % 16 != 0) return QGEMV_ERR_UNSUPPORTED_SHAPE;
@@ -455,6 +552,7 @@ int qgemv_gemm_skinny(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16
     if ((reinterpret_cast<uintptr_t>(x_bf16) & 15u) != 0) return QGEMV_ERR_INVALID_ARG;
     if (M < 16 || M > qg::kGsMaxM || M % 16 != 0) return QGEMV_ERR_UNSUPPORTED_SHAPE;
     if (w->n_stack != 1 || w->N % 128 != 0 || w->K % 64 != 0) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+    if (w->fmt == QGEMV_FMT_NVFP4_TC) return QGEMV_ERR_UNSUPPORTED_SHAPE;  // wants the lane-ordered layout
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     QG_CUDA(cudaSetDevice(h->cfg.device));
     const int tiles = int(w->N / 128);
@@ -594,6 +692,12 @@ int qgemv_dequant_f32(qgemv_handle* h, const qgemv_weight* w, int which, float* 
     const int threads = 128;
     const unsigned blocks = unsigned((warps * 32 + threads - 1) / threads);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (w->fmt == QGEMV_FMT_NVFP4_TC) {
+        const int64_t n_threads = w->N * (w->K / 16);
+        qg::dequant_tc_kernel<<<unsigned((n_threads + 255) / 256), 256, 0, s>>>(payload, w->host_tensor_scale[which], int32_t(w->N),
+                                                                                int32_t(w->K), int32_t(w->units), out_dev);
+        return cudaGetLastError() == cudaSuccess ? QGEMV_OK : QGEMV_ERR_CUDA;
+    }
     if (w->fmt == QGEMV_FMT_NVFP4) {
         qg::dequant_kernel<QGEMV_FMT_NVFP4><<<blocks, threads, 0, s>>>(payload, chan, ts, int32_t(w->N),
                                                                       int32_t(w->K), int32_t(w->units), out_dev);

@@ -1,0 +1,533 @@
+// NVFP4 GEMV, batch 1..8, on the block-scaled tensor-core path: the packed weights are consumed
+// exactly as stored.
+//
+// The CUDA-core GEMV (gemv_stream.cuh) converts every E2M1 code to f16 and multiplies it by its
+// block scale in registers; measured, that instruction stream -- not HBM -- bounds it.  Here no SM
+// instruction touches a weight byte: tcgen05.mma kind::mxf4nvf4 with scale_vec::4X takes E2M1
+// operands with one E4M3 scale per 16 K elements, which is NVFP4 itself.  The packer
+// (QGEMV_FMT_NVFP4_TC) stores a 128-row x 64-K ITEM as 4096 bytes of codes in the K-major no-swizzle
+// core-matrix order of the MMA's A operand followed by 512 bytes of scales in the order
+// tcgen05.cp.32x128b.warpx4 copies into tensor memory; items of one row tile are contiguous along
+// K, so a bulk copy of any run of items is one contiguous range.  The kernel is then a pure
+// stream: bulk copies into a shared-memory ring, one tcgen05.cp + one tcgen05.mma per item issued
+// by a single thread, accumulators in tensor memory.
+//
+// Activations are bf16 and must stay (nearly) exact, but the B operand of this MMA kind is E2M1
+// too.  Each activation row is therefore written as EIGHT E2M1 digit planes: the row is scaled by a
+// power of two so that its largest magnitude lies in [2^15, 2^16), rounded to a 16-bit integer
+// magnitude n, and plane j holds the base-4 digit d_j = (n >> 2j) & 3 as the E2M1 code of d_j / 2
+// (codes 0..3 are 0, 0.5, 1, 1.5) with the element's sign; the plane's block scale is the constant
+// 2^(2j-6), a power of two that E4M3 holds exactly.  The eight planes of a row are eight columns of
+// the MMA's N extent; their accumulators are added in plane order in the epilogue and the power of
+// two is undone in fp32.  A row element is exact when it lies within 2^-8 of the row maximum
+// (bf16 has 8 significant bits) and otherwise rounded to 2^-16 of the row maximum.
+//
+// Work split: the linear space (row tile, item) is cut evenly over the CTAs; a CTA's range is a
+// sequence of segments, each a K range of one row tile.  A segment that covers its whole tile
+// stores y; otherwise the fp32 partial sums go to a workspace slot and the last contributor of the
+// tile (atomic counter) adds all parts in CTA order -- a deterministic split along K that depends
+// only on the shape and the CTA count.
+//
+// Warp roles (10 warps):
+//   0     one thread issues the bulk copies of packed items (ring of stages)
+//   1     allocates tensor memory; one elected lane issues tcgen05.cp / tcgen05.mma and the commits
+//   2-9   convert the activations into digit planes (after the dependency wait), then run the
+//         epilogues: warps 2-5 take the CTA's even segments, 6-9 the odd ones (two accumulators)
+// Every wait is bounded; tensor memory is always released before the CTA exits.
+#pragma once
+#include "aux_kernels.cuh"
+#include "gemm_skinny.cuh"
+#include "gemv_stream.cuh"
+
+namespace qg {
+
+constexpr int kTcItemBytes = QG_TC_ITEM_BYTES;  // 4608
+constexpr int kTcCodeBytes = 4096;
+constexpr int kTcPlanes = 8;
+constexpr int kTcConvWarps = 8;
+constexpr int kTcWarpProd = 0, kTcWarpMma = 1, kTcWarpConv0 = 2;
+constexpr int kTcConvThreads = 32 * kTcConvWarps;
+constexpr int kTcThreads = 32 * (2 + kTcConvWarps);  // 320
+constexpr int kTcMaxRing = 16;
+constexpr int kTcSfaSlots = 8;
+constexpr int kTcMaxTiles = 8192;  // 128-row tiles a handle keeps counters for (N <= 1,048,576)
+
+struct TcParams {
+    const uint8_t* payload;  // items: (tile * kt_total + kt) * 4608
+    const uint16_t* x;       // bf16 activations, first element of the K window
+    void* y;                 // [B][N]
+    float* ws;               // partial slots: (2 * cta + which) of [8][128] fp32
+    int32_t* counters;       // [tile][4], zero between launches
+    int32_t* status;
+    int64_t spin_limit;
+    float tensor_scale;
+    int32_t N;               // rows of the matrix
+    int32_t K;               // valid activation elements in the window
+    int32_t tiles;           // ceil(N / 128)
+    int32_t kt_total;        // items per row tile in the blob
+    int32_t kt0, kt_len;     // the window of items this launch covers
+    int32_t x_stride;        // elements between activation rows
+    int32_t B, y_dtype, debug;
+    int32_t npad;            // MMA N extent: 8 * B rounded up to 16
+    int32_t ring, stage_items;
+    int32_t x_slots;         // item slots of digit planes in shared memory
+};
+
+struct TcSmem {
+    static constexpr int kBarFull = 0;      // kTcMaxRing
+    static constexpr int kBarEmpty = 128;   // kTcMaxRing
+    static constexpr int kBarDFull = 256;   // 2
+    static constexpr int kBarDFree = 272;   // 2
+    static constexpr int kBarXReady = 288;
+    static constexpr int kBarDrain = 296;
+    static constexpr int kTmemPtr = 304;
+    static constexpr int kAbort = 308;
+    static constexpr int kIssued = 312;
+    static constexpr int kConsumed = 316;
+    static constexpr int kRowMax = 320;     // 8 words
+    static constexpr int kSfb = 1024;       // 512 bytes: block scales of the digit planes
+    static constexpr int kX = 1536;         // x_slots * npad * 32
+    __host__ __device__ static constexpr int x_bytes(int x_slots, int npad) { return x_slots * npad * 32; }
+    __host__ __device__ static constexpr int ring_off(int x_slots, int npad) {
+        return (kX + x_bytes(x_slots, npad) + 127) / 128 * 128;
+    }
+    __host__ __device__ static constexpr int total(int x_slots, int npad, int ring, int stage_items) {
+        return ring_off(x_slots, npad) + ring * stage_items * kTcItemBytes;
+    }
+    __host__ __device__ static int tmem_columns(int npad) {
+        int n = 32;
+        while (n < 2 * npad + 4 + 4 * kTcSfaSlots) n <<= 1;
+        return n;
+    }
+};
+
+// ---- tcgen05 wrappers for the block-scaled kind ---------------------------------------------------
+// 32 rows x 16 bytes of shared memory -> 32 lanes x 4 columns of tensor memory, replicated into all
+// four lane quarters: the scale factors of 128 rows x 4 blocks, row r at lane r % 32, column r / 32.
+__device__ __forceinline__ void tc_cp_sf(uint32_t taddr, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+// D[tmem] (+)= (A[smem] * SFA[tmem]) * (B[smem] * SFB[tmem]), E2M1 operands, E4M3 scales per 16 K
+__device__ __forceinline__ void tc_mma_nvf4(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                            uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %6, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n}" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(tmem_sfa), "r"(tmem_sfb), "r"(accumulate)
+        : "memory");
+}
+
+// ---- activation digit planes ------------------------------------------------------------------------
+// Exponent E such that max * 2^-E lies in [2^15, 2^16), from the largest |bf16| bit pattern.
+__device__ __forceinline__ int tc_row_exponent(uint32_t m) {
+    if (m == 0) return 0;
+    const int ef = int(m >> 7);
+    const int E = (ef == 0 ? -126 : ef - 127) - 15;
+    return E < -100 ? -100 : (E > 112 ? 112 : E);
+}
+// 16-bit magnitude -> its eight base-4 digits, one per nibble
+__device__ __forceinline__ uint32_t tc_spread(uint32_t n) {
+    n = (n | (n << 8)) & 0x00FF00FFu;
+    n = (n | (n << 4)) & 0x0F0F0F0Fu;
+    n = (n | (n << 2)) & 0x33333333u;
+    return n;
+}
+__device__ __forceinline__ uint32_t tc_digits(uint32_t bf, float sf) {
+    const uint32_t n = min(__float2uint_rn(__uint_as_float((bf & 0x7FFFu) << 16) * sf), 65535u);
+    return tc_spread(n) | (0u - ((bf >> 15) & 1u)) & 0x88888888u;
+}
+// Eight consecutive bf16 elements -> out[j] = the eight E2M1 codes of plane j (element i in nibble i).
+__device__ __forceinline__ void tc_digits8(uint4 v, float sf, uint32_t (&out)[8]) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t a[4], b[4];  // byte q of a[p]: plane 2q of elements (2p, 2p+1); b[p]: plane 2q+1
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+        const uint32_t s0 = tc_digits(w[p] & 0xFFFFu, sf), s1 = tc_digits(w[p] >> 16, sf);
+        a[p] = (s0 & 0x0F0F0F0Fu) | ((s1 & 0x0F0F0F0Fu) << 4);
+        b[p] = ((s0 >> 4) & 0x0F0F0F0Fu) | (s1 & 0xF0F0F0F0u);
+    }
+    uint32_t t0 = __byte_perm(a[0], a[1], 0x5140), t1 = __byte_perm(a[2], a[3], 0x5140);
+    uint32_t t2 = __byte_perm(a[0], a[1], 0x7362), t3 = __byte_perm(a[2], a[3], 0x7362);
+    out[0] = __byte_perm(t0, t1, 0x5410), out[2] = __byte_perm(t0, t1, 0x7632);
+    out[4] = __byte_perm(t2, t3, 0x5410), out[6] = __byte_perm(t2, t3, 0x7632);
+    t0 = __byte_perm(b[0], b[1], 0x5140), t1 = __byte_perm(b[2], b[3], 0x5140);
+    t2 = __byte_perm(b[0], b[1], 0x7362), t3 = __byte_perm(b[2], b[3], 0x7362);
+    out[1] = __byte_perm(t0, t1, 0x5410), out[3] = __byte_perm(t0, t1, 0x7632);
+    out[5] = __byte_perm(t2, t3, 0x5410), out[7] = __byte_perm(t2, t3, 0x7632);
+}
+
+// Stages of a CTA's range: up to `S` consecutive items of one row tile, never across a tile boundary.
+struct TcStage {
+    int32_t tile, u, cnt;
+    bool seg_first, seg_last;
+};
+struct TcStageWalker {
+    int32_t pos, begin, end, kt_len, S;
+    __device__ __forceinline__ void init(int32_t total, int32_t kt_len_, int32_t S_, int cta, int grid) {
+        kt_len = kt_len_, S = S_;
+        begin = pos = int32_t((int64_t(cta) * total) / grid);
+        end = int32_t((int64_t(cta + 1) * total) / grid);
+    }
+    __device__ __forceinline__ bool next(TcStage& st) {
+        if (pos >= end) return false;
+        st.tile = pos / kt_len;
+        st.u = pos - st.tile * kt_len;
+        const int32_t seg_end = min(end, (st.tile + 1) * kt_len);
+        st.cnt = min(S, seg_end - pos);
+        st.seg_first = pos == begin || st.u == 0;
+        st.seg_last = pos + st.cnt == seg_end;
+        pos += st.cnt;
+        return true;
+    }
+};
+
+__global__ void __launch_bounds__(kTcThreads, 2) gemv_tc_kernel(const TcParams P) {
+    extern __shared__ __align__(128) unsigned char tc_smem[];
+    const uint32_t sbase = smem_u32(tc_smem);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int grid = gridDim.x, cta = blockIdx.x;
+    const int kt_len = P.kt_len, npad = P.npad, R = P.ring, S = P.stage_items;
+    const int32_t total = P.tiles * kt_len;
+    const int32_t r_begin = int32_t((int64_t(cta) * total) / grid);
+    const int32_t r_end = int32_t((int64_t(cta + 1) * total) / grid);
+    // digit planes: slot of item u (window-relative) = (u - xs0) mod kt_len
+    const int32_t n_items = r_end - r_begin;
+    const int32_t xs0 = n_items >= kt_len ? 0 : r_begin % kt_len;
+    const int32_t n_slots = n_items >= kt_len ? kt_len : n_items;
+    const uint32_t xslot_bytes = uint32_t(npad) * 32u;
+    const uint32_t xbase = sbase + TcSmem::kX;
+    const uint32_t stage_bytes = uint32_t(S) * kTcItemBytes;
+    const uint32_t ring0 = sbase + uint32_t(TcSmem::ring_off(P.x_slots, npad));
+    const uint32_t ncols = uint32_t(TcSmem::tmem_columns(npad));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tc_smem + TcSmem::kAbort);
+    volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(tc_smem + TcSmem::kTmemPtr);
+    volatile int* n_issued = reinterpret_cast<volatile int*>(tc_smem + TcSmem::kIssued);
+    volatile int* n_consumed = reinterpret_cast<volatile int*>(tc_smem + TcSmem::kConsumed);
+    unsigned int* rowmax = reinterpret_cast<unsigned int*>(tc_smem + TcSmem::kRowMax);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kTcMaxRing; ++s) {
+            mbar_init(sbase + TcSmem::kBarFull + 8 * s, 1);
+            mbar_init(sbase + TcSmem::kBarEmpty + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(sbase + TcSmem::kBarDFull + 8 * b, 1);
+            mbar_init(sbase + TcSmem::kBarDFree + 8 * b, 4);
+        }
+        mbar_init(sbase + TcSmem::kBarXReady, 1);
+        mbar_init(sbase + TcSmem::kBarDrain, 1);
+        *abort_flag = 0;
+        *n_issued = 0;
+        *n_consumed = 0;
+        for (int b = 0; b < 8; ++b) reinterpret_cast<volatile unsigned int*>(rowmax)[b] = 0u;
+        mbar_fence_init();
+    }
+    if (warp == kTcWarpMma) {
+        __syncwarp();
+        tmem_alloc(sbase + TcSmem::kTmemPtr, ncols);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_ptr;
+    pdl_launch_dependents();
+    // tensor-memory columns: two accumulators, the planes' block scales, a ring of weight block scales
+    const uint32_t tmem_sfb = tmem_base + 2u * uint32_t(npad);
+    const uint32_t tmem_sfa0 = tmem_sfb + 4u;
+
+    if (warp == kTcWarpProd) {
+        // ================= packed-weight producer (weights never depend on the preceding kernel) =================
+        if (lane == 0) {
+            const uint64_t pol = policy_evict_first();
+            const bool drop = (P.debug & 2) != 0;  // host-set fault injection: never issue a copy
+            TcStageWalker wk;
+            wk.init(total, kt_len, S, cta, grid);
+            TcStage st;
+            int s = 0, issued = 0;
+            uint32_t use = 0;
+            while (wk.next(st)) {
+                if (use > 0 && !mbar_wait_probe(sbase + TcSmem::kBarEmpty + 8 * s, (use - 1) & 1, P.spin_limit)) {
+                    report(P.status, QGEMV_ERR_TIMEOUT, 61, st.tile);
+                    *abort_flag = 1;
+                    break;
+                }
+                if (*abort_flag) break;
+                const uint32_t bytes = uint32_t(st.cnt) * kTcItemBytes;
+                const uint8_t* src = P.payload + (uint64_t(st.tile) * P.kt_total + uint64_t(P.kt0 + st.u)) * kTcItemBytes;
+                if (!drop) {
+                    const uint32_t bar = sbase + TcSmem::kBarFull + 8 * s;
+                    mbar_arrive_expect_tx(bar, bytes);
+                    bulk_g2s(ring0 + s * stage_bytes, src, bytes, bar, pol);
+                    ++issued;
+                }
+                if (++s == R) s = 0, ++use;
+            }
+            *n_issued = issued;
+        }
+    } else if (warp == kTcWarpMma) {
+        // ================= MMA issuer: one elected lane =================
+        if (elect_one()) {
+            // E2M1 x E2M1, E4M3 scales, K-major operands, M = 128, N = npad
+            const uint32_t idesc = (1u << 7) | (1u << 10) | (uint32_t(npad >> 3) << 17) | (uint32_t(128 >> 4) << 24);
+            bool ok = mbar_wait(sbase + TcSmem::kBarXReady, 0, P.spin_limit);
+            if (!ok) {
+                report(P.status, QGEMV_ERR_TIMEOUT, 62, 0);
+                *abort_flag = 1;
+            }
+            int consumed = 0;
+            if (ok) {
+                tc_fence_after();
+                tc_cp_sf(tmem_sfb, smem_desc(sbase + TcSmem::kSfb, 0, 128));
+                TcStageWalker wk;
+                wk.init(total, kt_len, S, cta, grid);
+                TcStage st;
+                int s = 0;
+                uint32_t use = 0, nseg = 0, acc = 0, n_mma = 0;
+                uint32_t tmem_d = tmem_base;
+                while (ok && wk.next(st)) {
+                    if (st.seg_first) {
+                        // the accumulator is free once the epilogue of the segment before last has read it
+                        if (nseg >= 2 &&
+                            !mbar_wait_probe(sbase + TcSmem::kBarDFree + 8 * (nseg & 1), ((nseg >> 1) - 1) & 1, P.spin_limit)) {
+                            report(P.status, QGEMV_ERR_TIMEOUT, 63, int(nseg));
+                            *abort_flag = 1;
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
+                        tmem_d = tmem_base + (nseg & 1) * uint32_t(npad);
+                        acc = 0;  // the segment's first MMA overwrites D
+                    }
+                    if (!mbar_wait_probe(sbase + TcSmem::kBarFull + 8 * s, use & 1, P.spin_limit)) {
+                        report(P.status, QGEMV_ERR_TIMEOUT, 64, st.tile);
+                        *abort_flag = 1;
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t item0 = ring0 + s * stage_bytes;
+                    int32_t slot = st.u - xs0;
+                    if (slot < 0) slot += kt_len;
+                    for (int i = 0; i < st.cnt; ++i) {
+                        const uint32_t item = item0 + uint32_t(i) * kTcItemBytes;
+                        const uint32_t sfa = tmem_sfa0 + 4u * (n_mma % kTcSfaSlots);
+                        tc_cp_sf(sfa, smem_desc(item + kTcCodeBytes, 0, 128));
+                        tc_mma_nvf4(tmem_d, smem_desc(item, 128, 256), smem_desc(xbase + uint32_t(slot) * xslot_bytes, 128, 256),
+                                    idesc, sfa, tmem_sfb, acc);
+                        acc = 1;
+                        ++n_mma;
+                        if (++slot == kt_len) slot = 0;
+                    }
+                    tc_commit(sbase + TcSmem::kBarEmpty + 8 * s);  // the stage is reusable once these retire
+                    ++consumed;
+                    if (++s == R) s = 0, ++use;
+                    if (st.seg_last) {
+                        tc_commit(sbase + TcSmem::kBarDFull + 8 * (nseg & 1));
+                        ++nseg;
+                    }
+                }
+            }
+            *n_consumed = consumed;
+        }
+        __syncwarp();
+    } else {
+        // ================= activation digit planes, then the epilogues =================
+        const int ct = threadIdx.x - 32 * kTcWarpConv0;  // 0..255
+        const int Bl = P.B;
+        pdl_wait();  // activations come from the preceding kernel; y, workspace and counters may still be in use by it
+        // ---- row maxima over the whole window (every CTA computes the same scale) ----
+        for (int b = 0; b < Bl; ++b) {
+            const uint16_t* xr = P.x + int64_t(b) * P.x_stride;
+            uint32_t m = 0;
+            for (int k = ct * 8; k < P.K; k += kTcConvThreads * 8) {
+                const uint4 v = __ldcg(reinterpret_cast<const uint4*>(xr + k));
+                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int z = 0; z < 4; ++z) {
+                    m = max(m, w[z] & 0x7FFFu);
+                    m = max(m, (w[z] >> 16) & 0x7FFFu);
+                }
+            }
+            m = __reduce_max_sync(0xFFFFFFFFu, m);
+            if (lane == 0 && m != 0) atomicMax(rowmax + b, m);
+        }
+        // block scales of the planes: column n = 8 b + j carries 2^(2j - 6) in all four K blocks
+        if (ct < 128) {
+            const int n = ct, j = n & 7;
+            const uint32_t byte = n < 8 * Bl ? uint32_t(2 * j + 1) << 3 : 0u;
+            *reinterpret_cast<volatile uint32_t*>(tc_smem + TcSmem::kSfb + (n & 31) * 16 + (n >> 5) * 4) = byte * 0x01010101u;
+        }
+        named_bar_sync(1, kTcConvThreads);
+        // ---- digit planes of the items this CTA multiplies: work unit = (slot, row, 32-element half) ----
+        const int n_work = n_slots * Bl * 2;
+        for (int wu = ct; wu < n_work; wu += kTcConvThreads) {
+            const int c = wu & 1;
+            const int sb = wu >> 1;
+            const int slot = sb / Bl, b = sb - slot * Bl;
+            int32_t u = slot + xs0;
+            if (u >= kt_len) u -= kt_len;
+            const int k0 = u * 64 + c * 32;
+            const float sf = pow2i(-tc_row_exponent(rowmax[b]));
+            const uint16_t* src = P.x + int64_t(b) * P.x_stride + k0;
+            uint32_t pl[4][8];
+#pragma unroll
+            for (int o = 0; o < 4; ++o) {
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (k0 + 8 * o + 8 <= P.K) v = __ldcg(reinterpret_cast<const uint4*>(src + 8 * o));
+                tc_digits8(v, sf, pl[o]);
+            }
+            const uint32_t dst = xbase + uint32_t(slot) * xslot_bytes + uint32_t(b) * 256u + uint32_t(c) * 128u;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) sts128(dst + j * 16, make_uint4(pl[0][j], pl[1][j], pl[2][j], pl[3][j]));
+        }
+        fence_proxy_async_smem();  // the planes are read by the tensor core (async proxy)
+        named_bar_sync(1, kTcConvThreads);
+        if (ct == 0) mbar_arrive(sbase + TcSmem::kBarXReady);
+
+        // ---- epilogues: group g takes the segments with nseg % 2 == g; this warp owns lane quarter q ----
+        const int g = (warp - kTcWarpConv0) >> 2, q = warp & 3;
+        const uint32_t lane_base = uint32_t(32 * q) << 16;
+        const int row = 32 * q + lane;
+        GsWalker wk;
+        wk.init(total, kt_len, cta, grid);
+        GsSeg sg;
+        uint32_t nseg = 0;
+        float scale[8];
+#pragma unroll
+        for (int b = 0; b < 8; ++b) scale[b] = b < Bl ? P.tensor_scale * pow2i(tc_row_exponent(rowmax[b]) + 7) : 0.f;
+        while (wk.next(sg)) {
+            if (int(nseg & 1) != g) {
+                ++nseg;
+                continue;
+            }
+            if (!__all_sync(0xFFFFFFFFu, mbar_wait_probe(sbase + TcSmem::kBarDFull + 8 * g, (nseg >> 1) & 1, P.spin_limit))) {
+                if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 65, int(nseg));
+                *abort_flag = 1;
+                break;
+            }
+            tc_fence_after();
+            float val[8];
+#pragma unroll
+            for (int b = 0; b < 8; ++b) {
+                val[b] = 0.f;
+                if (b < Bl) {
+                    uint32_t r[8];
+                    tmem_ld8(tmem_base + lane_base + uint32_t(g * npad + 8 * b), r);
+                    float a = __uint_as_float(r[0]);
+#pragma unroll
+                    for (int j = 1; j < 8; ++j) a += __uint_as_float(r[j]);
+                    val[b] = a * scale[b];
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(sbase + TcSmem::kBarDFree + 8 * g);  // the accumulator may be overwritten
+            const int n = sg.tile * 128 + row;
+            auto store_row = [&](const float (&v)[8]) {
+                if (n < P.N) {
+#pragma unroll
+                    for (int b = 0; b < 8; ++b) {
+                        if (b < Bl) {
+                            const int64_t idx = int64_t(b) * P.N + n;
+                            if (P.y_dtype == QGEMV_OUT_F32) {
+                                static_cast<float*>(P.y)[idx] = v[b];
+                            } else {
+                                static_cast<__nv_bfloat16*>(P.y)[idx] = __float2bfloat16_rn(v[b]);
+                            }
+                        }
+                    }
+                }
+            };
+            if (sg.u0 == 0 && sg.u1 == kt_len) {
+                store_row(val);
+            } else {
+                // partial: park the fp32 sums; the last contributor of (tile, lane quarter) adds all
+                // parts in CTA order
+                float* slot = P.ws + size_t(gs_slot(cta, sg.tile, kt_len, total, grid)) * 1024;
+#pragma unroll
+                for (int b = 0; b < 8; ++b)
+                    if (b < Bl) __stcg(slot + b * 128 + row, val[b]);
+                __threadfence();
+                __syncwarp();
+                const int32_t c_lo = int32_t(cta_of(int64_t(sg.tile) * kt_len, total, grid));
+                const int32_t c_hi = int32_t(cta_of(int64_t(sg.tile + 1) * kt_len - 1, total, grid));
+                int old = 0;
+                if (lane == 0) old = atomicAdd(P.counters + sg.tile * 4 + q, 1);
+                old = __shfl_sync(0xFFFFFFFFu, old, 0);
+                if (old == c_hi - c_lo) {
+                    __threadfence();
+                    float v[8];
+                    for (int32_t cc = c_lo; cc <= c_hi; ++cc) {
+                        const float* sl = P.ws + size_t(gs_slot(cc, sg.tile, kt_len, total, grid)) * 1024;
+#pragma unroll
+                        for (int b = 0; b < 8; ++b) {
+                            if (b < Bl) {
+                                const float qv = __ldcg(sl + b * 128 + row);
+                                v[b] = cc == c_lo ? qv : v[b] + qv;
+                            }
+                        }
+                    }
+                    store_row(v);
+                    __syncwarp();
+                    if (lane == 0) P.counters[sg.tile * 4 + q] = 0;
+                }
+            }
+            ++nseg;
+        }
+    }
+    // ---- release tensor memory (always), after every role is done with it ----
+    tc_fence_before();
+    __syncthreads();
+    if (warp == kTcWarpMma) {
+        __syncwarp();
+        if (*abort_flag) {
+            // let whatever MMAs were issued retire before the columns are handed back (bounded)
+            if (lane == 0) {
+                tc_commit(sbase + TcSmem::kBarDrain);
+                (void)mbar_wait_probe(sbase + TcSmem::kBarDrain, 0, int64_t(1) << 16);
+            }
+            __syncwarp();
+        }
+        tc_fence_after();
+        tmem_dealloc(tmem_base, ncols);
+    } else if (threadIdx.x == 0 && *abort_flag) {
+        // never leave with copies in flight: wait (bounded) for every copy that nothing consumed
+        const int issued = *n_issued;
+        for (int i = *n_consumed; i < issued; ++i)
+            (void)mbar_wait(sbase + TcSmem::kBarFull + 8 * (i % R), uint32_t(i / R) & 1u, int64_t(1) << 20);
+    }
+}
+
+// Parity hook for the tensor-core layout: one thread per (row, 16-element block), the conversion
+// instructions of the CUDA-core kernels (cvt.e2m1x2, cvt.e4m3x2, one f16x2 multiply: exact), then
+// fp32 times the tensor scale.
+__global__ void dequant_tc_kernel(const uint8_t* payload, float tensor_scale, int32_t N, int32_t K, int32_t kt_total,
+                                  float* out) {
+    const int64_t id = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    const int64_t blocks_per_row = K / 16;
+    const int64_t n = id / blocks_per_row;
+    if (n >= N) return;
+    const int kbg = int(id - n * blocks_per_row);  // block index along K
+    const int tile = int(n >> 7), row = int(n & 127), kt = kbg >> 2, kb = kbg & 3;
+    const uint8_t* item = payload + (uint64_t(tile) * kt_total + kt) * kTcItemBytes;
+    int hi;
+    const uint2 cw = *reinterpret_cast<const uint2*>(item + qg_tc_code_offset(row, kb * 16, &hi));
+    const uint32_t sbyte = item[qg_tc_scale_offset(row, kb)];
+    uint32_t s2, unused;
+    cvt_e4m3x4(sbyte | (sbyte << 8), s2, unused);  // (scale, scale) as f16x2
+    const uint32_t w[2] = {cw.x, cw.y};
+#pragma unroll
+    for (int z = 0; z < 2; ++z) {
+        uint32_t a[4];
+        cvt_e2m1x8(w[z], a[0], a[1], a[2], a[3]);  // byte i -> elements 2i (low half), 2i+1 (high half)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t pr = hmul2(a[i], s2);
+            const int64_t k = int64_t(kbg) * 16 + 8 * z + 2 * i;
+            out[n * K + k] = __fmul_rn(h_lo(pr), tensor_scale);
+            out[n * K + k + 1] = __fmul_rn(h_hi(pr), tensor_scale);
+        }
+    }
+}
+
+}  // namespace qg

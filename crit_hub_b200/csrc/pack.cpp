@@ -21,7 +21,7 @@ struct Dims {
 };
 
 bool make_dims(int fmt, int64_t N, int64_t K, const qgemv_shard* sh, Dims* d) {
-    if (fmt != QGEMV_FMT_NVFP4 && fmt != QGEMV_FMT_FP8) return false;
+    if (fmt != QGEMV_FMT_NVFP4 && fmt != QGEMV_FMT_FP8 && fmt != QGEMV_FMT_NVFP4_TC) return false;
     if (N <= 0 || K <= 0 || (K % 16) != 0) return false;
     d->n0 = 0, d->n1 = N, d->k0 = 0, d->k1 = K;
     if (sh) {
@@ -33,8 +33,9 @@ bool make_dims(int fmt, int64_t N, int64_t K, const qgemv_shard* sh, Dims* d) {
     d->n = d->n1 - d->n0;
     d->k = d->k1 - d->k0;
     d->panels = (d->n + QG_PANEL_ROWS - 1) / QG_PANEL_ROWS;
+    if (fmt == QGEMV_FMT_NVFP4_TC) d->panels = (d->n + QG_TC_TILE_ROWS - 1) / QG_TC_TILE_ROWS * 8;  // whole 128-row tiles
     d->units = (d->k + QG_UNIT_K - 1) / QG_UNIT_K;
-    d->unit_bytes = fmt == QGEMV_FMT_NVFP4 ? QG_NVFP4_UNIT_BYTES : QG_FP8_UNIT_BYTES;
+    d->unit_bytes = fmt == QGEMV_FMT_FP8 ? QG_FP8_UNIT_BYTES : QG_NVFP4_UNIT_BYTES;
     d->aux_bytes = 0;
     if (fmt == QGEMV_FMT_FP8) d->aux_bytes = (uint64_t(d->panels) * 16 * 4 + 255) / 256 * 256;
     d->payload_bytes = uint64_t(d->panels) * uint64_t(d->units) * d->unit_bytes;
@@ -59,10 +60,11 @@ const qg_blob_header* check_header(const void* blob, size_t bytes) {
     const qg_blob_header* hd = static_cast<const qg_blob_header*>(blob);
     if (hd->magic != QG_BLOB_MAGIC || hd->version != QG_BLOB_VERSION) return nullptr;
     if (hd->header_bytes != QG_HEADER_BYTES) return nullptr;
-    if (hd->fmt != QGEMV_FMT_NVFP4 && hd->fmt != QGEMV_FMT_FP8) return nullptr;
-    if (hd->N <= 0 || hd->K <= 0) return nullptr;
-    if (hd->n_panels != (hd->N + 15) / 16 || hd->units_per_panel != (hd->K + 63) / 64) return nullptr;
-    const uint32_t ub = hd->fmt == QGEMV_FMT_NVFP4 ? QG_NVFP4_UNIT_BYTES : QG_FP8_UNIT_BYTES;
+    if (hd->fmt != QGEMV_FMT_NVFP4 && hd->fmt != QGEMV_FMT_FP8 && hd->fmt != QGEMV_FMT_NVFP4_TC) return nullptr;
+    if (hd->N <= 0 || hd->K <= 0 || hd->K % 16 != 0) return nullptr;
+    const int64_t want_panels = hd->fmt == QGEMV_FMT_NVFP4_TC ? (hd->N + 127) / 128 * 8 : (hd->N + 15) / 16;
+    if (hd->n_panels != want_panels || hd->units_per_panel != (hd->K + 63) / 64) return nullptr;
+    const uint32_t ub = hd->fmt == QGEMV_FMT_FP8 ? QG_FP8_UNIT_BYTES : QG_NVFP4_UNIT_BYTES;
     if (hd->unit_bytes != ub) return nullptr;
     if (hd->payload_bytes != uint64_t(hd->n_panels) * uint64_t(hd->units_per_panel) * ub) return nullptr;
     if (uint64_t(bytes) != QG_HEADER_BYTES + hd->aux_bytes + hd->payload_bytes) return nullptr;
@@ -96,7 +98,7 @@ int qgemv_pack_host(int fmt, const void* codes_v, const void* scales_v, float te
     hd.n_panels = d.panels;
     hd.units_per_panel = d.units;
     hd.unit_bytes = d.unit_bytes;
-    hd.tensor_scale = fmt == QGEMV_FMT_NVFP4 ? tensor_scale : 1.0f;
+    hd.tensor_scale = fmt == QGEMV_FMT_FP8 ? 1.0f : tensor_scale;
     hd.aux_bytes = d.aux_bytes;
     hd.payload_bytes = d.payload_bytes;
 
@@ -110,8 +112,33 @@ int qgemv_pack_host(int fmt, const void* codes_v, const void* scales_v, float te
         std::memcpy(aux, cs + d.n0, size_t(d.n) * 4);
     }
 
+    if (fmt == QGEMV_FMT_NVFP4_TC) {
+        const uint8_t* sc = static_cast<const uint8_t*>(scales_v);
+        const int64_t tiles = d.panels / 8;
 #pragma omp parallel for schedule(static)
-    for (int64_t p = 0; p < d.panels; ++p) {
+        for (int64_t q = 0; q < tiles; ++q) {
+            for (int64_t kt = 0; kt < d.units; ++kt) {
+                uint8_t* item = payload + (uint64_t(q) * d.units + kt) * QG_TC_ITEM_BYTES;
+                std::memset(item, 0, QG_TC_ITEM_BYTES);
+                for (int row = 0; row < QG_TC_TILE_ROWS; ++row) {
+                    const int64_t n = q * QG_TC_TILE_ROWS + row;
+                    if (n >= d.n) break;
+                    const int64_t gn = d.n0 + n;
+                    for (int kb = 0; kb < 4; ++kb) {
+                        const int64_t kk = kt * 64 + kb * 16;  // window-relative k of the block
+                        if (kk >= d.k) break;
+                        const int64_t gk = d.k0 + kk;
+                        int hi;
+                        // 16 codes = 8 bytes, already in the item's nibble order (low nibble = even k)
+                        std::memcpy(item + qg_tc_code_offset(row, kb * 16, &hi), codes + gn * (K / 2) + gk / 2, 8);
+                        item[qg_tc_scale_offset(row, kb)] = sc[gn * (K / 16) + gk / 16];
+                    }
+                }
+            }
+        }
+    }
+#pragma omp parallel for schedule(static)
+    for (int64_t p = 0; p < (fmt == QGEMV_FMT_NVFP4_TC ? 0 : d.panels); ++p) {
         for (int64_t u = 0; u < d.units; ++u) {
             uint8_t* unit = payload + (uint64_t(p) * d.units + u) * d.unit_bytes;
             std::memset(unit, 0, d.unit_bytes);
@@ -179,6 +206,21 @@ int qgemv_unpack_host(const void* blob, size_t bytes, void* codes_out, void* sca
         std::memcpy(scales_out, aux, size_t(N) * 4);
     } else {
         std::memset(codes, 0, size_t(N) * size_t(K / 2));
+    }
+    if (hd->fmt == QGEMV_FMT_NVFP4_TC) {
+#pragma omp parallel for schedule(static)
+        for (int64_t n = 0; n < N; ++n) {
+            const int64_t q = n / QG_TC_TILE_ROWS;
+            const int row = int(n % QG_TC_TILE_ROWS);
+            for (int64_t kk = 0; kk < K; kk += 16) {
+                const uint8_t* item = payload + (uint64_t(q) * units + kk / 64) * QG_TC_ITEM_BYTES;
+                const int kb = int((kk % 64) / 16);
+                int hi;
+                std::memcpy(codes + n * (K / 2) + kk / 2, item + qg_tc_code_offset(row, kb * 16, &hi), 8);
+                static_cast<uint8_t*>(scales_out)[n * (K / 16) + kk / 16] = item[qg_tc_scale_offset(row, kb)];
+            }
+        }
+        return QGEMV_OK;
     }
 #pragma omp parallel for schedule(static)
     for (int64_t n = 0; n < N; ++n) {

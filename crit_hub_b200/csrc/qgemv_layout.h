@@ -28,6 +28,20 @@
 // FP8 unit (1024 bytes):
 //   half hf = T >> 1 at hf*512; lane l: 16 bytes at hf*512 + l*16; tile T & 1 at +8*(T & 1);
 //   16-bit slot jb = rowhi + 2*r at +2*jb; low byte = block 2*pr (h = 0), high byte = h = 1.
+//
+// Tensor-core layout (QGEMV_FMT_NVFP4_TC): the same NVFP4 values in the order the block-scaled
+// tcgen05.mma (kind::mxf4nvf4, one E4M3 scale per 16 K elements) consumes without any conversion.
+// The matrix is cut into row TILES of 128 rows and ITEMS of 64 K elements; the blob stores items
+// tile-major:
+//     payload offset of (tile q, item kt) = (q * items_per_tile + kt) * 4608
+// ITEM (4608 bytes):
+//   [0, 4096)     E2M1 codes as the MMA's K-major, no-swizzle A operand: core matrices of 8 rows x
+//                 16 bytes (32 codes, low nibble = even k); row r, element k at
+//                 (r / 8) * 256 + (k / 32) * 128 + (r % 8) * 16 + (k % 32) / 2.
+//   [4096, 4608)  E4M3 block scales in the order tcgen05.cp.32x128b.warpx4 copies into tensor
+//                 memory: row r, block kb at (r % 32) * 16 + (r / 32) * 4 + kb.
+// In the blob header such a matrix reports n_panels = 8 * tiles and unit_bytes = 576 (an item is
+// eight panels' worth of units), so payload_bytes = n_panels * units_per_panel * unit_bytes holds.
 #ifndef QGEMV_LAYOUT_H_
 #define QGEMV_LAYOUT_H_
 
@@ -43,6 +57,8 @@
 #define QG_UNIT_K 64
 #define QG_NVFP4_UNIT_BYTES 576
 #define QG_FP8_UNIT_BYTES 1024
+#define QG_TC_TILE_ROWS 128
+#define QG_TC_ITEM_BYTES 4608
 #define QG_PHASE_UNITS 16 /* activation staging window: 1024 K elements */
 #define QG_BLOB_MAGIC 0x564D4751u /* "QGMV" */
 #define QG_BLOB_VERSION 3u
@@ -91,6 +107,15 @@ QG_HD uint32_t qg_xfrag_offset(int q, int kb, int e, int b) {
     const int pr = kb >> 1, h = kb & 1;
     const int t = e >> 2, sub = (e >> 1) & 1, r = e & 1;
     return (uint32_t)(q * 1024 + pr * 512 + (4 * b + t) * 16 + (2 * sub + r) * 4 + h * 2);
+}
+
+/* Tensor-core layout: byte offset inside an item of the code of (row 0..127, element k 0..63). */
+QG_HD uint32_t qg_tc_code_offset(int row, int k, int* nibble_hi) {
+    *nibble_hi = k & 1;
+    return (uint32_t)((row >> 3) * 256 + (k >> 5) * 128 + (row & 7) * 16 + ((k & 31) >> 1));
+}
+QG_HD uint32_t qg_tc_scale_offset(int row, int kb) {
+    return (uint32_t)(4096 + (row & 31) * 16 + (row >> 5) * 4 + kb);
 }
 
 #endif /* QGEMV_LAYOUT_H_ */

@@ -51,7 +51,16 @@ enum {
     QGEMV_FMT_NVFP4 = 1,
     /* E4M3 codes with one fp32 scale per output channel ("FP8 per-channel ... output head",
      *  tools/fixtures/engines/crit-labs/mtp4-nvfp4-mma/card.yaml:74). */
-    QGEMV_FMT_FP8 = 2
+    QGEMV_FMT_FP8 = 2,
+    /* The same values as QGEMV_FMT_NVFP4 (same canonical inputs, same dequantisation rule), stored
+     * in the tile order that the block-scaled tensor-core instruction consumes as it is (E2M1
+     * operands, one E4M3 scale per 16 K elements): the GEMV streams such a weight without
+     * executing a single conversion instruction.  The engines' decode rows read "the stored NVFP4
+     * ... matrices" (engines/crit-labs/mtp5-nvfp4-drafts/card.yaml:77); this is the stored form for
+     * the B200's native FP4 path.  Served by qgemv_gemv / qgemv_gemv_prefetch (all batch sizes)
+     * and qgemv_dequant_f32; not by the MoE and skinny-GEMM entry points, which want
+     * QGEMV_FMT_NVFP4. */
+    QGEMV_FMT_NVFP4_TC = 3
 };
 
 enum { QGEMV_OUT_BF16 = 0, QGEMV_OUT_F32 = 1 };
@@ -76,6 +85,10 @@ typedef struct qgemv_config {
                               bit 9: schedule override for tests -- the streaming kernel always
                               splits K across CTAs (partial sums + fixed-order fix-up) */
     int64_t spin_limit;    /* poll budget of every in-kernel wait; 0 = default */
+    int32_t tc_stage_items; /* QGEMV_FMT_NVFP4_TC GEMV: 4608-byte items per bulk copy; 0 = default (4) */
+    int32_t tc_smem_kb;     /* ... shared memory per CTA the ring may grow to, in KiB; 0 = default
+                               (about half an SM, so that the next kernel's CTA is resident and
+                               prefetches its weights while this one streams) */
 } qgemv_config;
 
 /* Rows [n0,n1) and columns [k0,k1) of the canonical matrix: a tensor-parallel shard.

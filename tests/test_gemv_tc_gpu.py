@@ -1,0 +1,227 @@
+"""GPU parity tests of the tensor-core NVFP4 GEMV (QGEMV_FMT_NVFP4_TC): weights consumed as stored by
+the block-scaled tcgen05.mma, activations as eight E2M1 digit planes.  Every call goes through the
+C ABI and is compared with the CPU oracle on the same seeded inputs."""
+import numpy as np
+import pytest
+
+import gpu_util as U
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+# fp32 outputs against the fp64 oracle (relative L2).  The digit planes round an activation to
+# 2^-16 of its row's largest magnitude (exact within 2^-8 of it), which moves the result by a few
+# 1e-6 on N(0,1) rows; the bound is the one the CUDA-core path is held to.
+TOL_F32 = 5e-5
+TOL_BF16 = 2e-3  # the stated bound for bf16 outputs
+
+
+def _load(qg, h, codes, scales, ts):
+    return h.load(qg.pack(qg.FMT_NVFP4_TC, codes, scales, ts))
+
+
+def test_dequant_tc_exhaustive(qg, handle):
+    """All 16 codes x all 256 scale bytes laid out in the tensor-core order, read back bit-exact."""
+    N = 256
+    nib = np.tile(np.arange(16, dtype=np.uint8), (N, 1))
+    codes = (nib[:, 0::2] | (nib[:, 1::2] << 4)).astype(np.uint8)
+    scales = np.arange(256, dtype=np.uint8).reshape(N, 1)
+    for ts in (1.0, 0.3):
+        w = _load(qg, handle, codes, scales, ts)
+        U.assert_bits_equal(U.dequant(qg, handle, w), O.dequant_nvfp4(codes, scales, ts))
+        w.unload()
+
+
+@pytest.mark.parametrize("N,K", [(64, 256), (100, 448), (1024, 4096), (17, 1040), (300, 80)])
+def test_dequant_tc_random(qg, handle, N, K):
+    codes, scales, ts = O.make_nvfp4(N, K, seed=N + K, ts=0.8125)
+    w = _load(qg, handle, codes, scales, ts)
+    U.assert_bits_equal(U.dequant(qg, handle, w), O.dequant_nvfp4(codes, scales, ts))
+    w.unload()
+
+
+def test_tc_config0(qg, handle):
+    """BASELINE configs[0]: 4096 x 4096 NVFP4, batch 1, bf16 output, tensor scale 1."""
+    codes, scales, ts = O.make_nvfp4(4096, 4096, seed=1)
+    x = O.make_x(1, 4096, seed=1)
+    ref = O.gemv_nvfp4_f64(codes, scales, ts, x)
+    w = _load(qg, handle, codes, scales, ts)
+    y32 = U.run_gemv(qg, handle, w, x, out_f32=True)
+    y16 = U.run_gemv(qg, handle, w, x, out_f32=False)
+    U.status_ok(handle)
+    assert O.rel_l2(y32, ref) < TOL_F32
+    assert O.rel_l2(O.bf16_decode(y16), ref) < TOL_BF16
+    assert np.array_equal(y16, O.bf16_encode(y32))  # the bf16 output is the fp32 result rounded once
+    w.unload()
+
+
+@pytest.mark.parametrize("N,K", [(128, 64), (16, 64), (48, 1024), (100, 448), (33, 1104), (1000, 2112), (6144, 4096),
+                                 (4096, 14336), (272, 16), (130, 4096)])
+@pytest.mark.parametrize("B", [1, 2, 3, 8])
+def test_tc_gemv_shapes(qg, handle, N, K, B):
+    codes, scales, ts = O.make_nvfp4(N, K, seed=N * 3 + K, ts=1.25)
+    x = O.make_x(B, K, seed=B + K)
+    w = _load(qg, handle, codes, scales, ts)
+    y = U.run_gemv(qg, handle, w, x)
+    U.status_ok(handle)
+    assert not np.isnan(y).any()
+    ref = O.gemv_nvfp4_f64(codes, scales, ts, x)
+    for b in range(B):
+        assert O.rel_l2(y[b], ref[b]) < TOL_F32, (b, N, K, B)
+    w.unload()
+
+
+def test_tc_matches_cuda_core_path(qg, handle):
+    """The same canonical matrix through both stored forms gives the same result to rounding."""
+    N, K, B = 768, 2048, 4
+    codes, scales, ts = O.make_nvfp4(N, K, seed=77, ts=0.6)
+    x = O.make_x(B, K, seed=78)
+    w_tc = _load(qg, handle, codes, scales, ts)
+    w_cc = handle.load(qg.pack(qg.FMT_NVFP4, codes, scales, ts))
+    y_tc = U.run_gemv(qg, handle, w_tc, x)
+    y_cc = U.run_gemv(qg, handle, w_cc, x)
+    U.status_ok(handle)
+    assert O.rel_l2(y_tc, y_cc) < TOL_F32
+    w_tc.unload()
+    w_cc.unload()
+
+
+def test_tc_column_invariance_and_determinism(qg, handle):
+    """Row b of the result has the same bits whatever the batch is, and from run to run."""
+    N, K = 1024, 4096
+    codes, scales, ts = O.make_nvfp4(N, K, seed=11)
+    x = O.make_x(8, K, seed=12)
+    w = _load(qg, handle, codes, scales, ts)
+    y8 = U.run_gemv(qg, handle, w, x)
+    assert np.array_equal(U.bits(y8), U.bits(U.run_gemv(qg, handle, w, x)))
+    for B in (1, 2, 5):
+        yb = U.run_gemv(qg, handle, w, x[:B])
+        assert np.array_equal(U.bits(yb), U.bits(y8[:B]))
+    y1 = U.run_gemv(qg, handle, w, x[3:4])
+    assert np.array_equal(U.bits(y1[0]), U.bits(y8[3]))
+    U.status_ok(handle)
+    w.unload()
+
+
+@pytest.mark.parametrize("grid", [1, 3, 37, 148, 296])
+def test_tc_k_split_across_ctas(qg, grid):
+    """Different CTA counts move the K split; every split sums its parts in a fixed order."""
+    h = qg.QGemv(device=0, grid_override=grid, debug=True)
+    N, K = 300, 4288
+    codes, scales, ts = O.make_nvfp4(N, K, seed=grid)
+    x = O.make_x(4, K, seed=grid + 1)
+    w = _load(qg, h, codes, scales, ts)
+    ref = O.gemv_nvfp4_f64(codes, scales, ts, x)
+    y = U.run_gemv(qg, h, w, x, h=h)
+    U.status_ok(h)
+    assert O.rel_l2(y, ref) < TOL_F32
+    # the arrival counters are back to zero: a second launch gives the same bits
+    assert np.array_equal(U.bits(y), U.bits(U.run_gemv(qg, h, w, x, h=h)))
+    w.unload()
+    h.close()
+
+
+@pytest.mark.parametrize("stage_items,smem_kb", [(1, 0), (2, 64), (8, 227), (4, 227)])
+def test_tc_ring_shapes(qg, stage_items, smem_kb):
+    """Ring geometry is a tuning knob, never a result: same bits for every stage size and depth."""
+    N, K, B = 640, 4160, 2
+    codes, scales, ts = O.make_nvfp4(N, K, seed=5)
+    x = O.make_x(B, K, seed=6)
+    h0 = qg.QGemv(device=0)
+    w0 = _load(qg, h0, codes, scales, ts)
+    y0 = U.run_gemv(qg, h0, w0, x, h=h0)
+    h = qg.QGemv(device=0, tc_stage_items=stage_items, tc_smem_kb=smem_kb)
+    w = _load(qg, h, codes, scales, ts)
+    y = U.run_gemv(qg, h, w, x, h=h)
+    U.status_ok(h)
+    assert O.rel_l2(y, O.gemv_nvfp4_f64(codes, scales, ts, x)) < TOL_F32
+    assert np.array_equal(U.bits(y), U.bits(y0))
+    w.unload(), w0.unload()
+    h.close(), h0.close()
+
+
+@pytest.mark.parametrize("N,K,B", [(8192, 8192, 8), (4096, 14336, 8), (1024, 28672, 8), (57344, 8192, 5)])
+def test_tc_large_activations(qg, handle, N, K, B):
+    """Digit planes that need most of an SM's shared memory, or several launches over K chunks whose
+    fp32 results are added in chunk order; bf16 output is rounded once."""
+    codes, scales, ts = O.make_nvfp4(N, K, seed=N + K + B, ts=0.9)
+    x = O.make_x(B, K, seed=B * 7 + 1)
+    ref = O.gemv_nvfp4_f64(codes, scales, ts, x)
+    w = _load(qg, handle, codes, scales, ts)
+    y32 = U.run_gemv(qg, handle, w, x)
+    y16 = U.run_gemv(qg, handle, w, x, out_f32=False)
+    U.status_ok(handle)
+    assert O.rel_l2(y32, ref) < TOL_F32
+    assert np.array_equal(y16, O.bf16_encode(y32))
+    assert np.array_equal(U.bits(y32), U.bits(U.run_gemv(qg, handle, w, x)))
+    w.unload()
+
+
+def test_tc_activation_ranges(qg, handle):
+    """Huge, tiny, zero and mixed-magnitude rows.  Rows whose elements all lie within 2^-8 of the row
+    maximum are exact; an element far below its row's maximum is rounded to 2^-16 of that maximum,
+    so those rows are held to an absolute bound relative to the row maximum."""
+    N, K = 256, 2048
+    codes, scales, ts = O.make_nvfp4(N, K, seed=21)
+    rng = np.random.default_rng(22)
+    base = rng.standard_normal((6, K)).astype(np.float32)
+    base[0] *= 1e30
+    base[1] *= 1e-30
+    base[2] = 0.0
+    base[3, : K // 2] *= 1e4
+    base[3, K // 2:] *= 1e-4      # below 2^-16 of the row maximum: rounded away
+    base[4, 5] = 1e37
+    base[5] *= 70000.0
+    x = O.bf16_encode(base)
+    w = _load(qg, handle, codes, scales, ts)
+    y = U.run_gemv(qg, handle, w, x)
+    U.status_ok(handle)
+    ref = O.gemv_nvfp4_f64(codes, scales, ts, x)
+    assert np.isfinite(y).all()
+    for b in (0, 1, 5):
+        assert O.rel_l2(y[b], ref[b]) < TOL_F32, b
+    assert not y[2].any()
+    # rows 3 and 4: error bounded by 2^-17 of the row maximum per element, against the weights' L1 mass
+    W = np.abs(O.dequant_nvfp4(codes, scales, ts).astype(np.float64))
+    xm = np.abs(O.bf16_decode(x).astype(np.float64)).max(axis=1)
+    for b in (3, 4):
+        bound = W.sum(axis=1) * xm[b] * 2.0 ** -16
+        assert (np.abs(y[b] - ref[b]) <= bound + 1e-6 * np.abs(ref[b])).all(), b
+    w.unload()
+
+
+def test_tc_bounded_wait_reports_timeout(qg):
+    """Host-set injection: the producer issues no copy, the MMA issuer's wait on the first stage runs
+    out of its small poll budget, the kernel reports and returns, and the context stays usable."""
+    h = qg.QGemv(device=0, spin_limit=2000, inject_drop_copies=True)
+    codes, scales, ts = O.make_nvfp4(512, 4096, seed=5)
+    w = _load(qg, h, codes, scales, ts)
+    x = O.make_x(1, 4096, seed=5)
+    U.run_gemv(qg, h, w, x, h=h)
+    st = h.device_status()
+    assert st.code == qg.ERR_TIMEOUT and st.where in (61, 62, 63, 64, 65)
+    assert h.device_status().code == 0  # reading clears it
+    w.unload()
+    h.close()
+    h2 = qg.QGemv(device=0)
+    w2 = _load(qg, h2, codes, scales, ts)
+    y = U.run_gemv(qg, h2, w2, x, h=h2)
+    assert O.rel_l2(y, O.gemv_nvfp4_f64(codes, scales, ts, x)) < TOL_F32
+    w2.unload()
+    h2.close()
+
+
+def test_tc_refused_by_other_entry_points(qg, handle):
+    import torch
+    codes, scales, ts = O.make_nvfp4(128, 64, seed=1)
+    w = _load(qg, handle, codes, scales, ts)
+    x = torch.zeros(16 * 64, dtype=torch.bfloat16, device="cuda")
+    y = torch.zeros(16 * 128, dtype=torch.float32, device="cuda")
+    with pytest.raises(qg.QgemvError) as e:
+        handle.gemm_skinny(w, x.data_ptr(), 16, y.data_ptr(), qg.OUT_F32)
+    assert e.value.status == qg.ERR_UNSUPPORTED_SHAPE
+    w.unload()
+    blobs = np.stack([qg.pack(qg.FMT_NVFP4_TC, codes, scales, ts)] * 2)
+    with pytest.raises(qg.QgemvError) as e:
+        handle.load_stacked(blobs)
+    assert e.value.status == qg.ERR_UNSUPPORTED_SHAPE

@@ -94,3 +94,51 @@ def test_rejects(qg):
     bad[4] += 1                                                # version of a stale layout
     with pytest.raises(qg.QgemvError):
         qg.blob_info(bad)
+
+
+# ---- tensor-core layout (QGEMV_FMT_NVFP4_TC) ------------------------------------------------------
+@pytest.mark.parametrize("N,K", [(128, 64), (1, 16), (100, 448), (17, 1040), (256, 4096), (300, 80)])
+def test_tc_roundtrip(qg, N, K):
+    codes, scales, ts = O.make_nvfp4(N, K, seed=N * 7 + K, ts=0.625)
+    blob = qg.pack(qg.FMT_NVFP4_TC, codes, scales, ts)
+    assert blob.size == qg.packed_size(qg.FMT_NVFP4_TC, N, K)
+    assert blob.size == 256 + ((N + 127) // 128) * ((K + 63) // 64) * 4608
+    assert qg.blob_info(blob) == (qg.FMT_NVFP4_TC, N, K)
+    assert qg.blob_verify(blob) == 0
+    c2, s2, ts2 = qg.unpack(blob)
+    assert np.array_equal(c2, codes) and np.array_equal(s2, scales) and ts2 == np.float32(0.625)
+    bad = blob.copy()
+    bad[300] ^= 1
+    assert qg.blob_verify(bad) != 0
+
+
+def test_tc_item_order(qg):
+    """The item is the MMA operand itself: codes as 8-row x 16-byte core matrices (K-major, no
+    swizzle), scales in the 32-lane x 4-column order of the tensor-memory copy."""
+    N, K = 256, 192
+    codes, scales, ts = O.make_nvfp4(N, K, seed=9)
+    payload = qg.pack(qg.FMT_NVFP4_TC, codes, scales, ts)[256:]
+    items_per_tile = K // 64
+    for n in (0, 7, 8, 31, 32, 127, 128, 200, 255):
+        for k in (0, 1, 31, 32, 63, 64, 130, 191):
+            item = payload[((n // 128) * items_per_tile + k // 64) * 4608:][:4608]
+            r, kk = n % 128, k % 64
+            byte = item[(r // 8) * 256 + (kk // 32) * 128 + (r % 8) * 16 + (kk % 32) // 2]
+            code = (byte >> 4) if kk & 1 else (byte & 15)
+            want = codes[n, k // 2]
+            assert code == ((want >> 4) if k & 1 else (want & 15))
+            assert item[4096 + (r % 32) * 16 + (r // 32) * 4 + kk // 16] == scales[n, k // 16]
+
+
+def test_tc_shards(qg):
+    N, K = 384, 512
+    codes, scales, ts = O.make_nvfp4(N, K, seed=3)
+    for world in (2, 4):
+        for r in range(world):
+            sh = qg.Shard(r * N // world, (r + 1) * N // world, 0, K)
+            c, s, _ = qg.unpack(qg.pack(qg.FMT_NVFP4_TC, codes, scales, ts, shard=sh))
+            assert np.array_equal(c, codes[sh.n0:sh.n1]) and np.array_equal(s, scales[sh.n0:sh.n1])
+            sh = qg.Shard(0, N, r * K // world, (r + 1) * K // world)
+            c, s, _ = qg.unpack(qg.pack(qg.FMT_NVFP4_TC, codes, scales, ts, shard=sh))
+            assert np.array_equal(c, codes[:, sh.k0 // 2:sh.k1 // 2])
+            assert np.array_equal(s, scales[:, sh.k0 // 16:sh.k1 // 16])
