@@ -91,6 +91,7 @@ def _load() -> C.CDLL:
     L.qgemv_init.argtypes = [C.POINTER(_Config), C.POINTER(vp)]
     L.qgemv_destroy.argtypes = [vp]
     L.qgemv_sm_count.argtypes = [vp]
+    L.qgemv_set_trace.argtypes = [vp, vp]
     L.qgemv_packed_size.restype = sz
     L.qgemv_packed_size.argtypes = [i32, i64, i64, C.POINTER(Shard)]
     L.qgemv_pack_host.argtypes = [i32, vp, vp, C.c_float, i64, i64, C.POINTER(Shard), vp]
@@ -235,6 +236,10 @@ class QGemv:
     @property
     def sm_count(self) -> int:
         return int(_load().qgemv_sm_count(self._ptr))
+
+    def set_trace(self, dev_ptr: int | None) -> None:
+        """Phase timestamps of the tensor-core GEMV into a device buffer of 16 u64 per CTA (None: off)."""
+        _check(_load().qgemv_set_trace(self._ptr, dev_ptr), "set_trace")
 
     def load(self, blob: np.ndarray) -> Weight:
         fmt, N, K = blob_info(blob)

@@ -39,6 +39,7 @@ struct qgemv_handle {
     // tensor-core GEMV: partial slots (two per CTA, [8][128] fp32 each) and per-tile arrival counters
     float* tc_ws;
     int32_t* tc_counters;
+    unsigned long long* tc_trace;  // caller's device buffer for phase timestamps, or null
 };
 
 struct qgemv_weight {
@@ -188,7 +189,7 @@ bool tc_plan(const qgemv_handle* h, int64_t tiles, int64_t kt_len, int B, TcPlan
     pl->npad = (8 * B + 15) / 16 * 16;
     const int64_t per_cta = (total + pl->grid - 1) / pl->grid;
     pl->x_slots = int(std::min<int64_t>(kt_len, per_cta));
-    pl->stage_items = h->cfg.tc_stage_items > 0 ? std::min(h->cfg.tc_stage_items, 8) : 4;
+    pl->stage_items = h->cfg.tc_stage_items > 0 ? std::min(h->cfg.tc_stage_items, 8) : 2;
     const int stage_bytes = pl->stage_items * qg::kTcItemBytes;
     const int base = qg::TcSmem::ring_off(pl->x_slots, pl->npad);
     // Prefer a footprint of about half an SM: the CTA of the next kernel in the stream is then
@@ -197,6 +198,8 @@ bool tc_plan(const qgemv_handle* h, int64_t tiles, int64_t kt_len, int B, TcPlan
     int ring = (want_cap - base) / stage_bytes;
     if (ring < 4) ring = (qg::kGsSmemBudget - base) / stage_bytes;  // large activations: the whole SM
     if (ring > qg::kTcMaxRing) ring = qg::kTcMaxRing;
+    // every ring item owns a 4-column slot of block scales in tensor memory
+    ring = std::min(ring, qg::TcSmem::max_ring_items(pl->npad) / pl->stage_items);
     if (ring < 2) return false;
     pl->ring = ring;
     pl->smem = size_t(qg::TcSmem::total(pl->x_slots, pl->npad, ring, pl->stage_items));
@@ -245,6 +248,7 @@ int gemv_tc(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, int B, v
         P.ring = pl.ring;
         P.stage_items = pl.stage_items;
         P.x_slots = pl.x_slots;
+        P.trace = h->tc_trace;
         if (launch(h, qg::gemv_tc_kernel, dim3(unsigned(pl.grid)), dim3(qg::kTcThreads), pl.smem, stream, P) != cudaSuccess)
             return QGEMV_ERR_CUDA;
     }
@@ -300,7 +304,7 @@ int qgemv_init(const qgemv_config* cfg, qgemv_handle** out) {
     for (int i = 0; i < qg::kTpMaxWorld; ++i) h->tp_peer[i] = nullptr;
     h->gs_ws = nullptr, h->gs_ws_bytes = 0;
     h->chunk_ws = nullptr;
-    h->tc_ws = nullptr, h->tc_counters = nullptr;
+    h->tc_ws = nullptr, h->tc_counters = nullptr, h->tc_trace = nullptr;
     const size_t tc_ws_bytes = size_t(2) * size_t(std::max(h->sm_count, cfg->grid_override)) * 1024 * sizeof(float);
     if (cudaMalloc(&h->tc_ws, tc_ws_bytes) != cudaSuccess ||
         cudaMalloc(&h->tc_counters, size_t(qg::kTcMaxTiles) * 4 * sizeof(int32_t)) != cudaSuccess ||
@@ -357,6 +361,12 @@ int qgemv_destroy(qgemv_handle* h) {
 }
 
 int qgemv_sm_count(const qgemv_handle* h) { return h ? h->sm_count : QGEMV_ERR_INVALID_ARG; }
+
+int qgemv_set_trace(qgemv_handle* h, void* dev_buf) {
+    if (!h) return QGEMV_ERR_INVALID_ARG;
+    h->tc_trace = static_cast<unsigned long long*>(dev_buf);
+    return QGEMV_OK;
+}
 
 int qgemv_load_stacked(qgemv_handle* h, const void* host_blobs, size_t bytes_each, int n_stacked,
                        qgemv_weight** out) {

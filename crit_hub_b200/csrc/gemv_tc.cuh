@@ -13,14 +13,16 @@
 // by a single thread, accumulators in tensor memory.
 //
 // Activations are bf16 and must stay (nearly) exact, but the B operand of this MMA kind is E2M1
-// too.  Each activation row is therefore written as EIGHT E2M1 digit planes: the row is scaled by a
-// power of two so that its largest magnitude lies in [2^15, 2^16), rounded to a 16-bit integer
+// too.  Each activation row is therefore written as EIGHT E2M1 digit planes: the part of the row that
+// a CTA multiplies is scaled by a power of two so that its largest magnitude lies in [2^15, 2^16)
+// (the scale belongs to one accumulation, so every CTA may take it from its own K range; it depends
+// on the shape and the CTA count only, never on the batch), rounded to a 16-bit integer
 // magnitude n, and plane j holds the base-4 digit d_j = (n >> 2j) & 3 as the E2M1 code of d_j / 2
 // (codes 0..3 are 0, 0.5, 1, 1.5) with the element's sign; the plane's block scale is the constant
 // 2^(2j-6), a power of two that E4M3 holds exactly.  The eight planes of a row are eight columns of
 // the MMA's N extent; their accumulators are added in plane order in the epilogue and the power of
-// two is undone in fp32.  A row element is exact when it lies within 2^-8 of the row maximum
-// (bf16 has 8 significant bits) and otherwise rounded to 2^-16 of the row maximum.
+// two is undone in fp32.  An element is exact when it lies within 2^-8 of that maximum (bf16 has 8
+// significant bits) and otherwise rounded to 2^-16 of it.
 //
 // Work split: the linear space (row tile, item) is cut evenly over the CTAs; a CTA's range is a
 // sequence of segments, each a K range of one row tile.  A segment that covers its whole tile
@@ -49,7 +51,7 @@ constexpr int kTcWarpProd = 0, kTcWarpMma = 1, kTcWarpConv0 = 2;
 constexpr int kTcConvThreads = 32 * kTcConvWarps;
 constexpr int kTcThreads = 32 * (2 + kTcConvWarps);  // 320
 constexpr int kTcMaxRing = 16;
-constexpr int kTcSfaSlots = 8;
+constexpr int kTcTmemCols = 256;  // two such CTAs fit the SM's 512 columns
 constexpr int kTcMaxTiles = 8192;  // 128-row tiles a handle keeps counters for (N <= 1,048,576)
 
 struct TcParams {
@@ -71,6 +73,7 @@ struct TcParams {
     int32_t npad;            // MMA N extent: 8 * B rounded up to 16
     int32_t ring, stage_items;
     int32_t x_slots;         // item slots of digit planes in shared memory
+    unsigned long long* trace;  // optional: 16 globaltimer stamps per CTA (diagnostics), or null
 };
 
 struct TcSmem {
@@ -84,7 +87,8 @@ struct TcSmem {
     static constexpr int kAbort = 308;
     static constexpr int kIssued = 312;
     static constexpr int kConsumed = 316;
-    static constexpr int kRowMax = 320;     // 8 words
+    static constexpr int kRowMax = 320;     // 8 words: largest |bf16| pattern per activation row
+    static constexpr int kWarpMax = 384;    // kTcConvWarps x 8 words: the same per converting warp
     static constexpr int kSfb = 1024;       // 512 bytes: block scales of the digit planes
     static constexpr int kX = 1536;         // x_slots * npad * 32
     __host__ __device__ static constexpr int x_bytes(int x_slots, int npad) { return x_slots * npad * 32; }
@@ -94,11 +98,9 @@ struct TcSmem {
     __host__ __device__ static constexpr int total(int x_slots, int npad, int ring, int stage_items) {
         return ring_off(x_slots, npad) + ring * stage_items * kTcItemBytes;
     }
-    __host__ __device__ static int tmem_columns(int npad) {
-        int n = 32;
-        while (n < 2 * npad + 4 + 4 * kTcSfaSlots) n <<= 1;
-        return n;
-    }
+    // tensor memory: two accumulators of npad columns, 4 columns of plane scales, then one 4-column
+    // slot of weight block scales per ring item
+    __host__ __device__ static constexpr int max_ring_items(int npad) { return (kTcTmemCols - 2 * npad - 4) / 4; }
 };
 
 // ---- tcgen05 wrappers for the block-scaled kind ---------------------------------------------------
@@ -117,13 +119,19 @@ __device__ __forceinline__ void tc_mma_nvf4(uint32_t tmem_d, uint64_t desc_a, ui
         : "memory");
 }
 
+__device__ __forceinline__ int atom_add_acq_rel(int32_t* p, int v) {
+    int old;
+    asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+    return old;
+}
+
 // ---- activation digit planes ------------------------------------------------------------------------
 // Exponent E such that max * 2^-E lies in [2^15, 2^16), from the largest |bf16| bit pattern.
 __device__ __forceinline__ int tc_row_exponent(uint32_t m) {
     if (m == 0) return 0;
     const int ef = int(m >> 7);
     const int E = (ef == 0 ? -126 : ef - 127) - 15;
-    return E < -100 ? -100 : (E > 112 ? 112 : E);
+    return E < -126 ? -126 : (E > 112 ? 112 : E);  // 2^-E and 2^(E+7) both stay normal fp32 numbers
 }
 // 16-bit magnitude -> its eight base-4 digits, one per nibble
 __device__ __forceinline__ uint32_t tc_spread(uint32_t n) {
@@ -198,7 +206,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemv_tc_kernel(const TcParams P
     const uint32_t xbase = sbase + TcSmem::kX;
     const uint32_t stage_bytes = uint32_t(S) * kTcItemBytes;
     const uint32_t ring0 = sbase + uint32_t(TcSmem::ring_off(P.x_slots, npad));
-    const uint32_t ncols = uint32_t(TcSmem::tmem_columns(npad));
+    const uint32_t ncols = kTcTmemCols;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tc_smem + TcSmem::kAbort);
     volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(tc_smem + TcSmem::kTmemPtr);
     volatile int* n_issued = reinterpret_cast<volatile int*>(tc_smem + TcSmem::kIssued);
@@ -219,7 +227,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemv_tc_kernel(const TcParams P
         *abort_flag = 0;
         *n_issued = 0;
         *n_consumed = 0;
-        for (int b = 0; b < 8; ++b) reinterpret_cast<volatile unsigned int*>(rowmax)[b] = 0u;
+        for (int b = 0; b < 16 + 8 * kTcConvWarps; ++b) reinterpret_cast<volatile unsigned int*>(rowmax)[b] = 0u;
         mbar_fence_init();
     }
     if (warp == kTcWarpMma) {
@@ -231,6 +239,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemv_tc_kernel(const TcParams P
     tc_fence_after();
     const uint32_t tmem_base = *tmem_ptr;
     pdl_launch_dependents();
+    if (P.trace && threadIdx.x == 0) P.trace[cta * 16 + 0] = globaltimer_ns();
     // tensor-memory columns: two accumulators, the planes' block scales, a ring of weight block scales
     const uint32_t tmem_sfb = tmem_base + 2u * uint32_t(npad);
     const uint32_t tmem_sfa0 = tmem_sfb + 4u;
@@ -258,6 +267,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemv_tc_kernel(const TcParams P
                     const uint32_t bar = sbase + TcSmem::kBarFull + 8 * s;
                     mbar_arrive_expect_tx(bar, bytes);
                     bulk_g2s(ring0 + s * stage_bytes, src, bytes, bar, pol);
+                    if (P.trace && P.debug & 16 && issued < 64) P.trace[gridDim.x * 16 + cta * 256 + issued * 4 + 0] = clock64();
                     ++issued;
                 }
                 if (++s == R) s = 0, ++use;
@@ -266,123 +276,217 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemv_tc_kernel(const TcParams P
         }
     } else if (warp == kTcWarpMma) {
         // ================= MMA issuer: one elected lane =================
+        // Two cursors walk the CTA's stages.  The scale cursor copies a landed stage's block scales into
+        // tensor memory (one 4-column slot per ring item) -- that needs no activations, so the prefetched
+        // stages are done before the digit planes exist.  The MMA cursor follows once the planes are
+        // ready.  tcgen05.cp and tcgen05.mma of one thread execute in issue order, and a stage's slots
+        // are rewritten only after the stage was refilled, i.e. after its previous MMAs retired.
         if (elect_one()) {
             // E2M1 x E2M1, E4M3 scales, K-major operands, M = 128, N = npad
             const uint32_t idesc = (1u << 7) | (1u << 10) | (uint32_t(npad >> 3) << 17) | (uint32_t(128 >> 4) << 24);
-            bool ok = mbar_wait(sbase + TcSmem::kBarXReady, 0, P.spin_limit);
-            if (!ok) {
-                report(P.status, QGEMV_ERR_TIMEOUT, 62, 0);
-                *abort_flag = 1;
-            }
-            int consumed = 0;
-            if (ok) {
-                tc_fence_after();
-                tc_cp_sf(tmem_sfb, smem_desc(sbase + TcSmem::kSfb, 0, 128));
-                TcStageWalker wk;
-                wk.init(total, kt_len, S, cta, grid);
-                TcStage st;
-                int s = 0;
-                uint32_t use = 0, nseg = 0, acc = 0, n_mma = 0;
-                uint32_t tmem_d = tmem_base;
-                while (ok && wk.next(st)) {
-                    if (st.seg_first) {
+            // descriptors differ in their 14-bit address field only (shared memory is below 256 KB)
+            const uint64_t d_ab = smem_desc(0, 128, 256), d_sf = smem_desc(0, 0, 128);
+            const uint64_t d_x0 = d_ab | (xbase >> 4);
+            const uint32_t xslot16 = xslot_bytes >> 4;
+            TcStageWalker wk_c, wk_m;
+            wk_c.init(total, kt_len, S, cta, grid);
+            wk_m.init(total, kt_len, S, cta, grid);
+            TcStage st_c, st_m;
+            bool have_c = wk_c.next(st_c), have_m = wk_m.next(st_m);
+            int ci = 0, mi = 0;        // stages whose scales are copied / whose MMAs are issued
+            int sc = 0, sm = 0;        // their ring slots
+            uint32_t use_c = 0, nseg = 0, acc = 0;
+            uint32_t tmem_d = tmem_base;
+            bool x_ready = false, ok = true;
+            int64_t polls = 0;
+            const uint64_t t_begin = globaltimer_ns();
+            while (have_m) {
+                bool progress = false;
+                // ---- scale cursor: every landed stage, at most a ring ahead of the MMAs ----
+                while (have_c && ci < mi + R && mbar_test_wait(sbase + TcSmem::kBarFull + 8 * sc, use_c & 1)) {
+                    tc_fence_after();
+                    if (P.trace && ci == 0) P.trace[cta * 16 + 4] = globaltimer_ns();
+                    if (P.trace && P.debug & 16 && ci < 64) P.trace[gridDim.x * 16 + cta * 256 + ci * 4 + 1] = clock64();
+                    uint32_t sf16 = (ring0 + sc * stage_bytes + kTcCodeBytes) >> 4;
+                    uint32_t sfa = tmem_sfa0 + 4u * uint32_t(sc * S);
+                    for (int i = 0; i < st_c.cnt; ++i) {
+                        tc_cp_sf(sfa, d_sf | sf16);
+                        sf16 += kTcItemBytes >> 4;
+                        sfa += 4u;
+                    }
+                    ++ci;
+                    if (++sc == R) sc = 0, ++use_c;
+                    have_c = wk_c.next(st_c);
+                    progress = true;
+                }
+                if (!x_ready && mbar_test_wait(sbase + TcSmem::kBarXReady, 0)) {
+                    tc_fence_after();
+                    if (P.trace) P.trace[cta * 16 + 3] = globaltimer_ns();
+                    tc_cp_sf(tmem_sfb, d_sf | ((sbase + TcSmem::kSfb) >> 4));
+                    x_ready = true;
+                    progress = true;
+                }
+                // ---- MMA cursor ----
+                if (x_ready && mi < ci) {
+                    bool d_ok = true;
+                    if (st_m.seg_first) {
                         // the accumulator is free once the epilogue of the segment before last has read it
                         if (nseg >= 2 &&
                             !mbar_wait_probe(sbase + TcSmem::kBarDFree + 8 * (nseg & 1), ((nseg >> 1) - 1) & 1, P.spin_limit)) {
                             report(P.status, QGEMV_ERR_TIMEOUT, 63, int(nseg));
                             *abort_flag = 1;
                             ok = false;
-                            break;
+                            d_ok = false;
                         }
                         tc_fence_after();
                         tmem_d = tmem_base + (nseg & 1) * uint32_t(npad);
                         acc = 0;  // the segment's first MMA overwrites D
                     }
-                    if (!mbar_wait_probe(sbase + TcSmem::kBarFull + 8 * s, use & 1, P.spin_limit)) {
-                        report(P.status, QGEMV_ERR_TIMEOUT, 64, st.tile);
+                    if (!d_ok) break;
+                    uint32_t item16 = (ring0 + sm * stage_bytes) >> 4;
+                    uint32_t sfa = tmem_sfa0 + 4u * uint32_t(sm * S);
+                    int32_t slot = st_m.u - xs0;
+                    if (slot < 0) slot += kt_len;
+                    uint64_t d_x = d_x0 + uint64_t(uint32_t(slot) * xslot16);
+                    for (int i = 0; i < st_m.cnt; ++i) {
+                        tc_mma_nvf4(tmem_d, d_ab | item16, d_x, idesc, sfa, tmem_sfb, acc);
+                        acc = 1;
+                        item16 += kTcItemBytes >> 4;
+                        sfa += 4u;
+                        d_x += xslot16;
+                    }
+                    tc_commit(sbase + TcSmem::kBarEmpty + 8 * sm);  // the stage is reusable once these retire
+                    if (P.trace && P.debug & 16 && mi < 64) P.trace[gridDim.x * 16 + cta * 256 + mi * 4 + 2] = clock64();
+                    if (st_m.seg_last) {
+                        tc_commit(sbase + TcSmem::kBarDFull + 8 * (nseg & 1));
+                        ++nseg;
+                    }
+                    ++mi;
+                    if (++sm == R) sm = 0;
+                    have_m = wk_m.next(st_m);
+                    progress = true;
+                }
+                if (progress) continue;
+                // Nothing to do.  Block (bounded, the hardware suspends the thread) on the one event that
+                // can come next: with every ring slot's scales copied only the digit planes are missing,
+                // and with the planes ready only the next stage; otherwise both can happen, so probe.
+                if (x_ready) {
+                    if (!mbar_wait(sbase + TcSmem::kBarFull + 8 * sc, use_c & 1, P.spin_limit)) {
+                        report(P.status, QGEMV_ERR_TIMEOUT, 64, mi);
                         *abort_flag = 1;
                         ok = false;
                         break;
                     }
-                    tc_fence_after();
-                    const uint32_t item0 = ring0 + s * stage_bytes;
-                    int32_t slot = st.u - xs0;
-                    if (slot < 0) slot += kt_len;
-                    for (int i = 0; i < st.cnt; ++i) {
-                        const uint32_t item = item0 + uint32_t(i) * kTcItemBytes;
-                        const uint32_t sfa = tmem_sfa0 + 4u * (n_mma % kTcSfaSlots);
-                        tc_cp_sf(sfa, smem_desc(item + kTcCodeBytes, 0, 128));
-                        tc_mma_nvf4(tmem_d, smem_desc(item, 128, 256), smem_desc(xbase + uint32_t(slot) * xslot_bytes, 128, 256),
-                                    idesc, sfa, tmem_sfb, acc);
-                        acc = 1;
-                        ++n_mma;
-                        if (++slot == kt_len) slot = 0;
+                } else if (!have_c || ci >= mi + R) {
+                    if (!mbar_wait(sbase + TcSmem::kBarXReady, 0, P.spin_limit)) {
+                        report(P.status, QGEMV_ERR_TIMEOUT, 62, mi);
+                        *abort_flag = 1;
+                        ok = false;
+                        break;
                     }
-                    tc_commit(sbase + TcSmem::kBarEmpty + 8 * s);  // the stage is reusable once these retire
-                    ++consumed;
-                    if (++s == R) s = 0, ++use;
-                    if (st.seg_last) {
-                        tc_commit(sbase + TcSmem::kBarDFull + 8 * (nseg & 1));
-                        ++nseg;
-                    }
+                } else if (++polls > P.spin_limit || ((polls & 4095) == 4095 && globaltimer_ns() - t_begin > 4000000000ull)) {
+                    report(P.status, QGEMV_ERR_TIMEOUT, 62, mi);
+                    *abort_flag = 1;
+                    ok = false;
+                    break;
                 }
             }
-            *n_consumed = consumed;
+            if (P.trace) P.trace[cta * 16 + 5] = globaltimer_ns();
+            (void)ok;
+            *n_consumed = mi;
         }
         __syncwarp();
     } else {
         // ================= activation digit planes, then the epilogues =================
         const int ct = threadIdx.x - 32 * kTcWarpConv0;  // 0..255
         const int Bl = P.B;
-        pdl_wait();  // activations come from the preceding kernel; y, workspace and counters may still be in use by it
-        // ---- row maxima over the whole window (every CTA computes the same scale) ----
-        for (int b = 0; b < Bl; ++b) {
-            const uint16_t* xr = P.x + int64_t(b) * P.x_stride;
-            uint32_t m = 0;
-            for (int k = ct * 8; k < P.K; k += kTcConvThreads * 8) {
-                const uint4 v = __ldcg(reinterpret_cast<const uint4*>(xr + k));
-                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                for (int z = 0; z < 4; ++z) {
-                    m = max(m, w[z] & 0x7FFFu);
-                    m = max(m, (w[z] >> 16) & 0x7FFFu);
-                }
-            }
-            m = __reduce_max_sync(0xFFFFFFFFu, m);
-            if (lane == 0 && m != 0) atomicMax(rowmax + b, m);
-        }
+        unsigned int* wmax = reinterpret_cast<unsigned int*>(tc_smem + TcSmem::kWarpMax) + (warp - kTcWarpConv0) * 8;
         // block scales of the planes: column n = 8 b + j carries 2^(2j - 6) in all four K blocks
         if (ct < 128) {
             const int n = ct, j = n & 7;
             const uint32_t byte = n < 8 * Bl ? uint32_t(2 * j + 1) << 3 : 0u;
             *reinterpret_cast<volatile uint32_t*>(tc_smem + TcSmem::kSfb + (n & 31) * 16 + (n >> 5) * 4) = byte * 0x01010101u;
         }
-        named_bar_sync(1, kTcConvThreads);
-        // ---- digit planes of the items this CTA multiplies: work unit = (slot, row, 32-element half) ----
-        const int n_work = n_slots * Bl * 2;
-        for (int wu = ct; wu < n_work; wu += kTcConvThreads) {
-            const int c = wu & 1;
-            const int sb = wu >> 1;
-            const int slot = sb / Bl, b = sb - slot * Bl;
+        pdl_wait();  // activations come from the preceding kernel; y, workspace and counters may still be in use by it
+        if (P.trace && ct == 0) P.trace[cta * 16 + 1] = globaltimer_ns();
+        // ---- digit planes of the items this CTA multiplies.  Work unit w = ((row b) * n_slots + slot) * 8
+        // + octet: eight consecutive elements, one 16-byte load.  One pass loads and finds the row maxima
+        // (the first four units of a thread stay in registers), a second one converts. ----
+        const int n_work = n_slots * Bl * 8;
+        constexpr int kKeep = 4;
+        auto unit_src = [&](int wu, int& b, uint32_t& dst) -> uint4 {
+            const int o = wu & 7, sb = wu >> 3;
+            b = sb / n_slots;
+            const int slot = sb - b * n_slots;
             int32_t u = slot + xs0;
             if (u >= kt_len) u -= kt_len;
-            const int k0 = u * 64 + c * 32;
-            const float sf = pow2i(-tc_row_exponent(rowmax[b]));
-            const uint16_t* src = P.x + int64_t(b) * P.x_stride + k0;
-            uint32_t pl[4][8];
+            const int k0 = u * 64 + o * 8;
+            // plane j of (slot, row b): 16 bytes per 32 elements at + (o / 4) * 128 + j * 16; this octet's word (o % 4)
+            dst = xbase + uint32_t(slot) * xslot_bytes + uint32_t(b) * 256u + uint32_t(o >> 2) * 128u + uint32_t(o & 3) * 4u;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (k0 + 8 <= P.K) v = *reinterpret_cast<const uint4*>(P.x + int64_t(b) * P.x_stride + k0);
+            return v;
+        };
+        auto unit_max = [&](const uint4& v) {
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+            uint32_t m = 0;
 #pragma unroll
-            for (int o = 0; o < 4; ++o) {
-                uint4 v = make_uint4(0, 0, 0, 0);
-                if (k0 + 8 * o + 8 <= P.K) v = __ldcg(reinterpret_cast<const uint4*>(src + 8 * o));
-                tc_digits8(v, sf, pl[o]);
+            for (int z = 0; z < 4; ++z) {
+                m = max(m, w[z] & 0x7FFFu);
+                m = max(m, (w[z] >> 16) & 0x7FFFu);
             }
-            const uint32_t dst = xbase + uint32_t(slot) * xslot_bytes + uint32_t(b) * 256u + uint32_t(c) * 128u;
+            return m;
+        };
+        auto row_max = [&](int b) {
+            const unsigned int* all = reinterpret_cast<const unsigned int*>(tc_smem + TcSmem::kWarpMax);
+            uint32_t m = 0;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) sts128(dst + j * 16, make_uint4(pl[0][j], pl[1][j], pl[2][j], pl[3][j]));
+            for (int w = 0; w < kTcConvWarps; ++w) m = max(m, all[w * 8 + b]);
+            return m;
+        };
+        auto store_unit = [&](int b, uint32_t dst, const uint4& v) {
+            const float sf = pow2i(-tc_row_exponent(row_max(b)));
+            uint32_t pl[8];
+            tc_digits8(v, sf, pl);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) asm volatile("st.shared.b32 [%0], %1;" ::"r"(dst + j * 16), "r"(pl[j]) : "memory");
+        };
+        uint4 keep[kKeep];
+        int kb[kKeep];
+        uint32_t kdst[kKeep];
+#pragma unroll
+        for (int i = 0; i < kKeep; ++i) {
+            const int wu = ct + i * kTcConvThreads;
+            kb[i] = 0, kdst[i] = 0;
+            keep[i] = make_uint4(0, 0, 0, 0);
+            if (wu < n_work) keep[i] = unit_src(wu, kb[i], kdst[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < kKeep; ++i) {
+            const uint32_t m = unit_max(keep[i]);
+            if (m) atomicMax(wmax + kb[i], m);
+        }
+        for (int wu = ct + kKeep * kTcConvThreads; wu < n_work; wu += kTcConvThreads) {
+            int b;
+            uint32_t dst;
+            const uint32_t m = unit_max(unit_src(wu, b, dst));
+            if (m) atomicMax(wmax + b, m);
+        }
+        named_bar_sync(1, kTcConvThreads);
+        if (ct < 8) rowmax[ct] = row_max(ct);
+#pragma unroll
+        for (int i = 0; i < kKeep; ++i)
+            if (ct + i * kTcConvThreads < n_work) store_unit(kb[i], kdst[i], keep[i]);
+        for (int wu = ct + kKeep * kTcConvThreads; wu < n_work; wu += kTcConvThreads) {
+            int b;
+            uint32_t dst;
+            const uint4 v = unit_src(wu, b, dst);
+            store_unit(b, dst, v);
         }
         fence_proxy_async_smem();  // the planes are read by the tensor core (async proxy)
         named_bar_sync(1, kTcConvThreads);
         if (ct == 0) mbar_arrive(sbase + TcSmem::kBarXReady);
+        if (P.trace && ct == 0) P.trace[cta * 16 + 2] = globaltimer_ns();
 
         // ---- epilogues: group g takes the segments with nseg % 2 == g; this warp owns lane quarter q ----
         const int g = (warp - kTcWarpConv0) >> 2, q = warp & 3;
@@ -400,12 +504,23 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemv_tc_kernel(const TcParams P
                 ++nseg;
                 continue;
             }
+            // a partial segment's bookkeeping does not need the accumulator: do it while the MMAs run
+            const bool whole = sg.u0 == 0 && sg.u1 == kt_len;
+            int32_t c_lo = 0, c_hi = 0, lo_slot = 0;
+            if (!whole) {
+                c_lo = int32_t(cta_of(int64_t(sg.tile) * kt_len, total, grid));
+                c_hi = int32_t(cta_of(int64_t(sg.tile + 1) * kt_len - 1, total, grid));
+                // every contributor after the first starts its range inside this tile: its part is in its
+                // slot 0; the first one's range may have started in an earlier tile
+                lo_slot = gs_slot(c_lo, sg.tile, kt_len, total, grid);
+            }
             if (!__all_sync(0xFFFFFFFFu, mbar_wait_probe(sbase + TcSmem::kBarDFull + 8 * g, (nseg >> 1) & 1, P.spin_limit))) {
                 if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 65, int(nseg));
                 *abort_flag = 1;
                 break;
             }
             tc_fence_after();
+            if (P.trace && lane == 0 && q == 0) P.trace[cta * 16 + 6] = globaltimer_ns();  // the last one stays
             float val[8];
 #pragma unroll
             for (int b = 0; b < 8; ++b) {
@@ -438,32 +553,44 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemv_tc_kernel(const TcParams P
                     }
                 }
             };
-            if (sg.u0 == 0 && sg.u1 == kt_len) {
+            if (whole) {
                 store_row(val);
             } else {
                 // partial: park the fp32 sums; the last contributor of (tile, lane quarter) adds all
-                // parts in CTA order
-                float* slot = P.ws + size_t(gs_slot(cta, sg.tile, kt_len, total, grid)) * 1024;
+                // parts in CTA order.  The arrival counter is bumped with release / acquire semantics
+                // by one lane after the warp has converged, which orders the whole warp's stores
+                // before it and the other warps' parts before the loads below.
+                const int32_t my_slot = cta == c_lo ? lo_slot : 2 * cta;
+                float* slot = P.ws + size_t(my_slot) * 1024 + row;
 #pragma unroll
                 for (int b = 0; b < 8; ++b)
-                    if (b < Bl) __stcg(slot + b * 128 + row, val[b]);
-                __threadfence();
+                    if (b < Bl) __stcg(slot + b * 128, val[b]);
                 __syncwarp();
-                const int32_t c_lo = int32_t(cta_of(int64_t(sg.tile) * kt_len, total, grid));
-                const int32_t c_hi = int32_t(cta_of(int64_t(sg.tile + 1) * kt_len - 1, total, grid));
                 int old = 0;
-                if (lane == 0) old = atomicAdd(P.counters + sg.tile * 4 + q, 1);
+                if (lane == 0) old = atom_add_acq_rel(P.counters + sg.tile * 4 + q, 1);
                 old = __shfl_sync(0xFFFFFFFFu, old, 0);
                 if (old == c_hi - c_lo) {
-                    __threadfence();
                     float v[8];
-                    for (int32_t cc = c_lo; cc <= c_hi; ++cc) {
-                        const float* sl = P.ws + size_t(gs_slot(cc, sg.tile, kt_len, total, grid)) * 1024;
+                    const float* p0 = P.ws + size_t(lo_slot) * 1024 + row;
 #pragma unroll
-                        for (int b = 0; b < 8; ++b) {
-                            if (b < Bl) {
-                                const float qv = __ldcg(sl + b * 128 + row);
-                                v[b] = cc == c_lo ? qv : v[b] + qv;
+                    for (int b = 0; b < 8; ++b)
+                        if (b < Bl) v[b] = __ldcg(p0 + b * 128);
+                    // four parts' loads in flight at a time; the additions stay in CTA order
+                    for (int32_t cc = c_lo + 1; cc <= c_hi; cc += 4) {
+                        float t[4][8];
+#pragma unroll
+                        for (int z = 0; z < 4; ++z) {
+                            const float* pz = P.ws + size_t(2 * min(cc + z, c_hi)) * 1024 + row;
+#pragma unroll
+                            for (int b = 0; b < 8; ++b)
+                                if (b < Bl) t[z][b] = __ldcg(pz + b * 128);
+                        }
+#pragma unroll
+                        for (int z = 0; z < 4; ++z) {
+                            if (cc + z <= c_hi) {
+#pragma unroll
+                                for (int b = 0; b < 8; ++b)
+                                    if (b < Bl) v[b] += t[z][b];
                             }
                         }
                     }
@@ -474,10 +601,12 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemv_tc_kernel(const TcParams P
             }
             ++nseg;
         }
+        if (P.trace && lane == 0) atomicMax(P.trace + cta * 16 + 8, globaltimer_ns());
     }
     // ---- release tensor memory (always), after every role is done with it ----
     tc_fence_before();
     __syncthreads();
+    if (P.trace && threadIdx.x == 0) P.trace[cta * 16 + 7] = globaltimer_ns();
     if (warp == kTcWarpMma) {
         __syncwarp();
         if (*abort_flag) {

@@ -49,7 +49,7 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
 }
 __device__ __forceinline__ uint64_t globaltimer_ns() {
     uint64_t t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)::"memory");  // ordered with barriers and stores
     return t;
 }
 // Bounded wait: gives up after `spin_limit` polls or two seconds, whichever comes first.  A warp

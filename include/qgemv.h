@@ -85,7 +85,7 @@ typedef struct qgemv_config {
                               bit 9: schedule override for tests -- the streaming kernel always
                               splits K across CTAs (partial sums + fixed-order fix-up) */
     int64_t spin_limit;    /* poll budget of every in-kernel wait; 0 = default */
-    int32_t tc_stage_items; /* QGEMV_FMT_NVFP4_TC GEMV: 4608-byte items per bulk copy; 0 = default (4) */
+    int32_t tc_stage_items; /* QGEMV_FMT_NVFP4_TC GEMV: 4608-byte items per bulk copy; 0 = default (2) */
     int32_t tc_smem_kb;     /* ... shared memory per CTA the ring may grow to, in KiB; 0 = default
                                (about half an SM, so that the next kernel's CTA is resident and
                                prefetches its weights while this one streams) */
@@ -269,6 +269,13 @@ int qgemv_dequant_f32(qgemv_handle* h, const qgemv_weight* w, int which, float* 
                       void* stream);
 
 /* ---- diagnostics ------------------------------------------------------------------------------ */
+/* Phase timestamps of the tensor-core GEMV (diagnostics; no counterpart in the registry).  `dev_buf`:
+ * device memory of 16 x 8 bytes per CTA (one CTA per SM unless grid_override says otherwise), or NULL
+ * to switch it off again.  Every later QGEMV_FMT_NVFP4_TC launch on the handle makes each CTA store
+ * %globaltimer (ns) at: [0] set-up done, [1] dependency wait over, [2] activation digit planes
+ * written, [3] MMA issuer released, [4] its first weight stage landed, [5] its last MMA issued,
+ * [6] last accumulator complete, [7] CTA done.  The caller zeroes and reads the buffer. */
+int qgemv_set_trace(qgemv_handle* h, void* dev_buf);
 /* Synchronises `stream`, reads and clears the device status word. */
 int qgemv_last_device_status(qgemv_handle* h, void* stream, qgemv_dev_status* out);
 
