@@ -511,7 +511,7 @@ def main():
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "lmhead", "moe"],
                     help="decode: the headline GEMV layer stack; prefill: the skinny GEMM over one 70B-shaped layer; "
                          "lmhead: the FP8 output head; moe: the grouped expert GEMV (--tokens 1/8/64)")
-    ap.add_argument("--layout", default="lane", choices=["tc", "lane"],
+    ap.add_argument("--layout", default="tc", choices=["tc", "lane"],
                     help="stored form of the NVFP4 weights: tc = tile order consumed as stored by the block-scaled "
                          "tensor-core GEMV; lane = lane-ordered units for the CUDA-core GEMV")
     ap.add_argument("--tokens", type=int, default=256, help="rows of the prefill workload (16..256, multiple of 16)")

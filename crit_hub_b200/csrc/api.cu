@@ -36,9 +36,8 @@ struct qgemv_handle {
     size_t gs_ws_bytes;
     // K-chunked GEMV: fp32 partial results [chunk][B][N], fixed size, allocated with the handle
     float* chunk_ws;
-    // tensor-core GEMV: partial slots (two per CTA, [8][128] fp32 each) and per-tile arrival counters
+    // tensor-core GEMV: split-K hand-over slots (two per CTA, [8][128] pairs {fp32, flag}), all zero between launches
     float* tc_ws;
-    int32_t* tc_counters;
     unsigned long long* tc_trace;  // caller's device buffer for phase timestamps, or null
 };
 
@@ -189,7 +188,8 @@ bool tc_plan(const qgemv_handle* h, int64_t tiles, int64_t kt_len, int B, TcPlan
     pl->npad = (8 * B + 15) / 16 * 16;
     const int64_t per_cta = (total + pl->grid - 1) / pl->grid;
     pl->x_slots = int(std::min<int64_t>(kt_len, per_cta));
-    pl->stage_items = h->cfg.tc_stage_items > 0 ? std::min(h->cfg.tc_stage_items, 8) : 2;
+    const int si = h->cfg.tc_stage_items;
+    pl->stage_items = si >= 8 ? 8 : (si >= 4 ? 4 : (si >= 2 ? 2 : (si == 1 ? 1 : 4)));  // 1, 2, 4 or 8; default 4
     const int stage_bytes = pl->stage_items * qg::kTcItemBytes;
     const int base = qg::TcSmem::ring_off(pl->x_slots, pl->npad);
     // Prefer a footprint of about half an SM: the CTA of the next kernel in the stream is then
@@ -230,7 +230,6 @@ int gemv_tc(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, int B, v
         P.x = static_cast<const uint16_t*>(x_bf16) + k0 * 64;
         P.y = n_chunks == 1 ? y : static_cast<void*>(h->chunk_ws + c * slice);
         P.ws = h->tc_ws;
-        P.counters = h->tc_counters;
         P.status = h->status_dev;
         P.spin_limit = default_spin(h);
         P.tensor_scale = w->host_tensor_scale[0];
@@ -249,8 +248,12 @@ int gemv_tc(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, int B, v
         P.stage_items = pl.stage_items;
         P.x_slots = pl.x_slots;
         P.trace = h->tc_trace;
-        if (launch(h, qg::gemv_tc_kernel, dim3(unsigned(pl.grid)), dim3(qg::kTcThreads), pl.smem, stream, P) != cudaSuccess)
-            return QGEMV_ERR_CUDA;
+        const dim3 g(unsigned(pl.grid)), blk(qg::kTcThreads);
+        const cudaError_t err = pl.stage_items == 1   ? launch(h, qg::gemv_tc_kernel<1>, g, blk, pl.smem, stream, P)
+                                : pl.stage_items == 2 ? launch(h, qg::gemv_tc_kernel<2>, g, blk, pl.smem, stream, P)
+                                : pl.stage_items == 4 ? launch(h, qg::gemv_tc_kernel<4>, g, blk, pl.smem, stream, P)
+                                                      : launch(h, qg::gemv_tc_kernel<8>, g, blk, pl.smem, stream, P);
+        if (err != cudaSuccess) return QGEMV_ERR_CUDA;
     }
     if (n_chunks > 1) {
         const cudaError_t err = launch(h, qg::chunk_sum_kernel, dim3(unsigned((slice + 255) / 256)), dim3(256), 0, stream,
@@ -304,11 +307,9 @@ int qgemv_init(const qgemv_config* cfg, qgemv_handle** out) {
     for (int i = 0; i < qg::kTpMaxWorld; ++i) h->tp_peer[i] = nullptr;
     h->gs_ws = nullptr, h->gs_ws_bytes = 0;
     h->chunk_ws = nullptr;
-    h->tc_ws = nullptr, h->tc_counters = nullptr, h->tc_trace = nullptr;
-    const size_t tc_ws_bytes = size_t(2) * size_t(std::max(h->sm_count, cfg->grid_override)) * 1024 * sizeof(float);
-    if (cudaMalloc(&h->tc_ws, tc_ws_bytes) != cudaSuccess ||
-        cudaMalloc(&h->tc_counters, size_t(qg::kTcMaxTiles) * 4 * sizeof(int32_t)) != cudaSuccess ||
-        cudaMemset(h->tc_counters, 0, size_t(qg::kTcMaxTiles) * 4 * sizeof(int32_t)) != cudaSuccess ||
+    h->tc_ws = nullptr, h->tc_trace = nullptr;
+    const size_t tc_ws_bytes = size_t(2) * size_t(std::max(h->sm_count, cfg->grid_override)) * 1024 * 8;
+    if (cudaMalloc(&h->tc_ws, tc_ws_bytes) != cudaSuccess || cudaMemset(h->tc_ws, 0, tc_ws_bytes) != cudaSuccess ||
         cudaMalloc(&h->chunk_ws, kChunkWsBytes) != cudaSuccess ||
         cudaMalloc(&h->status_dev, 4 * sizeof(int32_t)) != cudaSuccess ||
         cudaMemset(h->status_dev, 0, 4 * sizeof(int32_t)) != cudaSuccess) {
@@ -333,7 +334,10 @@ int qgemv_init(const qgemv_config* cfg, qgemv_handle** out) {
         cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_NVFP4, false, 1, true>, dyn, qg::SSmem::total<QGEMV_FMT_NVFP4>()) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8, true, 1, true>, dyn, qg::SSmem::total<QGEMV_FMT_FP8>()) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8, false, 1, true>, dyn, qg::SSmem::total<QGEMV_FMT_FP8>()) != cudaSuccess ||
-        cudaFuncSetAttribute(qg::gemv_tc_kernel, dyn, qg::kGsSmemBudget) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_tc_kernel<1>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_tc_kernel<2>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_tc_kernel<4>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_tc_kernel<8>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemm_skinny_kernel<QGEMV_FMT_NVFP4>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemm_skinny_kernel<QGEMV_FMT_FP8>, dyn, qg::kGsSmemBudget) != cudaSuccess) {
         g_last_cuda_error = cudaGetLastError();
@@ -354,7 +358,6 @@ int qgemv_destroy(qgemv_handle* h) {
     cudaFree(h->gs_ws);
     cudaFree(h->chunk_ws);
     cudaFree(h->tc_ws);
-    cudaFree(h->tc_counters);
     cudaFree(h->status_dev);
     delete h;
     return QGEMV_OK;
@@ -385,7 +388,7 @@ int qgemv_load_stacked(qgemv_handle* h, const void* host_blobs, size_t bytes_eac
     if (h0->N > INT32_MAX || h0->K > INT32_MAX || h0->n_panels * h0->units_per_panel > (int64_t(1) << 40))
         return QGEMV_ERR_UNSUPPORTED_SHAPE;
     if (h0->fmt == QGEMV_FMT_NVFP4_TC &&
-        (n_stacked != 1 || h0->n_panels / 8 > qg::kTcMaxTiles || h0->n_panels / 8 * h0->units_per_panel > INT32_MAX))
+        (n_stacked != 1 || h0->n_panels / 8 * h0->units_per_panel > INT32_MAX))
         return QGEMV_ERR_UNSUPPORTED_SHAPE;
     QG_CUDA(cudaSetDevice(h->cfg.device));
     qgemv_weight* w = new (std::nothrow) qgemv_weight;

@@ -26,9 +26,9 @@
 //
 // Work split: the linear space (row tile, item) is cut evenly over the CTAs; a CTA's range is a
 // sequence of segments, each a K range of one row tile.  A segment that covers its whole tile
-// stores y; otherwise the fp32 partial sums go to a workspace slot and the last contributor of the
-// tile (atomic counter) adds all parts in CTA order -- a deterministic split along K that depends
-// only on the shape and the CTA count.
+// stores y; otherwise the tile's first contributor collects the other CTAs' fp32 partial sums
+// (flagged 8-byte hand-over slots, bounded wait) and adds them in CTA order -- a deterministic
+// split along K that depends only on the shape and the CTA count.
 //
 // Warp roles (10 warps):
 //   0     one thread issues the bulk copies of packed items (ring of stages)
@@ -52,14 +52,12 @@ constexpr int kTcConvThreads = 32 * kTcConvWarps;
 constexpr int kTcThreads = 32 * (2 + kTcConvWarps);  // 320
 constexpr int kTcMaxRing = 16;
 constexpr int kTcTmemCols = 256;  // two such CTAs fit the SM's 512 columns
-constexpr int kTcMaxTiles = 8192;  // 128-row tiles a handle keeps counters for (N <= 1,048,576)
 
 struct TcParams {
     const uint8_t* payload;  // items: (tile * kt_total + kt) * 4608
     const uint16_t* x;       // bf16 activations, first element of the K window
     void* y;                 // [B][N]
-    float* ws;               // partial slots: (2 * cta + which) of [8][128] fp32
-    int32_t* counters;       // [tile][4], zero between launches
+    float* ws;               // hand-over slots: (2 * cta) of [8][128] pairs {fp32, flag}, all zero between launches
     int32_t* status;
     int64_t spin_limit;
     float tensor_scale;
@@ -109,6 +107,21 @@ struct TcSmem {
 __device__ __forceinline__ void tc_cp_sf(uint32_t taddr, uint64_t sdesc) {
     asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
 }
+// The same with the descriptor given as two 32-bit halves: the issuing thread's address arithmetic
+// stays 32-bit (only the low half, which holds the address field, changes from item to item).
+__device__ __forceinline__ void tc_cp_sf2(uint32_t taddr, uint32_t desc_lo, uint32_t desc_hi) {
+    asm volatile("{\n .reg .b64 d;\n mov.b64 d, {%1, %2};\n tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], d;\n}" ::"r"(taddr),
+                 "r"(desc_lo), "r"(desc_hi)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_mma_nvf4_2(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t ab_hi, uint32_t idesc,
+                                              uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n .reg .b64 da, db;\n setp.ne.b32 p, %7, 0;\n mov.b64 da, {%1, %3};\n mov.b64 db, {%2, %3};\n"
+        " tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], da, db, %4, [%5], [%6], p;\n}" ::"r"(tmem_d),
+        "r"(a_lo), "r"(b_lo), "r"(ab_hi), "r"(idesc), "r"(tmem_sfa), "r"(tmem_sfb), "r"(accumulate)
+        : "memory");
+}
 // D[tmem] (+)= (A[smem] * SFA[tmem]) * (B[smem] * SFB[tmem]), E2M1 operands, E4M3 scales per 16 K
 __device__ __forceinline__ void tc_mma_nvf4(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
                                             uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
@@ -119,10 +132,15 @@ __device__ __forceinline__ void tc_mma_nvf4(uint32_t tmem_d, uint64_t desc_a, ui
         : "memory");
 }
 
-__device__ __forceinline__ int atom_add_acq_rel(int32_t* p, int v) {
-    int old;
-    asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
-    return old;
+// Split-K hand-over: an aligned 8-byte element {fp32 value, flag 1} written and read as one access.
+__device__ __forceinline__ void st_flagged(unsigned long long* p, float v) {
+    const unsigned long long w = (1ull << 32) | __float_as_uint(v);
+    asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_flagged(const unsigned long long* p) {
+    unsigned long long w;
+    asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+    return w;
 }
 
 // ---- activation digit planes ------------------------------------------------------------------------
@@ -164,37 +182,63 @@ __device__ __forceinline__ void tc_digits8(uint4 v, float sf, uint32_t (&out)[8]
     out[5] = __byte_perm(t2, t3, 0x5410), out[7] = __byte_perm(t2, t3, 0x7632);
 }
 
-// Stages of a CTA's range: up to `S` consecutive items of one row tile, never across a tile boundary.
-struct TcStage {
-    int32_t tile, u, cnt;
-    bool seg_first, seg_last;
-};
-struct TcStageWalker {
-    int32_t pos, begin, end, kt_len, S;
-    __device__ __forceinline__ void init(int32_t total, int32_t kt_len_, int32_t S_, int cta, int grid) {
-        kt_len = kt_len_, S = S_;
-        begin = pos = int32_t((int64_t(cta) * total) / grid);
-        end = int32_t((int64_t(cta + 1) * total) / grid);
+// The tile's first contributor gathers the parts of CTAs c_lo + 1 .. c_hi, two activation rows at a
+// time with the loads of up to eight parts in flight together, re-polling -- bounded -- what is
+// missing, then adds them to `val` in CTA order and clears the slots it has read.
+__device__ __forceinline__ bool tc_collect(const TcParams& P, float (&val)[8], int Bl, int32_t c_lo, int32_t c_hi, int row,
+                                           volatile int* abort_flag) {
+    constexpr int KP = 8;
+    uint64_t t_wait = 0;  // read on the first miss only: %globaltimer is a slow register
+    unsigned long long* ws = reinterpret_cast<unsigned long long*>(P.ws) + row;
+#pragma unroll
+    for (int b0 = 0; b0 < 8; b0 += 2) {
+        if (b0 >= Bl) break;
+        const bool two = b0 + 1 < Bl;
+        for (int32_t cc = c_lo + 1; cc <= c_hi; cc += KP) {
+            uint32_t w0[KP], w1[KP];
+            uint32_t missing = (1u << min(KP, c_hi - cc + 1)) - 1u;
+            for (int64_t it = 0; missing != 0; ++it) {
+#pragma unroll
+                for (int z = 0; z < KP; ++z) {
+                    if (!(missing >> z & 1)) continue;
+                    const unsigned long long* pz = ws + size_t(2 * (cc + z)) * 1024 + b0 * 128;
+                    const unsigned long long e0 = ld_flagged(pz);
+                    const unsigned long long e1 = two ? ld_flagged(pz + 128) : (1ull << 32);
+                    w0[z] = uint32_t(e0), w1[z] = uint32_t(e1);
+                    if ((e0 >> 32) != 0 && (e1 >> 32) != 0) missing &= ~(1u << z);
+                }
+                if (missing != 0 && t_wait == 0) t_wait = globaltimer_ns();
+                if (missing != 0 && (it >= P.spin_limit || ((it & 63) == 63 && globaltimer_ns() - t_wait > 2000000000ull))) {
+                    report(P.status, QGEMV_ERR_TIMEOUT, 66, cc);
+                    *abort_flag = 1;
+                    return false;
+                }
+            }
+#pragma unroll
+            for (int z = 0; z < KP; ++z) {
+                if (cc + z <= c_hi) {
+                    unsigned long long* pz = ws + size_t(2 * (cc + z)) * 1024 + b0 * 128;
+                    val[b0] += __uint_as_float(w0[z]);
+                    pz[0] = 0ull;
+                    if (two) {
+                        val[b0 + 1] += __uint_as_float(w1[z]);
+                        pz[128] = 0ull;
+                    }
+                }
+            }
+        }
     }
-    __device__ __forceinline__ bool next(TcStage& st) {
-        if (pos >= end) return false;
-        st.tile = pos / kt_len;
-        st.u = pos - st.tile * kt_len;
-        const int32_t seg_end = min(end, (st.tile + 1) * kt_len);
-        st.cnt = min(S, seg_end - pos);
-        st.seg_first = pos == begin || st.u == 0;
-        st.seg_last = pos + st.cnt == seg_end;
-        pos += st.cnt;
-        return true;
-    }
-};
+    return true;
+}
 
+// S: items per ring stage (one bulk copy, one release); a stage never crosses a row-tile boundary.
+template <int S>
 __global__ void __launch_bounds__(kTcThreads, 2) gemv_tc_kernel(const TcParams P) {
     extern __shared__ __align__(128) unsigned char tc_smem[];
     const uint32_t sbase = smem_u32(tc_smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int grid = gridDim.x, cta = blockIdx.x;
-    const int kt_len = P.kt_len, npad = P.npad, R = P.ring, S = P.stage_items;
+    const int kt_len = P.kt_len, npad = P.npad, R = P.ring;
     const int32_t total = P.tiles * kt_len;
     const int32_t r_begin = int32_t((int64_t(cta) * total) / grid);
     const int32_t r_end = int32_t((int64_t(cta + 1) * total) / grid);
@@ -246,153 +290,160 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemv_tc_kernel(const TcParams P
 
     if (warp == kTcWarpProd) {
         // ================= packed-weight producer (weights never depend on the preceding kernel) =================
+        // One thread runs this loop, so its dependent-instruction count per stage bounds the stream:
+        // the divisions and 64-bit address arithmetic happen once per segment, a stage is a handful
+        // of adds around the wait and the copy.
         if (lane == 0) {
             const uint64_t pol = policy_evict_first();
             const bool drop = (P.debug & 2) != 0;  // host-set fault injection: never issue a copy
-            TcStageWalker wk;
-            wk.init(total, kt_len, S, cta, grid);
-            TcStage st;
+            GsWalker wk;
+            wk.init(total, kt_len, cta, grid);
+            GsSeg sg;
             int s = 0, issued = 0;
             uint32_t use = 0;
-            while (wk.next(st)) {
-                if (use > 0 && !mbar_wait_probe(sbase + TcSmem::kBarEmpty + 8 * s, (use - 1) & 1, P.spin_limit)) {
-                    report(P.status, QGEMV_ERR_TIMEOUT, 61, st.tile);
-                    *abort_flag = 1;
-                    break;
+            bool ok = true;
+            while (ok && wk.next(sg)) {
+                const uint8_t* src = P.payload + (uint64_t(sg.tile) * P.kt_total + uint64_t(P.kt0 + sg.u0)) * kTcItemBytes;
+                for (int32_t left = sg.u1 - sg.u0; left > 0; left -= S) {
+                    if (use > 0 && !mbar_wait_probe(sbase + TcSmem::kBarEmpty + 8 * s, (use - 1) & 1, P.spin_limit)) {
+                        report(P.status, QGEMV_ERR_TIMEOUT, 61, sg.tile);
+                        *abort_flag = 1;
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t bytes = uint32_t(min(S, left)) * kTcItemBytes;
+                    if (!drop) {
+                        const uint32_t bar = sbase + TcSmem::kBarFull + 8 * s;
+                        mbar_arrive_expect_tx(bar, bytes);
+                        bulk_g2s(ring0 + s * stage_bytes, src, bytes, bar, pol);
+                        ++issued;
+                    }
+                    src += bytes;
+                    if (++s == R) s = 0, ++use;
                 }
                 if (*abort_flag) break;
-                const uint32_t bytes = uint32_t(st.cnt) * kTcItemBytes;
-                const uint8_t* src = P.payload + (uint64_t(st.tile) * P.kt_total + uint64_t(P.kt0 + st.u)) * kTcItemBytes;
-                if (!drop) {
-                    const uint32_t bar = sbase + TcSmem::kBarFull + 8 * s;
-                    mbar_arrive_expect_tx(bar, bytes);
-                    bulk_g2s(ring0 + s * stage_bytes, src, bytes, bar, pol);
-                    if (P.trace && P.debug & 16 && issued < 64) P.trace[gridDim.x * 16 + cta * 256 + issued * 4 + 0] = clock64();
-                    ++issued;
-                }
-                if (++s == R) s = 0, ++use;
             }
             *n_issued = issued;
         }
     } else if (warp == kTcWarpMma) {
         // ================= MMA issuer: one elected lane =================
-        // Two cursors walk the CTA's stages.  The scale cursor copies a landed stage's block scales into
-        // tensor memory (one 4-column slot per ring item) -- that needs no activations, so the prefetched
-        // stages are done before the digit planes exist.  The MMA cursor follows once the planes are
-        // ready.  tcgen05.cp and tcgen05.mma of one thread execute in issue order, and a stage's slots
-        // are rewritten only after the stage was refilled, i.e. after its previous MMAs retired.
+        // A single thread: what bounds it is the length of its dependent instruction chain per stage,
+        // so the loops are nested (segment, stage, item) with all divisions in the segment level.
+        // Phase A copies the block scales of the prefetched stages into tensor memory (one 4-column
+        // slot per ring item) while the digit planes are still being made: that needs no activations.
+        // Phase B waits for the planes and issues the MMAs; from the second ring revolution on it also
+        // copies each landed stage's scales first.  tcgen05.cp and tcgen05.mma of one thread execute
+        // in issue order, and a ring slot's scales are rewritten only after the slot was refilled,
+        // i.e. after the MMAs that read them have retired.
         if (elect_one()) {
             // E2M1 x E2M1, E4M3 scales, K-major operands, M = 128, N = npad
             const uint32_t idesc = (1u << 7) | (1u << 10) | (uint32_t(npad >> 3) << 17) | (uint32_t(128 >> 4) << 24);
             // descriptors differ in their 14-bit address field only (shared memory is below 256 KB)
             const uint64_t d_ab = smem_desc(0, 128, 256), d_sf = smem_desc(0, 0, 128);
-            const uint64_t d_x0 = d_ab | (xbase >> 4);
-            const uint32_t xslot16 = xslot_bytes >> 4;
-            TcStageWalker wk_c, wk_m;
-            wk_c.init(total, kt_len, S, cta, grid);
-            wk_m.init(total, kt_len, S, cta, grid);
-            TcStage st_c, st_m;
-            bool have_c = wk_c.next(st_c), have_m = wk_m.next(st_m);
-            int ci = 0, mi = 0;        // stages whose scales are copied / whose MMAs are issued
-            int sc = 0, sm = 0;        // their ring slots
-            uint32_t use_c = 0, nseg = 0, acc = 0;
-            uint32_t tmem_d = tmem_base;
-            bool x_ready = false, ok = true;
-            int64_t polls = 0;
-            const uint64_t t_begin = globaltimer_ns();
-            while (have_m) {
-                bool progress = false;
-                // ---- scale cursor: every landed stage, at most a ring ahead of the MMAs ----
-                while (have_c && ci < mi + R && mbar_test_wait(sbase + TcSmem::kBarFull + 8 * sc, use_c & 1)) {
-                    tc_fence_after();
-                    if (P.trace && ci == 0) P.trace[cta * 16 + 4] = globaltimer_ns();
-                    if (P.trace && P.debug & 16 && ci < 64) P.trace[gridDim.x * 16 + cta * 256 + ci * 4 + 1] = clock64();
-                    uint32_t sf16 = (ring0 + sc * stage_bytes + kTcCodeBytes) >> 4;
-                    uint32_t sfa = tmem_sfa0 + 4u * uint32_t(sc * S);
-                    for (int i = 0; i < st_c.cnt; ++i) {
-                        tc_cp_sf(sfa, d_sf | sf16);
-                        sf16 += kTcItemBytes >> 4;
-                        sfa += 4u;
-                    }
-                    ++ci;
-                    if (++sc == R) sc = 0, ++use_c;
-                    have_c = wk_c.next(st_c);
-                    progress = true;
+            const uint32_t ab_hi = uint32_t(d_ab >> 32), ab_lo = uint32_t(d_ab), sf_hi = uint32_t(d_sf >> 32), sf_lo = uint32_t(d_sf);
+            const uint32_t x_lo0 = ab_lo | (xbase >> 4);
+            const uint32_t xslot16 = xslot_bytes >> 4, stage16 = stage_bytes >> 4, ring16 = ring0 >> 4;
+            constexpr uint32_t kItem16 = kTcItemBytes >> 4, kCode16 = kTcCodeBytes >> 4;
+            // block scales of the items of ring slot `slot` -> its tensor-memory columns
+            auto copy_scales = [&](uint32_t item16, uint32_t sfa, int cnt) {
+                if (cnt == S) {
+#pragma unroll
+                    for (int i = 0; i < S; ++i) tc_cp_sf2(sfa + 4u * i, sf_lo | (item16 + kCode16 + kItem16 * i), sf_hi);
+                } else {
+                    for (int i = 0; i < cnt; ++i) tc_cp_sf2(sfa + 4u * i, sf_lo | (item16 + kCode16 + kItem16 * i), sf_hi);
                 }
-                if (!x_ready && mbar_test_wait(sbase + TcSmem::kBarXReady, 0)) {
-                    tc_fence_after();
-                    if (P.trace) P.trace[cta * 16 + 3] = globaltimer_ns();
-                    tc_cp_sf(tmem_sfb, d_sf | ((sbase + TcSmem::kSfb) >> 4));
-                    x_ready = true;
-                    progress = true;
-                }
-                // ---- MMA cursor ----
-                if (x_ready && mi < ci) {
-                    bool d_ok = true;
-                    if (st_m.seg_first) {
-                        // the accumulator is free once the epilogue of the segment before last has read it
-                        if (nseg >= 2 &&
-                            !mbar_wait_probe(sbase + TcSmem::kBarDFree + 8 * (nseg & 1), ((nseg >> 1) - 1) & 1, P.spin_limit)) {
-                            report(P.status, QGEMV_ERR_TIMEOUT, 63, int(nseg));
+            };
+            bool ok = true;
+            int a_done = 0;  // stages whose scales phase A has copied
+            {
+                GsWalker wk;
+                wk.init(total, kt_len, cta, grid);
+                GsSeg sg;
+                while (ok && a_done < R && wk.next(sg)) {
+                    for (int32_t left = sg.u1 - sg.u0; left > 0 && a_done < R; left -= S) {
+                        if (!mbar_wait_probe(sbase + TcSmem::kBarFull + 8 * a_done, 0, P.spin_limit)) {
+                            report(P.status, QGEMV_ERR_TIMEOUT, 64, a_done);
                             *abort_flag = 1;
                             ok = false;
-                            d_ok = false;
+                            break;
                         }
                         tc_fence_after();
-                        tmem_d = tmem_base + (nseg & 1) * uint32_t(npad);
-                        acc = 0;  // the segment's first MMA overwrites D
+                        if (P.trace && a_done == 0) P.trace[cta * 16 + 4] = globaltimer_ns();
+                        copy_scales(ring16 + uint32_t(a_done) * stage16, tmem_sfa0 + uint32_t(a_done) * (4u * S), min(S, left));
+                        ++a_done;
                     }
-                    if (!d_ok) break;
-                    uint32_t item16 = (ring0 + sm * stage_bytes) >> 4;
-                    uint32_t sfa = tmem_sfa0 + 4u * uint32_t(sm * S);
-                    int32_t slot = st_m.u - xs0;
-                    if (slot < 0) slot += kt_len;
-                    uint64_t d_x = d_x0 + uint64_t(uint32_t(slot) * xslot16);
-                    for (int i = 0; i < st_m.cnt; ++i) {
-                        tc_mma_nvf4(tmem_d, d_ab | item16, d_x, idesc, sfa, tmem_sfb, acc);
-                        acc = 1;
-                        item16 += kTcItemBytes >> 4;
-                        sfa += 4u;
-                        d_x += xslot16;
-                    }
-                    tc_commit(sbase + TcSmem::kBarEmpty + 8 * sm);  // the stage is reusable once these retire
-                    if (P.trace && P.debug & 16 && mi < 64) P.trace[gridDim.x * 16 + cta * 256 + mi * 4 + 2] = clock64();
-                    if (st_m.seg_last) {
-                        tc_commit(sbase + TcSmem::kBarDFull + 8 * (nseg & 1));
-                        ++nseg;
-                    }
-                    ++mi;
-                    if (++sm == R) sm = 0;
-                    have_m = wk_m.next(st_m);
-                    progress = true;
-                }
-                if (progress) continue;
-                // Nothing to do.  Block (bounded, the hardware suspends the thread) on the one event that
-                // can come next: with every ring slot's scales copied only the digit planes are missing,
-                // and with the planes ready only the next stage; otherwise both can happen, so probe.
-                if (x_ready) {
-                    if (!mbar_wait(sbase + TcSmem::kBarFull + 8 * sc, use_c & 1, P.spin_limit)) {
-                        report(P.status, QGEMV_ERR_TIMEOUT, 64, mi);
-                        *abort_flag = 1;
-                        ok = false;
-                        break;
-                    }
-                } else if (!have_c || ci >= mi + R) {
-                    if (!mbar_wait(sbase + TcSmem::kBarXReady, 0, P.spin_limit)) {
-                        report(P.status, QGEMV_ERR_TIMEOUT, 62, mi);
-                        *abort_flag = 1;
-                        ok = false;
-                        break;
-                    }
-                } else if (++polls > P.spin_limit || ((polls & 4095) == 4095 && globaltimer_ns() - t_begin > 4000000000ull)) {
-                    report(P.status, QGEMV_ERR_TIMEOUT, 62, mi);
-                    *abort_flag = 1;
-                    ok = false;
-                    break;
                 }
             }
-            if (P.trace) P.trace[cta * 16 + 5] = globaltimer_ns();
-            (void)ok;
+            // everything the first segment needs is computed before the wait for the planes
+            GsWalker wk;
+            wk.init(total, kt_len, cta, grid);
+            GsSeg sg;
+            bool have = wk.next(sg);
+            uint32_t nseg = 0, full_par = 0;
+            uint32_t item16 = ring16, sfa = tmem_sfa0, bar_full = sbase + TcSmem::kBarFull, bar_empty = sbase + TcSmem::kBarEmpty;
+            const uint32_t ring_end16 = ring16 + uint32_t(R) * stage16;
+            if (ok && !mbar_wait(sbase + TcSmem::kBarXReady, 0, P.spin_limit)) {
+                report(P.status, QGEMV_ERR_TIMEOUT, 62, 0);
+                *abort_flag = 1;
+                ok = false;
+            }
+            int mi = 0;  // stages issued
+            if (ok) {
+                tc_fence_after();
+                if (P.trace) P.trace[cta * 16 + 3] = globaltimer_ns();
+                tc_cp_sf2(tmem_sfb, sf_lo | ((sbase + TcSmem::kSfb) >> 4), sf_hi);
+                for (; ok && have; have = wk.next(sg)) {
+                    // the accumulator is free once the epilogue of the segment before last has read it
+                    if (nseg >= 2 &&
+                        !mbar_wait_probe(sbase + TcSmem::kBarDFree + 8 * (nseg & 1), ((nseg >> 1) - 1) & 1, P.spin_limit)) {
+                        report(P.status, QGEMV_ERR_TIMEOUT, 63, int(nseg));
+                        *abort_flag = 1;
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t tmem_d = tmem_base + (nseg & 1) * uint32_t(npad);
+                    uint32_t acc = 0;  // the segment's first MMA overwrites D
+                    int32_t slot = sg.u0 - xs0;
+                    if (slot < 0) slot += kt_len;
+                    uint32_t x_lo = x_lo0 + uint32_t(slot) * xslot16;
+                    for (int32_t left = sg.u1 - sg.u0; left > 0; left -= S) {
+                        if (mi >= a_done) {
+                            if (!mbar_wait_probe(bar_full, full_par, P.spin_limit)) {
+                                report(P.status, QGEMV_ERR_TIMEOUT, 64, mi);
+                                *abort_flag = 1;
+                                ok = false;
+                                break;
+                            }
+                            tc_fence_after();
+                            copy_scales(item16, sfa, min(S, left));
+                        }
+                        if (left >= S) {
+#pragma unroll
+                            for (int i = 0; i < S; ++i)
+                                tc_mma_nvf4_2(tmem_d, ab_lo | (item16 + kItem16 * i), x_lo + xslot16 * i, ab_hi, idesc, sfa + 4u * i,
+                                              tmem_sfb, i == 0 ? acc : 1u);
+                        } else {
+                            for (int i = 0; i < left; ++i)
+                                tc_mma_nvf4_2(tmem_d, ab_lo | (item16 + kItem16 * i), x_lo + xslot16 * i, ab_hi, idesc, sfa + 4u * i,
+                                              tmem_sfb, i == 0 ? acc : 1u);
+                        }
+                        acc = 1;
+                        x_lo += xslot16 * S;
+                        tc_commit(bar_empty);  // the stage is reusable once these retire
+                        ++mi;
+                        item16 += stage16, sfa += 4u * S, bar_full += 8, bar_empty += 8;
+                        if (item16 == ring_end16) {
+                            item16 = ring16, sfa = tmem_sfa0, full_par ^= 1u;
+                            bar_full = sbase + TcSmem::kBarFull, bar_empty = sbase + TcSmem::kBarEmpty;
+                        }
+                    }
+                    if (!ok) break;
+                    tc_commit(sbase + TcSmem::kBarDFull + 8 * (nseg & 1));
+                    ++nseg;
+                }
+                if (P.trace) P.trace[cta * 16 + 5] = globaltimer_ns();
+            }
             *n_consumed = mi;
         }
         __syncwarp();
@@ -407,7 +458,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemv_tc_kernel(const TcParams P
             const uint32_t byte = n < 8 * Bl ? uint32_t(2 * j + 1) << 3 : 0u;
             *reinterpret_cast<volatile uint32_t*>(tc_smem + TcSmem::kSfb + (n & 31) * 16 + (n >> 5) * 4) = byte * 0x01010101u;
         }
-        pdl_wait();  // activations come from the preceding kernel; y, workspace and counters may still be in use by it
+        pdl_wait();  // activations come from the preceding kernel; y and the hand-over slots may still be in use by it
         if (P.trace && ct == 0) P.trace[cta * 16 + 1] = globaltimer_ns();
         // ---- digit planes of the items this CTA multiplies.  Work unit w = ((row b) * n_slots + slot) * 8
         // + octet: eight consecutive elements, one 16-byte load.  One pass loads and finds the row maxima
@@ -506,13 +557,10 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemv_tc_kernel(const TcParams P
             }
             // a partial segment's bookkeeping does not need the accumulator: do it while the MMAs run
             const bool whole = sg.u0 == 0 && sg.u1 == kt_len;
-            int32_t c_lo = 0, c_hi = 0, lo_slot = 0;
+            int32_t c_lo = 0, c_hi = 0;
             if (!whole) {
                 c_lo = int32_t(cta_of(int64_t(sg.tile) * kt_len, total, grid));
                 c_hi = int32_t(cta_of(int64_t(sg.tile + 1) * kt_len - 1, total, grid));
-                // every contributor after the first starts its range inside this tile: its part is in its
-                // slot 0; the first one's range may have started in an earlier tile
-                lo_slot = gs_slot(c_lo, sg.tile, kt_len, total, grid);
             }
             if (!__all_sync(0xFFFFFFFFu, mbar_wait_probe(sbase + TcSmem::kBarDFull + 8 * g, (nseg >> 1) & 1, P.spin_limit))) {
                 if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 65, int(nseg));
@@ -555,49 +603,23 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemv_tc_kernel(const TcParams P
             };
             if (whole) {
                 store_row(val);
-            } else {
-                // partial: park the fp32 sums; the last contributor of (tile, lane quarter) adds all
-                // parts in CTA order.  The arrival counter is bumped with release / acquire semantics
-                // by one lane after the warp has converged, which orders the whole warp's stores
-                // before it and the other warps' parts before the loads below.
-                const int32_t my_slot = cta == c_lo ? lo_slot : 2 * cta;
-                float* slot = P.ws + size_t(my_slot) * 1024 + row;
+            } else if (cta != c_lo) {
+                // Partial, and not the tile's first contributor: hand the fp32 sums to it.  Every later
+                // contributor starts its range inside this tile, so the tile is its first segment and
+                // the part goes to its slot 0.  A slot element is the 8-byte pair {value, 1}: the
+                // arrival flag travels in the same store as the data, so there is no fence, no counter
+                // and no round trip on this side.
+                unsigned long long* slot = reinterpret_cast<unsigned long long*>(P.ws) + size_t(2 * cta) * 1024 + row;
 #pragma unroll
                 for (int b = 0; b < 8; ++b)
-                    if (b < Bl) __stcg(slot + b * 128, val[b]);
-                __syncwarp();
-                int old = 0;
-                if (lane == 0) old = atom_add_acq_rel(P.counters + sg.tile * 4 + q, 1);
-                old = __shfl_sync(0xFFFFFFFFu, old, 0);
-                if (old == c_hi - c_lo) {
-                    float v[8];
-                    const float* p0 = P.ws + size_t(lo_slot) * 1024 + row;
-#pragma unroll
-                    for (int b = 0; b < 8; ++b)
-                        if (b < Bl) v[b] = __ldcg(p0 + b * 128);
-                    // four parts' loads in flight at a time; the additions stay in CTA order
-                    for (int32_t cc = c_lo + 1; cc <= c_hi; cc += 4) {
-                        float t[4][8];
-#pragma unroll
-                        for (int z = 0; z < 4; ++z) {
-                            const float* pz = P.ws + size_t(2 * min(cc + z, c_hi)) * 1024 + row;
-#pragma unroll
-                            for (int b = 0; b < 8; ++b)
-                                if (b < Bl) t[z][b] = __ldcg(pz + b * 128);
-                        }
-#pragma unroll
-                        for (int z = 0; z < 4; ++z) {
-                            if (cc + z <= c_hi) {
-#pragma unroll
-                                for (int b = 0; b < 8; ++b)
-                                    if (b < Bl) v[b] += t[z][b];
-                            }
-                        }
-                    }
-                    store_row(v);
-                    __syncwarp();
-                    if (lane == 0) P.counters[sg.tile * 4 + q] = 0;
-                }
+                    if (b < Bl) st_flagged(slot + b * 128, val[b]);
+            } else {
+                // The first contributor (for which the tile is the last segment of its range) adds the
+                // parts in CTA order -- a fixed order, whatever the arrival order -- as they arrive,
+                // clears every slot it has read (the next launch finds them empty) and stores the rows.
+                // The loads of up to eight parts are in flight together; the wait is bounded.
+                const bool ok = tc_collect(P, val, Bl, c_lo, c_hi, row, abort_flag);
+                if (ok) store_row(val);
             }
             ++nseg;
         }

@@ -85,7 +85,7 @@ typedef struct qgemv_config {
                               bit 9: schedule override for tests -- the streaming kernel always
                               splits K across CTAs (partial sums + fixed-order fix-up) */
     int64_t spin_limit;    /* poll budget of every in-kernel wait; 0 = default */
-    int32_t tc_stage_items; /* QGEMV_FMT_NVFP4_TC GEMV: 4608-byte items per bulk copy; 0 = default (2) */
+    int32_t tc_stage_items; /* QGEMV_FMT_NVFP4_TC GEMV: 4608-byte items per bulk copy: 1, 2, 4 or 8; 0 = default (4) */
     int32_t tc_smem_kb;     /* ... shared memory per CTA the ring may grow to, in KiB; 0 = default
                                (about half an SM, so that the next kernel's CTA is resident and
                                prefetches its weights while this one streams) */
