@@ -79,6 +79,8 @@ int64_t default_spin(const qgemv_handle* h) {
     return h->cfg.spin_limit > 0 ? h->cfg.spin_limit : (int64_t(1) << 26);
 }
 
+thread_local int g_launch_cluster = 1;  // thread-block cluster size of the next launch() (1: none)
+
 template <typename... KArgs, typename... Args>
 cudaError_t launch(const qgemv_handle* h, void (*kernel)(KArgs...), dim3 grid, dim3 block,
                    size_t smem, cudaStream_t stream, Args... args) {
@@ -88,11 +90,23 @@ cudaError_t launch(const qgemv_handle* h, void (*kernel)(KArgs...), dim3 grid, d
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int n_attr = 0;
+    if (h->cfg.use_pdl) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attr;
+    }
+    if (g_launch_cluster > 1) {
+        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+        attr[n_attr].val.clusterDim.x = unsigned(g_launch_cluster);
+        attr[n_attr].val.clusterDim.y = 1;
+        attr[n_attr].val.clusterDim.z = 1;
+        ++n_attr;
+        g_launch_cluster = 1;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = h->cfg.use_pdl ? 1 : 0;
+    cfg.numAttrs = n_attr;
     const cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
     if (err != cudaSuccess) g_last_cuda_error = err;
     return err;
@@ -179,19 +193,32 @@ int launch_gemv(const qgemv_handle* h, const qgemv_weight* w, const qg::GemvPara
 // Shared-memory plan of one launch over `kt_len` items per tile: digit-plane slots for the items a
 // CTA can own, then as many ring stages as the cap allows.
 struct TcPlan {
-    int grid, npad, x_slots, ring, stage_items;
+    int grid, npad, x_slots, ring, stage_items, cluster;
     size_t smem;
 };
 bool tc_plan(const qgemv_handle* h, int64_t tiles, int64_t kt_len, int B, TcPlan* pl) {
     const int64_t total = tiles * kt_len;
     pl->grid = int(std::min<int64_t>(gemv_grid(h), total));
-    pl->npad = (8 * B + 15) / 16 * 16;
+    // Optional (debug bit 5), for matrices with few row tiles: a thread-block cluster per tile, the
+    // tile's K range cut evenly over its CTAs, partial sums handed over in distributed shared memory.
+    // Measured on the 8B stack it shortens the hand-over (1.5 against 2.3 us after the last MMA) but
+    // some clusters are scheduled late behind the previous launch's, and the layer gets slower
+    // (40.7 against 38.4 us): off by default.
+    pl->cluster = 1;
+    if (h->cfg.grid_override == 0 && (h->cfg.debug & 32) && tiles * 2 <= h->sm_count && kt_len >= 2) {
+        const int64_t c = std::min<int64_t>({8, h->sm_count / tiles, kt_len});
+        if (c >= 2) {
+            pl->cluster = int(c);
+            pl->grid = int(tiles * c);
+        }
+    }
+    pl->npad = (8 * B + 15) / 16 * 16;  // M = 128 wants N in multiples of 16 (N = 8 gave wrong sums and a memory fault)
     const int64_t per_cta = (total + pl->grid - 1) / pl->grid;
     pl->x_slots = int(std::min<int64_t>(kt_len, per_cta));
     const int si = h->cfg.tc_stage_items;
     pl->stage_items = si >= 8 ? 8 : (si >= 4 ? 4 : (si >= 2 ? 2 : (si == 1 ? 1 : 4)));  // 1, 2, 4 or 8; default 4
     const int stage_bytes = pl->stage_items * qg::kTcItemBytes;
-    const int base = qg::TcSmem::ring_off(pl->x_slots, pl->npad);
+    const int base = qg::TcSmem::ring_off(pl->x_slots, pl->npad, pl->cluster, B);
     // Prefer a footprint of about half an SM: the CTA of the next kernel in the stream is then
     // resident beside this one and fills its ring while this one still streams.
     const int want_cap = (h->cfg.tc_smem_kb > 0 ? std::min(h->cfg.tc_smem_kb, 227) : 112) * 1024;
@@ -202,12 +229,12 @@ bool tc_plan(const qgemv_handle* h, int64_t tiles, int64_t kt_len, int B, TcPlan
     ring = std::min(ring, qg::TcSmem::max_ring_items(pl->npad) / pl->stage_items);
     if (ring < 2) return false;
     pl->ring = ring;
-    pl->smem = size_t(qg::TcSmem::total(pl->x_slots, pl->npad, ring, pl->stage_items));
+    pl->smem = size_t(qg::TcSmem::total(pl->x_slots, pl->npad, ring, pl->stage_items, pl->cluster, B));
     return pl->smem <= size_t(qg::kGsSmemBudget);
 }
 
 int gemv_tc(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, int B, void* y, int y_dtype,
-            cudaStream_t stream) {
+            const qgemv_weight* next, cudaStream_t stream) {
     const int64_t tiles = w->n_panels / 8, kt_total = w->units;
     // K window per launch: the whole K when the digit planes of a CTA's items fit beside a ring,
     // otherwise chunks of items whose fp32 results are added in chunk order (as the K-chunked
@@ -247,8 +274,21 @@ int gemv_tc(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, int B, v
         P.ring = pl.ring;
         P.stage_items = pl.stage_items;
         P.x_slots = pl.x_slots;
+        P.cluster = pl.cluster;
         P.trace = h->tc_trace;
+        if (next && next->fmt == QGEMV_FMT_NVFP4_TC && next->n_stack == 1 && c + 1 == n_chunks) {
+            // the last launch of this call pulls the next weight towards L2, split as its own launch
+            // (same batch assumed) will split it
+            TcPlan np;
+            if (tc_plan(h, next->n_panels / 8, next->units, B, &np)) {
+                P.pf_base = next->dev_blob + QG_HEADER_BYTES + next->aux_bytes;
+                P.pf_total = int32_t(next->n_panels / 8 * next->units);
+                P.pf_grid = np.grid;
+                P.pf_skip = uint32_t(np.ring) * uint32_t(np.stage_items) * qg::kTcItemBytes;
+            }
+        }
         const dim3 g(unsigned(pl.grid)), blk(qg::kTcThreads);
+        g_launch_cluster = pl.cluster;
         const cudaError_t err = pl.stage_items == 1   ? launch(h, qg::gemv_tc_kernel<1>, g, blk, pl.smem, stream, P)
                                 : pl.stage_items == 2 ? launch(h, qg::gemv_tc_kernel<2>, g, blk, pl.smem, stream, P)
                                 : pl.stage_items == 4 ? launch(h, qg::gemv_tc_kernel<4>, g, blk, pl.smem, stream, P)
@@ -466,7 +506,8 @@ int qgemv_gemv_prefetch(qgemv_handle* h, const qgemv_weight* w, const void* x_bf
     if (B < 1 || B > QGEMV_MAX_ROWS) return QGEMV_ERR_UNSUPPORTED_SHAPE;
     if (y_dtype != QGEMV_OUT_BF16 && y_dtype != QGEMV_OUT_F32) return QGEMV_ERR_INVALID_ARG;
     if ((reinterpret_cast<uintptr_t>(x_bf16) & 15u) != 0) return QGEMV_ERR_INVALID_ARG;
-    if (w->fmt == QGEMV_FMT_NVFP4_TC && B <= QGEMV_MAX_BATCH) return gemv_tc(h, w, x_bf16, B, y, y_dtype, static_cast<cudaStream_t>(stream));
+    if (w->fmt == QGEMV_FMT_NVFP4_TC && B <= QGEMV_MAX_BATCH)
+        return gemv_tc(h, w, x_bf16, B, y, y_dtype, next, static_cast<cudaStream_t>(stream));
     if (B > QGEMV_MAX_BATCH) {
         // two launches: rows 0..7, then the rest (the second one names the next matrix)
         if ((w->K * 2 * QGEMV_MAX_BATCH) % 16 != 0) return QGEMV_ERR_UNSUPPORTED_SHAPE;

@@ -71,7 +71,15 @@ struct TcParams {
     int32_t npad;            // MMA N extent: 8 * B rounded up to 16
     int32_t ring, stage_items;
     int32_t x_slots;         // item slots of digit planes in shared memory
+    int32_t cluster;         // CTAs per thread-block cluster (1: none).  Above 1 the launch has tiles * cluster
+                             // CTAs, a cluster owns one row tile and hands partial sums over in shared memory
     unsigned long long* trace;  // optional: 16 globaltimer stamps per CTA (diagnostics), or null
+    // optional L2 prefetch of the weight the caller multiplies by next (same kind of blob): CTA c pulls
+    // what CTA c of that launch will stream, minus the head its own ring prefetches
+    const uint8_t* pf_base;     // payload of the next weight, or null
+    int32_t pf_total;           // its items (tiles * items per tile)
+    int32_t pf_grid;            // CTAs of its launch
+    uint32_t pf_skip;           // bytes at the head of every CTA's share to leave out
 };
 
 struct TcSmem {
@@ -87,14 +95,17 @@ struct TcSmem {
     static constexpr int kConsumed = 316;
     static constexpr int kRowMax = 320;     // 8 words: largest |bf16| pattern per activation row
     static constexpr int kWarpMax = 384;    // kTcConvWarps x 8 words: the same per converting warp
+    static constexpr int kBarParts = 640;   // cluster mode: arrivals of the other ranks' partial sums
     static constexpr int kSfb = 1024;       // 512 bytes: block scales of the digit planes
-    static constexpr int kX = 1536;         // x_slots * npad * 32
+    static constexpr int kParts = 1536;     // cluster mode: (cluster - 1) x B x 128 fp32 partial sums, rank 0 only
+    __host__ __device__ static constexpr int parts_bytes(int cluster, int B) { return cluster > 1 ? (cluster - 1) * B * 512 : 0; }
+    __host__ __device__ static constexpr int x_off(int cluster, int B) { return kParts + parts_bytes(cluster, B); }
     __host__ __device__ static constexpr int x_bytes(int x_slots, int npad) { return x_slots * npad * 32; }
-    __host__ __device__ static constexpr int ring_off(int x_slots, int npad) {
-        return (kX + x_bytes(x_slots, npad) + 127) / 128 * 128;
+    __host__ __device__ static constexpr int ring_off(int x_slots, int npad, int cluster, int B) {
+        return (x_off(cluster, B) + x_bytes(x_slots, npad) + 127) / 128 * 128;
     }
-    __host__ __device__ static constexpr int total(int x_slots, int npad, int ring, int stage_items) {
-        return ring_off(x_slots, npad) + ring * stage_items * kTcItemBytes;
+    __host__ __device__ static constexpr int total(int x_slots, int npad, int ring, int stage_items, int cluster, int B) {
+        return ring_off(x_slots, npad, cluster, B) + ring * stage_items * kTcItemBytes;
     }
     // tensor memory: two accumulators of npad columns, 4 columns of plane scales, then one 4-column
     // slot of weight block scales per ring item
@@ -130,6 +141,45 @@ __device__ __forceinline__ void tc_mma_nvf4(uint32_t tmem_d, uint64_t desc_a, ui
         " tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n}" ::"r"(tmem_d),
         "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(tmem_sfa), "r"(tmem_sfb), "r"(accumulate)
         : "memory");
+}
+
+// ---- thread-block cluster helpers (distributed shared memory) --------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared-memory address of `local` in the CTA of rank `rank` of this cluster
+__device__ __forceinline__ uint32_t cluster_map(uint32_t local, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t remote_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
+}
+// bounded wait with cluster-scope acquire: the data it guards was written by other CTAs of the cluster
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, int64_t spin_limit) {
+    uint64_t t0 = 0;
+    for (int64_t i = 0; i <= spin_limit; ++i) {
+        if (i == 1) t0 = globaltimer_ns();
+        if ((i & 63) == 63 && globaltimer_ns() - t0 > 2000000000ull) return false;
+        uint32_t ok;
+        asm volatile(
+            "{\n .reg .pred p;\n mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n"
+            " selp.u32 %0, 1, 0, p;\n}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity), "r"(20000u)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
 }
 
 // Split-K hand-over: an aligned 8-byte element {fp32 value, flag 1} written and read as one access.
@@ -247,9 +297,9 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemv_tc_kernel(const TcParams P
     const int32_t xs0 = n_items >= kt_len ? 0 : r_begin % kt_len;
     const int32_t n_slots = n_items >= kt_len ? kt_len : n_items;
     const uint32_t xslot_bytes = uint32_t(npad) * 32u;
-    const uint32_t xbase = sbase + TcSmem::kX;
+    const uint32_t xbase = sbase + uint32_t(TcSmem::x_off(P.cluster, P.B));
     const uint32_t stage_bytes = uint32_t(S) * kTcItemBytes;
-    const uint32_t ring0 = sbase + uint32_t(TcSmem::ring_off(P.x_slots, npad));
+    const uint32_t ring0 = sbase + uint32_t(TcSmem::ring_off(P.x_slots, npad, P.cluster, P.B));
     const uint32_t ncols = kTcTmemCols;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tc_smem + TcSmem::kAbort);
     volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(tc_smem + TcSmem::kTmemPtr);
@@ -268,6 +318,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemv_tc_kernel(const TcParams P
         }
         mbar_init(sbase + TcSmem::kBarXReady, 1);
         mbar_init(sbase + TcSmem::kBarDrain, 1);
+        mbar_init(sbase + TcSmem::kBarParts, P.cluster > 1 ? uint32_t(128 * (P.cluster - 1)) : 1u);
         *abort_flag = 0;
         *n_issued = 0;
         *n_consumed = 0;
@@ -282,8 +333,10 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemv_tc_kernel(const TcParams P
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_ptr;
+    // cluster mode: rank 0's hand-over barrier must exist before any other rank can arrive on it
+    if (P.cluster > 1) cluster_sync_all();
     pdl_launch_dependents();
-    if (P.trace && threadIdx.x == 0) P.trace[cta * 16 + 0] = globaltimer_ns();
+    if (P.trace && threadIdx.x == 0) { P.trace[cta * 16 + 0] = globaltimer_ns(); P.trace[cta * 16 + 9] = clock64(); }
     // tensor-memory columns: two accumulators, the planes' block scales, a ring of weight block scales
     const uint32_t tmem_sfb = tmem_base + 2u * uint32_t(npad);
     const uint32_t tmem_sfa0 = tmem_sfb + 4u;
@@ -324,6 +377,16 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemv_tc_kernel(const TcParams P
                 if (*abort_flag) break;
             }
             *n_issued = issued;
+            // This launch's last copy is on its way: from here on HBM would idle through the epilogue,
+            // the launch boundary and the next launch's activation conversion.  Pull the next weight
+            // towards L2 meanwhile (weights are immutable, so an early prefetch is always safe).
+            if (P.pf_base != nullptr && ok) {
+                for (int c2 = cta; c2 < P.pf_grid; c2 += grid) {
+                    uint64_t lo = (uint64_t(c2) * uint64_t(P.pf_total)) / uint64_t(P.pf_grid) * kTcItemBytes + P.pf_skip;
+                    const uint64_t hi = (uint64_t(c2 + 1) * uint64_t(P.pf_total)) / uint64_t(P.pf_grid) * kTcItemBytes;
+                    for (; lo < hi; lo += 32768) bulk_prefetch_l2(P.pf_base + lo, uint32_t(min(uint64_t(32768), hi - lo)));
+                }
+            }
         }
     } else if (warp == kTcWarpMma) {
         // ================= MMA issuer: one elected lane =================
@@ -341,8 +404,10 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemv_tc_kernel(const TcParams P
             // descriptors differ in their 14-bit address field only (shared memory is below 256 KB)
             const uint64_t d_ab = smem_desc(0, 128, 256), d_sf = smem_desc(0, 0, 128);
             const uint32_t ab_hi = uint32_t(d_ab >> 32), ab_lo = uint32_t(d_ab), sf_hi = uint32_t(d_sf >> 32), sf_lo = uint32_t(d_sf);
-            const uint32_t x_lo0 = ab_lo | (xbase >> 4);
-            const uint32_t xslot16 = xslot_bytes >> 4, stage16 = stage_bytes >> 4, ring16 = ring0 >> 4;
+            // In a cluster launch a CTA's shared-memory addresses carry its window's base above bit 18;
+            // the descriptors take the 14-bit field (address within the CTA's window, in 16-byte units).
+            const uint32_t x_lo0 = ab_lo | ((xbase >> 4) & 0x3FFFu);
+            const uint32_t xslot16 = xslot_bytes >> 4, stage16 = stage_bytes >> 4, ring16 = (ring0 >> 4) & 0x3FFFu;
             constexpr uint32_t kItem16 = kTcItemBytes >> 4, kCode16 = kTcCodeBytes >> 4;
             // block scales of the items of ring slot `slot` -> its tensor-memory columns
             auto copy_scales = [&](uint32_t item16, uint32_t sfa, int cnt) {
@@ -368,7 +433,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemv_tc_kernel(const TcParams P
                             break;
                         }
                         tc_fence_after();
-                        if (P.trace && a_done == 0) P.trace[cta * 16 + 4] = globaltimer_ns();
+                        if (P.trace && a_done == 0) P.trace[cta * 16 + 4] = clock64();
                         copy_scales(ring16 + uint32_t(a_done) * stage16, tmem_sfa0 + uint32_t(a_done) * (4u * S), min(S, left));
                         ++a_done;
                     }
@@ -390,8 +455,9 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemv_tc_kernel(const TcParams P
             int mi = 0;  // stages issued
             if (ok) {
                 tc_fence_after();
-                if (P.trace) P.trace[cta * 16 + 3] = globaltimer_ns();
-                tc_cp_sf2(tmem_sfb, sf_lo | ((sbase + TcSmem::kSfb) >> 4), sf_hi);
+                if (P.trace) P.trace[cta * 16 + 3] = clock64();
+                tc_cp_sf2(tmem_sfb, sf_lo | (((sbase + TcSmem::kSfb) >> 4) & 0x3FFFu), sf_hi);
+                if (P.trace && (P.debug & 16)) P.trace[gridDim.x * 16 + cta * 64 + 63] = clock64();
                 for (; ok && have; have = wk.next(sg)) {
                     // the accumulator is free once the epilogue of the segment before last has read it
                     if (nseg >= 2 &&
@@ -431,6 +497,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemv_tc_kernel(const TcParams P
                         acc = 1;
                         x_lo += xslot16 * S;
                         tc_commit(bar_empty);  // the stage is reusable once these retire
+                        if (P.trace && (P.debug & 16) && mi < 60) P.trace[gridDim.x * 16 + cta * 64 + mi] = clock64();
                         ++mi;
                         item16 += stage16, sfa += 4u * S, bar_full += 8, bar_empty += 8;
                         if (item16 == ring_end16) {
@@ -442,7 +509,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemv_tc_kernel(const TcParams P
                     tc_commit(sbase + TcSmem::kBarDFull + 8 * (nseg & 1));
                     ++nseg;
                 }
-                if (P.trace) P.trace[cta * 16 + 5] = globaltimer_ns();
+                if (P.trace) P.trace[cta * 16 + 5] = clock64();
             }
             *n_consumed = mi;
         }
@@ -459,7 +526,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemv_tc_kernel(const TcParams P
             *reinterpret_cast<volatile uint32_t*>(tc_smem + TcSmem::kSfb + (n & 31) * 16 + (n >> 5) * 4) = byte * 0x01010101u;
         }
         pdl_wait();  // activations come from the preceding kernel; y and the hand-over slots may still be in use by it
-        if (P.trace && ct == 0) P.trace[cta * 16 + 1] = globaltimer_ns();
+        if (P.trace && ct == 0) { P.trace[cta * 16 + 1] = clock64(); P.trace[cta * 16 + 10] = globaltimer_ns(); }
         // ---- digit planes of the items this CTA multiplies.  Work unit w = ((row b) * n_slots + slot) * 8
         // + octet: eight consecutive elements, one 16-byte load.  One pass loads and finds the row maxima
         // (the first four units of a thread stay in registers), a second one converts. ----
@@ -537,7 +604,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemv_tc_kernel(const TcParams P
         fence_proxy_async_smem();  // the planes are read by the tensor core (async proxy)
         named_bar_sync(1, kTcConvThreads);
         if (ct == 0) mbar_arrive(sbase + TcSmem::kBarXReady);
-        if (P.trace && ct == 0) P.trace[cta * 16 + 2] = globaltimer_ns();
+        if (P.trace && ct == 0) P.trace[cta * 16 + 2] = clock64();
 
         // ---- epilogues: group g takes the segments with nseg % 2 == g; this warp owns lane quarter q ----
         const int g = (warp - kTcWarpConv0) >> 2, q = warp & 3;
@@ -568,7 +635,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemv_tc_kernel(const TcParams P
                 break;
             }
             tc_fence_after();
-            if (P.trace && lane == 0 && q == 0) P.trace[cta * 16 + 6] = globaltimer_ns();  // the last one stays
+            if (P.trace && lane == 0 && q == 0) P.trace[cta * 16 + 6] = clock64();  // the last one stays
             float val[8];
 #pragma unroll
             for (int b = 0; b < 8; ++b) {
@@ -603,6 +670,40 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemv_tc_kernel(const TcParams P
             };
             if (whole) {
                 store_row(val);
+            } else if (P.cluster > 1) {
+                // The cluster owns this row tile and every CTA of it has exactly this one segment: the
+                // partial sums travel through rank 0's shared memory and arrive on its barrier; rank 0
+                // adds them in rank order and stores.  No global-memory round trip.  Every thread
+                // releases its own stores with its own arrival (one arrival per warp after a warp
+                // barrier left some rows unwritten when rank 0 read them, and rank 0 gone when they
+                // landed).
+                const uint32_t rank = cluster_ctarank();
+                if (rank != uint32_t(cta % P.cluster)) {
+                    // not launched as the clusters the host planned: touch nobody's shared memory
+                    if (lane == 0) report(P.status, QGEMV_ERR_BOUNDS, 68, int(rank));
+                    *abort_flag = 1;
+                    break;
+                }
+                if (rank != 0) {
+                    const uint32_t dst = cluster_map(sbase + TcSmem::kParts, 0) + ((rank - 1) * uint32_t(Bl) * 128u + uint32_t(row)) * 4u;
+#pragma unroll
+                    for (int b = 0; b < 8; ++b)
+                        if (b < Bl) st_cluster_f32(dst + b * 512, val[b]);
+                    mbar_arrive_cluster(cluster_map(sbase + TcSmem::kBarParts, 0));
+                } else {
+                    if (!__all_sync(0xFFFFFFFFu, mbar_wait_cluster(sbase + TcSmem::kBarParts, 0, P.spin_limit))) {
+                        if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 67, sg.tile);
+                        *abort_flag = 1;
+                        break;
+                    }
+                    const float* parts = reinterpret_cast<const float*>(tc_smem + TcSmem::kParts) + row;
+                    for (int r = 1; r < P.cluster; ++r) {
+#pragma unroll
+                        for (int b = 0; b < 8; ++b)
+                            if (b < Bl) val[b] += parts[((r - 1) * Bl + b) * 128];
+                    }
+                    store_row(val);
+                }
             } else if (cta != c_lo) {
                 // Partial, and not the tile's first contributor: hand the fp32 sums to it.  Every later
                 // contributor starts its range inside this tile, so the tile is its first segment and
@@ -623,7 +724,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemv_tc_kernel(const TcParams P
             }
             ++nseg;
         }
-        if (P.trace && lane == 0) atomicMax(P.trace + cta * 16 + 8, globaltimer_ns());
+        if (P.trace && lane == 0 && g == 0 && q == 0) { P.trace[cta * 16 + 8] = clock64(); P.trace[cta * 16 + 11] = globaltimer_ns(); }
     }
     // ---- release tensor memory (always), after every role is done with it ----
     tc_fence_before();

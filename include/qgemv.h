@@ -83,7 +83,11 @@ typedef struct qgemv_config {
                               bit 8: schedule override for tests -- dense GEMV and MoE use the
                               general CTA-wide ring kernel instead of the per-warp streaming one;
                               bit 9: schedule override for tests -- the streaming kernel always
-                              splits K across CTAs (partial sums + fixed-order fix-up) */
+                              splits K across CTAs (partial sums + fixed-order fix-up);
+                              bit 5: schedule override -- the tensor-core GEMV launches a
+                              thread-block cluster per row tile for matrices with few tiles
+                              (partial sums handed over in distributed shared memory instead of
+                              global-memory slots) */
     int64_t spin_limit;    /* poll budget of every in-kernel wait; 0 = default */
     int32_t tc_stage_items; /* QGEMV_FMT_NVFP4_TC GEMV: 4608-byte items per bulk copy: 1, 2, 4 or 8; 0 = default (4) */
     int32_t tc_smem_kb;     /* ... shared memory per CTA the ring may grow to, in KiB; 0 = default
@@ -272,9 +276,11 @@ int qgemv_dequant_f32(qgemv_handle* h, const qgemv_weight* w, int which, float* 
 /* Phase timestamps of the tensor-core GEMV (diagnostics; no counterpart in the registry).  `dev_buf`:
  * device memory of 16 x 8 bytes per CTA (one CTA per SM unless grid_override says otherwise), or NULL
  * to switch it off again.  Every later QGEMV_FMT_NVFP4_TC launch on the handle makes each CTA store
- * %globaltimer (ns) at: [0] set-up done, [1] dependency wait over, [2] activation digit planes
- * written, [3] MMA issuer released, [4] its first weight stage landed, [5] its last MMA issued,
- * [6] last accumulator complete, [7] CTA done.  The caller zeroes and reads the buffer. */
+ * %globaltimer (ns) at [0] set-up done and [7] CTA done, and the SM's cycle counter (cheap to read;
+ * comparable inside one CTA only) at: [9] set-up done, [1] dependency wait over, [2] activation
+ * digit planes written, [3] MMA issuer released, [4] its first weight stage landed, [5] its last MMA
+ * issued, [6] last accumulator complete, [8] last epilogue warp done.  The caller zeroes and reads
+ * the buffer. */
 int qgemv_set_trace(qgemv_handle* h, void* dev_buf);
 /* Synchronises `stream`, reads and clears the device status word. */
 int qgemv_last_device_status(qgemv_handle* h, void* stream, qgemv_dev_status* out);

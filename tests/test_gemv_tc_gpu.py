@@ -121,6 +121,23 @@ def test_tc_k_split_across_ctas(qg, grid):
     h.close()
 
 
+@pytest.mark.parametrize("N,K,B", [(128, 4096, 1), (4096, 4096, 1), (6144, 4096, 3), (1000, 2112, 8), (300, 128, 2)])
+def test_tc_cluster_handover(qg, N, K, B):
+    """Debug bit 5: a thread-block cluster per row tile, partial sums through distributed shared memory."""
+    h = qg.QGemv(device=0, debug_bits=32)
+    codes, scales, ts = O.make_nvfp4(N, K, seed=N + K)
+    x = O.make_x(B, K, seed=B)
+    w = _load(qg, h, codes, scales, ts)
+    y = U.run_gemv(qg, h, w, x, h=h)
+    U.status_ok(h)
+    ref = O.gemv_nvfp4_f64(codes, scales, ts, x)
+    for b in range(B):
+        assert O.rel_l2(y[b], ref[b]) < TOL_F32, b
+    assert np.array_equal(U.bits(y), U.bits(U.run_gemv(qg, h, w, x, h=h)))
+    w.unload()
+    h.close()
+
+
 @pytest.mark.parametrize("stage_items,smem_kb", [(1, 0), (2, 64), (8, 227), (4, 227)])
 def test_tc_ring_shapes(qg, stage_items, smem_kb):
     """Ring geometry is a tuning knob, never a result: same bits for every stage size and depth."""
