@@ -99,7 +99,7 @@ class ClockSampler:
         return out
 
 
-def build_stack(model, batch, rank, world, dev_index, layout="tc", prefetch_next=True):
+def build_stack(model, batch, rank, world, dev_index, layout="tc", prefetch_next=True, fused=True):
     """The rank's share of the layer stack.  Tensor parallel: QKV and gate/up are column-parallel
     (this rank holds N/world output rows), o and down are row-parallel (K/world input columns; their
     outputs are partial sums that are all-reduced right after the GEMV, inside the captured graph).
@@ -147,7 +147,8 @@ def build_stack(model, batch, rank, world, dev_index, layout="tc", prefetch_next
             handle.tp_allreduce(out.data_ptr(), qg.OUT_BF16, out.numel(), torch.cuda.current_stream().cuda_stream)
 
     stack = LayerStack(handle, weights, batch, qg.OUT_BF16, device=dev_index,
-                       after_call=after_call if world > 1 else None, prefetch_next=prefetch_next)
+                       after_call=after_call if world > 1 else None, prefetch_next=prefetch_next,
+                       fused=fused and layout == "tc" and world == 1)
     stack_ref.append(stack)
     g = torch.Generator()
     g.manual_seed(7 + rank)
@@ -514,6 +515,7 @@ def main():
     ap.add_argument("--layout", default="tc", choices=["tc", "lane"],
                     help="stored form of the NVFP4 weights: tc = tile order consumed as stored by the block-scaled "
                          "tensor-core GEMV; lane = lane-ordered units for the CUDA-core GEMV")
+    ap.add_argument("--no-fused", action="store_true", help="one launch per GEMV instead of one persistent launch per step")
     ap.add_argument("--no-prefetch", action="store_true", help="do not name the next matrix in each GEMV call (no L2 prefetch)")
     ap.add_argument("--tokens", type=int, default=256, help="rows of the prefill workload (16..256, multiple of 16)")
     args = ap.parse_args()
@@ -557,7 +559,7 @@ def main():
 
     note("building the stack")
     handle, stack, rank_bytes = build_stack(model, args.batch, rank, world, local, args.layout,
-                                            prefetch_next=not args.no_prefetch)
+                                            prefetch_next=not args.no_prefetch, fused=not args.no_fused)
     note("capturing")
     stack.capture()
     note("captured")

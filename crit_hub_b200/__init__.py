@@ -57,6 +57,10 @@ class Shard(C.Structure):
     _fields_ = [("n0", C.c_int64), ("n1", C.c_int64), ("k0", C.c_int64), ("k1", C.c_int64)]
 
 
+class _Job(C.Structure):
+    _fields_ = [("w", C.c_void_p), ("x", C.c_void_p), ("y", C.c_void_p), ("y_dtype", C.c_int32), ("flags", C.c_int32)]
+
+
 class _DevStatus(C.Structure):
     _fields_ = [("code", C.c_int32), ("where", C.c_int32), ("block", C.c_int32), ("extra", C.c_int32)]
 
@@ -104,6 +108,9 @@ def _load() -> C.CDLL:
     L.qgemv_weight_bytes.restype = i64
     L.qgemv_weight_bytes.argtypes = [vp]
     L.qgemv_gemv.argtypes = [vp, vp, vp, i32, vp, i32, vp]
+    L.qgemv_sequence_create.argtypes = [vp, C.POINTER(_Job), i32, i32, C.POINTER(vp)]
+    L.qgemv_sequence_run.argtypes = [vp, vp, vp]
+    L.qgemv_sequence_destroy.argtypes = [vp, vp]
     L.qgemv_gemv_prefetch.argtypes = [vp, vp, vp, i32, vp, i32, vp, vp]
     L.qgemv_gemm_skinny.argtypes = [vp, vp, vp, i32, vp, i32, i32, vp]
     L.qgemv_gemm_skinny_plan.argtypes = [i32, i64, i64, i32, i32, C.POINTER(SkinnyPlan)]
@@ -213,6 +220,21 @@ class Weight:
             self._ptr = None
 
 
+class Sequence:
+    """A job list resident on the device (qgemv_sequence): run() launches it as one persistent kernel."""
+
+    def __init__(self, owner: "QGemv", ptr: int, n_jobs: int, B: int):
+        self._owner, self._ptr, self.n_jobs, self.B = owner, ptr, n_jobs, B
+
+    def run(self, stream: int = 0) -> None:
+        _check(_load().qgemv_sequence_run(self._owner._ptr, self._ptr, stream), "sequence_run")
+
+    def destroy(self) -> None:
+        if self._ptr:
+            _load().qgemv_sequence_destroy(self._owner._ptr, self._ptr)
+            self._ptr = None
+
+
 class QGemv:
     """One library handle on one device."""
 
@@ -265,6 +287,16 @@ class QGemv:
         else:
             _check(_load().qgemv_gemv_prefetch(self._ptr, w._ptr, x_ptr, B, y_ptr, y_dtype, next_weight._ptr,
                                                stream), "gemv")
+
+    def sequence(self, jobs: list[tuple[Weight, int, int, int]], B: int) -> "Sequence":
+        """jobs: (weight, x_ptr, y_ptr, y_dtype) in execution order; one persistent launch runs them all,
+        each job free to read what the one before it wrote.  NVFP4_TC weights only."""
+        arr = (_Job * len(jobs))()
+        for i, (w, x_ptr, y_ptr, y_dtype) in enumerate(jobs):
+            arr[i] = _Job(w._ptr, x_ptr, y_ptr, y_dtype, 0)
+        q = C.c_void_p()
+        _check(_load().qgemv_sequence_create(self._ptr, arr, len(jobs), B, C.byref(q)), "sequence_create")
+        return Sequence(self, q.value, len(jobs), B)
 
     def gemm_skinny(self, w: Weight, x_ptr: int, M: int, y_ptr: int, y_dtype: int = OUT_BF16,
                     act_mode: int = ACT_A16_EXACT, stream: int = 0) -> None:

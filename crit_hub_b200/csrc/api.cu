@@ -15,6 +15,7 @@
 #include "gemv_stream.cuh"
 #include "gemm_skinny.cuh"
 #include "gemv_tc.cuh"
+#include "gemv_seq.cuh"
 #include "moe_stream.cuh"
 #include "tp_allreduce.cuh"
 #include "qgemv_layout.h"
@@ -39,6 +40,15 @@ struct qgemv_handle {
     // tensor-core GEMV: split-K hand-over slots (two per CTA, [8][128] pairs {fp32, flag}), all zero between launches
     float* tc_ws;
     unsigned long long* tc_trace;  // caller's device buffer for phase timestamps, or null
+    unsigned int* seq_barrier;     // grid-wide arrival counter of the GEMV-sequence kernel, zero between launches
+    size_t tc_ws_bytes;
+};
+
+struct qgemv_sequence {
+    qg::SeqJob* dev_jobs;
+    int n_jobs, B;
+    int grid, npad, x_slots, ring, stage_items;
+    size_t smem;
 };
 
 struct qgemv_weight {
@@ -80,6 +90,7 @@ int64_t default_spin(const qgemv_handle* h) {
 }
 
 thread_local int g_launch_cluster = 1;  // thread-block cluster size of the next launch() (1: none)
+thread_local bool g_launch_cooperative = false;  // the next launch()'s CTAs wait on one another: all co-resident
 
 template <typename... KArgs, typename... Args>
 cudaError_t launch(const qgemv_handle* h, void (*kernel)(KArgs...), dim3 grid, dim3 block,
@@ -90,8 +101,14 @@ cudaError_t launch(const qgemv_handle* h, void (*kernel)(KArgs...), dim3 grid, d
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[2];
+    cudaLaunchAttribute attr[3];
     int n_attr = 0;
+    if (g_launch_cooperative) {
+        attr[n_attr].id = cudaLaunchAttributeCooperative;
+        attr[n_attr].val.cooperative = 1;
+        ++n_attr;
+        g_launch_cooperative = false;
+    }
     if (h->cfg.use_pdl) {
         attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
@@ -347,9 +364,11 @@ int qgemv_init(const qgemv_config* cfg, qgemv_handle** out) {
     for (int i = 0; i < qg::kTpMaxWorld; ++i) h->tp_peer[i] = nullptr;
     h->gs_ws = nullptr, h->gs_ws_bytes = 0;
     h->chunk_ws = nullptr;
-    h->tc_ws = nullptr, h->tc_trace = nullptr;
+    h->tc_ws = nullptr, h->tc_trace = nullptr, h->seq_barrier = nullptr;
     const size_t tc_ws_bytes = size_t(2) * size_t(std::max(h->sm_count, cfg->grid_override)) * 1024 * 8;
+    h->tc_ws_bytes = tc_ws_bytes;
     if (cudaMalloc(&h->tc_ws, tc_ws_bytes) != cudaSuccess || cudaMemset(h->tc_ws, 0, tc_ws_bytes) != cudaSuccess ||
+        cudaMalloc(&h->seq_barrier, 256) != cudaSuccess || cudaMemset(h->seq_barrier, 0, 256) != cudaSuccess ||
         cudaMalloc(&h->chunk_ws, kChunkWsBytes) != cudaSuccess ||
         cudaMalloc(&h->status_dev, 4 * sizeof(int32_t)) != cudaSuccess ||
         cudaMemset(h->status_dev, 0, 4 * sizeof(int32_t)) != cudaSuccess) {
@@ -374,6 +393,9 @@ int qgemv_init(const qgemv_config* cfg, qgemv_handle** out) {
         cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_NVFP4, false, 1, true>, dyn, qg::SSmem::total<QGEMV_FMT_NVFP4>()) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8, true, 1, true>, dyn, qg::SSmem::total<QGEMV_FMT_FP8>()) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8, false, 1, true>, dyn, qg::SSmem::total<QGEMV_FMT_FP8>()) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_seq_kernel<2>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_seq_kernel<4>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_seq_kernel<8>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_tc_kernel<1>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_tc_kernel<2>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_tc_kernel<4>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
@@ -398,6 +420,7 @@ int qgemv_destroy(qgemv_handle* h) {
     cudaFree(h->gs_ws);
     cudaFree(h->chunk_ws);
     cudaFree(h->tc_ws);
+    cudaFree(h->seq_barrier);
     cudaFree(h->status_dev);
     delete h;
     return QGEMV_OK;
@@ -493,6 +516,96 @@ int64_t qgemv_weight_bytes(const qgemv_weight* w) {
     if (!w) return QGEMV_ERR_INVALID_ARG;
     if (w->fmt != QGEMV_FMT_FP8) return w->N * w->K / 2 + w->N * w->K / 16 + 4;
     return w->N * w->K + 4 * w->N;
+}
+
+int qgemv_sequence_create(qgemv_handle* h, const qgemv_job* jobs, int n_jobs, int B, qgemv_sequence** out) {
+    if (!h || !jobs || !out || n_jobs < 1) return QGEMV_ERR_INVALID_ARG;
+    *out = nullptr;
+    if (B < 1 || B > QGEMV_MAX_BATCH) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+    const int grid = gemv_grid(h);
+    if (grid > h->sm_count) return QGEMV_ERR_UNSUPPORTED_SHAPE;  // the CTAs wait on one another: one per SM at most
+    std::vector<qg::SeqJob> tab(static_cast<size_t>(n_jobs));
+    int64_t x_slots = 1;
+    for (int i = 0; i < n_jobs; ++i) {
+        const qgemv_job& jb = jobs[i];
+        if (!jb.w || !jb.x || !jb.y) return QGEMV_ERR_INVALID_ARG;
+        if (jb.w->fmt != QGEMV_FMT_NVFP4_TC || jb.w->n_stack != 1) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+        if (jb.y_dtype != QGEMV_OUT_BF16 && jb.y_dtype != QGEMV_OUT_F32) return QGEMV_ERR_INVALID_ARG;
+        if ((reinterpret_cast<uintptr_t>(jb.x) & 15u) != 0) return QGEMV_ERR_INVALID_ARG;
+        qg::SeqJob& sj = tab[size_t(i)];
+        std::memset(&sj, 0, sizeof sj);
+        sj.payload = jb.w->dev_blob + QG_HEADER_BYTES + jb.w->aux_bytes;
+        sj.x = static_cast<const uint16_t*>(jb.x);
+        sj.y = jb.y;
+        sj.tensor_scale = jb.w->host_tensor_scale[0];
+        sj.N = int32_t(jb.w->N), sj.K = int32_t(jb.w->K);
+        sj.tiles = int32_t(jb.w->n_panels / 8), sj.kt = int32_t(jb.w->units);
+        sj.x_stride = int32_t(jb.w->K);
+        sj.y_dtype = jb.y_dtype;
+        sj.flags = jb.flags;
+        const int64_t total = int64_t(sj.tiles) * sj.kt;
+        x_slots = std::max(x_slots, std::min<int64_t>(sj.kt, (total + grid - 1) / grid));
+    }
+    qgemv_sequence* q = new (std::nothrow) qgemv_sequence;
+    if (!q) return QGEMV_ERR_INVALID_ARG;
+    q->dev_jobs = nullptr;
+    q->n_jobs = n_jobs, q->B = B, q->grid = grid;
+    q->npad = (8 * B + 15) / 16 * 16;
+    q->x_slots = int(x_slots);
+    const int si = h->cfg.tc_stage_items;
+    q->stage_items = si >= 8 ? 8 : (si >= 4 ? 4 : (si >= 2 ? 2 : 4));
+    const int base = qg::SeqSmem::ring_off(q->x_slots, q->npad);
+    const int cap = (h->cfg.tc_smem_kb > 0 ? std::min(h->cfg.tc_smem_kb, 227) : 227) * 1024;
+    int ring = (cap - base) / (q->stage_items * qg::kTcItemBytes);
+    ring = std::min({ring, qg::kTcMaxRing, qg::SeqSmem::max_ring_items(q->npad) / q->stage_items});
+    if (ring < 2) {
+        delete q;
+        return QGEMV_ERR_UNSUPPORTED_SHAPE;  // the digit planes of one job leave no room for a ring: call qgemv_gemv per job
+    }
+    q->ring = ring;
+    q->smem = size_t(qg::SeqSmem::total(q->x_slots, q->npad, ring, q->stage_items));
+    if (cudaSetDevice(h->cfg.device) != cudaSuccess || cudaMalloc(&q->dev_jobs, size_t(n_jobs) * sizeof(qg::SeqJob)) != cudaSuccess ||
+        cudaMemcpy(q->dev_jobs, tab.data(), size_t(n_jobs) * sizeof(qg::SeqJob), cudaMemcpyHostToDevice) != cudaSuccess) {
+        g_last_cuda_error = cudaGetLastError();
+        cudaFree(q->dev_jobs);
+        delete q;
+        return QGEMV_ERR_CUDA;
+    }
+    *out = q;
+    return QGEMV_OK;
+}
+
+int qgemv_sequence_destroy(qgemv_handle* h, qgemv_sequence* q) {
+    if (!h || !q) return QGEMV_ERR_INVALID_ARG;
+    cudaSetDevice(h->cfg.device);
+    cudaFree(q->dev_jobs);
+    delete q;
+    return QGEMV_OK;
+}
+
+int qgemv_sequence_run(qgemv_handle* h, const qgemv_sequence* q, void* stream) {
+    if (!h || !q) return QGEMV_ERR_INVALID_ARG;
+    qg::SeqParams P;
+    std::memset(&P, 0, sizeof P);
+    P.jobs = q->dev_jobs;
+    P.ws = h->tc_ws;
+    P.barrier = h->seq_barrier;
+    P.status = h->status_dev;
+    P.spin_limit = default_spin(h);
+    P.n_jobs = q->n_jobs;
+    P.B = q->B;
+    P.npad = q->npad;
+    P.ring = q->ring;
+    P.x_slots = q->x_slots;
+    P.debug = h->cfg.debug;
+    P.trace = h->tc_trace;
+    const dim3 g(unsigned(q->grid)), blk(qg::kTcThreads);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    g_launch_cooperative = true;
+    const cudaError_t err = q->stage_items == 2   ? launch(h, qg::gemv_seq_kernel<2>, g, blk, q->smem, st, P)
+                            : q->stage_items == 4 ? launch(h, qg::gemv_seq_kernel<4>, g, blk, q->smem, st, P)
+                                                  : launch(h, qg::gemv_seq_kernel<8>, g, blk, q->smem, st, P);
+    return err == cudaSuccess ? QGEMV_OK : QGEMV_ERR_CUDA;
 }
 
 int qgemv_gemv(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, int B, void* y,
@@ -772,7 +885,12 @@ int qgemv_last_device_status(qgemv_handle* h, void* stream, qgemv_dev_status* ou
     out->where = v[1];
     out->block = v[2];
     out->extra = v[3];
-    if (v[0] != 0) QG_CUDA(cudaMemset(h->status_dev, 0, sizeof v));
+    if (v[0] != 0) {
+        QG_CUDA(cudaMemset(h->status_dev, 0, sizeof v));
+        // a kernel that gave up may have left hand-over flags and the arrival counter behind
+        QG_CUDA(cudaMemset(h->tc_ws, 0, h->tc_ws_bytes));
+        QG_CUDA(cudaMemset(h->seq_barrier, 0, 256));
+    }
     return QGEMV_OK;
 }
 

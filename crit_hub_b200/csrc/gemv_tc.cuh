@@ -235,7 +235,8 @@ __device__ __forceinline__ void tc_digits8(uint4 v, float sf, uint32_t (&out)[8]
 // The tile's first contributor gathers the parts of CTAs c_lo + 1 .. c_hi, two activation rows at a
 // time with the loads of up to eight parts in flight together, re-polling -- bounded -- what is
 // missing, then adds them to `val` in CTA order and clears the slots it has read.
-__device__ __forceinline__ bool tc_collect(const TcParams& P, float (&val)[8], int Bl, int32_t c_lo, int32_t c_hi, int row,
+template <class PT>
+__device__ __forceinline__ bool tc_collect(const PT& P, float (&val)[8], int Bl, int32_t c_lo, int32_t c_hi, int row,
                                            volatile int* abort_flag) {
     constexpr int KP = 8;
     uint64_t t_wait = 0;  // read on the first miss only: %globaltimer is a slow register

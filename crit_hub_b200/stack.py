@@ -31,8 +31,11 @@ class LayerStack:
     """Owns an activation arena [sum B*K] bf16 and an output arena [sum B*N]; one GEMV per weight."""
 
     def __init__(self, handle: QGemv, weights: list[Weight], batch: int, out_dtype: int = OUT_BF16,
-                 device: int = 0, prefetch_next: bool = False, after_call=None):
+                 device: int = 0, prefetch_next: bool = False, after_call=None, fused: bool = False):
         self.handle, self.batch, self.out_dtype = handle, batch, out_dtype
+        # fused: the whole list as ONE persistent launch (qgemv_sequence_*; tensor-core layout only, no hooks)
+        self.fused = fused and after_call is None
+        self.sequence = None
         # after_call(i): optional hook enqueued on the same stream right after GEMV i (and captured
         # with it), e.g. the all-reduce of a row-parallel projection's partial outputs
         self.after_call = after_call
@@ -79,6 +82,12 @@ class LayerStack:
         xe, ye = self.x_dev.element_size(), self.y_dev.element_size()
         xb, yb = self.x_dev.data_ptr(), self.y_dev.data_ptr()
         n = len(self.calls)
+        if self.fused:
+            if self.sequence is None:
+                self.sequence = self.handle.sequence(
+                    [(c.weight, xb + c.x_off * xe, yb + c.y_off * ye, self.out_dtype) for c in self.calls], self.batch)
+            self.sequence.run(stream_handle)
+            return
         for i, c in enumerate(self.calls):
             nxt = self.calls[(i + 1) % n].weight if self.prefetch_next and n > 1 else None
             self.handle.gemv(c.weight, xb + c.x_off * xe, self.batch, yb + c.y_off * ye, self.out_dtype,
@@ -117,7 +126,7 @@ class LayerStack:
 
     @property
     def launches_per_step(self) -> int:
-        return len(self.calls)
+        return 1 if self.fused else len(self.calls)
 
 
 def llama_layer_shapes(hidden: int, q_heads: int, kv_heads: int, head_dim: int, inter: int):

@@ -170,6 +170,32 @@ int qgemv_gemv(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, int B
 int qgemv_gemv_prefetch(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, int B, void* y,
                         int y_dtype, const qgemv_weight* next, void* stream);
 
+/* ---- a sequence of GEMVs as one launch --------------------------------------------------------
+ * The projections of a decode step, in order, as ONE persistent kernel ("one CUDA graph per round",
+ * tools/fixtures/engines/crit-labs/mtp4-nvfp4-mma/card.yaml:75, taken one step further: one launch).
+ * Job i computes y_i = W_i x_i exactly as qgemv_gemv would; job i + 1 may read anything job i wrote
+ * (a grid-wide barrier separates them), so x_{i+1} may be y_i or a function of it computed by the
+ * caller earlier.  While the CTAs finish one job and convert the next one's activations, the
+ * weights of the following jobs keep streaming into shared memory, so HBM does not idle at the
+ * boundaries the way it does between separate launches.
+ * Weights: QGEMV_FMT_NVFP4_TC only.  All jobs share the batch size B (1..8).  The job list is
+ * copied to the device by qgemv_sequence_create (which allocates); qgemv_sequence_run launches,
+ * allocates nothing and may be captured into a CUDA graph.  The kernel's CTAs wait on one another:
+ * the launch is cooperative and takes every SM (grid_override above the SM count is refused).
+ * QGEMV_ERR_UNSUPPORTED_SHAPE when the activations of one job (B * K digit planes) leave no room
+ * for a weight ring in shared memory: call qgemv_gemv per job then. */
+typedef struct qgemv_job {
+    const qgemv_weight* w;
+    const void* x;   /* device bf16 [B][K], 16-byte aligned */
+    void* y;         /* device [B][N] */
+    int32_t y_dtype; /* QGEMV_OUT_BF16 or QGEMV_OUT_F32 */
+    int32_t flags;   /* 0 (reserved) */
+} qgemv_job;
+typedef struct qgemv_sequence qgemv_sequence;
+int qgemv_sequence_create(qgemv_handle* h, const qgemv_job* jobs, int n_jobs, int B, qgemv_sequence** out);
+int qgemv_sequence_run(qgemv_handle* h, const qgemv_sequence* seq, void* stream);
+int qgemv_sequence_destroy(qgemv_handle* h, qgemv_sequence* seq);
+
 /* ---- tensor-parallel exchange -------------------------------------------------------------------
  * Not in the registry (every listed engine runs on one GPU, engines/crit-labs/mtp5-nvfp4-drafts/
  * card.yaml:100); needed for the row-parallel projections (o, down) of a model sharded over the

@@ -242,3 +242,116 @@ def test_tc_refused_by_other_entry_points(qg, handle):
     with pytest.raises(qg.QgemvError) as e:
         handle.load_stacked(blobs)
     assert e.value.status == qg.ERR_UNSUPPORTED_SHAPE
+
+
+# ---- a sequence of GEMVs as one persistent launch -------------------------------------------------
+def _chain(qg, h, shapes, B, seed):
+    """Weights W_i: N_i x K_i with K_{i+1} = N_i; device buffers; the job list x_{i+1} = y_i (bf16)."""
+    import torch
+    ws, mats = [], []
+    for i, (N, K) in enumerate(shapes):
+        codes, scales, ts = O.make_nvfp4(N, K, seed=seed + i, ts=0.02)   # small scale keeps the chain finite
+        mats.append((codes, scales, ts))
+        ws.append(h.load(qg.pack(qg.FMT_NVFP4_TC, codes, scales, ts)))
+    x0 = O.make_x(B, shapes[0][1], seed=seed + 100)
+    bufs = [U.dev_u16(x0)] + [torch.full((B, N), float("nan"), dtype=torch.bfloat16, device="cuda") for N, _ in shapes]
+    jobs = [(ws[i], bufs[i].data_ptr(), bufs[i + 1].data_ptr(), qg.OUT_BF16) for i in range(len(shapes))]
+    return ws, mats, x0, bufs, jobs
+
+
+@pytest.mark.parametrize("B", [1, 3, 8])
+def test_sequence_chain(qg, handle, B):
+    """Each job reads what the one before it wrote: parity of every link against the oracle fed with
+    the previous link's device result, bit-equality with one launch per GEMV, and a second run."""
+    import torch
+    shapes = [(2048, 1024), (512, 2048), (4096, 512), (144, 4096)]
+    ws, mats, x0, bufs, jobs = _chain(qg, handle, shapes, B, seed=40)
+    seq = handle.sequence(jobs, B)
+    for rep in range(2):
+        for b in bufs[1:]:
+            b.fill_(float("nan"))
+        seq.run()
+        torch.cuda.synchronize()
+        U.status_ok(handle)
+        xin = x0
+        for i, (codes, scales, ts) in enumerate(mats):
+            got = bufs[i + 1].view(torch.int16).cpu().numpy().view(np.uint16)
+            ref = O.gemv_nvfp4_f64(codes, scales, ts, xin)
+            assert not np.isnan(O.bf16_decode(got)).any(), (rep, i)
+            assert O.rel_l2(O.bf16_decode(got), ref) < TOL_BF16, (rep, i)
+            xin = got
+    # the same chain, one launch per GEMV: same split along K, same bits
+    seq_out = [b.clone() for b in bufs[1:]]
+    for i, (w, xp, yp, dt) in enumerate(jobs):
+        bufs[i + 1].fill_(float("nan"))
+        handle.gemv(w, xp, B, yp, dt)
+    torch.cuda.synchronize()
+    for a, b in zip(seq_out, bufs[1:]):
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+    seq.destroy()
+    for w in ws:
+        w.unload()
+
+
+def test_sequence_in_a_graph_and_small_jobs(qg, handle):
+    """Jobs with fewer items than CTAs, fp32 outputs, replayed from a CUDA graph."""
+    import torch
+    B = 2
+    shapes = [(128, 64), (16, 128), (300, 16)]
+    codes_l, ws, xs, ys = [], [], [], []
+    for i, (N, K) in enumerate(shapes):
+        codes, scales, ts = O.make_nvfp4(N, K, seed=60 + i)
+        codes_l.append((codes, scales, ts))
+        ws.append(handle.load(qg.pack(qg.FMT_NVFP4_TC, codes, scales, ts)))
+        xs.append(O.make_x(B, K, seed=70 + i))
+        ys.append(torch.full((B, N), float("nan"), dtype=torch.float32, device="cuda"))
+    xd = [U.dev_u16(x) for x in xs]
+    seq = handle.sequence([(ws[i], xd[i].data_ptr(), ys[i].data_ptr(), qg.OUT_F32) for i in range(len(shapes))], B)
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        seq.run(st.cuda_stream)
+    st.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=st):
+        seq.run(torch.cuda.current_stream().cuda_stream)
+    for y in ys:
+        y.fill_(float("nan"))
+    with torch.cuda.stream(st):
+        g.replay()
+        g.replay()
+    st.synchronize()
+    U.status_ok(handle)
+    for (codes, scales, ts), x, y in zip(codes_l, xs, ys):
+        assert O.rel_l2(y.cpu().numpy(), O.gemv_nvfp4_f64(codes, scales, ts, x)) < TOL_F32
+    seq.destroy()
+    for w in ws:
+        w.unload()
+
+
+def test_sequence_bounded_wait_reports_timeout(qg):
+    """Host-set injection (no weight copy is ever issued): every wait of the persistent kernel runs
+    out, the CTAs leave together, the status word says why, and the handle works afterwards."""
+    import torch
+    h = qg.QGemv(device=0, spin_limit=2000, inject_drop_copies=True)
+    ws, mats, x0, bufs, jobs = _chain(qg, h, [(1024, 1024), (512, 1024)], 1, seed=80)
+    seq = h.sequence(jobs, 1)
+    seq.run()
+    torch.cuda.synchronize()
+    st = h.device_status()
+    assert st.code == qg.ERR_TIMEOUT and 71 <= st.where <= 76
+    seq.destroy()
+    for w in ws:
+        w.unload()
+    h.close()
+    h2 = qg.QGemv(device=0)
+    ws, mats, x0, bufs, jobs = _chain(qg, h2, [(1024, 1024), (512, 1024)], 1, seed=80)
+    seq = h2.sequence(jobs, 1)
+    seq.run()
+    torch.cuda.synchronize()
+    assert h2.device_status().code == 0
+    got = bufs[1].view(torch.int16).cpu().numpy().view(np.uint16)
+    assert O.rel_l2(O.bf16_decode(got), O.gemv_nvfp4_f64(*mats[0], x0)) < TOL_BF16
+    seq.destroy()
+    for w in ws:
+        w.unload()
+    h2.close()
