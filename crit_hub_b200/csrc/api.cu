@@ -40,7 +40,8 @@ struct qgemv_handle {
     // tensor-core GEMV: split-K hand-over slots (two per CTA, [8][128] pairs {fp32, flag}), all zero between launches
     float* tc_ws;
     unsigned long long* tc_trace;  // caller's device buffer for phase timestamps, or null
-    unsigned int* seq_barrier;     // grid-wide arrival counter of the GEMV-sequence kernel, zero between launches
+    unsigned int* seq_barrier;     // arrival / leave counters of the GEMV-sequence kernel, zero between launches
+    float* seq_parts;              // its parts buffer: [2][2 * grid][8][128] fp32
     size_t tc_ws_bytes;
 };
 
@@ -364,11 +365,12 @@ int qgemv_init(const qgemv_config* cfg, qgemv_handle** out) {
     for (int i = 0; i < qg::kTpMaxWorld; ++i) h->tp_peer[i] = nullptr;
     h->gs_ws = nullptr, h->gs_ws_bytes = 0;
     h->chunk_ws = nullptr;
-    h->tc_ws = nullptr, h->tc_trace = nullptr, h->seq_barrier = nullptr;
+    h->tc_ws = nullptr, h->tc_trace = nullptr, h->seq_barrier = nullptr, h->seq_parts = nullptr;
     const size_t tc_ws_bytes = size_t(2) * size_t(std::max(h->sm_count, cfg->grid_override)) * 1024 * 8;
     h->tc_ws_bytes = tc_ws_bytes;
     if (cudaMalloc(&h->tc_ws, tc_ws_bytes) != cudaSuccess || cudaMemset(h->tc_ws, 0, tc_ws_bytes) != cudaSuccess ||
         cudaMalloc(&h->seq_barrier, 256) != cudaSuccess || cudaMemset(h->seq_barrier, 0, 256) != cudaSuccess ||
+        cudaMalloc(&h->seq_parts, tc_ws_bytes) != cudaSuccess ||
         cudaMalloc(&h->chunk_ws, kChunkWsBytes) != cudaSuccess ||
         cudaMalloc(&h->status_dev, 4 * sizeof(int32_t)) != cudaSuccess ||
         cudaMemset(h->status_dev, 0, 4 * sizeof(int32_t)) != cudaSuccess) {
@@ -421,6 +423,7 @@ int qgemv_destroy(qgemv_handle* h) {
     cudaFree(h->chunk_ws);
     cudaFree(h->tc_ws);
     cudaFree(h->seq_barrier);
+    cudaFree(h->seq_parts);
     cudaFree(h->status_dev);
     delete h;
     return QGEMV_OK;
@@ -542,7 +545,17 @@ int qgemv_sequence_create(qgemv_handle* h, const qgemv_job* jobs, int n_jobs, in
         sj.tiles = int32_t(jb.w->n_panels / 8), sj.kt = int32_t(jb.w->units);
         sj.x_stride = int32_t(jb.w->K);
         sj.y_dtype = jb.y_dtype;
-        sj.flags = jb.flags;
+        sj.flags = 0;
+        if (i > 0) {
+            // does this job read or overwrite the previous job's output?  Then that output must be
+            // complete (its split tiles added up) before this job starts.
+            const qgemv_job& pj = jobs[i - 1];
+            const auto lo = [](const void* p) { return reinterpret_cast<uintptr_t>(p); };
+            const uintptr_t py0 = lo(pj.y), py1 = py0 + size_t(B) * size_t(pj.w->N) * (pj.y_dtype == QGEMV_OUT_F32 ? 4 : 2);
+            const uintptr_t x0 = lo(jb.x), x1 = x0 + size_t(B) * size_t(jb.w->K) * 2;
+            const uintptr_t y0 = lo(jb.y), y1 = y0 + size_t(B) * size_t(jb.w->N) * (jb.y_dtype == QGEMV_OUT_F32 ? 4 : 2);
+            if ((x0 < py1 && py0 < x1) || (y0 < py1 && py0 < y1)) sj.flags |= 1;
+        }
         const int64_t total = int64_t(sj.tiles) * sj.kt;
         x_slots = std::max(x_slots, std::min<int64_t>(sj.kt, (total + grid - 1) / grid));
     }
@@ -588,7 +601,7 @@ int qgemv_sequence_run(qgemv_handle* h, const qgemv_sequence* q, void* stream) {
     qg::SeqParams P;
     std::memset(&P, 0, sizeof P);
     P.jobs = q->dev_jobs;
-    P.ws = h->tc_ws;
+    P.ws = h->seq_parts;
     P.barrier = h->seq_barrier;
     P.status = h->status_dev;
     P.spin_limit = default_spin(h);

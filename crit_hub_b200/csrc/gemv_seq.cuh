@@ -14,11 +14,18 @@
 // kind::mxf4nvf4, activations as eight E2M1 digit planes scaled per CTA range, split along K over
 // the CTAs with a deterministic hand-over to each row tile's first contributor.
 //
-// Between jobs: every CTA, once its own results of job j are stored (and the hand-over slots it
-// read are cleared), bumps a global counter with release semantics; before converting the
-// activations of job j+1 one thread per CTA polls -- bounded -- until all CTAs have arrived
-// (acquire), then the CTA's converting warps synchronise.  The CTAs wait on one another, so the
-// launch is cooperative (all CTAs co-resident).
+// Between jobs: every CTA, once its own results of job j are stored, bumps a global counter with
+// release semantics; before converting the activations of job j+1 one thread per CTA polls --
+// bounded -- until all CTAs have arrived (acquire), then the CTA's converting warps synchronise.
+// The CTAs wait on one another, so the launch is cooperative (all CTAs co-resident).
+//
+// Split along K without a wait: a CTA that holds only part of a row tile stores its fp32 partial
+// sums in its own slot of a parts buffer (double-buffered by job parity) and moves on.  The tile's
+// first contributor adds the parts in CTA order -- a fixed order -- and stores the rows AFTER the
+// barrier, when every part is known to be there, and after it has handed the next job's digit
+// planes to the tensor core: the sum is off the critical path and polls nothing.  Only when the
+// next job reads or overwrites this job's output (the host compares the address ranges) is the sum
+// done first, followed by one more barrier.
 //
 // Warp roles as in gemv_tc.cuh: 0 producer, 1 MMA issuer, 2-9 digit planes + epilogues.
 #pragma once
@@ -35,15 +42,15 @@ struct SeqJob {               // 64 bytes, device memory
     int32_t tiles, kt;        // ceil(N / 128), ceil(K / 64)
     int32_t x_stride;         // elements between activation rows
     int32_t y_dtype;
-    int32_t flags;            // reserved
+    int32_t flags;            // bit 0: this job's x or y overlaps the previous job's y -- finish that one first
     int32_t pad;
 };
 static_assert(sizeof(SeqJob) == 64, "SeqJob layout");
 
 struct SeqParams {
     const SeqJob* jobs;
-    float* ws;                  // hand-over slots: (2 * cta) of [8][128] pairs {fp32, flag}, all zero between launches
-    unsigned int* barrier;      // grid-wide arrival counter, zero between launches
+    float* ws;                  // parts buffer: [job parity][2 * cta + which][8][128] fp32 partial sums
+    unsigned int* barrier;      // [0] grid-wide arrival counter, [1] CTAs that have left; both zero between launches
     int32_t* status;
     int64_t spin_limit;
     int32_t n_jobs;
@@ -51,7 +58,7 @@ struct SeqParams {
     int32_t ring;
     int32_t x_slots;            // item slots of digit planes in shared memory (the largest any job needs)
     int32_t debug;
-    unsigned long long* trace;  // optional diagnostics: per CTA, per job 4 stamps (see qgemv_set_trace), or null
+    unsigned long long* trace;  // optional diagnostics: per CTA, per job 8 stamps (see qgemv_set_trace), or null
 };
 
 struct SeqSmem {
@@ -239,6 +246,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_seq_kernel(const SeqParams
                     break;
                 }
                 tc_fence_after();
+                if (P.trace) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 3] = globaltimer_ns();
                 if (j == 0) tc_cp_sf2(tmem_sfb, sf_lo | (((sbase + SeqSmem::kSfb) >> 4) & 0x3FFFu), sf_hi);
                 for (; ok && have; have = wk.next(sg)) {
                     // the accumulator is free once the epilogue of the segment before last has read it
@@ -256,13 +264,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_seq_kernel(const SeqParams
                     if (slot < 0) slot += kt_len;
                     uint32_t x_lo = x_lo0 + uint32_t(slot) * xslot16;
                     for (int32_t left = sg.u1 - sg.u0; left > 0; left -= S) {
+                        // (the stage was written through the async proxy and is read through it: the
+                        // barrier's acquire is all the ordering the MMAs need -- no tcgen05 fence here,
+                        // which costs this thread a few hundred cycles per stage)
                         if (!mbar_wait_probe(bar_full, full_par, P.spin_limit)) {
                             report(P.status, QGEMV_ERR_TIMEOUT, 74, mi);
                             *abort_flag = 1;
                             ok = false;
                             break;
                         }
-                        tc_fence_after();
                         if (left >= S) {
 #pragma unroll
                             for (int i = 0; i < S; ++i) tc_cp_sf2(sfa + 4u * i, sf_lo | (item16 + kCode16 + kItem16 * i), sf_hi);
@@ -279,6 +289,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_seq_kernel(const SeqParams
                         acc = 1;
                         x_lo += xslot16 * S;
                         tc_commit(bar_empty);  // the stage is reusable once these retire
+                        if (P.trace && P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 7] == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 7] = globaltimer_ns();
                         ++mi;
                         item16 += stage16, sfa += 4u * S, bar_full += 8, bar_empty += 8;
                         if (item16 == ring_end16) {
@@ -290,6 +301,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_seq_kernel(const SeqParams
                     tc_commit(sbase + SeqSmem::kBarDFull + 8 * (nseg & 1));
                     ++nseg;
                 }
+                if (P.trace) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 4] = globaltimer_ns();
                 job = next;
             }
             *n_consumed = mi;
@@ -313,6 +325,63 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_seq_kernel(const SeqParams
         pdl_wait();  // whatever ran before this launch has finished with x, y and the hand-over slots
         uint32_t nseg = 0;
         bool ok = true;  // this warp's own view; leaving the job loop is decided for all eight warps together
+        unsigned int n_bar = 0;  // grid-wide barriers so far: the same number on every CTA
+        auto grid_arrive = [&]() {  // after a barrier of the eight warps: this CTA's stores are ordered before it
+            if (ct == 0) red_release_add(P.barrier, 1u);
+            ++n_bar;
+        };
+        auto grid_wait = [&](int j) {
+            if (ct == 0) {
+                const unsigned int target = n_bar * unsigned(grid);
+                uint64_t t0 = 0;
+                for (int64_t it = 0; ld_acquire(P.barrier) < target; ++it) {
+                    if (it == 0) t0 = globaltimer_ns();
+                    if (it >= P.spin_limit || ((it & 63) == 63 && globaltimer_ns() - t0 > 2000000000ull)) {
+                        report(P.status, QGEMV_ERR_TIMEOUT, 75, j);
+                        *abort_flag = 1;
+                        break;
+                    }
+                }
+            }
+        };
+        // The row tile of the job before, if this CTA is its first contributor and the tile was split:
+        // its rows are the sum of the parts, added here in CTA order once all of them are known to be stored.
+        struct {
+            bool valid;
+            int32_t tile, c_lo, c_hi, lo_slot, N, y_dtype, parity;
+            void* y;
+        } pend;
+        pend.valid = false;
+        auto finalize_pending = [&]() {
+            if (pend.valid && ct < 128) {
+                const int n = pend.tile * 128 + ct;
+                const float* parts = P.ws + size_t(pend.parity) * size_t(2 * grid) * 1024 + ct;
+                if (n < pend.N) {
+#pragma unroll
+                    for (int b = 0; b < 8; ++b) {
+                        if (b < Bl) {
+                            // eight parts' loads in flight together; the additions stay in CTA order
+                            float v = __ldcg(parts + size_t(pend.lo_slot) * 1024 + b * 128);
+                            for (int32_t cc = pend.c_lo + 1; cc <= pend.c_hi; cc += 8) {
+                                float t[8];
+#pragma unroll
+                                for (int z = 0; z < 8; ++z) t[z] = __ldcg(parts + size_t(2 * min(cc + z, pend.c_hi)) * 1024 + b * 128);
+#pragma unroll
+                                for (int z = 0; z < 8; ++z)
+                                    if (cc + z <= pend.c_hi) v += t[z];
+                            }
+                            const int64_t idx = int64_t(b) * pend.N + n;
+                            if (pend.y_dtype == QGEMV_OUT_F32) {
+                                static_cast<float*>(pend.y)[idx] = v;
+                            } else {
+                                static_cast<__nv_bfloat16*>(pend.y)[idx] = __float2bfloat16_rn(v);
+                            }
+                        }
+                    }
+                }
+            }
+            pend.valid = false;
+        };
         volatile int* decision = reinterpret_cast<volatile int*>(sq_smem + SeqSmem::kDecision);
         SeqJob job = seq_load_job(P.jobs);
         for (int j = 0; j < P.n_jobs; ++j) {
@@ -326,28 +395,25 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_seq_kernel(const SeqParams
             const int32_t n_items = r_end - r_begin;
             const int32_t xs0 = n_items >= kt_len ? 0 : r_begin % kt_len;
             const int32_t n_slots = n_items >= kt_len ? kt_len : n_items;
-            // ---- grid-wide barrier: every CTA has stored its results of job j - 1 ----
+            // ---- grid-wide barrier: every CTA has stored its results (or parts) of job j - 1 ----
             if (ct < 8 * kTcConvWarps) all_max[ct] = 0u;  // per-warp row maxima of the last job
-            if (j > 0) {
-                if (ct == 0) {
-                    const unsigned int target = unsigned(j) * unsigned(grid);
-                    uint64_t t0 = 0;
-                    for (int64_t it = 0; ld_acquire(P.barrier) < target; ++it) {
-                        if (it == 0) t0 = globaltimer_ns();
-                        if (it >= P.spin_limit || ((it & 63) == 63 && globaltimer_ns() - t0 > 2000000000ull)) {
-                            report(P.status, QGEMV_ERR_TIMEOUT, 75, j);
-                            *abort_flag = 1;
-                            break;
-                        }
-                    }
-                }
-            }
+            if (j > 0) grid_wait(j);
             // Named barriers have no time-out, so all eight warps must leave the job loop at the same
             // place: one thread samples the abort flag, everybody reads that sample after the barrier.
             if (ct == 0) *decision = *abort_flag;
             named_bar_sync(1, kTcConvThreads);
             if (*decision) break;
-            if (P.trace && ct == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 4 + 0] = globaltimer_ns();
+            if (j > 0 && (job.flags & 1)) {
+                // this job reads or overwrites what the previous one produced: finish that first
+                finalize_pending();
+                named_bar_sync(1, kTcConvThreads);
+                grid_arrive();
+                grid_wait(j);
+                if (ct == 0) *decision = *abort_flag;
+                named_bar_sync(1, kTcConvThreads);
+                if (*decision) break;
+            }
+            if (P.trace && ct == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 0] = globaltimer_ns();
             // ---- digit planes of the items this CTA multiplies in job j (see gemv_tc.cuh) ----
             const int n_work = n_slots * Bl * 8;
             constexpr int kKeep = 4;
@@ -422,7 +488,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_seq_kernel(const SeqParams
             fence_proxy_async_smem();  // the planes are read by the tensor core (async proxy)
             named_bar_sync(1, kTcConvThreads);
             if (ct == 0) mbar_arrive(sbase + SeqSmem::kBarXReady);
-            if (P.trace && ct == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 4 + 1] = globaltimer_ns();
+            if (P.trace && ct == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 1] = globaltimer_ns();
+            // the tensor core is busy with this job now: add up the split tile of the job before
+            finalize_pending();
+            if (P.trace && ct == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 6] = globaltimer_ns();
 
             // ---- epilogues of job j: group g takes the segments with (global) nseg % 2 == g ----
             float scale[8];
@@ -432,15 +501,23 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_seq_kernel(const SeqParams
             seq_walker(wk, total, kt_len, cta, gj);
             GsSeg sg;
             while (ok && wk.next(sg)) {
-                if (int(nseg & 1) != g) {
-                    ++nseg;
-                    continue;
-                }
                 const bool whole = sg.u0 == 0 && sg.u1 == kt_len;
-                int32_t c_lo = 0, c_hi = 0;
+                int32_t c_lo = 0, c_hi = 0, my_slot = 0;
                 if (!whole) {
                     c_lo = int32_t(cta_of(int64_t(sg.tile) * kt_len, total, gj));
                     c_hi = int32_t(cta_of(int64_t(sg.tile + 1) * kt_len - 1, total, gj));
+                    // every contributor after the first starts its range inside this tile (slot 0 of its
+                    // pair); the first one's range may have started in an earlier tile
+                    my_slot = cta == c_lo ? gs_slot(c_lo, sg.tile, kt_len, total, gj) : 2 * cta;
+                    if (cta == c_lo) {  // all eight warps note it, whichever group runs the segment
+                        pend.valid = true;
+                        pend.tile = sg.tile, pend.c_lo = c_lo, pend.c_hi = c_hi, pend.lo_slot = my_slot;
+                        pend.N = job.N, pend.y_dtype = job.y_dtype, pend.parity = j & 1, pend.y = job.y;
+                    }
+                }
+                if (int(nseg & 1) != g) {
+                    ++nseg;
+                    continue;
                 }
                 if (!__all_sync(0xFFFFFFFFu, mbar_wait_probe(sbase + SeqSmem::kBarDFull + 8 * g, (nseg >> 1) & 1, P.spin_limit))) {
                     if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 76, int(nseg));
@@ -449,6 +526,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_seq_kernel(const SeqParams
                     break;
                 }
                 tc_fence_after();
+                if (P.trace && lane == 0 && q == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 5] = globaltimer_ns();  // the last one stays
                 float val[8];
 #pragma unroll
                 for (int b = 0; b < 8; ++b) {
@@ -483,31 +561,33 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_seq_kernel(const SeqParams
                 };
                 if (whole) {
                     store_row(val);
-                } else if (cta != c_lo) {
-                    unsigned long long* slot = reinterpret_cast<unsigned long long*>(P.ws) + size_t(2 * cta) * 1024 + row;
+                } else {
+                    float* slot = P.ws + (size_t(j & 1) * size_t(2 * grid) + size_t(my_slot)) * 1024 + row;
 #pragma unroll
                     for (int b = 0; b < 8; ++b)
-                        if (b < Bl) st_flagged(slot + b * 128, val[b]);
-                } else {
-                    if (tc_collect(P, val, Bl, c_lo, c_hi, row, abort_flag)) {
-                        store_row(val);
-                    } else {
-                        ok = false;
-                    }
+                        if (b < Bl) __stcg(slot + b * 128, val[b]);
                 }
                 ++nseg;
             }
-            if (P.trace && ct == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 4 + 2] = globaltimer_ns();
-            // ---- this CTA's results of job j are stored (and the slots it read are cleared): arrive ----
+            if (P.trace && ct == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 2] = globaltimer_ns();
+            // ---- this CTA's results and parts of job j are stored: arrive ----
             named_bar_sync(1, kTcConvThreads);
-            if (ct == 0) {
-                if (j + 1 < P.n_jobs) {
-                    red_release_add(P.barrier, 1u);
-                } else if (atom_release_add(P.barrier, 1u) == unsigned(P.n_jobs) * unsigned(grid) - 1u) {
-                    *P.barrier = 0u;  // the last arrival of the launch leaves the counter at zero for the next one
+            grid_arrive();
+            job = next;
+        }
+        // ---- the last job's split tile, once every CTA has arrived; then leave the counters at zero ----
+        if (!*decision) {
+            grid_wait(P.n_jobs);
+            if (ct == 0) *decision = *abort_flag;
+            named_bar_sync(1, kTcConvThreads);
+            if (!*decision) {
+                finalize_pending();
+                named_bar_sync(1, kTcConvThreads);
+                if (ct == 0 && atom_release_add(P.barrier + 1, 1u) == unsigned(grid) - 1u) {
+                    P.barrier[0] = 0u;  // the last CTA to leave: nobody polls any more
+                    P.barrier[1] = 0u;
                 }
             }
-            job = next;
         }
     }
     // ---- release tensor memory (always), after every role is done with it ----

@@ -174,8 +174,9 @@ int qgemv_gemv_prefetch(qgemv_handle* h, const qgemv_weight* w, const void* x_bf
  * The projections of a decode step, in order, as ONE persistent kernel ("one CUDA graph per round",
  * tools/fixtures/engines/crit-labs/mtp4-nvfp4-mma/card.yaml:75, taken one step further: one launch).
  * Job i computes y_i = W_i x_i exactly as qgemv_gemv would; job i + 1 may read anything job i wrote
- * (a grid-wide barrier separates them), so x_{i+1} may be y_i or a function of it computed by the
- * caller earlier.  While the CTAs finish one job and convert the next one's activations, the
+ * (a grid-wide barrier separates them; where job i + 1 reads or overwrites y_i -- the address ranges
+ * are compared when the sequence is created -- the barrier also waits for the row tiles of y_i
+ * that were split along K to be added up).  While the CTAs finish one job and convert the next one's activations, the
  * weights of the following jobs keep streaming into shared memory, so HBM does not idle at the
  * boundaries the way it does between separate launches.
  * Weights: QGEMV_FMT_NVFP4_TC only.  All jobs share the batch size B (1..8).  The job list is
