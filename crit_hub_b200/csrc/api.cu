@@ -40,13 +40,15 @@ struct qgemv_handle {
     // tensor-core GEMV: split-K hand-over slots (two per CTA, [8][128] pairs {fp32, flag}), all zero between launches
     float* tc_ws;
     unsigned long long* tc_trace;  // caller's device buffer for phase timestamps, or null
-    unsigned int* seq_barrier;     // arrival / leave counters of the GEMV-sequence kernel, zero between launches
-    float* seq_parts;              // its parts buffer: [2][2 * grid][8][128] fp32
+    unsigned int* seq_barrier;     // CTAs that have left a GEMV-sequence launch, zero between launches
+    float* seq_parts;              // its parts buffers: [kSeqPartBufs][2 * grid][8][128] fp32
     size_t tc_ws_bytes;
+    std::vector<qgemv_sequence*>* sequences;  // live job lists: their counters are cleared after a reported error
 };
 
 struct qgemv_sequence {
     qg::SeqJob* dev_jobs;
+    unsigned int* dev_counters;  // done[n_jobs], fin[n_jobs]: zero between launches
     int n_jobs, B;
     int grid, npad, x_slots, ring, stage_items;
     size_t smem;
@@ -366,11 +368,12 @@ int qgemv_init(const qgemv_config* cfg, qgemv_handle** out) {
     h->gs_ws = nullptr, h->gs_ws_bytes = 0;
     h->chunk_ws = nullptr;
     h->tc_ws = nullptr, h->tc_trace = nullptr, h->seq_barrier = nullptr, h->seq_parts = nullptr;
+    h->sequences = new (std::nothrow) std::vector<qgemv_sequence*>();
     const size_t tc_ws_bytes = size_t(2) * size_t(std::max(h->sm_count, cfg->grid_override)) * 1024 * 8;
     h->tc_ws_bytes = tc_ws_bytes;
     if (cudaMalloc(&h->tc_ws, tc_ws_bytes) != cudaSuccess || cudaMemset(h->tc_ws, 0, tc_ws_bytes) != cudaSuccess ||
         cudaMalloc(&h->seq_barrier, 256) != cudaSuccess || cudaMemset(h->seq_barrier, 0, 256) != cudaSuccess ||
-        cudaMalloc(&h->seq_parts, tc_ws_bytes) != cudaSuccess ||
+        cudaMalloc(&h->seq_parts, size_t(qg::kSeqPartBufs) * size_t(2) * size_t(std::max(h->sm_count, cfg->grid_override)) * 4096) != cudaSuccess ||
         cudaMalloc(&h->chunk_ws, kChunkWsBytes) != cudaSuccess ||
         cudaMalloc(&h->status_dev, 4 * sizeof(int32_t)) != cudaSuccess ||
         cudaMemset(h->status_dev, 0, 4 * sizeof(int32_t)) != cudaSuccess) {
@@ -424,6 +427,7 @@ int qgemv_destroy(qgemv_handle* h) {
     cudaFree(h->tc_ws);
     cudaFree(h->seq_barrier);
     cudaFree(h->seq_parts);
+    delete h->sequences;
     cudaFree(h->status_dev);
     delete h;
     return QGEMV_OK;
@@ -545,23 +549,28 @@ int qgemv_sequence_create(qgemv_handle* h, const qgemv_job* jobs, int n_jobs, in
         sj.tiles = int32_t(jb.w->n_panels / 8), sj.kt = int32_t(jb.w->units);
         sj.x_stride = int32_t(jb.w->K);
         sj.y_dtype = jb.y_dtype;
-        sj.flags = 0;
-        if (i > 0) {
-            // does this job read or overwrite the previous job's output?  Then that output must be
-            // complete (its split tiles added up) before this job starts.
-            const qgemv_job& pj = jobs[i - 1];
+        // the latest earlier job this one must not overtake: it reads that job's output (RAW), or
+        // overwrites its output (WAW) or its input (WAR)
+        sj.dep = -1;
+        {
             const auto lo = [](const void* p) { return reinterpret_cast<uintptr_t>(p); };
-            const uintptr_t py0 = lo(pj.y), py1 = py0 + size_t(B) * size_t(pj.w->N) * (pj.y_dtype == QGEMV_OUT_F32 ? 4 : 2);
-            const uintptr_t x0 = lo(jb.x), x1 = x0 + size_t(B) * size_t(jb.w->K) * 2;
-            const uintptr_t y0 = lo(jb.y), y1 = y0 + size_t(B) * size_t(jb.w->N) * (jb.y_dtype == QGEMV_OUT_F32 ? 4 : 2);
-            if ((x0 < py1 && py0 < x1) || (y0 < py1 && py0 < y1)) sj.flags |= 1;
+            const auto ysize = [&](const qgemv_job& q) { return size_t(B) * size_t(q.w->N) * (q.y_dtype == QGEMV_OUT_F32 ? 4 : 2); };
+            const uintptr_t x0 = lo(jb.x), x1 = x0 + size_t(B) * size_t(jb.w->K) * 2, y0 = lo(jb.y), y1 = y0 + ysize(jb);
+            for (int e = i - 1; e >= 0; --e) {
+                const qgemv_job& pj = jobs[e];
+                const uintptr_t py0 = lo(pj.y), py1 = py0 + ysize(pj), px0 = lo(pj.x), px1 = px0 + size_t(B) * size_t(pj.w->K) * 2;
+                if ((x0 < py1 && py0 < x1) || (y0 < py1 && py0 < y1) || (y0 < px1 && px0 < y1)) {
+                    sj.dep = e;
+                    break;
+                }
+            }
         }
         const int64_t total = int64_t(sj.tiles) * sj.kt;
         x_slots = std::max(x_slots, std::min<int64_t>(sj.kt, (total + grid - 1) / grid));
     }
     qgemv_sequence* q = new (std::nothrow) qgemv_sequence;
     if (!q) return QGEMV_ERR_INVALID_ARG;
-    q->dev_jobs = nullptr;
+    q->dev_jobs = nullptr, q->dev_counters = nullptr;
     q->n_jobs = n_jobs, q->B = B, q->grid = grid;
     q->npad = (8 * B + 15) / 16 * 16;
     q->x_slots = int(x_slots);
@@ -578,12 +587,16 @@ int qgemv_sequence_create(qgemv_handle* h, const qgemv_job* jobs, int n_jobs, in
     q->ring = ring;
     q->smem = size_t(qg::SeqSmem::total(q->x_slots, q->npad, ring, q->stage_items));
     if (cudaSetDevice(h->cfg.device) != cudaSuccess || cudaMalloc(&q->dev_jobs, size_t(n_jobs) * sizeof(qg::SeqJob)) != cudaSuccess ||
-        cudaMemcpy(q->dev_jobs, tab.data(), size_t(n_jobs) * sizeof(qg::SeqJob), cudaMemcpyHostToDevice) != cudaSuccess) {
+        cudaMemcpy(q->dev_jobs, tab.data(), size_t(n_jobs) * sizeof(qg::SeqJob), cudaMemcpyHostToDevice) != cudaSuccess ||
+        cudaMalloc(&q->dev_counters, size_t(2 * n_jobs) * 4) != cudaSuccess ||
+        cudaMemset(q->dev_counters, 0, size_t(2 * n_jobs) * 4) != cudaSuccess) {
         g_last_cuda_error = cudaGetLastError();
         cudaFree(q->dev_jobs);
+        cudaFree(q->dev_counters);
         delete q;
         return QGEMV_ERR_CUDA;
     }
+    if (h->sequences) h->sequences->push_back(q);
     *out = q;
     return QGEMV_OK;
 }
@@ -591,7 +604,9 @@ int qgemv_sequence_create(qgemv_handle* h, const qgemv_job* jobs, int n_jobs, in
 int qgemv_sequence_destroy(qgemv_handle* h, qgemv_sequence* q) {
     if (!h || !q) return QGEMV_ERR_INVALID_ARG;
     cudaSetDevice(h->cfg.device);
+    if (h->sequences) h->sequences->erase(std::remove(h->sequences->begin(), h->sequences->end(), q), h->sequences->end());
     cudaFree(q->dev_jobs);
+    cudaFree(q->dev_counters);
     delete q;
     return QGEMV_OK;
 }
@@ -603,6 +618,8 @@ int qgemv_sequence_run(qgemv_handle* h, const qgemv_sequence* q, void* stream) {
     P.jobs = q->dev_jobs;
     P.ws = h->seq_parts;
     P.barrier = h->seq_barrier;
+    P.done = q->dev_counters;
+    P.fin = q->dev_counters + q->n_jobs;
     P.status = h->status_dev;
     P.spin_limit = default_spin(h);
     P.n_jobs = q->n_jobs;
@@ -612,7 +629,7 @@ int qgemv_sequence_run(qgemv_handle* h, const qgemv_sequence* q, void* stream) {
     P.x_slots = q->x_slots;
     P.debug = h->cfg.debug;
     P.trace = h->tc_trace;
-    const dim3 g(unsigned(q->grid)), blk(qg::kTcThreads);
+    const dim3 g(unsigned(q->grid)), blk(qg::kSeqThreads);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     g_launch_cooperative = true;
     const cudaError_t err = q->stage_items == 2   ? launch(h, qg::gemv_seq_kernel<2>, g, blk, q->smem, st, P)
@@ -903,6 +920,8 @@ int qgemv_last_device_status(qgemv_handle* h, void* stream, qgemv_dev_status* ou
         // a kernel that gave up may have left hand-over flags and the arrival counter behind
         QG_CUDA(cudaMemset(h->tc_ws, 0, h->tc_ws_bytes));
         QG_CUDA(cudaMemset(h->seq_barrier, 0, 256));
+        if (h->sequences)
+            for (qgemv_sequence* q : *h->sequences) QG_CUDA(cudaMemset(q->dev_counters, 0, size_t(2 * q->n_jobs) * 4));
     }
     return QGEMV_OK;
 }

@@ -33,6 +33,8 @@
 
 namespace qg {
 
+constexpr int kSeqPartBufs = 8;  // jobs a CTA may run ahead of the slowest one before it waits for its parts buffer
+
 struct SeqJob {               // 64 bytes, device memory
     const uint8_t* payload;   // items of the weight: (tile * kt + item) * 4608
     const uint16_t* x;        // bf16 [B][K]
@@ -42,15 +44,18 @@ struct SeqJob {               // 64 bytes, device memory
     int32_t tiles, kt;        // ceil(N / 128), ceil(K / 64)
     int32_t x_stride;         // elements between activation rows
     int32_t y_dtype;
-    int32_t flags;            // bit 0: this job's x or y overlaps the previous job's y -- finish that one first
+    int32_t dep;              // latest earlier job whose output this job reads or overwrites, or whose input it
+                              // overwrites (address ranges compared by the host); -1: none
     int32_t pad;
 };
 static_assert(sizeof(SeqJob) == 64, "SeqJob layout");
 
 struct SeqParams {
     const SeqJob* jobs;
-    float* ws;                  // parts buffer: [job parity][2 * cta + which][8][128] fp32 partial sums
-    unsigned int* barrier;      // [0] grid-wide arrival counter, [1] CTAs that have left; both zero between launches
+    float* ws;                  // parts buffers: [job % kSeqPartBufs][2 * cta + which][8][128] fp32 partial sums
+    unsigned int* barrier;      // CTAs that have left the launch; zero between launches
+    unsigned int* done;         // [n_jobs] CTAs whose results and parts of the job are stored; zero between launches
+    unsigned int* fin;          // [n_jobs] CTAs that have added up their split tile of the job; zero between launches
     int32_t* status;
     int64_t spin_limit;
     int32_t n_jobs;
@@ -66,18 +71,22 @@ struct SeqSmem {
     static constexpr int kBarEmpty = 128;   // kTcMaxRing
     static constexpr int kBarDFull = 256;   // 2
     static constexpr int kBarDFree = 272;   // 2
-    static constexpr int kBarXReady = 288;
-    static constexpr int kBarDrain = 296;
-    static constexpr int kTmemPtr = 304;
-    static constexpr int kAbort = 308;
-    static constexpr int kIssued = 312;
-    static constexpr int kConsumed = 316;
-    static constexpr int kRowMax = 320;     // 8 words
-    static constexpr int kDecision = 352;   // the converting warps' common verdict on the abort flag, per job
-    static constexpr int kWarpMax = 384;    // kTcConvWarps x 8 words
+    static constexpr int kBarXReady = 288;  // 2: one per plane buffer
+    static constexpr int kBarEDone = 656;   // 2: the epilogues of the job that used a plane buffer are through
+    static constexpr int kBarMDone = 696;   // 2: the MMA issuer is through with the job that used a plane buffer
+    static constexpr int kBarDrain = 304;
+    static constexpr int kTmemPtr = 312;
+    static constexpr int kAbort = 316;
+    static constexpr int kRowMax = 320;     // [plane buffer][8] words: largest |bf16| pattern per activation row
+    static constexpr int kWarpMax = 384;    // kTcConvWarps x 8 words: the same per converting warp
+    static constexpr int kIssued = 640;
+    static constexpr int kConsumed = 644;
+    static constexpr int kDecision = 672;   // [3] every warp group's common sample of the abort flag
+    static constexpr int kFinAll = 688;     // jobs up to this index are added up on every CTA (-1: none)
     static constexpr int kSfb = 1024;       // 512 bytes
     static constexpr int kX = 1536;
-    __host__ __device__ static constexpr int ring_off(int x_slots, int npad) { return (kX + x_slots * npad * 32 + 127) / 128 * 128; }
+    // two buffers of digit planes (jobs alternate), then the ring
+    __host__ __device__ static constexpr int ring_off(int x_slots, int npad) { return (kX + 2 * x_slots * npad * 32 + 127) / 128 * 128; }
     __host__ __device__ static constexpr int total(int x_slots, int npad, int ring, int stage_items) {
         return ring_off(x_slots, npad) + ring * stage_items * kTcItemBytes;
     }
@@ -124,8 +133,10 @@ __device__ __forceinline__ void seq_walker(GsWalker& wk, int32_t total, int32_t 
     seq_range(total, cta, gj, wk.pos, wk.end);
 }
 
+constexpr int kSeqThreads = 32 * (2 + 12);  // producer, MMA issuer, three groups of four warps
+
 template <int S>
-__global__ void __launch_bounds__(kTcThreads, 1) gemv_seq_kernel(const SeqParams P) {
+__global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParams P) {
     extern __shared__ __align__(128) unsigned char sq_smem[];
     const uint32_t sbase = smem_u32(sq_smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -133,6 +144,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_seq_kernel(const SeqParams
     const int npad = P.npad, R = P.ring;
     const uint32_t xslot_bytes = uint32_t(npad) * 32u;
     const uint32_t xbase = sbase + SeqSmem::kX;
+    const uint32_t xbuf_bytes = uint32_t(P.x_slots) * xslot_bytes;  // one buffer of digit planes
     constexpr uint32_t stage_bytes = uint32_t(S) * kTcItemBytes;
     const uint32_t ring0 = sbase + uint32_t(SeqSmem::ring_off(P.x_slots, npad));
     constexpr uint32_t ncols = SeqSmem::kTmemCols;
@@ -140,7 +152,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_seq_kernel(const SeqParams
     volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(sq_smem + SeqSmem::kTmemPtr);
     volatile int* n_issued = reinterpret_cast<volatile int*>(sq_smem + SeqSmem::kIssued);
     volatile int* n_consumed = reinterpret_cast<volatile int*>(sq_smem + SeqSmem::kConsumed);
-    unsigned int* rowmax = reinterpret_cast<unsigned int*>(sq_smem + SeqSmem::kRowMax);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kTcMaxRing; ++s) {
@@ -152,7 +163,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_seq_kernel(const SeqParams
             mbar_init(sbase + SeqSmem::kBarDFree + 8 * b, 4);
         }
         mbar_init(sbase + SeqSmem::kBarXReady, 1);
+        mbar_init(sbase + SeqSmem::kBarXReady + 8, 1);
         mbar_init(sbase + SeqSmem::kBarDrain, 1);
+        mbar_init(sbase + SeqSmem::kBarEDone, 1);
+        mbar_init(sbase + SeqSmem::kBarEDone + 8, 1);
+        mbar_init(sbase + SeqSmem::kBarMDone, 1);
+        mbar_init(sbase + SeqSmem::kBarMDone + 8, 1);
+        *reinterpret_cast<volatile int*>(sq_smem + SeqSmem::kFinAll) = -1;
         *abort_flag = 0;
         *n_issued = 0;
         *n_consumed = 0;
@@ -239,7 +256,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_seq_kernel(const SeqParams
                 GsSeg sg;
                 bool have = wk.next(sg);
                 // the digit planes of this job (every CTA signals, also one without items)
-                if (!mbar_wait(sbase + SeqSmem::kBarXReady, uint32_t(j) & 1u, P.spin_limit)) {
+                if (!mbar_wait(sbase + SeqSmem::kBarXReady + 8 * (j & 1), uint32_t(j >> 1) & 1u, P.spin_limit)) {
                     report(P.status, QGEMV_ERR_TIMEOUT, 72, j);
                     *abort_flag = 1;
                     ok = false;
@@ -262,7 +279,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_seq_kernel(const SeqParams
                     uint32_t acc = 0;
                     int32_t slot = sg.u0 - xs0;
                     if (slot < 0) slot += kt_len;
-                    uint32_t x_lo = x_lo0 + uint32_t(slot) * xslot16;
+                    uint32_t x_lo = x_lo0 + uint32_t(j & 1) * (xbuf_bytes >> 4) + uint32_t(slot) * xslot16;
                     for (int32_t left = sg.u1 - sg.u0; left > 0; left -= S) {
                         // (the stage was written through the async proxy and is read through it: the
                         // barrier's acquire is all the ordering the MMAs need -- no tcgen05 fence here,
@@ -302,293 +319,352 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_seq_kernel(const SeqParams
                     ++nseg;
                 }
                 if (P.trace) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 4] = globaltimer_ns();
+                // Barrier phases are told apart by one parity bit, so nobody may complete a barrier twice
+                // before every waiter has seen the first completion: the planes of job j + 2 are only made
+                // once this thread (here) and the epilogue group are through with job j.
+                if (ok) mbar_arrive(sbase + SeqSmem::kBarMDone + 8 * (j & 1));
                 job = next;
             }
             *n_consumed = mi;
         }
         __syncwarp();
     } else {
-        // ================= digit planes and epilogues, job after job =================
-        const int ct = threadIdx.x - 32 * kTcWarpConv0;  // 0..255
+        // ================= three independent warp groups, job after job =================
+        // The chores of a job are round trips to global memory (activations in, results out, "has
+        // every CTA finished?"), each most of a microsecond.  Run one after the other by the same warps
+        // they cost 6-7 us per job; so they are dealt to three groups of four warps that only meet
+        // through barriers in shared memory and counters in global memory:
+        //   PLANES   (warps 2-5)   digit planes of job j into plane buffer j % 2, up to two jobs ahead of
+        //                          the epilogues; a job that the host found to depend on an earlier one
+        //                          (address ranges) first waits until that job is complete on every CTA
+        //   EPILOGUE (warps 6-9)   accumulators of job j's segments -> y rows, or parts of a split tile
+        //   FINISH   (warps 10-13) once every CTA has stored its parts of job j: adds up the split tile
+        //                          this CTA is the first contributor of, in CTA order, and stores its rows
+        const int grp = (warp - kTcWarpConv0) >> 2;        // 0 PLANES, 1 EPILOGUE, 2 FINISH
+        const int gt = threadIdx.x - 32 * (kTcWarpConv0 + 4 * grp);  // 0..127 inside the group
+        const int bar_id = 1 + grp;                         // the group's named barrier
         const int Bl = P.B;
-        const int g = (warp - kTcWarpConv0) >> 2, q = warp & 3;
-        const uint32_t lane_base = uint32_t(32 * q) << 16;
-        const int row = 32 * q + lane;
         unsigned int* all_max = reinterpret_cast<unsigned int*>(sq_smem + SeqSmem::kWarpMax);
-        unsigned int* wmax = all_max + (warp - kTcWarpConv0) * 8;
-        // block scales of the planes: column n = 8 b + j carries 2^(2j - 6) in all four K blocks
-        if (ct < 128) {
-            const int n = ct, j = n & 7;
-            const uint32_t byte = n < 8 * Bl ? uint32_t(2 * j + 1) << 3 : 0u;
-            *reinterpret_cast<volatile uint32_t*>(sq_smem + SeqSmem::kSfb + (n & 31) * 16 + (n >> 5) * 4) = byte * 0x01010101u;
-        }
-        pdl_wait();  // whatever ran before this launch has finished with x, y and the hand-over slots
-        uint32_t nseg = 0;
-        bool ok = true;  // this warp's own view; leaving the job loop is decided for all eight warps together
-        unsigned int n_bar = 0;  // grid-wide barriers so far: the same number on every CTA
-        auto grid_arrive = [&]() {  // after a barrier of the eight warps: this CTA's stores are ordered before it
-            if (ct == 0) red_release_add(P.barrier, 1u);
-            ++n_bar;
+        unsigned int* rowmax2 = reinterpret_cast<unsigned int*>(sq_smem + SeqSmem::kRowMax);  // [plane buffer][8]
+        volatile int* decision = reinterpret_cast<volatile int*>(sq_smem + SeqSmem::kDecision) + grp;
+        volatile int* fin_all = reinterpret_cast<volatile int*>(sq_smem + SeqSmem::kFinAll);
+        // Named barriers have no time-out, so a group leaves its job loop at one place for all its
+        // warps: one thread samples the abort flag, everybody reads that sample.
+        auto group_alive = [&]() -> bool {
+            if (gt == 0) *decision = *abort_flag;
+            named_bar_sync(bar_id, 128);
+            const bool go = *decision == 0;
+            named_bar_sync(bar_id, 128);  // nobody overwrites the sample before everybody has read it
+            return go;
         };
-        auto grid_wait = [&](int j) {
-            if (ct == 0) {
-                const unsigned int target = n_bar * unsigned(grid);
+        // bounded poll by the group's first thread until *counter == grid (every CTA has passed that point)
+        auto poll_all = [&](const unsigned int* counter, int site, int j) {
+            if (gt == 0) {
                 uint64_t t0 = 0;
-                for (int64_t it = 0; ld_acquire(P.barrier) < target; ++it) {
+                for (int64_t it = 0; ld_acquire(counter) < unsigned(grid); ++it) {
+                    if (*abort_flag) break;
                     if (it == 0) t0 = globaltimer_ns();
                     if (it >= P.spin_limit || ((it & 63) == 63 && globaltimer_ns() - t0 > 2000000000ull)) {
-                        report(P.status, QGEMV_ERR_TIMEOUT, 75, j);
+                        report(P.status, QGEMV_ERR_TIMEOUT, site, j);
                         *abort_flag = 1;
                         break;
                     }
                 }
             }
         };
-        // The row tile of the job before, if this CTA is its first contributor and the tile was split:
-        // its rows are the sum of the parts, added here in CTA order once all of them are known to be stored.
-        struct {
-            bool valid;
-            int32_t tile, c_lo, c_hi, lo_slot, N, y_dtype, parity;
-            void* y;
-        } pend;
-        pend.valid = false;
-        auto finalize_pending = [&]() {
-            if (pend.valid && ct < 128) {
-                const int n = pend.tile * 128 + ct;
-                const float* parts = P.ws + size_t(pend.parity) * size_t(2 * grid) * 1024 + ct;
-                if (n < pend.N) {
+        pdl_wait();  // whatever ran before this launch has finished with x, y and the scratch
+
+        if (grp == 0) {
+            // ---------------- PLANES ----------------
+            const int wq = warp - kTcWarpConv0;  // 0..3
+            unsigned int* wmax = all_max + wq * 8;
+            if (gt < 128) {  // block scales of the planes: column n = 8 b + j carries 2^(2j - 6) in all four K blocks
+                const int n = gt, jj = n & 7;
+                const uint32_t byte = n < 8 * Bl ? uint32_t(2 * jj + 1) << 3 : 0u;
+                *reinterpret_cast<volatile uint32_t*>(sq_smem + SeqSmem::kSfb + (n & 31) * 16 + (n >> 5) * 4) = byte * 0x01010101u;
+            }
+            SeqJob job = seq_load_job(P.jobs);
+            for (int j = 0; j < P.n_jobs; ++j) {
+                SeqJob next = job;
+                if (j + 1 < P.n_jobs) next = seq_load_job(P.jobs + j + 1);
+                // plane buffer j % 2 and its row maxima were last used by job j - 2: its epilogues must be through
+                if (j >= 2 && gt == 0 &&
+                    !mbar_wait(sbase + SeqSmem::kBarEDone + 8 * (j & 1), uint32_t((j >> 1) - 1) & 1u, P.spin_limit)) {
+                    report(P.status, QGEMV_ERR_TIMEOUT, 78, j);
+                    *abort_flag = 1;
+                }
+                if (job.dep >= 0) poll_all(P.fin + job.dep, 80, j);  // an earlier job's output (or input) is involved
+                if (!group_alive()) break;
+                if (P.trace && gt == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 0] = globaltimer_ns();
+                const int32_t kt_len = job.kt;
+                const int32_t total = job.tiles * kt_len;
+                int32_t r_begin, r_end;
+                seq_range(total, cta, seq_job_grid(total, grid), r_begin, r_end);
+                const int32_t n_items = r_end - r_begin;
+                const int32_t xs0 = n_items >= kt_len ? 0 : r_begin % kt_len;
+                const int32_t n_slots = n_items >= kt_len ? kt_len : n_items;
+                const uint32_t xb = xbase + uint32_t(j & 1) * xbuf_bytes;
+                if (gt < 32) all_max[gt] = 0u;
+                named_bar_sync(bar_id, 128);
+                const int n_work = n_slots * Bl * 8;
+                constexpr int kKeep = 4;
+                auto unit_src = [&](int wu, int& b, uint32_t& dst) -> uint4 {
+                    const int o = wu & 7, sb = wu >> 3;
+                    b = sb / n_slots;
+                    const int slot = sb - b * n_slots;
+                    int32_t u = slot + xs0;
+                    if (u >= kt_len) u -= kt_len;
+                    const int k0 = u * 64 + o * 8;
+                    dst = xb + uint32_t(slot) * xslot_bytes + uint32_t(b) * 256u + uint32_t(o >> 2) * 128u + uint32_t(o & 3) * 4u;
+                    uint4 v = make_uint4(0, 0, 0, 0);
+                    // possibly written by other SMs during an earlier job: read through L2, never a stale L1 line
+                    if (k0 + 8 <= job.K) v = __ldcg(reinterpret_cast<const uint4*>(job.x + int64_t(b) * job.x_stride + k0));
+                    return v;
+                };
+                auto unit_max = [&](const uint4& v) {
+                    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+                    uint32_t m = 0;
 #pragma unroll
-                    for (int b = 0; b < 8; ++b) {
-                        if (b < Bl) {
-                            // eight parts' loads in flight together; the additions stay in CTA order
-                            float v = __ldcg(parts + size_t(pend.lo_slot) * 1024 + b * 128);
-                            for (int32_t cc = pend.c_lo + 1; cc <= pend.c_hi; cc += 8) {
-                                float t[8];
+                    for (int z = 0; z < 4; ++z) {
+                        m = max(m, w[z] & 0x7FFFu);
+                        m = max(m, (w[z] >> 16) & 0x7FFFu);
+                    }
+                    return m;
+                };
+                auto row_max = [&](int b) {
+                    uint32_t m = 0;
 #pragma unroll
-                                for (int z = 0; z < 8; ++z) t[z] = __ldcg(parts + size_t(2 * min(cc + z, pend.c_hi)) * 1024 + b * 128);
+                    for (int w = 0; w < 4; ++w) m = max(m, all_max[w * 8 + b]);
+                    return m;
+                };
+                auto store_unit = [&](int b, uint32_t dst, const uint4& v) {
+                    const float sf = pow2i(-tc_row_exponent(row_max(b)));
+                    uint32_t pl[8];
+                    tc_digits8(v, sf, pl);
 #pragma unroll
-                                for (int z = 0; z < 8; ++z)
-                                    if (cc + z <= pend.c_hi) v += t[z];
-                            }
-                            const int64_t idx = int64_t(b) * pend.N + n;
-                            if (pend.y_dtype == QGEMV_OUT_F32) {
-                                static_cast<float*>(pend.y)[idx] = v;
-                            } else {
-                                static_cast<__nv_bfloat16*>(pend.y)[idx] = __float2bfloat16_rn(v);
-                            }
+                    for (int z = 0; z < 8; ++z) asm volatile("st.shared.b32 [%0], %1;" ::"r"(dst + z * 16), "r"(pl[z]) : "memory");
+                };
+                uint4 keep[kKeep];
+                int kb[kKeep];
+                uint32_t kdst[kKeep];
+#pragma unroll
+                for (int i = 0; i < kKeep; ++i) {
+                    const int wu = gt + i * 128;
+                    kb[i] = 0, kdst[i] = 0;
+                    keep[i] = make_uint4(0, 0, 0, 0);
+                    if (wu < n_work) keep[i] = unit_src(wu, kb[i], kdst[i]);
+                }
+#pragma unroll
+                for (int i = 0; i < kKeep; ++i) {
+                    const uint32_t m = unit_max(keep[i]);
+                    if (m) atomicMax(wmax + kb[i], m);
+                }
+                for (int wu = gt + kKeep * 128; wu < n_work; wu += 128) {
+                    int b;
+                    uint32_t dst;
+                    const uint32_t m = unit_max(unit_src(wu, b, dst));
+                    if (m) atomicMax(wmax + b, m);
+                }
+                named_bar_sync(bar_id, 128);
+                if (gt < 8) rowmax2[(j & 1) * 8 + gt] = row_max(gt);
+#pragma unroll
+                for (int i = 0; i < kKeep; ++i)
+                    if (gt + i * 128 < n_work) store_unit(kb[i], kdst[i], keep[i]);
+                for (int wu = gt + kKeep * 128; wu < n_work; wu += 128) {
+                    int b;
+                    uint32_t dst;
+                    const uint4 v = unit_src(wu, b, dst);
+                    store_unit(b, dst, v);
+                }
+                fence_proxy_async_smem();  // the planes are read by the tensor core (async proxy)
+                named_bar_sync(bar_id, 128);
+                if (gt == 0) mbar_arrive(sbase + SeqSmem::kBarXReady + 8 * (j & 1));
+                if (P.trace && gt == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 1] = globaltimer_ns();
+                job = next;
+            }
+        } else if (grp == 1) {
+            // ---------------- EPILOGUE ----------------
+            const int q = warp & 3;
+            const uint32_t lane_base = uint32_t(32 * q) << 16;
+            const int row = 32 * q + lane;
+            uint32_t nseg = 0;
+            SeqJob job = seq_load_job(P.jobs);
+            for (int j = 0; j < P.n_jobs; ++j) {
+                SeqJob next = job;
+                if (j + 1 < P.n_jobs) next = seq_load_job(P.jobs + j + 1);
+                const int32_t kt_len = job.kt;
+                const int32_t total = job.tiles * kt_len;
+                const int gj = seq_job_grid(total, grid);
+                int32_t rb, re;
+                seq_range(total, cta, gj, rb, re);
+                // A split tile's parts go to buffer j % kSeqPartBufs, last used by job j - kSeqPartBufs: every
+                // CTA must have added that job's tiles up (the FINISH group publishes how far that has come)
+                if (re > rb && (rb % kt_len != 0 || re % kt_len != 0) && j >= kSeqPartBufs && gt == 0) {
+                    uint64_t t0 = 0;
+                    for (int64_t it = 0; *fin_all < j - kSeqPartBufs; ++it) {
+                        if (*abort_flag) break;
+                        if (it == 0) t0 = globaltimer_ns();
+                        __nanosleep(64);
+                        if (it >= P.spin_limit || ((it & 63) == 63 && globaltimer_ns() - t0 > 2000000000ull)) {
+                            report(P.status, QGEMV_ERR_TIMEOUT, 79, j);
+                            *abort_flag = 1;
+                            break;
                         }
                     }
                 }
-            }
-            pend.valid = false;
-        };
-        volatile int* decision = reinterpret_cast<volatile int*>(sq_smem + SeqSmem::kDecision);
-        SeqJob job = seq_load_job(P.jobs);
-        for (int j = 0; j < P.n_jobs; ++j) {
-            SeqJob next = job;
-            if (j + 1 < P.n_jobs) next = seq_load_job(P.jobs + j + 1);
-            const int32_t kt_len = job.kt;
-            const int32_t total = job.tiles * kt_len;
-            const int gj = seq_job_grid(total, grid);
-            int32_t r_begin, r_end;
-            seq_range(total, cta, gj, r_begin, r_end);
-            const int32_t n_items = r_end - r_begin;
-            const int32_t xs0 = n_items >= kt_len ? 0 : r_begin % kt_len;
-            const int32_t n_slots = n_items >= kt_len ? kt_len : n_items;
-            // ---- grid-wide barrier: every CTA has stored its results (or parts) of job j - 1 ----
-            if (ct < 8 * kTcConvWarps) all_max[ct] = 0u;  // per-warp row maxima of the last job
-            if (j > 0) grid_wait(j);
-            // Named barriers have no time-out, so all eight warps must leave the job loop at the same
-            // place: one thread samples the abort flag, everybody reads that sample after the barrier.
-            if (ct == 0) *decision = *abort_flag;
-            named_bar_sync(1, kTcConvThreads);
-            if (*decision) break;
-            if (j > 0 && (job.flags & 1)) {
-                // this job reads or overwrites what the previous one produced: finish that first
-                finalize_pending();
-                named_bar_sync(1, kTcConvThreads);
-                grid_arrive();
-                grid_wait(j);
-                if (ct == 0) *decision = *abort_flag;
-                named_bar_sync(1, kTcConvThreads);
-                if (*decision) break;
-            }
-            if (P.trace && ct == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 0] = globaltimer_ns();
-            // ---- digit planes of the items this CTA multiplies in job j (see gemv_tc.cuh) ----
-            const int n_work = n_slots * Bl * 8;
-            constexpr int kKeep = 4;
-            auto unit_src = [&](int wu, int& b, uint32_t& dst) -> uint4 {
-                const int o = wu & 7, sb = wu >> 3;
-                b = sb / n_slots;
-                const int slot = sb - b * n_slots;
-                int32_t u = slot + xs0;
-                if (u >= kt_len) u -= kt_len;
-                const int k0 = u * 64 + o * 8;
-                dst = xbase + uint32_t(slot) * xslot_bytes + uint32_t(b) * 256u + uint32_t(o >> 2) * 128u + uint32_t(o & 3) * 4u;
-                uint4 v = make_uint4(0, 0, 0, 0);
-                // written by other SMs during the previous job: read through L2, never a stale L1 line
-                if (k0 + 8 <= job.K) v = __ldcg(reinterpret_cast<const uint4*>(job.x + int64_t(b) * job.x_stride + k0));
-                return v;
-            };
-            auto unit_max = [&](const uint4& v) {
-                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-                uint32_t m = 0;
-#pragma unroll
-                for (int z = 0; z < 4; ++z) {
-                    m = max(m, w[z] & 0x7FFFu);
-                    m = max(m, (w[z] >> 16) & 0x7FFFu);
-                }
-                return m;
-            };
-            auto row_max = [&](int b) {
-                uint32_t m = 0;
-#pragma unroll
-                for (int w = 0; w < kTcConvWarps; ++w) m = max(m, all_max[w * 8 + b]);
-                return m;
-            };
-            auto store_unit = [&](int b, uint32_t dst, const uint4& v) {
-                const float sf = pow2i(-tc_row_exponent(row_max(b)));
-                uint32_t pl[8];
-                tc_digits8(v, sf, pl);
-#pragma unroll
-                for (int z = 0; z < 8; ++z) asm volatile("st.shared.b32 [%0], %1;" ::"r"(dst + z * 16), "r"(pl[z]) : "memory");
-            };
-            uint4 keep[kKeep];
-            int kb[kKeep];
-            uint32_t kdst[kKeep];
-#pragma unroll
-            for (int i = 0; i < kKeep; ++i) {
-                const int wu = ct + i * kTcConvThreads;
-                kb[i] = 0, kdst[i] = 0;
-                keep[i] = make_uint4(0, 0, 0, 0);
-                if (wu < n_work) keep[i] = unit_src(wu, kb[i], kdst[i]);
-            }
-#pragma unroll
-            for (int i = 0; i < kKeep; ++i) {
-                const uint32_t m = unit_max(keep[i]);
-                if (m) atomicMax(wmax + kb[i], m);
-            }
-            for (int wu = ct + kKeep * kTcConvThreads; wu < n_work; wu += kTcConvThreads) {
-                int b;
-                uint32_t dst;
-                const uint32_t m = unit_max(unit_src(wu, b, dst));
-                if (m) atomicMax(wmax + b, m);
-            }
-            named_bar_sync(1, kTcConvThreads);
-            if (ct < 8) rowmax[ct] = row_max(ct);
-#pragma unroll
-            for (int i = 0; i < kKeep; ++i)
-                if (ct + i * kTcConvThreads < n_work) store_unit(kb[i], kdst[i], keep[i]);
-            for (int wu = ct + kKeep * kTcConvThreads; wu < n_work; wu += kTcConvThreads) {
-                int b;
-                uint32_t dst;
-                const uint4 v = unit_src(wu, b, dst);
-                store_unit(b, dst, v);
-            }
-            fence_proxy_async_smem();  // the planes are read by the tensor core (async proxy)
-            named_bar_sync(1, kTcConvThreads);
-            if (ct == 0) mbar_arrive(sbase + SeqSmem::kBarXReady);
-            if (P.trace && ct == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 1] = globaltimer_ns();
-            // the tensor core is busy with this job now: add up the split tile of the job before
-            finalize_pending();
-            if (P.trace && ct == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 6] = globaltimer_ns();
-
-            // ---- epilogues of job j: group g takes the segments with (global) nseg % 2 == g ----
-            float scale[8];
-#pragma unroll
-            for (int b = 0; b < 8; ++b) scale[b] = b < Bl ? job.tensor_scale * pow2i(tc_row_exponent(rowmax[b]) + 7) : 0.f;
-            GsWalker wk;
-            seq_walker(wk, total, kt_len, cta, gj);
-            GsSeg sg;
-            while (ok && wk.next(sg)) {
-                const bool whole = sg.u0 == 0 && sg.u1 == kt_len;
-                int32_t c_lo = 0, c_hi = 0, my_slot = 0;
-                if (!whole) {
-                    c_lo = int32_t(cta_of(int64_t(sg.tile) * kt_len, total, gj));
-                    c_hi = int32_t(cta_of(int64_t(sg.tile + 1) * kt_len - 1, total, gj));
-                    // every contributor after the first starts its range inside this tile (slot 0 of its
-                    // pair); the first one's range may have started in an earlier tile
-                    my_slot = cta == c_lo ? gs_slot(c_lo, sg.tile, kt_len, total, gj) : 2 * cta;
-                    if (cta == c_lo) {  // all eight warps note it, whichever group runs the segment
-                        pend.valid = true;
-                        pend.tile = sg.tile, pend.c_lo = c_lo, pend.c_hi = c_hi, pend.lo_slot = my_slot;
-                        pend.N = job.N, pend.y_dtype = job.y_dtype, pend.parity = j & 1, pend.y = job.y;
-                    }
-                }
-                if (int(nseg & 1) != g) {
-                    ++nseg;
-                    continue;
-                }
-                if (!__all_sync(0xFFFFFFFFu, mbar_wait_probe(sbase + SeqSmem::kBarDFull + 8 * g, (nseg >> 1) & 1, P.spin_limit))) {
-                    if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 76, int(nseg));
+                // (a CTA without items in a run of jobs would otherwise race ahead of the PLANES group and
+                // complete its barrier twice before that group has looked)
+                if (gt == 0 && !*abort_flag &&
+                    !mbar_wait(sbase + SeqSmem::kBarXReady + 8 * (j & 1), uint32_t(j >> 1) & 1u, P.spin_limit)) {
+                    report(P.status, QGEMV_ERR_TIMEOUT, 81, j);
                     *abort_flag = 1;
-                    ok = false;
-                    break;
                 }
-                tc_fence_after();
-                if (P.trace && lane == 0 && q == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 5] = globaltimer_ns();  // the last one stays
-                float val[8];
+                if (!group_alive()) break;
+                GsWalker wk;
+                seq_walker(wk, total, kt_len, cta, gj);
+                GsSeg sg;
+                bool ok = true;
+                float scale[8];
+                bool have_scale = false;
+                while (wk.next(sg)) {
+                    if (!ok) continue;  // this warp gave up: it still reaches the group's barriers below
+                    const bool whole = sg.u0 == 0 && sg.u1 == kt_len;
+                    const uint32_t acc = nseg & 1;
+                    if (!__all_sync(0xFFFFFFFFu, mbar_wait_probe(sbase + SeqSmem::kBarDFull + 8 * acc, (nseg >> 1) & 1, P.spin_limit))) {
+                        if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 76, int(nseg));
+                        *abort_flag = 1;
+                        ok = false;
+                        continue;
+                    }
+                    tc_fence_after();
+                    if (P.trace && gt == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 5] = globaltimer_ns();  // the last one stays
+                    if (!have_scale) {  // the MMAs of this job have run, so its planes and row maxima are there
 #pragma unroll
-                for (int b = 0; b < 8; ++b) {
-                    val[b] = 0.f;
-                    if (b < Bl) {
-                        uint32_t r[8];
-                        tmem_ld8(tmem_base + lane_base + uint32_t(g * npad + 8 * b), r);
-                        float a = __uint_as_float(r[0]);
+                        for (int b = 0; b < 8; ++b)
+                            scale[b] = b < Bl ? job.tensor_scale * pow2i(tc_row_exponent(rowmax2[(j & 1) * 8 + b]) + 7) : 0.f;
+                        have_scale = true;
+                    }
+                    float val[8];
 #pragma unroll
-                        for (int z = 1; z < 8; ++z) a += __uint_as_float(r[z]);
-                        val[b] = a * scale[b];
+                    for (int b = 0; b < 8; ++b) {
+                        val[b] = 0.f;
+                        if (b < Bl) {
+                            uint32_t r[8];
+                            tmem_ld8(tmem_base + lane_base + acc * uint32_t(npad) + uint32_t(8 * b), r);
+                            float a = __uint_as_float(r[0]);
+#pragma unroll
+                            for (int z = 1; z < 8; ++z) a += __uint_as_float(r[z]);
+                            val[b] = a * scale[b];
+                        }
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(sbase + SeqSmem::kBarDFree + 8 * acc);  // the accumulator may be overwritten
+                    ++nseg;
+                    const int n = sg.tile * 128 + row;
+                    if (whole) {
+                        if (n < job.N) {
+#pragma unroll
+                            for (int b = 0; b < 8; ++b) {
+                                if (b < Bl) {
+                                    const int64_t idx = int64_t(b) * job.N + n;
+                                    if (job.y_dtype == QGEMV_OUT_F32) {
+                                        static_cast<float*>(job.y)[idx] = val[b];
+                                    } else {
+                                        static_cast<__nv_bfloat16*>(job.y)[idx] = __float2bfloat16_rn(val[b]);
+                                    }
+                                }
+                            }
+                        }
+                    } else {
+                        // every contributor after the first starts its range inside this tile (slot 0 of its
+                        // pair); the first one's range may have started in an earlier tile
+                        const int32_t c_lo = int32_t(cta_of(int64_t(sg.tile) * kt_len, total, gj));
+                        const int32_t my_slot = cta == c_lo ? gs_slot(c_lo, sg.tile, kt_len, total, gj) : 2 * cta;
+                        float* slot = P.ws + (size_t(j & (kSeqPartBufs - 1)) * size_t(2 * grid) + size_t(my_slot)) * 1024 + row;
+#pragma unroll
+                        for (int b = 0; b < 8; ++b)
+                            if (b < Bl) __stcg(slot + b * 128, val[b]);
                     }
                 }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(sbase + SeqSmem::kBarDFree + 8 * g);  // the accumulator may be overwritten
-                const int n = sg.tile * 128 + row;
-                auto store_row = [&](const float (&v)[8]) {
+                if (P.trace && gt == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 2] = globaltimer_ns();
+                // this CTA's rows and parts of job j are stored; its plane buffer may be reused
+                named_bar_sync(bar_id, 128);
+                if (gt == 0) {
+                    red_release_add(P.done + j, 1u);
+                    if (!*abort_flag && !mbar_wait(sbase + SeqSmem::kBarMDone + 8 * (j & 1), uint32_t(j >> 1) & 1u, P.spin_limit)) {
+                        report(P.status, QGEMV_ERR_TIMEOUT, 82, j);
+                        *abort_flag = 1;
+                    }
+                    mbar_arrive(sbase + SeqSmem::kBarEDone + 8 * (j & 1));
+                }
+                job = next;
+            }
+        } else {
+            // ---------------- FINISH ----------------
+            int known = -1;  // jobs up to here are added up on every CTA (published in fin_all)
+            SeqJob job = seq_load_job(P.jobs);
+            for (int j = 0; j < P.n_jobs; ++j) {
+                SeqJob next = job;
+                if (j + 1 < P.n_jobs) next = seq_load_job(P.jobs + j + 1);
+                // is this CTA the first contributor of a split tile of job j?  (only its last segment can be)
+                const int32_t kt_len = job.kt;
+                const int32_t total = job.tiles * kt_len;
+                const int gj = seq_job_grid(total, grid);
+                int32_t rb, re;
+                seq_range(total, cta, gj, rb, re);
+                bool pending = false;
+                int32_t tile = 0, c_lo = 0, c_hi = 0, lo_slot = 0;
+                if (re > rb && re % kt_len != 0) {
+                    tile = (re - 1) / kt_len;
+                    c_lo = int32_t(cta_of(int64_t(tile) * kt_len, total, gj));
+                    c_hi = int32_t(cta_of(int64_t(tile + 1) * kt_len - 1, total, gj));
+                    pending = c_lo == cta;
+                    lo_slot = gs_slot(c_lo, tile, kt_len, total, gj);
+                }
+                poll_all(P.done + j, 77, j);
+                // how far have ALL CTAs come with this step?  One probe per job, in flight with nothing else to do
+                if (gt == 0 && known + 1 < j && ld_acquire(P.fin + known + 1) >= unsigned(grid)) *fin_all = ++known;
+                if (!group_alive()) break;
+                if (pending && gt < 128) {
+                    const int n = tile * 128 + gt;
+                    const float* parts = P.ws + size_t(j & (kSeqPartBufs - 1)) * size_t(2 * grid) * 1024 + gt;
                     if (n < job.N) {
 #pragma unroll
                         for (int b = 0; b < 8; ++b) {
                             if (b < Bl) {
+                                // eight parts' loads in flight together; the additions stay in CTA order
+                                float v = __ldcg(parts + size_t(lo_slot) * 1024 + b * 128);
+                                for (int32_t cc = c_lo + 1; cc <= c_hi; cc += 8) {
+                                    float t[8];
+#pragma unroll
+                                    for (int z = 0; z < 8; ++z) t[z] = __ldcg(parts + size_t(2 * min(cc + z, c_hi)) * 1024 + b * 128);
+#pragma unroll
+                                    for (int z = 0; z < 8; ++z)
+                                        if (cc + z <= c_hi) v += t[z];
+                                }
                                 const int64_t idx = int64_t(b) * job.N + n;
                                 if (job.y_dtype == QGEMV_OUT_F32) {
-                                    static_cast<float*>(job.y)[idx] = v[b];
+                                    static_cast<float*>(job.y)[idx] = v;
                                 } else {
-                                    static_cast<__nv_bfloat16*>(job.y)[idx] = __float2bfloat16_rn(v[b]);
+                                    static_cast<__nv_bfloat16*>(job.y)[idx] = __float2bfloat16_rn(v);
                                 }
                             }
                         }
                     }
-                };
-                if (whole) {
-                    store_row(val);
-                } else {
-                    float* slot = P.ws + (size_t(j & 1) * size_t(2 * grid) + size_t(my_slot)) * 1024 + row;
-#pragma unroll
-                    for (int b = 0; b < 8; ++b)
-                        if (b < Bl) __stcg(slot + b * 128, val[b]);
                 }
-                ++nseg;
-            }
-            if (P.trace && ct == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 2] = globaltimer_ns();
-            // ---- this CTA's results and parts of job j are stored: arrive ----
-            named_bar_sync(1, kTcConvThreads);
-            grid_arrive();
-            job = next;
-        }
-        // ---- the last job's split tile, once every CTA has arrived; then leave the counters at zero ----
-        if (!*decision) {
-            grid_wait(P.n_jobs);
-            if (ct == 0) *decision = *abort_flag;
-            named_bar_sync(1, kTcConvThreads);
-            if (!*decision) {
-                finalize_pending();
-                named_bar_sync(1, kTcConvThreads);
-                if (ct == 0 && atom_release_add(P.barrier + 1, 1u) == unsigned(grid) - 1u) {
-                    P.barrier[0] = 0u;  // the last CTA to leave: nobody polls any more
-                    P.barrier[1] = 0u;
-                }
+                if (P.trace && gt == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 6] = globaltimer_ns();
+                named_bar_sync(bar_id, 128);
+                if (gt == 0) red_release_add(P.fin + j, 1u);
+                job = next;
             }
         }
+    }
+    // ---- every role is through (or has given up): the last CTA to leave puts the counters back to zero ----
+    __syncthreads();
+    if (threadIdx.x == 0 && !*abort_flag && atom_release_add(P.barrier, 1u) == unsigned(grid) - 1u) {
+        for (int i = 0; i < P.n_jobs; ++i) P.done[i] = 0u, P.fin[i] = 0u;  // nobody polls any more
+        P.barrier[0] = 0u;
     }
     // ---- release tensor memory (always), after every role is done with it ----
     tc_fence_before();

@@ -338,7 +338,7 @@ def test_sequence_bounded_wait_reports_timeout(qg):
     seq.run()
     torch.cuda.synchronize()
     st = h.device_status()
-    assert st.code == qg.ERR_TIMEOUT and 71 <= st.where <= 76
+    assert st.code == qg.ERR_TIMEOUT and 71 <= st.where <= 82
     seq.destroy()
     for w in ws:
         w.unload()
@@ -355,3 +355,52 @@ def test_sequence_bounded_wait_reports_timeout(qg):
     for w in ws:
         w.unload()
     h2.close()
+
+
+def test_sequence_independent_and_distant_dependencies(qg, handle):
+    """Twelve jobs: most independent of one another (no barrier between them: their digit planes are
+    made while the job before still multiplies, and the parts buffers wrap around), two that read
+    the output of a job two and five places back."""
+    import torch
+    B = 2
+    shapes = [(640, 1024), (4096, 512), (256, 4160), (1000, 640), (6144, 1024), (512, 256),
+              (2048, 2048), (384, 4096), (128, 1024), (3000, 320), (768, 640), (130, 2048)]
+    mats, ws, xh, xd, ys = [], [], [], [], []
+    for i, (N, K) in enumerate(shapes):
+        codes, scales, ts = O.make_nvfp4(N, K, seed=200 + i, ts=0.03)
+        mats.append((codes, scales, ts))
+        ws.append(handle.load(qg.pack(qg.FMT_NVFP4_TC, codes, scales, ts)))
+        xh.append(O.make_x(B, K, seed=300 + i))
+        xd.append(U.dev_u16(xh[-1]))
+        ys.append(torch.full((B, N), float("nan"), dtype=torch.bfloat16, device="cuda"))
+    # job 3 (K = 640) reads y of job 0 (N = 640); job 10 (K = 640) reads y of job 0 as well... and
+    # job 8 (K = 1024) reads nothing new.  Job 5 (K = 256)'s input is y of job 2?  No: N of job 2 is 256.
+    src = {3: 0, 10: 0, 5: 2}
+    jobs = []
+    for i in range(len(shapes)):
+        xp = ys[src[i]].data_ptr() if i in src else xd[i].data_ptr()
+        jobs.append((ws[i], xp, ys[i].data_ptr(), qg.OUT_BF16))
+    seq = handle.sequence(jobs, B)
+    for rep in range(3):
+        for y in ys:
+            y.fill_(float("nan"))
+        seq.run()
+        torch.cuda.synchronize()
+        U.status_ok(handle)
+        outs = [y.view(torch.int16).cpu().numpy().view(np.uint16) for y in ys]
+        for i, (codes, scales, ts) in enumerate(mats):
+            xin = outs[src[i]] if i in src else xh[i]
+            ref = O.gemv_nvfp4_f64(codes, scales, ts, xin)
+            assert not np.isnan(O.bf16_decode(outs[i])).any(), (rep, i)
+            assert O.rel_l2(O.bf16_decode(outs[i]), ref) < TOL_BF16, (rep, i)
+    # bit-equal to one launch per GEMV
+    keep = [o.copy() for o in outs]
+    for i, (w, xp, yp, dt) in enumerate(jobs):
+        ys[i].fill_(float("nan"))
+        handle.gemv(w, xp, B, yp, dt)
+    torch.cuda.synchronize()
+    for i, y in enumerate(ys):
+        assert np.array_equal(y.view(torch.int16).cpu().numpy().view(np.uint16), keep[i]), i
+    seq.destroy()
+    for w in ws:
+        w.unload()
