@@ -33,7 +33,8 @@
 
 namespace qg {
 
-constexpr int kSeqPartBufs = 8;  // jobs a CTA may run ahead of the slowest one before it waits for its parts buffer
+constexpr int kSeqPartBufs = 8;
+constexpr int kSeqPlaneBufs = 3;  // buffers of digit planes: the PLANES group may be this many jobs ahead of the epilogues  // jobs a CTA may run ahead of the slowest one before it waits for its parts buffer
 
 struct SeqJob {               // 64 bytes, device memory
     const uint8_t* payload;   // items of the weight: (tile * kt + item) * 4608
@@ -71,22 +72,23 @@ struct SeqSmem {
     static constexpr int kBarEmpty = 128;   // kTcMaxRing
     static constexpr int kBarDFull = 256;   // 2
     static constexpr int kBarDFree = 272;   // 2
-    static constexpr int kBarXReady = 288;  // 2: one per plane buffer
-    static constexpr int kBarEDone = 656;   // 2: the epilogues of the job that used a plane buffer are through
-    static constexpr int kBarMDone = 696;   // 2: the MMA issuer is through with the job that used a plane buffer
+    static constexpr int kBarXReady = 704;  // kSeqPlaneBufs: the digit planes in a buffer are ready
+    static constexpr int kBarEDone = 736;   // kSeqPlaneBufs: the epilogues of the job that used a plane buffer are through
+    static constexpr int kBarMDone = 768;   // kSeqPlaneBufs: the MMA issuer is through with the job that used a plane buffer
+    static constexpr int kRange = 800;      // [kSeqPlaneBufs][2] ints: this CTA's item range of the job in a plane buffer
+    static constexpr int kRowMax = 832;     // [kSeqPlaneBufs][8] words: largest |bf16| pattern per activation row
     static constexpr int kBarDrain = 304;
     static constexpr int kTmemPtr = 312;
     static constexpr int kAbort = 316;
-    static constexpr int kRowMax = 320;     // [plane buffer][8] words: largest |bf16| pattern per activation row
     static constexpr int kWarpMax = 384;    // kTcConvWarps x 8 words: the same per converting warp
     static constexpr int kIssued = 640;
     static constexpr int kConsumed = 644;
-    static constexpr int kDecision = 672;   // [3] every warp group's common sample of the abort flag
+    static constexpr int kDecision = 928;   // [2][4] every warp group's common samples of the abort flag
     static constexpr int kFinAll = 688;     // jobs up to this index are added up on every CTA (-1: none)
     static constexpr int kSfb = 1024;       // 512 bytes
     static constexpr int kX = 1536;
-    // two buffers of digit planes (jobs alternate), then the ring
-    __host__ __device__ static constexpr int ring_off(int x_slots, int npad) { return (kX + 2 * x_slots * npad * 32 + 127) / 128 * 128; }
+    // kSeqPlaneBufs buffers of digit planes (jobs take them in turn), then the ring
+    __host__ __device__ static constexpr int ring_off(int x_slots, int npad) { return (kX + kSeqPlaneBufs * x_slots * npad * 32 + 127) / 128 * 128; }
     __host__ __device__ static constexpr int total(int x_slots, int npad, int ring, int stage_items) {
         return ring_off(x_slots, npad) + ring * stage_items * kTcItemBytes;
     }
@@ -162,13 +164,12 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
             mbar_init(sbase + SeqSmem::kBarDFull + 8 * b, 1);
             mbar_init(sbase + SeqSmem::kBarDFree + 8 * b, 4);
         }
-        mbar_init(sbase + SeqSmem::kBarXReady, 1);
-        mbar_init(sbase + SeqSmem::kBarXReady + 8, 1);
         mbar_init(sbase + SeqSmem::kBarDrain, 1);
-        mbar_init(sbase + SeqSmem::kBarEDone, 1);
-        mbar_init(sbase + SeqSmem::kBarEDone + 8, 1);
-        mbar_init(sbase + SeqSmem::kBarMDone, 1);
-        mbar_init(sbase + SeqSmem::kBarMDone + 8, 1);
+        for (int b = 0; b < kSeqPlaneBufs; ++b) {
+            mbar_init(sbase + SeqSmem::kBarXReady + 8 * b, 1);
+            mbar_init(sbase + SeqSmem::kBarEDone + 8 * b, 1);
+            mbar_init(sbase + SeqSmem::kBarMDone + 8 * b, 1);
+        }
         *reinterpret_cast<volatile int*>(sq_smem + SeqSmem::kFinAll) = -1;
         *abort_flag = 0;
         *n_issued = 0;
@@ -246,17 +247,8 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 SeqJob next = job;
                 if (j + 1 < P.n_jobs) next = seq_load_job(P.jobs + j + 1);
                 const int32_t kt_len = job.kt;
-                const int gj = seq_job_grid(job.tiles * kt_len, grid);
-                int32_t r_begin, r_end;
-                seq_range(job.tiles * kt_len, cta, gj, r_begin, r_end);
-                const int32_t n_items = r_end - r_begin;
-                const int32_t xs0 = n_items >= kt_len ? 0 : r_begin % kt_len;
-                GsWalker wk;
-                seq_walker(wk, job.tiles * kt_len, kt_len, cta, gj);
-                GsSeg sg;
-                bool have = wk.next(sg);
                 // the digit planes of this job (every CTA signals, also one without items)
-                if (!mbar_wait(sbase + SeqSmem::kBarXReady + 8 * (j & 1), uint32_t(j >> 1) & 1u, P.spin_limit)) {
+                if (!mbar_wait(sbase + SeqSmem::kBarXReady + 8 * (j % kSeqPlaneBufs), uint32_t(j / kSeqPlaneBufs) & 1u, P.spin_limit)) {
                     report(P.status, QGEMV_ERR_TIMEOUT, 72, j);
                     *abort_flag = 1;
                     ok = false;
@@ -264,6 +256,15 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 }
                 tc_fence_after();
                 if (P.trace) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 3] = globaltimer_ns();
+                // this CTA's item range of the job, computed by the PLANES group
+                const volatile int* rg = reinterpret_cast<const volatile int*>(sq_smem + SeqSmem::kRange) + (j % kSeqPlaneBufs) * 2;
+                const int32_t r_begin = rg[0], r_end = rg[1];
+                const int32_t n_items = r_end - r_begin;
+                const int32_t xs0 = n_items >= kt_len ? 0 : r_begin % kt_len;
+                GsWalker wk;
+                wk.units = kt_len, wk.pos = r_begin, wk.end = r_end;
+                GsSeg sg;
+                bool have = wk.next(sg);
                 if (j == 0) tc_cp_sf2(tmem_sfb, sf_lo | (((sbase + SeqSmem::kSfb) >> 4) & 0x3FFFu), sf_hi);
                 for (; ok && have; have = wk.next(sg)) {
                     // the accumulator is free once the epilogue of the segment before last has read it
@@ -279,7 +280,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                     uint32_t acc = 0;
                     int32_t slot = sg.u0 - xs0;
                     if (slot < 0) slot += kt_len;
-                    uint32_t x_lo = x_lo0 + uint32_t(j & 1) * (xbuf_bytes >> 4) + uint32_t(slot) * xslot16;
+                    uint32_t x_lo = x_lo0 + uint32_t(j % kSeqPlaneBufs) * (xbuf_bytes >> 4) + uint32_t(slot) * xslot16;
                     for (int32_t left = sg.u1 - sg.u0; left > 0; left -= S) {
                         // (the stage was written through the async proxy and is read through it: the
                         // barrier's acquire is all the ordering the MMAs need -- no tcgen05 fence here,
@@ -322,7 +323,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 // Barrier phases are told apart by one parity bit, so nobody may complete a barrier twice
                 // before every waiter has seen the first completion: the planes of job j + 2 are only made
                 // once this thread (here) and the epilogue group are through with job j.
-                if (ok) mbar_arrive(sbase + SeqSmem::kBarMDone + 8 * (j & 1));
+                if (ok) mbar_arrive(sbase + SeqSmem::kBarMDone + 8 * (j % kSeqPlaneBufs));
                 job = next;
             }
             *n_consumed = mi;
@@ -334,7 +335,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
         // every CTA finished?"), each most of a microsecond.  Run one after the other by the same warps
         // they cost 6-7 us per job; so they are dealt to three groups of four warps that only meet
         // through barriers in shared memory and counters in global memory:
-        //   PLANES   (warps 2-5)   digit planes of job j into plane buffer j % 2, up to two jobs ahead of
+        //   PLANES   (warps 2-5)   digit planes of job j into one of kSeqPlaneBufs buffers, that many jobs ahead of
         //                          the epilogues; a job that the host found to depend on an earlier one
         //                          (address ranges) first waits until that job is complete on every CTA
         //   EPILOGUE (warps 6-9)   accumulators of job j's segments -> y rows, or parts of a split tile
@@ -350,12 +351,13 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
         volatile int* fin_all = reinterpret_cast<volatile int*>(sq_smem + SeqSmem::kFinAll);
         // Named barriers have no time-out, so a group leaves its job loop at one place for all its
         // warps: one thread samples the abort flag, everybody reads that sample.
+        int sample_no = 0;  // two sample slots in turn: the next sample cannot overwrite one that is still being read
         auto group_alive = [&]() -> bool {
-            if (gt == 0) *decision = *abort_flag;
+            volatile int* slot = decision + 4 * (sample_no & 1);
+            ++sample_no;
+            if (gt == 0) *slot = *abort_flag;
             named_bar_sync(bar_id, 128);
-            const bool go = *decision == 0;
-            named_bar_sync(bar_id, 128);  // nobody overwrites the sample before everybody has read it
-            return go;
+            return *slot == 0;
         };
         // bounded poll by the group's first thread until *counter == grid (every CTA has passed that point)
         auto poll_all = [&](const unsigned int* counter, int site, int j) {
@@ -387,9 +389,9 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
             for (int j = 0; j < P.n_jobs; ++j) {
                 SeqJob next = job;
                 if (j + 1 < P.n_jobs) next = seq_load_job(P.jobs + j + 1);
-                // plane buffer j % 2 and its row maxima were last used by job j - 2: its epilogues must be through
-                if (j >= 2 && gt == 0 &&
-                    !mbar_wait(sbase + SeqSmem::kBarEDone + 8 * (j & 1), uint32_t((j >> 1) - 1) & 1u, P.spin_limit)) {
+                // the plane buffer and its row maxima were last used by job j - kSeqPlaneBufs: its epilogues must be through
+                if (j >= kSeqPlaneBufs && gt == 0 &&
+                    !mbar_wait(sbase + SeqSmem::kBarEDone + 8 * (j % kSeqPlaneBufs), uint32_t(j / kSeqPlaneBufs - 1) & 1u, P.spin_limit)) {
                     report(P.status, QGEMV_ERR_TIMEOUT, 78, j);
                     *abort_flag = 1;
                 }
@@ -403,7 +405,11 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 const int32_t n_items = r_end - r_begin;
                 const int32_t xs0 = n_items >= kt_len ? 0 : r_begin % kt_len;
                 const int32_t n_slots = n_items >= kt_len ? kt_len : n_items;
-                const uint32_t xb = xbase + uint32_t(j & 1) * xbuf_bytes;
+                const uint32_t xb = xbase + uint32_t(j % kSeqPlaneBufs) * xbuf_bytes;
+                if (gt == 0) {  // for the MMA issuer: one thread there, and 64-bit divisions are slow
+                    volatile int* rg = reinterpret_cast<volatile int*>(sq_smem + SeqSmem::kRange) + (j % kSeqPlaneBufs) * 2;
+                    rg[0] = r_begin, rg[1] = r_end;
+                }
                 if (gt < 32) all_max[gt] = 0u;
                 named_bar_sync(bar_id, 128);
                 const int n_work = n_slots * Bl * 8;
@@ -466,7 +472,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                     if (m) atomicMax(wmax + b, m);
                 }
                 named_bar_sync(bar_id, 128);
-                if (gt < 8) rowmax2[(j & 1) * 8 + gt] = row_max(gt);
+                if (gt < 8) rowmax2[(j % kSeqPlaneBufs) * 8 + gt] = row_max(gt);
 #pragma unroll
                 for (int i = 0; i < kKeep; ++i)
                     if (gt + i * 128 < n_work) store_unit(kb[i], kdst[i], keep[i]);
@@ -478,7 +484,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 }
                 fence_proxy_async_smem();  // the planes are read by the tensor core (async proxy)
                 named_bar_sync(bar_id, 128);
-                if (gt == 0) mbar_arrive(sbase + SeqSmem::kBarXReady + 8 * (j & 1));
+                if (gt == 0) mbar_arrive(sbase + SeqSmem::kBarXReady + 8 * (j % kSeqPlaneBufs));
                 if (P.trace && gt == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 1] = globaltimer_ns();
                 job = next;
             }
@@ -495,8 +501,15 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 const int32_t kt_len = job.kt;
                 const int32_t total = job.tiles * kt_len;
                 const int gj = seq_job_grid(total, grid);
-                int32_t rb, re;
-                seq_range(total, cta, gj, rb, re);
+                // the planes of this job are ready, and with them this CTA's item range (a CTA without items
+                // in a run of jobs would otherwise race ahead of the PLANES group and complete its barrier
+                // twice before that group has looked)
+                if (!*abort_flag && !mbar_wait(sbase + SeqSmem::kBarXReady + 8 * (j % kSeqPlaneBufs), uint32_t(j / kSeqPlaneBufs) & 1u, P.spin_limit)) {
+                    if (gt == 0) report(P.status, QGEMV_ERR_TIMEOUT, 81, j);
+                    *abort_flag = 1;
+                }
+                const volatile int* rg = reinterpret_cast<const volatile int*>(sq_smem + SeqSmem::kRange) + (j % kSeqPlaneBufs) * 2;
+                const int32_t rb = rg[0], re = rg[1];
                 // A split tile's parts go to buffer j % kSeqPartBufs, last used by job j - kSeqPartBufs: every
                 // CTA must have added that job's tiles up (the FINISH group publishes how far that has come)
                 if (re > rb && (rb % kt_len != 0 || re % kt_len != 0) && j >= kSeqPartBufs && gt == 0) {
@@ -512,16 +525,9 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                         }
                     }
                 }
-                // (a CTA without items in a run of jobs would otherwise race ahead of the PLANES group and
-                // complete its barrier twice before that group has looked)
-                if (gt == 0 && !*abort_flag &&
-                    !mbar_wait(sbase + SeqSmem::kBarXReady + 8 * (j & 1), uint32_t(j >> 1) & 1u, P.spin_limit)) {
-                    report(P.status, QGEMV_ERR_TIMEOUT, 81, j);
-                    *abort_flag = 1;
-                }
                 if (!group_alive()) break;
                 GsWalker wk;
-                seq_walker(wk, total, kt_len, cta, gj);
+                wk.units = kt_len, wk.pos = rb, wk.end = re;
                 GsSeg sg;
                 bool ok = true;
                 float scale[8];
@@ -541,7 +547,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                     if (!have_scale) {  // the MMAs of this job have run, so its planes and row maxima are there
 #pragma unroll
                         for (int b = 0; b < 8; ++b)
-                            scale[b] = b < Bl ? job.tensor_scale * pow2i(tc_row_exponent(rowmax2[(j & 1) * 8 + b]) + 7) : 0.f;
+                            scale[b] = b < Bl ? job.tensor_scale * pow2i(tc_row_exponent(rowmax2[(j % kSeqPlaneBufs) * 8 + b]) + 7) : 0.f;
                         have_scale = true;
                     }
                     float val[8];
@@ -591,12 +597,12 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 // this CTA's rows and parts of job j are stored; its plane buffer may be reused
                 named_bar_sync(bar_id, 128);
                 if (gt == 0) {
-                    red_release_add(P.done + j, 1u);
-                    if (!*abort_flag && !mbar_wait(sbase + SeqSmem::kBarMDone + 8 * (j & 1), uint32_t(j >> 1) & 1u, P.spin_limit)) {
+                    if (!*abort_flag && !mbar_wait(sbase + SeqSmem::kBarMDone + 8 * (j % kSeqPlaneBufs), uint32_t(j / kSeqPlaneBufs) & 1u, P.spin_limit)) {
                         report(P.status, QGEMV_ERR_TIMEOUT, 82, j);
                         *abort_flag = 1;
                     }
-                    mbar_arrive(sbase + SeqSmem::kBarEDone + 8 * (j & 1));
+                    mbar_arrive(sbase + SeqSmem::kBarEDone + 8 * (j % kSeqPlaneBufs));  // first: the PLANES group may be waiting
+                    red_release_add(P.done + j, 1u);
                 }
                 job = next;
             }
