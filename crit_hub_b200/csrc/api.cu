@@ -50,7 +50,7 @@ struct qgemv_sequence {
     qg::SeqJob* dev_jobs;
     unsigned int* dev_counters;  // done[n_jobs], fin[n_jobs]: zero between launches
     int n_jobs, B;
-    int grid, npad, x_slots, ring, stage_items;
+    int grid, npad, x_slots, nbuf, ring, stage_items;
     size_t smem;
 };
 
@@ -576,16 +576,21 @@ int qgemv_sequence_create(qgemv_handle* h, const qgemv_job* jobs, int n_jobs, in
     q->x_slots = int(x_slots);
     const int si = h->cfg.tc_stage_items;
     q->stage_items = si >= 8 ? 8 : (si >= 4 ? 4 : (si >= 2 ? 2 : 4));
-    const int base = qg::SeqSmem::ring_off(q->x_slots, q->npad);
     const int cap = (h->cfg.tc_smem_kb > 0 ? std::min(h->cfg.tc_smem_kb, 227) : 227) * 1024;
-    int ring = (cap - base) / (q->stage_items * qg::kTcItemBytes);
-    ring = std::min({ring, qg::kTcMaxRing, qg::SeqSmem::max_ring_items(q->npad) / q->stage_items});
+    // as many plane buffers (jobs the conversion may run ahead) as still leave a ring of four stages
+    int ring = 0;
+    for (q->nbuf = qg::kSeqPlaneBufsMax; q->nbuf >= 1; --q->nbuf) {
+        const int base = qg::SeqSmem::ring_off(q->x_slots, q->npad, q->nbuf);
+        ring = (cap - base) / (q->stage_items * qg::kTcItemBytes);
+        ring = std::min({ring, qg::kTcMaxRing, qg::SeqSmem::max_ring_items(q->npad) / q->stage_items});
+        if (ring >= 4 || q->nbuf == 1) break;
+    }
     if (ring < 2) {
         delete q;
         return QGEMV_ERR_UNSUPPORTED_SHAPE;  // the digit planes of one job leave no room for a ring: call qgemv_gemv per job
     }
     q->ring = ring;
-    q->smem = size_t(qg::SeqSmem::total(q->x_slots, q->npad, ring, q->stage_items));
+    q->smem = size_t(qg::SeqSmem::total(q->x_slots, q->npad, q->nbuf, ring, q->stage_items));
     if (cudaSetDevice(h->cfg.device) != cudaSuccess || cudaMalloc(&q->dev_jobs, size_t(n_jobs) * sizeof(qg::SeqJob)) != cudaSuccess ||
         cudaMemcpy(q->dev_jobs, tab.data(), size_t(n_jobs) * sizeof(qg::SeqJob), cudaMemcpyHostToDevice) != cudaSuccess ||
         cudaMalloc(&q->dev_counters, size_t(2 * n_jobs) * 4) != cudaSuccess ||
@@ -627,6 +632,7 @@ int qgemv_sequence_run(qgemv_handle* h, const qgemv_sequence* q, void* stream) {
     P.npad = q->npad;
     P.ring = q->ring;
     P.x_slots = q->x_slots;
+    P.nbuf = q->nbuf;
     P.debug = h->cfg.debug;
     P.trace = h->tc_trace;
     const dim3 g(unsigned(q->grid)), blk(qg::kSeqThreads);

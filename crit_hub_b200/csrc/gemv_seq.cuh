@@ -34,7 +34,8 @@
 namespace qg {
 
 constexpr int kSeqPartBufs = 8;
-constexpr int kSeqPlaneBufs = 3;  // buffers of digit planes: the PLANES group may be this many jobs ahead of the epilogues  // jobs a CTA may run ahead of the slowest one before it waits for its parts buffer
+constexpr int kSeqPlaneBufsMax = 3;  // buffers of digit planes (1..3, as many as leave room for a ring): the PLANES group
+                                     // may be that many jobs ahead of the epilogues  // jobs a CTA may run ahead of the slowest one before it waits for its parts buffer
 
 struct SeqJob {               // 64 bytes, device memory
     const uint8_t* payload;   // items of the weight: (tile * kt + item) * 4608
@@ -62,7 +63,8 @@ struct SeqParams {
     int32_t n_jobs;
     int32_t B, npad;
     int32_t ring;
-    int32_t x_slots;            // item slots of digit planes in shared memory (the largest any job needs)
+    int32_t x_slots;            // item slots of digit planes in one buffer (the largest any job needs)
+    int32_t nbuf;               // buffers of digit planes, 1..kSeqPlaneBufsMax
     int32_t debug;
     unsigned long long* trace;  // optional diagnostics: per CTA, per job 8 stamps (see qgemv_set_trace), or null
 };
@@ -72,11 +74,11 @@ struct SeqSmem {
     static constexpr int kBarEmpty = 128;   // kTcMaxRing
     static constexpr int kBarDFull = 256;   // 2
     static constexpr int kBarDFree = 272;   // 2
-    static constexpr int kBarXReady = 704;  // kSeqPlaneBufs: the digit planes in a buffer are ready
-    static constexpr int kBarEDone = 736;   // kSeqPlaneBufs: the epilogues of the job that used a plane buffer are through
-    static constexpr int kBarMDone = 768;   // kSeqPlaneBufs: the MMA issuer is through with the job that used a plane buffer
-    static constexpr int kRange = 800;      // [kSeqPlaneBufs][2] ints: this CTA's item range of the job in a plane buffer
-    static constexpr int kRowMax = 832;     // [kSeqPlaneBufs][8] words: largest |bf16| pattern per activation row
+    static constexpr int kBarXReady = 704;  // kSeqPlaneBufsMax: the digit planes in a buffer are ready
+    static constexpr int kBarEDone = 736;   // kSeqPlaneBufsMax: the epilogues of the job that used a plane buffer are through
+    static constexpr int kBarMDone = 768;   // kSeqPlaneBufsMax: the MMA issuer is through with the job that used a plane buffer
+    static constexpr int kRange = 800;      // [kSeqPlaneBufsMax][2] ints: this CTA's item range of the job in a plane buffer
+    static constexpr int kRowMax = 832;     // [kSeqPlaneBufsMax][8] words: largest |bf16| pattern per activation row
     static constexpr int kBarDrain = 304;
     static constexpr int kTmemPtr = 312;
     static constexpr int kAbort = 316;
@@ -87,10 +89,10 @@ struct SeqSmem {
     static constexpr int kFinAll = 688;     // jobs up to this index are added up on every CTA (-1: none)
     static constexpr int kSfb = 1024;       // 512 bytes
     static constexpr int kX = 1536;
-    // kSeqPlaneBufs buffers of digit planes (jobs take them in turn), then the ring
-    __host__ __device__ static constexpr int ring_off(int x_slots, int npad) { return (kX + kSeqPlaneBufs * x_slots * npad * 32 + 127) / 128 * 128; }
-    __host__ __device__ static constexpr int total(int x_slots, int npad, int ring, int stage_items) {
-        return ring_off(x_slots, npad) + ring * stage_items * kTcItemBytes;
+    // nbuf buffers of digit planes (jobs take them in turn), then the ring
+    __host__ __device__ static constexpr int ring_off(int x_slots, int npad, int nbuf) { return (kX + nbuf * x_slots * npad * 32 + 127) / 128 * 128; }
+    __host__ __device__ static constexpr int total(int x_slots, int npad, int nbuf, int ring, int stage_items) {
+        return ring_off(x_slots, npad, nbuf) + ring * stage_items * kTcItemBytes;
     }
     static constexpr int kTmemCols = 512;   // one CTA per SM owns all of it
     __host__ __device__ static constexpr int max_ring_items(int npad) { return (kTmemCols - 2 * npad - 4) / 4; }
@@ -148,7 +150,8 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
     const uint32_t xbase = sbase + SeqSmem::kX;
     const uint32_t xbuf_bytes = uint32_t(P.x_slots) * xslot_bytes;  // one buffer of digit planes
     constexpr uint32_t stage_bytes = uint32_t(S) * kTcItemBytes;
-    const uint32_t ring0 = sbase + uint32_t(SeqSmem::ring_off(P.x_slots, npad));
+    const int nb = P.nbuf;
+    const uint32_t ring0 = sbase + uint32_t(SeqSmem::ring_off(P.x_slots, npad, nb));
     constexpr uint32_t ncols = SeqSmem::kTmemCols;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(sq_smem + SeqSmem::kAbort);
     volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(sq_smem + SeqSmem::kTmemPtr);
@@ -165,7 +168,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
             mbar_init(sbase + SeqSmem::kBarDFree + 8 * b, 4);
         }
         mbar_init(sbase + SeqSmem::kBarDrain, 1);
-        for (int b = 0; b < kSeqPlaneBufs; ++b) {
+        for (int b = 0; b < kSeqPlaneBufsMax; ++b) {
             mbar_init(sbase + SeqSmem::kBarXReady + 8 * b, 1);
             mbar_init(sbase + SeqSmem::kBarEDone + 8 * b, 1);
             mbar_init(sbase + SeqSmem::kBarMDone + 8 * b, 1);
@@ -243,12 +246,14 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
             bool ok = true;
             int mi = 0;  // stages issued
             SeqJob job = seq_load_job(P.jobs);
-            for (int j = 0; j < P.n_jobs && ok; ++j) {
+            int pb = 0;        // plane buffer of job j: j % nbuf, kept as a counter (no division in this thread)
+            uint32_t pph = 0;  // parity of that buffer's use: (j / nbuf) & 1
+            for (int j = 0; j < P.n_jobs && ok; ++j, pph ^= (pb + 1 == nb) ? 1u : 0u, pb = (pb + 1 == nb) ? 0 : pb + 1) {
                 SeqJob next = job;
                 if (j + 1 < P.n_jobs) next = seq_load_job(P.jobs + j + 1);
                 const int32_t kt_len = job.kt;
                 // the digit planes of this job (every CTA signals, also one without items)
-                if (!mbar_wait(sbase + SeqSmem::kBarXReady + 8 * (j % kSeqPlaneBufs), uint32_t(j / kSeqPlaneBufs) & 1u, P.spin_limit)) {
+                if (!mbar_wait(sbase + SeqSmem::kBarXReady + 8 * pb, pph, P.spin_limit)) {
                     report(P.status, QGEMV_ERR_TIMEOUT, 72, j);
                     *abort_flag = 1;
                     ok = false;
@@ -257,7 +262,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 tc_fence_after();
                 if (P.trace) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 3] = globaltimer_ns();
                 // this CTA's item range of the job, computed by the PLANES group
-                const volatile int* rg = reinterpret_cast<const volatile int*>(sq_smem + SeqSmem::kRange) + (j % kSeqPlaneBufs) * 2;
+                const volatile int* rg = reinterpret_cast<const volatile int*>(sq_smem + SeqSmem::kRange) + pb * 2;
                 const int32_t r_begin = rg[0], r_end = rg[1];
                 const int32_t n_items = r_end - r_begin;
                 const int32_t xs0 = n_items >= kt_len ? 0 : r_begin % kt_len;
@@ -280,7 +285,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                     uint32_t acc = 0;
                     int32_t slot = sg.u0 - xs0;
                     if (slot < 0) slot += kt_len;
-                    uint32_t x_lo = x_lo0 + uint32_t(j % kSeqPlaneBufs) * (xbuf_bytes >> 4) + uint32_t(slot) * xslot16;
+                    uint32_t x_lo = x_lo0 + uint32_t(pb) * (xbuf_bytes >> 4) + uint32_t(slot) * xslot16;
                     for (int32_t left = sg.u1 - sg.u0; left > 0; left -= S) {
                         // (the stage was written through the async proxy and is read through it: the
                         // barrier's acquire is all the ordering the MMAs need -- no tcgen05 fence here,
@@ -323,7 +328,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 // Barrier phases are told apart by one parity bit, so nobody may complete a barrier twice
                 // before every waiter has seen the first completion: the planes of job j + 2 are only made
                 // once this thread (here) and the epilogue group are through with job j.
-                if (ok) mbar_arrive(sbase + SeqSmem::kBarMDone + 8 * (j % kSeqPlaneBufs));
+                if (ok) mbar_arrive(sbase + SeqSmem::kBarMDone + 8 * pb);
                 job = next;
             }
             *n_consumed = mi;
@@ -335,7 +340,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
         // every CTA finished?"), each most of a microsecond.  Run one after the other by the same warps
         // they cost 6-7 us per job; so they are dealt to three groups of four warps that only meet
         // through barriers in shared memory and counters in global memory:
-        //   PLANES   (warps 2-5)   digit planes of job j into one of kSeqPlaneBufs buffers, that many jobs ahead of
+        //   PLANES   (warps 2-5)   digit planes of job j into one of nbuf buffers, that many jobs ahead of
         //                          the epilogues; a job that the host found to depend on an earlier one
         //                          (address ranges) first waits until that job is complete on every CTA
         //   EPILOGUE (warps 6-9)   accumulators of job j's segments -> y rows, or parts of a split tile
@@ -386,12 +391,14 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 *reinterpret_cast<volatile uint32_t*>(sq_smem + SeqSmem::kSfb + (n & 31) * 16 + (n >> 5) * 4) = byte * 0x01010101u;
             }
             SeqJob job = seq_load_job(P.jobs);
-            for (int j = 0; j < P.n_jobs; ++j) {
+            int pb = 0;        // plane buffer of job j (j % nbuf) and the parity of its use ((j / nbuf) & 1), as counters
+            uint32_t pph = 0;
+            for (int j = 0; j < P.n_jobs; ++j, pph ^= (pb + 1 == nb) ? 1u : 0u, pb = (pb + 1 == nb) ? 0 : pb + 1) {
                 SeqJob next = job;
                 if (j + 1 < P.n_jobs) next = seq_load_job(P.jobs + j + 1);
-                // the plane buffer and its row maxima were last used by job j - kSeqPlaneBufs: its epilogues must be through
-                if (j >= kSeqPlaneBufs && gt == 0 &&
-                    !mbar_wait(sbase + SeqSmem::kBarEDone + 8 * (j % kSeqPlaneBufs), uint32_t(j / kSeqPlaneBufs - 1) & 1u, P.spin_limit)) {
+                // the plane buffer and its row maxima were last used by job j - nbuf: its epilogues must be through
+                if (j >= nb && gt == 0 &&
+                    !mbar_wait(sbase + SeqSmem::kBarEDone + 8 * pb, (pph ^ 1u), P.spin_limit)) {
                     report(P.status, QGEMV_ERR_TIMEOUT, 78, j);
                     *abort_flag = 1;
                 }
@@ -405,9 +412,9 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 const int32_t n_items = r_end - r_begin;
                 const int32_t xs0 = n_items >= kt_len ? 0 : r_begin % kt_len;
                 const int32_t n_slots = n_items >= kt_len ? kt_len : n_items;
-                const uint32_t xb = xbase + uint32_t(j % kSeqPlaneBufs) * xbuf_bytes;
+                const uint32_t xb = xbase + uint32_t(pb) * xbuf_bytes;
                 if (gt == 0) {  // for the MMA issuer: one thread there, and 64-bit divisions are slow
-                    volatile int* rg = reinterpret_cast<volatile int*>(sq_smem + SeqSmem::kRange) + (j % kSeqPlaneBufs) * 2;
+                    volatile int* rg = reinterpret_cast<volatile int*>(sq_smem + SeqSmem::kRange) + pb * 2;
                     rg[0] = r_begin, rg[1] = r_end;
                 }
                 if (gt < 32) all_max[gt] = 0u;
@@ -472,7 +479,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                     if (m) atomicMax(wmax + b, m);
                 }
                 named_bar_sync(bar_id, 128);
-                if (gt < 8) rowmax2[(j % kSeqPlaneBufs) * 8 + gt] = row_max(gt);
+                if (gt < 8) rowmax2[pb * 8 + gt] = row_max(gt);
 #pragma unroll
                 for (int i = 0; i < kKeep; ++i)
                     if (gt + i * 128 < n_work) store_unit(kb[i], kdst[i], keep[i]);
@@ -484,7 +491,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 }
                 fence_proxy_async_smem();  // the planes are read by the tensor core (async proxy)
                 named_bar_sync(bar_id, 128);
-                if (gt == 0) mbar_arrive(sbase + SeqSmem::kBarXReady + 8 * (j % kSeqPlaneBufs));
+                if (gt == 0) mbar_arrive(sbase + SeqSmem::kBarXReady + 8 * pb);
                 if (P.trace && gt == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 1] = globaltimer_ns();
                 job = next;
             }
@@ -495,7 +502,9 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
             const int row = 32 * q + lane;
             uint32_t nseg = 0;
             SeqJob job = seq_load_job(P.jobs);
-            for (int j = 0; j < P.n_jobs; ++j) {
+            int pb = 0;
+            uint32_t pph = 0;
+            for (int j = 0; j < P.n_jobs; ++j, pph ^= (pb + 1 == nb) ? 1u : 0u, pb = (pb + 1 == nb) ? 0 : pb + 1) {
                 SeqJob next = job;
                 if (j + 1 < P.n_jobs) next = seq_load_job(P.jobs + j + 1);
                 const int32_t kt_len = job.kt;
@@ -504,11 +513,11 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 // the planes of this job are ready, and with them this CTA's item range (a CTA without items
                 // in a run of jobs would otherwise race ahead of the PLANES group and complete its barrier
                 // twice before that group has looked)
-                if (!*abort_flag && !mbar_wait(sbase + SeqSmem::kBarXReady + 8 * (j % kSeqPlaneBufs), uint32_t(j / kSeqPlaneBufs) & 1u, P.spin_limit)) {
+                if (!*abort_flag && !mbar_wait(sbase + SeqSmem::kBarXReady + 8 * pb, pph, P.spin_limit)) {
                     if (gt == 0) report(P.status, QGEMV_ERR_TIMEOUT, 81, j);
                     *abort_flag = 1;
                 }
-                const volatile int* rg = reinterpret_cast<const volatile int*>(sq_smem + SeqSmem::kRange) + (j % kSeqPlaneBufs) * 2;
+                const volatile int* rg = reinterpret_cast<const volatile int*>(sq_smem + SeqSmem::kRange) + pb * 2;
                 const int32_t rb = rg[0], re = rg[1];
                 // A split tile's parts go to buffer j % kSeqPartBufs, last used by job j - kSeqPartBufs: every
                 // CTA must have added that job's tiles up (the FINISH group publishes how far that has come)
@@ -547,7 +556,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                     if (!have_scale) {  // the MMAs of this job have run, so its planes and row maxima are there
 #pragma unroll
                         for (int b = 0; b < 8; ++b)
-                            scale[b] = b < Bl ? job.tensor_scale * pow2i(tc_row_exponent(rowmax2[(j % kSeqPlaneBufs) * 8 + b]) + 7) : 0.f;
+                            scale[b] = b < Bl ? job.tensor_scale * pow2i(tc_row_exponent(rowmax2[pb * 8 + b]) + 7) : 0.f;
                         have_scale = true;
                     }
                     float val[8];
@@ -597,11 +606,11 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 // this CTA's rows and parts of job j are stored; its plane buffer may be reused
                 named_bar_sync(bar_id, 128);
                 if (gt == 0) {
-                    if (!*abort_flag && !mbar_wait(sbase + SeqSmem::kBarMDone + 8 * (j % kSeqPlaneBufs), uint32_t(j / kSeqPlaneBufs) & 1u, P.spin_limit)) {
+                    if (!*abort_flag && !mbar_wait(sbase + SeqSmem::kBarMDone + 8 * pb, pph, P.spin_limit)) {
                         report(P.status, QGEMV_ERR_TIMEOUT, 82, j);
                         *abort_flag = 1;
                     }
-                    mbar_arrive(sbase + SeqSmem::kBarEDone + 8 * (j % kSeqPlaneBufs));  // first: the PLANES group may be waiting
+                    mbar_arrive(sbase + SeqSmem::kBarEDone + 8 * pb);  // first: the PLANES group may be waiting
                     red_release_add(P.done + j, 1u);
                 }
                 job = next;

@@ -84,10 +84,17 @@ class LayerStack:
         n = len(self.calls)
         if self.fused:
             if self.sequence is None:
-                self.sequence = self.handle.sequence(
-                    [(c.weight, xb + c.x_off * xe, yb + c.y_off * ye, self.out_dtype) for c in self.calls], self.batch)
-            self.sequence.run(stream_handle)
-            return
+                from . import ERR_UNSUPPORTED_SHAPE, QgemvError
+                try:
+                    self.sequence = self.handle.sequence(
+                        [(c.weight, xb + c.x_off * xe, yb + c.y_off * ye, self.out_dtype) for c in self.calls], self.batch)
+                except QgemvError as e:  # e.g. activations too large for the persistent kernel: one launch per GEMV
+                    if e.status != ERR_UNSUPPORTED_SHAPE:
+                        raise
+                    self.fused = False
+            if self.fused:
+                self.sequence.run(stream_handle)
+                return
         for i, c in enumerate(self.calls):
             nxt = self.calls[(i + 1) % n].weight if self.prefetch_next and n > 1 else None
             self.handle.gemv(c.weight, xb + c.x_off * xe, self.batch, yb + c.y_off * ye, self.out_dtype,
