@@ -18,6 +18,8 @@ from . import _build
 FMT_NVFP4 = 1
 FMT_FP8 = 2
 FMT_NVFP4_TC = 3   # NVFP4 in the tile order the block-scaled tensor-core GEMV consumes as stored
+JOB_AFTER_PREVIOUS = 1   # qgemv_job.flags: wait for the job before this one
+JOB_ALLREDUCE = 2        # qgemv_job.flags: row-parallel projection, summed over the ranks inside the launch
 OUT_BF16 = 0
 OUT_F32 = 1
 ACT_A16_EXACT = 0
@@ -58,7 +60,8 @@ class Shard(C.Structure):
 
 
 class _Job(C.Structure):
-    _fields_ = [("w", C.c_void_p), ("x", C.c_void_p), ("y", C.c_void_p), ("y_dtype", C.c_int32), ("flags", C.c_int32)]
+    _fields_ = [("w", C.c_void_p), ("x", C.c_void_p), ("y", C.c_void_p), ("y_dtype", C.c_int32), ("flags", C.c_int32),
+                ("x_stride", C.c_int64)]
 
 
 class _DevStatus(C.Structure):
@@ -105,6 +108,10 @@ def _load() -> C.CDLL:
     L.qgemv_load.argtypes = [vp, vp, sz, C.POINTER(vp)]
     L.qgemv_load_stacked.argtypes = [vp, vp, sz, i32, C.POINTER(vp)]
     L.qgemv_unload.argtypes = [vp, vp]
+    L.qgemv_load_device.argtypes = [vp, i32, vp, vp, C.c_float, i64, i64, C.POINTER(Shard), vp, C.POINTER(vp)]
+    L.qgemv_weight_read.argtypes = [vp, vp, vp, sz]
+    L.qgemv_pack_header.argtypes = [i32, C.c_float, i64, i64, C.POINTER(Shard), vp]
+    L.qgemv_set_host_threads.argtypes = [i32]
     L.qgemv_weight_bytes.restype = i64
     L.qgemv_weight_bytes.argtypes = [vp]
     L.qgemv_gemv.argtypes = [vp, vp, vp, i32, vp, i32, vp]
@@ -117,6 +124,9 @@ def _load() -> C.CDLL:
     L.qgemv_tp_create.argtypes = [vp, i32, i32, i64, vp]
     L.qgemv_tp_connect.argtypes = [vp, vp]
     L.qgemv_tp_allreduce.argtypes = [vp, vp, i32, i64, vp]
+    L.qgemv_tp_allgather.argtypes = [vp, vp, vp, i32, i64, vp]
+    L.qgemv_tp_buffer.argtypes = [vp, C.POINTER(vp), C.POINTER(sz)]
+    L.qgemv_tp_connect_ptrs.argtypes = [vp, C.POINTER(vp)]
     L.qgemv_gemv_noalloc.argtypes = [vp, vp, vp, i32, vp, i32, vp]
     L.qgemv_noalloc_last_status.argtypes = [vp, C.POINTER(_DevStatus)]
     L.qgemv_moe_gemv.argtypes = [vp, vp, vp, vp, i32, i32, i32, vp, i32, vp]
@@ -145,6 +155,11 @@ def _np_ptr(a: np.ndarray) -> C.c_void_p:
 
 
 # ---- host packer ---------------------------------------------------------------------------------
+def set_host_threads(n: int) -> None:
+    """Threads of the host packer (a launcher may have exported OMP_NUM_THREADS=1)."""
+    _check(_load().qgemv_set_host_threads(int(n)), "set_host_threads")
+
+
 def packed_size(fmt: int, N: int, K: int, shard: Shard | None = None) -> int:
     return int(_load().qgemv_packed_size(fmt, N, K, C.byref(shard) if shard else None))
 
@@ -214,6 +229,12 @@ class Weight:
         """Algorithmic weight bytes of one matrix (codes + scales)."""
         return int(_load().qgemv_weight_bytes(self._ptr))
 
+    def read_blob(self) -> np.ndarray:
+        """The packed blob(s) as they sit in device memory, copied back to the host."""
+        out = np.empty(self.n_stack * packed_size(self.fmt, self.N, self.K), dtype=np.uint8)
+        _check(_load().qgemv_weight_read(self._owner._ptr, self._ptr, _np_ptr(out), out.size), "weight_read")
+        return out
+
     def unload(self) -> None:
         if self._ptr:
             _check(_load().qgemv_unload(self._owner._ptr, self._ptr), "unload")
@@ -269,6 +290,17 @@ class QGemv:
         _check(_load().qgemv_load(self._ptr, _np_ptr(blob), blob.size, C.byref(w)), "load")
         return Weight(self, w.value, fmt, N, K, 1)
 
+    def load_device(self, fmt: int, codes_ptr: int, scales_ptr: int, N: int, K: int, tensor_scale: float = 1.0,
+                    shard: Shard | None = None, stream: int = 0) -> Weight:
+        """Weight from canonical NVFP4 arrays in device memory (codes u8 [N][K/2], scales u8 [N][K/16]),
+        packed by a kernel; NVFP4_TC only.  The arrays may be freed when this returns."""
+        w = C.c_void_p()
+        _check(_load().qgemv_load_device(self._ptr, fmt, codes_ptr, scales_ptr, C.c_float(tensor_scale), N, K,
+                                         C.byref(shard) if shard else None, stream, C.byref(w)), "load_device")
+        n = (shard.n1 - shard.n0) if shard else N
+        k = (shard.k1 - shard.k0) if shard else K
+        return Weight(self, w.value, fmt, n, k, 1)
+
     def load_stacked(self, blobs: np.ndarray) -> Weight:
         """blobs: u8 [E][bytes_each], every row a packed blob of the same shape and format."""
         if blobs.ndim != 2:
@@ -288,12 +320,15 @@ class QGemv:
             _check(_load().qgemv_gemv_prefetch(self._ptr, w._ptr, x_ptr, B, y_ptr, y_dtype, next_weight._ptr,
                                                stream), "gemv")
 
-    def sequence(self, jobs: list[tuple[Weight, int, int, int]], B: int) -> "Sequence":
-        """jobs: (weight, x_ptr, y_ptr, y_dtype) in execution order; one persistent launch runs them all,
-        each job free to read what the one before it wrote.  NVFP4_TC weights only."""
+    def sequence(self, jobs: list[tuple], B: int, chained: bool = False) -> "Sequence":
+        """jobs: (weight, x_ptr, y_ptr, y_dtype) in execution order; one persistent launch runs them all.
+        A job waits for the earlier jobs whose buffers it reads or overwrites; with `chained` every job
+        also waits for the one before it, whatever the addresses say.  NVFP4_TC weights only."""
         arr = (_Job * len(jobs))()
-        for i, (w, x_ptr, y_ptr, y_dtype) in enumerate(jobs):
-            arr[i] = _Job(w._ptr, x_ptr, y_ptr, y_dtype, 0)
+        for i, jb in enumerate(jobs):   # (weight, x_ptr, y_ptr, y_dtype[, flags[, x_stride]])
+            w, x_ptr, y_ptr, y_dtype = jb[:4]
+            flags = (jb[4] if len(jb) > 4 else 0) | (JOB_AFTER_PREVIOUS if chained else 0)
+            arr[i] = _Job(w._ptr, x_ptr, y_ptr, y_dtype, flags, jb[5] if len(jb) > 5 else 0)
         q = C.c_void_p()
         _check(_load().qgemv_sequence_create(self._ptr, arr, len(jobs), B, C.byref(q)), "sequence_create")
         return Sequence(self, q.value, len(jobs), B)
@@ -331,6 +366,21 @@ class QGemv:
 
     def tp_allreduce(self, y_ptr: int, y_dtype: int, n: int, stream: int = 0) -> None:
         _check(_load().qgemv_tp_allreduce(self._ptr, y_ptr, y_dtype, n, stream), "tp_allreduce")
+
+    def tp_allgather(self, shard_ptr: int, y_ptr: int, y_dtype: int, n_shard: int, stream: int = 0) -> None:
+        """y[r * n_shard + e] = rank r's shard[e]."""
+        _check(_load().qgemv_tp_allgather(self._ptr, shard_ptr, y_ptr, y_dtype, n_shard, stream), "tp_allgather")
+
+    def tp_buffer(self) -> tuple[int, int]:
+        """(device pointer, bytes) of this rank's exchange buffer."""
+        p, n = C.c_void_p(), C.c_size_t()
+        _check(_load().qgemv_tp_buffer(self._ptr, C.byref(p), C.byref(n)), "tp_buffer")
+        return int(p.value), int(n.value)
+
+    def tp_connect_ptrs(self, peer_ptrs: list[int]) -> None:
+        """Single process, several GPUs (or a test): the other ranks' buffers as device pointers, rank order."""
+        arr = (C.c_void_p * len(peer_ptrs))(*[C.c_void_p(p) for p in peer_ptrs])
+        _check(_load().qgemv_tp_connect_ptrs(self._ptr, arr), "tp_connect_ptrs")
 
     def device_status(self, stream: int = 0) -> DeviceStatus:
         st = _DevStatus()

@@ -31,7 +31,10 @@ struct qgemv_handle {
     int64_t tp_max_elems;
     uint8_t* tp_local;                     // this rank's exchange buffer
     uint8_t* tp_peer[qg::kTpMaxWorld];     // every rank's buffer as mapped here (tp_peer[rank] == tp_local)
-    uint32_t* tp_epochs;
+    uint32_t* tp_epochs;                   // [0] exchanges completed by qgemv_tp_allreduce / _allgather, [1] their arrival counter
+    bool tp_ipc_opened[qg::kTpMaxWorld];   // mapped by qgemv_tp_connect (closed on destroy), not handed in as a pointer
+    int64_t tp_seq_cursor;                 // elements [tp_seq_cursor, tp_max_elems) of every slot belong to job lists
+    int64_t tp_call_high;                  // the longest vector a stand-alone exchange has used so far
     // skinny GEMM: f16 activation tiles + per-row exponents, grown on demand
     uint8_t* gs_ws;
     size_t gs_ws_bytes;
@@ -41,17 +44,20 @@ struct qgemv_handle {
     float* tc_ws;
     unsigned long long* tc_trace;  // caller's device buffer for phase timestamps, or null
     unsigned int* seq_barrier;     // CTAs that have left a GEMV-sequence launch, zero between launches
-    float* seq_parts;              // its parts buffers: [kSeqPartBufs][2 * grid][8][128] fp32
+    unsigned long long* seq_parts; // its parts buffers: [kSeqPartBufs][2 * grid][8][128] pairs {fp32, tag}
     size_t tc_ws_bytes;
     std::vector<qgemv_sequence*>* sequences;  // live job lists: their counters are cleared after a reported error
 };
 
 struct qgemv_sequence {
     qg::SeqJob* dev_jobs;
-    unsigned int* dev_counters;  // done[n_jobs], fin[n_jobs]: zero between launches
+    unsigned int* dev_counters;  // fin[n_jobs]: zero between launches; [n_jobs]: launches of this list
+    uint32_t* dev_pub;           // outputs that later jobs of the list read as their activations, as tagged words
     int n_jobs, B;
     int grid, npad, x_slots, nbuf, ring, stage_items;
     size_t smem;
+    int64_t xchg_elems;  // elements of every exchange slot held by this list's all-reduce jobs (0: none)
+    int64_t xchg_first;  // where they start
 };
 
 struct qgemv_weight {
@@ -364,7 +370,8 @@ int qgemv_init(const qgemv_config* cfg, qgemv_handle** out) {
     h->status_dev = nullptr;
     h->tp_rank = 0, h->tp_world = 0, h->tp_max_elems = 0;
     h->tp_local = nullptr, h->tp_epochs = nullptr;
-    for (int i = 0; i < qg::kTpMaxWorld; ++i) h->tp_peer[i] = nullptr;
+    for (int i = 0; i < qg::kTpMaxWorld; ++i) h->tp_peer[i] = nullptr, h->tp_ipc_opened[i] = false;
+    h->tp_seq_cursor = 0, h->tp_call_high = 0;
     h->gs_ws = nullptr, h->gs_ws_bytes = 0;
     h->chunk_ws = nullptr;
     h->tc_ws = nullptr, h->tc_trace = nullptr, h->seq_barrier = nullptr, h->seq_parts = nullptr;
@@ -373,7 +380,7 @@ int qgemv_init(const qgemv_config* cfg, qgemv_handle** out) {
     h->tc_ws_bytes = tc_ws_bytes;
     if (cudaMalloc(&h->tc_ws, tc_ws_bytes) != cudaSuccess || cudaMemset(h->tc_ws, 0, tc_ws_bytes) != cudaSuccess ||
         cudaMalloc(&h->seq_barrier, 256) != cudaSuccess || cudaMemset(h->seq_barrier, 0, 256) != cudaSuccess ||
-        cudaMalloc(&h->seq_parts, size_t(qg::kSeqPartBufs) * size_t(2) * size_t(std::max(h->sm_count, cfg->grid_override)) * 4096) != cudaSuccess ||
+        cudaMalloc(&h->seq_parts, size_t(qg::kSeqPartBufs) * size_t(2) * size_t(std::max(h->sm_count, cfg->grid_override)) * 8192) != cudaSuccess ||
         cudaMalloc(&h->chunk_ws, kChunkWsBytes) != cudaSuccess ||
         cudaMalloc(&h->status_dev, 4 * sizeof(int32_t)) != cudaSuccess ||
         cudaMemset(h->status_dev, 0, 4 * sizeof(int32_t)) != cudaSuccess) {
@@ -419,7 +426,7 @@ int qgemv_destroy(qgemv_handle* h) {
     if (!h) return QGEMV_ERR_INVALID_ARG;
     cudaSetDevice(h->cfg.device);
     for (int i = 0; i < h->tp_world; ++i)
-        if (i != h->tp_rank && h->tp_peer[i]) cudaIpcCloseMemHandle(h->tp_peer[i]);
+        if (i != h->tp_rank && h->tp_peer[i] && h->tp_ipc_opened[i]) cudaIpcCloseMemHandle(h->tp_peer[i]);
     cudaFree(h->tp_local);
     cudaFree(h->tp_epochs);
     cudaFree(h->gs_ws);
@@ -441,20 +448,11 @@ int qgemv_set_trace(qgemv_handle* h, void* dev_buf) {
     return QGEMV_OK;
 }
 
-int qgemv_load_stacked(qgemv_handle* h, const void* host_blobs, size_t bytes_each, int n_stacked,
-                       qgemv_weight** out) {
-    if (!h || !host_blobs || !out || n_stacked <= 0) return QGEMV_ERR_INVALID_ARG;
-    *out = nullptr;
-    const uint8_t* src = static_cast<const uint8_t*>(host_blobs);
-    const qg_blob_header* h0 = reinterpret_cast<const qg_blob_header*>(src);
-    std::vector<float> ts(size_t(n_stacked), 1.0f);
-    for (int i = 0; i < n_stacked; ++i) {
-        const uint8_t* b = src + size_t(i) * bytes_each;
-        if (qgemv_blob_verify(b, bytes_each) != QGEMV_OK) return QGEMV_ERR_BAD_BLOB;
-        const qg_blob_header* hi = reinterpret_cast<const qg_blob_header*>(b);
-        if (hi->fmt != h0->fmt || hi->N != h0->N || hi->K != h0->K) return QGEMV_ERR_BAD_BLOB;
-        ts[size_t(i)] = hi->tensor_scale;
-    }
+namespace {
+// Allocates a weight object and its device buffers for n_stacked blobs with header `h0`; the blob
+// bytes themselves are put there by the caller.
+int new_weight(qgemv_handle* h, const qg_blob_header* h0, int n_stacked, size_t bytes_each, const float* ts,
+               qgemv_weight** out) {
     if (h0->N > INT32_MAX || h0->K > INT32_MAX || h0->n_panels * h0->units_per_panel > (int64_t(1) << 40))
         return QGEMV_ERR_UNSUPPORTED_SHAPE;
     if (h0->fmt == QGEMV_FMT_NVFP4_TC &&
@@ -478,7 +476,7 @@ int qgemv_load_stacked(qgemv_handle* h, const void* host_blobs, size_t bytes_eac
         delete w;
         return QGEMV_ERR_INVALID_ARG;
     }
-    std::memcpy(w->host_tensor_scale, ts.data(), size_t(n_stacked) * 4);
+    std::memcpy(w->host_tensor_scale, ts, size_t(n_stacked) * 4);
     w->max_prob = n_stacked > 1 ? n_stacked + kMaxMoeSlots / 8 : 1;
     const size_t n_counters = size_t(w->max_prob) * size_t(w->n_panels);
     const size_t ws_bytes = size_t(2) * size_t(gemv_grid(h) > h->sm_count ? gemv_grid(h) : h->sm_count) * 512;
@@ -488,13 +486,76 @@ int qgemv_load_stacked(qgemv_handle* h, const void* host_blobs, size_t bytes_eac
               cudaMalloc(&w->counters, n_counters * 4) == cudaSuccess;
     if (ok && n_stacked > 1)
         ok = cudaMalloc(&w->prob, (size_t(w->max_prob) * qg::kProbInts + 1) * 4) == cudaSuccess;
-    ok = ok && cudaMemcpy(w->dev_blob, src, size_t(n_stacked) * bytes_each, cudaMemcpyHostToDevice) == cudaSuccess &&
-         cudaMemcpy(w->dev_tensor_scale, ts.data(), size_t(n_stacked) * 4, cudaMemcpyHostToDevice) == cudaSuccess &&
+    ok = ok && cudaMemcpy(w->dev_tensor_scale, ts, size_t(n_stacked) * 4, cudaMemcpyHostToDevice) == cudaSuccess &&
          cudaMemset(w->counters, 0, n_counters * 4) == cudaSuccess &&
          cudaMemset(w->ws, 0, ws_bytes) == cudaSuccess;
     if (ok && w->prob) ok = cudaMemset(w->prob, 0, (size_t(w->max_prob) * qg::kProbInts + 1) * 4) == cudaSuccess;
     if (!ok) {
-        (void)cudaGetLastError();
+        g_last_cuda_error = cudaGetLastError();
+        qgemv_unload(h, w);
+        return QGEMV_ERR_CUDA;
+    }
+    *out = w;
+    return QGEMV_OK;
+}
+}  // namespace
+
+int qgemv_load_stacked(qgemv_handle* h, const void* host_blobs, size_t bytes_each, int n_stacked,
+                       qgemv_weight** out) {
+    if (!h || !host_blobs || !out || n_stacked <= 0) return QGEMV_ERR_INVALID_ARG;
+    *out = nullptr;
+    const uint8_t* src = static_cast<const uint8_t*>(host_blobs);
+    const qg_blob_header* h0 = reinterpret_cast<const qg_blob_header*>(src);
+    std::vector<float> ts(size_t(n_stacked), 1.0f);
+    for (int i = 0; i < n_stacked; ++i) {
+        const uint8_t* b = src + size_t(i) * bytes_each;
+        if (qgemv_blob_verify(b, bytes_each) != QGEMV_OK) return QGEMV_ERR_BAD_BLOB;
+        const qg_blob_header* hi = reinterpret_cast<const qg_blob_header*>(b);
+        if (hi->fmt != h0->fmt || hi->N != h0->N || hi->K != h0->K) return QGEMV_ERR_BAD_BLOB;
+        ts[size_t(i)] = hi->tensor_scale;
+    }
+    qgemv_weight* w = nullptr;
+    const int rc = new_weight(h, h0, n_stacked, bytes_each, ts.data(), &w);
+    if (rc != QGEMV_OK) return rc;
+    if (cudaMemcpy(w->dev_blob, src, size_t(n_stacked) * bytes_each, cudaMemcpyHostToDevice) != cudaSuccess) {
+        g_last_cuda_error = cudaGetLastError();
+        qgemv_unload(h, w);
+        return QGEMV_ERR_CUDA;
+    }
+    *out = w;
+    return QGEMV_OK;
+}
+
+int qgemv_load_device(qgemv_handle* h, int fmt, const void* codes_dev, const void* scales_dev, float tensor_scale,
+                      int64_t N, int64_t K, const qgemv_shard* shard, void* stream, qgemv_weight** out) {
+    if (!h || !codes_dev || !scales_dev || !out) return QGEMV_ERR_INVALID_ARG;
+    *out = nullptr;
+    if (fmt != QGEMV_FMT_NVFP4_TC) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(codes_dev) & 7u) != 0) return QGEMV_ERR_INVALID_ARG;  // read in 8-byte groups
+    qg_blob_header hd;
+    const int rc0 = qgemv_pack_header(fmt, tensor_scale, N, K, shard, &hd);
+    if (rc0 != QGEMV_OK) return rc0;
+    qgemv_weight* w = nullptr;
+    const int rc = new_weight(h, &hd, 1, size_t(QG_HEADER_BYTES + hd.aux_bytes + hd.payload_bytes), &tensor_scale, &w);
+    if (rc != QGEMV_OK) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    qg::PackTcParams P;
+    P.codes = static_cast<const uint8_t*>(codes_dev);
+    P.scales = static_cast<const uint8_t*>(scales_dev);
+    P.payload = w->dev_blob + QG_HEADER_BYTES + hd.aux_bytes;
+    P.N = N, P.K = K;
+    P.n0 = shard ? shard->n0 : 0, P.k0 = shard ? shard->k0 : 0;
+    P.n = hd.N, P.k = hd.K;
+    P.tiles = hd.n_panels / 8, P.kt = hd.units_per_panel;
+    const int64_t chunks = P.tiles * P.kt * (QG_TC_ITEM_BYTES / 16);
+    const unsigned blocks = unsigned(std::min<int64_t>((chunks + 255) / 256, int64_t(h->sm_count) * 16));
+    bool ok = cudaMemcpyAsync(w->dev_blob, &hd, sizeof hd, cudaMemcpyHostToDevice, st) == cudaSuccess;
+    if (ok) {
+        qg::pack_tc_kernel<<<blocks, 256, 0, st>>>(P);
+        ok = cudaGetLastError() == cudaSuccess && cudaStreamSynchronize(st) == cudaSuccess;  // hd lives on this stack frame
+    }
+    if (!ok) {
+        g_last_cuda_error = cudaGetLastError();
         qgemv_unload(h, w);
         return QGEMV_ERR_CUDA;
     }
@@ -519,6 +580,14 @@ int qgemv_unload(qgemv_handle* h, qgemv_weight* w) {
     return QGEMV_OK;
 }
 
+int qgemv_weight_read(qgemv_handle* h, const qgemv_weight* w, void* host_out, size_t bytes) {
+    if (!h || !w || !host_out) return QGEMV_ERR_INVALID_ARG;
+    if (bytes != size_t(w->n_stack) * w->blob_bytes) return QGEMV_ERR_INVALID_ARG;
+    QG_CUDA(cudaSetDevice(h->cfg.device));
+    QG_CUDA(cudaMemcpy(host_out, w->dev_blob, bytes, cudaMemcpyDeviceToHost));
+    return QGEMV_OK;
+}
+
 int64_t qgemv_weight_bytes(const qgemv_weight* w) {
     if (!w) return QGEMV_ERR_INVALID_ARG;
     if (w->fmt != QGEMV_FMT_FP8) return w->N * w->K / 2 + w->N * w->K / 16 + 4;
@@ -532,7 +601,7 @@ int qgemv_sequence_create(qgemv_handle* h, const qgemv_job* jobs, int n_jobs, in
     const int grid = gemv_grid(h);
     if (grid > h->sm_count) return QGEMV_ERR_UNSUPPORTED_SHAPE;  // the CTAs wait on one another: one per SM at most
     std::vector<qg::SeqJob> tab(static_cast<size_t>(n_jobs));
-    int64_t x_slots = 1;
+    int64_t x_slots = 1, xchg_elems = 0;
     for (int i = 0; i < n_jobs; ++i) {
         const qgemv_job& jb = jobs[i];
         if (!jb.w || !jb.x || !jb.y) return QGEMV_ERR_INVALID_ARG;
@@ -547,30 +616,87 @@ int qgemv_sequence_create(qgemv_handle* h, const qgemv_job* jobs, int n_jobs, in
         sj.tensor_scale = jb.w->host_tensor_scale[0];
         sj.N = int32_t(jb.w->N), sj.K = int32_t(jb.w->K);
         sj.tiles = int32_t(jb.w->n_panels / 8), sj.kt = int32_t(jb.w->units);
-        sj.x_stride = int32_t(jb.w->K);
         sj.y_dtype = jb.y_dtype;
-        // the latest earlier job this one must not overtake: it reads that job's output (RAW), or
-        // overwrites its output (WAW) or its input (WAR)
-        sj.dep = -1;
+        // Ordering against the earlier jobs, from the address ranges.  RAW: x inside an earlier y.  WAW /
+        // WAR: y over an earlier y or x.  The common chain -- x is (a column range of) the bf16 output of
+        // ONE earlier job, every row, same row stride -- takes the fast way: the producer publishes its
+        // rows as tagged words and this job's conversion picks them up as they appear (src_job).  Every
+        // other hazard waits until the job in question is complete on every CTA (dep).
+        sj.dep = -1, sj.xoff = -1, sj.pub_off = -1, sj.src_off = -1, sj.src_job = -1;
+        if ((jb.flags & ~(QGEMV_JOB_AFTER_PREVIOUS | QGEMV_JOB_ALLREDUCE)) != 0) return QGEMV_ERR_INVALID_ARG;
+        if (jb.x_stride != 0 && (jb.x_stride < jb.w->K || jb.x_stride > INT32_MAX || (jb.x_stride % 8) != 0)) return QGEMV_ERR_INVALID_ARG;
+        sj.x_stride = int32_t(jb.x_stride != 0 ? jb.x_stride : jb.w->K);
         {
             const auto lo = [](const void* p) { return reinterpret_cast<uintptr_t>(p); };
             const auto ysize = [&](const qgemv_job& q) { return size_t(B) * size_t(q.w->N) * (q.y_dtype == QGEMV_OUT_F32 ? 4 : 2); };
-            const uintptr_t x0 = lo(jb.x), x1 = x0 + size_t(B) * size_t(jb.w->K) * 2, y0 = lo(jb.y), y1 = y0 + ysize(jb);
+            const auto xsize = [&](const qgemv_job& q) {
+                const size_t st = q.x_stride != 0 ? size_t(q.x_stride) : size_t(q.w->K);
+                return (size_t(B - 1) * st + size_t(q.w->K)) * 2;
+            };
+            const uintptr_t x0 = lo(jb.x), x1 = x0 + xsize(jb), y0 = lo(jb.y), y1 = y0 + ysize(jb);
+            int raw = -1, n_raw = 0, other = -1;
             for (int e = i - 1; e >= 0; --e) {
                 const qgemv_job& pj = jobs[e];
-                const uintptr_t py0 = lo(pj.y), py1 = py0 + ysize(pj), px0 = lo(pj.x), px1 = px0 + size_t(B) * size_t(pj.w->K) * 2;
-                if ((x0 < py1 && py0 < x1) || (y0 < py1 && py0 < y1) || (y0 < px1 && px0 < y1)) {
-                    sj.dep = e;
-                    break;
+                const uintptr_t py0 = lo(pj.y), py1 = py0 + ysize(pj), px0 = lo(pj.x), px1 = px0 + xsize(pj);
+                const bool r = x0 < py1 && py0 < x1, o = (y0 < py1 && py0 < y1) || (y0 < px1 && px0 < y1);
+                if (r && n_raw++ == 0) raw = e;
+                if (o && other < 0) other = e;
+            }
+            bool fast = false;
+            if (n_raw == 1 && raw > other && (jb.flags & QGEMV_JOB_AFTER_PREVIOUS) == 0) {
+                const qgemv_job& pj = jobs[raw];
+                const uintptr_t py0 = lo(pj.y);
+                const int64_t c0 = (int64_t(x0) - int64_t(py0)) / 2;
+                if (pj.y_dtype == QGEMV_OUT_BF16 && x0 >= py0 && c0 + jb.w->K <= pj.w->N && (B == 1 || sj.x_stride == pj.w->N) &&
+                    (pj.w->N % 4) == 0 && (c0 % 4) == 0) {
+                    fast = true;
+                    sj.src_job = raw;
+                    sj.src_off = int32_t(c0);        // + the producer's pub_off, below
+                    sj.x_stride = int32_t(pj.w->N);
                 }
             }
+            sj.dep = fast ? other : std::max(raw, other);
+            if ((jb.flags & QGEMV_JOB_AFTER_PREVIOUS) != 0 && i > 0) sj.dep = i - 1;
+        }
+        if ((jb.flags & QGEMV_JOB_ALLREDUCE) != 0 && h->tp_world > 1) {
+            // the sum over the ranks is formed by the thread that adds up a split row tile: every
+            // tile must be split, i.e. no CTA's share of the job may hold a whole tile
+            const int64_t tot = int64_t(sj.tiles) * sj.kt;
+            const int64_t gj = std::min<int64_t>(grid, tot);
+            if ((tot + gj - 1) / gj >= sj.kt) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+            for (int r = 0; r < h->tp_world; ++r)
+                if (!h->tp_peer[r]) return QGEMV_ERR_INVALID_ARG;  // qgemv_tp_connect has not run
+            xchg_elems += int64_t(B) * sj.N;
+            sj.xoff = 0;  // placed below, once the total is known
         }
         const int64_t total = int64_t(sj.tiles) * sj.kt;
         x_slots = std::max(x_slots, std::min<int64_t>(sj.kt, (total + grid - 1) / grid));
     }
+    if (n_jobs > 4094) return QGEMV_ERR_UNSUPPORTED_SHAPE;  // the job index is part of a 12-bit tag
+    // published outputs: one block of B * N words for every job that a later job reads the fast way
+    int64_t pub_words = 0;
+    for (int i = 0; i < n_jobs; ++i) {
+        qg::SeqJob& sj = tab[size_t(i)];
+        if (sj.src_job < 0) continue;
+        qg::SeqJob& pj = tab[size_t(sj.src_job)];
+        if (pj.pub_off < 0) {
+            pj.pub_off = int32_t(pub_words);
+            pub_words += (int64_t(B) * pj.N + 3) / 4 * 4;
+            if (pub_words > INT32_MAX / 2) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+        }
+        sj.src_off += pj.pub_off;
+    }
+    // the all-reduce jobs take their blocks from the top of the exchange slots downwards
+    if (xchg_elems > 0 && h->tp_seq_cursor - xchg_elems < h->tp_call_high) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+    {
+        int64_t off = h->tp_seq_cursor - xchg_elems;
+        for (qg::SeqJob& sj : tab)
+            if (sj.xoff >= 0) sj.xoff = int32_t(off), off += int64_t(B) * sj.N;
+    }
     qgemv_sequence* q = new (std::nothrow) qgemv_sequence;
     if (!q) return QGEMV_ERR_INVALID_ARG;
-    q->dev_jobs = nullptr, q->dev_counters = nullptr;
+    q->dev_jobs = nullptr, q->dev_counters = nullptr, q->dev_pub = nullptr;
+    q->xchg_elems = xchg_elems, q->xchg_first = h->tp_seq_cursor - xchg_elems;
     q->n_jobs = n_jobs, q->B = B, q->grid = grid;
     q->npad = (8 * B + 15) / 16 * 16;
     q->x_slots = int(x_slots);
@@ -593,15 +719,19 @@ int qgemv_sequence_create(qgemv_handle* h, const qgemv_job* jobs, int n_jobs, in
     q->smem = size_t(qg::SeqSmem::total(q->x_slots, q->npad, q->nbuf, ring, q->stage_items));
     if (cudaSetDevice(h->cfg.device) != cudaSuccess || cudaMalloc(&q->dev_jobs, size_t(n_jobs) * sizeof(qg::SeqJob)) != cudaSuccess ||
         cudaMemcpy(q->dev_jobs, tab.data(), size_t(n_jobs) * sizeof(qg::SeqJob), cudaMemcpyHostToDevice) != cudaSuccess ||
-        cudaMalloc(&q->dev_counters, size_t(2 * n_jobs) * 4) != cudaSuccess ||
-        cudaMemset(q->dev_counters, 0, size_t(2 * n_jobs) * 4) != cudaSuccess) {
+        cudaMalloc(&q->dev_counters, size_t(n_jobs + 1) * 4) != cudaSuccess ||
+        cudaMemset(q->dev_counters, 0, size_t(n_jobs + 1) * 4) != cudaSuccess ||
+        cudaMalloc(&q->dev_pub, size_t(std::max<int64_t>(pub_words, 4)) * 4) != cudaSuccess ||
+        cudaMemset(q->dev_pub, 0, size_t(std::max<int64_t>(pub_words, 4)) * 4) != cudaSuccess) {
         g_last_cuda_error = cudaGetLastError();
         cudaFree(q->dev_jobs);
         cudaFree(q->dev_counters);
+        cudaFree(q->dev_pub);
         delete q;
         return QGEMV_ERR_CUDA;
     }
     if (h->sequences) h->sequences->push_back(q);
+    h->tp_seq_cursor -= xchg_elems;
     *out = q;
     return QGEMV_OK;
 }
@@ -610,8 +740,10 @@ int qgemv_sequence_destroy(qgemv_handle* h, qgemv_sequence* q) {
     if (!h || !q) return QGEMV_ERR_INVALID_ARG;
     cudaSetDevice(h->cfg.device);
     if (h->sequences) h->sequences->erase(std::remove(h->sequences->begin(), h->sequences->end(), q), h->sequences->end());
+    if (q->xchg_elems > 0 && q->xchg_first == h->tp_seq_cursor) h->tp_seq_cursor += q->xchg_elems;  // the latest list: its blocks are free again
     cudaFree(q->dev_jobs);
     cudaFree(q->dev_counters);
+    cudaFree(q->dev_pub);
     delete q;
     return QGEMV_OK;
 }
@@ -623,8 +755,8 @@ int qgemv_sequence_run(qgemv_handle* h, const qgemv_sequence* q, void* stream) {
     P.jobs = q->dev_jobs;
     P.ws = h->seq_parts;
     P.barrier = h->seq_barrier;
-    P.done = q->dev_counters;
-    P.fin = q->dev_counters + q->n_jobs;
+    P.fin = q->dev_counters;
+    P.pub = q->dev_pub;
     P.status = h->status_dev;
     P.spin_limit = default_spin(h);
     P.n_jobs = q->n_jobs;
@@ -635,6 +767,12 @@ int qgemv_sequence_run(qgemv_handle* h, const qgemv_sequence* q, void* stream) {
     P.nbuf = q->nbuf;
     P.debug = h->cfg.debug;
     P.trace = h->tc_trace;
+    P.world = 1;
+    if (q->xchg_elems > 0) {
+        for (int r = 0; r < h->tp_world; ++r) P.xbuf[r] = h->tp_peer[r];
+        P.x_max_elems = h->tp_max_elems;
+        P.rank = h->tp_rank, P.world = h->tp_world;
+    }
     const dim3 g(unsigned(q->grid)), blk(qg::kSeqThreads);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     g_launch_cooperative = true;
@@ -925,9 +1063,20 @@ int qgemv_last_device_status(qgemv_handle* h, void* stream, qgemv_dev_status* ou
         QG_CUDA(cudaMemset(h->status_dev, 0, sizeof v));
         // a kernel that gave up may have left hand-over flags and the arrival counter behind
         QG_CUDA(cudaMemset(h->tc_ws, 0, h->tc_ws_bytes));
-        QG_CUDA(cudaMemset(h->seq_barrier, 0, 256));
-        if (h->sequences)
-            for (qgemv_sequence* q : *h->sequences) QG_CUDA(cudaMemset(q->dev_counters, 0, size_t(2 * q->n_jobs) * 4));
+        // ... and tagged words under the tags of a launch that never counted itself: count it here
+        unsigned int cnt[3];
+        QG_CUDA(cudaMemcpy(cnt, h->seq_barrier, sizeof cnt, cudaMemcpyDeviceToHost));
+        cnt[0] = 0u, cnt[2] += 1u;
+        QG_CUDA(cudaMemcpy(h->seq_barrier, cnt, sizeof cnt, cudaMemcpyHostToDevice));
+        if (h->sequences) {
+            for (qgemv_sequence* q : *h->sequences) {
+                unsigned int run = 0;
+                QG_CUDA(cudaMemcpy(&run, q->dev_counters + q->n_jobs, 4, cudaMemcpyDeviceToHost));
+                run += 1u;
+                QG_CUDA(cudaMemset(q->dev_counters, 0, size_t(q->n_jobs) * 4));
+                QG_CUDA(cudaMemcpy(q->dev_counters + q->n_jobs, &run, 4, cudaMemcpyHostToDevice));
+            }
+        }
     }
     return QGEMV_OK;
 }
@@ -937,14 +1086,13 @@ int qgemv_last_device_status(qgemv_handle* h, void* stream, qgemv_dev_status* ou
 int qgemv_tp_create(qgemv_handle* h, int rank, int world, int64_t max_elems, void* ipc_handle_out) {
     if (!h || !ipc_handle_out || world < 1 || world > qg::kTpMaxWorld || rank < 0 || rank >= world)
         return QGEMV_ERR_INVALID_ARG;
-    if (max_elems < 4 || h->tp_local) return QGEMV_ERR_INVALID_ARG;
+    if (max_elems < 4 || max_elems > (int64_t(1) << 30) || h->tp_local) return QGEMV_ERR_INVALID_ARG;
     QG_CUDA(cudaSetDevice(h->cfg.device));
     max_elems = (max_elems + 3) / 4 * 4;
     const size_t bytes = qg::tp_buffer_bytes(world, max_elems);
     cudaIpcMemHandle_t mh;
     const bool ok = cudaMalloc(&h->tp_local, bytes) == cudaSuccess && cudaMemset(h->tp_local, 0, bytes) == cudaSuccess &&
-                    cudaMalloc(&h->tp_epochs, qg::kTpCtas * 4) == cudaSuccess &&
-                    cudaMemset(h->tp_epochs, 0, qg::kTpCtas * 4) == cudaSuccess &&
+                    cudaMalloc(&h->tp_epochs, 2 * 4) == cudaSuccess && cudaMemset(h->tp_epochs, 0, 2 * 4) == cudaSuccess &&
                     cudaDeviceSynchronize() == cudaSuccess && cudaIpcGetMemHandle(&mh, h->tp_local) == cudaSuccess;
     if (!ok) {
         // leave the handle as it was, so that the call can be retried
@@ -959,6 +1107,8 @@ int qgemv_tp_create(qgemv_handle* h, int rank, int world, int64_t max_elems, voi
     h->tp_rank = rank;
     h->tp_world = world;
     h->tp_max_elems = max_elems;
+    h->tp_seq_cursor = max_elems;
+    h->tp_call_high = 0;
     h->tp_peer[rank] = h->tp_local;
     return QGEMV_OK;
 }
@@ -968,38 +1118,72 @@ int qgemv_tp_connect(qgemv_handle* h, const void* all_handles) {
     QG_CUDA(cudaSetDevice(h->cfg.device));
     const uint8_t* src = static_cast<const uint8_t*>(all_handles);
     for (int r = 0; r < h->tp_world; ++r) {
-        if (r == h->tp_rank) continue;
+        if (r == h->tp_rank || h->tp_peer[r]) continue;
         cudaIpcMemHandle_t mh;
         std::memcpy(&mh, src + size_t(r) * QGEMV_IPC_HANDLE_BYTES, sizeof mh);
         void* p = nullptr;
         QG_CUDA(cudaIpcOpenMemHandle(&p, mh, cudaIpcMemLazyEnablePeerAccess));
         h->tp_peer[r] = static_cast<uint8_t*>(p);
+        h->tp_ipc_opened[r] = true;
     }
     return QGEMV_OK;
 }
 
-int qgemv_tp_allreduce(qgemv_handle* h, void* y, int y_dtype, int64_t n, void* stream) {
-    if (!h || !y || n < 1) return QGEMV_ERR_INVALID_ARG;
+int qgemv_tp_connect_ptrs(qgemv_handle* h, void* const* peer_buffers) {
+    if (!h || !peer_buffers || !h->tp_local) return QGEMV_ERR_INVALID_ARG;
+    for (int r = 0; r < h->tp_world; ++r) {
+        if (r == h->tp_rank) continue;
+        if (!peer_buffers[r] || h->tp_peer[r] || (reinterpret_cast<uintptr_t>(peer_buffers[r]) & 7u) != 0) return QGEMV_ERR_INVALID_ARG;
+    }
+    for (int r = 0; r < h->tp_world; ++r)
+        if (r != h->tp_rank) h->tp_peer[r] = static_cast<uint8_t*>(peer_buffers[r]);
+    return QGEMV_OK;
+}
+
+int qgemv_tp_buffer(qgemv_handle* h, void** dev_ptr, size_t* bytes) {
+    if (!h || !dev_ptr || !bytes || !h->tp_local) return QGEMV_ERR_INVALID_ARG;
+    *dev_ptr = h->tp_local;
+    *bytes = qg::tp_buffer_bytes(h->tp_world, h->tp_max_elems);
+    return QGEMV_OK;
+}
+
+namespace {
+int tp_exchange(qgemv_handle* h, const void* in, void* y, int y_dtype, int64_t n, int gather, void* stream) {
+    if (!h || !in || !y || n < 1) return QGEMV_ERR_INVALID_ARG;
     if (!h->tp_local) return QGEMV_ERR_INVALID_ARG;
-    if (n > h->tp_max_elems) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+    if (n > h->tp_seq_cursor) return QGEMV_ERR_UNSUPPORTED_SHAPE;  // beyond the buffer, or into the part that job lists hold
     if (y_dtype != QGEMV_OUT_BF16 && y_dtype != QGEMV_OUT_F32) return QGEMV_ERR_INVALID_ARG;
     for (int r = 0; r < h->tp_world; ++r)
         if (!h->tp_peer[r]) return QGEMV_ERR_INVALID_ARG;  // qgemv_tp_connect has not run
+    h->tp_call_high = std::max(h->tp_call_high, n);
     qg::TpParams P;
     std::memset(&P, 0, sizeof P);
     for (int r = 0; r < h->tp_world; ++r) P.buf[r] = h->tp_peer[r];
     P.rank = h->tp_rank;
     P.world = h->tp_world;
     P.max_elems = h->tp_max_elems;
+    P.in = in;
     P.y = y;
     P.y_dtype = y_dtype;
+    P.gather = gather;
     P.n = n;
-    P.epochs = h->tp_epochs;
+    P.epoch = h->tp_epochs;
     P.status = h->status_dev;
     P.spin_limit = default_spin(h);
-    const cudaError_t err = launch(h, qg::tp_allreduce_kernel, dim3(qg::kTpCtas), dim3(qg::kTpThreads), 0,
+    const unsigned ctas = unsigned((n + qg::kTpThreads - 1) / qg::kTpThreads);
+    const cudaError_t err = launch(h, qg::tp_exchange_kernel, dim3(ctas), dim3(qg::kTpThreads), 0,
                                    static_cast<cudaStream_t>(stream), P);
     return err == cudaSuccess ? QGEMV_OK : QGEMV_ERR_CUDA;
+}
+}  // namespace
+
+int qgemv_tp_allreduce(qgemv_handle* h, void* y, int y_dtype, int64_t n, void* stream) {
+    return tp_exchange(h, y, y, y_dtype, n, 0, stream);
+}
+
+int qgemv_tp_allgather(qgemv_handle* h, const void* shard, void* y, int y_dtype, int64_t n_shard, void* stream) {
+    if (shard == y) return QGEMV_ERR_INVALID_ARG;
+    return tp_exchange(h, shard, y, y_dtype, n_shard, 1, stream);
 }
 
 // ---- allocation-free GEMV ----------------------------------------------------------------------

@@ -207,4 +207,62 @@ __global__ void chunk_sum_kernel(const float* parts, int n_chunks, int64_t n, vo
     }
 }
 
+// ---- device-side packer of the tensor-core layout ------------------------------------------------
+// Canonical NVFP4 (codes u8 [N][K/2], scales u8 [N][K/16], row-major, in device memory) -> the item
+// order of QGEMV_FMT_NVFP4_TC, the same bytes qgemv_pack_host writes.  The layout is a permutation of
+// 8-byte code groups and single scale bytes, so one thread builds one 16-byte chunk of the payload
+// and stores it whole; rows and K blocks beyond the window are zero.
+struct PackTcParams {
+    const uint8_t* codes;
+    const uint8_t* scales;
+    uint8_t* payload;
+    int64_t N, K;      // the canonical matrix
+    int64_t n0, k0;    // origin of the window that is packed
+    int64_t n, k;      // its extent
+    int64_t tiles, kt; // ceil(n / 128), ceil(k / 64)
+};
+
+__global__ void __launch_bounds__(256) pack_tc_kernel(const PackTcParams P) {
+    constexpr int kChunks = QG_TC_ITEM_BYTES / 16;  // 288: 256 of codes, 32 of scales
+    const int64_t total = P.tiles * P.kt * kChunks;
+    for (int64_t c = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; c < total; c += int64_t(gridDim.x) * blockDim.x) {
+        const int64_t it = c / kChunks;
+        const int within = int(c - it * kChunks);
+        const int64_t tile = it / P.kt, item = it - tile * P.kt;
+        uint4 out = make_uint4(0, 0, 0, 0);
+        if (within < 256) {
+            // chunk (r / 8) * 16 + (k / 32) * 8 + r % 8: codes of row r, 32 elements from k
+            const int r = (within >> 4) * 8 + (within & 7);
+            const int64_t n = tile * QG_TC_TILE_ROWS + r, kk = item * 64 + ((within >> 3) & 1) * 32;
+            if (n < P.n) {
+                const uint8_t* src = P.codes + (P.n0 + n) * (P.K / 2) + (P.k0 + kk) / 2;
+                if (kk < P.k) {
+                    const uint2 v = *reinterpret_cast<const uint2*>(src);
+                    out.x = v.x, out.y = v.y;
+                }
+                if (kk + 16 < P.k) {
+                    const uint2 v = *reinterpret_cast<const uint2*>(src + 8);
+                    out.z = v.x, out.w = v.y;
+                }
+            }
+        } else {
+            // chunk r % 32: block scales of rows r % 32 + 32 q, q = 0..3, four K blocks each
+            const int r32 = within - 256;
+            uint32_t w[4] = {0, 0, 0, 0};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int64_t n = tile * QG_TC_TILE_ROWS + r32 + 32 * q;
+                if (n < P.n) {
+                    const uint8_t* src = P.scales + (P.n0 + n) * (P.K / 16) + (P.k0 + item * 64) / 16;
+#pragma unroll
+                    for (int kb = 0; kb < 4; ++kb)
+                        if (item * 64 + kb * 16 < P.k) w[q] |= uint32_t(src[kb]) << (8 * kb);
+                }
+            }
+            out = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        *reinterpret_cast<uint4*>(P.payload + it * QG_TC_ITEM_BYTES + (within < 256 ? within * 16 : 4096 + (within - 256) * 16)) = out;
+    }
+}
+
 }  // namespace qg

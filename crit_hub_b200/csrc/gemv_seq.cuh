@@ -1,35 +1,42 @@
 // A SEQUENCE of NVFP4 GEMVs (tensor-core layout) as ONE persistent launch: the projections of a
-// decode step, executed in order, each allowed to read what the one before it wrote.
+// decode step, executed in order, each allowed to read what the ones before it wrote.
 //
 // Launched one by one, each GEMV of a decode layer pays a serial chain that no weight byte overlaps:
 // the previous grid's last partial sums, the launch boundary, the activation conversion, the first
-// MMAs -- about 5 us, four times per layer, against 19 us of HBM time.  A launch can only prefetch
-// what its own ring holds while it waits.  Here one grid of one CTA per SM walks the whole job
-// list.  The producer thread never stops at a job boundary: while the CTA's other warps finish job
-// j (epilogue, grid-wide barrier, digit planes of job j+1), it already streams the items of job
-// j+1, j+2, ... into a ring that takes most of the SM's shared memory, so HBM stays busy across the
-// boundary and the MMAs of the next job find their first ~190 KB per SM waiting.
+// MMAs -- about 5 us, four times per layer, against 19 us of HBM time.  Here one grid of one CTA per
+// SM walks the whole job list.  The producer thread never stops at a job boundary: while the CTA's
+// other warps finish job j and convert the activations of job j+1, it already streams the items of
+// job j+1, j+2, ... into a ring that takes most of the SM's shared memory, so HBM stays busy across
+// the boundary and the MMAs of the next job find their first ~190 KB per SM waiting.
 //
 // Per job the arithmetic is gemv_tc.cuh's: weights consumed as stored by tcgen05.mma
 // kind::mxf4nvf4, activations as eight E2M1 digit planes scaled per CTA range, split along K over
 // the CTAs with a deterministic hand-over to each row tile's first contributor.
 //
-// Between jobs: every CTA, once its own results of job j are stored, bumps a global counter with
-// release semantics; before converting the activations of job j+1 one thread per CTA polls --
-// bounded -- until all CTAs have arrived (acquire), then the CTA's converting warps synchronise.
+// Warps: 0 producer, 1 MMA issuer, then three groups of four warps that run side by side and meet
+// only through mbarriers in shared memory and two counters per job in global memory:
+//   PLANES    digit planes of job j into one of up to three buffers (so it may be that many jobs
+//             ahead of the epilogues).  A job that must not overtake an earlier one -- the host
+//             compares the address ranges of every job's x and y with those of the jobs before it,
+//             or the caller says so -- first waits until fin[that job] has been bumped by every CTA.
+//   EPILOGUE  accumulators -> y rows (a CTA that holds a whole row tile) or fp32 partial sums in the
+//             CTA's slot of a parts buffer (eight buffers, taken in turn by the jobs); then bumps
+//             done[j] with release semantics.
+//   FINISH    once done[j] shows every CTA: the first contributor of a split row tile adds the parts
+//             in CTA order -- a fixed order -- and stores the rows; then bumps fin[j].  Nothing here
+//             is on the MMA issuer's critical path.
 // The CTAs wait on one another, so the launch is cooperative (all CTAs co-resident).
 //
-// Split along K without a wait: a CTA that holds only part of a row tile stores its fp32 partial
-// sums in its own slot of a parts buffer (double-buffered by job parity) and moves on.  The tile's
-// first contributor adds the parts in CTA order -- a fixed order -- and stores the rows AFTER the
-// barrier, when every part is known to be there, and after it has handed the next job's digit
-// planes to the tensor core: the sum is off the critical path and polls nothing.  Only when the
-// next job reads or overwrites this job's output (the host compares the address ranges) is the sum
-// done first, followed by one more barrier.
-//
-// Warp roles as in gemv_tc.cuh: 0 producer, 1 MMA issuer, 2-9 digit planes + epilogues.
+// Tensor parallel: a row-parallel projection's output is the sum over the ranks.  For such a job
+// (xoff >= 0) the FINISH thread that has added up a row pushes the fp32 partial sum, tagged with
+// the count of launches, into its rank's slot of every rank's exchange buffer over NVLink, then
+// gathers the ranks' pairs for that row from its own buffer (all loads in flight, bounded
+// re-polling), adds them in rank order and stores the row: the all-reduce costs no launch and no
+// grid-wide wait (tp_allreduce.cuh describes the slots).  Every rank runs the same job list on the
+// same grid, so the same CTA holds a row on every rank.
 #pragma once
 #include "gemv_tc.cuh"
+#include "tp_allreduce.cuh"
 
 namespace qg {
 
@@ -37,7 +44,7 @@ constexpr int kSeqPartBufs = 8;
 constexpr int kSeqPlaneBufsMax = 3;  // buffers of digit planes (1..3, as many as leave room for a ring): the PLANES group
                                      // may be that many jobs ahead of the epilogues  // jobs a CTA may run ahead of the slowest one before it waits for its parts buffer
 
-struct SeqJob {               // 64 bytes, device memory
+struct SeqJob {               // 80 bytes, device memory
     const uint8_t* payload;   // items of the weight: (tile * kt + item) * 4608
     const uint16_t* x;        // bf16 [B][K]
     void* y;                  // [B][N]
@@ -46,18 +53,27 @@ struct SeqJob {               // 64 bytes, device memory
     int32_t tiles, kt;        // ceil(N / 128), ceil(K / 64)
     int32_t x_stride;         // elements between activation rows
     int32_t y_dtype;
-    int32_t dep;              // latest earlier job whose output this job reads or overwrites, or whose input it
-                              // overwrites (address ranges compared by the host); -1: none
-    int32_t pad;
+    int32_t dep;              // latest earlier job that must be complete on every CTA before this job's activations
+                              // are read (an address-range hazard found by the host, or the caller's order); -1: none
+    int32_t xoff;             // >= 0: a row-parallel projection, y = sum over the ranks; element offset of this job's
+                              // [B][N] block inside every slot of the exchange buffers.  -1: local job
+    int32_t pub_off;          // >= 0: a later job reads this job's bf16 output as its activations: every row is also
+                              // published as a word {tag, bf16} at pub[pub_off + b * N + n].  -1: not published
+    int32_t src_off;          // >= 0: the activations are read from pub[src_off + b * x_stride + k], published by job
+                              // src_job, word by word as they appear (no grid-wide wait).  -1: from x
+    int32_t src_job;
+    int32_t pad[2];
 };
-static_assert(sizeof(SeqJob) == 64, "SeqJob layout");
+static_assert(sizeof(SeqJob) == 80, "SeqJob layout");
 
 struct SeqParams {
     const SeqJob* jobs;
-    float* ws;                  // parts buffers: [job % kSeqPartBufs][2 * cta + which][8][128] fp32 partial sums
-    unsigned int* barrier;      // CTAs that have left the launch; zero between launches
-    unsigned int* done;         // [n_jobs] CTAs whose results and parts of the job are stored; zero between launches
-    unsigned int* fin;          // [n_jobs] CTAs that have added up their split tile of the job; zero between launches
+    unsigned long long* ws;     // parts buffers: [job % kSeqPartBufs][2 * cta + which][8][128] pairs {fp32 partial sum, tag}
+    unsigned int* barrier;      // [0] CTAs that have left the launch (zero between launches), [1] launches of this
+                                // handle that exchanged between ranks, [2] sequence launches of this handle
+    unsigned int* fin;          // [n_jobs] CTAs that are through with the job (rows stored, split tile added up); zero
+                                // between launches.  [n_jobs]: launches of this job list
+    uint32_t* pub;              // published outputs of this job list, words {16-bit tag, bf16}
     int32_t* status;
     int64_t spin_limit;
     int32_t n_jobs;
@@ -67,6 +83,10 @@ struct SeqParams {
     int32_t nbuf;               // buffers of digit planes, 1..kSeqPlaneBufsMax
     int32_t debug;
     unsigned long long* trace;  // optional diagnostics: per CTA, per job 8 stamps (see qgemv_set_trace), or null
+    // tensor-parallel exchange (world == 1: none)
+    uint8_t* xbuf[kTpMaxWorld];
+    int64_t x_max_elems;
+    int32_t rank, world;
 };
 
 struct SeqSmem {
@@ -87,6 +107,7 @@ struct SeqSmem {
     static constexpr int kConsumed = 644;
     static constexpr int kDecision = 928;   // [2][4] every warp group's common samples of the abort flag
     static constexpr int kFinAll = 688;     // jobs up to this index are added up on every CTA (-1: none)
+    static constexpr int kEpiDone = 692;    // jobs whose epilogues this CTA has been through (release / acquire at CTA scope)
     static constexpr int kSfb = 1024;       // 512 bytes
     static constexpr int kX = 1536;
     // nbuf buffers of digit planes (jobs take them in turn), then the ring
@@ -111,13 +132,39 @@ __device__ __forceinline__ unsigned int ld_acquire(const unsigned int* p) {
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
+__device__ __forceinline__ void st_release_cta_shared(uint32_t addr, int v) {
+    asm volatile("st.release.cta.shared.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_cta_shared(uint32_t addr) {
+    int v;
+    asm volatile("ld.acquire.cta.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_tagged(unsigned long long* p, float v, uint32_t tag) {
+    const unsigned long long w = (static_cast<unsigned long long>(tag) << 32) | __float_as_uint(v);
+    asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+__device__ __forceinline__ void st_pub(uint32_t* p, uint32_t w) {
+    asm volatile("st.relaxed.gpu.global.b32 [%0], %1;" ::"l"(p), "r"(w) : "memory");
+}
+__device__ __forceinline__ uint4 ld_pub4(const uint32_t* p) {
+    uint4 v;
+    asm volatile("ld.relaxed.gpu.global.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+// tag of a partial sum: the handle's launch count and the job; of a published word: the job list's
+// launch count (low bits) and the job.  A slot is rewritten by every launch that reads it, so what
+// is left from before carries another launch's tag.
+__device__ __forceinline__ uint32_t seq_part_tag(uint32_t launch, int j) { return launch * 4099u + uint32_t(j) + 1u; }
+__device__ __forceinline__ uint32_t seq_pub_tag(uint32_t run, int j) { return ((run & 15u) << 12) | (uint32_t(j + 1) & 0xFFFu); }
+
 __device__ __forceinline__ SeqJob seq_load_job(const SeqJob* j) {
     const uint4* p = reinterpret_cast<const uint4*>(j);
     union {
-        uint4 q[4];
+        uint4 q[5];
         SeqJob job;
     } u;
-    u.q[0] = __ldg(p), u.q[1] = __ldg(p + 1), u.q[2] = __ldg(p + 2), u.q[3] = __ldg(p + 3);
+    u.q[0] = __ldg(p), u.q[1] = __ldg(p + 1), u.q[2] = __ldg(p + 2), u.q[3] = __ldg(p + 3), u.q[4] = __ldg(p + 4);
     return u.job;
 }
 // A job is split over min(grid, items) CTAs, exactly as a launch of its own would be; the other CTAs
@@ -174,6 +221,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
             mbar_init(sbase + SeqSmem::kBarMDone + 8 * b, 1);
         }
         *reinterpret_cast<volatile int*>(sq_smem + SeqSmem::kFinAll) = -1;
+        *reinterpret_cast<volatile int*>(sq_smem + SeqSmem::kEpiDone) = 0;
         *abort_flag = 0;
         *n_issued = 0;
         *n_consumed = 0;
@@ -336,16 +384,19 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
         __syncwarp();
     } else {
         // ================= three independent warp groups, job after job =================
-        // The chores of a job are round trips to global memory (activations in, results out, "has
-        // every CTA finished?"), each most of a microsecond.  Run one after the other by the same warps
+        // The chores of a job are round trips to global memory (activations in, results out, other
+        // CTAs' partial sums), each most of a microsecond.  Run one after the other by the same warps
         // they cost 6-7 us per job; so they are dealt to three groups of four warps that only meet
-        // through barriers in shared memory and counters in global memory:
+        // through barriers in shared memory and tagged words in global memory:
         //   PLANES   (warps 2-5)   digit planes of job j into one of nbuf buffers, that many jobs ahead of
-        //                          the epilogues; a job that the host found to depend on an earlier one
-        //                          (address ranges) first waits until that job is complete on every CTA
-        //   EPILOGUE (warps 6-9)   accumulators of job j's segments -> y rows, or parts of a split tile
-        //   FINISH   (warps 10-13) once every CTA has stored its parts of job j: adds up the split tile
-        //                          this CTA is the first contributor of, in CTA order, and stores its rows
+        //                          the epilogues.  Activations that an earlier job of the list produced are
+        //                          taken word by word from that job's published output as the tags appear;
+        //                          any other hazard the host found waits for fin[dep] on every CTA
+        //   EPILOGUE (warps 6-9)   accumulators of job j's segments -> y rows (+ published words), or tagged
+        //                          parts of a split tile
+        //   FINISH   (warps 10-13) adds up the split tile this CTA is the first contributor of, in CTA order,
+        //                          as the contributors' tagged parts appear; exchanges it between ranks where
+        //                          the job says so; stores (and publishes) its rows; counts the job in fin[j]
         const int grp = (warp - kTcWarpConv0) >> 2;        // 0 PLANES, 1 EPILOGUE, 2 FINISH
         const int gt = threadIdx.x - 32 * (kTcWarpConv0 + 4 * grp);  // 0..127 inside the group
         const int bar_id = 1 + grp;                         // the group's named barrier
@@ -364,14 +415,18 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
             named_bar_sync(bar_id, 128);
             return *slot == 0;
         };
+        // a bounded spin's budget: iterations, and two seconds of wall clock
+        auto out_of_time = [&](int64_t it, uint64_t& t0) -> bool {
+            if (it == 0) t0 = globaltimer_ns();
+            return it >= P.spin_limit || ((it & 63) == 63 && globaltimer_ns() - t0 > 2000000000ull);
+        };
         // bounded poll by the group's first thread until *counter == grid (every CTA has passed that point)
         auto poll_all = [&](const unsigned int* counter, int site, int j) {
             if (gt == 0) {
                 uint64_t t0 = 0;
                 for (int64_t it = 0; ld_acquire(counter) < unsigned(grid); ++it) {
                     if (*abort_flag) break;
-                    if (it == 0) t0 = globaltimer_ns();
-                    if (it >= P.spin_limit || ((it & 63) == 63 && globaltimer_ns() - t0 > 2000000000ull)) {
+                    if (out_of_time(it, t0)) {
                         report(P.status, QGEMV_ERR_TIMEOUT, site, j);
                         *abort_flag = 1;
                         break;
@@ -379,7 +434,8 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 }
             }
         };
-        pdl_wait();  // whatever ran before this launch has finished with x, y and the scratch
+        pdl_wait();  // whatever ran before this launch has finished with x, y and the scratch, and has counted itself
+        const uint32_t launch_no = __ldcg(P.barrier + 2), run_no = __ldcg(P.fin + P.n_jobs);
 
         if (grp == 0) {
             // ---------------- PLANES ----------------
@@ -402,7 +458,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                     report(P.status, QGEMV_ERR_TIMEOUT, 78, j);
                     *abort_flag = 1;
                 }
-                if (job.dep >= 0) poll_all(P.fin + job.dep, 80, j);  // an earlier job's output (or input) is involved
+                if (job.dep >= 0) poll_all(P.fin + job.dep, 80, j);  // an earlier job's buffers are involved
                 if (!group_alive()) break;
                 if (P.trace && gt == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 0] = globaltimer_ns();
                 const int32_t kt_len = job.kt;
@@ -421,18 +477,51 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 named_bar_sync(bar_id, 128);
                 const int n_work = n_slots * Bl * 8;
                 constexpr int kKeep = 4;
-                auto unit_src = [&](int wu, int& b, uint32_t& dst) -> uint4 {
+                const bool from_pub = job.src_off >= 0;
+                const uint32_t want = seq_pub_tag(run_no, job.src_job) << 16;
+                bool alive = true;
+                // unit wu of this CTA's share: eight consecutive activations of row b; where they go in the planes
+                auto unit_at = [&](int wu, int& b, uint32_t& dst) -> int {
                     const int o = wu & 7, sb = wu >> 3;
                     b = sb / n_slots;
                     const int slot = sb - b * n_slots;
                     int32_t u = slot + xs0;
                     if (u >= kt_len) u -= kt_len;
-                    const int k0 = u * 64 + o * 8;
                     dst = xb + uint32_t(slot) * xslot_bytes + uint32_t(b) * 256u + uint32_t(o >> 2) * 128u + uint32_t(o & 3) * 4u;
-                    uint4 v = make_uint4(0, 0, 0, 0);
+                    const int k0 = u * 64 + o * 8;
+                    return k0 + 8 <= job.K ? k0 : -1;
+                };
+                auto pub_ok = [&](const uint4& a, const uint4& c) -> bool {
+                    const uint32_t m = (a.x ^ want) | (a.y ^ want) | (a.z ^ want) | (a.w ^ want) | (c.x ^ want) | (c.y ^ want) | (c.z ^ want) | (c.w ^ want);
+                    return (m >> 16) == 0u;
+                };
+                auto pub_pack = [&](const uint4& a, const uint4& c) -> uint4 {
+                    return make_uint4(__byte_perm(a.x, a.y, 0x5410), __byte_perm(a.z, a.w, 0x5410), __byte_perm(c.x, c.y, 0x5410),
+                                      __byte_perm(c.z, c.w, 0x5410));
+                };
+                // published words of a unit, re-read -- bounded -- until all eight carry the producing job's tag
+                auto pub_wait = [&](const uint32_t* p, uint4 a, uint4 c) -> uint4 {
+                    uint64_t t0 = 0;
+                    for (int64_t it = 0; !pub_ok(a, c); ++it) {
+                        if (*abort_flag || out_of_time(it, t0)) {
+                            if (!*abort_flag) report(P.status, QGEMV_ERR_TIMEOUT, 84, j);
+                            *abort_flag = 1;
+                            alive = false;
+                            break;
+                        }
+                        a = ld_pub4(p), c = ld_pub4(p + 4);
+                    }
+                    return pub_pack(a, c);
+                };
+                auto unit_src = [&](int wu, int& b, uint32_t& dst) -> uint4 {
+                    const int k0 = unit_at(wu, b, dst);
+                    if (k0 < 0) return make_uint4(0, 0, 0, 0);
+                    if (from_pub) {
+                        const uint32_t* p = P.pub + size_t(job.src_off) + size_t(b) * size_t(job.x_stride) + size_t(k0);
+                        return pub_wait(p, ld_pub4(p), ld_pub4(p + 4));
+                    }
                     // possibly written by other SMs during an earlier job: read through L2, never a stale L1 line
-                    if (k0 + 8 <= job.K) v = __ldcg(reinterpret_cast<const uint4*>(job.x + int64_t(b) * job.x_stride + k0));
-                    return v;
+                    return __ldcg(reinterpret_cast<const uint4*>(job.x + int64_t(b) * job.x_stride + k0));
                 };
                 auto unit_max = [&](const uint4& v) {
                     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
@@ -460,12 +549,33 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 uint4 keep[kKeep];
                 int kb[kKeep];
                 uint32_t kdst[kKeep];
+                if (from_pub) {
+                    // the loads of all kept units first, then the waits: one round trip when the words are there
+                    uint4 ka[kKeep], kc[kKeep];
+                    const uint32_t* kp[kKeep];
 #pragma unroll
-                for (int i = 0; i < kKeep; ++i) {
-                    const int wu = gt + i * 128;
-                    kb[i] = 0, kdst[i] = 0;
-                    keep[i] = make_uint4(0, 0, 0, 0);
-                    if (wu < n_work) keep[i] = unit_src(wu, kb[i], kdst[i]);
+                    for (int i = 0; i < kKeep; ++i) {
+                        const int wu = gt + i * 128;
+                        kb[i] = 0, kdst[i] = 0, kp[i] = nullptr;
+                        ka[i] = kc[i] = make_uint4(0, 0, 0, 0);
+                        if (wu < n_work) {
+                            const int k0 = unit_at(wu, kb[i], kdst[i]);
+                            if (k0 >= 0) {
+                                kp[i] = P.pub + size_t(job.src_off) + size_t(kb[i]) * size_t(job.x_stride) + size_t(k0);
+                                ka[i] = ld_pub4(kp[i]), kc[i] = ld_pub4(kp[i] + 4);
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int i = 0; i < kKeep; ++i) keep[i] = kp[i] ? pub_wait(kp[i], ka[i], kc[i]) : make_uint4(0, 0, 0, 0);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < kKeep; ++i) {
+                        const int wu = gt + i * 128;
+                        kb[i] = 0, kdst[i] = 0;
+                        keep[i] = make_uint4(0, 0, 0, 0);
+                        if (wu < n_work) keep[i] = unit_src(wu, kb[i], kdst[i]);
+                    }
                 }
 #pragma unroll
                 for (int i = 0; i < kKeep; ++i) {
@@ -493,6 +603,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 named_bar_sync(bar_id, 128);
                 if (gt == 0) mbar_arrive(sbase + SeqSmem::kBarXReady + 8 * pb);
                 if (P.trace && gt == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 1] = globaltimer_ns();
+                (void)alive;
                 job = next;
             }
         } else if (grp == 1) {
@@ -524,10 +635,9 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 if (re > rb && (rb % kt_len != 0 || re % kt_len != 0) && j >= kSeqPartBufs && gt == 0) {
                     uint64_t t0 = 0;
                     for (int64_t it = 0; *fin_all < j - kSeqPartBufs; ++it) {
-                        if (*abort_flag) break;
-                        if (it == 0) t0 = globaltimer_ns();
-                        __nanosleep(64);
-                        if (it >= P.spin_limit || ((it & 63) == 63 && globaltimer_ns() - t0 > 2000000000ull)) {
+                        // (asked directly: this CTA's FINISH group may itself be waiting for the part written below)
+                        if (*abort_flag || ld_acquire(P.fin + (j - kSeqPartBufs)) >= unsigned(grid)) break;
+                        if (out_of_time(it, t0)) {
                             report(P.status, QGEMV_ERR_TIMEOUT, 79, j);
                             *abort_flag = 1;
                             break;
@@ -535,6 +645,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                     }
                 }
                 if (!group_alive()) break;
+                const uint32_t part_tag = seq_part_tag(launch_no, j), pub_tag = seq_pub_tag(run_no, j) << 16;
                 GsWalker wk;
                 wk.units = kt_len, wk.pos = rb, wk.end = re;
                 GsSeg sg;
@@ -586,7 +697,9 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                                     if (job.y_dtype == QGEMV_OUT_F32) {
                                         static_cast<float*>(job.y)[idx] = val[b];
                                     } else {
-                                        static_cast<__nv_bfloat16*>(job.y)[idx] = __float2bfloat16_rn(val[b]);
+                                        const __nv_bfloat16 hv = __float2bfloat16_rn(val[b]);
+                                        static_cast<__nv_bfloat16*>(job.y)[idx] = hv;
+                                        if (job.pub_off >= 0) st_pub(P.pub + size_t(job.pub_off) + size_t(idx), pub_tag | uint32_t(__bfloat16_as_ushort(hv)));
                                     }
                                 }
                             }
@@ -596,10 +709,10 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                         // pair); the first one's range may have started in an earlier tile
                         const int32_t c_lo = int32_t(cta_of(int64_t(sg.tile) * kt_len, total, gj));
                         const int32_t my_slot = cta == c_lo ? gs_slot(c_lo, sg.tile, kt_len, total, gj) : 2 * cta;
-                        float* slot = P.ws + (size_t(j & (kSeqPartBufs - 1)) * size_t(2 * grid) + size_t(my_slot)) * 1024 + row;
+                        unsigned long long* slot = P.ws + (size_t(j & (kSeqPartBufs - 1)) * size_t(2 * grid) + size_t(my_slot)) * 1024 + row;
 #pragma unroll
                         for (int b = 0; b < 8; ++b)
-                            if (b < Bl) __stcg(slot + b * 128, val[b]);
+                            if (b < Bl) st_tagged(slot + b * 128, val[b], part_tag);
                     }
                 }
                 if (P.trace && gt == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 2] = globaltimer_ns();
@@ -611,7 +724,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                         *abort_flag = 1;
                     }
                     mbar_arrive(sbase + SeqSmem::kBarEDone + 8 * pb);  // first: the PLANES group may be waiting
-                    red_release_add(P.done + j, 1u);
+                    st_release_cta_shared(sbase + SeqSmem::kEpiDone, j + 1);  // for the FINISH group's count of the job
                 }
                 job = next;
             }
@@ -619,6 +732,13 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
             // ---------------- FINISH ----------------
             int known = -1;  // jobs up to here are added up on every CTA (published in fin_all)
             SeqJob job = seq_load_job(P.jobs);
+            TpExchange X;
+            X.buf = P.xbuf, X.rank = P.rank, X.world = P.world, X.max_elems = P.x_max_elems;
+            X.tag = 0u, X.par_off = 0;
+            if (P.world > 1) {
+                X.tag = __ldcg(P.barrier + 1) + 1u;
+                X.par_off = size_t(X.tag & 1u) * size_t(P.world) * size_t(P.x_max_elems);
+            }
             for (int j = 0; j < P.n_jobs; ++j) {
                 SeqJob next = job;
                 if (j + 1 < P.n_jobs) next = seq_load_job(P.jobs + j + 1);
@@ -637,38 +757,104 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                     pending = c_lo == cta;
                     lo_slot = gs_slot(c_lo, tile, kt_len, total, gj);
                 }
-                poll_all(P.done + j, 77, j);
                 // how far have ALL CTAs come with this step?  One probe per job, in flight with nothing else to do
                 if (gt == 0 && known + 1 < j && ld_acquire(P.fin + known + 1) >= unsigned(grid)) *fin_all = ++known;
                 if (!group_alive()) break;
-                if (pending && gt < 128) {
+                if (pending) {
                     const int n = tile * 128 + gt;
-                    const float* parts = P.ws + size_t(j & (kSeqPartBufs - 1)) * size_t(2 * grid) * 1024 + gt;
+                    const unsigned long long* parts = P.ws + size_t(j & (kSeqPartBufs - 1)) * size_t(2 * grid) * 1024 + gt;
+                    const uint32_t part_tag = seq_part_tag(launch_no, j), pub_tag = seq_pub_tag(run_no, j) << 16;
                     if (n < job.N) {
+                        bool have = true;
+                        uint64_t t0 = 0;
+                        int64_t spins = 0;
+                        // a contributor's tagged part, re-read -- bounded -- until it carries this job's tag
+                        auto part_wait = [&](const unsigned long long* p, unsigned long long w, int who) -> float {
+                            while (have && uint32_t(w >> 32) != part_tag) {
+                                if (*abort_flag || out_of_time(spins++, t0)) {
+                                    if (!*abort_flag) report(P.status, QGEMV_ERR_TIMEOUT, 77, who);
+                                    *abort_flag = 1;
+                                    have = false;
+                                    break;
+                                }
+                                w = ld_flagged(p);
+                            }
+                            return __uint_as_float(uint32_t(w));
+                        };
+                        float v[8];
 #pragma unroll
                         for (int b = 0; b < 8; ++b) {
+                            v[b] = 0.f;
                             if (b < Bl) {
                                 // eight parts' loads in flight together; the additions stay in CTA order
-                                float v = __ldcg(parts + size_t(lo_slot) * 1024 + b * 128);
+                                const unsigned long long* p0 = parts + size_t(lo_slot) * 1024 + b * 128;
+                                float a = part_wait(p0, ld_flagged(p0), c_lo);
                                 for (int32_t cc = c_lo + 1; cc <= c_hi; cc += 8) {
-                                    float t[8];
+                                    unsigned long long t[8];
 #pragma unroll
-                                    for (int z = 0; z < 8; ++z) t[z] = __ldcg(parts + size_t(2 * min(cc + z, c_hi)) * 1024 + b * 128);
+                                    for (int z = 0; z < 8; ++z) t[z] = ld_flagged(parts + size_t(2 * min(cc + z, c_hi)) * 1024 + b * 128);
 #pragma unroll
                                     for (int z = 0; z < 8; ++z)
-                                        if (cc + z <= c_hi) v += t[z];
+                                        if (cc + z <= c_hi) a += part_wait(parts + size_t(2 * (cc + z)) * 1024 + b * 128, t[z], cc + z);
                                 }
-                                const int64_t idx = int64_t(b) * job.N + n;
-                                if (job.y_dtype == QGEMV_OUT_F32) {
-                                    static_cast<float*>(job.y)[idx] = v;
-                                } else {
-                                    static_cast<__nv_bfloat16*>(job.y)[idx] = __float2bfloat16_rn(v);
+                                v[b] = a;
+                            }
+                        }
+                        if (have && job.xoff >= 0) {
+                            // this rank's partial sums out to every rank first, then the ranks' sums for this row
+#pragma unroll
+                            for (int b = 0; b < 8; ++b)
+                                if (b < Bl) X.push(int64_t(job.xoff) + int64_t(b) * job.N + n, v[b]);
+#pragma unroll
+                            for (int b = 0; b < 8; ++b) {
+                                if (b < Bl && have) {
+                                    float part[kTpMaxWorld];
+                                    int missing = 0;
+                                    if (X.gather(int64_t(job.xoff) + int64_t(b) * job.N + n, part, P.spin_limit, missing)) {
+                                        float a = part[0];
+                                        for (int r = 1; r < P.world; ++r) a += part[r];
+                                        v[b] = a;
+                                    } else {
+                                        report(P.status, QGEMV_ERR_TIMEOUT, 83, missing);
+                                        *abort_flag = 1;
+                                        have = false;
+                                    }
+                                }
+                            }
+                        }
+                        if (have) {
+#pragma unroll
+                            for (int b = 0; b < 8; ++b) {
+                                if (b < Bl) {
+                                    const int64_t idx = int64_t(b) * job.N + n;
+                                    if (job.y_dtype == QGEMV_OUT_F32) {
+                                        static_cast<float*>(job.y)[idx] = v[b];
+                                    } else {
+                                        const __nv_bfloat16 hv = __float2bfloat16_rn(v[b]);
+                                        static_cast<__nv_bfloat16*>(job.y)[idx] = hv;
+                                        if (job.pub_off >= 0) st_pub(P.pub + size_t(job.pub_off) + size_t(idx), pub_tag | uint32_t(__bfloat16_as_ushort(hv)));
+                                    }
                                 }
                             }
                         }
                     }
                 }
                 if (P.trace && gt == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 6] = globaltimer_ns();
+                // the job counts as finished on this CTA when its epilogues are through as well (rows of whole
+                // tiles, parts): then fin[j] == grid means that all of y is there
+                if (gt == 0) {
+                    uint64_t t0 = 0;
+                    for (int64_t it = 0; ld_acquire_cta_shared(sbase + SeqSmem::kEpiDone) <= j; ++it) {
+                        if (*abort_flag) break;
+                        // (the epilogue may itself be waiting for fin_all to move before it reuses a parts buffer)
+                        if (known + 1 < j && ld_acquire(P.fin + known + 1) >= unsigned(grid)) *fin_all = ++known;
+                        if (out_of_time(it, t0)) {
+                            report(P.status, QGEMV_ERR_TIMEOUT, 85, j);
+                            *abort_flag = 1;
+                            break;
+                        }
+                    }
+                }
                 named_bar_sync(bar_id, 128);
                 if (gt == 0) red_release_add(P.fin + j, 1u);
                 job = next;
@@ -678,8 +864,11 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
     // ---- every role is through (or has given up): the last CTA to leave puts the counters back to zero ----
     __syncthreads();
     if (threadIdx.x == 0 && !*abort_flag && atom_release_add(P.barrier, 1u) == unsigned(grid) - 1u) {
-        for (int i = 0; i < P.n_jobs; ++i) P.done[i] = 0u, P.fin[i] = 0u;  // nobody polls any more
+        for (int i = 0; i < P.n_jobs; ++i) P.fin[i] = 0u;  // nobody polls any more
         P.barrier[0] = 0u;
+        if (P.world > 1) P.barrier[1] = P.barrier[1] + 1u;  // the tag of the next launch's exchange
+        P.barrier[2] = P.barrier[2] + 1u;                   // of the next launch's partial sums
+        P.fin[P.n_jobs] = P.fin[P.n_jobs] + 1u;             // of this job list's next published words
     }
     // ---- release tensor memory (always), after every role is done with it ----
     tc_fence_before();

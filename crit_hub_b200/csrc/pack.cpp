@@ -6,6 +6,9 @@
 // re-laid once at load time; no value is re-encoded.
 #include <cstdint>
 #include <cstring>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 
 #include "../../include/qgemv.h"
 #include "qgemv_layout.h"
@@ -55,6 +58,22 @@ uint64_t checksum64(const uint8_t* p, uint64_t bytes) {
     return h ^ bytes;
 }
 
+void fill_header(qg_blob_header* hd, int fmt, const Dims& d, float tensor_scale) {
+    std::memset(hd, 0, sizeof *hd);
+    hd->magic = QG_BLOB_MAGIC;
+    hd->version = QG_BLOB_VERSION;
+    hd->fmt = uint32_t(fmt);
+    hd->header_bytes = QG_HEADER_BYTES;
+    hd->N = d.n;
+    hd->K = d.k;
+    hd->n_panels = d.panels;
+    hd->units_per_panel = d.units;
+    hd->unit_bytes = d.unit_bytes;
+    hd->tensor_scale = fmt == QGEMV_FMT_FP8 ? 1.0f : tensor_scale;
+    hd->aux_bytes = d.aux_bytes;
+    hd->payload_bytes = d.payload_bytes;
+}
+
 const qg_blob_header* check_header(const void* blob, size_t bytes) {
     if (!blob || bytes < QG_HEADER_BYTES) return nullptr;
     const qg_blob_header* hd = static_cast<const qg_blob_header*>(blob);
@@ -81,6 +100,26 @@ size_t qgemv_packed_size(int fmt, int64_t N, int64_t K, const qgemv_shard* shard
     return size_t(QG_HEADER_BYTES + d.aux_bytes + d.payload_bytes);
 }
 
+// Threads of the packer's OpenMP loops.  Launchers of one process per GPU often export
+// OMP_NUM_THREADS=1; a process that packs many matrices sets its share of the cores here.
+int qgemv_set_host_threads(int n) {
+    if (n < 1) return QGEMV_ERR_INVALID_ARG;
+#ifdef _OPENMP
+    omp_set_num_threads(n);
+#endif
+    return QGEMV_OK;
+}
+
+// The 256-byte header qgemv_pack_host would write for this matrix (checksum left zero): for
+// callers that lay the payload out themselves, on the device.
+int qgemv_pack_header(int fmt, float tensor_scale, int64_t N, int64_t K, const qgemv_shard* shard, void* header_out) {
+    Dims d;
+    if (!header_out) return QGEMV_ERR_INVALID_ARG;
+    if (!make_dims(fmt, N, K, shard, &d)) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+    fill_header(static_cast<qg_blob_header*>(header_out), fmt, d, tensor_scale);
+    return QGEMV_OK;
+}
+
 int qgemv_pack_host(int fmt, const void* codes_v, const void* scales_v, float tensor_scale,
                     int64_t N, int64_t K, const qgemv_shard* shard, void* blob_out) {
     Dims d;
@@ -88,19 +127,7 @@ int qgemv_pack_host(int fmt, const void* codes_v, const void* scales_v, float te
     if (!make_dims(fmt, N, K, shard, &d)) return QGEMV_ERR_UNSUPPORTED_SHAPE;
     uint8_t* blob = static_cast<uint8_t*>(blob_out);
     qg_blob_header hd;
-    std::memset(&hd, 0, sizeof hd);
-    hd.magic = QG_BLOB_MAGIC;
-    hd.version = QG_BLOB_VERSION;
-    hd.fmt = uint32_t(fmt);
-    hd.header_bytes = QG_HEADER_BYTES;
-    hd.N = d.n;
-    hd.K = d.k;
-    hd.n_panels = d.panels;
-    hd.units_per_panel = d.units;
-    hd.unit_bytes = d.unit_bytes;
-    hd.tensor_scale = fmt == QGEMV_FMT_FP8 ? 1.0f : tensor_scale;
-    hd.aux_bytes = d.aux_bytes;
-    hd.payload_bytes = d.payload_bytes;
+    fill_header(&hd, fmt, d, tensor_scale);
 
     uint8_t* aux = blob + QG_HEADER_BYTES;
     uint8_t* payload = aux + d.aux_bytes;

@@ -31,10 +31,15 @@ class LayerStack:
     """Owns an activation arena [sum B*K] bf16 and an output arena [sum B*N]; one GEMV per weight."""
 
     def __init__(self, handle: QGemv, weights: list[Weight], batch: int, out_dtype: int = OUT_BF16,
-                 device: int = 0, prefetch_next: bool = False, after_call=None, fused: bool = False):
+                 device: int = 0, prefetch_next: bool = False, after_call=None, fused: bool = False,
+                 chained: bool = False, job_flags: list[int] | None = None, chain: bool = False):
         self.handle, self.batch, self.out_dtype = handle, batch, out_dtype
         # fused: the whole list as ONE persistent launch (qgemv_sequence_*; tensor-core layout only, no hooks)
         self.fused = fused and after_call is None
+        # chained: every job of the fused launch waits for the one before it, as a decode step's
+        # projections do (each consumes, through attention / activation / norm, what the previous produced)
+        self.chained = chained
+        self.job_flags = job_flags  # per-call qgemv_job flags of the fused launch (e.g. JOB_ALLREDUCE), or None
         self.sequence = None
         # after_call(i): optional hook enqueued on the same stream right after GEMV i (and captured
         # with it), e.g. the all-reduce of a row-parallel projection's partial outputs
@@ -42,10 +47,16 @@ class LayerStack:
         self.prefetch_next = prefetch_next  # name the following matrix in every call (L2 prefetch)
         self.device = torch.device("cuda", device)
         self.calls: list[_Call] = []
+        # chain: call i reads the first K_i columns of call i - 1's output (a decode step's data flow with the
+        # element-wise work between the projections left out); only the first call has an input of its own.
+        # Needs the fused launch (rows of a column range are strided) and bf16 outputs.
+        self.chain = chain and self.fused and out_dtype == OUT_BF16 and all(
+            weights[i].K <= weights[i - 1].N and weights[i - 1].N % 8 == 0 for i in range(1, len(weights)))
         x_total = y_total = 0
-        for w in weights:
+        for i, w in enumerate(weights):
             self.calls.append(_Call(w, x_total, y_total))
-            x_total += ((batch * w.K + 7) // 8) * 8      # keep every row block 16-byte aligned
+            if not self.chain or i == 0:
+                x_total += ((batch * w.K + 7) // 8) * 8      # keep every row block 16-byte aligned
             y_total += ((batch * w.N + 7) // 8) * 8
         self.x_dev = torch.zeros(x_total, dtype=torch.bfloat16, device=self.device)
         ydt = torch.bfloat16 if out_dtype == OUT_BF16 else torch.float32
@@ -59,10 +70,17 @@ class LayerStack:
     # ---- buffers --------------------------------------------------------------------------
     def set_inputs(self, xs: list[torch.Tensor]) -> None:
         """xs[i]: bf16 [batch][K_i] activations of call i (host or device tensors)."""
-        for c, x in zip(self.calls, xs):
+        for c, x in zip(self.calls[:1] if self.chain else self.calls, xs):
             n = self.batch * c.weight.K
             self.x_host[c.x_off:c.x_off + n].copy_(x.reshape(-1).to(torch.bfloat16).cpu())
         self.x_dev.copy_(self.x_host, non_blocking=False)
+
+    def input(self, i: int) -> torch.Tensor:
+        """Host copy of call i's activations [batch][K] as of the last step_host()."""
+        c = self.calls[i]
+        if self.chain and i > 0:
+            return self.output(i - 1, host=True)[:, :c.weight.K]
+        return self.x_host[c.x_off:c.x_off + self.batch * c.weight.K].view(self.batch, c.weight.K)
 
     def output(self, i: int, host: bool = False) -> torch.Tensor:
         c = self.calls[i]
@@ -86,10 +104,17 @@ class LayerStack:
             if self.sequence is None:
                 from . import ERR_UNSUPPORTED_SHAPE, QgemvError
                 try:
-                    self.sequence = self.handle.sequence(
-                        [(c.weight, xb + c.x_off * xe, yb + c.y_off * ye, self.out_dtype) for c in self.calls], self.batch)
+                    jobs = []
+                    for i, c in enumerate(self.calls):
+                        fl = self.job_flags[i] if self.job_flags else 0
+                        if self.chain and i > 0:
+                            prev = self.calls[i - 1]
+                            jobs.append((c.weight, yb + prev.y_off * ye, yb + c.y_off * ye, self.out_dtype, fl, prev.weight.N))
+                        else:
+                            jobs.append((c.weight, xb + c.x_off * xe, yb + c.y_off * ye, self.out_dtype, fl))
+                    self.sequence = self.handle.sequence(jobs, self.batch, chained=self.chained)
                 except QgemvError as e:  # e.g. activations too large for the persistent kernel: one launch per GEMV
-                    if e.status != ERR_UNSUPPORTED_SHAPE:
+                    if e.status != ERR_UNSUPPORTED_SHAPE or self.chain:
                         raise
                     self.fused = False
             if self.fused:
@@ -142,14 +167,20 @@ def llama_layer_shapes(hidden: int, q_heads: int, kv_heads: int, head_dim: int, 
             ("gate_up", 2 * inter, hidden), ("down", hidden, inter)]
 
 
-def synth_nvfp4(N: int, K: int, seed: int, device: torch.device):
-    """Seeded synthetic NVFP4 matrix: codes uniform over the 16 E2M1 codes, E4M3 scales of
-    |N(0,1)| * 0.05 per 16-element block, tensor scale 1.0.  Returns host numpy (codes, scales)."""
+def synth_nvfp4_dev(N: int, K: int, seed: int, device: torch.device):
+    """Seeded synthetic NVFP4 matrix in device memory: codes uniform over the 16 E2M1 codes, E4M3
+    scales of |N(0,1)| * 0.05 per 16-element block.  Returns device tensors (codes u8 [N][K/2],
+    scales u8 [N][K/16]); the same seed gives the same matrix on every GPU."""
     g = torch.Generator(device=device)
     g.manual_seed(seed)
     codes = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=device, generator=g)
     sc = torch.randn((N, K // 16), dtype=torch.float32, device=device, generator=g).abs_().mul_(0.05)
-    scales = sc.to(torch.float8_e4m3fn).view(torch.uint8)
+    return codes, sc.to(torch.float8_e4m3fn).view(torch.uint8)
+
+
+def synth_nvfp4(N: int, K: int, seed: int, device: torch.device):
+    """synth_nvfp4_dev copied to the host: numpy (codes, scales), tensor scale 1.0."""
+    codes, scales = synth_nvfp4_dev(N, K, seed, device)
     return codes.cpu().numpy(), scales.cpu().numpy()
 
 

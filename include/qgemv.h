@@ -129,6 +129,12 @@ int qgemv_sm_count(const qgemv_handle* h);
 size_t qgemv_packed_size(int fmt, int64_t N, int64_t K, const qgemv_shard* shard /* nullable */);
 int qgemv_pack_host(int fmt, const void* codes, const void* scales, float tensor_scale, int64_t N,
                     int64_t K, const qgemv_shard* shard /* nullable */, void* blob_out);
+/* The 256-byte header alone (checksum zero), for callers that lay the payload out themselves. */
+int qgemv_pack_header(int fmt, float tensor_scale, int64_t N, int64_t K, const qgemv_shard* shard /* nullable */,
+                      void* header_out);
+/* Threads of the host packer's loops (launchers of one process per GPU often export
+ * OMP_NUM_THREADS=1). */
+int qgemv_set_host_threads(int n);
 /* Inverse of qgemv_pack_host for the (possibly sharded) sub-matrix held by the blob.
  * scales_out is u8 [n][k/16] (NVFP4) or float [n] (FP8). */
 int qgemv_unpack_host(const void* blob, size_t bytes, void* codes_out, void* scales_out,
@@ -142,11 +148,23 @@ int qgemv_blob_info(const void* blob, size_t bytes, int* fmt, int64_t* N, int64_
  * Copies a packed blob to the device.  `n_stacked` > 1 loads that many equally shaped blobs laid
  * back to back in host memory as one stacked weight (the experts of an MoE layer). */
 int qgemv_load(qgemv_handle* h, const void* host_blob, size_t bytes, qgemv_weight** out);
+/* The same weight from CANONICAL NVFP4 arrays that are already in device memory (codes u8
+ * [N][K/2], 8-byte aligned, and scales u8 [N][K/16], row-major): the layout is produced by a
+ * kernel, byte for byte what qgemv_pack_host writes, so a checkpoint that was read straight into
+ * device memory needs no host pass.  fmt: QGEMV_FMT_NVFP4_TC only (others:
+ * QGEMV_ERR_UNSUPPORTED_SHAPE).  shard as in qgemv_pack_host.  Returns after the kernel has run on
+ * `stream`; the inputs may be freed then.  No counterpart in the registry (its engines load
+ * pre-quantised files through their own loaders, engines/crit-labs/mtp5-nvfp4-drafts/card.yaml:69). */
+int qgemv_load_device(qgemv_handle* h, int fmt, const void* codes_dev, const void* scales_dev, float tensor_scale,
+                      int64_t N, int64_t K, const qgemv_shard* shard /* nullable */, void* stream, qgemv_weight** out);
 int qgemv_load_stacked(qgemv_handle* h, const void* host_blobs, size_t bytes_each, int n_stacked,
                        qgemv_weight** out);
 int qgemv_unload(qgemv_handle* h, qgemv_weight* w);
 /* Algorithmic weight bytes of one matrix: N*K*0.5625 + 4 (NVFP4) or N*K + 4*N (FP8). */
 int64_t qgemv_weight_bytes(const qgemv_weight* w);
+/* Copies the packed blob(s) of a loaded weight back to host memory; bytes must be n_stacked *
+ * qgemv_packed_size(...).  (A weight made by qgemv_load_device carries a zero checksum.) */
+int qgemv_weight_read(qgemv_handle* h, const qgemv_weight* w, void* host_out, size_t bytes);
 
 /* ---- decode GEMV, batch 1..8 (up to 16 rows per call as two launches) -------------------------
  * y[b][n] = sum_k dequant(W)[n][k] * x[b][k], fp32 accumulation, output bf16 or fp32.
@@ -173,24 +191,30 @@ int qgemv_gemv_prefetch(qgemv_handle* h, const qgemv_weight* w, const void* x_bf
 /* ---- a sequence of GEMVs as one launch --------------------------------------------------------
  * The projections of a decode step, in order, as ONE persistent kernel ("one CUDA graph per round",
  * tools/fixtures/engines/crit-labs/mtp4-nvfp4-mma/card.yaml:75, taken one step further: one launch).
- * Job i computes y_i = W_i x_i exactly as qgemv_gemv would; job i + 1 may read anything job i wrote
- * (a grid-wide barrier separates them; where job i + 1 reads or overwrites y_i -- the address ranges
- * are compared when the sequence is created -- the barrier also waits for the row tiles of y_i
- * that were split along K to be added up).  While the CTAs finish one job and convert the next one's activations, the
- * weights of the following jobs keep streaming into shared memory, so HBM does not idle at the
- * boundaries the way it does between separate launches.
+ * Job i computes y_i = W_i x_i exactly as qgemv_gemv would.  Ordering follows the data: when the
+ * sequence is created the address ranges of every job's x and y are compared with those of the
+ * jobs before it, and a job waits (for the complete output, split row tiles added up) for the
+ * latest earlier job whose output it reads or overwrites, or whose input it overwrites.  A job
+ * whose ranges touch no earlier job's may overlap the tail of the jobs before it.  A caller whose
+ * dependency is not visible in the addresses sets QGEMV_JOB_AFTER_PREVIOUS on the job: it then
+ * waits for the job before it in any case.  While the CTAs finish one job and convert the next
+ * one's activations, the weights of the following jobs keep streaming into shared memory, so HBM
+ * does not idle at the boundaries the way it does between separate launches.
  * Weights: QGEMV_FMT_NVFP4_TC only.  All jobs share the batch size B (1..8).  The job list is
  * copied to the device by qgemv_sequence_create (which allocates); qgemv_sequence_run launches,
  * allocates nothing and may be captured into a CUDA graph.  The kernel's CTAs wait on one another:
  * the launch is cooperative and takes every SM (grid_override above the SM count is refused).
  * QGEMV_ERR_UNSUPPORTED_SHAPE when the activations of one job (B * K digit planes) leave no room
  * for a weight ring in shared memory: call qgemv_gemv per job then. */
+#define QGEMV_JOB_AFTER_PREVIOUS 1 /* start only when the job before this one is complete */
+#define QGEMV_JOB_ALLREDUCE 2      /* row-parallel projection: y = sum over the ranks of W_r x_r (see the exchange below) */
 typedef struct qgemv_job {
     const qgemv_weight* w;
     const void* x;   /* device bf16 [B][K], 16-byte aligned */
     void* y;         /* device [B][N] */
     int32_t y_dtype; /* QGEMV_OUT_BF16 or QGEMV_OUT_F32 */
-    int32_t flags;   /* 0 (reserved) */
+    int32_t flags;   /* 0, or QGEMV_JOB_AFTER_PREVIOUS | QGEMV_JOB_ALLREDUCE */
+    int64_t x_stride; /* elements between the rows of x; 0 = K.  A multiple of 8, at least K */
 } qgemv_job;
 typedef struct qgemv_sequence qgemv_sequence;
 int qgemv_sequence_create(qgemv_handle* h, const qgemv_job* jobs, int n_jobs, int B, qgemv_sequence** out);
@@ -199,19 +223,42 @@ int qgemv_sequence_destroy(qgemv_handle* h, qgemv_sequence* seq);
 
 /* ---- tensor-parallel exchange -------------------------------------------------------------------
  * Not in the registry (every listed engine runs on one GPU, engines/crit-labs/mtp5-nvfp4-drafts/
- * card.yaml:100); needed for the row-parallel projections (o, down) of a model sharded over the
- * GPUs of one node.  One process per GPU.  qgemv_tp_create allocates this rank's exchange buffer
- * and returns its CUDA IPC handle (QGEMV_IPC_HANDLE_BYTES); the caller gathers the handles of all
- * ranks (any transport) and passes the concatenation, rank order, to qgemv_tp_connect.
- * qgemv_tp_allreduce then sums a vector of n <= max_elems elements over the ranks in place
- * (fp32 accumulation in rank order: every rank gets the same bits): every rank pushes its partial
- * into its slot of every rank's buffer over NVLink, flags it, waits -- bounded -- for the flags
- * in its own buffer and reduces locally.  Asynchronous on `stream`, graph-capturable; all ranks
- * must issue the same sequence of calls. */
+ * card.yaml:100); needed for the projections of a model sharded over the GPUs of one node:
+ * column-parallel QKV and gate/up (shards from qgemv_pack_host / qgemv_load_device with a row
+ * range), row-parallel o and down (a column range) whose outputs are partial sums.
+ * One process per GPU: qgemv_tp_create allocates this rank's exchange buffer and returns its CUDA
+ * IPC handle (QGEMV_IPC_HANDLE_BYTES); the caller gathers the handles of all ranks (any transport)
+ * and passes the concatenation, rank order, to qgemv_tp_connect.  One process driving several
+ * GPUs (peer access enabled by the caller) hands the other ranks' buffers over as pointers instead:
+ * qgemv_tp_buffer of each handle, then qgemv_tp_connect_ptrs (peer_buffers[own rank] is ignored).
+ *
+ * The buffer: two parities x `world` slots x max_elems pairs {fp32 value, 32-bit tag}, 8 bytes
+ * each, all zero at first: slot s of parity p starts at ((p * world + s) * max_elems) * 8.  A rank
+ * pushes its values, tagged with the count of exchanges, into its slot of EVERY rank's buffer over
+ * NVLink (plain peer stores), then reads the pairs of all ranks from its own buffer, re-polling --
+ * bounded -- the ones whose tag is not there yet.  Sums are formed in fp32 in rank order, so every
+ * rank gets the same bits.  No multicast; peers are only written to.
+ *
+ * qgemv_tp_allreduce: y (bf16 or fp32, n elements) becomes the sum over the ranks, in place.
+ * qgemv_tp_allgather: y[r * n_shard + e] = rank r's shard[e] (column-parallel outputs, the logits
+ * of a vocabulary-parallel output head); shard and y must not overlap.
+ * Both are asynchronous on `stream` and may be captured into a CUDA graph; all ranks must issue
+ * the same sequence of calls.  They use elements [0, n) of the slots.
+ * Inside a job list (qgemv_sequence_create) a job flagged QGEMV_JOB_ALLREDUCE is reduced over the
+ * ranks by the sequence kernel itself: the thread that has added up a row of the partial output
+ * pushes it and gathers the other ranks' -- no launch, no grid-wide wait.  Such jobs take B * N
+ * elements each from the TOP of the slots for as long as the list lives, so max_elems must cover
+ * them plus the longest stand-alone exchange; QGEMV_ERR_UNSUPPORTED_SHAPE when it does not, or when
+ * one CTA's share of the job would hold a whole 128-row tile (N above about 128 rows per SM).  Every
+ * rank must create and run the same lists in the same order.  With world == 1 the flag is ignored.
+ * After QGEMV_ERR_TIMEOUT from an exchange the ranks' counts may differ: destroy the handles. */
 #define QGEMV_IPC_HANDLE_BYTES 64
 int qgemv_tp_create(qgemv_handle* h, int rank, int world, int64_t max_elems, void* ipc_handle_out);
 int qgemv_tp_connect(qgemv_handle* h, const void* all_handles);
+int qgemv_tp_buffer(qgemv_handle* h, void** dev_ptr, size_t* bytes);
+int qgemv_tp_connect_ptrs(qgemv_handle* h, void* const* peer_buffers /* [world] */);
 int qgemv_tp_allreduce(qgemv_handle* h, void* y, int y_dtype, int64_t n, void* stream);
+int qgemv_tp_allgather(qgemv_handle* h, const void* shard, void* y, int y_dtype, int64_t n_shard, void* stream);
 
 /* ---- allocation-free GEMV --------------------------------------------------------------------
  * No counterpart in the crit-hub registry; added for callers that cannot allocate device memory

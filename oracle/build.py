@@ -31,5 +31,35 @@ def build(force: bool = False) -> str:
     return OUT
 
 
+OUT_NATIVE = os.path.join(OUT_DIR, "libqgemv_oracle_native.so")
+
+
+def build_native(force: bool = False) -> str | None:
+    """The same source for the machine it is compiled on (-O3 -march=native): used only for the TIMED
+    fp32 CPU baseline, and only on the machine that built it (the instruction set does not travel).
+    A marker file records the CPU it was built for.  Returns None when the compile fails."""
+    os.makedirs(OUT_DIR, exist_ok=True)
+    marker = OUT_NATIVE + ".cpu"
+    cpu = ""
+    try:
+        with open("/proc/cpuinfo") as f:
+            cpu = next((ln.split(":", 1)[1].strip() for ln in f if ln.startswith("model name")), "")
+    except OSError:
+        pass
+    fresh = (os.path.exists(OUT_NATIVE) and os.path.exists(marker)
+             and os.path.getmtime(OUT_NATIVE) >= os.path.getmtime(SRC) and open(marker).read() == cpu)
+    if fresh and not force:
+        return OUT_NATIVE
+    cmd = ["g++", "-std=c++17", "-O3", "-fopenmp", "-ffp-contract=off", "-fno-fast-math", "-march=native",
+           "-shared", "-fPIC", SRC, "-o", OUT_NATIVE]
+    try:
+        subprocess.run(cmd, check=True, capture_output=True)
+    except (subprocess.CalledProcessError, OSError):
+        return None
+    with open(marker, "w") as f:
+        f.write(cpu)
+    return OUT_NATIVE
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv))

@@ -51,6 +51,36 @@ def lib() -> C.CDLL:
     return _LIB
 
 
+_FAST = None
+
+
+def fast_lib() -> C.CDLL:
+    """The library the TIMED fp32 baseline runs from: this machine's own build (-O3 -march=native)
+    when it can be compiled here, else the portable one.  Parity checks always use lib()."""
+    global _FAST
+    if _FAST is None:
+        import importlib.util
+        spec = importlib.util.spec_from_file_location("_oracle_build", os.path.join(_HERE, "build.py"))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        path = mod.build_native()
+        if path is None:
+            _FAST = lib()
+        else:
+            _FAST = C.CDLL(path)
+            _FAST.orc_num_threads.restype = C.c_int
+            _FAST.orc_gemv_nvfp4_fast.restype = C.c_int
+            _FAST.orc_gemv_fp8_fast.restype = C.c_int
+    return _FAST
+
+
+def set_threads(n: int) -> None:
+    """Host threads of the OpenMP loops (both builds): launchers may have exported OMP_NUM_THREADS=1."""
+    lib().orc_set_threads(C.c_int(int(n)))
+    if fast_lib() is not lib():
+        fast_lib().orc_set_threads(C.c_int(int(n)))
+
+
 def _p(a: np.ndarray):
     assert a.flags["C_CONTIGUOUS"]
     return a.ctypes.data_as(C.c_void_p)
@@ -113,14 +143,15 @@ def gemv_fp8_f64(codes, ch_scale, x_bf16) -> np.ndarray:
     return y
 
 
-def gemv_nvfp4_fast(codes, scales, ts, x_bf16):
+def gemv_nvfp4_fast(codes, scales, ts, x_bf16, native: bool = False):
     """fp32-accumulated OpenMP GEMV (the timed CPU baseline). Returns (y fp32 [B][N], threads)."""
     N, K = scales.shape[0], scales.shape[1] * 16
     x_bf16 = np.ascontiguousarray(x_bf16.reshape(-1, K))
     B = x_bf16.shape[0]
     y = np.empty((B, N), dtype=np.float32)
-    th = lib().orc_gemv_nvfp4_fast(_p(codes), _p(scales), C.c_float(ts), C.c_int64(N), C.c_int64(K),
-                                   _p(x_bf16), C.c_int64(B), _p(y))
+    L = fast_lib() if native else lib()
+    th = L.orc_gemv_nvfp4_fast(_p(codes), _p(scales), C.c_float(ts), C.c_int64(N), C.c_int64(K),
+                               _p(x_bf16), C.c_int64(B), _p(y))
     return y, th
 
 

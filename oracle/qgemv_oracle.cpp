@@ -297,6 +297,16 @@ void orc_moe_gemv_nvfp4_f64(const uint8_t* codes, const uint8_t* scales, const f
     }
 }
 
+// The host threads the OpenMP loops may use.  A launcher may export OMP_NUM_THREADS=1 for its worker
+// processes (torchrun does); the timed CPU baseline sets the count it wants explicitly.
+void orc_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int orc_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -338,7 +338,12 @@ def test_sequence_bounded_wait_reports_timeout(qg):
     seq.run()
     torch.cuda.synchronize()
     st = h.device_status()
-    assert st.code == qg.ERR_TIMEOUT and 71 <= st.where <= 82
+    assert st.code == qg.ERR_TIMEOUT and 71 <= st.where <= 85
+    # the same list once more on the same handle: the abandoned launch's tagged words must not be taken for new ones
+    seq.run()
+    torch.cuda.synchronize()
+    st = h.device_status()
+    assert st.code == qg.ERR_TIMEOUT and 71 <= st.where <= 85
     seq.destroy()
     for w in ws:
         w.unload()
@@ -401,6 +406,120 @@ def test_sequence_independent_and_distant_dependencies(qg, handle):
     torch.cuda.synchronize()
     for i, y in enumerate(ys):
         assert np.array_equal(y.view(torch.int16).cpu().numpy().view(np.uint16), keep[i]), i
+    seq.destroy()
+    for w in ws:
+        w.unload()
+
+
+def test_sequence_forced_order_flag(qg, handle):
+    """QGEMV_JOB_AFTER_PREVIOUS: jobs whose buffers are unrelated run strictly one after the other;
+    the results are the bits of the unordered list and of one launch per GEMV."""
+    import torch
+    B = 2
+    shapes = [(640, 1024), (4096, 512), (256, 4160), (6144, 1024), (130, 2048)]
+    ws, xd, ys, refs = [], [], [], []
+    for i, (N, K) in enumerate(shapes):
+        codes, scales, ts = O.make_nvfp4(N, K, seed=500 + i, ts=0.5)
+        ws.append(handle.load(qg.pack(qg.FMT_NVFP4_TC, codes, scales, ts)))
+        xh = O.make_x(B, K, seed=600 + i)
+        xd.append(U.dev_u16(xh))
+        ys.append(torch.full((B, N), float("nan"), dtype=torch.float32, device="cuda"))
+        refs.append(O.gemv_nvfp4_f64(codes, scales, ts, xh))
+    jobs = [(ws[i], xd[i].data_ptr(), ys[i].data_ptr(), qg.OUT_F32) for i in range(len(shapes))]
+    outs = {}
+    for chained in (False, True):
+        seq = handle.sequence(jobs, B, chained=chained)
+        for rep in range(2):
+            for y in ys:
+                y.fill_(float("nan"))
+            seq.run()
+            torch.cuda.synchronize()
+            U.status_ok(handle)
+        outs[chained] = [y.cpu().numpy().copy() for y in ys]
+        seq.destroy()
+    for i in range(len(shapes)):
+        assert O.rel_l2(outs[True][i], refs[i]) < TOL_F32, i
+        U.assert_bits_equal(outs[True][i], outs[False][i])
+    for w in ws:
+        w.unload()
+
+
+@pytest.mark.parametrize("N,K,shard", [(128, 64, None), (272, 2112, None), (1000, 4112, None), (6144, 4096, None),
+                                       (1024, 4096, (0, 1024, 2048, 4096)), (1000, 2112, (300, 811, 0, 2112)),
+                                       (512, 1024, (128, 384, 16, 1008))])
+def test_load_device_matches_host_pack(qg, handle, N, K, shard):
+    """The device-side packer writes byte for byte what the host packer writes (header apart from the
+    checksum, payload, zero padding), also for shards; and the GEMV on it matches the oracle."""
+    import torch
+    codes, scales, ts = O.make_nvfp4(N, K, seed=N + K, ts=0.625)
+    sh = qg.Shard(*shard) if shard else None
+    blob = qg.pack(qg.FMT_NVFP4_TC, codes, scales, ts, shard=sh)
+    cd, sd = torch.from_numpy(codes).cuda(), torch.from_numpy(scales).cuda()
+    w = handle.load_device(qg.FMT_NVFP4_TC, cd.data_ptr(), sd.data_ptr(), N, K, ts, shard=sh)
+    got = w.read_blob()
+    assert got.size == blob.size
+    assert np.array_equal(got[256:], blob[256:])
+    assert np.array_equal(got[:80], blob[:80]) and np.array_equal(got[88:256], blob[88:256])   # [80, 88): checksum
+    n0, n1, k0, k1 = shard if shard else (0, N, 0, K)
+    assert (w.N, w.K) == (n1 - n0, k1 - k0)
+    cs, ss, t2 = qg.unpack(blob)
+    x = O.make_x(2, k1 - k0, seed=7)
+    assert O.rel_l2(U.run_gemv(qg, handle, w, x), O.gemv_nvfp4_f64(cs, ss, t2, x)) < TOL_F32
+    w.unload()
+    with pytest.raises(qg.QgemvError) as e:
+        handle.load_device(qg.FMT_NVFP4, cd.data_ptr(), sd.data_ptr(), N, K, ts)
+    assert e.value.status == qg.ERR_UNSUPPORTED_SHAPE
+
+
+@pytest.mark.parametrize("B", [1, 4])
+def test_sequence_column_range_chain(qg, handle, B):
+    """Jobs that read a column range of the previous job's output (row stride = that job's N): the
+    path that picks the producer's rows up as they are published.  Checked link by link against
+    the oracle, run three times (the tags of one run must not satisfy the next), and compared with
+    one launch per GEMV on copies of the ranges."""
+    import torch
+    shapes = [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336), (6144, 4096), (1024, 2048)]
+    ws, mats = [], []
+    for i, (N, K) in enumerate(shapes):
+        codes, scales, _ = O.make_nvfp4(N, K, seed=700 + i)
+        ts = 1.0 / (0.1463 * K ** 0.5)
+        mats.append((codes, scales, ts))
+        ws.append(handle.load(qg.pack(qg.FMT_NVFP4_TC, codes, scales, ts)))
+    x0 = O.make_x(B, shapes[0][1], seed=777)
+    x0d = U.dev_u16(x0)
+    ys = [torch.full((B, N), float("nan"), dtype=torch.bfloat16, device="cuda") for N, _ in shapes]
+    jobs = [(ws[0], x0d.data_ptr(), ys[0].data_ptr(), qg.OUT_BF16)]
+    for i in range(1, len(shapes)):
+        jobs.append((ws[i], ys[i - 1].data_ptr(), ys[i].data_ptr(), qg.OUT_BF16, 0, shapes[i - 1][0]))
+    seq = handle.sequence(jobs, B)
+    first = None
+    for rep in range(3):
+        for y in ys:
+            y.fill_(float("nan"))
+        seq.run()
+        torch.cuda.synchronize()
+        U.status_ok(handle)
+        outs = [y.view(torch.int16).cpu().numpy().view(np.uint16) for y in ys]
+        xin = x0
+        for i, (codes, scales, ts) in enumerate(mats):
+            assert not np.isnan(O.bf16_decode(outs[i])).any(), (rep, i)
+            assert O.rel_l2(O.bf16_decode(outs[i]), O.gemv_nvfp4_f64(codes, scales, ts, xin)) < TOL_BF16, (rep, i)
+            if i + 1 < len(shapes):
+                xin = np.ascontiguousarray(outs[i][:, :shapes[i + 1][1]])
+        if first is None:
+            first = [o.copy() for o in outs]
+        else:
+            for a, b in zip(first, outs):
+                assert np.array_equal(a, b)
+    # one launch per GEMV on contiguous copies of the column ranges: the same bits
+    xin = x0d
+    for i, (N, K) in enumerate(shapes):
+        y = torch.full((B, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        handle.gemv(ws[i], xin.data_ptr(), B, y.data_ptr(), qg.OUT_BF16)
+        torch.cuda.synchronize()
+        assert np.array_equal(y.view(torch.int16).cpu().numpy().view(np.uint16), first[i]), i
+        if i + 1 < len(shapes):
+            xin = y[:, :shapes[i + 1][1]].contiguous()
     seq.destroy()
     for w in ws:
         w.unload()
