@@ -689,8 +689,10 @@ def main():
         g.manual_seed(1234)
         attn = torch.randn((B, ds.shapes[1][2]), generator=g).to(torch.bfloat16)          # o's full input
         mlp = torch.randn((B, ds.shapes[3][2]), generator=g).to(torch.bfloat16)           # down's full input
-        errs = []
+        errs, got = [], {}
         same = True
+        dist.barrier()
+        torch.cuda.synchronize()
         for mi, xin in ((1, attn), (3, mlp)):
             name, N, K = ds.shapes[mi]
             k0, k1 = rank * K // world, (rank + 1) * K // world
@@ -718,11 +720,14 @@ def main():
             eq = torch.tensor([1 if torch.equal(y0.view(torch.int32), y.view(torch.int32)) else 0], device=ds.device)
             dist.all_reduce(eq, op=dist.ReduceOp.MIN)
             same = same and bool(eq.item())
-            if rank == 0:
+            got[mi] = y.cpu().numpy()
+        if rank == 0:   # (after the exchanges: the other ranks' kernels must not wait for this host work)
+            for mi, xin in ((1, attn), (3, mlp)):
+                name, N, K = ds.shapes[mi]
                 codes, scales = synth_nvfp4_dev(N, K, mi, ds.device)       # layer 0's canonical matrix, unsharded
                 idx = sample_rows(N)
                 ref = O.gemv_nvfp4_f64(codes[idx].cpu().numpy(), scales[idx].cpu().numpy(), tensor_scale_for(K), u16(xin))
-                errs.append(O.rel_l2(y.cpu().numpy()[:, idx], ref))
+                errs.append(O.rel_l2(got[mi][:, idx], ref))
                 del codes, scales
         ok_t = torch.tensor([1 if (rank != 0 or max(errs) < TOL_F32) else 0], device=ds.device)
         dist.all_reduce(ok_t, op=dist.ReduceOp.MIN)
