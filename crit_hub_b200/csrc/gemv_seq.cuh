@@ -184,6 +184,15 @@ __device__ __forceinline__ void seq_walker(GsWalker& wk, int32_t total, int32_t 
     seq_range(total, cta, gj, wk.pos, wk.end);
 }
 
+// Eight activations of one row -> their eight digit planes in shared memory.  Not inlined: the kernel's five
+// roles run different code on an SM at once and share its instruction cache, so the code is kept small.
+__device__ __noinline__ void seq_store_unit(uint32_t dst, uint4 v, float sf) {
+    uint32_t pl[8];
+    tc_digits8(v, sf, pl);
+#pragma unroll
+    for (int z = 0; z < 8; ++z) asm volatile("st.shared.b32 [%0], %1;" ::"r"(dst + z * 16), "r"(pl[z]) : "memory");
+}
+
 constexpr int kSeqThreads = 32 * (2 + 12);  // producer, MMA issuer, three groups of four warps
 
 template <int S>
@@ -539,13 +548,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                     for (int w = 0; w < 4; ++w) m = max(m, all_max[w * 8 + b]);
                     return m;
                 };
-                auto store_unit = [&](int b, uint32_t dst, const uint4& v) {
-                    const float sf = pow2i(-tc_row_exponent(row_max(b)));
-                    uint32_t pl[8];
-                    tc_digits8(v, sf, pl);
-#pragma unroll
-                    for (int z = 0; z < 8; ++z) asm volatile("st.shared.b32 [%0], %1;" ::"r"(dst + z * 16), "r"(pl[z]) : "memory");
-                };
+                auto store_unit = [&](int b, uint32_t dst, const uint4& v) { seq_store_unit(dst, v, pow2i(-tc_row_exponent(row_max(b)))); };
                 uint4 keep[kKeep];
                 int kb[kKeep];
                 uint32_t kdst[kKeep];
@@ -566,8 +569,27 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                             }
                         }
                     }
+                    {
+                        uint64_t t0 = 0;
+                        for (int64_t it = 0;; ++it) {
+                            unsigned miss = 0;
 #pragma unroll
-                    for (int i = 0; i < kKeep; ++i) keep[i] = kp[i] ? pub_wait(kp[i], ka[i], kc[i]) : make_uint4(0, 0, 0, 0);
+                            for (int i = 0; i < kKeep; ++i)
+                                if (kp[i] && !pub_ok(ka[i], kc[i])) miss |= 1u << i;
+                            if (miss == 0) break;
+                            if (*abort_flag || out_of_time(it, t0)) {
+                                if (!*abort_flag) report(P.status, QGEMV_ERR_TIMEOUT, 84, j);
+                                *abort_flag = 1;
+                                alive = false;
+                                break;
+                            }
+#pragma unroll
+                            for (int i = 0; i < kKeep; ++i)
+                                if (miss & (1u << i)) ka[i] = ld_pub4(kp[i]), kc[i] = ld_pub4(kp[i] + 4);
+                        }
+                    }
+#pragma unroll
+                    for (int i = 0; i < kKeep; ++i) keep[i] = kp[i] ? pub_pack(ka[i], kc[i]) : make_uint4(0, 0, 0, 0);
                 } else {
 #pragma unroll
                     for (int i = 0; i < kKeep; ++i) {
@@ -582,6 +604,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                     const uint32_t m = unit_max(keep[i]);
                     if (m) atomicMax(wmax + kb[i], m);
                 }
+#pragma unroll 1
                 for (int wu = gt + kKeep * 128; wu < n_work; wu += 128) {
                     int b;
                     uint32_t dst;
@@ -593,6 +616,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
 #pragma unroll
                 for (int i = 0; i < kKeep; ++i)
                     if (gt + i * 128 < n_work) store_unit(kb[i], kdst[i], keep[i]);
+#pragma unroll 1
                 for (int wu = gt + kKeep * 128; wu < n_work; wu += 128) {
                     int b;
                     uint32_t dst;
@@ -650,8 +674,6 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 wk.units = kt_len, wk.pos = rb, wk.end = re;
                 GsSeg sg;
                 bool ok = true;
-                float scale[8];
-                bool have_scale = false;
                 while (wk.next(sg)) {
                     if (!ok) continue;  // this warp gave up: it still reaches the group's barriers below
                     const bool whole = sg.u0 == 0 && sg.u1 == kt_len;
@@ -664,56 +686,42 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                     }
                     tc_fence_after();
                     if (P.trace && gt == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 5] = globaltimer_ns();  // the last one stays
-                    if (!have_scale) {  // the MMAs of this job have run, so its planes and row maxima are there
-#pragma unroll
-                        for (int b = 0; b < 8; ++b)
-                            scale[b] = b < Bl ? job.tensor_scale * pow2i(tc_row_exponent(rowmax2[pb * 8 + b]) + 7) : 0.f;
-                        have_scale = true;
+                    const int n = sg.tile * 128 + row;
+                    // every contributor after the first starts its range inside this tile (slot 0 of its
+                    // pair); the first one's range may have started in an earlier tile
+                    unsigned long long* slot = nullptr;
+                    if (!whole) {
+                        const int32_t c_lo = int32_t(cta_of(int64_t(sg.tile) * kt_len, total, gj));
+                        const int32_t my_slot = cta == c_lo ? gs_slot(c_lo, sg.tile, kt_len, total, gj) : 2 * cta;
+                        slot = P.ws + (size_t(j & (kSeqPartBufs - 1)) * size_t(2 * grid) + size_t(my_slot)) * 1024 + row;
                     }
-                    float val[8];
+                    // (one row of the batch after the other, not unrolled: the code of this group has to stay small)
+#pragma unroll 1
+                    for (int b = 0; b < Bl; ++b) {
+                        uint32_t r[8];
+                        tmem_ld8(tmem_base + lane_base + acc * uint32_t(npad) + uint32_t(8 * b), r);
+                        float a = __uint_as_float(r[0]);
 #pragma unroll
-                    for (int b = 0; b < 8; ++b) {
-                        val[b] = 0.f;
-                        if (b < Bl) {
-                            uint32_t r[8];
-                            tmem_ld8(tmem_base + lane_base + acc * uint32_t(npad) + uint32_t(8 * b), r);
-                            float a = __uint_as_float(r[0]);
-#pragma unroll
-                            for (int z = 1; z < 8; ++z) a += __uint_as_float(r[z]);
-                            val[b] = a * scale[b];
+                        for (int z = 1; z < 8; ++z) a += __uint_as_float(r[z]);
+                        // (the MMAs of this job have run, so its planes and row maxima are there)
+                        a *= job.tensor_scale * pow2i(tc_row_exponent(rowmax2[pb * 8 + b]) + 7);
+                        if (!whole) {
+                            st_tagged(slot + b * 128, a, part_tag);
+                        } else if (n < job.N) {
+                            const int64_t idx = int64_t(b) * job.N + n;
+                            if (job.y_dtype == QGEMV_OUT_F32) {
+                                static_cast<float*>(job.y)[idx] = a;
+                            } else {
+                                const __nv_bfloat16 hv = __float2bfloat16_rn(a);
+                                static_cast<__nv_bfloat16*>(job.y)[idx] = hv;
+                                if (job.pub_off >= 0) st_pub(P.pub + size_t(job.pub_off) + size_t(idx), pub_tag | uint32_t(__bfloat16_as_ushort(hv)));
+                            }
                         }
                     }
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(sbase + SeqSmem::kBarDFree + 8 * acc);  // the accumulator may be overwritten
                     ++nseg;
-                    const int n = sg.tile * 128 + row;
-                    if (whole) {
-                        if (n < job.N) {
-#pragma unroll
-                            for (int b = 0; b < 8; ++b) {
-                                if (b < Bl) {
-                                    const int64_t idx = int64_t(b) * job.N + n;
-                                    if (job.y_dtype == QGEMV_OUT_F32) {
-                                        static_cast<float*>(job.y)[idx] = val[b];
-                                    } else {
-                                        const __nv_bfloat16 hv = __float2bfloat16_rn(val[b]);
-                                        static_cast<__nv_bfloat16*>(job.y)[idx] = hv;
-                                        if (job.pub_off >= 0) st_pub(P.pub + size_t(job.pub_off) + size_t(idx), pub_tag | uint32_t(__bfloat16_as_ushort(hv)));
-                                    }
-                                }
-                            }
-                        }
-                    } else {
-                        // every contributor after the first starts its range inside this tile (slot 0 of its
-                        // pair); the first one's range may have started in an earlier tile
-                        const int32_t c_lo = int32_t(cta_of(int64_t(sg.tile) * kt_len, total, gj));
-                        const int32_t my_slot = cta == c_lo ? gs_slot(c_lo, sg.tile, kt_len, total, gj) : 2 * cta;
-                        unsigned long long* slot = P.ws + (size_t(j & (kSeqPartBufs - 1)) * size_t(2 * grid) + size_t(my_slot)) * 1024 + row;
-#pragma unroll
-                        for (int b = 0; b < 8; ++b)
-                            if (b < Bl) st_tagged(slot + b * 128, val[b], part_tag);
-                    }
                 }
                 if (P.trace && gt == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 2] = globaltimer_ns();
                 // this CTA's rows and parts of job j are stored; its plane buffer may be reused
@@ -760,94 +768,18 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 // how far have ALL CTAs come with this step?  One probe per job, in flight with nothing else to do
                 if (gt == 0 && known + 1 < j && ld_acquire(P.fin + known + 1) >= unsigned(grid)) *fin_all = ++known;
                 if (!group_alive()) break;
-                if (pending) {
-                    const int n = tile * 128 + gt;
-                    const unsigned long long* parts = P.ws + size_t(j & (kSeqPartBufs - 1)) * size_t(2 * grid) * 1024 + gt;
-                    const uint32_t part_tag = seq_part_tag(launch_no, j), pub_tag = seq_pub_tag(run_no, j) << 16;
-                    if (n < job.N) {
-                        bool have = true;
-                        uint64_t t0 = 0;
-                        int64_t spins = 0;
-                        // a contributor's tagged part, re-read -- bounded -- until it carries this job's tag
-                        auto part_wait = [&](const unsigned long long* p, unsigned long long w, int who) -> float {
-                            while (have && uint32_t(w >> 32) != part_tag) {
-                                if (*abort_flag || out_of_time(spins++, t0)) {
-                                    if (!*abort_flag) report(P.status, QGEMV_ERR_TIMEOUT, 77, who);
-                                    *abort_flag = 1;
-                                    have = false;
-                                    break;
-                                }
-                                w = ld_flagged(p);
-                            }
-                            return __uint_as_float(uint32_t(w));
-                        };
-                        float v[8];
-#pragma unroll
-                        for (int b = 0; b < 8; ++b) {
-                            v[b] = 0.f;
-                            if (b < Bl) {
-                                // eight parts' loads in flight together; the additions stay in CTA order
-                                const unsigned long long* p0 = parts + size_t(lo_slot) * 1024 + b * 128;
-                                float a = part_wait(p0, ld_flagged(p0), c_lo);
-                                for (int32_t cc = c_lo + 1; cc <= c_hi; cc += 8) {
-                                    unsigned long long t[8];
-#pragma unroll
-                                    for (int z = 0; z < 8; ++z) t[z] = ld_flagged(parts + size_t(2 * min(cc + z, c_hi)) * 1024 + b * 128);
-#pragma unroll
-                                    for (int z = 0; z < 8; ++z)
-                                        if (cc + z <= c_hi) a += part_wait(parts + size_t(2 * (cc + z)) * 1024 + b * 128, t[z], cc + z);
-                                }
-                                v[b] = a;
-                            }
-                        }
-                        if (have && job.xoff >= 0) {
-                            // this rank's partial sums out to every rank first, then the ranks' sums for this row
-#pragma unroll
-                            for (int b = 0; b < 8; ++b)
-                                if (b < Bl) X.push(int64_t(job.xoff) + int64_t(b) * job.N + n, v[b]);
-#pragma unroll
-                            for (int b = 0; b < 8; ++b) {
-                                if (b < Bl && have) {
-                                    float part[kTpMaxWorld];
-                                    int missing = 0;
-                                    if (X.gather(int64_t(job.xoff) + int64_t(b) * job.N + n, part, P.spin_limit, missing)) {
-                                        float a = part[0];
-                                        for (int r = 1; r < P.world; ++r) a += part[r];
-                                        v[b] = a;
-                                    } else {
-                                        report(P.status, QGEMV_ERR_TIMEOUT, 83, missing);
-                                        *abort_flag = 1;
-                                        have = false;
-                                    }
-                                }
-                            }
-                        }
-                        if (have) {
-#pragma unroll
-                            for (int b = 0; b < 8; ++b) {
-                                if (b < Bl) {
-                                    const int64_t idx = int64_t(b) * job.N + n;
-                                    if (job.y_dtype == QGEMV_OUT_F32) {
-                                        static_cast<float*>(job.y)[idx] = v[b];
-                                    } else {
-                                        const __nv_bfloat16 hv = __float2bfloat16_rn(v[b]);
-                                        static_cast<__nv_bfloat16*>(job.y)[idx] = hv;
-                                        if (job.pub_off >= 0) st_pub(P.pub + size_t(job.pub_off) + size_t(idx), pub_tag | uint32_t(__bfloat16_as_ushort(hv)));
-                                    }
-                                }
-                            }
-                        }
-                    }
-                }
-                if (P.trace && gt == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 6] = globaltimer_ns();
-                // the job counts as finished on this CTA when its epilogues are through as well (rows of whole
-                // tiles, parts): then fin[j] == grid means that all of y is there
+                // this CTA's own part of the tile comes first, and the other contributors finish at about the same
+                // time: nothing is asked of global memory before this CTA's epilogues are through with the job
                 if (gt == 0) {
                     uint64_t t0 = 0;
                     for (int64_t it = 0; ld_acquire_cta_shared(sbase + SeqSmem::kEpiDone) <= j; ++it) {
                         if (*abort_flag) break;
                         // (the epilogue may itself be waiting for fin_all to move before it reuses a parts buffer)
-                        if (known + 1 < j && ld_acquire(P.fin + known + 1) >= unsigned(grid)) *fin_all = ++known;
+                        if (known + 1 < j && ld_acquire(P.fin + known + 1) >= unsigned(grid)) {
+                            *fin_all = ++known;
+                        } else {
+                            __nanosleep(100);
+                        }
                         if (out_of_time(it, t0)) {
                             report(P.status, QGEMV_ERR_TIMEOUT, 85, j);
                             *abort_flag = 1;
@@ -855,6 +787,82 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                         }
                     }
                 }
+                named_bar_sync(bar_id, 128);
+                if (pending) {
+                    const int n = tile * 128 + gt;
+                    const unsigned long long* parts = P.ws + size_t(j & (kSeqPartBufs - 1)) * size_t(2 * grid) * 1024 + gt;
+                    const uint32_t part_tag = seq_part_tag(launch_no, j), pub_tag = seq_pub_tag(run_no, j) << 16;
+                    if (n < job.N && !*abort_flag) {
+                        bool have = true;
+                        uint64_t t0 = 0;
+                        int64_t spins = 0;
+                        // (one row of the batch after the other, not unrolled: this group's code has to stay small --
+                        // five roles run different code on the SM at once and share its instruction cache)
+#pragma unroll 1
+                        for (int b = 0; b < Bl && have; ++b) {
+                            // the first contributor's own part, then the others eight at a time: the loads of a group
+                            // are in flight together, the ones whose tag is not there yet are re-read together
+                            // -- bounded --, and the additions stay in CTA order
+                            float a = 0.f;
+#pragma unroll 1
+                            for (int32_t cc = c_lo; cc <= c_hi && have; cc += 8) {
+                                const unsigned long long* pz[8];
+                                unsigned long long t[8];
+#pragma unroll
+                                for (int z = 0; z < 8; ++z) {
+                                    const int32_t c = min(cc + z, c_hi);
+                                    pz[z] = parts + size_t(c == c_lo ? lo_slot : 2 * c) * 1024 + b * 128;
+                                    t[z] = ld_flagged(pz[z]);
+                                }
+                                for (;;) {
+                                    unsigned miss = 0;
+#pragma unroll
+                                    for (int z = 0; z < 8; ++z)
+                                        if (uint32_t(t[z] >> 32) != part_tag) miss |= 1u << z;
+                                    if (miss == 0) break;
+                                    if (*abort_flag || out_of_time(spins++, t0)) {
+                                        if (!*abort_flag) report(P.status, QGEMV_ERR_TIMEOUT, 77, cc + __ffs(int(miss)) - 1);
+                                        *abort_flag = 1;
+                                        have = false;
+                                        break;
+                                    }
+#pragma unroll
+                                    for (int z = 0; z < 8; ++z)
+                                        if (miss & (1u << z)) t[z] = ld_flagged(pz[z]);
+                                }
+#pragma unroll
+                                for (int z = 0; z < 8; ++z)
+                                    if (cc + z <= c_hi) a = (cc + z == c_lo) ? __uint_as_float(uint32_t(t[z])) : a + __uint_as_float(uint32_t(t[z]));
+                            }
+                            if (!have) break;
+                            const int64_t idx = int64_t(b) * job.N + n;
+                            if (job.xoff >= 0) {
+                                // this rank's partial sum out to every rank, then the ranks' sums for this row, added in rank order
+                                X.push(int64_t(job.xoff) + idx, a);
+                                float part[kTpMaxWorld];
+                                int missing = 0;
+                                if (X.gather(int64_t(job.xoff) + idx, part, P.spin_limit, missing)) {
+                                    a = part[0];
+                                    for (int r = 1; r < P.world; ++r) a += part[r];
+                                } else {
+                                    report(P.status, QGEMV_ERR_TIMEOUT, 83, missing);
+                                    *abort_flag = 1;
+                                    have = false;
+                                    break;
+                                }
+                            }
+                            if (job.y_dtype == QGEMV_OUT_F32) {
+                                static_cast<float*>(job.y)[idx] = a;
+                            } else {
+                                const __nv_bfloat16 hv = __float2bfloat16_rn(a);
+                                static_cast<__nv_bfloat16*>(job.y)[idx] = hv;
+                                if (job.pub_off >= 0) st_pub(P.pub + size_t(job.pub_off) + size_t(idx), pub_tag | uint32_t(__bfloat16_as_ushort(hv)));
+                            }
+                        }
+                    }
+                }
+                if (P.trace && gt == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 6] = globaltimer_ns();
+                // (the epilogues of the job are through, see above: fin[j] == grid means that all of y is there)
                 named_bar_sync(bar_id, 128);
                 if (gt == 0) red_release_add(P.fin + j, 1u);
                 job = next;
