@@ -184,6 +184,8 @@ __device__ __forceinline__ void seq_walker(GsWalker& wk, int32_t total, int32_t 
     seq_range(total, cta, gj, wk.pos, wk.end);
 }
 
+__device__ __noinline__ void seq_report(int32_t* status, int where, int extra) { report(status, QGEMV_ERR_TIMEOUT, where, extra); }
+
 // Eight activations of one row -> their eight digit planes in shared memory.  Not inlined: the kernel's five
 // roles run different code on an SM at once and share its instruction cache, so the code is kept small.
 __device__ __noinline__ void seq_store_unit(uint32_t dst, uint4 v, float sf) {
@@ -267,7 +269,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                     const uint8_t* src = job.payload + (uint64_t(sg.tile) * job.kt + uint64_t(sg.u0)) * kTcItemBytes;
                     for (int32_t left = sg.u1 - sg.u0; left > 0; left -= S) {
                         if (use > 0 && !mbar_wait_probe(sbase + SeqSmem::kBarEmpty + 8 * s, (use - 1) & 1, P.spin_limit)) {
-                            report(P.status, QGEMV_ERR_TIMEOUT, 71, j);
+                            seq_report(P.status, 71, j);
                             *abort_flag = 1;
                             ok = false;
                             break;
@@ -311,7 +313,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 const int32_t kt_len = job.kt;
                 // the digit planes of this job (every CTA signals, also one without items)
                 if (!mbar_wait(sbase + SeqSmem::kBarXReady + 8 * pb, pph, P.spin_limit)) {
-                    report(P.status, QGEMV_ERR_TIMEOUT, 72, j);
+                    seq_report(P.status, 72, j);
                     *abort_flag = 1;
                     ok = false;
                     break;
@@ -332,7 +334,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                     // the accumulator is free once the epilogue of the segment before last has read it
                     if (nseg >= 2 &&
                         !mbar_wait_probe(sbase + SeqSmem::kBarDFree + 8 * (nseg & 1), ((nseg >> 1) - 1) & 1, P.spin_limit)) {
-                        report(P.status, QGEMV_ERR_TIMEOUT, 73, int(nseg));
+                        seq_report(P.status, 73, int(nseg));
                         *abort_flag = 1;
                         ok = false;
                         break;
@@ -348,7 +350,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                         // barrier's acquire is all the ordering the MMAs need -- no tcgen05 fence here,
                         // which costs this thread a few hundred cycles per stage)
                         if (!mbar_wait_probe(bar_full, full_par, P.spin_limit)) {
-                            report(P.status, QGEMV_ERR_TIMEOUT, 74, mi);
+                            seq_report(P.status, 74, mi);
                             *abort_flag = 1;
                             ok = false;
                             break;
@@ -436,7 +438,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 for (int64_t it = 0; ld_acquire(counter) < unsigned(grid); ++it) {
                     if (*abort_flag) break;
                     if (out_of_time(it, t0)) {
-                        report(P.status, QGEMV_ERR_TIMEOUT, site, j);
+                        seq_report(P.status, site, j);
                         *abort_flag = 1;
                         break;
                     }
@@ -464,7 +466,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 // the plane buffer and its row maxima were last used by job j - nbuf: its epilogues must be through
                 if (j >= nb && gt == 0 &&
                     !mbar_wait(sbase + SeqSmem::kBarEDone + 8 * pb, (pph ^ 1u), P.spin_limit)) {
-                    report(P.status, QGEMV_ERR_TIMEOUT, 78, j);
+                    seq_report(P.status, 78, j);
                     *abort_flag = 1;
                 }
                 if (job.dep >= 0) poll_all(P.fin + job.dep, 80, j);  // an earlier job's buffers are involved
@@ -491,9 +493,9 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 bool alive = true;
                 // unit wu of this CTA's share: eight consecutive activations of row b; where they go in the planes
                 auto unit_at = [&](int wu, int& b, uint32_t& dst) -> int {
-                    const int o = wu & 7, sb = wu >> 3;
-                    b = sb / n_slots;
-                    const int slot = sb - b * n_slots;
+                    const int o = wu & 7;
+                    int slot = wu >> 3;
+                    for (b = 0; slot >= n_slots; ++b) slot -= n_slots;  // b < 8: cheaper and smaller than a division
                     int32_t u = slot + xs0;
                     if (u >= kt_len) u -= kt_len;
                     dst = xb + uint32_t(slot) * xslot_bytes + uint32_t(b) * 256u + uint32_t(o >> 2) * 128u + uint32_t(o & 3) * 4u;
@@ -513,7 +515,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                     uint64_t t0 = 0;
                     for (int64_t it = 0; !pub_ok(a, c); ++it) {
                         if (*abort_flag || out_of_time(it, t0)) {
-                            if (!*abort_flag) report(P.status, QGEMV_ERR_TIMEOUT, 84, j);
+                            if (!*abort_flag) seq_report(P.status, 84, j);
                             *abort_flag = 1;
                             alive = false;
                             break;
@@ -578,7 +580,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                                 if (kp[i] && !pub_ok(ka[i], kc[i])) miss |= 1u << i;
                             if (miss == 0) break;
                             if (*abort_flag || out_of_time(it, t0)) {
-                                if (!*abort_flag) report(P.status, QGEMV_ERR_TIMEOUT, 84, j);
+                                if (!*abort_flag) seq_report(P.status, 84, j);
                                 *abort_flag = 1;
                                 alive = false;
                                 break;
@@ -649,7 +651,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 // in a run of jobs would otherwise race ahead of the PLANES group and complete its barrier
                 // twice before that group has looked)
                 if (!*abort_flag && !mbar_wait(sbase + SeqSmem::kBarXReady + 8 * pb, pph, P.spin_limit)) {
-                    if (gt == 0) report(P.status, QGEMV_ERR_TIMEOUT, 81, j);
+                    if (gt == 0) seq_report(P.status, 81, j);
                     *abort_flag = 1;
                 }
                 const volatile int* rg = reinterpret_cast<const volatile int*>(sq_smem + SeqSmem::kRange) + pb * 2;
@@ -662,7 +664,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                         // (asked directly: this CTA's FINISH group may itself be waiting for the part written below)
                         if (*abort_flag || ld_acquire(P.fin + (j - kSeqPartBufs)) >= unsigned(grid)) break;
                         if (out_of_time(it, t0)) {
-                            report(P.status, QGEMV_ERR_TIMEOUT, 79, j);
+                            seq_report(P.status, 79, j);
                             *abort_flag = 1;
                             break;
                         }
@@ -679,7 +681,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                     const bool whole = sg.u0 == 0 && sg.u1 == kt_len;
                     const uint32_t acc = nseg & 1;
                     if (!__all_sync(0xFFFFFFFFu, mbar_wait_probe(sbase + SeqSmem::kBarDFull + 8 * acc, (nseg >> 1) & 1, P.spin_limit))) {
-                        if (lane == 0) report(P.status, QGEMV_ERR_TIMEOUT, 76, int(nseg));
+                        if (lane == 0) seq_report(P.status, 76, int(nseg));
                         *abort_flag = 1;
                         ok = false;
                         continue;
@@ -728,7 +730,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 named_bar_sync(bar_id, 128);
                 if (gt == 0) {
                     if (!*abort_flag && !mbar_wait(sbase + SeqSmem::kBarMDone + 8 * pb, pph, P.spin_limit)) {
-                        report(P.status, QGEMV_ERR_TIMEOUT, 82, j);
+                        seq_report(P.status, 82, j);
                         *abort_flag = 1;
                     }
                     mbar_arrive(sbase + SeqSmem::kBarEDone + 8 * pb);  // first: the PLANES group may be waiting
@@ -781,7 +783,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                             __nanosleep(100);
                         }
                         if (out_of_time(it, t0)) {
-                            report(P.status, QGEMV_ERR_TIMEOUT, 85, j);
+                            seq_report(P.status, 85, j);
                             *abort_flag = 1;
                             break;
                         }
@@ -821,7 +823,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                                         if (uint32_t(t[z] >> 32) != part_tag) miss |= 1u << z;
                                     if (miss == 0) break;
                                     if (*abort_flag || out_of_time(spins++, t0)) {
-                                        if (!*abort_flag) report(P.status, QGEMV_ERR_TIMEOUT, 77, cc + __ffs(int(miss)) - 1);
+                                        if (!*abort_flag) seq_report(P.status, 77, cc + __ffs(int(miss)) - 1);
                                         *abort_flag = 1;
                                         have = false;
                                         break;
@@ -845,7 +847,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                                     a = part[0];
                                     for (int r = 1; r < P.world; ++r) a += part[r];
                                 } else {
-                                    report(P.status, QGEMV_ERR_TIMEOUT, 83, missing);
+                                    seq_report(P.status, 83, missing);
                                     *abort_flag = 1;
                                     have = false;
                                     break;

@@ -79,7 +79,8 @@ struct TpExchange {
             st_pair_sys(slot + elem, __float_as_uint(value), tag);
         }
     }
-    __device__ __forceinline__ bool gather(int64_t elem, float* out, int64_t spin_limit, int& missing) const {
+    // (not inlined: the GEMV-sequence kernel keeps its code small, and calls this only when ranks exchange)
+    __device__ __noinline__ bool gather(int64_t elem, float* out, int64_t spin_limit, int& missing) const {
         const unsigned long long* slots = reinterpret_cast<const unsigned long long*>(buf[rank]) + par_off + elem;
         unsigned long long w[kTpMaxWorld];
 #pragma unroll
