@@ -670,6 +670,7 @@ int qgemv_sequence_create(qgemv_handle* h, const qgemv_job* jobs, int n_jobs, in
             sj.xoff = 0;  // placed below, once the total is known
         }
         const int64_t total = int64_t(sj.tiles) * sj.kt;
+        if ((total + 1) * grid >= (int64_t(1) << 32)) return QGEMV_ERR_UNSUPPORTED_SHAPE;  // the kernel splits in 32-bit arithmetic
         x_slots = std::max(x_slots, std::min<int64_t>(sj.kt, (total + grid - 1) / grid));
     }
     if (n_jobs > 4094) return QGEMV_ERR_UNSUPPORTED_SHAPE;  // the job index is part of a 12-bit tag

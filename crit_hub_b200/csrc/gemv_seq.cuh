@@ -171,12 +171,23 @@ __device__ __forceinline__ SeqJob seq_load_job(const SeqJob* j) {
 // only take part in the job's barriers.  Range [begin, end) of CTA `cta` in the job's linear
 // (tile, item) space; empty for a CTA beyond the job's share.
 __device__ __forceinline__ int seq_job_grid(int32_t total, int grid) { return total < grid ? total : grid; }
+// (32-bit arithmetic: the host refuses job lists with (items + 1) * grid >= 2^32, and 64-bit divisions are
+// long instruction sequences that this kernel, whose roles share an instruction cache, can do without)
 __device__ __forceinline__ void seq_range(int32_t total, int cta, int gj, int32_t& begin, int32_t& end) {
     begin = end = 0;
     if (cta < gj) {
-        begin = int32_t((int64_t(cta) * total) / gj);
-        end = int32_t((int64_t(cta + 1) * total) / gj);
+        begin = int32_t((uint32_t(cta) * uint32_t(total)) / uint32_t(gj));
+        end = int32_t((uint32_t(cta + 1) * uint32_t(total)) / uint32_t(gj));
     }
+}
+// the CTA whose range holds item idx; the parts slot of CTA c for row tile `tile` (first segment 2c, last 2c + 1):
+// the values of cta_of() and gs_slot()
+__device__ __forceinline__ int32_t seq_cta_of(int32_t idx, int32_t total, int gj) {
+    return int32_t((uint32_t(idx + 1) * uint32_t(gj) - 1u) / uint32_t(total));
+}
+__device__ __forceinline__ int32_t seq_slot(int32_t c, int32_t tile, int32_t units, int32_t total, int gj) {
+    const uint32_t a = (uint32_t(c) * uint32_t(total)) / uint32_t(gj);
+    return 2 * c + (int32_t(a / uint32_t(units)) == tile ? 0 : 1);
 }
 // segment walker of CTA `cta` for a job (no segments for a CTA beyond the job's share)
 __device__ __forceinline__ void seq_walker(GsWalker& wk, int32_t total, int32_t kt, int cta, int gj) {
@@ -184,6 +195,14 @@ __device__ __forceinline__ void seq_walker(GsWalker& wk, int32_t total, int32_t 
     seq_range(total, cta, gj, wk.pos, wk.end);
 }
 
+// The waits' slow paths out of line as well: a wait that finds its barrier complete costs a probe.
+__device__ __noinline__ bool seq_mbar_spin(uint32_t bar, uint32_t parity, int64_t spin_limit) { return mbar_wait(bar, parity, spin_limit); }
+__device__ __forceinline__ bool seq_mbar_wait(uint32_t bar, uint32_t parity, int64_t spin_limit) {
+    return mbar_try_wait(bar, parity) || seq_mbar_spin(bar, parity, spin_limit);
+}
+__device__ __forceinline__ bool seq_mbar_probe(uint32_t bar, uint32_t parity, int64_t spin_limit) {
+    return mbar_test_wait(bar, parity) || seq_mbar_spin(bar, parity, spin_limit);
+}
 __device__ __noinline__ void seq_report(int32_t* status, int where, int extra) { report(status, QGEMV_ERR_TIMEOUT, where, extra); }
 
 // Eight activations of one row -> their eight digit planes in shared memory.  Not inlined: the kernel's five
@@ -268,7 +287,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 while (ok && wk.next(sg)) {
                     const uint8_t* src = job.payload + (uint64_t(sg.tile) * job.kt + uint64_t(sg.u0)) * kTcItemBytes;
                     for (int32_t left = sg.u1 - sg.u0; left > 0; left -= S) {
-                        if (use > 0 && !mbar_wait_probe(sbase + SeqSmem::kBarEmpty + 8 * s, (use - 1) & 1, P.spin_limit)) {
+                        if (use > 0 && !seq_mbar_probe(sbase + SeqSmem::kBarEmpty + 8 * s, (use - 1) & 1, P.spin_limit)) {
                             seq_report(P.status, 71, j);
                             *abort_flag = 1;
                             ok = false;
@@ -312,7 +331,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 if (j + 1 < P.n_jobs) next = seq_load_job(P.jobs + j + 1);
                 const int32_t kt_len = job.kt;
                 // the digit planes of this job (every CTA signals, also one without items)
-                if (!mbar_wait(sbase + SeqSmem::kBarXReady + 8 * pb, pph, P.spin_limit)) {
+                if (!seq_mbar_wait(sbase + SeqSmem::kBarXReady + 8 * pb, pph, P.spin_limit)) {
                     seq_report(P.status, 72, j);
                     *abort_flag = 1;
                     ok = false;
@@ -333,7 +352,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 for (; ok && have; have = wk.next(sg)) {
                     // the accumulator is free once the epilogue of the segment before last has read it
                     if (nseg >= 2 &&
-                        !mbar_wait_probe(sbase + SeqSmem::kBarDFree + 8 * (nseg & 1), ((nseg >> 1) - 1) & 1, P.spin_limit)) {
+                        !seq_mbar_probe(sbase + SeqSmem::kBarDFree + 8 * (nseg & 1), ((nseg >> 1) - 1) & 1, P.spin_limit)) {
                         seq_report(P.status, 73, int(nseg));
                         *abort_flag = 1;
                         ok = false;
@@ -349,7 +368,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                         // (the stage was written through the async proxy and is read through it: the
                         // barrier's acquire is all the ordering the MMAs need -- no tcgen05 fence here,
                         // which costs this thread a few hundred cycles per stage)
-                        if (!mbar_wait_probe(bar_full, full_par, P.spin_limit)) {
+                        if (!seq_mbar_probe(bar_full, full_par, P.spin_limit)) {
                             seq_report(P.status, 74, mi);
                             *abort_flag = 1;
                             ok = false;
@@ -465,7 +484,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 if (j + 1 < P.n_jobs) next = seq_load_job(P.jobs + j + 1);
                 // the plane buffer and its row maxima were last used by job j - nbuf: its epilogues must be through
                 if (j >= nb && gt == 0 &&
-                    !mbar_wait(sbase + SeqSmem::kBarEDone + 8 * pb, (pph ^ 1u), P.spin_limit)) {
+                    !seq_mbar_wait(sbase + SeqSmem::kBarEDone + 8 * pb, (pph ^ 1u), P.spin_limit)) {
                     seq_report(P.status, 78, j);
                     *abort_flag = 1;
                 }
@@ -650,7 +669,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 // the planes of this job are ready, and with them this CTA's item range (a CTA without items
                 // in a run of jobs would otherwise race ahead of the PLANES group and complete its barrier
                 // twice before that group has looked)
-                if (!*abort_flag && !mbar_wait(sbase + SeqSmem::kBarXReady + 8 * pb, pph, P.spin_limit)) {
+                if (!*abort_flag && !seq_mbar_wait(sbase + SeqSmem::kBarXReady + 8 * pb, pph, P.spin_limit)) {
                     if (gt == 0) seq_report(P.status, 81, j);
                     *abort_flag = 1;
                 }
@@ -680,7 +699,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                     if (!ok) continue;  // this warp gave up: it still reaches the group's barriers below
                     const bool whole = sg.u0 == 0 && sg.u1 == kt_len;
                     const uint32_t acc = nseg & 1;
-                    if (!__all_sync(0xFFFFFFFFu, mbar_wait_probe(sbase + SeqSmem::kBarDFull + 8 * acc, (nseg >> 1) & 1, P.spin_limit))) {
+                    if (!__all_sync(0xFFFFFFFFu, seq_mbar_probe(sbase + SeqSmem::kBarDFull + 8 * acc, (nseg >> 1) & 1, P.spin_limit))) {
                         if (lane == 0) seq_report(P.status, 76, int(nseg));
                         *abort_flag = 1;
                         ok = false;
@@ -693,8 +712,8 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                     // pair); the first one's range may have started in an earlier tile
                     unsigned long long* slot = nullptr;
                     if (!whole) {
-                        const int32_t c_lo = int32_t(cta_of(int64_t(sg.tile) * kt_len, total, gj));
-                        const int32_t my_slot = cta == c_lo ? gs_slot(c_lo, sg.tile, kt_len, total, gj) : 2 * cta;
+                        const int32_t c_lo = seq_cta_of(sg.tile * kt_len, total, gj);
+                        const int32_t my_slot = cta == c_lo ? seq_slot(c_lo, sg.tile, kt_len, total, gj) : 2 * cta;
                         slot = P.ws + (size_t(j & (kSeqPartBufs - 1)) * size_t(2 * grid) + size_t(my_slot)) * 1024 + row;
                     }
                     // (one row of the batch after the other, not unrolled: the code of this group has to stay small)
@@ -729,7 +748,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 // this CTA's rows and parts of job j are stored; its plane buffer may be reused
                 named_bar_sync(bar_id, 128);
                 if (gt == 0) {
-                    if (!*abort_flag && !mbar_wait(sbase + SeqSmem::kBarMDone + 8 * pb, pph, P.spin_limit)) {
+                    if (!*abort_flag && !seq_mbar_wait(sbase + SeqSmem::kBarMDone + 8 * pb, pph, P.spin_limit)) {
                         seq_report(P.status, 82, j);
                         *abort_flag = 1;
                     }
@@ -762,10 +781,10 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 int32_t tile = 0, c_lo = 0, c_hi = 0, lo_slot = 0;
                 if (re > rb && re % kt_len != 0) {
                     tile = (re - 1) / kt_len;
-                    c_lo = int32_t(cta_of(int64_t(tile) * kt_len, total, gj));
-                    c_hi = int32_t(cta_of(int64_t(tile + 1) * kt_len - 1, total, gj));
+                    c_lo = seq_cta_of(tile * kt_len, total, gj);
+                    c_hi = seq_cta_of((tile + 1) * kt_len - 1, total, gj);
                     pending = c_lo == cta;
-                    lo_slot = gs_slot(c_lo, tile, kt_len, total, gj);
+                    lo_slot = seq_slot(c_lo, tile, kt_len, total, gj);
                 }
                 // how far have ALL CTAs come with this step?  One probe per job, in flight with nothing else to do
                 if (gt == 0 && known + 1 < j && ld_acquire(P.fin + known + 1) >= unsigned(grid)) *fin_all = ++known;
@@ -888,7 +907,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
         if (*abort_flag) {
             if (lane == 0) {
                 tc_commit(sbase + SeqSmem::kBarDrain);
-                (void)mbar_wait_probe(sbase + SeqSmem::kBarDrain, 0, int64_t(1) << 16);
+                (void)seq_mbar_probe(sbase + SeqSmem::kBarDrain, 0, int64_t(1) << 16);
             }
             __syncwarp();
         }
@@ -898,7 +917,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
         // never leave with copies in flight: wait (bounded) for every copy that nothing consumed
         const int issued = *n_issued;
         for (int i = *n_consumed; i < issued; ++i)
-            (void)mbar_wait(sbase + SeqSmem::kBarFull + 8 * (i % R), uint32_t(i / R) & 1u, int64_t(1) << 20);
+            (void)seq_mbar_wait(sbase + SeqSmem::kBarFull + 8 * (i % R), uint32_t(i / R) & 1u, int64_t(1) << 20);
     }
 }
 
