@@ -98,69 +98,3 @@ def make_result(gpu: str, model: str, stats: dict, settings: str, method: str = 
         result["throughput"] = throughput
     result["evidence"] = [{"file": SELF_REPORTED, "sha256": hashlib.sha256(blob).hexdigest()}]
     return result, blob
-
-
-# ---- the registry's rules, restated as checks ---------------------------------------------------
-def check_stats(stats, more=None) -> list:
-    """tools/check_engines.py:391-420: six keys in order, decode required, the rest nullable."""
-    if not isinstance(stats, dict) or list(stats) != list(STATS):
-        return ["stats holds " + ", ".join(STATS) + ", in that order"]
-    problems = []
-    if not is_figure(stats["decode_tok_s"]):
-        problems.append("decode_tok_s is a positive number or [low, high]")
-    for key in ("prefill_tok_s", "ttft_ms"):
-        if stats[key] is not None and not is_figure(stats[key]):
-            problems.append(f"{key} is a positive number, [low, high] or null")
-    t = stats["context_tokens"]
-    if t is not None and not (isinstance(t, int) and not isinstance(t, bool) and t > 0):
-        problems.append("context_tokens is a positive whole number or null")
-    ppl = stats["ppl"]
-    if ppl is not None and not (isinstance(ppl, dict) and len(ppl) == 1 and set(ppl) <= {"vs_reference", "absolute"}
-                                and _positive(next(iter(ppl.values())))):
-        problems.append("ppl is {vs_reference: r}, {absolute: p} or null")
-    if stats["kld_mean"] is not None and not _positive(stats["kld_mean"]):
-        problems.append("kld_mean is a positive number or null")
-    if more is not None and (not isinstance(more, dict) or set(more) - set(MORE)):
-        problems.append("more holds any of " + ", ".join(MORE))
-    return problems
-
-
-def check_throughput(throughput) -> list:
-    """tools/check_engines.py:423-436: {concurrency, tok_s} levels, concurrency ascending, each once."""
-    if not (isinstance(throughput, list) and throughput
-            and all(isinstance(t, dict) and set(t) == set(THROUGHPUT) for t in throughput)):
-        return ["throughput lists {concurrency, tok_s}"]
-    problems = []
-    levels = [t["concurrency"] for t in throughput]
-    if not all(type(n) is int and n >= 1 for n in levels) or levels != sorted(set(levels)):
-        problems.append("concurrency is a whole number >= 1, each once, ascending")
-    problems += [f"tok_s at concurrency {t['concurrency']} is not a figure" for t in throughput if not is_figure(t["tok_s"])]
-    return problems
-
-
-def check_result(result: dict, evidence_blob: bytes) -> list:
-    """The self-reported rules: open track, every stated figure recorded verbatim in the evidence
-    (tools/check_engines.py:639-674, 721-724), and the listed hash matches the file."""
-    problems = check_stats(result.get("stats"), result.get("more", {}))
-    if "throughput" in result:
-        problems += check_throughput(result["throughput"])
-    if result.get("track") != "open":
-        problems.append("a self-reported result is on the open track")
-    ev = result.get("evidence", [])
-    if not ev or ev[0].get("sha256") != hashlib.sha256(evidence_blob).hexdigest():
-        problems.append("evidence hash does not match the file")
-    data = json.loads(evidence_blob)
-    entries = data.get("results") if isinstance(data, dict) and set(data) == {"results"} else None
-    entry = next((e for e in entries or [] if (e.get("gpu"), e.get("model")) == (result["gpu"], result["model"])), None)
-    if entry is None:
-        return problems + ["the evidence has no entry for this GPU and model"]
-    recorded = [m.get("figures", {}) for m in entry.get("measurements", [])]
-    if problems:
-        return problems
-    for key, value in {**result["stats"], **result.get("more", {})}.items():
-        if value is not None and not any(f.get(key) == value for f in recorded):
-            problems.append(f"{key} {value} is not a figure the evidence records")
-    for level in result.get("throughput") or []:
-        if not any(isinstance(f.get("throughput"), list) and level in f["throughput"] for f in recorded):
-            problems.append(f"throughput at concurrency {level['concurrency']} is not recorded in the evidence")
-    return problems
