@@ -191,21 +191,29 @@ int qgemv_gemv_prefetch(qgemv_handle* h, const qgemv_weight* w, const void* x_bf
 /* ---- a sequence of GEMVs as one launch --------------------------------------------------------
  * The projections of a decode step, in order, as ONE persistent kernel ("one CUDA graph per round",
  * tools/fixtures/engines/crit-labs/mtp4-nvfp4-mma/card.yaml:75, taken one step further: one launch).
- * Job i computes y_i = W_i x_i exactly as qgemv_gemv would.  Ordering follows the data: when the
- * sequence is created the address ranges of every job's x and y are compared with those of the
- * jobs before it, and a job waits (for the complete output, split row tiles added up) for the
- * latest earlier job whose output it reads or overwrites, or whose input it overwrites.  A job
- * whose ranges touch no earlier job's may overlap the tail of the jobs before it.  A caller whose
- * dependency is not visible in the addresses sets QGEMV_JOB_AFTER_PREVIOUS on the job: it then
- * waits for the job before it in any case.  While the CTAs finish one job and convert the next
+ * Job i computes y_i = W_i x_i exactly as qgemv_gemv would (same split along K, same bits).
+ * Ordering follows the data.  When the sequence is created the address ranges of every job's x and y
+ * are compared with those of the jobs before it:
+ *   - x_i is the bf16 output of ONE earlier job, or a column range of it (x_i points into that y,
+ *     x_stride = that job's N when B > 1), and nothing else touches those buffers in between: the
+ *     producer publishes its rows as it finishes them and job i converts them as they appear -- no
+ *     grid-wide wait between the two jobs;
+ *   - any other overlap (x_i over several outputs or an fp32 output, y_i over an earlier x or y):
+ *     job i waits until the latest such job is complete on every CTA;
+ *   - no overlap: job i may run alongside the tail of the jobs before it.
+ * A caller whose dependency is not visible in the addresses sets QGEMV_JOB_AFTER_PREVIOUS on the job:
+ * it then waits for the job before it in any case.  While the CTAs finish one job and convert the next
  * one's activations, the weights of the following jobs keep streaming into shared memory, so HBM
  * does not idle at the boundaries the way it does between separate launches.
- * Weights: QGEMV_FMT_NVFP4_TC only.  All jobs share the batch size B (1..8).  The job list is
- * copied to the device by qgemv_sequence_create (which allocates); qgemv_sequence_run launches,
- * allocates nothing and may be captured into a CUDA graph.  The kernel's CTAs wait on one another:
- * the launch is cooperative and takes every SM (grid_override above the SM count is refused).
- * QGEMV_ERR_UNSUPPORTED_SHAPE when the activations of one job (B * K digit planes) leave no room
- * for a weight ring in shared memory: call qgemv_gemv per job then. */
+ * Weights: QGEMV_FMT_NVFP4_TC only.  All jobs share the batch size B (1..8).  At most 4094 jobs, each
+ * of fewer than 2^32 / SMs (128-row tile, 64-column item) pairs.  The job list is copied to the device by
+ * qgemv_sequence_create (which allocates); qgemv_sequence_run launches, allocates nothing and may be
+ * captured into a CUDA graph.  The kernel's CTAs wait on one another: the launch is cooperative and takes
+ * every SM (grid_override above the SM count is refused).  QGEMV_ERR_UNSUPPORTED_SHAPE when the
+ * activations of one job (B * K digit planes) leave no room for a weight ring in shared memory: call
+ * qgemv_gemv per job then.  After a run that reported QGEMV_ERR_TIMEOUT, read the status
+ * (qgemv_last_device_status) before the handle's next sequence run: that call puts the kernel's counters
+ * and tags back in order. */
 #define QGEMV_JOB_AFTER_PREVIOUS 1 /* start only when the job before this one is complete */
 #define QGEMV_JOB_ALLREDUCE 2      /* row-parallel projection: y = sum over the ranks of W_r x_r (see the exchange below) */
 typedef struct qgemv_job {
@@ -353,8 +361,12 @@ int qgemv_dequant_f32(qgemv_handle* h, const qgemv_weight* w, int which, float* 
  * %globaltimer (ns) at [0] set-up done and [7] CTA done, and the SM's cycle counter (cheap to read;
  * comparable inside one CTA only) at: [9] set-up done, [1] dependency wait over, [2] activation
  * digit planes written, [3] MMA issuer released, [4] its first weight stage landed, [5] its last MMA
- * issued, [6] last accumulator complete, [8] last epilogue warp done.  The caller zeroes and reads
- * the buffer. */
+ * issued, [6] last accumulator complete, [8] last epilogue warp done.  A sequence launch
+ * (qgemv_sequence_run) instead stores 8 x 8 bytes per (CTA, job) at [(cta * n_jobs + job) * 8 + k],
+ * all %globaltimer: [0] conversion of the job's activations begins (its dependencies are met), [1] digit
+ * planes ready, [3] MMA issuer sees them, [7] its first stage of the job issued, [4] its last, [5] last
+ * accumulator seen by the epilogue, [2] rows / parts stored, [6] split tile added up and stored.  The
+ * caller zeroes and reads the buffer; the stamps cost time, so a traced run is slower. */
 int qgemv_set_trace(qgemv_handle* h, void* dev_buf);
 /* Synchronises `stream`, reads and clears the device status word. */
 int qgemv_last_device_status(qgemv_handle* h, void* stream, qgemv_dev_status* out);
