@@ -75,8 +75,8 @@ def test_moe_128_experts_top8(qg, handle, T):
         rows = T * topk if per_slot else T
         x = O.make_x(rows, K, seed=T + N)
         out = torch.full((T * topk, N), float("nan"), dtype=torch.float32, device="cuda")
-        handle.moe_gemv(w, torch.from_numpy(ids).cuda().data_ptr(), U.dev_u16(x).data_ptr(), T, topk, per_slot,
-                        out.data_ptr(), qg.OUT_F32)
+        idd, xd = torch.from_numpy(ids).cuda(), U.dev_u16(x)      # kept alive until the kernel has run
+        handle.moe_gemv(w, idd.data_ptr(), xd.data_ptr(), T, topk, per_slot, out.data_ptr(), qg.OUT_F32)
         torch.cuda.synchronize()
         U.status_ok(handle)
         got = out.cpu().numpy()
@@ -120,7 +120,8 @@ def test_skinny_gemm_70b_shapes(qg, handle, N, K, M):
     w = handle.load(qg.pack(qg.FMT_NVFP4, codes, scales, ts))
     x = O.make_x(M, K, seed=M)
     y = torch.full((M, N), float("nan"), dtype=torch.float32, device="cuda")
-    handle.gemm_skinny(w, U.dev_u16(x).data_ptr(), M, y.data_ptr(), qg.OUT_F32)
+    xd = U.dev_u16(x)
+    handle.gemm_skinny(w, xd.data_ptr(), M, y.data_ptr(), qg.OUT_F32)
     torch.cuda.synchronize()
     U.status_ok(handle)
     got = y.cpu().numpy()
