@@ -856,8 +856,8 @@ def main():
                      "`chained_gbs`: the same weights with every GEMV reading the output of the one before it (its first K columns) -- a "
                      "decode step's data flow with the element-wise work left out, where each job waits for the last row of the one before; "
                      "`forced_order_gbs`: independent inputs, each job made to wait for the one before it")
-            traffic, tsrc = int(per_launch_bytes * 1.003), ("ncu capture of a 2-layer launch of the same kernel: DRAM read+write = 1.003 x "
-                                                             "algorithmic weight bytes; scaled by bytes")
+            traffic, tsrc = int(per_launch_bytes * 1.032), ("ncu capture of a 2-layer launch of the same kernel (profiles/gemv_seq_llama8b_2layers.md): "
+                                                             "DRAM read 1.001 x, read+write 1.032 x the algorithmic weight bytes; scaled by bytes")
         elif args.layout == "tc":
             kernel, order = "gemv_tc_kernel<4>", "stream order"
             traffic, tsrc = None, None
