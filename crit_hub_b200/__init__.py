@@ -23,6 +23,8 @@ JOB_ALLREDUCE = 2        # qgemv_job.flags: row-parallel projection, summed over
 OUT_BF16 = 0
 OUT_F32 = 1
 ACT_A16_EXACT = 0
+ACT_A4_BLOCKSCALED = 1
+ACT_A8 = 2
 MAX_BATCH = 8
 
 ERR_INVALID_ARG = -1
@@ -120,6 +122,7 @@ def _load() -> C.CDLL:
     L.qgemv_sequence_destroy.argtypes = [vp, vp]
     L.qgemv_gemv_prefetch.argtypes = [vp, vp, vp, i32, vp, i32, vp, vp]
     L.qgemv_gemm_skinny.argtypes = [vp, vp, vp, i32, vp, i32, i32, vp]
+    L.qgemv_quantize_a4.argtypes = [vp, vp, i32, i64, vp, vp, vp, vp]
     L.qgemv_gemm_skinny_plan.argtypes = [i32, i64, i64, i32, i32, C.POINTER(SkinnyPlan)]
     L.qgemv_tp_create.argtypes = [vp, i32, i32, i64, vp]
     L.qgemv_tp_connect.argtypes = [vp, vp]
@@ -338,6 +341,12 @@ class QGemv:
         """Y[M][N] = X[M][K] dequant(W)^T on the tcgen05 tensor cores, M = 16..256 (multiple of 16)."""
         _check(_load().qgemv_gemm_skinny(self._ptr, w._ptr, x_ptr, M, y_ptr, y_dtype, act_mode, stream),
                "gemm_skinny")
+
+    def quantize_a4(self, x_ptr: int, M: int, K: int, codes_ptr: int, scales_ptr: int, row_scales_ptr: int,
+                    stream: int = 0) -> None:
+        """The A4 mode's activation quantiser alone: canonical codes [M][K/2], scales [M][K/16], row scales f32 [M]."""
+        _check(_load().qgemv_quantize_a4(self._ptr, x_ptr, M, K, codes_ptr, scales_ptr, row_scales_ptr, stream),
+               "quantize_a4")
 
     def moe_gemv(self, experts: Weight, expert_ids_ptr: int, x_ptr: int, T: int, topk: int,
                  per_slot_input: bool, out_ptr: int, out_dtype: int = OUT_F32, stream: int = 0) -> None:

@@ -17,7 +17,7 @@ INCLUDE = os.path.join(os.path.dirname(PKG_DIR), "include")
 LIB_PATH = os.path.join(PKG_DIR, "libqgemv.so")
 
 SOURCES = ["api.cu", "pack.cpp"]
-HEADERS = ["ptx.cuh", "gemv_kernel.cuh", "gemv_stream.cuh", "moe_stream.cuh", "gemm_skinny.cuh", "gemv_tc.cuh", "gemv_seq.cuh", "tp_allreduce.cuh", "aux_kernels.cuh", "qgemv_layout.h"]
+HEADERS = ["ptx.cuh", "gemv_kernel.cuh", "gemv_stream.cuh", "moe_stream.cuh", "gemm_skinny.cuh", "gemv_tc.cuh", "gemv_seq.cuh", "gemm_tc_a4.cuh", "tp_allreduce.cuh", "aux_kernels.cuh", "qgemv_layout.h"]
 
 
 def _newest_source_mtime() -> float:

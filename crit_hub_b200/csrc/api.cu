@@ -18,6 +18,7 @@
 #include "gemv_seq.cuh"
 #include "moe_stream.cuh"
 #include "tp_allreduce.cuh"
+#include "gemm_tc_a4.cuh"
 #include "qgemv_layout.h"
 
 extern "C" int qgemv_blob_verify(const void* blob, size_t bytes);
@@ -46,6 +47,8 @@ struct qgemv_handle {
     unsigned int* seq_barrier;     // CTAs that have left a GEMV-sequence launch, zero between launches
     unsigned long long* seq_parts; // its parts buffers: [kSeqPartBufs][2 * grid][8][128] pairs {fp32, tag}
     size_t tc_ws_bytes;
+    uint8_t* a4_ws;        // block-scaled prefill: quantised activation items, then the row scales
+    size_t a4_ws_bytes;
     std::vector<qgemv_sequence*>* sequences;  // live job lists: their counters are cleared after a reported error
 };
 
@@ -375,6 +378,7 @@ int qgemv_init(const qgemv_config* cfg, qgemv_handle** out) {
     h->gs_ws = nullptr, h->gs_ws_bytes = 0;
     h->chunk_ws = nullptr;
     h->tc_ws = nullptr, h->tc_trace = nullptr, h->seq_barrier = nullptr, h->seq_parts = nullptr;
+    h->a4_ws = nullptr, h->a4_ws_bytes = 0;
     h->sequences = new (std::nothrow) std::vector<qgemv_sequence*>();
     const size_t tc_ws_bytes = size_t(2) * size_t(std::max(h->sm_count, cfg->grid_override)) * 1024 * 8;
     h->tc_ws_bytes = tc_ws_bytes;
@@ -434,6 +438,7 @@ int qgemv_destroy(qgemv_handle* h) {
     cudaFree(h->tc_ws);
     cudaFree(h->seq_barrier);
     cudaFree(h->seq_parts);
+    cudaFree(h->a4_ws);
     delete h->sequences;
     cudaFree(h->status_dev);
     delete h;
@@ -886,9 +891,110 @@ int qgemv_gemm_skinny_plan(int fmt, int64_t N, int64_t K, int M, int sm_count, q
     return QGEMV_OK;
 }
 
+namespace {
+// scratch of the block-scaled prefill: activation items [kt][a4_item_bytes(M)] then fp32 row scales [256]
+int a4_scratch(qgemv_handle* h, int M, int64_t kt, uint8_t** items, float** g) {
+    const size_t items_bytes = (size_t(kt) * size_t(qg::a4_item_bytes(M)) + 255) / 256 * 256;
+    const size_t need = items_bytes + 256 * sizeof(float);
+    if (need > h->a4_ws_bytes) {
+        // growing the scratch synchronises; it happens on the first call of a new largest shape
+        // only and must not fall inside a stream capture
+        QG_CUDA(cudaDeviceSynchronize());
+        cudaFree(h->a4_ws);
+        h->a4_ws = nullptr, h->a4_ws_bytes = 0;
+        QG_CUDA(cudaMalloc(&h->a4_ws, need));
+        h->a4_ws_bytes = need;
+    }
+    *items = h->a4_ws;
+    *g = reinterpret_cast<float*>(h->a4_ws + h->a4_ws_bytes - 256 * sizeof(float));
+    return QGEMV_OK;
+}
+
+// Y = Xq Wq^T with the activations quantised to NVFP4 by the stated quantiser (gemm_tc_a4.cuh).
+int gemm_a4(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, int M, void* y, int y_dtype, cudaStream_t st) {
+    if (w->fmt != QGEMV_FMT_NVFP4_TC || w->n_stack != 1) return QGEMV_ERR_UNSUPPORTED_SHAPE;  // weights consumed as stored
+    if (w->K % 16 != 0) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+    QG_CUDA(cudaSetDevice(h->cfg.device));
+    const int64_t kt = w->units, tiles = w->n_panels / 8;
+    uint8_t* items = nullptr;
+    float* g = nullptr;
+    const int rc = a4_scratch(h, M, kt, &items, &g);
+    if (rc != QGEMV_OK) return rc;
+    const int grid = std::min(gemv_grid(h), h->sm_count);
+    // fewer row tiles than CTAs: cut K into chunks (fp32 partial results, added in chunk order)
+    int n_chunk = 1;
+    if (tiles < grid) {
+        n_chunk = int(std::min<int64_t>({int64_t(grid) / tiles, 8, kt, int64_t(kChunkWsBytes / (size_t(M) * size_t(w->N) * 4))}));
+        if (n_chunk < 1) n_chunk = 1;
+    }
+    const int chunk_items = int((kt + n_chunk - 1) / n_chunk);
+    n_chunk = int((kt + chunk_items - 1) / chunk_items);
+    QG_CUDA(cudaMemsetAsync(items, 0, size_t(kt) * size_t(qg::a4_item_bytes(M)), st));  // tokens and K blocks beyond the data are zero
+    qg::A4QuantParams Q;
+    Q.x = static_cast<const uint16_t*>(x_bf16);
+    Q.M = M, Q.K = int32_t(w->K);
+    Q.items = items, Q.g = g, Q.codes = nullptr, Q.scales = nullptr;
+    if (launch(h, qg::a4_quant_kernel, dim3(unsigned(M)), dim3(256), 0, st, Q) != cudaSuccess) return QGEMV_ERR_CUDA;
+    qg::A4Params P;
+    std::memset(&P, 0, sizeof P);
+    P.payload = w->dev_blob + QG_HEADER_BYTES + w->aux_bytes;
+    P.xq = items;
+    P.g = g;
+    P.y = n_chunk == 1 ? y : static_cast<void*>(h->chunk_ws);
+    P.status = h->status_dev;
+    P.spin_limit = default_spin(h);
+    P.tensor_scale = w->host_tensor_scale[0];
+    P.N = int32_t(w->N), P.M = M;
+    P.tiles = int32_t(tiles), P.kt = int32_t(kt);
+    P.n_chunk = n_chunk, P.chunk_items = chunk_items;
+    P.xq_item_bytes = qg::a4_item_bytes(M);
+    const int cap = 227 * 1024;
+    P.ring = std::min({qg::kA4MaxRing, (cap - qg::A4Smem::kRing) / qg::A4Smem::stage_bytes(M), qg::A4Smem::max_ring(M)});
+    P.y_dtype = y_dtype;
+    P.debug = h->cfg.debug;
+    const size_t smem = size_t(qg::A4Smem::total(M, P.ring));
+    static bool attr_set[64] = {};
+    if (!attr_set[h->cfg.device & 63]) {
+        QG_CUDA(cudaFuncSetAttribute(qg::gemm_a4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, cap));
+        attr_set[h->cfg.device & 63] = true;
+    }
+    const int ctas = int(std::min<int64_t>(grid, tiles * n_chunk));
+    if (launch(h, qg::gemm_a4_kernel, dim3(unsigned(ctas)), dim3(qg::kA4Threads), smem, st, P) != cudaSuccess) return QGEMV_ERR_CUDA;
+    if (n_chunk > 1) {
+        const int64_t slice = int64_t(M) * w->N;
+        if (launch(h, qg::chunk_sum_kernel, dim3(unsigned((slice + 255) / 256)), dim3(256), 0, st,
+                   static_cast<const float*>(h->chunk_ws), n_chunk, slice, y, y_dtype) != cudaSuccess)
+            return QGEMV_ERR_CUDA;
+    }
+    return QGEMV_OK;
+}
+}  // namespace
+
+int qgemv_quantize_a4(qgemv_handle* h, const void* x_bf16, int M, int64_t K, void* codes_dev, void* scales_dev,
+                      float* row_scales_dev, void* stream) {
+    if (!h || !x_bf16 || !codes_dev || !scales_dev || !row_scales_dev) return QGEMV_ERR_INVALID_ARG;
+    if (M < 1 || K < 16 || K % 16 != 0 || K > INT32_MAX) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(x_bf16) & 15u) != 0 || (reinterpret_cast<uintptr_t>(codes_dev) & 7u) != 0) return QGEMV_ERR_INVALID_ARG;
+    QG_CUDA(cudaSetDevice(h->cfg.device));
+    qg::A4QuantParams Q;
+    Q.x = static_cast<const uint16_t*>(x_bf16);
+    Q.M = M, Q.K = int32_t(K);
+    Q.items = nullptr, Q.g = row_scales_dev;
+    Q.codes = static_cast<uint8_t*>(codes_dev), Q.scales = static_cast<uint8_t*>(scales_dev);
+    return launch(h, qg::a4_quant_kernel, dim3(unsigned(M)), dim3(256), 0, static_cast<cudaStream_t>(stream), Q) == cudaSuccess
+               ? QGEMV_OK
+               : QGEMV_ERR_CUDA;
+}
+
 int qgemv_gemm_skinny(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, int M, void* y,
                       int y_dtype, int act_mode, void* stream) {
     if (!h || !w || !x_bf16 || !y) return QGEMV_ERR_INVALID_ARG;
+    if (act_mode == QGEMV_ACT_A4_BLOCKSCALED) {
+        if (y_dtype != QGEMV_OUT_BF16 && y_dtype != QGEMV_OUT_F32) return QGEMV_ERR_INVALID_ARG;
+        if ((reinterpret_cast<uintptr_t>(x_bf16) & 15u) != 0) return QGEMV_ERR_INVALID_ARG;
+        if (M < 16 || M > 256 || M % 16 != 0) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+        return gemm_a4(h, w, x_bf16, M, y, y_dtype, static_cast<cudaStream_t>(stream));
+    }
     if (act_mode != QGEMV_ACT_A16_EXACT) return QGEMV_ERR_UNSUPPORTED_SHAPE;
     if (y_dtype != QGEMV_OUT_BF16 && y_dtype != QGEMV_OUT_F32) return QGEMV_ERR_INVALID_ARG;
     if ((reinterpret_cast<uintptr_t>(x_bf16) & 15u) != 0) return QGEMV_ERR_INVALID_ARG;

@@ -304,9 +304,20 @@ int qgemv_noalloc_last_status(void* stream, qgemv_dev_status* out);
  * x: device bf16 [M][K], 16-byte aligned; y: device [M][N] bf16 or fp32.
  * act_mode QGEMV_ACT_A16_EXACT: weights are dequantised exactly to f16 tiles, activations stay
  * 16-bit (bf16 -> f16 with an exact per-row power-of-two scale), kind::f16 MMA: same 2e-3 bound
- * as the GEMV.  The block-scaled FP4 / FP8-activation modes quantise the activations and are a
- * different operator; they return QGEMV_ERR_UNSUPPORTED_SHAPE.
- * Shapes: single (unstacked) weight, N a multiple of 128, K a multiple of 64.
+ * as the GEMV.  Weights in the lane order (QGEMV_FMT_NVFP4 / QGEMV_FMT_FP8).
+ * act_mode QGEMV_ACT_A4_BLOCKSCALED: a different operator -- the activations are quantised to NVFP4
+ * (E2M1 codes, one E4M3 scale per 16 K elements, one fp32 scale per token) and both operands go
+ * through tcgen05.mma kind::mxf4nvf4 as stored ("NVFP4 ... prefill GEMMs",
+ * tools/fixtures/engines/crit-labs/mtp4-nvfp4-mma/card.yaml:77).  Weights: QGEMV_FMT_NVFP4_TC, any N,
+ * K a multiple of 16.  The quantiser is fixed bit for bit: per token row, fp32 round-to-nearest-even,
+ *   g = max|x| / 2688 (1 if the row is zero);  per block  s = E4M3(max|x_block| / (6 g)), saturating;
+ *   t = decode(s) g;  code = t == 0 ? 0 : E2M1(x / t), saturating;   x_q = decode(code) decode(s) g
+ * and y[m][n] = tensor_scale * g[m] * sum_k w(n, k) x_q-without-g(m, k), fp32 in the tensor core.
+ * Against an fp64 GEMM on the SAME quantised activations the result is within 2e-3 (far inside);
+ * against unquantised activations it carries FP4's quantisation error (about 9 % relative L2 on N(0,1)
+ * rows).  qgemv_quantize_a4 exposes the quantiser for parity checks.
+ * QGEMV_ACT_A8 (FP8 activations) is not built: QGEMV_ERR_UNSUPPORTED_SHAPE.
+ * Shapes of the A16 mode: single (unstacked) weight, N a multiple of 128, K a multiple of 64.
  * The call keeps an internal f16 copy of the activations (M*K*2 bytes); the first call with a
  * new largest M*K grows it with cudaMalloc after a device synchronise -- make that call outside
  * stream capture.  Three launches per call (activation row maxima, activation conversion, GEMM). */
@@ -315,6 +326,11 @@ int qgemv_noalloc_last_status(void* stream, qgemv_dev_status* out);
 #define QGEMV_ACT_A8 2
 int qgemv_gemm_skinny(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, int M, void* y,
                       int y_dtype, int act_mode, void* stream);
+/* The A4 mode's activation quantiser alone (parity hook; no counterpart in the registry): x bf16 [M][K]
+ * -> canonical codes u8 [M][K/2] (low nibble = even k, 8-byte aligned), block scales u8 [M][K/16] and
+ * row scales fp32 [M], all in device memory. */
+int qgemv_quantize_a4(qgemv_handle* h, const void* x_bf16, int M, int64_t K, void* codes_dev, void* scales_dev,
+                      float* row_scales_dev, void* stream);
 /* How qgemv_gemm_skinny would run a shape: pipeline grain, ring depths, tensor-memory and shared-
  * memory use, CTA count and scratch bytes.  Pure host arithmetic (no device needed); returns
  * QGEMV_ERR_UNSUPPORTED_SHAPE for shapes the GEMM refuses.  No counterpart in the reference. */

@@ -179,6 +179,28 @@ def moe_gemv_nvfp4_f64(codes, scales, ts, expert_ids, x_bf16, per_slot_input: bo
     return out
 
 
+def quantize_a4(x_bf16: np.ndarray):
+    """bf16 activations [M][K] -> NVFP4 (codes u8 [M][K/2], block scales u8 [M][K/16], row scales f32 [M])
+    by the stated quantiser of the skinny GEMM's A4 mode."""
+    M, K = x_bf16.shape
+    x = np.ascontiguousarray(x_bf16, dtype=np.uint16)
+    codes = np.empty((M, K // 2), dtype=np.uint8)
+    scales = np.empty((M, K // 16), dtype=np.uint8)
+    g = np.empty((M,), dtype=np.float32)
+    lib().orc_quantize_a4(_p(x), C.c_int64(M), C.c_int64(K), _p(codes), _p(scales), _p(g))
+    return codes, scales, g
+
+
+def gemm_nvfp4_a4_f64(wcodes, wscales, ts, xcodes, xscales, g) -> np.ndarray:
+    """fp64 Y[M][N] from NVFP4 weights and NVFP4-quantised activations."""
+    N, K = wscales.shape[0], wscales.shape[1] * 16
+    M = xcodes.shape[0]
+    y = np.empty((M, N), dtype=np.float64)
+    lib().orc_gemm_nvfp4_a4_f64(_p(wcodes), _p(wscales), C.c_float(ts), C.c_int64(N), C.c_int64(K), _p(xcodes),
+                                _p(xscales), _p(np.ascontiguousarray(g, dtype=np.float32)), C.c_int64(M), _p(y))
+    return y
+
+
 def num_threads() -> int:
     return int(lib().orc_num_threads())
 

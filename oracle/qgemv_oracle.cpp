@@ -41,6 +41,7 @@
 #include <cmath>
 #include <cstdint>
 #include <cstring>
+#include <vector>
 #include <limits>
 
 #ifdef _OPENMP
@@ -122,6 +123,23 @@ inline uint16_t bf16_encode(float f) {
     const uint32_t lsb = (u >> 16) & 1u;
     u += 0x7FFFu + lsb;
     return uint16_t(u >> 16);
+}
+
+// fp32 -> E2M1 code, round to nearest, ties to the even mantissa bit, saturating at +-6; the sign bit
+// of the input is kept (so -0 and tiny negatives give code 8).  The grid is 0, .5, 1, 1.5, 2, 3, 4, 6.
+inline uint8_t e2m1_encode(float f) {
+    const uint8_t sign = std::signbit(f) ? 8u : 0u;
+    const float a = std::fabs(f);
+    uint8_t c;
+    if (a <= 0.25f) c = 0;          // tie 0.25 -> 0   (mantissa 0)
+    else if (a < 0.75f) c = 1;      // 0.5
+    else if (a <= 1.25f) c = 2;     // ties 0.75 -> 1, 1.25 -> 1
+    else if (a < 1.75f) c = 3;      // 1.5
+    else if (a <= 2.5f) c = 4;      // ties 1.75 -> 2, 2.5 -> 2
+    else if (a < 3.5f) c = 5;       // 3
+    else if (a <= 5.0f) c = 6;      // ties 3.5 -> 4, 5 -> 4
+    else c = 7;                     // 6 (saturating)
+    return uint8_t(sign | c);
 }
 
 inline float nvfp4_weight(uint32_t code, uint32_t scale_byte, float tensor_scale) {
@@ -293,6 +311,69 @@ void orc_moe_gemv_nvfp4_f64(const uint8_t* codes, const uint8_t* scales, const f
             const int64_t xrow = per_slot_input ? (t * topk + j) : t;
             orc_gemv_nvfp4_f64(codes + e * cstride, scales + e * sstride, tensor_scales[e], N, K,
                                x + xrow * K, 1, out + (t * topk + j) * N);
+        }
+    }
+}
+
+// ---- activations quantised to NVFP4 (the A4 mode of the skinny GEMM) -----------------------------
+// The quantiser, stated once so that the device kernel can be held to it bit for bit.  Per row m of
+// bf16 activations (K a multiple of 16), all arithmetic in fp32 with round-to-nearest-even:
+//   amax = max |x[m][:]|;  g = amax == 0 ? 1 : amax / 2688           (2688 = 6 * 448)
+//   per block of 16:  a = max |x| in the block;  s = E4M3(a / (6 * g))   (saturating)
+//                     t = decode(s) * g;  code[k] = t == 0 ? 0 : E2M1(x[k] / t)   (saturating, sign kept)
+// The dequantised activation is decode(code) * decode(s) * g.
+void orc_quantize_a4(const uint16_t* x, int64_t M, int64_t K, uint8_t* codes, uint8_t* scales, float* g_out) {
+#pragma omp parallel for schedule(static)
+    for (int64_t m = 0; m < M; ++m) {
+        const uint16_t* xr = x + m * K;
+        float amax = 0.f;
+        for (int64_t k = 0; k < K; ++k) amax = std::max(amax, std::fabs(bf16_decode(xr[k])));
+        volatile float g = amax == 0.f ? 1.0f : amax / 2688.0f;
+        g_out[m] = g;
+        volatile float d6 = 6.0f * g;
+        for (int64_t kb = 0; kb < K / 16; ++kb) {
+            float a = 0.f;
+            for (int e = 0; e < 16; ++e) a = std::max(a, std::fabs(bf16_decode(xr[kb * 16 + e])));
+            volatile float sf = a / d6;
+            const uint8_t sb = e4m3_encode(sf);
+            scales[m * (K / 16) + kb] = sb;
+            volatile float t = e4m3_decode(sb) * g;
+            for (int e = 0; e < 16; e += 2) {
+                uint8_t c[2] = {0, 0};
+                if (t != 0.f) {
+                    for (int z = 0; z < 2; ++z) {
+                        volatile float q = bf16_decode(xr[kb * 16 + e + z]) / t;
+                        c[z] = e2m1_encode(q);
+                    }
+                }
+                codes[m * (K / 2) + (kb * 16 + e) / 2] = uint8_t(c[0] | (c[1] << 4));
+            }
+        }
+    }
+}
+
+// Y[M][N] in fp64 from NVFP4 weights and NVFP4-quantised activations (codes, block scales, row scales).
+void orc_gemm_nvfp4_a4_f64(const uint8_t* wcodes, const uint8_t* wscales, float tensor_scale, int64_t N, int64_t K,
+                           const uint8_t* xcodes, const uint8_t* xscales, const float* g, int64_t M, double* y) {
+    std::vector<double> xq(size_t(M) * size_t(K));
+    for (int64_t m = 0; m < M; ++m)
+        for (int64_t k = 0; k < K; ++k) {
+            const uint8_t byte = xcodes[m * (K / 2) + k / 2];
+            const uint32_t code = (k & 1) ? (byte >> 4) : (byte & 15u);
+            xq[size_t(m * K + k)] = double(e2m1_decode(code)) * double(e4m3_decode(xscales[m * (K / 16) + k / 16])) * double(g[m]);
+        }
+#pragma omp parallel for schedule(static)
+    for (int64_t n = 0; n < N; ++n) {
+        std::vector<double> w(static_cast<size_t>(K));
+        for (int64_t k = 0; k < K; ++k) {
+            const uint8_t byte = wcodes[n * (K / 2) + k / 2];
+            const uint32_t code = (k & 1) ? (byte >> 4) : (byte & 15u);
+            w[size_t(k)] = double(e2m1_decode(code)) * double(e4m3_decode(wscales[n * (K / 16) + k / 16]));
+        }
+        for (int64_t m = 0; m < M; ++m) {
+            double acc = 0.0;
+            for (int64_t k = 0; k < K; ++k) acc += w[size_t(k)] * xq[size_t(m * K + k)];
+            y[m * N + n] = acc * double(tensor_scale);
         }
     }
 }
