@@ -2,6 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl ours|reference]
     python bench.py --workload prefill [--tokens M]      (one secondary workload alone: skinny GEMM)
+    python bench.py --workload prefill_a4 [--tokens M]   (block-scaled prefill, NVFP4 activations)
     python bench.py --workload lmhead [--batch B]        (FP8 output head)
     python bench.py --workload moe [--tokens T]          (grouped MoE GEMV)
 
@@ -381,6 +382,107 @@ def run_prefill(args, M=None):
     return line
 
 
+def run_prefill_a4(args, M=None):
+    """The block-scaled prefill: the same 70B-shaped layer with the activations quantised to NVFP4 by the
+    library's stated quantiser and both operands consumed as stored by tcgen05 kind::mxf4nvf4
+    (QGEMV_ACT_A4_BLOCKSCALED).  A different operator from the W4A16-exact GEMM: verified against an
+    fp64 GEMM on the SAME quantised activations; the error against unquantised activations (FP4's own)
+    is reported beside it."""
+    import torch
+
+    import crit_hub_b200 as qg
+    from crit_hub_b200.stack import llama_layer_shapes, synth_nvfp4_dev
+    from oracle import oracle as O
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    M = M or args.tokens
+    model = LLAMA_70B
+    h = qg.QGemv(device=0, use_pdl=True)
+    shapes = llama_layer_shapes(model["hidden"], model["q_heads"], model["kv_heads"], model["head_dim"], model["inter"])
+    ws, xs, ys, xh, yh = [], [], [], [], []
+    g = torch.Generator()
+    g.manual_seed(13)
+    kept = None
+    for mi, (name, N, K) in enumerate(shapes):
+        codes, scales = synth_nvfp4_dev(N, K, 177 + mi, dev)
+        if mi == 0:
+            idx = sample_rows(N, 96)
+            kept = (idx, codes[idx].cpu().numpy().copy(), scales[idx].cpu().numpy().copy())
+        ws.append(h.load_device(qg.FMT_NVFP4_TC, codes.data_ptr(), scales.data_ptr(), N, K, 1.0))
+        xh.append(torch.randn((M, K), generator=g).to(torch.bfloat16).pin_memory())
+        xs.append(xh[-1].to(dev))
+        ys.append(torch.empty((M, N), dtype=torch.bfloat16, device=dev))
+        yh.append(torch.empty((M, N), dtype=torch.bfloat16).pin_memory())
+        del codes, scales
+    flops = sum(2.0 * M * w.N * w.K for w in ws)
+    wbytes = sum(w.weight_bytes for w in ws)
+    stream = torch.cuda.Stream(device=dev)
+
+    def dev_step():
+        for w, x, y in zip(ws, xs, ys):
+            h.gemm_skinny(w, x.data_ptr(), M, y.data_ptr(), qg.OUT_BF16, qg.ACT_A4_BLOCKSCALED, stream=stream.cuda_stream)
+
+    def host_step():
+        with torch.cuda.stream(stream):
+            for x, xp in zip(xs, xh):
+                x.copy_(xp, non_blocking=True)
+        dev_step()
+        with torch.cuda.stream(stream):
+            for y, yp in zip(ys, yh):
+                yp.copy_(y, non_blocking=True)
+        stream.synchronize()
+
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
+        dev_step()
+    sampler = ClockSampler(0).start()
+    ms = timed(stream, dev_step, args.steps)
+    clocks = sampler.stop()
+    host_step()
+    ms_host = timed(stream, host_step, args.steps)
+    st = h.device_status(stream.cuda_stream)
+    if st.code != 0:
+        raise SystemExit(f"kernel reported {st}")
+    idx, codes, scales = kept
+    x0 = u16(xh[0])
+    xc, xsc, xg = O.quantize_a4(x0)
+    ref = O.gemm_nvfp4_a4_f64(codes, scales, 1.0, xc, xsc, xg)
+    got = yh[0].float().numpy()[:, idx]
+    err = O.rel_l2(got, ref)
+    err_unq = O.rel_l2(got, O.gemv_nvfp4_f64(codes, scales, 1.0, x0))
+    tf = flops * args.steps / (ms * 1e-3) / 1e12
+    tf_host = flops * args.steps / (ms_host * 1e-3) / 1e12
+    gbs = wbytes * args.steps / (ms * 1e-3) / 1e9
+    peak, kind = measured_peak_gbs()
+    line = {
+        "metric": "nvfp4_a4_prefill_gemm_tflops", "value": round(tf, 1), "unit": "TFLOP/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": warmup, "ms_per_step": round(ms / args.steps, 5), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "e2m1 x ue4m3 block-scaled, both operands (tcgen05 kind::mxf4nvf4), fp32 accumulate",
+        "data": "synthetic",
+        "config": {"workload": f"llama-3-70b-shaped layer (qkv, o, gate_up, down), NVFP4 weights and NVFP4-quantised activations, {M} tokens",
+                   "tokens": M, "flops_per_step": flops, "weight_bytes_per_step": wbytes,
+                   "launches_per_gemm": "zero-fill, activation quantiser, GEMM (+ chunk sum where row tiles are fewer than SMs)",
+                   "cache": "weights per step (481 MB) exceed L2 (126 MB)"},
+        "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": UNIT, "frac": round(gbs / peak, 4),
+                     "traffic": None, "peak_kind": kind,
+                     "note": "at the FP4 tensor rate this shape is bound by the weight stream, so the fraction is of HBM bandwidth; "
+                             "no FP4 peak is in MEASURED_PEAKS.json (nominal dense 9 PFLOP/s)",
+                     "kernel": "gemm_a4_kernel", "bytes_per_launch": wbytes // 4, "us_per_launch": round(ms * 1e3 / (4 * args.steps), 2)},
+        "e2e": {"value": round(tf_host, 1), "unit": "TFLOP/s",
+                "h2d_bytes_per_step": sum(x.numel() * 2 for x in xh), "d2h_bytes_per_step": sum(y.numel() * 2 for y in yh),
+                "ms_per_step": round(ms_host / args.steps, 5)},
+        "gpu_launches": 10 * args.steps, "clocks": clocks,
+        "verified": bool(err < TOL_BF16),
+        "verify": {"rel_l2_same_quantiser": float(f"{err:.3e}"), "tol": TOL_BF16, "rel_l2_vs_unquantised_activations": float(f"{err_unq:.3e}"),
+                   "checked": f"{len(idx)} sampled output rows of the qkv projection, all {M} tokens, fp64 GEMM on the oracle's quantised activations"},
+    }
+    for w in ws:
+        w.unload()
+    h.close()
+    return line
+
+
 def run_lmhead(args, B=None):
     """The FP8-E4M3 output head (128256 x 4096, per-channel scales, fp32 logits) at decode batch B;
     two copies of the matrix alternate so every launch streams from HBM.  Verified on sampled rows."""
@@ -595,7 +697,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true", help="N = 1: skip the secondary workloads")
     ap.add_argument("--no-tp1", action="store_true", help="N > 1: do not time the unsharded stack on rank 0")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "lmhead", "moe"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "prefill_a4", "lmhead", "moe"],
                     help="decode: the headline GEMV layer stack; prefill: the skinny GEMM over one 70B-shaped layer; "
                          "lmhead: the FP8 output head; moe: the grouped expert GEMV (--tokens 1/8/64)")
     ap.add_argument("--layout", default="tc", choices=["tc", "lane"],
@@ -614,7 +716,7 @@ def main():
     if args.workload != "decode":
         if int(os.environ.get("WORLD_SIZE", "1")) != 1:
             raise SystemExit(f"--workload {args.workload} is a single-GPU workload")
-        line = {"prefill": run_prefill, "lmhead": run_lmhead, "moe": run_moe}[args.workload](args)
+        line = {"prefill": run_prefill, "prefill_a4": run_prefill_a4, "lmhead": run_lmhead, "moe": run_moe}[args.workload](args)
         print(json.dumps(line), flush=True)
         if not line["verified"]:
             raise SystemExit("verification against the oracle failed")
@@ -926,6 +1028,8 @@ def main():
                 sec[f"moe_tokens_{t}"] = brief(run_moe(small, t))
             for m in (128, 256):
                 sec[f"prefill_tokens_{m}"] = brief(run_prefill(small, m))
+            for m in (16, 128, 256):
+                sec[f"prefill_a4_tokens_{m}"] = brief(run_prefill_a4(small, m))
             line["secondary"] = sec
             line["verified"] = bool(line["verified"] and all(s["verified"] for s in sec.values()))
         print(json.dumps(line), flush=True)

@@ -32,8 +32,11 @@ namespace qg {
 
 constexpr int kA4Threads = 32 * 6;
 constexpr int kA4MaxRing = 16;
+constexpr int kA4StageItems = 4;   // items of each operand per pipeline stage: one wait and one commit per stage
 constexpr int kA4TmemCols = 512;
 
+// the stage of its K range at which the unit of row tile `tile` starts (the order is part of the result's bits)
+__host__ __device__ inline int a4_first_stage(int tile, int n_stages) { return int((uint32_t(tile) * 7u) % uint32_t(n_stages)); }
 __host__ __device__ inline int a4_item_bytes(int M) { return M * 32 + ((M + 127) / 128) * 512; }
 
 // fp32 pair -> two E4M3 bytes (a in the low byte), four fp32 -> four E2M1 codes (a in the low nibble)
@@ -158,11 +161,11 @@ struct A4Smem {
     static constexpr int kIssued = 288;
     static constexpr int kConsumed = 292;
     static constexpr int kRing = 384;
-    __host__ __device__ static constexpr int stage_bytes(int M) { return kTcItemBytes + M * 32 + ((M + 127) / 128) * 512; }
+    __host__ __device__ static constexpr int stage_bytes(int M) { return kA4StageItems * (kTcItemBytes + M * 32 + ((M + 127) / 128) * 512); }
     __host__ __device__ static constexpr int total(int M, int ring) { return kRing + ring * stage_bytes(M); }
     // tensor memory: accumulators in columns [0, 256), then per ring stage 4 columns of weight scales and
     // 4 per 128 tokens of activation scales
-    __host__ __device__ static constexpr int max_ring(int M) { return (kA4TmemCols - 256) / (4 + 4 * ((M + 127) / 128)); }
+    __host__ __device__ static constexpr int max_ring(int M) { return (kA4TmemCols - 256) / (kA4StageItems * (4 + 4 * ((M + 127) / 128))); }
 };
 
 __global__ void __launch_bounds__(kA4Threads, 1) gemm_a4_kernel(const A4Params P) {
@@ -172,7 +175,7 @@ __global__ void __launch_bounds__(kA4Threads, 1) gemm_a4_kernel(const A4Params P
     const int grid = gridDim.x, cta = blockIdx.x;
     const int M = P.M, R = P.ring;
     const int n_half = (M + 127) / 128;                 // MMAs per item: one per 128 tokens
-    const uint32_t stage_bytes = uint32_t(A4Smem::stage_bytes(M));
+    const uint32_t stage_bytes = uint32_t(A4Smem::stage_bytes(M));   // of a whole stage (kA4StageItems items of each operand)
     const uint32_t ring0 = sbase + A4Smem::kRing;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(a4_smem + A4Smem::kAbort);
     volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(a4_smem + A4Smem::kTmemPtr);
@@ -205,6 +208,7 @@ __global__ void __launch_bounds__(kA4Threads, 1) gemm_a4_kernel(const A4Params P
         // ---- producer: a weight item and the matching activation item per stage ----
         if (lane == 0) {
             const uint64_t pol_w = policy_evict_first();
+            const uint32_t xib = uint32_t(P.xq_item_bytes);
             const bool drop = (P.debug & 2) != 0;   // host-set injection: never issue a copy
             int s = 0, issued = 0;
             uint32_t use = 0;
@@ -214,8 +218,14 @@ __global__ void __launch_bounds__(kA4Threads, 1) gemm_a4_kernel(const A4Params P
             for (int u = cta; u < total_units && ok; u += grid) {
                 const int tile = u / P.n_chunk, chunk = u - tile * P.n_chunk;
                 const int i0 = chunk * P.chunk_items, i1 = min(P.kt, i0 + P.chunk_items);
-                const uint8_t* wsrc = P.payload + (uint64_t(tile) * P.kt + uint64_t(i0)) * kTcItemBytes;
-                for (int i = i0; i < i1 && ok; ++i, wsrc += kTcItemBytes) {
+                const uint8_t* wbase = P.payload + uint64_t(tile) * P.kt * kTcItemBytes;
+                // The CTAs walk K in the same direction but start at different stages (by tile): at any
+                // moment they ask L2 for different activation items instead of all for the same one.
+                const int nst = (i1 - i0 + kA4StageItems - 1) / kA4StageItems;
+                int sidx = a4_first_stage(tile, nst);
+                for (int j = 0; j < nst && ok; ++j, sidx = sidx + 1 == nst ? 0 : sidx + 1) {
+                    const int i = i0 + sidx * kA4StageItems;
+                    const uint8_t* wsrc = wbase + uint64_t(i) * kTcItemBytes;
                     if (use > 0 && !mbar_wait_probe(sbase + A4Smem::kBarEmpty + 8 * s, (use - 1) & 1, P.spin_limit)) {
                         report(P.status, QGEMV_ERR_TIMEOUT, 91, i);
                         *abort_flag = 1;
@@ -225,10 +235,11 @@ __global__ void __launch_bounds__(kA4Threads, 1) gemm_a4_kernel(const A4Params P
                     if (!drop) {
                         const uint32_t bar = sbase + A4Smem::kBarFull + 8 * s;
                         const uint32_t dst = ring0 + uint32_t(s) * stage_bytes;
-                        mbar_arrive_expect_tx(bar, stage_bytes);
-                        bulk_g2s(dst, wsrc, kTcItemBytes, bar, pol_w);
+                        const uint32_t n = uint32_t(min(kA4StageItems, i1 - i));
+                        mbar_arrive_expect_tx(bar, n * (uint32_t(kTcItemBytes) + xib));
+                        bulk_g2s(dst, wsrc, n * kTcItemBytes, bar, pol_w);
                         if (!waited) pdl_wait(), waited = true;   // the quantiser's output
-                        bulk_g2s_plain(dst + kTcItemBytes, P.xq + uint64_t(i) * uint32_t(P.xq_item_bytes), uint32_t(P.xq_item_bytes), bar);
+                        bulk_g2s_plain(dst + kA4StageItems * kTcItemBytes, P.xq + uint64_t(i) * xib, n * xib, bar);
                         ++issued;
                     }
                     if (++s == R) s = 0, ++use;
@@ -245,6 +256,7 @@ __global__ void __launch_bounds__(kA4Threads, 1) gemm_a4_kernel(const A4Params P
             const uint32_t idesc0 = (1u << 7) | (1u << 10) | ((n0 >> 3) << 17) | (uint32_t(128 >> 4) << 24);
             const uint32_t idesc1 = (1u << 7) | (1u << 10) | ((n1 >> 3) << 17) | (uint32_t(128 >> 4) << 24);
             const uint32_t sf_cols = 4u + 4u * uint32_t(n_half);
+            const uint32_t xib = uint32_t(P.xq_item_bytes);
             int s = 0, mi = 0;
             uint32_t full_par = 0, nunit = 0;
             bool ok = true;
@@ -259,24 +271,37 @@ __global__ void __launch_bounds__(kA4Threads, 1) gemm_a4_kernel(const A4Params P
                 }
                 tc_fence_after();
                 uint32_t acc = 0;
-                for (int i = i0; i < i1; ++i) {
+                const int nst = (i1 - i0 + kA4StageItems - 1) / kA4StageItems;
+                int sidx = a4_first_stage(tile, nst);
+                for (int j = 0; j < nst; ++j, sidx = sidx + 1 == nst ? 0 : sidx + 1) {
+                    const int i = i0 + sidx * kA4StageItems;
                     if (!mbar_wait_probe(sbase + A4Smem::kBarFull + 8 * s, full_par, P.spin_limit)) {
                         report(P.status, QGEMV_ERR_TIMEOUT, 93, mi);
                         *abort_flag = 1;
                         ok = false;
                         break;
                     }
-                    const uint32_t st = ring0 + uint32_t(s) * stage_bytes;
-                    const uint32_t sfa = tmem_base + 256u + uint32_t(s) * sf_cols, sfb = sfa + 4u;
-                    const uint32_t xb = st + kTcItemBytes;
-                    tc_cp_sf(sfa, d_sf | uint64_t(((st + kTcCodeBytes) >> 4) & 0x3FFFu));
-                    tc_cp_sf(sfb, d_sf | uint64_t(((xb + uint32_t(M) * 32u) >> 4) & 0x3FFFu));
-                    if (n_half > 1) tc_cp_sf(sfb + 4u, d_sf | uint64_t(((xb + uint32_t(M) * 32u + 512u) >> 4) & 0x3FFFu));
-                    tc_mma_nvf4(tmem_base, d_ab | uint64_t((st >> 4) & 0x3FFFu), d_ab | uint64_t((xb >> 4) & 0x3FFFu), idesc0, sfa, sfb, acc);
-                    if (n_half > 1)
-                        tc_mma_nvf4(tmem_base + 128u, d_ab | uint64_t((st >> 4) & 0x3FFFu), d_ab | uint64_t(((xb + 4096u) >> 4) & 0x3FFFu),
-                                    idesc1, sfa, sfb + 4u, acc);
-                    acc = 1;
+                    const int n = min(kA4StageItems, i1 - i);
+                    const uint32_t st = ring0 + uint32_t(s) * stage_bytes;          // S weight items, then S activation items
+                    const uint32_t xs = st + kA4StageItems * kTcItemBytes;
+                    const uint32_t sf0 = tmem_base + 256u + uint32_t(s) * (sf_cols * kA4StageItems);
+                    // the scales of all the stage's items first, then its MMAs
+                    for (int z = 0; z < n; ++z) {
+                        const uint32_t wi = st + uint32_t(z) * kTcItemBytes, xb = xs + uint32_t(z) * xib;
+                        const uint32_t sfa = sf0 + uint32_t(z) * sf_cols;
+                        tc_cp_sf(sfa, d_sf | uint64_t(((wi + kTcCodeBytes) >> 4) & 0x3FFFu));
+                        tc_cp_sf(sfa + 4u, d_sf | uint64_t(((xb + uint32_t(M) * 32u) >> 4) & 0x3FFFu));
+                        if (n_half > 1) tc_cp_sf(sfa + 8u, d_sf | uint64_t(((xb + uint32_t(M) * 32u + 512u) >> 4) & 0x3FFFu));
+                    }
+                    for (int z = 0; z < n; ++z) {
+                        const uint32_t wi = st + uint32_t(z) * kTcItemBytes, xb = xs + uint32_t(z) * xib;
+                        const uint32_t sfa = sf0 + uint32_t(z) * sf_cols;
+                        tc_mma_nvf4(tmem_base, d_ab | uint64_t((wi >> 4) & 0x3FFFu), d_ab | uint64_t((xb >> 4) & 0x3FFFu), idesc0, sfa, sfa + 4u, acc);
+                        if (n_half > 1)
+                            tc_mma_nvf4(tmem_base + 128u, d_ab | uint64_t((wi >> 4) & 0x3FFFu), d_ab | uint64_t(((xb + 4096u) >> 4) & 0x3FFFu),
+                                        idesc1, sfa, sfa + 8u, acc);
+                        acc = 1;
+                    }
                     tc_commit(sbase + A4Smem::kBarEmpty + 8 * s);
                     ++mi;
                     if (++s == R) s = 0, full_par ^= 1u;
