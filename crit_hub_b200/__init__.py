@@ -20,6 +20,7 @@ FMT_FP8 = 2
 FMT_NVFP4_TC = 3   # NVFP4 in the tile order the block-scaled tensor-core GEMV consumes as stored
 JOB_AFTER_PREVIOUS = 1   # qgemv_job.flags: wait for the job before this one
 JOB_ALLREDUCE = 2        # qgemv_job.flags: row-parallel projection, summed over the ranks inside the launch
+JOB_X_SILU_MUL = 4       # qgemv_job.flags: the rows of x hold gate and up values; the GEMV multiplies silu(gate) * up
 OUT_BF16 = 0
 OUT_F32 = 1
 ACT_A16_EXACT = 0
@@ -63,7 +64,8 @@ class Shard(C.Structure):
 
 class _Job(C.Structure):
     _fields_ = [("w", C.c_void_p), ("x", C.c_void_p), ("y", C.c_void_p), ("y_dtype", C.c_int32), ("flags", C.c_int32),
-                ("x_stride", C.c_int64)]
+                ("x_stride", C.c_int64), ("norm_weight", C.c_void_p), ("residual", C.c_void_p), ("norm_eps", C.c_float),
+                ("reserved", C.c_int32)]
 
 
 class _DevStatus(C.Structure):
@@ -328,10 +330,12 @@ class QGemv:
         A job waits for the earlier jobs whose buffers it reads or overwrites; with `chained` every job
         also waits for the one before it, whatever the addresses say.  NVFP4_TC weights only."""
         arr = (_Job * len(jobs))()
-        for i, jb in enumerate(jobs):   # (weight, x_ptr, y_ptr, y_dtype[, flags[, x_stride]])
+        for i, jb in enumerate(jobs):   # (weight, x_ptr, y_ptr, y_dtype[, flags[, x_stride[, fused]]])
             w, x_ptr, y_ptr, y_dtype = jb[:4]
             flags = (jb[4] if len(jb) > 4 else 0) | (JOB_AFTER_PREVIOUS if chained else 0)
-            arr[i] = _Job(w._ptr, x_ptr, y_ptr, y_dtype, flags, jb[5] if len(jb) > 5 else 0)
+            fz = jb[6] if len(jb) > 6 and jb[6] else {}     # {"norm_weight": ptr, "norm_eps": e, "residual": ptr}
+            arr[i] = _Job(w._ptr, x_ptr, y_ptr, y_dtype, flags, jb[5] if len(jb) > 5 else 0,
+                          fz.get("norm_weight"), fz.get("residual"), float(fz.get("norm_eps", 0.0)), 0)
         q = C.c_void_p()
         _check(_load().qgemv_sequence_create(self._ptr, arr, len(jobs), B, C.byref(q)), "sequence_create")
         return Sequence(self, q.value, len(jobs), B)

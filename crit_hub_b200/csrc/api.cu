@@ -61,6 +61,7 @@ struct qgemv_sequence {
     size_t smem;
     int64_t xchg_elems;  // elements of every exchange slot held by this list's all-reduce jobs (0: none)
     int64_t xchg_first;  // where they start
+    bool fused;          // some job has an activation function, a norm or a residual: the kernel instantiation with that code
 };
 
 struct qgemv_weight {
@@ -409,9 +410,12 @@ int qgemv_init(const qgemv_config* cfg, qgemv_handle** out) {
         cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_NVFP4, false, 1, true>, dyn, qg::SSmem::total<QGEMV_FMT_NVFP4>()) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8, true, 1, true>, dyn, qg::SSmem::total<QGEMV_FMT_FP8>()) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8, false, 1, true>, dyn, qg::SSmem::total<QGEMV_FMT_FP8>()) != cudaSuccess ||
-        cudaFuncSetAttribute(qg::gemv_seq_kernel<2>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
-        cudaFuncSetAttribute(qg::gemv_seq_kernel<4>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
-        cudaFuncSetAttribute(qg::gemv_seq_kernel<8>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_seq_kernel<2, false>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_seq_kernel<4, false>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_seq_kernel<8, false>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_seq_kernel<2, true>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_seq_kernel<4, true>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_seq_kernel<8, true>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_tc_kernel<1>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_tc_kernel<2>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_tc_kernel<4>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
@@ -607,6 +611,7 @@ int qgemv_sequence_create(qgemv_handle* h, const qgemv_job* jobs, int n_jobs, in
     if (grid > h->sm_count) return QGEMV_ERR_UNSUPPORTED_SHAPE;  // the CTAs wait on one another: one per SM at most
     std::vector<qg::SeqJob> tab(static_cast<size_t>(n_jobs));
     int64_t x_slots = 1, xchg_elems = 0;
+    bool fused = false;
     for (int i = 0; i < n_jobs; ++i) {
         const qgemv_job& jb = jobs[i];
         if (!jb.w || !jb.x || !jb.y) return QGEMV_ERR_INVALID_ARG;
@@ -628,22 +633,32 @@ int qgemv_sequence_create(qgemv_handle* h, const qgemv_job* jobs, int n_jobs, in
         // rows as tagged words and this job's conversion picks them up as they appear (src_job).  Every
         // other hazard waits until the job in question is complete on every CTA (dep).
         sj.dep = -1, sj.xoff = -1, sj.pub_off = -1, sj.src_off = -1, sj.src_job = -1;
-        if ((jb.flags & ~(QGEMV_JOB_AFTER_PREVIOUS | QGEMV_JOB_ALLREDUCE)) != 0) return QGEMV_ERR_INVALID_ARG;
-        if (jb.x_stride != 0 && (jb.x_stride < jb.w->K || jb.x_stride > INT32_MAX || (jb.x_stride % 8) != 0)) return QGEMV_ERR_INVALID_ARG;
-        sj.x_stride = int32_t(jb.x_stride != 0 ? jb.x_stride : jb.w->K);
+        if ((jb.flags & ~(QGEMV_JOB_AFTER_PREVIOUS | QGEMV_JOB_ALLREDUCE | QGEMV_JOB_X_SILU_MUL)) != 0 || jb.reserved != 0) return QGEMV_ERR_INVALID_ARG;
+        const int64_t x_cols = (jb.flags & QGEMV_JOB_X_SILU_MUL) != 0 ? 2 * jb.w->K : jb.w->K;   // values per stored row of x
+        if (jb.x_stride != 0 && (jb.x_stride < x_cols || jb.x_stride > INT32_MAX || (jb.x_stride % 8) != 0)) return QGEMV_ERR_INVALID_ARG;
+        if ((jb.flags & QGEMV_JOB_X_SILU_MUL) != 0 && jb.w->K % 8 != 0) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+        if (jb.norm_weight && ((reinterpret_cast<uintptr_t>(jb.norm_weight) & 15u) != 0 || !(jb.norm_eps >= 0.f))) return QGEMV_ERR_INVALID_ARG;
+        sj.x_stride = int32_t(jb.x_stride != 0 ? jb.x_stride : x_cols);
+        sj.act = (jb.flags & QGEMV_JOB_X_SILU_MUL) != 0 ? 1 : 0;
+        sj.norm_w = static_cast<const uint16_t*>(jb.norm_weight);
+        sj.norm_eps = jb.norm_eps;
+        sj.residual = jb.residual;
+        if (sj.act || sj.norm_w || sj.residual) fused = true;
         {
             const auto lo = [](const void* p) { return reinterpret_cast<uintptr_t>(p); };
             const auto ysize = [&](const qgemv_job& q) { return size_t(B) * size_t(q.w->N) * (q.y_dtype == QGEMV_OUT_F32 ? 4 : 2); };
             const auto xsize = [&](const qgemv_job& q) {
-                const size_t st = q.x_stride != 0 ? size_t(q.x_stride) : size_t(q.w->K);
-                return (size_t(B - 1) * st + size_t(q.w->K)) * 2;
+                const size_t cols = (q.flags & QGEMV_JOB_X_SILU_MUL) != 0 ? size_t(2 * q.w->K) : size_t(q.w->K);
+                const size_t st = q.x_stride != 0 ? size_t(q.x_stride) : cols;
+                return (size_t(B - 1) * st + cols) * 2;
             };
             const uintptr_t x0 = lo(jb.x), x1 = x0 + xsize(jb), y0 = lo(jb.y), y1 = y0 + ysize(jb);
             int raw = -1, n_raw = 0, other = -1;
             for (int e = i - 1; e >= 0; --e) {
                 const qgemv_job& pj = jobs[e];
                 const uintptr_t py0 = lo(pj.y), py1 = py0 + ysize(pj), px0 = lo(pj.x), px1 = px0 + xsize(pj);
-                const bool r = x0 < py1 && py0 < x1, o = (y0 < py1 && py0 < y1) || (y0 < px1 && px0 < y1);
+                const uintptr_t r0 = lo(jb.residual), r1 = jb.residual ? r0 + ysize(jb) : r0;   // the residual is read as well
+                const bool r = x0 < py1 && py0 < x1, o = (y0 < py1 && py0 < y1) || (y0 < px1 && px0 < y1) || (r0 < py1 && py0 < r1);
                 if (r && n_raw++ == 0) raw = e;
                 if (o && other < 0) other = e;
             }
@@ -652,7 +667,7 @@ int qgemv_sequence_create(qgemv_handle* h, const qgemv_job* jobs, int n_jobs, in
                 const qgemv_job& pj = jobs[raw];
                 const uintptr_t py0 = lo(pj.y);
                 const int64_t c0 = (int64_t(x0) - int64_t(py0)) / 2;
-                if (pj.y_dtype == QGEMV_OUT_BF16 && x0 >= py0 && c0 + jb.w->K <= pj.w->N && (B == 1 || sj.x_stride == pj.w->N) &&
+                if (pj.y_dtype == QGEMV_OUT_BF16 && x0 >= py0 && c0 + x_cols <= pj.w->N && (B == 1 || sj.x_stride == pj.w->N) &&
                     (pj.w->N % 4) == 0 && (c0 % 4) == 0) {
                     fast = true;
                     sj.src_job = raw;
@@ -703,6 +718,7 @@ int qgemv_sequence_create(qgemv_handle* h, const qgemv_job* jobs, int n_jobs, in
     if (!q) return QGEMV_ERR_INVALID_ARG;
     q->dev_jobs = nullptr, q->dev_counters = nullptr, q->dev_pub = nullptr;
     q->xchg_elems = xchg_elems, q->xchg_first = h->tp_seq_cursor - xchg_elems;
+    q->fused = fused;
     q->n_jobs = n_jobs, q->B = B, q->grid = grid;
     q->npad = (8 * B + 15) / 16 * 16;
     q->x_slots = int(x_slots);
@@ -782,9 +798,16 @@ int qgemv_sequence_run(qgemv_handle* h, const qgemv_sequence* q, void* stream) {
     const dim3 g(unsigned(q->grid)), blk(qg::kSeqThreads);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     g_launch_cooperative = true;
-    const cudaError_t err = q->stage_items == 2   ? launch(h, qg::gemv_seq_kernel<2>, g, blk, q->smem, st, P)
-                            : q->stage_items == 4 ? launch(h, qg::gemv_seq_kernel<4>, g, blk, q->smem, st, P)
-                                                  : launch(h, qg::gemv_seq_kernel<8>, g, blk, q->smem, st, P);
+    cudaError_t err;
+    if (q->fused) {
+        err = q->stage_items == 2   ? launch(h, qg::gemv_seq_kernel<2, true>, g, blk, q->smem, st, P)
+              : q->stage_items == 4 ? launch(h, qg::gemv_seq_kernel<4, true>, g, blk, q->smem, st, P)
+                                    : launch(h, qg::gemv_seq_kernel<8, true>, g, blk, q->smem, st, P);
+    } else {
+        err = q->stage_items == 2   ? launch(h, qg::gemv_seq_kernel<2, false>, g, blk, q->smem, st, P)
+              : q->stage_items == 4 ? launch(h, qg::gemv_seq_kernel<4, false>, g, blk, q->smem, st, P)
+                                    : launch(h, qg::gemv_seq_kernel<8, false>, g, blk, q->smem, st, P);
+    }
     return err == cudaSuccess ? QGEMV_OK : QGEMV_ERR_CUDA;
 }
 

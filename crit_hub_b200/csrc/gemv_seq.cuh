@@ -62,9 +62,13 @@ struct SeqJob {               // 80 bytes, device memory
     int32_t src_off;          // >= 0: the activations are read from pub[src_off + b * x_stride + k], published by job
                               // src_job, word by word as they appear (no grid-wide wait).  -1: from x
     int32_t src_job;
-    int32_t pad[2];
+    int32_t act;              // 1: the activations are silu(x[k]) * x[K + k] of rows that hold 2 K values (rounded to bf16)
+    float norm_eps;
+    const uint16_t* norm_w;   // bf16 [K] or null: x'[k] = bf16(x[k] * norm_w[k]); y is scaled by rsqrt(mean(x^2) + eps)
+    const void* residual;     // [B][N] in y's dtype or null: added to the result before it is rounded
+    int64_t pad[2];
 };
-static_assert(sizeof(SeqJob) == 80, "SeqJob layout");
+static_assert(sizeof(SeqJob) == 112, "SeqJob layout");
 
 struct SeqParams {
     const SeqJob* jobs;
@@ -107,6 +111,7 @@ struct SeqSmem {
     static constexpr int kConsumed = 644;
     static constexpr int kDecision = 928;   // [2][4] every warp group's common samples of the abort flag
     static constexpr int kFinAll = 688;     // jobs up to this index are added up on every CTA (-1: none)
+    static constexpr int kRowScale = 512;   // [kSeqPlaneBufsMax][8] floats: rsqrt(mean(x^2) + eps) per activation row of a job with a norm
     static constexpr int kEpiDone = 692;    // jobs whose epilogues this CTA has been through (release / acquire at CTA scope)
     static constexpr int kSfb = 1024;       // 512 bytes
     static constexpr int kX = 1536;
@@ -161,10 +166,11 @@ __device__ __forceinline__ uint32_t seq_pub_tag(uint32_t run, int j) { return ((
 __device__ __forceinline__ SeqJob seq_load_job(const SeqJob* j) {
     const uint4* p = reinterpret_cast<const uint4*>(j);
     union {
-        uint4 q[5];
+        uint4 q[7];
         SeqJob job;
     } u;
     u.q[0] = __ldg(p), u.q[1] = __ldg(p + 1), u.q[2] = __ldg(p + 2), u.q[3] = __ldg(p + 3), u.q[4] = __ldg(p + 4);
+    u.q[5] = __ldg(p + 5), u.q[6] = __ldg(p + 6);
     return u.job;
 }
 // A job is split over min(grid, items) CTAs, exactly as a launch of its own would be; the other CTAs
@@ -214,9 +220,42 @@ __device__ __noinline__ void seq_store_unit(uint32_t dst, uint4 v, float sf) {
     for (int z = 0; z < 8; ++z) asm volatile("st.shared.b32 [%0], %1;" ::"r"(dst + z * 16), "r"(pl[z]) : "memory");
 }
 
+// ---- fused activation transforms (FUSE instantiation only) ----------------------------------------------
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+__device__ __forceinline__ uint32_t bf16_pack(float lo, float hi) {
+    return uint32_t(__bfloat16_as_ushort(__float2bfloat16_rn(lo))) | (uint32_t(__bfloat16_as_ushort(__float2bfloat16_rn(hi))) << 16);
+}
+__device__ __forceinline__ float silu_f32(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
+// eight gate values and eight up values -> bf16(silu(gate) * up)
+__device__ __noinline__ uint4 seq_silu_mul(uint4 g, uint4 u) {
+    const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int z = 0; z < 4; ++z) o[z] = bf16_pack(silu_f32(bf16_lo(gw[z])) * bf16_lo(uw[z]), silu_f32(bf16_hi(gw[z])) * bf16_hi(uw[z]));
+    return make_uint4(o[0], o[1], o[2], o[3]);
+}
+// eight activations times eight norm weights -> bf16
+__device__ __noinline__ uint4 seq_mul_w(uint4 x, uint4 w) {
+    const uint32_t xw[4] = {x.x, x.y, x.z, x.w}, ww[4] = {w.x, w.y, w.z, w.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int z = 0; z < 4; ++z) o[z] = bf16_pack(bf16_lo(xw[z]) * bf16_lo(ww[z]), bf16_hi(xw[z]) * bf16_hi(ww[z]));
+    return make_uint4(o[0], o[1], o[2], o[3]);
+}
+__device__ __forceinline__ float seq_sumsq(uint4 x) {
+    const uint32_t xw[4] = {x.x, x.y, x.z, x.w};
+    float a = 0.f;
+#pragma unroll
+    for (int z = 0; z < 4; ++z) a = fmaf(bf16_lo(xw[z]), bf16_lo(xw[z]), fmaf(bf16_hi(xw[z]), bf16_hi(xw[z]), a));
+    return a;
+}
+
 constexpr int kSeqThreads = 32 * (2 + 12);  // producer, MMA issuer, three groups of four warps
 
-template <int S>
+// FUSE: the job list holds jobs with an activation function, a norm or a residual; the plain instantiation
+// carries none of that code.
+template <int S, bool FUSE>
 __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParams P) {
     extern __shared__ __align__(128) unsigned char sq_smem[];
     const uint32_t sbase = smem_u32(sq_smem);
@@ -543,9 +582,8 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                     }
                     return pub_pack(a, c);
                 };
-                auto unit_src = [&](int wu, int& b, uint32_t& dst) -> uint4 {
-                    const int k0 = unit_at(wu, b, dst);
-                    if (k0 < 0) return make_uint4(0, 0, 0, 0);
+                // eight raw activations of row b from column k0 (of the row as it is stored)
+                auto fetch8 = [&](int b, int k0) -> uint4 {
                     if (from_pub) {
                         const uint32_t* p = P.pub + size_t(job.src_off) + size_t(b) * size_t(job.x_stride) + size_t(k0);
                         return pub_wait(p, ld_pub4(p), ld_pub4(p + 4));
@@ -553,6 +591,42 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                     // possibly written by other SMs during an earlier job: read through L2, never a stale L1 line
                     return __ldcg(reinterpret_cast<const uint4*>(job.x + int64_t(b) * job.x_stride + k0));
                 };
+                // ... and what the GEMV multiplies: the activation function and the norm weight applied (FUSE)
+                auto shaped8 = [&](int b, int k0, uint4 v) -> uint4 {
+                    if constexpr (FUSE) {
+                        if (job.act == 1) v = seq_silu_mul(v, fetch8(b, k0 + job.K));
+                        if (job.norm_w) v = seq_mul_w(v, __ldg(reinterpret_cast<const uint4*>(job.norm_w + k0)));
+                    }
+                    return v;
+                };
+                auto unit_src = [&](int wu, int& b, uint32_t& dst) -> uint4 {
+                    const int k0 = unit_at(wu, b, dst);
+                    if (k0 < 0) return make_uint4(0, 0, 0, 0);
+                    return shaped8(b, k0, fetch8(b, k0));
+                };
+                if constexpr (FUSE) {
+                    // RMS norm: every CTA needs the whole row's mean square (its own K range is only a part of the
+                    // row): one more pass over the row, summed in a fixed order so that every CTA gets the same bits
+                    if (job.norm_w) {
+                        float* red = reinterpret_cast<float*>(all_max);        // 32 words, free until the maxima are taken
+                        float* rowscale = reinterpret_cast<float*>(sq_smem + SeqSmem::kRowScale) + pb * 8;
+                        for (int b = 0; b < Bl; ++b) {
+                            float a = 0.f;
+                            for (int k0 = gt * 8; k0 + 8 <= job.K; k0 += 128 * 8) {
+                                uint4 v = fetch8(b, k0);
+                                if (job.act == 1) v = seq_silu_mul(v, fetch8(b, k0 + job.K));
+                                a += seq_sumsq(v);
+                            }
+                            for (int d = 16; d > 0; d >>= 1) a += __shfl_xor_sync(0xFFFFFFFFu, a, d);
+                            if (lane == 0) red[wq] = a;
+                            named_bar_sync(bar_id, 128);
+                            if (gt == 0) rowscale[b] = rsqrtf((red[0] + red[1] + red[2] + red[3]) / float(job.K) + job.norm_eps);
+                            named_bar_sync(bar_id, 128);
+                        }
+                        if (gt < 32) all_max[gt] = 0u;
+                        named_bar_sync(bar_id, 128);
+                    }
+                }
                 auto unit_max = [&](const uint4& v) {
                     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
                     uint32_t m = 0;
@@ -611,6 +685,13 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                     }
 #pragma unroll
                     for (int i = 0; i < kKeep; ++i) keep[i] = kp[i] ? pub_pack(ka[i], kc[i]) : make_uint4(0, 0, 0, 0);
+                    if constexpr (FUSE) {
+                        if (job.act == 1 || job.norm_w) {
+#pragma unroll 1
+                            for (int i = 0; i < kKeep; ++i)
+                                if (kp[i]) keep[i] = shaped8(kb[i], int(kp[i] - (P.pub + size_t(job.src_off) + size_t(kb[i]) * size_t(job.x_stride))), keep[i]);
+                        }
+                    }
                 } else {
 #pragma unroll
                     for (int i = 0; i < kKeep; ++i) {
@@ -726,10 +807,18 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                         for (int z = 1; z < 8; ++z) a += __uint_as_float(r[z]);
                         // (the MMAs of this job have run, so its planes and row maxima are there)
                         a *= job.tensor_scale * pow2i(tc_row_exponent(rowmax2[pb * 8 + b]) + 7);
+                        if constexpr (FUSE) {
+                            if (job.norm_w) a *= reinterpret_cast<const float*>(sq_smem + SeqSmem::kRowScale)[pb * 8 + b];
+                        }
                         if (!whole) {
                             st_tagged(slot + b * 128, a, part_tag);
                         } else if (n < job.N) {
                             const int64_t idx = int64_t(b) * job.N + n;
+                            if constexpr (FUSE) {
+                                if (job.residual)
+                                    a += job.y_dtype == QGEMV_OUT_F32 ? __ldcg(static_cast<const float*>(job.residual) + idx)
+                                                                      : __bfloat162float(__ldcg(static_cast<const __nv_bfloat16*>(job.residual) + idx));
+                            }
                             if (job.y_dtype == QGEMV_OUT_F32) {
                                 static_cast<float*>(job.y)[idx] = a;
                             } else {
@@ -871,6 +960,11 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                                     have = false;
                                     break;
                                 }
+                            }
+                            if constexpr (FUSE) {
+                                if (job.residual)
+                                    a += job.y_dtype == QGEMV_OUT_F32 ? __ldcg(static_cast<const float*>(job.residual) + idx)
+                                                                      : __bfloat162float(__ldcg(static_cast<const __nv_bfloat16*>(job.residual) + idx));
                             }
                             if (job.y_dtype == QGEMV_OUT_F32) {
                                 static_cast<float*>(job.y)[idx] = a;

@@ -216,13 +216,23 @@ int qgemv_gemv_prefetch(qgemv_handle* h, const qgemv_weight* w, const void* x_bf
  * and tags back in order. */
 #define QGEMV_JOB_AFTER_PREVIOUS 1 /* start only when the job before this one is complete */
 #define QGEMV_JOB_ALLREDUCE 2      /* row-parallel projection: y = sum over the ranks of W_r x_r (see the exchange below) */
+#define QGEMV_JOB_X_SILU_MUL 4     /* the rows of x hold 2 K values (gate, then up): the GEMV multiplies bf16(silu(gate[k]) * up[k]) */
 typedef struct qgemv_job {
     const qgemv_weight* w;
     const void* x;   /* device bf16 [B][K], 16-byte aligned */
     void* y;         /* device [B][N] */
     int32_t y_dtype; /* QGEMV_OUT_BF16 or QGEMV_OUT_F32 */
-    int32_t flags;   /* 0, or QGEMV_JOB_AFTER_PREVIOUS | QGEMV_JOB_ALLREDUCE */
-    int64_t x_stride; /* elements between the rows of x; 0 = K.  A multiple of 8, at least K */
+    int32_t flags;   /* 0, or an OR of QGEMV_JOB_AFTER_PREVIOUS, QGEMV_JOB_ALLREDUCE, QGEMV_JOB_X_SILU_MUL */
+    int64_t x_stride; /* elements between the rows of x; 0 = K (2 K with QGEMV_JOB_X_SILU_MUL).  A multiple of 8 */
+    /* Element-wise work of a decoder layer folded into the job ("fused norm / activation", the engines'
+     * decode-gemv slot, engines/crit-labs/mtp5-nvfp4-drafts/card.yaml:81).  All optional (NULL / 0): */
+    const void* norm_weight; /* device bf16 [K], 16-byte aligned: RMS norm of the activations.  The GEMV multiplies
+                              * x'[k] = bf16(x[k] * norm_weight[k]) and its result is scaled by
+                              * rsqrt(mean_k x[k]^2 + norm_eps) in fp32 (the mean over the activations as the GEMV
+                              * sees them, i.e. after QGEMV_JOB_X_SILU_MUL when both are set) */
+    const void* residual;    /* device [B][N] in y's dtype: added to the result in fp32 before it is rounded; may be y */
+    float norm_eps;
+    int32_t reserved;        /* 0 */
 } qgemv_job;
 typedef struct qgemv_sequence qgemv_sequence;
 int qgemv_sequence_create(qgemv_handle* h, const qgemv_job* jobs, int n_jobs, int B, qgemv_sequence** out);

@@ -523,3 +523,77 @@ def test_sequence_column_range_chain(qg, handle, B):
     seq.destroy()
     for w in ws:
         w.unload()
+
+
+def _silu_mul_bf16(gu_bits, K):
+    """bf16(silu(gate) * up) from rows that hold K gate values and then K up values (fp64 inside)."""
+    v = O.bf16_decode(gu_bits).astype(np.float64)
+    g, u = v[:, :K], v[:, K:2 * K]
+    return O.bf16_encode((g / (1.0 + np.exp(-g)) * u).astype(np.float32))
+
+
+def _rms_parts(x_bits, w_bits, eps):
+    """What a job with a norm multiplies, bf16(x * w), and the fp64 row factor rsqrt(mean(x^2) + eps)."""
+    x = O.bf16_decode(x_bits)
+    xs = O.bf16_encode((x * O.bf16_decode(w_bits)[None, :]).astype(np.float32))      # the fp32 product of two bf16 is exact
+    r = 1.0 / np.sqrt((x.astype(np.float64) ** 2).mean(axis=1) + eps)
+    return xs, r
+
+
+@pytest.mark.parametrize("B", [1, 3])
+def test_sequence_fused_decoder_layer(qg, handle, B):
+    """The element-wise work of a decoder layer folded into the jobs: o-projection + residual, RMS norm
+    into gate/up, SiLU * up into down + residual, RMS norm into the next QKV -- four jobs, one launch,
+    every link checked against the fp64 oracle fed with the device's previous output."""
+    import torch
+    H, I, Q = 1024, 2816, 1536
+    eps = 1e-5
+    mk = lambda N, K, seed: O.make_nvfp4(N, K, seed=seed, ts=1.0 / (0.1463 * K ** 0.5))
+    m_o, m_gu, m_dn, m_qkv = mk(H, H, 901), mk(2 * I, H, 902), mk(H, I, 903), mk(Q, H, 904)
+    ws = [handle.load(qg.pack(qg.FMT_NVFP4_TC, *m)) for m in (m_o, m_gu, m_dn, m_qkv)]
+    attn, h0 = O.make_x(B, H, seed=905), O.make_x(B, H, seed=906)
+    nw1 = O.bf16_encode(1.0 + 0.1 * O.bf16_decode(O.make_x(1, H, seed=907))[0])
+    nw2 = O.bf16_encode(1.0 + 0.1 * O.bf16_decode(O.make_x(1, H, seed=908))[0])
+    d = lambda a: U.dev_u16(a)
+    attn_d, h0_d, nw1_d, nw2_d = d(attn), d(h0), d(nw1), d(nw2)
+    y0 = torch.zeros((B, H), dtype=torch.bfloat16, device="cuda")
+    y1 = torch.zeros((B, 2 * I), dtype=torch.bfloat16, device="cuda")
+    y2 = torch.zeros((B, H), dtype=torch.bfloat16, device="cuda")
+    y3 = torch.zeros((B, Q), dtype=torch.float32, device="cuda")
+    jobs = [(ws[0], attn_d.data_ptr(), y0.data_ptr(), qg.OUT_BF16, 0, 0, {"residual": h0_d.data_ptr()}),
+            (ws[1], y0.data_ptr(), y1.data_ptr(), qg.OUT_BF16, 0, 0, {"norm_weight": nw1_d.data_ptr(), "norm_eps": eps}),
+            (ws[2], y1.data_ptr(), y2.data_ptr(), qg.OUT_BF16, qg.JOB_X_SILU_MUL, 0, {"residual": y0.data_ptr()}),
+            (ws[3], y2.data_ptr(), y3.data_ptr(), qg.OUT_F32, 0, 0, {"norm_weight": nw2_d.data_ptr(), "norm_eps": eps})]
+    seq = handle.sequence(jobs, B)
+    bits = lambda t: t.view(torch.int16).cpu().numpy().view(np.uint16)
+    for rep in range(2):
+        for y in (y0, y1, y2, y3):
+            y.zero_()
+        seq.run()
+        torch.cuda.synchronize()
+        U.status_ok(handle)
+        g0, g1, g2 = bits(y0), bits(y1), bits(y2)
+        ref0 = O.gemv_nvfp4_f64(*m_o, attn) + O.bf16_decode(h0)
+        assert O.rel_l2(O.bf16_decode(g0), ref0) < TOL_BF16, rep
+        xs, r = _rms_parts(g0, nw1, eps)
+        ref1 = O.gemv_nvfp4_f64(*m_gu, xs) * r[:, None]
+        assert O.rel_l2(O.bf16_decode(g1), ref1) < TOL_BF16, rep
+        ref2 = O.gemv_nvfp4_f64(*m_dn, _silu_mul_bf16(g1, I)) + O.bf16_decode(g0)
+        assert O.rel_l2(O.bf16_decode(g2), ref2) < TOL_BF16, rep
+        xs, r = _rms_parts(g2, nw2, eps)
+        ref3 = O.gemv_nvfp4_f64(*m_qkv, xs) * r[:, None]
+        assert O.rel_l2(y3.cpu().numpy(), ref3) < 2e-4, rep      # fp32 output; silu's fast exp sits upstream only
+    seq.destroy()
+    # the same options on jobs whose inputs are plain buffers (no published rows), fp32 residual
+    res32 = torch.randn((B, H), device="cuda")
+    y4 = torch.zeros((B, H), dtype=torch.float32, device="cuda")
+    gu_in = d(O.make_x(B, 2 * I, seed=909))
+    seq = handle.sequence([(ws[2], gu_in.data_ptr(), y4.data_ptr(), qg.OUT_F32, qg.JOB_X_SILU_MUL, 0, {"residual": res32.data_ptr()})], B)
+    seq.run()
+    torch.cuda.synchronize()
+    U.status_ok(handle)
+    ref4 = O.gemv_nvfp4_f64(*m_dn, _silu_mul_bf16(O.make_x(B, 2 * I, seed=909), I)) + res32.cpu().numpy().astype(np.float64)
+    assert O.rel_l2(y4.cpu().numpy(), ref4) < 2e-4
+    seq.destroy()
+    for w in ws:
+        w.unload()
