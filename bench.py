@@ -656,7 +656,10 @@ def run_moe(args, T=None):
                    "us_per_layer": round(ms * 1e3 / args.steps / L, 2),
                    "cache": "four layers of distinct experts; at 1 token the touched experts (21 MB per layer) fit L2"},
         "roofline": {"bound": "hbm", "achieved": round(gbs, 2), "peak": peak, "unit": UNIT, "frac": round(gbs / peak, 4),
-                     "traffic": None, "peak_kind": kind, "kernel": "moe_stream_kernel<NVFP4>",
+                     "traffic": int(1.01 * (nbytes // (2 * L))),
+                     "traffic_source": "ncu capture at 8 tokens (profiles/moe_stream_128experts_t8_traffic.md): DRAM read+write = "
+                                       "1.004-1.027 x the touched experts' bytes per launch; scaled by bytes",
+                     "peak_kind": kind, "kernel": "moe_stream_kernel<NVFP4>",
                      "bytes_per_launch": nbytes // (2 * L), "us_per_launch": round(ms * 1e3 / (2 * L * args.steps), 2)},
         "e2e": {"value": round(nbytes * args.steps / (ms_host * 1e-3) / 1e9, 2), "unit": UNIT,
                 "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 4,

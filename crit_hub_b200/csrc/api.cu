@@ -952,7 +952,9 @@ int gemm_a4(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, int M, v
     }
     const int chunk_items = int((kt + n_chunk - 1) / n_chunk);
     n_chunk = int((kt + chunk_items - 1) / chunk_items);
-    QG_CUDA(cudaMemsetAsync(items, 0, size_t(kt) * size_t(qg::a4_item_bytes(M)), st));  // tokens and K blocks beyond the data are zero
+    // K blocks beyond the data must be zero codes with zero scales; with K a multiple of 64 the quantiser writes
+    // every byte the MMAs read (scale rows of tokens beyond M are copied to tensor memory but never used)
+    if (w->K % 64 != 0) QG_CUDA(cudaMemsetAsync(items, 0, size_t(kt) * size_t(qg::a4_item_bytes(M)), st));
     qg::A4QuantParams Q;
     Q.x = static_cast<const uint16_t*>(x_bf16);
     Q.M = M, Q.K = int32_t(w->K);
