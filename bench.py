@@ -213,12 +213,13 @@ class DecodeStack:
                 del codes, scales
         torch.cuda.synchronize()
 
-    def runner(self, batch, fused=True, chained=False, prefetch_next=True, after_call=None, weights=None, flags=None, chain=False):
+    def runner(self, batch, fused=True, chained=False, prefetch_next=True, after_call=None, weights=None, flags=None, chain=False,
+               opts=None):
         import torch
         from crit_hub_b200.stack import LayerStack
         ws = weights if weights is not None else self.weights
         st = LayerStack(self.handle, ws, batch, self.qg.OUT_BF16, device=self.device.index, after_call=after_call,
-                        prefetch_next=prefetch_next, fused=fused and self.layout == "tc", chained=chained, job_flags=flags, chain=chain)
+                        prefetch_next=prefetch_next, fused=fused and self.layout == "tc", chained=chained, job_flags=flags, chain=chain, job_opts=opts)
         g = torch.Generator()
         g.manual_seed(7 + self.rank + 100 * batch)
         st.set_inputs([torch.randn((batch, w.K), generator=g).to(torch.bfloat16) for w in ws])
@@ -234,6 +235,33 @@ class DecodeStack:
             got = stack.output(call, host=True).float().numpy()[:, idx]
             worst = max(worst, O.rel_l2(got, O.gemv_nvfp4_f64(codes, scales, ts, x)))
         return worst
+
+
+def _verify_fused(self, stack, flags, opts, norm_w_bits, resid_bits):
+    """Sampled rows of the kept calls of a runner whose jobs carry a norm, SiLU x up or a residual: the
+    fp64 oracle applied to the device's own input of each call."""
+    import numpy as np
+    from oracle import oracle as O
+    worst = 0.0
+    for call, (idx, codes, scales, ts) in self.kept.items():
+        x = O.bf16_decode(u16(stack.input(call))).astype(np.float64)
+        K = stack.calls[call].weight.K
+        if flags[call] & self.qg.JOB_X_SILU_MUL:
+            g, u = x[:, :K], x[:, K:2 * K]
+            x = O.bf16_decode(O.bf16_encode((g / (1.0 + np.exp(-g)) * u).astype(np.float32))).astype(np.float64)
+        r = np.ones(x.shape[0])
+        if "norm_weight" in opts[call]:
+            r = 1.0 / np.sqrt((x ** 2).mean(axis=1) + opts[call]["norm_eps"])
+            x = O.bf16_decode(O.bf16_encode((x.astype(np.float32) * O.bf16_decode(norm_w_bits)[None, :]))).astype(np.float64)
+        ref = O.gemv_nvfp4_f64(codes, scales, ts, O.bf16_encode(x.astype(np.float32))) * r[:, None]
+        if "residual" in opts[call]:
+            ref = ref + O.bf16_decode(resid_bits)[:, idx]
+        got = stack.output(call, host=True).float().numpy()[:, idx]
+        worst = max(worst, O.rel_l2(got, ref))
+    return worst
+
+
+DecodeStack.verify_fused = _verify_fused
 
 
 def cpu_reference_sample(model, batch, steps, warmup, threads):
@@ -909,6 +937,27 @@ def main():
             extra["chained_gbs"] = round(ds.bytes * args.steps / (ms_chain * 1e-3) / 1e9, 2)
             extra["chained_us_per_layer"] = round(ms_chain * 1e3 / args.steps / model["layers"], 3)
             extra["chained_verify_rel_l2"] = float(f"{ds.verify(chain):.3e}")
+            # ... and that chain with the element-wise work of a decoder layer folded into the jobs: RMS norm into
+            # qkv and gate/up, residual added to o and down, SiLU(gate) * up into down (which then reads all 2 K
+            # columns of gate/up's output)
+            hid = model["hidden"]
+            gnorm = torch.Generator()
+            gnorm.manual_seed(99)
+            norm_w = (1.0 + 0.1 * torch.randn(hid, generator=gnorm)).to(torch.bfloat16).to(ds.device)
+            resid = torch.randn((B, hid), generator=gnorm).to(torch.bfloat16).to(ds.device)
+            fl, op = [], []
+            for i in range(len(ds.weights)):
+                name = ds.shapes[i % 4][0]
+                fl.append(qg.JOB_X_SILU_MUL if name == "down" else 0)
+                op.append({"norm_weight": norm_w.data_ptr(), "norm_eps": 1e-5} if name in ("qkv", "gate_up") else {"residual": resid.data_ptr()})
+            lay = ds.runner(B, fused=True, chain=True, flags=fl, opts=op)
+            lay.capture()
+            for _ in range(warmup):
+                lay.step()
+            ms_lay = timed(lay.stream, lay.step, args.steps)
+            lay.step_host()
+            extra["chained_fused_layer_gbs"] = round(ds.bytes * args.steps / (ms_lay * 1e-3) / 1e9, 2)
+            extra["chained_fused_layer_verify_rel_l2"] = float(f"{ds.verify_fused(lay, fl, op, u16(norm_w), u16(resid)):.3e}")
             # ... and independent inputs with every job made to wait for the one before it all the same
             slow = ds.runner(B, fused=True, chained=True)
             slow.capture()
@@ -960,7 +1009,8 @@ def main():
                      "the job list orders jobs only where their buffers overlap, so here they may overlap in time.  "
                      "`chained_gbs`: the same weights with every GEMV reading the output of the one before it (its first K columns) -- a "
                      "decode step's data flow with the element-wise work left out, where each job waits for the last row of the one before; "
-                     "`forced_order_gbs`: independent inputs, each job made to wait for the one before it")
+                     "`chained_fused_layer_gbs`: that chain with RMS norm (qkv, gate/up), SiLU x up (down) and residual adds (o, down) "
+                     "folded into the jobs; `forced_order_gbs`: independent inputs, each job made to wait for the one before it")
             traffic, tsrc = int(per_launch_bytes * 1.032), ("ncu capture of a 2-layer launch of the same kernel (profiles/gemv_seq_llama8b_2layers.md): "
                                                              "DRAM read 1.001 x, read+write 1.032 x the algorithmic weight bytes; scaled by bytes")
         elif args.layout == "tc":

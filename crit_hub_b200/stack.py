@@ -32,7 +32,8 @@ class LayerStack:
 
     def __init__(self, handle: QGemv, weights: list[Weight], batch: int, out_dtype: int = OUT_BF16,
                  device: int = 0, prefetch_next: bool = False, after_call=None, fused: bool = False,
-                 chained: bool = False, job_flags: list[int] | None = None, chain: bool = False):
+                 chained: bool = False, job_flags: list[int] | None = None, chain: bool = False,
+                 job_opts: list[dict | None] | None = None):
         self.handle, self.batch, self.out_dtype = handle, batch, out_dtype
         # fused: the whole list as ONE persistent launch (qgemv_sequence_*; tensor-core layout only, no hooks)
         self.fused = fused and after_call is None
@@ -40,6 +41,8 @@ class LayerStack:
         # projections do (each consumes, through attention / activation / norm, what the previous produced)
         self.chained = chained
         self.job_flags = job_flags  # per-call qgemv_job flags of the fused launch (e.g. JOB_ALLREDUCE), or None
+        # per-call element-wise options of the fused launch ({"norm_weight": ptr, "norm_eps": e, "residual": ptr}), or None
+        self.job_opts = job_opts
         self.sequence = None
         # after_call(i): optional hook enqueued on the same stream right after GEMV i (and captured
         # with it), e.g. the all-reduce of a row-parallel projection's partial outputs
@@ -50,8 +53,10 @@ class LayerStack:
         # chain: call i reads the first K_i columns of call i - 1's output (a decode step's data flow with the
         # element-wise work between the projections left out); only the first call has an input of its own.
         # Needs the fused launch (rows of a column range are strided) and bf16 outputs.
+        from . import JOB_X_SILU_MUL
+        cols = lambda i: weights[i].K * (2 if job_flags and job_flags[i] & JOB_X_SILU_MUL else 1)   # columns of x call i reads
         self.chain = chain and self.fused and out_dtype == OUT_BF16 and all(
-            weights[i].K <= weights[i - 1].N and weights[i - 1].N % 8 == 0 for i in range(1, len(weights)))
+            cols(i) <= weights[i - 1].N and weights[i - 1].N % 8 == 0 for i in range(1, len(weights)))
         x_total = y_total = 0
         for i, w in enumerate(weights):
             self.calls.append(_Call(w, x_total, y_total))
@@ -79,7 +84,9 @@ class LayerStack:
         """Host copy of call i's activations [batch][K] as of the last step_host()."""
         c = self.calls[i]
         if self.chain and i > 0:
-            return self.output(i - 1, host=True)[:, :c.weight.K]
+            from . import JOB_X_SILU_MUL
+            k = c.weight.K * (2 if self.job_flags and self.job_flags[i] & JOB_X_SILU_MUL else 1)
+            return self.output(i - 1, host=True)[:, :k]
         return self.x_host[c.x_off:c.x_off + self.batch * c.weight.K].view(self.batch, c.weight.K)
 
     def output(self, i: int, host: bool = False) -> torch.Tensor:
@@ -107,11 +114,12 @@ class LayerStack:
                     jobs = []
                     for i, c in enumerate(self.calls):
                         fl = self.job_flags[i] if self.job_flags else 0
+                        opts = self.job_opts[i] if self.job_opts else None
                         if self.chain and i > 0:
                             prev = self.calls[i - 1]
-                            jobs.append((c.weight, yb + prev.y_off * ye, yb + c.y_off * ye, self.out_dtype, fl, prev.weight.N))
+                            jobs.append((c.weight, yb + prev.y_off * ye, yb + c.y_off * ye, self.out_dtype, fl, prev.weight.N, opts))
                         else:
-                            jobs.append((c.weight, xb + c.x_off * xe, yb + c.y_off * ye, self.out_dtype, fl))
+                            jobs.append((c.weight, xb + c.x_off * xe, yb + c.y_off * ye, self.out_dtype, fl, 0, opts))
                     self.sequence = self.handle.sequence(jobs, self.batch, chained=self.chained)
                 except QgemvError as e:  # e.g. activations too large for the persistent kernel: one launch per GEMV
                     if e.status != ERR_UNSUPPORTED_SHAPE or self.chain:
