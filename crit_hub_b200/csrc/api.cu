@@ -184,7 +184,9 @@ int launch_gemv(const qgemv_handle* h, const qgemv_weight* w, const qg::GemvPara
     if (qg::use_stream_path(P.prob == nullptr, P.B, P.units) && !(h->cfg.debug & 256)) {
         const dim3 sblock(qg::kSThreads);
         // whole panels per CTA (no cross-CTA fix-up)
-        const bool whole = wp_has_enough_panels(h, w) && !(h->cfg.debug & 512);
+        // (the whole-panel kernel keeps weight offsets in 32 bits: matrices of 4 GiB and more take the split kernel,
+        // whose offsets are 64-bit)
+        const bool whole = wp_has_enough_panels(h, w) && !(h->cfg.debug & 512) && w->payload_bytes < (uint64_t(1) << 32);
         if (w->fmt == QGEMV_FMT_NVFP4) {
             const size_t smem = qg::SSmem::total<QGEMV_FMT_NVFP4>();
             const bool full = P.units % qg::StreamTraits<QGEMV_FMT_NVFP4>::kChunkUnits == 0;

@@ -458,7 +458,6 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemv_tc_kernel(const TcParams P
                 tc_fence_after();
                 if (P.trace) P.trace[cta * 16 + 3] = clock64();
                 tc_cp_sf2(tmem_sfb, sf_lo | (((sbase + TcSmem::kSfb) >> 4) & 0x3FFFu), sf_hi);
-                if (P.trace && (P.debug & 16)) P.trace[gridDim.x * 16 + cta * 64 + 63] = clock64();
                 for (; ok && have; have = wk.next(sg)) {
                     // the accumulator is free once the epilogue of the segment before last has read it
                     if (nseg >= 2 &&
@@ -498,7 +497,6 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemv_tc_kernel(const TcParams P
                         acc = 1;
                         x_lo += xslot16 * S;
                         tc_commit(bar_empty);  // the stage is reusable once these retire
-                        if (P.trace && (P.debug & 16) && mi < 60) P.trace[gridDim.x * 16 + cta * 64 + mi] = clock64();
                         ++mi;
                         item16 += stage16, sfa += 4u * S, bar_full += 8, bar_empty += 8;
                         if (item16 == ring_end16) {
