@@ -250,14 +250,21 @@ __global__ void __launch_bounds__(kA4Threads, 1) gemm_a4_kernel(const A4Params P
         }
     } else if (warp == 1) {
         // ---- MMA issuer ----
+        // One thread, and a dependent instruction on one thread costs about five cycles: everything per stage
+        // is additions on 32-bit descriptor halves (addresses in 16-byte units), unrolled over the stage's items.
         if (elect_one()) {
             const uint64_t d_ab = smem_desc(0, 128, 256), d_sf = smem_desc(0, 0, 128);
+            const uint32_t ab_hi = uint32_t(d_ab >> 32), ab_lo = uint32_t(d_ab), sf_hi = uint32_t(d_sf >> 32), sf_lo = uint32_t(d_sf);
             const uint32_t n0 = uint32_t(M < 128 ? M : 128), n1 = uint32_t(M > 128 ? M - 128 : 0);
             const uint32_t idesc0 = (1u << 7) | (1u << 10) | ((n0 >> 3) << 17) | (uint32_t(128 >> 4) << 24);
             const uint32_t idesc1 = (1u << 7) | (1u << 10) | ((n1 >> 3) << 17) | (uint32_t(128 >> 4) << 24);
             const uint32_t sf_cols = 4u + 4u * uint32_t(n_half);
-            const uint32_t xib = uint32_t(P.xq_item_bytes);
-            int s = 0, mi = 0;
+            const uint32_t xib16 = uint32_t(P.xq_item_bytes) >> 4, m2_16 = (uint32_t(M) * 32u) >> 4;
+            constexpr uint32_t kItem16 = kTcItemBytes >> 4, kCode16 = kTcCodeBytes >> 4, kW16 = (kA4StageItems * kTcItemBytes) >> 4;
+            const uint32_t stage16 = stage_bytes >> 4, ring16 = (ring0 >> 4) & 0x3FFFu, ring_end16 = ring16 + uint32_t(R) * stage16;
+            const uint32_t sf_stage = sf_cols * kA4StageItems, sf_first = tmem_base + 256u;
+            uint32_t w16 = ring16, sf0 = sf_first, bar_full = sbase + A4Smem::kBarFull, bar_empty = sbase + A4Smem::kBarEmpty;
+            int mi = 0;
             uint32_t full_par = 0, nunit = 0;
             bool ok = true;
             for (int u = cta; u < total_units && ok; u += grid, ++nunit) {
@@ -273,38 +280,54 @@ __global__ void __launch_bounds__(kA4Threads, 1) gemm_a4_kernel(const A4Params P
                 uint32_t acc = 0;
                 const int nst = (i1 - i0 + kA4StageItems - 1) / kA4StageItems;
                 int sidx = a4_first_stage(tile, nst);
+                const int n_last = i1 - i0 - (nst - 1) * kA4StageItems;   // items of the K range's last stage
                 for (int j = 0; j < nst; ++j, sidx = sidx + 1 == nst ? 0 : sidx + 1) {
-                    const int i = i0 + sidx * kA4StageItems;
-                    if (!mbar_wait_probe(sbase + A4Smem::kBarFull + 8 * s, full_par, P.spin_limit)) {
+                    if (!mbar_wait_probe(bar_full, full_par, P.spin_limit)) {
                         report(P.status, QGEMV_ERR_TIMEOUT, 93, mi);
                         *abort_flag = 1;
                         ok = false;
                         break;
                     }
-                    const int n = min(kA4StageItems, i1 - i);
-                    const uint32_t st = ring0 + uint32_t(s) * stage_bytes;          // S weight items, then S activation items
-                    const uint32_t xs = st + kA4StageItems * kTcItemBytes;
-                    const uint32_t sf0 = tmem_base + 256u + uint32_t(s) * (sf_cols * kA4StageItems);
-                    // the scales of all the stage's items first, then its MMAs
-                    for (int z = 0; z < n; ++z) {
-                        const uint32_t wi = st + uint32_t(z) * kTcItemBytes, xb = xs + uint32_t(z) * xib;
-                        const uint32_t sfa = sf0 + uint32_t(z) * sf_cols;
-                        tc_cp_sf(sfa, d_sf | uint64_t(((wi + kTcCodeBytes) >> 4) & 0x3FFFu));
-                        tc_cp_sf(sfa + 4u, d_sf | uint64_t(((xb + uint32_t(M) * 32u) >> 4) & 0x3FFFu));
-                        if (n_half > 1) tc_cp_sf(sfa + 8u, d_sf | uint64_t(((xb + uint32_t(M) * 32u + 512u) >> 4) & 0x3FFFu));
+                    const uint32_t x16 = w16 + kW16;     // the stage: S weight items, then S activation items
+                    if (sidx + 1 < nst || n_last == kA4StageItems) {
+                        // the scales of all the stage's items first, then its MMAs
+#pragma unroll
+                        for (int z = 0; z < kA4StageItems; ++z) {
+                            const uint32_t sfa = sf0 + uint32_t(z) * sf_cols;
+                            tc_cp_sf2(sfa, sf_lo | (w16 + kCode16 + kItem16 * z), sf_hi);
+                            tc_cp_sf2(sfa + 4u, sf_lo | (x16 + m2_16 + xib16 * z), sf_hi);
+                            if (n_half > 1) tc_cp_sf2(sfa + 8u, sf_lo | (x16 + m2_16 + 32u + xib16 * z), sf_hi);
+                        }
+#pragma unroll
+                        for (int z = 0; z < kA4StageItems; ++z) {
+                            const uint32_t sfa = sf0 + uint32_t(z) * sf_cols;
+                            tc_mma_nvf4_2(tmem_base, ab_lo | (w16 + kItem16 * z), ab_lo | (x16 + xib16 * z), ab_hi, idesc0, sfa, sfa + 4u,
+                                          z == 0 ? acc : 1u);
+                            if (n_half > 1)
+                                tc_mma_nvf4_2(tmem_base + 128u, ab_lo | (w16 + kItem16 * z), ab_lo | (x16 + 256u + xib16 * z), ab_hi, idesc1, sfa,
+                                              sfa + 8u, z == 0 ? acc : 1u);
+                        }
+                    } else {
+                        for (int z = 0; z < n_last; ++z) {
+                            const uint32_t sfa = sf0 + uint32_t(z) * sf_cols;
+                            tc_cp_sf2(sfa, sf_lo | (w16 + kCode16 + kItem16 * z), sf_hi);
+                            tc_cp_sf2(sfa + 4u, sf_lo | (x16 + m2_16 + xib16 * z), sf_hi);
+                            if (n_half > 1) tc_cp_sf2(sfa + 8u, sf_lo | (x16 + m2_16 + 32u + xib16 * z), sf_hi);
+                        }
+                        for (int z = 0; z < n_last; ++z) {
+                            const uint32_t sfa = sf0 + uint32_t(z) * sf_cols;
+                            tc_mma_nvf4_2(tmem_base, ab_lo | (w16 + kItem16 * z), ab_lo | (x16 + xib16 * z), ab_hi, idesc0, sfa, sfa + 4u,
+                                          z == 0 ? acc : 1u);
+                            if (n_half > 1)
+                                tc_mma_nvf4_2(tmem_base + 128u, ab_lo | (w16 + kItem16 * z), ab_lo | (x16 + 256u + xib16 * z), ab_hi, idesc1, sfa,
+                                              sfa + 8u, z == 0 ? acc : 1u);
+                        }
                     }
-                    for (int z = 0; z < n; ++z) {
-                        const uint32_t wi = st + uint32_t(z) * kTcItemBytes, xb = xs + uint32_t(z) * xib;
-                        const uint32_t sfa = sf0 + uint32_t(z) * sf_cols;
-                        tc_mma_nvf4(tmem_base, d_ab | uint64_t((wi >> 4) & 0x3FFFu), d_ab | uint64_t((xb >> 4) & 0x3FFFu), idesc0, sfa, sfa + 4u, acc);
-                        if (n_half > 1)
-                            tc_mma_nvf4(tmem_base + 128u, d_ab | uint64_t((wi >> 4) & 0x3FFFu), d_ab | uint64_t(((xb + 4096u) >> 4) & 0x3FFFu),
-                                        idesc1, sfa, sfa + 8u, acc);
-                        acc = 1;
-                    }
-                    tc_commit(sbase + A4Smem::kBarEmpty + 8 * s);
+                    acc = 1;
+                    tc_commit(bar_empty);
                     ++mi;
-                    if (++s == R) s = 0, full_par ^= 1u;
+                    w16 += stage16, sf0 += sf_stage, bar_full += 8, bar_empty += 8;
+                    if (w16 == ring_end16) w16 = ring16, sf0 = sf_first, full_par ^= 1u, bar_full = sbase + A4Smem::kBarFull, bar_empty = sbase + A4Smem::kBarEmpty;
                 }
                 if (!ok) break;
                 tc_commit(sbase + A4Smem::kBarDFull);
