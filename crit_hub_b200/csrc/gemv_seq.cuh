@@ -251,6 +251,16 @@ __device__ __forceinline__ float seq_sumsq(uint4 x) {
     return a;
 }
 
+#ifdef QGEMV_SEQ_PROFILE   // diagnostics build only: where the MMA issuer's time goes (cycles per CTA, summed over the launch)
+#define SEQ_PROF_T0() const long long prof_t0 = clock64()
+#define SEQ_PROF_ADD(slot) prof[slot] += clock64() - prof_t0
+#define SEQ_STAMPS false
+#else
+#define SEQ_STAMPS true
+#define SEQ_PROF_T0()
+#define SEQ_PROF_ADD(slot)
+#endif
+
 constexpr int kSeqThreads = 32 * (2 + 12);  // producer, MMA issuer, three groups of four warps
 
 // FUSE: the job list holds jobs with an activation function, a norm or a residual; the plain instantiation
@@ -362,6 +372,10 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
             const uint32_t ring_end16 = ring16 + uint32_t(R) * stage16;
             bool ok = true;
             int mi = 0;  // stages issued
+#ifdef QGEMV_SEQ_PROFILE
+            long long prof[4] = {0, 0, 0, 0};
+            const long long prof_start = clock64();
+#endif
             SeqJob job = seq_load_job(P.jobs);
             int pb = 0;        // plane buffer of job j: j % nbuf, kept as a counter (no division in this thread)
             uint32_t pph = 0;  // parity of that buffer's use: (j / nbuf) & 1
@@ -370,14 +384,16 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 if (j + 1 < P.n_jobs) next = seq_load_job(P.jobs + j + 1);
                 const int32_t kt_len = job.kt;
                 // the digit planes of this job (every CTA signals, also one without items)
+                SEQ_PROF_T0();
                 if (!seq_mbar_wait(sbase + SeqSmem::kBarXReady + 8 * pb, pph, P.spin_limit)) {
                     seq_report(P.status, 72, j);
                     *abort_flag = 1;
                     ok = false;
                     break;
                 }
+                SEQ_PROF_ADD(0);
                 tc_fence_after();
-                if (P.trace) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 3] = globaltimer_ns();
+                if (SEQ_STAMPS && P.trace) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 3] = globaltimer_ns();
                 // this CTA's item range of the job, computed by the PLANES group
                 const volatile int* rg = reinterpret_cast<const volatile int*>(sq_smem + SeqSmem::kRange) + pb * 2;
                 const int32_t r_begin = rg[0], r_end = rg[1];
@@ -390,12 +406,16 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 if (j == 0) tc_cp_sf2(tmem_sfb, sf_lo | (((sbase + SeqSmem::kSfb) >> 4) & 0x3FFFu), sf_hi);
                 for (; ok && have; have = wk.next(sg)) {
                     // the accumulator is free once the epilogue of the segment before last has read it
-                    if (nseg >= 2 &&
-                        !seq_mbar_probe(sbase + SeqSmem::kBarDFree + 8 * (nseg & 1), ((nseg >> 1) - 1) & 1, P.spin_limit)) {
-                        seq_report(P.status, 73, int(nseg));
-                        *abort_flag = 1;
-                        ok = false;
-                        break;
+                    {
+                        SEQ_PROF_T0();
+                        if (nseg >= 2 &&
+                            !seq_mbar_probe(sbase + SeqSmem::kBarDFree + 8 * (nseg & 1), ((nseg >> 1) - 1) & 1, P.spin_limit)) {
+                            seq_report(P.status, 73, int(nseg));
+                            *abort_flag = 1;
+                            ok = false;
+                            break;
+                        }
+                        SEQ_PROF_ADD(1);
                     }
                     tc_fence_after();
                     const uint32_t tmem_d = tmem_base + (nseg & 1) * uint32_t(npad);
@@ -407,11 +427,15 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                         // (the stage was written through the async proxy and is read through it: the
                         // barrier's acquire is all the ordering the MMAs need -- no tcgen05 fence here,
                         // which costs this thread a few hundred cycles per stage)
-                        if (!seq_mbar_probe(bar_full, full_par, P.spin_limit)) {
-                            seq_report(P.status, 74, mi);
-                            *abort_flag = 1;
-                            ok = false;
-                            break;
+                        {
+                            SEQ_PROF_T0();
+                            if (!seq_mbar_probe(bar_full, full_par, P.spin_limit)) {
+                                seq_report(P.status, 74, mi);
+                                *abort_flag = 1;
+                                ok = false;
+                                break;
+                            }
+                            SEQ_PROF_ADD(2);
                         }
                         if (left >= S) {
 #pragma unroll
@@ -429,7 +453,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                         acc = 1;
                         x_lo += xslot16 * S;
                         tc_commit(bar_empty);  // the stage is reusable once these retire
-                        if (P.trace && P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 7] == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 7] = globaltimer_ns();
+                        if (SEQ_STAMPS && P.trace && P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 7] == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 7] = globaltimer_ns();
                         ++mi;
                         item16 += stage16, sfa += 4u * S, bar_full += 8, bar_empty += 8;
                         if (item16 == ring_end16) {
@@ -441,13 +465,19 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                     tc_commit(sbase + SeqSmem::kBarDFull + 8 * (nseg & 1));
                     ++nseg;
                 }
-                if (P.trace) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 4] = globaltimer_ns();
+                if (SEQ_STAMPS && P.trace) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 4] = globaltimer_ns();
                 // Barrier phases are told apart by one parity bit, so nobody may complete a barrier twice
                 // before every waiter has seen the first completion: the planes of job j + 2 are only made
                 // once this thread (here) and the epilogue group are through with job j.
                 if (ok) mbar_arrive(sbase + SeqSmem::kBarMDone + 8 * pb);
                 job = next;
             }
+#ifdef QGEMV_SEQ_PROFILE
+            if (P.trace) {   // per CTA: cycles waiting for planes, accumulators, weight stages; total
+                prof[3] = clock64() - prof_start;
+                for (int z = 0; z < 4; ++z) P.trace[size_t(gridDim.x) * P.n_jobs * 8 + size_t(cta) * 4 + z] = (unsigned long long)prof[z];
+            }
+#endif
             *n_consumed = mi;
         }
         __syncwarp();
