@@ -7,7 +7,7 @@
 // SM walks the whole job list.  The producer thread never stops at a job boundary: while the CTA's
 // other warps finish job j and convert the activations of job j+1, it already streams the items of
 // job j+1, j+2, ... into a ring that takes most of the SM's shared memory, so HBM stays busy across
-// the boundary and the MMAs of the next job find their first ~190 KB per SM waiting.
+// the boundary and the MMAs of the next job find their first 130-190 KB per SM waiting.
 //
 // Per job the arithmetic is gemv_tc.cuh's: weights consumed as stored by tcgen05.mma
 // kind::mxf4nvf4, activations as eight E2M1 digit planes scaled per CTA range, split along K over

@@ -175,8 +175,9 @@ int qgemv_weight_read(qgemv_handle* h, const qgemv_weight* w, void* host_out, si
  * count").  As there, row b of the result does not depend on B, and the split along K is fixed
  * by the shape and the CTA count, never by timing ("column invariant with a deterministic split
  * along K", tools/fixtures/engines/crit-labs/mtp-adaptive-width/card.yaml:77).  Exception: where
- * K * B exceeds 32768 elements the call is split along K in chunks whose length depends on B, and
- * a row then matches other batch sizes to fp32 rounding only.  B = 9..16 (the output head at batch
+ * ceil(K / 1024) * B exceeds 32 (lane-ordered weights) or the digit planes of B * K activations leave no
+ * room for a weight ring in shared memory (tensor-core layout), the call is split along K in chunks whose
+ * length depends on B, and a row then matches other batch sizes to fp32 rounding only.  B = 9..16 (the output head at batch
  * 16, engines/crit-labs/mtp5-nvfp4-drafts/card.yaml:77) streams the matrix twice: rows 0..7, then
  * the rest. */
 int qgemv_gemv(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, int B, void* y,
