@@ -727,9 +727,15 @@ int qgemv_sequence_create(qgemv_handle* h, const qgemv_job* jobs, int n_jobs, in
     const int si = h->cfg.tc_stage_items;
     q->stage_items = si >= 8 ? 8 : (si >= 4 ? 4 : (si >= 2 ? 2 : 4));
     const int cap = (h->cfg.tc_smem_kb > 0 ? std::min(h->cfg.tc_smem_kb, 227) : 227) * 1024;
-    // as many plane buffers (jobs the conversion may run ahead) as still leave a ring of four stages
+    // As many plane buffers (jobs the conversion may run ahead) as still leave a ring of four stages.  A list in
+    // which most jobs wait for the one before them cannot run ahead: there one buffer is enough and the shared
+    // memory goes to the weight ring, which keeps HBM busy while a job waits for its input.
+    int n_chain = 0;
+    for (int i = 1; i < n_jobs; ++i)
+        if (tab[size_t(i)].src_job == i - 1 || tab[size_t(i)].dep == i - 1) ++n_chain;
+    const int nbuf_max = 2 * n_chain > n_jobs ? 1 : qg::kSeqPlaneBufsMax;
     int ring = 0;
-    for (q->nbuf = qg::kSeqPlaneBufsMax; q->nbuf >= 1; --q->nbuf) {
+    for (q->nbuf = nbuf_max; q->nbuf >= 1; --q->nbuf) {
         const int base = qg::SeqSmem::ring_off(q->x_slots, q->npad, q->nbuf);
         ring = (cap - base) / (q->stage_items * qg::kTcItemBytes);
         ring = std::min({ring, qg::kTcMaxRing, qg::SeqSmem::max_ring_items(q->npad) / q->stage_items});
