@@ -597,6 +597,8 @@ def run_moe(args, T=None):
     dev = torch.device("cuda", 0)
     E, topk, hidden, inter, L = 128, 8, 2048, 768, 4
     T = T or (args.tokens if args.tokens <= 512 and args.tokens != 256 else 8)
+    tc = getattr(args, "moe_layout", "tc") == "tc"   # tensor-core layout: the expert list runs on the sequence kernel
+    fmt = qg.FMT_NVFP4_TC if tc else qg.FMT_NVFP4
     h = qg.QGemv(device=0, use_pdl=True)
     host0 = {}
 
@@ -606,7 +608,7 @@ def run_moe(args, T=None):
             c, s = synth_nvfp4(N, K, seed0 + e, dev)
             if keep is not None:
                 host0.setdefault(keep, []).append((c, s))
-            blobs.append(qg.pack(qg.FMT_NVFP4, c, s, 1.0))
+            blobs.append(qg.pack(fmt, c, s, 1.0))
         return np.stack(blobs)
 
     gu = [h.load_stacked(stacked(2 * inter, hidden, 1000 * l, "gu" if l == 0 else None)) for l in range(L)]
@@ -679,7 +681,7 @@ def run_moe(args, T=None):
         "warmup": warmup, "ms_per_step": round(ms / args.steps, 5), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16 (fp32 accumulate)", "data": "synthetic",
         "config": {"workload": f"MoE grouped GEMV: {E} experts, top-{topk}, hidden {hidden}, expert width {inter}, NVFP4, "
-                               f"{T} tokens, {L} layers (gate/up + down) in one CUDA graph",
+                               f"{T} tokens, {L} layers (gate/up + down) in one CUDA graph, {'tensor-core' if tc else 'lane-order'} layout",
                    "tokens": T, "distinct_experts": distinct, "touched_weight_bytes_per_step": nbytes,
                    "us_per_layer": round(ms * 1e3 / args.steps / L, 2),
                    "cache": "four layers of distinct experts; at 1 token the touched experts (21 MB per layer) fit L2"},
@@ -687,7 +689,7 @@ def run_moe(args, T=None):
                      "traffic": int(1.01 * (nbytes // (2 * L))),
                      "traffic_source": "ncu capture at 8 tokens (profiles/moe_stream_128experts_t8_traffic.md): DRAM read+write = "
                                        "1.004-1.027 x the touched experts' bytes per launch; scaled by bytes",
-                     "peak_kind": kind, "kernel": "moe_stream_kernel<NVFP4>",
+                     "peak_kind": kind, "kernel": "gemv_seq_kernel<4, expert list>" if tc else "moe_stream_kernel<NVFP4>",
                      "bytes_per_launch": nbytes // (2 * L), "us_per_launch": round(ms * 1e3 / (2 * L * args.steps), 2)},
         "e2e": {"value": round(nbytes * args.steps / (ms_host * 1e-3) / 1e9, 2), "unit": UNIT,
                 "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 4,
@@ -728,6 +730,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true", help="N = 1: skip the secondary workloads")
     ap.add_argument("--no-tp1", action="store_true", help="N > 1: do not time the unsharded stack on rank 0")
+    ap.add_argument("--moe-layout", default="tc", choices=["tc", "lane"],
+                    help="MoE workload: tc = experts in the tensor-core layout (sequence kernel), lane = lane order (mma.sync streaming kernel)")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "prefill_a4", "lmhead", "moe"],
                     help="decode: the headline GEMV layer stack; prefill: the skinny GEMM over one 70B-shaped layer; "
                          "lmhead: the FP8 output head; moe: the grouped expert GEMV (--tokens 1/8/64)")

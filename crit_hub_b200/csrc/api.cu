@@ -412,12 +412,13 @@ int qgemv_init(const qgemv_config* cfg, qgemv_handle** out) {
         cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_NVFP4, false, 1, true>, dyn, qg::SSmem::total<QGEMV_FMT_NVFP4>()) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8, true, 1, true>, dyn, qg::SSmem::total<QGEMV_FMT_FP8>()) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_stream_wp_kernel<QGEMV_FMT_FP8, false, 1, true>, dyn, qg::SSmem::total<QGEMV_FMT_FP8>()) != cudaSuccess ||
-        cudaFuncSetAttribute(qg::gemv_seq_kernel<2, false>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
-        cudaFuncSetAttribute(qg::gemv_seq_kernel<4, false>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
-        cudaFuncSetAttribute(qg::gemv_seq_kernel<8, false>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
-        cudaFuncSetAttribute(qg::gemv_seq_kernel<2, true>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
-        cudaFuncSetAttribute(qg::gemv_seq_kernel<4, true>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
-        cudaFuncSetAttribute(qg::gemv_seq_kernel<8, true>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_seq_kernel<2, qg::kSeqPlain>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_seq_kernel<4, qg::kSeqPlain>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_seq_kernel<8, qg::kSeqPlain>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_seq_kernel<2, qg::kSeqFuse>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_seq_kernel<4, qg::kSeqFuse>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_seq_kernel<8, qg::kSeqFuse>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
+        cudaFuncSetAttribute(qg::gemv_seq_kernel<4, qg::kSeqMoe>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_tc_kernel<1>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_tc_kernel<2>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
         cudaFuncSetAttribute(qg::gemv_tc_kernel<4>, dyn, qg::kGsSmemBudget) != cudaSuccess ||
@@ -466,8 +467,7 @@ int new_weight(qgemv_handle* h, const qg_blob_header* h0, int n_stacked, size_t 
                qgemv_weight** out) {
     if (h0->N > INT32_MAX || h0->K > INT32_MAX || h0->n_panels * h0->units_per_panel > (int64_t(1) << 40))
         return QGEMV_ERR_UNSUPPORTED_SHAPE;
-    if (h0->fmt == QGEMV_FMT_NVFP4_TC &&
-        (n_stacked != 1 || h0->n_panels / 8 * h0->units_per_panel > INT32_MAX))
+    if (h0->fmt == QGEMV_FMT_NVFP4_TC && h0->n_panels / 8 * h0->units_per_panel > INT32_MAX)
         return QGEMV_ERR_UNSUPPORTED_SHAPE;
     QG_CUDA(cudaSetDevice(h->cfg.device));
     qgemv_weight* w = new (std::nothrow) qgemv_weight;
@@ -808,13 +808,13 @@ int qgemv_sequence_run(qgemv_handle* h, const qgemv_sequence* q, void* stream) {
     g_launch_cooperative = true;
     cudaError_t err;
     if (q->fused) {
-        err = q->stage_items == 2   ? launch(h, qg::gemv_seq_kernel<2, true>, g, blk, q->smem, st, P)
-              : q->stage_items == 4 ? launch(h, qg::gemv_seq_kernel<4, true>, g, blk, q->smem, st, P)
-                                    : launch(h, qg::gemv_seq_kernel<8, true>, g, blk, q->smem, st, P);
+        err = q->stage_items == 2   ? launch(h, qg::gemv_seq_kernel<2, qg::kSeqFuse>, g, blk, q->smem, st, P)
+              : q->stage_items == 4 ? launch(h, qg::gemv_seq_kernel<4, qg::kSeqFuse>, g, blk, q->smem, st, P)
+                                    : launch(h, qg::gemv_seq_kernel<8, qg::kSeqFuse>, g, blk, q->smem, st, P);
     } else {
-        err = q->stage_items == 2   ? launch(h, qg::gemv_seq_kernel<2, false>, g, blk, q->smem, st, P)
-              : q->stage_items == 4 ? launch(h, qg::gemv_seq_kernel<4, false>, g, blk, q->smem, st, P)
-                                    : launch(h, qg::gemv_seq_kernel<8, false>, g, blk, q->smem, st, P);
+        err = q->stage_items == 2   ? launch(h, qg::gemv_seq_kernel<2, qg::kSeqPlain>, g, blk, q->smem, st, P)
+              : q->stage_items == 4 ? launch(h, qg::gemv_seq_kernel<4, qg::kSeqPlain>, g, blk, q->smem, st, P)
+                                    : launch(h, qg::gemv_seq_kernel<8, qg::kSeqPlain>, g, blk, q->smem, st, P);
     }
     return err == cudaSuccess ? QGEMV_OK : QGEMV_ERR_CUDA;
 }
@@ -1099,6 +1099,59 @@ int qgemv_gemm_skinny(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16
     return err == cudaSuccess ? QGEMV_OK : QGEMV_ERR_CUDA;
 }
 
+namespace {
+// The experts of a router table on the tensor-core layout: the sequence kernel in its expert-list mode, one
+// cooperative launch after the router walk.  Problems hold at most B activation rows.
+int moe_tc(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, void* out, int out_dtype, int B, cudaStream_t s) {
+    const int grid = gemv_grid(h);
+    if (grid > h->sm_count) return QGEMV_ERR_UNSUPPORTED_SHAPE;  // the CTAs wait on one another: one per SM at most
+    qg::SeqParams P;
+    std::memset(&P, 0, sizeof P);
+    qg::SeqJob& mj = P.moe_job;
+    mj.payload = w->dev_blob + QG_HEADER_BYTES + w->aux_bytes;
+    mj.x = static_cast<const uint16_t*>(x_bf16);
+    mj.y = out;
+    mj.tensor_scale = 1.0f;
+    mj.N = int32_t(w->N), mj.K = int32_t(w->K);
+    mj.tiles = int32_t(w->n_panels / 8), mj.kt = int32_t(w->units);
+    mj.x_stride = int32_t(w->K);
+    mj.y_dtype = out_dtype;
+    mj.dep = -1, mj.xoff = -1, mj.pub_off = -1, mj.src_off = -1, mj.src_job = -1;
+    const int64_t per = int64_t(mj.tiles) * mj.kt;
+    if ((int64_t(w->max_prob) * per + 1) * grid >= (int64_t(1) << 32)) return QGEMV_ERR_UNSUPPORTED_SHAPE;  // 32-bit split arithmetic
+    P.ws = h->seq_parts;
+    P.barrier = h->seq_barrier;
+    P.fin = reinterpret_cast<unsigned int*>(w->counters);  // [0]: launches with this weight (nothing else of a job list's counters is used)
+    P.status = h->status_dev;
+    P.spin_limit = default_spin(h);
+    P.n_jobs = 0;
+    P.B = B;
+    P.npad = (8 * B + 15) / 16 * 16;
+    P.x_slots = mj.kt;   // a CTA's share of an expert may span a whole row tile
+    P.debug = h->cfg.debug;
+    P.world = 1;
+    P.prob = w->prob;
+    P.expert_ts = w->dev_tensor_scale;
+    P.expert_stride = w->blob_bytes;
+    constexpr int kStage = 4;
+    const int cap = (h->cfg.tc_smem_kb > 0 ? std::min(h->cfg.tc_smem_kb, 227) : 227) * 1024;
+    // two plane buffers (a CTA's range mostly touches two experts) when that leaves a ring of four stages
+    int ring = 0;
+    for (P.nbuf = 2; P.nbuf >= 1; --P.nbuf) {
+        const int base = qg::SeqSmem::ring_off(P.x_slots, P.npad, P.nbuf);
+        ring = (cap - base) / (kStage * qg::kTcItemBytes);
+        ring = std::min({ring, qg::kTcMaxRing, qg::SeqSmem::max_ring_items(P.npad) / kStage});
+        if (ring >= 4 || P.nbuf == 1) break;
+    }
+    if (ring < 2) return QGEMV_ERR_UNSUPPORTED_SHAPE;  // K too long for the digit planes of one expert beside a ring
+    P.ring = ring;
+    const size_t smem = size_t(qg::SeqSmem::total(P.x_slots, P.npad, P.nbuf, ring, kStage));
+    g_launch_cooperative = true;
+    const cudaError_t err = launch(h, qg::gemv_seq_kernel<kStage, qg::kSeqMoe>, dim3(unsigned(grid)), dim3(qg::kSeqThreads), smem, s, P);
+    return err == cudaSuccess ? QGEMV_OK : QGEMV_ERR_CUDA;
+}
+}  // namespace
+
 int qgemv_moe_gemv(qgemv_handle* h, const qgemv_weight* experts, const int32_t* expert_ids,
                    const void* x_bf16, int T, int topk, int per_slot_input, void* out,
                    int out_dtype, void* stream) {
@@ -1109,10 +1162,15 @@ int qgemv_moe_gemv(qgemv_handle* h, const qgemv_weight* experts, const int32_t* 
     if ((reinterpret_cast<uintptr_t>(x_bf16) & 15u) != 0) return QGEMV_ERR_INVALID_ARG;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int threads = 1024;
+    // rows per problem: eight; on the tensor-core layout no more than there are tokens (the digit planes and
+    // the accumulator are sized for the largest problem)
+    const bool tc = experts->fmt == QGEMV_FMT_NVFP4_TC;
+    const int cap = tc ? std::min(QGEMV_MAX_BATCH, T) : 8;
     cudaError_t err = launch(h, qg::moe_prep_kernel, dim3(1), dim3(threads),
                              size_t(experts->n_stack) * 12 + size_t(T) * topk * 4 + 16, s, expert_ids, T, topk, experts->n_stack,
-                             per_slot_input, experts->max_prob, experts->prob, h->status_dev);
+                             per_slot_input, experts->max_prob, cap, experts->prob, h->status_dev);
     if (err != cudaSuccess) return QGEMV_ERR_CUDA;
+    if (tc) return moe_tc(h, experts, x_bf16, out, out_dtype, cap, s);
     qg::GemvParams P = base_params(h, experts);
     P.x = static_cast<const uint16_t*>(x_bf16);
     P.y = out;

@@ -66,7 +66,9 @@ struct SeqJob {               // 80 bytes, device memory
     float norm_eps;
     const uint16_t* norm_w;   // bf16 [K] or null: x'[k] = bf16(x[k] * norm_w[k]); y is scaled by rsqrt(mean(x^2) + eps)
     const void* residual;     // [B][N] in y's dtype or null: added to the result before it is rounded
-    int64_t pad[2];
+    const int32_t* rowmap;    // expert list only: [16] row of x for each of the job's activation rows, then row of y
+    int32_t rows;             // expert list only: activation rows of this job (<= B)
+    int32_t pad;
 };
 static_assert(sizeof(SeqJob) == 112, "SeqJob layout");
 
@@ -91,6 +93,13 @@ struct SeqParams {
     uint8_t* xbuf[kTpMaxWorld];
     int64_t x_max_elems;
     int32_t rank, world;
+    // expert list (MODE 2): the jobs are the problems of a router table, made on the device just before the launch
+    // (prob[0] = count, then kProbInts ints per problem: expert, rows, row of x [8], row of y [8]); every job is
+    // moe_job with the expert's payload and tensor scale
+    const int32_t* prob;
+    const float* expert_ts;
+    uint64_t expert_stride;
+    SeqJob moe_job;
 };
 
 struct SeqSmem {
@@ -106,6 +115,8 @@ struct SeqSmem {
     static constexpr int kBarDrain = 304;
     static constexpr int kTmemPtr = 312;
     static constexpr int kAbort = 316;
+    static constexpr int kRowMap0 = 320;    // expert list: rows of x [8] and of y [8] of the job in plane buffer 0 ...
+    static constexpr int kRowMap1 = 960;    // ... and 1 (that mode has two plane buffers at most)
     static constexpr int kWarpMax = 384;    // kTcConvWarps x 8 words: the same per converting warp
     static constexpr int kIssued = 640;
     static constexpr int kConsumed = 644;
@@ -173,6 +184,23 @@ __device__ __forceinline__ SeqJob seq_load_job(const SeqJob* j) {
     u.q[5] = __ldg(p + 5), u.q[6] = __ldg(p + 6);
     return u.job;
 }
+// MODE of the kernel: a plain job list; one with fused activation transforms; the experts of a router table.
+constexpr int kSeqPlain = 0, kSeqFuse = 1, kSeqMoe = 2;
+template <int MODE>
+__device__ __forceinline__ SeqJob seq_job_at(const SeqParams& P, int j) {
+    if constexpr (MODE == kSeqMoe) {
+        SeqJob job = P.moe_job;
+        const int32_t* pr = P.prob + 1 + j * kProbInts;   // written by the kernel before this one: read through L2
+        const int e = __ldcg(pr);
+        job.payload += uint64_t(e) * P.expert_stride;
+        job.tensor_scale = __ldg(P.expert_ts + e);
+        job.rows = __ldcg(pr + 1);
+        job.rowmap = pr + 2;
+        return job;
+    } else {
+        return seq_load_job(P.jobs + j);
+    }
+}
 // A job is split over min(grid, items) CTAs, exactly as a launch of its own would be; the other CTAs
 // only take part in the job's barriers.  Range [begin, end) of CTA `cta` in the job's linear
 // (tile, item) space; empty for a CTA beyond the job's share.
@@ -194,11 +222,6 @@ __device__ __forceinline__ int32_t seq_cta_of(int32_t idx, int32_t total, int gj
 __device__ __forceinline__ int32_t seq_slot(int32_t c, int32_t tile, int32_t units, int32_t total, int gj) {
     const uint32_t a = (uint32_t(c) * uint32_t(total)) / uint32_t(gj);
     return 2 * c + (int32_t(a / uint32_t(units)) == tile ? 0 : 1);
-}
-// segment walker of CTA `cta` for a job (no segments for a CTA beyond the job's share)
-__device__ __forceinline__ void seq_walker(GsWalker& wk, int32_t total, int32_t kt, int cta, int gj) {
-    wk.units = kt;
-    seq_range(total, cta, gj, wk.pos, wk.end);
 }
 
 // The waits' slow paths out of line as well: a wait that finds its barrier complete costs a probe.
@@ -263,10 +286,12 @@ __device__ __forceinline__ float seq_sumsq(uint4 x) {
 
 constexpr int kSeqThreads = 32 * (2 + 12);  // producer, MMA issuer, three groups of four warps
 
-// FUSE: the job list holds jobs with an activation function, a norm or a residual; the plain instantiation
-// carries none of that code.
-template <int S, bool FUSE>
+// MODE kSeqFuse: the job list holds jobs with an activation function, a norm or a residual; the plain
+// instantiation carries none of that code.  MODE kSeqMoe: the jobs are the problems of a router table (one
+// expert's matrix times up to eight gathered activation rows, results scattered to the slots' rows).
+template <int S, int MODE>
 __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParams P) {
+    constexpr bool FUSE = MODE == kSeqFuse, MOE = MODE == kSeqMoe;
     extern __shared__ __align__(128) unsigned char sq_smem[];
     const uint32_t sbase = smem_u32(sq_smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -318,6 +343,53 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
     const uint32_t tmem_sfb = tmem_base + 2u * uint32_t(npad);
     const uint32_t tmem_sfa0 = tmem_sfb + 4u;
 
+    // How a job's items are dealt to the CTAs.  A job of a list is split over min(grid, items) CTAs, as a launch
+    // of its own would be, and every CTA goes through every job.  The experts of a router table are ONE split
+    // space instead -- the problems' items laid end to end and dealt evenly -- so a CTA works on the one to three
+    // experts its range touches, goes through those jobs only, and hands over at most two split row tiles.
+    int j_lo = 0, j_hi = P.n_jobs;
+    int32_t g_total = 0, g_begin = 0, g_end = 0, g_per = 1;
+    int g_gj = grid;
+    if constexpr (MOE) {
+        pdl_wait();  // the problem table is the work of the kernel before this one
+        g_per = P.moe_job.tiles * P.moe_job.kt;
+        g_total = __ldcg(P.prob) * g_per;
+        g_gj = seq_job_grid(g_total, grid);
+        seq_range(g_total, cta, g_gj, g_begin, g_end);
+        j_lo = g_begin / g_per;
+        j_hi = g_end > g_begin ? (g_end - 1) / g_per + 1 : j_lo;
+    }
+    // this CTA's range [rb, re) of job j, in the job's own (tile, item) space
+    auto job_range = [&](const SeqJob& job, int j, int32_t& rb, int32_t& re) {
+        if constexpr (MOE) {
+            const int32_t base = j * g_per;
+            rb = min(max(g_begin - base, 0), g_per), re = min(max(g_end - base, 0), g_per);
+        } else {
+            const int32_t total = job.tiles * job.kt;
+            seq_range(total, cta, seq_job_grid(total, grid), rb, re);
+        }
+    };
+    // the CTA that holds item idx of job j; the parts slot of CTA c for row tile `tile` of job j
+    auto job_cta_of = [&](const SeqJob& job, int j, int32_t idx) -> int32_t {
+        if constexpr (MOE) {
+            return seq_cta_of(j * g_per + idx, g_total, g_gj);
+        } else {
+            const int32_t total = job.tiles * job.kt;
+            return seq_cta_of(idx, total, seq_job_grid(total, grid));
+        }
+    };
+    auto job_slot = [&](const SeqJob& job, int j, int32_t c, int32_t tile) -> int32_t {
+        if constexpr (MOE) {
+            return seq_slot(c, j * job.tiles + tile, job.kt, g_total, g_gj);
+        } else {
+            const int32_t total = job.tiles * job.kt;
+            return seq_slot(c, tile, job.kt, total, seq_job_grid(total, grid));
+        }
+    };
+    // the parts buffer of job j: the jobs of a list take eight in turn; a router table's CTAs each hand over at
+    // most two split tiles in the whole launch, so one buffer serves
+    auto job_parts = [&](int j) -> size_t { return MOE ? size_t(0) : size_t(j & (kSeqPartBufs - 1)); };
+
     if (warp == kTcWarpProd) {
         // ================= packed-weight producer: runs through the whole job list =================
         if (lane == 0) {
@@ -326,12 +398,14 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
             int s = 0, issued = 0;
             uint32_t use = 0;
             bool ok = true;
-            SeqJob job = seq_load_job(P.jobs);
-            for (int j = 0; j < P.n_jobs && ok; ++j) {
+            SeqJob job = P.moe_job;
+            if (j_lo < j_hi) job = seq_job_at<MODE>(P, j_lo);
+            for (int j = j_lo; j < j_hi && ok; ++j) {
                 SeqJob next = job;
-                if (j + 1 < P.n_jobs) next = seq_load_job(P.jobs + j + 1);  // in flight while this job streams
+                if (j + 1 < j_hi) next = seq_job_at<MODE>(P, j + 1);  // in flight while this job streams
                 GsWalker wk;
-                seq_walker(wk, job.tiles * job.kt, job.kt, cta, seq_job_grid(job.tiles * job.kt, grid));
+                wk.units = job.kt;
+                job_range(job, j, wk.pos, wk.end);
                 GsSeg sg;
                 while (ok && wk.next(sg)) {
                     const uint8_t* src = job.payload + (uint64_t(sg.tile) * job.kt + uint64_t(sg.u0)) * kTcItemBytes;
@@ -376,12 +450,13 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
             long long prof[4] = {0, 0, 0, 0};
             const long long prof_start = clock64();
 #endif
-            SeqJob job = seq_load_job(P.jobs);
+            SeqJob job = P.moe_job;
+            if (j_lo < j_hi) job = seq_job_at<MODE>(P, j_lo);
             int pb = 0;        // plane buffer of job j: j % nbuf, kept as a counter (no division in this thread)
             uint32_t pph = 0;  // parity of that buffer's use: (j / nbuf) & 1
-            for (int j = 0; j < P.n_jobs && ok; ++j, pph ^= (pb + 1 == nb) ? 1u : 0u, pb = (pb + 1 == nb) ? 0 : pb + 1) {
+            for (int j = j_lo; j < j_hi && ok; ++j, pph ^= (pb + 1 == nb) ? 1u : 0u, pb = (pb + 1 == nb) ? 0 : pb + 1) {
                 SeqJob next = job;
-                if (j + 1 < P.n_jobs) next = seq_load_job(P.jobs + j + 1);
+                if (j + 1 < j_hi) next = seq_job_at<MODE>(P, j + 1);
                 const int32_t kt_len = job.kt;
                 // the digit planes of this job (every CTA signals, also one without items)
                 SEQ_PROF_T0();
@@ -403,7 +478,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 wk.units = kt_len, wk.pos = r_begin, wk.end = r_end;
                 GsSeg sg;
                 bool have = wk.next(sg);
-                if (j == 0) tc_cp_sf2(tmem_sfb, sf_lo | (((sbase + SeqSmem::kSfb) >> 4) & 0x3FFFu), sf_hi);
+                if (j == j_lo) tc_cp_sf2(tmem_sfb, sf_lo | (((sbase + SeqSmem::kSfb) >> 4) & 0x3FFFu), sf_hi);
                 for (; ok && have; have = wk.next(sg)) {
                     // the accumulator is free once the epilogue of the segment before last has read it
                     {
@@ -545,14 +620,15 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 const uint32_t byte = n < 8 * Bl ? uint32_t(2 * jj + 1) << 3 : 0u;
                 *reinterpret_cast<volatile uint32_t*>(sq_smem + SeqSmem::kSfb + (n & 31) * 16 + (n >> 5) * 4) = byte * 0x01010101u;
             }
-            SeqJob job = seq_load_job(P.jobs);
+            SeqJob job = P.moe_job;
+            if (j_lo < j_hi) job = seq_job_at<MODE>(P, j_lo);
             int pb = 0;        // plane buffer of job j (j % nbuf) and the parity of its use ((j / nbuf) & 1), as counters
             uint32_t pph = 0;
-            for (int j = 0; j < P.n_jobs; ++j, pph ^= (pb + 1 == nb) ? 1u : 0u, pb = (pb + 1 == nb) ? 0 : pb + 1) {
+            for (int j = j_lo; j < j_hi; ++j, pph ^= (pb + 1 == nb) ? 1u : 0u, pb = (pb + 1 == nb) ? 0 : pb + 1) {
                 SeqJob next = job;
-                if (j + 1 < P.n_jobs) next = seq_load_job(P.jobs + j + 1);
+                if (j + 1 < j_hi) next = seq_job_at<MODE>(P, j + 1);
                 // the plane buffer and its row maxima were last used by job j - nbuf: its epilogues must be through
-                if (j >= nb && gt == 0 &&
+                if (j - j_lo >= nb && gt == 0 &&
                     !seq_mbar_wait(sbase + SeqSmem::kBarEDone + 8 * pb, (pph ^ 1u), P.spin_limit)) {
                     seq_report(P.status, 78, j);
                     *abort_flag = 1;
@@ -561,9 +637,9 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 if (!group_alive()) break;
                 if (P.trace && gt == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 0] = globaltimer_ns();
                 const int32_t kt_len = job.kt;
-                const int32_t total = job.tiles * kt_len;
+                const int Bj = MOE ? job.rows : Bl;  // activation rows of this job
                 int32_t r_begin, r_end;
-                seq_range(total, cta, seq_job_grid(total, grid), r_begin, r_end);
+                job_range(job, j, r_begin, r_end);
                 const int32_t n_items = r_end - r_begin;
                 const int32_t xs0 = n_items >= kt_len ? 0 : r_begin % kt_len;
                 const int32_t n_slots = n_items >= kt_len ? kt_len : n_items;
@@ -573,8 +649,12 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                     rg[0] = r_begin, rg[1] = r_end;
                 }
                 if (gt < 32) all_max[gt] = 0u;
+                volatile int* rowmap_s = reinterpret_cast<volatile int*>(sq_smem + (pb ? SeqSmem::kRowMap1 : SeqSmem::kRowMap0));
+                if constexpr (MOE) {
+                    if (gt >= 32 && gt < 48) rowmap_s[gt - 32] = __ldcg(job.rowmap + (gt - 32));
+                }
                 named_bar_sync(bar_id, 128);
-                const int n_work = n_slots * Bl * 8;
+                const int n_work = n_slots * Bj * 8;
                 constexpr int kKeep = 4;
                 const bool from_pub = job.src_off >= 0;
                 const uint32_t want = seq_pub_tag(run_no, job.src_job) << 16;
@@ -619,7 +699,8 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                         return pub_wait(p, ld_pub4(p), ld_pub4(p + 4));
                     }
                     // possibly written by other SMs during an earlier job: read through L2, never a stale L1 line
-                    return __ldcg(reinterpret_cast<const uint4*>(job.x + int64_t(b) * job.x_stride + k0));
+                    const int64_t xr = MOE ? int64_t(rowmap_s[b]) : int64_t(b);  // gathered rows
+                    return __ldcg(reinterpret_cast<const uint4*>(job.x + xr * job.x_stride + k0));
                 };
                 // ... and what the GEMV multiplies: the activation function and the norm weight applied (FUSE)
                 auto shaped8 = [&](int b, int k0, uint4 v) -> uint4 {
@@ -736,24 +817,38 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                     const uint32_t m = unit_max(keep[i]);
                     if (m) atomicMax(wmax + kb[i], m);
                 }
+                // The units beyond the kept ones (batches of several rows) are read twice, for the row maxima and
+                // for the planes, four loads in flight at a time; both passes run the same code.
 #pragma unroll 1
-                for (int wu = gt + kKeep * 128; wu < n_work; wu += 128) {
-                    int b;
-                    uint32_t dst;
-                    const uint32_t m = unit_max(unit_src(wu, b, dst));
-                    if (m) atomicMax(wmax + b, m);
-                }
-                named_bar_sync(bar_id, 128);
-                if (gt < 8) rowmax2[pb * 8 + gt] = row_max(gt);
+                for (int pass = 0; pass < 2; ++pass) {
+                    if (pass == 1) {
+                        named_bar_sync(bar_id, 128);
+                        if (gt < 8) rowmax2[pb * 8 + gt] = row_max(gt);
 #pragma unroll
-                for (int i = 0; i < kKeep; ++i)
-                    if (gt + i * 128 < n_work) store_unit(kb[i], kdst[i], keep[i]);
+                        for (int i = 0; i < kKeep; ++i)
+                            if (gt + i * 128 < n_work) store_unit(kb[i], kdst[i], keep[i]);
+                    }
 #pragma unroll 1
-                for (int wu = gt + kKeep * 128; wu < n_work; wu += 128) {
-                    int b;
-                    uint32_t dst;
-                    const uint4 v = unit_src(wu, b, dst);
-                    store_unit(b, dst, v);
+                    for (int wu0 = gt + kKeep * 128; wu0 < n_work; wu0 += 4 * 128) {
+                        uint4 v[4];
+                        int vb[4];
+                        uint32_t vdst[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            vb[i] = 0, vdst[i] = 0;
+                            v[i] = make_uint4(0, 0, 0, 0);
+                            if (wu0 + i * 128 < n_work) v[i] = unit_src(wu0 + i * 128, vb[i], vdst[i]);
+                        }
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            if (pass == 0) {
+                                const uint32_t m = unit_max(v[i]);
+                                if (m) atomicMax(wmax + vb[i], m);
+                            } else if (wu0 + i * 128 < n_work) {
+                                store_unit(vb[i], vdst[i], v[i]);
+                            }
+                        }
+                    }
                 }
                 fence_proxy_async_smem();  // the planes are read by the tensor core (async proxy)
                 named_bar_sync(bar_id, 128);
@@ -768,15 +863,15 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
             const uint32_t lane_base = uint32_t(32 * q) << 16;
             const int row = 32 * q + lane;
             uint32_t nseg = 0;
-            SeqJob job = seq_load_job(P.jobs);
+            SeqJob job = P.moe_job;
+            if (j_lo < j_hi) job = seq_job_at<MODE>(P, j_lo);
             int pb = 0;
             uint32_t pph = 0;
-            for (int j = 0; j < P.n_jobs; ++j, pph ^= (pb + 1 == nb) ? 1u : 0u, pb = (pb + 1 == nb) ? 0 : pb + 1) {
+            for (int j = j_lo; j < j_hi; ++j, pph ^= (pb + 1 == nb) ? 1u : 0u, pb = (pb + 1 == nb) ? 0 : pb + 1) {
                 SeqJob next = job;
-                if (j + 1 < P.n_jobs) next = seq_load_job(P.jobs + j + 1);
+                if (j + 1 < j_hi) next = seq_job_at<MODE>(P, j + 1);
                 const int32_t kt_len = job.kt;
-                const int32_t total = job.tiles * kt_len;
-                const int gj = seq_job_grid(total, grid);
+                const int Bj = MOE ? job.rows : Bl;
                 // the planes of this job are ready, and with them this CTA's item range (a CTA without items
                 // in a run of jobs would otherwise race ahead of the PLANES group and complete its barrier
                 // twice before that group has looked)
@@ -788,7 +883,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 const int32_t rb = rg[0], re = rg[1];
                 // A split tile's parts go to buffer j % kSeqPartBufs, last used by job j - kSeqPartBufs: every
                 // CTA must have added that job's tiles up (the FINISH group publishes how far that has come)
-                if (re > rb && (rb % kt_len != 0 || re % kt_len != 0) && j >= kSeqPartBufs && gt == 0) {
+                if (!MOE && re > rb && (rb % kt_len != 0 || re % kt_len != 0) && j >= kSeqPartBufs && gt == 0) {
                     uint64_t t0 = 0;
                     for (int64_t it = 0; *fin_all < j - kSeqPartBufs; ++it) {
                         // (asked directly: this CTA's FINISH group may itself be waiting for the part written below)
@@ -823,13 +918,13 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                     // pair); the first one's range may have started in an earlier tile
                     unsigned long long* slot = nullptr;
                     if (!whole) {
-                        const int32_t c_lo = seq_cta_of(sg.tile * kt_len, total, gj);
-                        const int32_t my_slot = cta == c_lo ? seq_slot(c_lo, sg.tile, kt_len, total, gj) : 2 * cta;
-                        slot = P.ws + (size_t(j & (kSeqPartBufs - 1)) * size_t(2 * grid) + size_t(my_slot)) * 1024 + row;
+                        const int32_t c_lo = job_cta_of(job, j, sg.tile * kt_len);
+                        const int32_t my_slot = cta == c_lo ? job_slot(job, j, c_lo, sg.tile) : 2 * cta;
+                        slot = P.ws + (job_parts(j) * size_t(2 * grid) + size_t(my_slot)) * 1024 + row;
                     }
                     // (one row of the batch after the other, not unrolled: the code of this group has to stay small)
 #pragma unroll 1
-                    for (int b = 0; b < Bl; ++b) {
+                    for (int b = 0; b < Bj; ++b) {
                         uint32_t r[8];
                         tmem_ld8(tmem_base + lane_base + acc * uint32_t(npad) + uint32_t(8 * b), r);
                         float a = __uint_as_float(r[0]);
@@ -843,7 +938,8 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                         if (!whole) {
                             st_tagged(slot + b * 128, a, part_tag);
                         } else if (n < job.N) {
-                            const int64_t idx = int64_t(b) * job.N + n;
+                            // (scattered rows: the PLANES group left the job's row map beside its planes)
+                            const int64_t idx = (MOE ? int64_t(reinterpret_cast<const volatile int*>(sq_smem + (pb ? SeqSmem::kRowMap1 : SeqSmem::kRowMap0))[8 + b]) : int64_t(b)) * job.N + n;
                             if constexpr (FUSE) {
                                 if (job.residual)
                                     a += job.y_dtype == QGEMV_OUT_F32 ? __ldcg(static_cast<const float*>(job.residual) + idx)
@@ -872,14 +968,15 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                         *abort_flag = 1;
                     }
                     mbar_arrive(sbase + SeqSmem::kBarEDone + 8 * pb);  // first: the PLANES group may be waiting
-                    st_release_cta_shared(sbase + SeqSmem::kEpiDone, j + 1);  // for the FINISH group's count of the job
+                    st_release_cta_shared(sbase + SeqSmem::kEpiDone, j - j_lo + 1);  // for the FINISH group's count of the job
                 }
                 job = next;
             }
         } else {
             // ---------------- FINISH ----------------
             int known = -1;  // jobs up to here are added up on every CTA (published in fin_all)
-            SeqJob job = seq_load_job(P.jobs);
+            SeqJob job = P.moe_job;
+            if (j_lo < j_hi) job = seq_job_at<MODE>(P, j_lo);
             TpExchange X;
             X.buf = P.xbuf, X.rank = P.rank, X.world = P.world, X.max_elems = P.x_max_elems;
             X.tag = 0u, X.par_off = 0;
@@ -887,35 +984,34 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 X.tag = __ldcg(P.barrier + 1) + 1u;
                 X.par_off = size_t(X.tag & 1u) * size_t(P.world) * size_t(P.x_max_elems);
             }
-            for (int j = 0; j < P.n_jobs; ++j) {
+            for (int j = j_lo; j < j_hi; ++j) {
                 SeqJob next = job;
-                if (j + 1 < P.n_jobs) next = seq_load_job(P.jobs + j + 1);
+                if (j + 1 < j_hi) next = seq_job_at<MODE>(P, j + 1);
                 // is this CTA the first contributor of a split tile of job j?  (only its last segment can be)
                 const int32_t kt_len = job.kt;
-                const int32_t total = job.tiles * kt_len;
-                const int gj = seq_job_grid(total, grid);
+                const int Bj = MOE ? job.rows : Bl;
                 int32_t rb, re;
-                seq_range(total, cta, gj, rb, re);
+                job_range(job, j, rb, re);
                 bool pending = false;
                 int32_t tile = 0, c_lo = 0, c_hi = 0, lo_slot = 0;
                 if (re > rb && re % kt_len != 0) {
                     tile = (re - 1) / kt_len;
-                    c_lo = seq_cta_of(tile * kt_len, total, gj);
-                    c_hi = seq_cta_of((tile + 1) * kt_len - 1, total, gj);
+                    c_lo = job_cta_of(job, j, tile * kt_len);
+                    c_hi = job_cta_of(job, j, (tile + 1) * kt_len - 1);
                     pending = c_lo == cta;
-                    lo_slot = seq_slot(c_lo, tile, kt_len, total, gj);
+                    lo_slot = job_slot(job, j, c_lo, tile);
                 }
                 // how far have ALL CTAs come with this step?  One probe per job, in flight with nothing else to do
-                if (gt == 0 && known + 1 < j && ld_acquire(P.fin + known + 1) >= unsigned(grid)) *fin_all = ++known;
+                if (!MOE && gt == 0 && known + 1 < j && ld_acquire(P.fin + known + 1) >= unsigned(grid)) *fin_all = ++known;
                 if (!group_alive()) break;
                 // this CTA's own part of the tile comes first, and the other contributors finish at about the same
                 // time: nothing is asked of global memory before this CTA's epilogues are through with the job
                 if (gt == 0) {
                     uint64_t t0 = 0;
-                    for (int64_t it = 0; ld_acquire_cta_shared(sbase + SeqSmem::kEpiDone) <= j; ++it) {
+                    for (int64_t it = 0; ld_acquire_cta_shared(sbase + SeqSmem::kEpiDone) <= j - j_lo; ++it) {
                         if (*abort_flag) break;
                         // (the epilogue may itself be waiting for fin_all to move before it reuses a parts buffer)
-                        if (known + 1 < j && ld_acquire(P.fin + known + 1) >= unsigned(grid)) {
+                        if (!MOE && known + 1 < j && ld_acquire(P.fin + known + 1) >= unsigned(grid)) {
                             *fin_all = ++known;
                         } else {
                             __nanosleep(100);
@@ -930,7 +1026,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 named_bar_sync(bar_id, 128);
                 if (pending) {
                     const int n = tile * 128 + gt;
-                    const unsigned long long* parts = P.ws + size_t(j & (kSeqPartBufs - 1)) * size_t(2 * grid) * 1024 + gt;
+                    const unsigned long long* parts = P.ws + job_parts(j) * size_t(2 * grid) * 1024 + gt;
                     const uint32_t part_tag = seq_part_tag(launch_no, j), pub_tag = seq_pub_tag(run_no, j) << 16;
                     if (n < job.N && !*abort_flag) {
                         bool have = true;
@@ -939,7 +1035,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                         // (one row of the batch after the other, not unrolled: this group's code has to stay small --
                         // five roles run different code on the SM at once and share its instruction cache)
 #pragma unroll 1
-                        for (int b = 0; b < Bl && have; ++b) {
+                        for (int b = 0; b < Bj && have; ++b) {
                             // the first contributor's own part, then the others eight at a time: the loads of a group
                             // are in flight together, the ones whose tag is not there yet are re-read together
                             // -- bounded --, and the additions stay in CTA order
@@ -975,7 +1071,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                                     if (cc + z <= c_hi) a = (cc + z == c_lo) ? __uint_as_float(uint32_t(t[z])) : a + __uint_as_float(uint32_t(t[z]));
                             }
                             if (!have) break;
-                            const int64_t idx = int64_t(b) * job.N + n;
+                            const int64_t idx = (MOE ? int64_t(__ldcg(job.rowmap + 8 + b)) : int64_t(b)) * job.N + n;
                             if (job.xoff >= 0) {
                                 // this rank's partial sum out to every rank, then the ranks' sums for this row, added in rank order
                                 X.push(int64_t(job.xoff) + idx, a);
@@ -1009,7 +1105,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 if (P.trace && gt == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 6] = globaltimer_ns();
                 // (the epilogues of the job are through, see above: fin[j] == grid means that all of y is there)
                 named_bar_sync(bar_id, 128);
-                if (gt == 0) red_release_add(P.fin + j, 1u);
+                if (!MOE && gt == 0) red_release_add(P.fin + j, 1u);
                 job = next;
             }
         }

@@ -62,7 +62,8 @@ def test_fp8_lm_head_128256x4096(qg, handle, B):
 
 
 @pytest.mark.parametrize("T", [1, 8, 64])
-def test_moe_128_experts_top8(qg, handle, T):
+@pytest.mark.parametrize("fmt_name", ["lane", "tc"])
+def test_moe_128_experts_top8(qg, handle, T, fmt_name):
     """128 experts, top-8: gate/up 1536 x 2048 on the tokens' rows, down 2048 x 768 on the slots' own rows.
     All experts are loaded; the experts of a handful of (token, choice) slots are checked in fp64."""
     import torch
@@ -71,7 +72,8 @@ def test_moe_128_experts_top8(qg, handle, T):
     ids = np.stack([rng.permutation(E)[:topk] for _ in range(T)]).astype(np.int32)
     for (N, K, per_slot) in ((1536, 2048, False), (2048, 768, True)):
         mats = [O.make_nvfp4(N, K, seed=5000 + e, ts=0.5 + e / 256.0) for e in range(E)]
-        w = handle.load_stacked(np.stack([qg.pack(qg.FMT_NVFP4, c, s, t) for c, s, t in mats]))
+        fmt = qg.FMT_NVFP4_TC if fmt_name == "tc" else qg.FMT_NVFP4
+        w = handle.load_stacked(np.stack([qg.pack(fmt, c, s, t) for c, s, t in mats]))
         rows = T * topk if per_slot else T
         x = O.make_x(rows, K, seed=T + N)
         out = torch.full((T * topk, N), float("nan"), dtype=torch.float32, device="cuda")

@@ -337,14 +337,18 @@ def _route(T, E, topk, seed):
     return ids, wts
 
 
-@pytest.mark.parametrize("T", [1, 8, 64])
+@pytest.mark.parametrize("T", [1, 3, 8, 64])
 @pytest.mark.parametrize("per_slot", [False, True])
-def test_moe_gemv(qg, handle, T, per_slot):
+@pytest.mark.parametrize("fmt_name", ["lane", "tc"])
+def test_moe_gemv(qg, handle, T, per_slot, fmt_name):
+    """Both layouts: the lane-order experts on the streaming kernel, the tensor-core layout as an expert list of
+    the sequence kernel (T = 64 gives experts with more than eight rows, i.e. two problems)."""
     import torch
     E, topk = 32, 4
     N, K = (96, 256) if not per_slot else (128, 192)
+    fmt = qg.FMT_NVFP4_TC if fmt_name == "tc" else qg.FMT_NVFP4
     codes, scales, ts = _experts(E, N, K, seed=300)
-    blobs = np.stack([qg.pack(qg.FMT_NVFP4, codes[e], scales[e], float(ts[e])) for e in range(E)])
+    blobs = np.stack([qg.pack(fmt, codes[e], scales[e], float(ts[e])) for e in range(E)])
     w = handle.load_stacked(blobs)
     ids, wts = _route(T, E, topk, seed=T)
     rows = T * topk if per_slot else T
@@ -369,12 +373,15 @@ def test_moe_gemv(qg, handle, T, per_slot):
     w.unload()
 
 
-def test_moe_gemv_long_k(qg, handle):
-    """Experts with K > 2048 run as K chunks of the streaming kernel, added in chunk order."""
+@pytest.mark.parametrize("fmt_name", ["lane", "tc"])
+def test_moe_gemv_long_k(qg, handle, fmt_name):
+    """Experts with K > 2048: lane order runs as K chunks of the streaming kernel, added in chunk order; the
+    tensor-core layout holds the digit planes of the whole K."""
     import torch
     E, topk, T, N, K = 16, 4, 8, 256, 4352
+    fmt = qg.FMT_NVFP4_TC if fmt_name == "tc" else qg.FMT_NVFP4
     codes, scales, ts = _experts(E, N, K, seed=900)
-    blobs = np.stack([qg.pack(qg.FMT_NVFP4, codes[e], scales[e], float(ts[e])) for e in range(E)])
+    blobs = np.stack([qg.pack(fmt, codes[e], scales[e], float(ts[e])) for e in range(E)])
     w = handle.load_stacked(blobs)
     ids, _ = _route(T, E, topk, seed=5)
     x = O.make_x(T, K, seed=6)

@@ -238,10 +238,12 @@ def test_tc_refused_by_other_entry_points(qg, handle):
         handle.gemm_skinny(w, x.data_ptr(), 16, y.data_ptr(), qg.OUT_F32)
     assert e.value.status == qg.ERR_UNSUPPORTED_SHAPE
     w.unload()
-    blobs = np.stack([qg.pack(qg.FMT_NVFP4_TC, codes, scales, ts)] * 2)
+    # a stacked weight (the experts of an MoE layer) is no job of a list
+    ws = handle.load_stacked(np.stack([qg.pack(qg.FMT_NVFP4_TC, codes, scales, ts)] * 2))
     with pytest.raises(qg.QgemvError) as e:
-        handle.load_stacked(blobs)
+        handle.sequence([(ws, x.data_ptr(), y.data_ptr(), qg.OUT_F32)], 1)
     assert e.value.status == qg.ERR_UNSUPPORTED_SHAPE
+    ws.unload()
 
 
 # ---- a sequence of GEMVs as one persistent launch -------------------------------------------------
