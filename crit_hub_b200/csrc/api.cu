@@ -1100,11 +1100,19 @@ int qgemv_gemm_skinny(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16
 }
 
 namespace {
-// The experts of a router table on the tensor-core layout: the sequence kernel in its expert-list mode, one
-// cooperative launch after the router walk.  Problems hold at most B activation rows.
-int moe_tc(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, void* out, int out_dtype, int B, cudaStream_t s) {
+// The experts of a router table on the tensor-core layout: the sequence kernel in its expert-list mode, ONE
+// cooperative launch (every CTA walks the top-k lists for itself).  Problems hold at most B activation rows.
+int moe_tc(qgemv_handle* h, const qgemv_weight* w, const int32_t* expert_ids, const void* x_bf16, int T, int topk,
+           int per_slot_input, void* out, int out_dtype, cudaStream_t s) {
     const int grid = gemv_grid(h);
     if (grid > h->sm_count) return QGEMV_ERR_UNSUPPORTED_SHAPE;  // the CTAs wait on one another: one per SM at most
+    // rows per problem: no more than there are tokens (the digit planes and the accumulator are sized for the
+    // largest problem)
+    const int B = std::min(QGEMV_MAX_BATCH, T);
+    const int slots = T * topk;
+    if (w->n_stack > qg::kMoeMaxExperts) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+    const int64_t most_prob = std::min<int64_t>(w->n_stack, slots) + slots / B;   // problems the lists can make
+    if ((most_prob + grid - 1) / grid + 1 > qg::kMoeLocalJobs) return QGEMV_ERR_UNSUPPORTED_SHAPE;
     qg::SeqParams P;
     std::memset(&P, 0, sizeof P);
     qg::SeqJob& mj = P.moe_job;
@@ -1118,7 +1126,7 @@ int moe_tc(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, void* out
     mj.y_dtype = out_dtype;
     mj.dep = -1, mj.xoff = -1, mj.pub_off = -1, mj.src_off = -1, mj.src_job = -1;
     const int64_t per = int64_t(mj.tiles) * mj.kt;
-    if ((int64_t(w->max_prob) * per + 1) * grid >= (int64_t(1) << 32)) return QGEMV_ERR_UNSUPPORTED_SHAPE;  // 32-bit split arithmetic
+    if ((most_prob * per + 1) * grid >= (int64_t(1) << 32)) return QGEMV_ERR_UNSUPPORTED_SHAPE;  // 32-bit split arithmetic
     P.ws = h->seq_parts;
     P.barrier = h->seq_barrier;
     P.fin = reinterpret_cast<unsigned int*>(w->counters);  // [0]: launches with this weight (nothing else of a job list's counters is used)
@@ -1130,11 +1138,13 @@ int moe_tc(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, void* out
     P.x_slots = mj.kt;   // a CTA's share of an expert may span a whole row tile
     P.debug = h->cfg.debug;
     P.world = 1;
-    P.prob = w->prob;
+    P.ids = expert_ids;
+    P.slots = slots, P.topk = topk, P.n_experts = w->n_stack, P.per_slot = per_slot_input ? 1 : 0;
     P.expert_ts = w->dev_tensor_scale;
     P.expert_stride = w->blob_bytes;
     constexpr int kStage = 4;
-    const int cap = (h->cfg.tc_smem_kb > 0 ? std::min(h->cfg.tc_smem_kb, 227) : 227) * 1024;
+    constexpr int kWalk = (qg::kMoeSmemBytes + 127) / 128 * 128;   // the walk's scratch, behind the ring
+    const int cap = (h->cfg.tc_smem_kb > 0 ? std::min(h->cfg.tc_smem_kb, 227) : 227) * 1024 - kWalk;
     // two plane buffers (a CTA's range mostly touches two experts) when that leaves a ring of four stages
     int ring = 0;
     for (P.nbuf = 2; P.nbuf >= 1; --P.nbuf) {
@@ -1145,7 +1155,8 @@ int moe_tc(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16, void* out
     }
     if (ring < 2) return QGEMV_ERR_UNSUPPORTED_SHAPE;  // K too long for the digit planes of one expert beside a ring
     P.ring = ring;
-    const size_t smem = size_t(qg::SeqSmem::total(P.x_slots, P.npad, P.nbuf, ring, kStage));
+    P.moe_smem = (qg::SeqSmem::total(P.x_slots, P.npad, P.nbuf, ring, kStage) + 127) / 128 * 128;
+    const size_t smem = size_t(P.moe_smem) + kWalk;
     g_launch_cooperative = true;
     const cudaError_t err = launch(h, qg::gemv_seq_kernel<kStage, qg::kSeqMoe>, dim3(unsigned(grid)), dim3(qg::kSeqThreads), smem, s, P);
     return err == cudaSuccess ? QGEMV_OK : QGEMV_ERR_CUDA;
@@ -1161,16 +1172,12 @@ int qgemv_moe_gemv(qgemv_handle* h, const qgemv_weight* experts, const int32_t* 
     if (out_dtype != QGEMV_OUT_BF16 && out_dtype != QGEMV_OUT_F32) return QGEMV_ERR_INVALID_ARG;
     if ((reinterpret_cast<uintptr_t>(x_bf16) & 15u) != 0) return QGEMV_ERR_INVALID_ARG;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (experts->fmt == QGEMV_FMT_NVFP4_TC) return moe_tc(h, experts, expert_ids, x_bf16, T, topk, per_slot_input, out, out_dtype, s);
     const int threads = 1024;
-    // rows per problem: eight; on the tensor-core layout no more than there are tokens (the digit planes and
-    // the accumulator are sized for the largest problem)
-    const bool tc = experts->fmt == QGEMV_FMT_NVFP4_TC;
-    const int cap = tc ? std::min(QGEMV_MAX_BATCH, T) : 8;
     cudaError_t err = launch(h, qg::moe_prep_kernel, dim3(1), dim3(threads),
                              size_t(experts->n_stack) * 12 + size_t(T) * topk * 4 + 16, s, expert_ids, T, topk, experts->n_stack,
-                             per_slot_input, experts->max_prob, cap, experts->prob, h->status_dev);
+                             per_slot_input, experts->max_prob, experts->prob, h->status_dev);
     if (err != cudaSuccess) return QGEMV_ERR_CUDA;
-    if (tc) return moe_tc(h, experts, x_bf16, out, out_dtype, cap, s);
     qg::GemvParams P = base_params(h, experts);
     P.x = static_cast<const uint16_t*>(x_bf16);
     P.y = out;

@@ -74,12 +74,12 @@ __global__ void dequant_kernel(const uint8_t* payload, const float* chan, float 
 }
 
 // Router walk: groups the (token, slot) pairs of expert_ids [T][topk] by expert, in ascending
-// (t, j) order, and cuts each group into problems of at most `cap` (1..8) activation rows.
+// (t, j) order, and cuts each group into problems of at most eight activation rows.
 // prob[0] = problem count; problem i = {expert, nrows, xrow[8], orow[8], 0, 0}.
 // One CTA: counts by a shared-memory histogram, a warp prefix scan, then one warp walks the list in
 // order, so the order inside every problem is the list order and the table is deterministic.
 __global__ void moe_prep_kernel(const int32_t* expert_ids, int T, int topk, int n_experts,
-                                int per_slot_input, int max_prob, int cap, int32_t* prob, int32_t* status) {
+                                int per_slot_input, int max_prob, int32_t* prob, int32_t* status) {
     extern __shared__ int sh[];  // ids[T*topk], counts[n_experts], base[n_experts], seen[n_experts], flags[2]
     const int total = T * topk;
     int* ids = sh;
@@ -109,7 +109,7 @@ __global__ void moe_prep_kernel(const int32_t* expert_ids, int T, int topk, int 
         int carry = 0;
         for (int e0 = 0; e0 < n_experts; e0 += 32) {
             const int e = e0 + lane;
-            const int np = e < n_experts ? (counts[e] + cap - 1) / cap : 0;
+            const int np = e < n_experts ? (counts[e] + 7) / 8 : 0;
             int incl = np;
             for (int d = 1; d < 32; d <<= 1) {
                 const int v = __shfl_up_sync(0xFFFFFFFFu, incl, d);
@@ -149,12 +149,12 @@ __global__ void moe_prep_kernel(const int32_t* expert_ids, int T, int topk, int 
             }
             __syncwarp();
             if (valid) {
-                const int q = k / cap, r = k - q * cap;
-                int32_t* p = prob + 1 + (base[e] + q) * kProbInts;
+                int32_t* p = prob + 1 + (base[e] + (k >> 3)) * kProbInts;
+                const int r = k & 7;
                 if (r == 0) {
                     p[0] = e;
                     const int left = cnt - k;
-                    p[1] = left < cap ? left : cap;
+                    p[1] = left < 8 ? left : 8;
                     p[18] = p[19] = 0;
                 }
                 p[2 + r] = per_slot_input ? i : i / topk;

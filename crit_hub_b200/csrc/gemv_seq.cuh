@@ -66,7 +66,7 @@ struct SeqJob {               // 80 bytes, device memory
     float norm_eps;
     const uint16_t* norm_w;   // bf16 [K] or null: x'[k] = bf16(x[k] * norm_w[k]); y is scaled by rsqrt(mean(x^2) + eps)
     const void* residual;     // [B][N] in y's dtype or null: added to the result before it is rounded
-    const int32_t* rowmap;    // expert list only: [16] row of x for each of the job's activation rows, then row of y
+    const int32_t* rowmap;    // expert list only: [16] row of x for each of the job's activation rows, then row of y (shared memory)
     int32_t rows;             // expert list only: activation rows of this job (<= B)
     int32_t pad;
 };
@@ -93,14 +93,20 @@ struct SeqParams {
     uint8_t* xbuf[kTpMaxWorld];
     int64_t x_max_elems;
     int32_t rank, world;
-    // expert list (MODE 2): the jobs are the problems of a router table, made on the device just before the launch
-    // (prob[0] = count, then kProbInts ints per problem: expert, rows, row of x [8], row of y [8]); every job is
-    // moe_job with the expert's payload and tensor scale
-    const int32_t* prob;
+    // expert list (kSeqMoe): the jobs are the problems of the router's table -- for every expert that the top-k lists
+    // [slots / topk][topk] name, its (token, choice) entries in list order, cut into problems of at most B
+    // activation rows.  Every CTA works the table out for itself at the start of the launch (the part of it that
+    // its range touches); every job is moe_job with the expert's payload and tensor scale.
+    const int32_t* ids;
     const float* expert_ts;
     uint64_t expert_stride;
+    int32_t slots, topk, n_experts, per_slot;  // per_slot: activation row = the entry's index (else its token)
+    int32_t moe_smem;                          // offset of the walk's scratch in shared memory (behind the ring)
     SeqJob moe_job;
 };
+constexpr int kMoeMaxExperts = 512;   // experts of a stacked weight that the expert-list mode takes
+constexpr int kMoeLocalJobs = 32;     // problems that one CTA's range may touch
+constexpr int kMoeSmemBytes = (2 * kMoeMaxExperts + kMoeLocalJobs * kProbInts + 32) * 4;
 
 struct SeqSmem {
     static constexpr int kBarFull = 0;      // kTcMaxRing
@@ -115,8 +121,6 @@ struct SeqSmem {
     static constexpr int kBarDrain = 304;
     static constexpr int kTmemPtr = 312;
     static constexpr int kAbort = 316;
-    static constexpr int kRowMap0 = 320;    // expert list: rows of x [8] and of y [8] of the job in plane buffer 0 ...
-    static constexpr int kRowMap1 = 960;    // ... and 1 (that mode has two plane buffers at most)
     static constexpr int kWarpMax = 384;    // kTcConvWarps x 8 words: the same per converting warp
     static constexpr int kIssued = 640;
     static constexpr int kConsumed = 644;
@@ -186,21 +190,6 @@ __device__ __forceinline__ SeqJob seq_load_job(const SeqJob* j) {
 }
 // MODE of the kernel: a plain job list; one with fused activation transforms; the experts of a router table.
 constexpr int kSeqPlain = 0, kSeqFuse = 1, kSeqMoe = 2;
-template <int MODE>
-__device__ __forceinline__ SeqJob seq_job_at(const SeqParams& P, int j) {
-    if constexpr (MODE == kSeqMoe) {
-        SeqJob job = P.moe_job;
-        const int32_t* pr = P.prob + 1 + j * kProbInts;   // written by the kernel before this one: read through L2
-        const int e = __ldcg(pr);
-        job.payload += uint64_t(e) * P.expert_stride;
-        job.tensor_scale = __ldg(P.expert_ts + e);
-        job.rows = __ldcg(pr + 1);
-        job.rowmap = pr + 2;
-        return job;
-    } else {
-        return seq_load_job(P.jobs + j);
-    }
-}
 // A job is split over min(grid, items) CTAs, exactly as a launch of its own would be; the other CTAs
 // only take part in the job's barriers.  Range [begin, end) of CTA `cta` in the job's linear
 // (tile, item) space; empty for a CTA beyond the job's share.
@@ -350,15 +339,106 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
     int j_lo = 0, j_hi = P.n_jobs;
     int32_t g_total = 0, g_begin = 0, g_end = 0, g_per = 1;
     int g_gj = grid;
+    const int* m_tab = nullptr;  // expert list: the problems this CTA's range touches, kProbInts ints each
     if constexpr (MOE) {
-        pdl_wait();  // the problem table is the work of the kernel before this one
+        // ---- the router walk: entries per expert (shared-memory histogram), problems per expert and their prefix
+        // (one warp), then one warp per problem of this CTA's range collects the problem's rows in list order ----
+        int* m_counts = reinterpret_cast<int*>(sq_smem + P.moe_smem);  // [n_experts] entries
+        int* m_base = m_counts + kMoeMaxExperts;                       // [n_experts] first problem
+        int* tab = m_base + kMoeMaxExperts;                            // [kMoeLocalJobs][kProbInts]
+        volatile int* m_misc = tab + kMoeLocalJobs * kProbInts;        // [0] problems, [1] an id out of range
+        m_tab = tab;
+        const int E = P.n_experts, slots = P.slots, cap = P.B;
+        pdl_wait();  // the lists are the work of whatever ran before this launch
+        for (int e = threadIdx.x; e < E; e += kSeqThreads) m_counts[e] = 0;
+        if (threadIdx.x == 0) m_misc[0] = 0, m_misc[1] = 0;
+        __syncthreads();
+        for (int i = threadIdx.x; i < slots; i += kSeqThreads) {
+            const int e = __ldcg(P.ids + i);
+            if (unsigned(e) >= unsigned(E)) {
+                m_misc[1] = 1;
+            } else {
+                atomicAdd(&m_counts[e], 1);
+            }
+        }
+        __syncthreads();
+        if (warp == 0) {
+            int carry = 0;
+            for (int e0 = 0; e0 < E; e0 += 32) {
+                const int e = e0 + lane;
+                const int np = e < E ? (m_counts[e] + cap - 1) / cap : 0;
+                int incl = np;
+                for (int d = 1; d < 32; d <<= 1) {
+                    const int v = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+                    if (lane >= d) incl += v;
+                }
+                if (e < E) m_base[e] = carry + incl - np;
+                carry += __shfl_sync(0xFFFFFFFFu, incl, 31);
+            }
+            if (lane == 0) {
+                if (m_misc[1]) {
+                    if (cta == 0) report(P.status, QGEMV_ERR_BOUNDS, 21, 0);
+                    carry = 0;  // every CTA sees the same lists and leaves without work
+                }
+                m_misc[0] = carry;
+            }
+        }
+        __syncthreads();
         g_per = P.moe_job.tiles * P.moe_job.kt;
-        g_total = __ldcg(P.prob) * g_per;
+        g_total = m_misc[0] * g_per;
         g_gj = seq_job_grid(g_total, grid);
         seq_range(g_total, cta, g_gj, g_begin, g_end);
         j_lo = g_begin / g_per;
         j_hi = g_end > g_begin ? (g_end - 1) / g_per + 1 : j_lo;
+        if (j_hi - j_lo > kMoeLocalJobs) {  // (the host refuses shapes that could come here)
+            if (threadIdx.x == 0) {
+                report(P.status, QGEMV_ERR_BOUNDS, 20, j_hi - j_lo);
+                *abort_flag = 1;
+            }
+            j_hi = j_lo;
+        }
+        for (int e = threadIdx.x; e < E; e += kSeqThreads) {
+            const int cnt = m_counts[e];
+            const int b0 = m_base[e], np = (cnt + cap - 1) / cap;
+            for (int j = max(j_lo, b0); j < min(j_hi, b0 + np); ++j) {
+                int* t = tab + (j - j_lo) * kProbInts;
+                const int q = j - b0;
+                t[0] = e, t[1] = min(cap, cnt - q * cap), t[18] = q;
+            }
+        }
+        __syncthreads();
+        for (int jl = warp; jl < j_hi - j_lo; jl += kSeqThreads / 32) {
+            int* t = tab + jl * kProbInts;
+            const int e = t[0], rows = t[1], r0 = t[18] * cap;
+            int seen = 0;
+            for (int i0 = 0; i0 < slots && seen < r0 + rows; i0 += 32) {
+                const int i = i0 + lane;
+                const int id = i < slots ? __ldcg(P.ids + i) : -1;
+                const unsigned m = __ballot_sync(0xFFFFFFFFu, id == e);
+                const int r = seen + __popc(m & ((1u << lane) - 1u)) - r0;
+                if (id == e && r >= 0 && r < rows) {
+                    t[2 + r] = P.per_slot ? i : i / P.topk;
+                    t[10 + r] = i;
+                }
+                seen += __popc(m);
+            }
+        }
+        __syncthreads();
     }
+    auto job_at = [&](int j) -> SeqJob {
+        if constexpr (MOE) {
+            SeqJob job = P.moe_job;
+            const int* t = m_tab + (j - j_lo) * kProbInts;
+            const int e = t[0];
+            job.payload += uint64_t(e) * P.expert_stride;
+            job.tensor_scale = __ldg(P.expert_ts + e);
+            job.rows = t[1];
+            job.rowmap = t + 2;
+            return job;
+        } else {
+            return seq_load_job(P.jobs + j);
+        }
+    };
     // this CTA's range [rb, re) of job j, in the job's own (tile, item) space
     auto job_range = [&](const SeqJob& job, int j, int32_t& rb, int32_t& re) {
         if constexpr (MOE) {
@@ -399,10 +479,10 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
             uint32_t use = 0;
             bool ok = true;
             SeqJob job = P.moe_job;
-            if (j_lo < j_hi) job = seq_job_at<MODE>(P, j_lo);
+            if (j_lo < j_hi) job = job_at(j_lo);
             for (int j = j_lo; j < j_hi && ok; ++j) {
                 SeqJob next = job;
-                if (j + 1 < j_hi) next = seq_job_at<MODE>(P, j + 1);  // in flight while this job streams
+                if (j + 1 < j_hi) next = job_at(j + 1);  // in flight while this job streams
                 GsWalker wk;
                 wk.units = job.kt;
                 job_range(job, j, wk.pos, wk.end);
@@ -451,12 +531,12 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
             const long long prof_start = clock64();
 #endif
             SeqJob job = P.moe_job;
-            if (j_lo < j_hi) job = seq_job_at<MODE>(P, j_lo);
+            if (j_lo < j_hi) job = job_at(j_lo);
             int pb = 0;        // plane buffer of job j: j % nbuf, kept as a counter (no division in this thread)
             uint32_t pph = 0;  // parity of that buffer's use: (j / nbuf) & 1
             for (int j = j_lo; j < j_hi && ok; ++j, pph ^= (pb + 1 == nb) ? 1u : 0u, pb = (pb + 1 == nb) ? 0 : pb + 1) {
                 SeqJob next = job;
-                if (j + 1 < j_hi) next = seq_job_at<MODE>(P, j + 1);
+                if (j + 1 < j_hi) next = job_at(j + 1);
                 const int32_t kt_len = job.kt;
                 // the digit planes of this job (every CTA signals, also one without items)
                 SEQ_PROF_T0();
@@ -621,12 +701,12 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 *reinterpret_cast<volatile uint32_t*>(sq_smem + SeqSmem::kSfb + (n & 31) * 16 + (n >> 5) * 4) = byte * 0x01010101u;
             }
             SeqJob job = P.moe_job;
-            if (j_lo < j_hi) job = seq_job_at<MODE>(P, j_lo);
+            if (j_lo < j_hi) job = job_at(j_lo);
             int pb = 0;        // plane buffer of job j (j % nbuf) and the parity of its use ((j / nbuf) & 1), as counters
             uint32_t pph = 0;
             for (int j = j_lo; j < j_hi; ++j, pph ^= (pb + 1 == nb) ? 1u : 0u, pb = (pb + 1 == nb) ? 0 : pb + 1) {
                 SeqJob next = job;
-                if (j + 1 < j_hi) next = seq_job_at<MODE>(P, j + 1);
+                if (j + 1 < j_hi) next = job_at(j + 1);
                 // the plane buffer and its row maxima were last used by job j - nbuf: its epilogues must be through
                 if (j - j_lo >= nb && gt == 0 &&
                     !seq_mbar_wait(sbase + SeqSmem::kBarEDone + 8 * pb, (pph ^ 1u), P.spin_limit)) {
@@ -649,10 +729,6 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                     rg[0] = r_begin, rg[1] = r_end;
                 }
                 if (gt < 32) all_max[gt] = 0u;
-                volatile int* rowmap_s = reinterpret_cast<volatile int*>(sq_smem + (pb ? SeqSmem::kRowMap1 : SeqSmem::kRowMap0));
-                if constexpr (MOE) {
-                    if (gt >= 32 && gt < 48) rowmap_s[gt - 32] = __ldcg(job.rowmap + (gt - 32));
-                }
                 named_bar_sync(bar_id, 128);
                 const int n_work = n_slots * Bj * 8;
                 constexpr int kKeep = 4;
@@ -699,7 +775,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                         return pub_wait(p, ld_pub4(p), ld_pub4(p + 4));
                     }
                     // possibly written by other SMs during an earlier job: read through L2, never a stale L1 line
-                    const int64_t xr = MOE ? int64_t(rowmap_s[b]) : int64_t(b);  // gathered rows
+                    const int64_t xr = MOE ? int64_t(job.rowmap[b]) : int64_t(b);  // gathered rows
                     return __ldcg(reinterpret_cast<const uint4*>(job.x + xr * job.x_stride + k0));
                 };
                 // ... and what the GEMV multiplies: the activation function and the norm weight applied (FUSE)
@@ -864,12 +940,12 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
             const int row = 32 * q + lane;
             uint32_t nseg = 0;
             SeqJob job = P.moe_job;
-            if (j_lo < j_hi) job = seq_job_at<MODE>(P, j_lo);
+            if (j_lo < j_hi) job = job_at(j_lo);
             int pb = 0;
             uint32_t pph = 0;
             for (int j = j_lo; j < j_hi; ++j, pph ^= (pb + 1 == nb) ? 1u : 0u, pb = (pb + 1 == nb) ? 0 : pb + 1) {
                 SeqJob next = job;
-                if (j + 1 < j_hi) next = seq_job_at<MODE>(P, j + 1);
+                if (j + 1 < j_hi) next = job_at(j + 1);
                 const int32_t kt_len = job.kt;
                 const int Bj = MOE ? job.rows : Bl;
                 // the planes of this job are ready, and with them this CTA's item range (a CTA without items
@@ -938,8 +1014,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                         if (!whole) {
                             st_tagged(slot + b * 128, a, part_tag);
                         } else if (n < job.N) {
-                            // (scattered rows: the PLANES group left the job's row map beside its planes)
-                            const int64_t idx = (MOE ? int64_t(reinterpret_cast<const volatile int*>(sq_smem + (pb ? SeqSmem::kRowMap1 : SeqSmem::kRowMap0))[8 + b]) : int64_t(b)) * job.N + n;
+                            const int64_t idx = (MOE ? int64_t(job.rowmap[8 + b]) : int64_t(b)) * job.N + n;  // scattered rows
                             if constexpr (FUSE) {
                                 if (job.residual)
                                     a += job.y_dtype == QGEMV_OUT_F32 ? __ldcg(static_cast<const float*>(job.residual) + idx)
@@ -976,7 +1051,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
             // ---------------- FINISH ----------------
             int known = -1;  // jobs up to here are added up on every CTA (published in fin_all)
             SeqJob job = P.moe_job;
-            if (j_lo < j_hi) job = seq_job_at<MODE>(P, j_lo);
+            if (j_lo < j_hi) job = job_at(j_lo);
             TpExchange X;
             X.buf = P.xbuf, X.rank = P.rank, X.world = P.world, X.max_elems = P.x_max_elems;
             X.tag = 0u, X.par_off = 0;
@@ -986,7 +1061,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
             }
             for (int j = j_lo; j < j_hi; ++j) {
                 SeqJob next = job;
-                if (j + 1 < j_hi) next = seq_job_at<MODE>(P, j + 1);
+                if (j + 1 < j_hi) next = job_at(j + 1);
                 // is this CTA the first contributor of a split tile of job j?  (only its last segment can be)
                 const int32_t kt_len = job.kt;
                 const int Bj = MOE ? job.rows : Bl;
@@ -1071,7 +1146,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                                     if (cc + z <= c_hi) a = (cc + z == c_lo) ? __uint_as_float(uint32_t(t[z])) : a + __uint_as_float(uint32_t(t[z]));
                             }
                             if (!have) break;
-                            const int64_t idx = (MOE ? int64_t(__ldcg(job.rowmap + 8 + b)) : int64_t(b)) * job.N + n;
+                            const int64_t idx = (MOE ? int64_t(job.rowmap[8 + b]) : int64_t(b)) * job.N + n;
                             if (job.xoff >= 0) {
                                 // this rank's partial sum out to every rank, then the ranks' sums for this row, added in rank order
                                 X.push(int64_t(job.xoff) + idx, a);

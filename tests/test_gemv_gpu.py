@@ -400,6 +400,37 @@ def test_moe_gemv_long_k(qg, handle, fmt_name):
     w.unload()
 
 
+@pytest.mark.parametrize("fmt_name", ["lane", "tc"])
+def test_moe_gemv_repeated_and_bad_ids(qg, handle, fmt_name):
+    """A token that names the same expert twice gets two rows of that expert's problem; an id outside the stacked
+    weight is reported in the status word (no result is written, nothing faults) and the next call is clean."""
+    import torch
+    E, topk, T, N, K = 8, 4, 2, 128, 128
+    fmt = qg.FMT_NVFP4_TC if fmt_name == "tc" else qg.FMT_NVFP4
+    codes, scales, ts = _experts(E, N, K, seed=77)
+    w = handle.load_stacked(np.stack([qg.pack(fmt, codes[e], scales[e], float(ts[e])) for e in range(E)]))
+    ids = np.array([[3, 3, 5, 3], [5, 0, 5, 7]], dtype=np.int32)      # three rows of expert 3 from ONE token: more rows than tokens
+    x = O.make_x(T, K, seed=9)
+    ref = O.moe_gemv_nvfp4_f64(codes, scales, ts, ids, x, per_slot_input=False)
+    xd, idd = U.dev_u16(x), torch.from_numpy(ids).cuda()
+    out = torch.full((T * topk, N), float("nan"), dtype=torch.float32, device="cuda")
+    handle.moe_gemv(w, idd.data_ptr(), xd.data_ptr(), T, topk, False, out.data_ptr(), qg.OUT_F32)
+    torch.cuda.synchronize()
+    U.status_ok(handle)
+    assert O.rel_l2(out.cpu().numpy(), ref) < TOL_F32
+    bad = torch.from_numpy(np.array([[3, 1, 5, 2], [5, 0, E, 7]], dtype=np.int32)).cuda()
+    handle.moe_gemv(w, bad.data_ptr(), xd.data_ptr(), T, topk, False, out.data_ptr(), qg.OUT_F32)
+    torch.cuda.synchronize()
+    st = handle.device_status()
+    assert st.code == qg.ERR_BOUNDS and st.where == 21
+    out.fill_(float("nan"))
+    handle.moe_gemv(w, idd.data_ptr(), xd.data_ptr(), T, topk, False, out.data_ptr(), qg.OUT_F32)
+    torch.cuda.synchronize()
+    U.status_ok(handle)
+    assert O.rel_l2(out.cpu().numpy(), ref) < TOL_F32
+    w.unload()
+
+
 # ---- tensor-parallel exchange ----------------------------------------------------------------------
 def test_tp_allreduce_single_rank(qg):
     """World of one: the exchange degenerates to push-to-self, flag, reduce; replaying it checks
