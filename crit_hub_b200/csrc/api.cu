@@ -797,6 +797,7 @@ int qgemv_sequence_run(qgemv_handle* h, const qgemv_sequence* q, void* stream) {
     P.nbuf = q->nbuf;
     P.debug = h->cfg.debug;
     P.trace = h->tc_trace;
+    P.trace_jobs = q->n_jobs;
     P.world = 1;
     if (q->xchg_elems > 0) {
         for (int r = 0; r < h->tp_world; ++r) P.xbuf[r] = h->tp_peer[r];
@@ -1137,6 +1138,8 @@ int moe_tc(qgemv_handle* h, const qgemv_weight* w, const int32_t* expert_ids, co
     P.npad = (8 * B + 15) / 16 * 16;
     P.x_slots = mj.kt;   // a CTA's share of an expert may span a whole row tile
     P.debug = h->cfg.debug;
+    P.trace = h->tc_trace;
+    P.trace_jobs = qg::kMoeLocalJobs;
     P.world = 1;
     P.ids = expert_ids;
     P.slots = slots, P.topk = topk, P.n_experts = w->n_stack, P.per_slot = per_slot_input ? 1 : 0;
@@ -1157,7 +1160,7 @@ int moe_tc(qgemv_handle* h, const qgemv_weight* w, const int32_t* expert_ids, co
     P.ring = ring;
     P.moe_smem = (qg::SeqSmem::total(P.x_slots, P.npad, P.nbuf, ring, kStage) + 127) / 128 * 128;
     const size_t smem = size_t(P.moe_smem) + kWalk;
-    g_launch_cooperative = true;
+    g_launch_cooperative = (h->cfg.debug & 2048) != 0;
     const cudaError_t err = launch(h, qg::gemv_seq_kernel<kStage, qg::kSeqMoe>, dim3(unsigned(grid)), dim3(qg::kSeqThreads), smem, s, P);
     return err == cudaSuccess ? QGEMV_OK : QGEMV_ERR_CUDA;
 }

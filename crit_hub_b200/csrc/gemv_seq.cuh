@@ -89,6 +89,7 @@ struct SeqParams {
     int32_t nbuf;               // buffers of digit planes, 1..kSeqPlaneBufsMax
     int32_t debug;
     unsigned long long* trace;  // optional diagnostics: per CTA, per job 8 stamps (see qgemv_set_trace), or null
+    int32_t trace_jobs;         // jobs per CTA in the trace (a list: n_jobs; an expert list: kMoeLocalJobs, the CTA's own problems)
     // tensor-parallel exchange (world == 1: none)
     uint8_t* xbuf[kTpMaxWorld];
     int64_t x_max_elems;
@@ -225,11 +226,25 @@ __device__ __noinline__ void seq_report(int32_t* status, int where, int extra) {
 
 // Eight activations of one row -> their eight digit planes in shared memory.  Not inlined: the kernel's five
 // roles run different code on an SM at once and share its instruction cache, so the code is kept small.
+// The 32 lanes of a warp work on units whose addresses differ by multiples of 128 bytes except for the word
+// inside a 16-byte plane row (unit mod 4): stored plane by plane they would hit four banks eight deep.  Each
+// lane therefore starts with another plane -- (lane / 4) mod 8, the part of its unit number that the bank
+// does not see -- so that one store instruction covers all 32 banks.
 __device__ __noinline__ void seq_store_unit(uint32_t dst, uint4 v, float sf) {
     uint32_t pl[8];
     tc_digits8(v, sf, pl);
+    const int rot = (threadIdx.x >> 2) & 7;
 #pragma unroll
-    for (int z = 0; z < 8; ++z) asm volatile("st.shared.b32 [%0], %1;" ::"r"(dst + z * 16), "r"(pl[z]) : "memory");
+    for (int sft = 1; sft < 8; sft <<= 1) {   // pl[z] <- pl[(z + rot) mod 8], one bit of rot at a time
+        const bool on = (rot & sft) != 0;
+        uint32_t q[8];
+#pragma unroll
+        for (int z = 0; z < 8; ++z) q[z] = on ? pl[(z + sft) & 7] : pl[z];
+#pragma unroll
+        for (int z = 0; z < 8; ++z) pl[z] = q[z];
+    }
+#pragma unroll
+    for (int z = 0; z < 8; ++z) asm volatile("st.shared.b32 [%0], %1;" ::"r"(dst + uint32_t((z + rot) & 7) * 16u), "r"(pl[z]) : "memory");
 }
 
 // ---- fused activation transforms (FUSE instantiation only) ----------------------------------------------
@@ -349,6 +364,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
         volatile int* m_misc = tab + kMoeLocalJobs * kProbInts;        // [0] problems, [1] an id out of range
         m_tab = tab;
         const int E = P.n_experts, slots = P.slots, cap = P.B;
+        if (P.trace && threadIdx.x == 0) P.trace[size_t(grid) * P.trace_jobs * 8 + size_t(cta) * 4 + 0] = globaltimer_ns();
         pdl_wait();  // the lists are the work of whatever ran before this launch
         for (int e = threadIdx.x; e < E; e += kSeqThreads) m_counts[e] = 0;
         if (threadIdx.x == 0) m_misc[0] = 0, m_misc[1] = 0;
@@ -424,6 +440,9 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
             }
         }
         __syncthreads();
+    }
+    if constexpr (MOE) {
+        if (P.trace && threadIdx.x == 0) P.trace[size_t(grid) * P.trace_jobs * 8 + size_t(cta) * 4 + 1] = globaltimer_ns();
     }
     auto job_at = [&](int j) -> SeqJob {
         if constexpr (MOE) {
@@ -548,7 +567,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 }
                 SEQ_PROF_ADD(0);
                 tc_fence_after();
-                if (SEQ_STAMPS && P.trace) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 3] = globaltimer_ns();
+                if (SEQ_STAMPS && P.trace) P.trace[(size_t(cta) * P.trace_jobs + (j - j_lo)) * 8 + 3] = globaltimer_ns();
                 // this CTA's item range of the job, computed by the PLANES group
                 const volatile int* rg = reinterpret_cast<const volatile int*>(sq_smem + SeqSmem::kRange) + pb * 2;
                 const int32_t r_begin = rg[0], r_end = rg[1];
@@ -608,7 +627,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                         acc = 1;
                         x_lo += xslot16 * S;
                         tc_commit(bar_empty);  // the stage is reusable once these retire
-                        if (SEQ_STAMPS && P.trace && P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 7] == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 7] = globaltimer_ns();
+                        if (SEQ_STAMPS && P.trace && P.trace[(size_t(cta) * P.trace_jobs + (j - j_lo)) * 8 + 7] == 0) P.trace[(size_t(cta) * P.trace_jobs + (j - j_lo)) * 8 + 7] = globaltimer_ns();
                         ++mi;
                         item16 += stage16, sfa += 4u * S, bar_full += 8, bar_empty += 8;
                         if (item16 == ring_end16) {
@@ -620,7 +639,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                     tc_commit(sbase + SeqSmem::kBarDFull + 8 * (nseg & 1));
                     ++nseg;
                 }
-                if (SEQ_STAMPS && P.trace) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 4] = globaltimer_ns();
+                if (SEQ_STAMPS && P.trace) P.trace[(size_t(cta) * P.trace_jobs + (j - j_lo)) * 8 + 4] = globaltimer_ns();
                 // Barrier phases are told apart by one parity bit, so nobody may complete a barrier twice
                 // before every waiter has seen the first completion: the planes of job j + 2 are only made
                 // once this thread (here) and the epilogue group are through with job j.
@@ -630,7 +649,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
 #ifdef QGEMV_SEQ_PROFILE
             if (P.trace) {   // per CTA: cycles waiting for planes, accumulators, weight stages; total
                 prof[3] = clock64() - prof_start;
-                for (int z = 0; z < 4; ++z) P.trace[size_t(gridDim.x) * P.n_jobs * 8 + size_t(cta) * 4 + z] = (unsigned long long)prof[z];
+                for (int z = 0; z < 4; ++z) P.trace[size_t(gridDim.x) * P.trace_jobs * 8 + size_t(cta) * 4 + z] = (unsigned long long)prof[z];
             }
 #endif
             *n_consumed = mi;
@@ -704,6 +723,13 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
             if (j_lo < j_hi) job = job_at(j_lo);
             int pb = 0;        // plane buffer of job j (j % nbuf) and the parity of its use ((j / nbuf) & 1), as counters
             uint32_t pph = 0;
+#ifdef QGEMV_SEQ_PROFILE
+            long long pprof[4] = {0, 0, 0, 0};  // cycles of this group: waiting to start a job, fetching, row maxima, writing planes
+            long long pt = clock64();
+#define SEQ_PPROF(slot) { const long long now_ = clock64(); pprof[slot] += now_ - pt; pt = now_; }
+#else
+#define SEQ_PPROF(slot)
+#endif
             for (int j = j_lo; j < j_hi; ++j, pph ^= (pb + 1 == nb) ? 1u : 0u, pb = (pb + 1 == nb) ? 0 : pb + 1) {
                 SeqJob next = job;
                 if (j + 1 < j_hi) next = job_at(j + 1);
@@ -715,7 +741,8 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 }
                 if (job.dep >= 0) poll_all(P.fin + job.dep, 80, j);  // an earlier job's buffers are involved
                 if (!group_alive()) break;
-                if (P.trace && gt == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 0] = globaltimer_ns();
+                SEQ_PPROF(0);
+                if (P.trace && gt == 0) P.trace[(size_t(cta) * P.trace_jobs + (j - j_lo)) * 8 + 0] = globaltimer_ns();
                 const int32_t kt_len = job.kt;
                 const int Bj = MOE ? job.rows : Bl;  // activation rows of this job
                 int32_t r_begin, r_end;
@@ -831,6 +858,93 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                     return m;
                 };
                 auto store_unit = [&](int b, uint32_t dst, const uint4& v) { seq_store_unit(dst, v, pow2i(-tc_row_exponent(row_max(b)))); };
+                // More units than a thread keeps in registers (batches of several rows), read from memory as it is:
+                // all of them are fetched at once by 16-byte asynchronous copies into the TOP of the job's plane
+                // buffer (the raw values take half the room of their planes), the row maxima are taken from there,
+                // and the planes are written from the bottom up in waves of four units per thread -- registers
+                // first, a barrier, then the stores.  Groups of eight units (64 activations of one row, 128 bytes raw,
+                // 256 bytes of planes) are numbered in address order; the planes of group g end at or below byte
+                // 256 (g + 1) and the raw values of group g' start at (end of buffer) - 128 (G - g'), so a wave only
+                // overwrites raw values of its own groups (already in registers) and of earlier waves.
+                bool staged = !from_pub && n_work > kKeep * 128;
+                if constexpr (FUSE) staged = staged && job.act == 0 && !job.norm_w;
+                if (staged) {
+                    const uint32_t raw0 = xb + uint32_t(n_slots) * xslot_bytes - uint32_t(n_slots * Bj) * 128u;
+                    // a thread's units are 128 apart, i.e. 16 groups: (slot, row) of the next one without a division
+                    const int g0 = gt >> 3, slot_first = g0 / Bj, b_first = g0 - slot_first * Bj;
+                    const int q16 = 16 / Bj, r16 = 16 - q16 * Bj;
+                    auto step = [&](int& slot, int& b) {
+                        slot += q16, b += r16;
+                        if (b >= Bj) b -= Bj, ++slot;
+                    };
+                    {
+                        int slot = slot_first, b = b_first;
+#pragma unroll 1
+                        for (int wu = gt; wu < n_work; wu += 128, step(slot, b)) {
+                            int32_t u = slot + xs0;
+                            if (u >= kt_len) u -= kt_len;
+                            const int64_t xr = MOE ? int64_t(job.rowmap[b]) : int64_t(b);
+                            cp_async16(raw0 + uint32_t(wu) * 16u, job.x + xr * job.x_stride + u * 64 + (wu & 7) * 8);
+                        }
+                    }
+                    cp_async_wait_all();
+                    named_bar_sync(bar_id, 128);
+                    SEQ_PPROF(1);
+                    {   // row maxima: kept in a register while the row stays the same (it does when B divides 16)
+                        int slot = slot_first, b = b_first, bm = b_first;
+                        uint32_t m = 0;
+#pragma unroll 1
+                        for (int wu = gt; wu < n_work; wu += 256) {   // two units a round, their loads together
+                            const bool two = wu + 128 < n_work;
+                            const uint4 v0 = lds128(raw0 + uint32_t(wu) * 16u);
+                            const uint4 v1 = two ? lds128(raw0 + uint32_t(wu + 128) * 16u) : make_uint4(0, 0, 0, 0);
+                            const uint32_t m0 = unit_max(v0), m1 = unit_max(v1);
+                            if (b != bm) {
+                                if (m) atomicMax(wmax + bm, m);
+                                bm = b, m = 0;
+                            }
+                            m = max(m, m0);
+                            step(slot, b);
+                            if (two) {
+                                if (b != bm) {
+                                    if (m) atomicMax(wmax + bm, m);
+                                    bm = b, m = 0;
+                                }
+                                m = max(m, m1);
+                                step(slot, b);
+                            }
+                        }
+                        if (m) atomicMax(wmax + bm, m);
+                    }
+                    named_bar_sync(bar_id, 128);
+                    SEQ_PPROF(2);
+                    if (gt < 8) rowmax2[pb * 8 + gt] = row_max(gt);
+                    {
+                        int slot = slot_first, b = b_first;
+#pragma unroll 1
+                        for (int w0 = gt; w0 < n_work + gt; w0 += 4 * 128) {   // (the same number of rounds for every thread)
+                            uint4 v[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                v[i] = make_uint4(0, 0, 0, 0);
+                                if (w0 + i * 128 < n_work) v[i] = lds128(raw0 + uint32_t(w0 + i * 128) * 16u);
+                            }
+                            named_bar_sync(bar_id, 128);
+                            const uint32_t in_group = uint32_t((gt & 7) >> 2) * 128u + uint32_t(gt & 3) * 4u;   // (unit mod 8 = gt mod 8)
+#pragma unroll 1
+                            for (int i = 0; i < 4; i += 2) {
+                                const int b0 = b;
+                                const uint32_t d0 = xb + uint32_t(slot) * xslot_bytes + uint32_t(b) * 256u + in_group;
+                                step(slot, b);
+                                const int b1 = b;
+                                const uint32_t d1 = xb + uint32_t(slot) * xslot_bytes + uint32_t(b) * 256u + in_group;
+                                step(slot, b);
+                                if (w0 + i * 128 < n_work) store_unit(b0, d0, v[i]);
+                                if (w0 + (i + 1) * 128 < n_work) store_unit(b1, d1, v[i + 1]);
+                            }
+                        }
+                    }
+                } else {
                 uint4 keep[kKeep];
                 int kb[kKeep];
                 uint32_t kdst[kKeep];
@@ -926,13 +1040,19 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                         }
                     }
                 }
+                }
                 fence_proxy_async_smem();  // the planes are read by the tensor core (async proxy)
                 named_bar_sync(bar_id, 128);
+                SEQ_PPROF(3);
                 if (gt == 0) mbar_arrive(sbase + SeqSmem::kBarXReady + 8 * pb);
-                if (P.trace && gt == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 1] = globaltimer_ns();
+                if (P.trace && gt == 0) P.trace[(size_t(cta) * P.trace_jobs + (j - j_lo)) * 8 + 1] = globaltimer_ns();
                 (void)alive;
                 job = next;
             }
+#ifdef QGEMV_SEQ_PROFILE
+            if (P.trace && gt == 0)
+                for (int z = 0; z < 4; ++z) P.trace[size_t(gridDim.x) * P.trace_jobs * 8 + size_t(gridDim.x) * 4 + size_t(cta) * 4 + z] = (unsigned long long)pprof[z];
+#endif
         } else if (grp == 1) {
             // ---------------- EPILOGUE ----------------
             const int q = warp & 3;
@@ -988,7 +1108,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                         continue;
                     }
                     tc_fence_after();
-                    if (P.trace && gt == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 5] = globaltimer_ns();  // the last one stays
+                    if (P.trace && gt == 0) P.trace[(size_t(cta) * P.trace_jobs + (j - j_lo)) * 8 + 5] = globaltimer_ns();  // the last one stays
                     const int n = sg.tile * 128 + row;
                     // every contributor after the first starts its range inside this tile (slot 0 of its
                     // pair); the first one's range may have started in an earlier tile
@@ -1034,7 +1154,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                     if (lane == 0) mbar_arrive(sbase + SeqSmem::kBarDFree + 8 * acc);  // the accumulator may be overwritten
                     ++nseg;
                 }
-                if (P.trace && gt == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 2] = globaltimer_ns();
+                if (P.trace && gt == 0) P.trace[(size_t(cta) * P.trace_jobs + (j - j_lo)) * 8 + 2] = globaltimer_ns();
                 // this CTA's rows and parts of job j are stored; its plane buffer may be reused
                 named_bar_sync(bar_id, 128);
                 if (gt == 0) {
@@ -1177,7 +1297,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                         }
                     }
                 }
-                if (P.trace && gt == 0) P.trace[(size_t(cta) * P.n_jobs + j) * 8 + 6] = globaltimer_ns();
+                if (P.trace && gt == 0) P.trace[(size_t(cta) * P.trace_jobs + (j - j_lo)) * 8 + 6] = globaltimer_ns();
                 // (the epilogues of the job are through, see above: fin[j] == grid means that all of y is there)
                 named_bar_sync(bar_id, 128);
                 if (!MOE && gt == 0) red_release_add(P.fin + j, 1u);
@@ -1187,6 +1307,9 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
     }
     // ---- every role is through (or has given up): the last CTA to leave puts the counters back to zero ----
     __syncthreads();
+    if constexpr (MOE) {
+        if (P.trace && threadIdx.x == 0) P.trace[size_t(grid) * P.trace_jobs * 8 + size_t(cta) * 4 + 2] = globaltimer_ns();
+    }
     if (threadIdx.x == 0 && !*abort_flag && atom_release_add(P.barrier, 1u) == unsigned(grid) - 1u) {
         for (int i = 0; i < P.n_jobs; ++i) P.fin[i] = 0u;  // nobody polls any more
         P.barrier[0] = 0u;

@@ -110,6 +110,12 @@ __device__ __forceinline__ void pdl_launch_dependents() {
 }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+// ---- 16-byte asynchronous copies global -> shared (through L2 only) -----------------------------
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 // ---- shared-memory vector access ---------------------------------------------------------------
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 v;

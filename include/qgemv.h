@@ -392,8 +392,11 @@ int qgemv_dequant_f32(qgemv_handle* h, const qgemv_weight* w, int which, float* 
  * (qgemv_sequence_run) instead stores 8 x 8 bytes per (CTA, job) at [(cta * n_jobs + job) * 8 + k],
  * all %globaltimer: [0] conversion of the job's activations begins (its dependencies are met), [1] digit
  * planes ready, [3] MMA issuer sees them, [7] its first stage of the job issued, [4] its last, [5] last
- * accumulator seen by the epilogue, [2] rows / parts stored, [6] split tile added up and stored.  The
- * caller zeroes and reads the buffer; the stamps cost time, so a traced run is slower. */
+ * accumulator seen by the epilogue, [2] rows / parts stored, [6] split tile added up and stored.  An
+ * expert-list launch (qgemv_moe_gemv on the tensor-core layout) stores the same eight stamps per (CTA, problem
+ * of the CTA's own range) at [(cta * 32 + local problem) * 8 + k], then per CTA at [(ctas * 32) * 8 + cta * 4 +
+ * k]: [0] kernel entered, [1] router lists walked, [2] all roles through.  The caller zeroes and reads the
+ * buffer; the stamps cost time, so a traced run is slower. */
 int qgemv_set_trace(qgemv_handle* h, void* dev_buf);
 /* Synchronises `stream`, reads and clears the device status word. */
 int qgemv_last_device_status(qgemv_handle* h, void* stream, qgemv_dev_status* out);
