@@ -686,15 +686,17 @@ def run_moe(args, T=None):
                    "us_per_layer": round(ms * 1e3 / args.steps / L, 2),
                    "cache": "four layers of distinct experts; at 1 token the touched experts (21 MB per layer) fit L2"},
         "roofline": {"bound": "hbm", "achieved": round(gbs, 2), "peak": peak, "unit": UNIT, "frac": round(gbs / peak, 4),
-                     "traffic": int(1.01 * (nbytes // (2 * L))),
-                     "traffic_source": "ncu capture at 8 tokens (profiles/moe_stream_128experts_t8_traffic.md): DRAM read+write = "
-                                       "1.004-1.027 x the touched experts' bytes per launch; scaled by bytes",
+                     "traffic": int((1.04 if tc else 1.01) * (nbytes // (2 * L))),
+                     "traffic_source": ("ncu capture at 8 tokens (profiles/moe_expert_list_128experts_t8_traffic.md): DRAM read+write = "
+                                        "1.019-1.066 x the touched experts' bytes per launch; scaled by bytes") if tc else
+                                       ("ncu capture at 8 tokens (profiles/moe_stream_128experts_t8_traffic.md): DRAM read+write = "
+                                        "1.004-1.027 x the touched experts' bytes per launch; scaled by bytes"),
                      "peak_kind": kind, "kernel": "gemv_seq_kernel<4, expert list>" if tc else "moe_stream_kernel<NVFP4>",
                      "bytes_per_launch": nbytes // (2 * L), "us_per_launch": round(ms * 1e3 / (2 * L * args.steps), 2)},
         "e2e": {"value": round(nbytes * args.steps / (ms_host * 1e-3) / 1e9, 2), "unit": UNIT,
                 "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 4,
                 "ms_per_step": round(ms_host / args.steps, 5)},
-        "gpu_launches": 4 * L * args.steps, "clocks": clocks,
+        "gpu_launches": (2 if tc else 4) * L * args.steps, "clocks": clocks,
         "verified": bool(err_gu < TOL_BF16 and err_dn < TOL_F32),
         "verify": {"rel_l2_gate_up_bf16": float(f"{err_gu:.3e}"), "rel_l2_down_f32": float(f"{err_dn:.3e}"),
                    "tol": [TOL_BF16, TOL_F32], "checked": f"{len(slots)} sampled (token, expert) slots of layer 0, all rows, fp64 oracle"},

@@ -1156,7 +1156,8 @@ int moe_tc(qgemv_handle* h, const qgemv_weight* w, const int32_t* expert_ids, co
         ring = std::min({ring, qg::kTcMaxRing, qg::SeqSmem::max_ring_items(P.npad) / kStage});
         if (ring >= 4 || P.nbuf == 1) break;
     }
-    if (ring < 2) return QGEMV_ERR_UNSUPPORTED_SHAPE;  // K too long for the digit planes of one expert beside a ring
+    if (ring < 2 || ring * kStage * qg::kTcItemBytes < qg::kMoeWalkBytes || slots > qg::kMoeMaxSlots)
+        return QGEMV_ERR_UNSUPPORTED_SHAPE;  // K too long for the digit planes of one expert beside a ring
     P.ring = ring;
     P.moe_smem = (qg::SeqSmem::total(P.x_slots, P.npad, P.nbuf, ring, kStage) + 127) / 128 * 128;
     const size_t smem = size_t(P.moe_smem) + kWalk;

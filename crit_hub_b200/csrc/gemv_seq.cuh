@@ -102,12 +102,14 @@ struct SeqParams {
     const float* expert_ts;
     uint64_t expert_stride;
     int32_t slots, topk, n_experts, per_slot;  // per_slot: activation row = the entry's index (else its token)
-    int32_t moe_smem;                          // offset of the walk's scratch in shared memory (behind the ring)
+    int32_t moe_smem;                          // offset of the CTA's problem table in shared memory (behind the ring)
     SeqJob moe_job;
 };
 constexpr int kMoeMaxExperts = 512;   // experts of a stacked weight that the expert-list mode takes
 constexpr int kMoeLocalJobs = 32;     // problems that one CTA's range may touch
-constexpr int kMoeSmemBytes = (2 * kMoeMaxExperts + kMoeLocalJobs * kProbInts + 32) * 4;
+constexpr int kMoeMaxSlots = 4096;    // (token, choice) entries of the lists
+constexpr int kMoeSmemBytes = (kMoeLocalJobs * kProbInts + 32) * 4;            // the table, kept for the whole launch
+constexpr int kMoeWalkBytes = (2 * kMoeMaxExperts + kMoeMaxSlots) * 4;          // the walk's scratch: lies in the (still empty) ring
 
 struct SeqSmem {
     static constexpr int kBarFull = 0;      // kTcMaxRing
@@ -358,9 +360,12 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
     if constexpr (MOE) {
         // ---- the router walk: entries per expert (shared-memory histogram), problems per expert and their prefix
         // (one warp), then one warp per problem of this CTA's range collects the problem's rows in list order ----
-        int* m_counts = reinterpret_cast<int*>(sq_smem + P.moe_smem);  // [n_experts] entries
+        // (counts, prefix and a copy of the lists live where the weight ring will be: no copy is issued before
+        // the walk is over and its accesses are fenced off against the asynchronous proxy)
+        int* m_counts = reinterpret_cast<int*>(sq_smem + SeqSmem::ring_off(P.x_slots, npad, nb));  // [n_experts] entries
         int* m_base = m_counts + kMoeMaxExperts;                       // [n_experts] first problem
-        int* tab = m_base + kMoeMaxExperts;                            // [kMoeLocalJobs][kProbInts]
+        int* m_ids = m_base + kMoeMaxExperts;                          // [slots] the lists
+        int* tab = reinterpret_cast<int*>(sq_smem + P.moe_smem);       // [kMoeLocalJobs][kProbInts]
         volatile int* m_misc = tab + kMoeLocalJobs * kProbInts;        // [0] problems, [1] an id out of range
         m_tab = tab;
         const int E = P.n_experts, slots = P.slots, cap = P.B;
@@ -371,6 +376,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
         __syncthreads();
         for (int i = threadIdx.x; i < slots; i += kSeqThreads) {
             const int e = __ldcg(P.ids + i);
+            m_ids[i] = e;
             if (unsigned(e) >= unsigned(E)) {
                 m_misc[1] = 1;
             } else {
@@ -429,7 +435,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
             int seen = 0;
             for (int i0 = 0; i0 < slots && seen < r0 + rows; i0 += 32) {
                 const int i = i0 + lane;
-                const int id = i < slots ? __ldcg(P.ids + i) : -1;
+                const int id = i < slots ? m_ids[i] : -1;
                 const unsigned m = __ballot_sync(0xFFFFFFFFu, id == e);
                 const int r = seen + __popc(m & ((1u << lane) - 1u)) - r0;
                 if (id == e && r >= 0 && r < rows) {
@@ -439,6 +445,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 seen += __popc(m);
             }
         }
+        fence_proxy_async_smem();  // the scratch becomes the ring: written next by bulk copies
         __syncthreads();
     }
     if constexpr (MOE) {

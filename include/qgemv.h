@@ -363,9 +363,15 @@ int qgemv_gemm_skinny_plan(int fmt, int64_t N, int64_t K, int M, int sm_count, q
  *   out[t*topk + j][:] = W[expert_ids[t][j]] . x[row][:],
  *   row = t (per_slot_input == 0, gate/up stage) or t*topk + j (per_slot_input == 1, down stage).
  * experts: a stacked weight from qgemv_load_stacked; expert_ids: device int32 [T][topk];
- * x: device bf16; out: device [T*topk][N] bf16 or fp32.  T*topk <= 4096.
- * Experts with K > 2048 run as several launches over K chunks plus a sum (fp32 partial results in
- * a scratch that belongs to the handle: keep calls that share a handle on one stream).
+ * x: device bf16; out: device [T*topk][N] bf16 or fp32.  T*topk <= 4096.  An id outside the stacked
+ * weight is reported in the status word (QGEMV_ERR_BOUNDS, where 21) and nothing is computed.
+ * Experts in the tensor-core layout (QGEMV_FMT_NVFP4_TC, the faster choice from a few tokens on) run as
+ * ONE launch that also walks the lists: at most 512 experts; the digit planes of min(8, T) rows x K must
+ * fit beside a weight ring in shared memory (K <= 4096 always does); QGEMV_ERR_UNSUPPORTED_SHAPE
+ * otherwise.  The split-tile scratch belongs to the handle: keep calls that share a handle on one stream.
+ * Lane-order experts (QGEMV_FMT_NVFP4, QGEMV_FMT_FP8) run as a router-walk kernel plus a streaming
+ * kernel; with K > 2048 as several launches over K chunks plus a sum (fp32 partial results in a scratch
+ * of the handle).
  * No listed engine publishes an MoE kernel; the shape is the registry's `host_expert_gbs`
  * probe slot (engines/crit-labs/mtp5-nvfp4-drafts/evidence/crit-eval.json:124). */
 int qgemv_moe_gemv(qgemv_handle* h, const qgemv_weight* experts, const int32_t* expert_ids,
