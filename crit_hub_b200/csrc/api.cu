@@ -1107,11 +1107,29 @@ int moe_tc(qgemv_handle* h, const qgemv_weight* w, const int32_t* expert_ids, co
            int per_slot_input, void* out, int out_dtype, cudaStream_t s) {
     const int grid = gemv_grid(h);
     if (grid > h->sm_count) return QGEMV_ERR_UNSUPPORTED_SHAPE;  // the CTAs wait on one another: one per SM at most
-    // rows per problem: no more than there are tokens (the digit planes and the accumulator are sized for the
-    // largest problem)
-    const int B = std::min(QGEMV_MAX_BATCH, T);
     const int slots = T * topk;
-    if (w->n_stack > qg::kMoeMaxExperts) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+    if (w->n_stack > qg::kMoeMaxExperts || slots > qg::kMoeMaxSlots) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+    // Rows per problem (B): no more than there are tokens, and as many of eight as leave a weight ring of three
+    // stages beside the digit planes of B rows x K (halved until they do: a long K gets problems of fewer
+    // rows, and an expert with more entries is then read once per problem).
+    constexpr int kStage = 4;
+    constexpr int kWalk = (qg::kMoeSmemBytes + 127) / 128 * 128;   // the CTA's problem table, behind the ring
+    const int cap = (h->cfg.tc_smem_kb > 0 ? std::min(h->cfg.tc_smem_kb, 227) : 227) * 1024 - kWalk;
+    const int x_slots = int(w->units);   // a CTA's share of an expert may span a whole row tile
+    int B = std::min(QGEMV_MAX_BATCH, T), npad = 0, nbuf = 1, ring = 0;
+    for (;; B = (B + 1) / 2) {
+        npad = (8 * B + 15) / 16 * 16;
+        // two plane buffers (a CTA's range mostly touches two experts) when that leaves a ring of four stages
+        for (nbuf = 2; nbuf >= 1; --nbuf) {
+            const int base = qg::SeqSmem::ring_off(x_slots, npad, nbuf);
+            ring = (cap - base) / (kStage * qg::kTcItemBytes);
+            ring = std::min({ring, qg::kTcMaxRing, qg::SeqSmem::max_ring_items(npad) / kStage});
+            if (ring >= 4 || nbuf == 1) break;
+        }
+        if (ring >= 3 || B == 1) break;
+    }
+    if (ring < 2 || ring * kStage * qg::kTcItemBytes < qg::kMoeWalkBytes)
+        return QGEMV_ERR_UNSUPPORTED_SHAPE;  // K too long for the digit planes of one row beside a ring
     const int64_t most_prob = std::min<int64_t>(w->n_stack, slots) + slots / B;   // problems the lists can make
     if ((most_prob + grid - 1) / grid + 1 > qg::kMoeLocalJobs) return QGEMV_ERR_UNSUPPORTED_SHAPE;
     qg::SeqParams P;
@@ -1135,8 +1153,9 @@ int moe_tc(qgemv_handle* h, const qgemv_weight* w, const int32_t* expert_ids, co
     P.spin_limit = default_spin(h);
     P.n_jobs = 0;
     P.B = B;
-    P.npad = (8 * B + 15) / 16 * 16;
-    P.x_slots = mj.kt;   // a CTA's share of an expert may span a whole row tile
+    P.npad = npad;
+    P.x_slots = x_slots;
+    P.nbuf = nbuf;
     P.debug = h->cfg.debug;
     P.trace = h->tc_trace;
     P.trace_jobs = qg::kMoeLocalJobs;
@@ -1145,19 +1164,6 @@ int moe_tc(qgemv_handle* h, const qgemv_weight* w, const int32_t* expert_ids, co
     P.slots = slots, P.topk = topk, P.n_experts = w->n_stack, P.per_slot = per_slot_input ? 1 : 0;
     P.expert_ts = w->dev_tensor_scale;
     P.expert_stride = w->blob_bytes;
-    constexpr int kStage = 4;
-    constexpr int kWalk = (qg::kMoeSmemBytes + 127) / 128 * 128;   // the walk's scratch, behind the ring
-    const int cap = (h->cfg.tc_smem_kb > 0 ? std::min(h->cfg.tc_smem_kb, 227) : 227) * 1024 - kWalk;
-    // two plane buffers (a CTA's range mostly touches two experts) when that leaves a ring of four stages
-    int ring = 0;
-    for (P.nbuf = 2; P.nbuf >= 1; --P.nbuf) {
-        const int base = qg::SeqSmem::ring_off(P.x_slots, P.npad, P.nbuf);
-        ring = (cap - base) / (kStage * qg::kTcItemBytes);
-        ring = std::min({ring, qg::kTcMaxRing, qg::SeqSmem::max_ring_items(P.npad) / kStage});
-        if (ring >= 4 || P.nbuf == 1) break;
-    }
-    if (ring < 2 || ring * kStage * qg::kTcItemBytes < qg::kMoeWalkBytes || slots > qg::kMoeMaxSlots)
-        return QGEMV_ERR_UNSUPPORTED_SHAPE;  // K too long for the digit planes of one expert beside a ring
     P.ring = ring;
     P.moe_smem = (qg::SeqSmem::total(P.x_slots, P.npad, P.nbuf, ring, kStage) + 127) / 128 * 128;
     const size_t smem = size_t(P.moe_smem) + kWalk;

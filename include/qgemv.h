@@ -366,9 +366,10 @@ int qgemv_gemm_skinny_plan(int fmt, int64_t N, int64_t K, int M, int sm_count, q
  * x: device bf16; out: device [T*topk][N] bf16 or fp32.  T*topk <= 4096.  An id outside the stacked
  * weight is reported in the status word (QGEMV_ERR_BOUNDS, where 21) and nothing is computed.
  * Experts in the tensor-core layout (QGEMV_FMT_NVFP4_TC, the faster choice from a few tokens on) run as
- * ONE launch that also walks the lists: at most 512 experts; the digit planes of min(8, T) rows x K must
- * fit beside a weight ring in shared memory (K <= 4096 always does); QGEMV_ERR_UNSUPPORTED_SHAPE
- * otherwise.  The split-tile scratch belongs to the handle: keep calls that share a handle on one stream.
+ * ONE launch that also walks the lists: at most 512 experts; an expert's entries are worked on up to
+ * min(8, T) rows at a time, fewer when the digit planes of that many rows x K would not fit beside a weight
+ * ring in shared memory (from K > 4096 on), down to one; QGEMV_ERR_UNSUPPORTED_SHAPE beyond that (K > 23000).
+ * The split-tile scratch belongs to the handle: keep calls that share a handle on one stream.
  * Lane-order experts (QGEMV_FMT_NVFP4, QGEMV_FMT_FP8) run as a router-walk kernel plus a streaming
  * kernel; with K > 2048 as several launches over K chunks plus a sum (fp32 partial results in a scratch
  * of the handle).

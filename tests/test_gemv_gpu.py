@@ -373,12 +373,13 @@ def test_moe_gemv(qg, handle, T, per_slot, fmt_name):
     w.unload()
 
 
-@pytest.mark.parametrize("fmt_name", ["lane", "tc"])
-def test_moe_gemv_long_k(qg, handle, fmt_name):
+@pytest.mark.parametrize("fmt_name,K", [("lane", 4352), ("tc", 4352), ("tc", 7168)])
+def test_moe_gemv_long_k(qg, handle, fmt_name, K):
     """Experts with K > 2048: lane order runs as K chunks of the streaming kernel, added in chunk order; the
-    tensor-core layout holds the digit planes of the whole K."""
+    tensor-core layout holds the digit planes of the whole K, for fewer rows at a time when K is very long
+    (7168: four rows, so the experts with more entries make two problems)."""
     import torch
-    E, topk, T, N, K = 16, 4, 8, 256, 4352
+    E, topk, T, N = 16, 4, 8, 256
     fmt = qg.FMT_NVFP4_TC if fmt_name == "tc" else qg.FMT_NVFP4
     codes, scales, ts = _experts(E, N, K, seed=900)
     blobs = np.stack([qg.pack(fmt, codes[e], scales[e], float(ts[e])) for e in range(E)])
