@@ -1203,8 +1203,9 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                     pending = c_lo == cta;
                     lo_slot = job_slot(job, j, c_lo, tile);
                 }
-                // how far have ALL CTAs come with this step?  One probe per job, in flight with nothing else to do
-                if (!MOE && gt == 0 && known + 1 < j && ld_acquire(P.fin + known + 1) >= unsigned(grid)) *fin_all = ++known;
+                // (how far ALL CTAs have come -- fin_all, which lets the epilogues reuse a parts buffer without asking
+                // global memory themselves -- is looked up below while this group waits anyway: a probe here would put
+                // a round trip to L2 into every job of a group whose time per job bounds the small jobs)
                 if (!group_alive()) break;
                 // this CTA's own part of the tile comes first, and the other contributors finish at about the same
                 // time: nothing is asked of global memory before this CTA's epilogues are through with the job
