@@ -357,6 +357,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
     int32_t g_total = 0, g_begin = 0, g_end = 0, g_per = 1;
     int g_gj = grid;
     const int* m_tab = nullptr;  // expert list: the problems this CTA's range touches, kProbInts ints each
+    uint32_t m_launch_no = 0, m_run_no = 0;  // expert list: the launch counts, fetched while the lists are walked
     if constexpr (MOE) {
         // ---- the router walk: entries per expert (shared-memory histogram), problems per expert and their prefix
         // (one warp), then one warp per problem of this CTA's range collects the problem's rows in list order ----
@@ -371,6 +372,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
         const int E = P.n_experts, slots = P.slots, cap = P.B;
         if (P.trace && threadIdx.x == 0) P.trace[size_t(grid) * P.trace_jobs * 8 + size_t(cta) * 4 + 0] = globaltimer_ns();
         pdl_wait();  // the lists are the work of whatever ran before this launch
+        m_launch_no = __ldcg(P.barrier + 2), m_run_no = __ldcg(P.fin + P.n_jobs);
         for (int e = threadIdx.x; e < E; e += kSeqThreads) m_counts[e] = 0;
         if (threadIdx.x == 0) m_misc[0] = 0, m_misc[1] = 0;
         __syncthreads();
@@ -715,7 +717,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
             }
         };
         pdl_wait();  // whatever ran before this launch has finished with x, y and the scratch, and has counted itself
-        const uint32_t launch_no = __ldcg(P.barrier + 2), run_no = __ldcg(P.fin + P.n_jobs);
+        const uint32_t launch_no = MOE ? m_launch_no : __ldcg(P.barrier + 2), run_no = MOE ? m_run_no : __ldcg(P.fin + P.n_jobs);
 
         if (grp == 0) {
             // ---------------- PLANES ----------------
