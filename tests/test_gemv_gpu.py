@@ -432,6 +432,34 @@ def test_moe_gemv_repeated_and_bad_ids(qg, handle, fmt_name):
     w.unload()
 
 
+def test_moe_gemv_tc_many_experts_and_limits(qg, handle):
+    """Tensor-core layout: 300 experts with top-1 routing (every problem a single row, most experts untouched), bf16
+    output; a stacked weight of more than 512 experts is refused by the expert-list launch."""
+    import torch
+    E, topk, T, N, K = 300, 1, 40, 128, 64
+    codes, scales, ts = _experts(E, N, K, seed=41)
+    blob = [qg.pack(qg.FMT_NVFP4_TC, codes[e], scales[e], float(ts[e])) for e in range(E)]
+    w = handle.load_stacked(np.stack(blob))
+    rng = np.random.default_rng(3)
+    ids = rng.integers(0, E, size=(T, topk)).astype(np.int32)
+    x = O.make_x(T, K, seed=4)
+    ref = O.moe_gemv_nvfp4_f64(codes, scales, ts, ids, x, per_slot_input=False)
+    xd, idd = U.dev_u16(x), torch.from_numpy(ids).cuda()
+    out = torch.full((T * topk, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    handle.moe_gemv(w, idd.data_ptr(), xd.data_ptr(), T, topk, False, out.data_ptr(), qg.OUT_BF16)
+    torch.cuda.synchronize()
+    U.status_ok(handle)
+    got = out.float().cpu().numpy()
+    assert not np.isnan(got).any()
+    assert O.rel_l2(got, ref) < TOL_BF16
+    w.unload()
+    big = handle.load_stacked(np.stack([blob[e % E] for e in range(513)]))
+    with pytest.raises(qg.QgemvError) as e:
+        handle.moe_gemv(big, idd.data_ptr(), xd.data_ptr(), T, topk, False, out.data_ptr(), qg.OUT_BF16)
+    assert e.value.status == qg.ERR_UNSUPPORTED_SHAPE
+    big.unload()
+
+
 # ---- tensor-parallel exchange ----------------------------------------------------------------------
 def test_tp_allreduce_single_rank(qg):
     """World of one: the exchange degenerates to push-to-self, flag, reduce; replaying it checks
