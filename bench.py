@@ -590,7 +590,7 @@ def run_moe(args, T=None):
     import torch
 
     import crit_hub_b200 as qg
-    from crit_hub_b200.stack import synth_nvfp4
+    from crit_hub_b200.stack import synth_nvfp4, synth_nvfp4_dev
     from oracle import oracle as O
 
     torch.cuda.set_device(0)
@@ -603,16 +603,22 @@ def run_moe(args, T=None):
     host0 = {}
 
     def stacked(N, K, seed0, keep=None):
+        """E seeded experts as one stacked weight: laid out on the device (tensor-core layout) or packed on the host."""
+        if tc:
+            mats = [synth_nvfp4_dev(N, K, seed0 + e, dev) for e in range(E)]
+            if keep is not None:
+                host0[keep] = [(c.cpu().numpy(), s.cpu().numpy()) for c, s in mats]
+            return h.load_stacked_device(fmt, [c.data_ptr() for c, _ in mats], [s.data_ptr() for _, s in mats], N, K, [1.0] * E)
         blobs = []
         for e in range(E):
             c, s = synth_nvfp4(N, K, seed0 + e, dev)
             if keep is not None:
                 host0.setdefault(keep, []).append((c, s))
             blobs.append(qg.pack(fmt, c, s, 1.0))
-        return np.stack(blobs)
+        return h.load_stacked(np.stack(blobs))
 
-    gu = [h.load_stacked(stacked(2 * inter, hidden, 1000 * l, "gu" if l == 0 else None)) for l in range(L)]
-    dn = [h.load_stacked(stacked(hidden, inter, 1000 * l + 500, "dn" if l == 0 else None)) for l in range(L)]
+    gu = [stacked(2 * inter, hidden, 1000 * l, "gu" if l == 0 else None) for l in range(L)]
+    dn = [stacked(hidden, inter, 1000 * l + 500, "dn" if l == 0 else None) for l in range(L)]
     per_expert = gu[0].weight_bytes + dn[0].weight_bytes
     g = torch.Generator(device=dev)
     g.manual_seed(T)

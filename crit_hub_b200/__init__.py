@@ -113,6 +113,8 @@ def _load() -> C.CDLL:
     L.qgemv_load_stacked.argtypes = [vp, vp, sz, i32, C.POINTER(vp)]
     L.qgemv_unload.argtypes = [vp, vp]
     L.qgemv_load_device.argtypes = [vp, i32, vp, vp, C.c_float, i64, i64, C.POINTER(Shard), vp, C.POINTER(vp)]
+    L.qgemv_load_stacked_device.argtypes = [vp, i32, C.POINTER(vp), C.POINTER(vp), C.POINTER(C.c_float), i32, i64, i64,
+                                            C.POINTER(Shard), vp, C.POINTER(vp)]
     L.qgemv_weight_read.argtypes = [vp, vp, vp, sz]
     L.qgemv_pack_header.argtypes = [i32, C.c_float, i64, i64, C.POINTER(Shard), vp]
     L.qgemv_set_host_threads.argtypes = [i32]
@@ -305,6 +307,23 @@ class QGemv:
         n = (shard.n1 - shard.n0) if shard else N
         k = (shard.k1 - shard.k0) if shard else K
         return Weight(self, w.value, fmt, n, k, 1)
+
+    def load_stacked_device(self, fmt: int, codes_ptrs: list[int], scales_ptrs: list[int], N: int, K: int,
+                            tensor_scales, shard: Shard | None = None, stream: int = 0) -> Weight:
+        """The experts of an MoE layer from canonical NVFP4 arrays in device memory (one pair of device pointers
+        and one tensor scale per expert), packed by a kernel into one stacked weight; NVFP4_TC only."""
+        E = len(codes_ptrs)
+        if E < 1 or len(scales_ptrs) != E or len(tensor_scales) != E:
+            raise ValueError("one codes pointer, one scales pointer and one tensor scale per expert")
+        cp = (C.c_void_p * E)(*codes_ptrs)
+        sp = (C.c_void_p * E)(*scales_ptrs)
+        ts = (C.c_float * E)(*[float(t) for t in tensor_scales])
+        w = C.c_void_p()
+        _check(_load().qgemv_load_stacked_device(self._ptr, fmt, cp, sp, ts, E, N, K, C.byref(shard) if shard else None,
+                                                 stream, C.byref(w)), "load_stacked_device")
+        n = (shard.n1 - shard.n0) if shard else N
+        k = (shard.k1 - shard.k0) if shard else K
+        return Weight(self, w.value, fmt, n, k, E)
 
     def load_stacked(self, blobs: np.ndarray) -> Weight:
         """blobs: u8 [E][bytes_each], every row a packed blob of the same shape and format."""

@@ -537,34 +537,57 @@ int qgemv_load_stacked(qgemv_handle* h, const void* host_blobs, size_t bytes_eac
     return QGEMV_OK;
 }
 
-int qgemv_load_device(qgemv_handle* h, int fmt, const void* codes_dev, const void* scales_dev, float tensor_scale,
-                      int64_t N, int64_t K, const qgemv_shard* shard, void* stream, qgemv_weight** out) {
-    if (!h || !codes_dev || !scales_dev || !out) return QGEMV_ERR_INVALID_ARG;
-    *out = nullptr;
-    if (fmt != QGEMV_FMT_NVFP4_TC) return QGEMV_ERR_UNSUPPORTED_SHAPE;
-    if ((reinterpret_cast<uintptr_t>(codes_dev) & 7u) != 0) return QGEMV_ERR_INVALID_ARG;  // read in 8-byte groups
-    qg_blob_header hd;
-    const int rc0 = qgemv_pack_header(fmt, tensor_scale, N, K, shard, &hd);
-    if (rc0 != QGEMV_OK) return rc0;
-    qgemv_weight* w = nullptr;
-    const int rc = new_weight(h, &hd, 1, size_t(QG_HEADER_BYTES + hd.aux_bytes + hd.payload_bytes), &tensor_scale, &w);
-    if (rc != QGEMV_OK) return rc;
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
+namespace {
+// Packs one canonical NVFP4 matrix (device memory) into blob `which` of a tensor-core-layout weight: header by a
+// copy, payload by the packing kernel.  `hd` must stay alive until the stream has been synchronised.
+bool pack_tc_into(qgemv_handle* h, qgemv_weight* w, int which, const void* codes_dev, const void* scales_dev,
+                  const qg_blob_header* hd, int64_t N, int64_t K, const qgemv_shard* shard, cudaStream_t st) {
+    uint8_t* blob = w->dev_blob + uint64_t(which) * w->blob_bytes;
     qg::PackTcParams P;
     P.codes = static_cast<const uint8_t*>(codes_dev);
     P.scales = static_cast<const uint8_t*>(scales_dev);
-    P.payload = w->dev_blob + QG_HEADER_BYTES + hd.aux_bytes;
+    P.payload = blob + QG_HEADER_BYTES + hd->aux_bytes;
     P.N = N, P.K = K;
     P.n0 = shard ? shard->n0 : 0, P.k0 = shard ? shard->k0 : 0;
-    P.n = hd.N, P.k = hd.K;
-    P.tiles = hd.n_panels / 8, P.kt = hd.units_per_panel;
+    P.n = hd->N, P.k = hd->K;
+    P.tiles = hd->n_panels / 8, P.kt = hd->units_per_panel;
     const int64_t chunks = P.tiles * P.kt * (QG_TC_ITEM_BYTES / 16);
     const unsigned blocks = unsigned(std::min<int64_t>((chunks + 255) / 256, int64_t(h->sm_count) * 16));
-    bool ok = cudaMemcpyAsync(w->dev_blob, &hd, sizeof hd, cudaMemcpyHostToDevice, st) == cudaSuccess;
-    if (ok) {
-        qg::pack_tc_kernel<<<blocks, 256, 0, st>>>(P);
-        ok = cudaGetLastError() == cudaSuccess && cudaStreamSynchronize(st) == cudaSuccess;  // hd lives on this stack frame
+    if (cudaMemcpyAsync(blob, hd, sizeof *hd, cudaMemcpyHostToDevice, st) != cudaSuccess) return false;
+    qg::pack_tc_kernel<<<blocks, 256, 0, st>>>(P);
+    return cudaGetLastError() == cudaSuccess;
+}
+}  // namespace
+
+int qgemv_load_device(qgemv_handle* h, int fmt, const void* codes_dev, const void* scales_dev, float tensor_scale,
+                      int64_t N, int64_t K, const qgemv_shard* shard, void* stream, qgemv_weight** out) {
+    const void* c[1] = {codes_dev};
+    const void* sc[1] = {scales_dev};
+    return qgemv_load_stacked_device(h, fmt, c, sc, &tensor_scale, 1, N, K, shard, stream, out);
+}
+
+int qgemv_load_stacked_device(qgemv_handle* h, int fmt, const void* const* codes_dev, const void* const* scales_dev,
+                              const float* tensor_scales, int n_stacked, int64_t N, int64_t K, const qgemv_shard* shard,
+                              void* stream, qgemv_weight** out) {
+    if (!h || !codes_dev || !scales_dev || !tensor_scales || !out || n_stacked < 1) return QGEMV_ERR_INVALID_ARG;
+    *out = nullptr;
+    if (fmt != QGEMV_FMT_NVFP4_TC) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+    for (int e = 0; e < n_stacked; ++e) {
+        if (!codes_dev[e] || !scales_dev[e]) return QGEMV_ERR_INVALID_ARG;
+        if ((reinterpret_cast<uintptr_t>(codes_dev[e]) & 7u) != 0) return QGEMV_ERR_INVALID_ARG;  // read in 8-byte groups
     }
+    std::vector<qg_blob_header> hd(static_cast<size_t>(n_stacked));
+    for (int e = 0; e < n_stacked; ++e) {
+        const int rc0 = qgemv_pack_header(fmt, tensor_scales[e], N, K, shard, &hd[size_t(e)]);
+        if (rc0 != QGEMV_OK) return rc0;
+    }
+    qgemv_weight* w = nullptr;
+    const int rc = new_weight(h, &hd[0], n_stacked, size_t(QG_HEADER_BYTES + hd[0].aux_bytes + hd[0].payload_bytes), tensor_scales, &w);
+    if (rc != QGEMV_OK) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    bool ok = true;
+    for (int e = 0; e < n_stacked && ok; ++e) ok = pack_tc_into(h, w, e, codes_dev[e], scales_dev[e], &hd[size_t(e)], N, K, shard, st);
+    ok = cudaStreamSynchronize(st) == cudaSuccess && ok;  // (the headers live in this frame)
     if (!ok) {
         g_last_cuda_error = cudaGetLastError();
         qgemv_unload(h, w);

@@ -100,3 +100,27 @@ def load_nvfp4_linear(handle: QGemv, f: SafetensorsFile, name: str, shard: Shard
     cd = torch.from_numpy(np.ascontiguousarray(codes)).to(dev)
     sd = torch.from_numpy(np.ascontiguousarray(scales)).to(dev)
     return handle.load_device(FMT_NVFP4_TC, cd.data_ptr(), sd.data_ptr(), N, K, ts, shard=shard)
+
+
+def load_nvfp4_experts(handle: QGemv, f: SafetensorsFile, names: list[str], shard: Shard | None = None) -> Weight:
+    """The equally shaped NVFP4 linear layers `names` (the experts of an MoE layer, one tensor triple each:
+    `<name>.weight`, `.weight_scale`, `.weight_scale_2`) as ONE stacked weight in the tensor-core layout, ready
+    for `moe_gemv`; expert e of the stack is names[e].  The arrays go to the device as they are in the file and
+    are laid out there."""
+    import torch
+
+    dev = torch.device("cuda", handle.device)
+    keep, cps, sps, tss = [], [], [], []
+    N = K = None
+    for name in names:
+        codes, scales, ts = nvfp4_linear_arrays(f, name)
+        n, k = scales.shape[0], scales.shape[1] * 16
+        if N is None:
+            N, K = n, k
+        elif (n, k) != (N, K):
+            raise ValueError(f"{name}: {n} x {k}, the first expert is {N} x {K}")
+        cd = torch.from_numpy(np.ascontiguousarray(codes)).to(dev)
+        sd = torch.from_numpy(np.ascontiguousarray(scales)).to(dev)
+        keep += [cd, sd]          # alive until the packing kernels have run (the call returns after them)
+        cps.append(cd.data_ptr()), sps.append(sd.data_ptr()), tss.append(ts)
+    return handle.load_stacked_device(FMT_NVFP4_TC, cps, sps, N, K, tss, shard=shard)

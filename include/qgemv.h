@@ -159,6 +159,14 @@ int qgemv_load_device(qgemv_handle* h, int fmt, const void* codes_dev, const voi
                       int64_t N, int64_t K, const qgemv_shard* shard /* nullable */, void* stream, qgemv_weight** out);
 int qgemv_load_stacked(qgemv_handle* h, const void* host_blobs, size_t bytes_each, int n_stacked,
                        qgemv_weight** out);
+/* The experts of an MoE layer from canonical NVFP4 arrays in device memory: qgemv_load_device for
+ * `n_stacked` equally shaped matrices into one stacked weight.  codes_dev / scales_dev: HOST arrays of
+ * n_stacked device pointers (a checkpoint stores every expert as a tensor of its own); tensor_scales:
+ * host fp32 [n_stacked].  The result is byte for byte what qgemv_load_stacked makes of the host-packed
+ * blobs (zero checksums). */
+int qgemv_load_stacked_device(qgemv_handle* h, int fmt, const void* const* codes_dev, const void* const* scales_dev,
+                              const float* tensor_scales, int n_stacked, int64_t N, int64_t K,
+                              const qgemv_shard* shard /* nullable */, void* stream, qgemv_weight** out);
 int qgemv_unload(qgemv_handle* h, qgemv_weight* w);
 /* Algorithmic weight bytes of one matrix: N*K*0.5625 + 4 (NVFP4) or N*K + 4*N (FP8). */
 int64_t qgemv_weight_bytes(const qgemv_weight* w);

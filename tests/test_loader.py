@@ -68,3 +68,43 @@ def test_checkpoint_layer_to_device(tmp_path, qg, handle):
     w.unload()
     ws.unload()
     f.close()
+
+
+@pytest.mark.gpu
+def test_checkpoint_experts_to_device(tmp_path, qg, handle):
+    """The experts of an MoE layer: one tensor triple each in the file -> one stacked weight laid out on the device,
+    byte for byte the stack of host-packed blobs (checksums aside); and the expert list computes with it."""
+    import torch
+    import gpu_util as U
+    from crit_hub_b200.loader import SafetensorsFile, load_nvfp4_experts
+    E, N, K, T, topk = 6, 256, 192, 5, 2
+    mats = [O.make_nvfp4(N, K, seed=70 + e, ts=0.25 + e / 8.0) for e in range(E)]
+    tensors = {}
+    for e, (c, s, t) in enumerate(mats):
+        tensors[f"mlp.experts.{e}.down.weight"] = ("U8", c)
+        tensors[f"mlp.experts.{e}.down.weight_scale"] = ("F8_E4M3", s)
+        tensors[f"mlp.experts.{e}.down.weight_scale_2"] = ("F32", np.array(t, dtype=np.float32))
+    path = str(tmp_path / "experts.safetensors")
+    write_safetensors(path, tensors)
+    f = SafetensorsFile(path)
+    w = load_nvfp4_experts(handle, f, [f"mlp.experts.{e}.down" for e in range(E)])
+    assert (w.N, w.K) == (N, K)
+    host = np.stack([qg.pack(qg.FMT_NVFP4_TC, c, s, t) for c, s, t in mats])
+    got = w.read_blob().reshape(host.shape)
+    # (the header's checksum field is the only difference: the device packer leaves it zero)
+    diff = np.nonzero(got != host)
+    assert diff[1].size == 0 or diff[1].max() < 256
+    assert np.array_equal(got[:, 256:], host[:, 256:])
+    rng = np.random.default_rng(5)
+    ids = np.stack([rng.permutation(E)[:topk] for _ in range(T)]).astype(np.int32)
+    x = O.make_x(T, K, seed=8)
+    codes = np.stack([m[0] for m in mats]); scales = np.stack([m[1] for m in mats]); ts = np.array([m[2] for m in mats], dtype=np.float32)
+    ref = O.moe_gemv_nvfp4_f64(codes, scales, ts, ids, x, per_slot_input=False)
+    xd, idd = U.dev_u16(x), torch.from_numpy(ids).cuda()
+    out = torch.full((T * topk, N), float("nan"), dtype=torch.float32, device="cuda")
+    handle.moe_gemv(w, idd.data_ptr(), xd.data_ptr(), T, topk, False, out.data_ptr(), qg.OUT_F32)
+    torch.cuda.synchronize()
+    U.status_ok(handle)
+    assert O.rel_l2(out.cpu().numpy(), ref) < 5e-5
+    w.unload()
+    f.close()
