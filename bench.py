@@ -635,7 +635,11 @@ def run_moe(args, T=None):
     def layers(st):
         for l in range(L):
             h.moe_gemv(gu[l], ids.data_ptr(), x.data_ptr(), T, topk, False, hbufs[l].data_ptr(), qg.OUT_BF16, st)
-            h.moe_gemv(dn[l], ids.data_ptr(), act.data_ptr(), T, topk, True, outs[l].data_ptr(), qg.OUT_F32, st)
+            if tc:   # the real data flow: the down stage reads the gate/up rows, silu(gate) * up applied inside the launch
+                h.moe_gemv(dn[l], ids.data_ptr(), hbufs[l].data_ptr(), T, topk, True, outs[l].data_ptr(), qg.OUT_F32, st,
+                           x_act=qg.MOE_X_SILU_MUL)
+            else:    # (lane-order experts have no fused activation: a stand-in input for the down stage)
+                h.moe_gemv(dn[l], ids.data_ptr(), act.data_ptr(), T, topk, True, outs[l].data_ptr(), qg.OUT_F32, st)
 
     with torch.cuda.stream(stream):
         layers(stream.cuda_stream)
@@ -670,6 +674,12 @@ def run_moe(args, T=None):
     ids_h = ids.cpu().numpy()
     xs_h, act_h = u16(x_host), u16(act)
     hb, ob = hbufs[0].float().cpu().numpy(), outs[0].cpu().numpy()
+    if tc:   # what the down stage multiplies: bf16(silu(gate) * up) of the gate/up rows the device produced (fp64 inside)
+        v = hb.astype(np.float64)
+        act_h = O.bf16_encode((v[:, :inter] / (1.0 + np.exp(-v[:, :inter])) * v[:, inter:]).astype(np.float32))
+    # (the device's fast exponential rounds one bf16 product in several hundred the other way: an error of one bf16 ulp
+    # in that share of the down stage's inputs, ~1.6e-4 at 64 tokens, well under the 2e-3 of bf16 results)
+    tol_dn = 5e-4 if tc else TOL_F32
     rng = np.random.default_rng(T)
     slots = sorted(set(int(s) for s in rng.integers(0, T * topk, size=6)) | {0, T * topk - 1})
     err_gu = err_dn = 0.0
@@ -703,9 +713,10 @@ def run_moe(args, T=None):
                 "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 4,
                 "ms_per_step": round(ms_host / args.steps, 5)},
         "gpu_launches": (2 if tc else 4) * L * args.steps, "clocks": clocks,
-        "verified": bool(err_gu < TOL_BF16 and err_dn < TOL_F32),
+        "verified": bool(err_gu < TOL_BF16 and err_dn < tol_dn),
         "verify": {"rel_l2_gate_up_bf16": float(f"{err_gu:.3e}"), "rel_l2_down_f32": float(f"{err_dn:.3e}"),
-                   "tol": [TOL_BF16, TOL_F32], "checked": f"{len(slots)} sampled (token, expert) slots of layer 0, all rows, fp64 oracle"},
+                   "tol": [TOL_BF16, tol_dn], "checked": f"{len(slots)} sampled (token, expert) slots of layer 0, all rows, fp64 oracle"
+                   + ("; the down stage reads the gate/up rows through silu(gate) * up inside its launch" if tc else "")},
     }
     for w in gu + dn:
         w.unload()

@@ -21,6 +21,7 @@ FMT_NVFP4_TC = 3   # NVFP4 in the tile order the block-scaled tensor-core GEMV c
 JOB_AFTER_PREVIOUS = 1   # qgemv_job.flags: wait for the job before this one
 JOB_ALLREDUCE = 2        # qgemv_job.flags: row-parallel projection, summed over the ranks inside the launch
 JOB_X_SILU_MUL = 4       # qgemv_job.flags: the rows of x hold gate and up values; the GEMV multiplies silu(gate) * up
+MOE_X_SILU_MUL = 1       # moe_gemv's x_act: the same for the experts' down stage
 OUT_BF16 = 0
 OUT_F32 = 1
 ACT_A16_EXACT = 0
@@ -137,6 +138,7 @@ def _load() -> C.CDLL:
     L.qgemv_gemv_noalloc.argtypes = [vp, vp, vp, i32, vp, i32, vp]
     L.qgemv_noalloc_last_status.argtypes = [vp, C.POINTER(_DevStatus)]
     L.qgemv_moe_gemv.argtypes = [vp, vp, vp, vp, i32, i32, i32, vp, i32, vp]
+    L.qgemv_moe_gemv_act.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, vp, i32, vp]
     L.qgemv_moe_combine.argtypes = [vp, vp, i32, vp, i32, i32, i64, vp, i32, vp]
     L.qgemv_dequant_f32.argtypes = [vp, vp, i32, vp, vp]
     L.qgemv_last_device_status.argtypes = [vp, vp, C.POINTER(_DevStatus)]
@@ -372,7 +374,13 @@ class QGemv:
                "quantize_a4")
 
     def moe_gemv(self, experts: Weight, expert_ids_ptr: int, x_ptr: int, T: int, topk: int,
-                 per_slot_input: bool, out_ptr: int, out_dtype: int = OUT_F32, stream: int = 0) -> None:
+                 per_slot_input: bool, out_ptr: int, out_dtype: int = OUT_F32, stream: int = 0, x_act: int = 0) -> None:
+        """x_act = MOE_X_SILU_MUL: the rows of x hold gate and up values (2 K) and the experts multiply
+        bf16(silu(gate) * up) -- the down stage fed straight from the gate/up stage's output rows."""
+        if x_act:
+            _check(_load().qgemv_moe_gemv_act(self._ptr, experts._ptr, expert_ids_ptr, x_ptr, T, topk,
+                                              1 if per_slot_input else 0, x_act, out_ptr, out_dtype, stream), "moe_gemv_act")
+            return
         _check(_load().qgemv_moe_gemv(self._ptr, experts._ptr, expert_ids_ptr, x_ptr, T, topk,
                                       1 if per_slot_input else 0, out_ptr, out_dtype, stream), "moe_gemv")
 

@@ -1127,7 +1127,7 @@ namespace {
 // The experts of a router table on the tensor-core layout: the sequence kernel in its expert-list mode, ONE
 // cooperative launch (every CTA walks the top-k lists for itself).  Problems hold at most B activation rows.
 int moe_tc(qgemv_handle* h, const qgemv_weight* w, const int32_t* expert_ids, const void* x_bf16, int T, int topk,
-           int per_slot_input, void* out, int out_dtype, cudaStream_t s) {
+           int per_slot_input, int x_act, void* out, int out_dtype, cudaStream_t s) {
     const int grid = gemv_grid(h);
     if (grid > h->sm_count) return QGEMV_ERR_UNSUPPORTED_SHAPE;  // the CTAs wait on one another: one per SM at most
     const int slots = T * topk;
@@ -1164,7 +1164,8 @@ int moe_tc(qgemv_handle* h, const qgemv_weight* w, const int32_t* expert_ids, co
     mj.tensor_scale = 1.0f;
     mj.N = int32_t(w->N), mj.K = int32_t(w->K);
     mj.tiles = int32_t(w->n_panels / 8), mj.kt = int32_t(w->units);
-    mj.x_stride = int32_t(w->K);
+    mj.x_stride = int32_t(x_act == QGEMV_MOE_X_SILU_MUL ? 2 * w->K : w->K);
+    mj.act = x_act == QGEMV_MOE_X_SILU_MUL ? 1 : 0;
     mj.y_dtype = out_dtype;
     mj.dep = -1, mj.xoff = -1, mj.pub_off = -1, mj.src_off = -1, mj.src_job = -1;
     const int64_t per = int64_t(mj.tiles) * mj.kt;
@@ -1199,13 +1200,21 @@ int moe_tc(qgemv_handle* h, const qgemv_weight* w, const int32_t* expert_ids, co
 int qgemv_moe_gemv(qgemv_handle* h, const qgemv_weight* experts, const int32_t* expert_ids,
                    const void* x_bf16, int T, int topk, int per_slot_input, void* out,
                    int out_dtype, void* stream) {
+    return qgemv_moe_gemv_act(h, experts, expert_ids, x_bf16, T, topk, per_slot_input, 0, out, out_dtype, stream);
+}
+
+int qgemv_moe_gemv_act(qgemv_handle* h, const qgemv_weight* experts, const int32_t* expert_ids,
+                       const void* x_bf16, int T, int topk, int per_slot_input, int x_act, void* out,
+                       int out_dtype, void* stream) {
     if (!h || !experts || !expert_ids || !x_bf16 || !out) return QGEMV_ERR_INVALID_ARG;
+    if (x_act != 0 && x_act != QGEMV_MOE_X_SILU_MUL) return QGEMV_ERR_INVALID_ARG;
+    if (x_act != 0 && experts->fmt != QGEMV_FMT_NVFP4_TC) return QGEMV_ERR_UNSUPPORTED_SHAPE;  // the expert-list launch only
     if (!experts->prob) return QGEMV_ERR_INVALID_ARG;  // not a stacked weight
     if (T < 1 || topk < 1 || int64_t(T) * topk > kMaxMoeSlots) return QGEMV_ERR_UNSUPPORTED_SHAPE;
     if (out_dtype != QGEMV_OUT_BF16 && out_dtype != QGEMV_OUT_F32) return QGEMV_ERR_INVALID_ARG;
     if ((reinterpret_cast<uintptr_t>(x_bf16) & 15u) != 0) return QGEMV_ERR_INVALID_ARG;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (experts->fmt == QGEMV_FMT_NVFP4_TC) return moe_tc(h, experts, expert_ids, x_bf16, T, topk, per_slot_input, out, out_dtype, s);
+    if (experts->fmt == QGEMV_FMT_NVFP4_TC) return moe_tc(h, experts, expert_ids, x_bf16, T, topk, per_slot_input, x_act, out, out_dtype, s);
     const int threads = 1024;
     cudaError_t err = launch(h, qg::moe_prep_kernel, dim3(1), dim3(threads),
                              size_t(experts->n_stack) * 12 + size_t(T) * topk * 4 + 16, s, expert_ids, T, topk, experts->n_stack,

@@ -298,6 +298,7 @@ constexpr int kSeqThreads = 32 * (2 + 12);  // producer, MMA issuer, three group
 template <int S, int MODE>
 __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParams P) {
     constexpr bool FUSE = MODE == kSeqFuse, MOE = MODE == kSeqMoe;
+    constexpr bool ACT = FUSE || MOE;  // jobs may apply an activation function to what they read (the experts' down stage)
     extern __shared__ __align__(128) unsigned char sq_smem[];
     const uint32_t sbase = smem_u32(sq_smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -816,8 +817,10 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 };
                 // ... and what the GEMV multiplies: the activation function and the norm weight applied (FUSE)
                 auto shaped8 = [&](int b, int k0, uint4 v) -> uint4 {
-                    if constexpr (FUSE) {
+                    if constexpr (ACT) {
                         if (job.act == 1) v = seq_silu_mul(v, fetch8(b, k0 + job.K));
+                    }
+                    if constexpr (FUSE) {
                         if (job.norm_w) v = seq_mul_w(v, __ldg(reinterpret_cast<const uint4*>(job.norm_w + k0)));
                     }
                     return v;
@@ -876,7 +879,8 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 // 256 (g + 1) and the raw values of group g' start at (end of buffer) - 128 (G - g'), so a wave only
                 // overwrites raw values of its own groups (already in registers) and of earlier waves.
                 bool staged = !from_pub && n_work > kKeep * 128;
-                if constexpr (FUSE) staged = staged && job.act == 0 && !job.norm_w;
+                if constexpr (ACT) staged = staged && job.act == 0;   // (gate and up values together are as large as their planes)
+                if constexpr (FUSE) staged = staged && !job.norm_w;
                 if (staged) {
                     const uint32_t raw0 = xb + uint32_t(n_slots) * xslot_bytes - uint32_t(n_slots * Bj) * 128u;
                     // a thread's units are 128 apart, i.e. 16 groups: (slot, row) of the next one without a division

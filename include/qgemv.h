@@ -386,6 +386,15 @@ int qgemv_gemm_skinny_plan(int fmt, int64_t N, int64_t K, int M, int sm_count, q
 int qgemv_moe_gemv(qgemv_handle* h, const qgemv_weight* experts, const int32_t* expert_ids,
                    const void* x_bf16, int T, int topk, int per_slot_input, void* out,
                    int out_dtype, void* stream);
+/* The same with an activation function applied to what is read (the experts' down stage without an element-wise
+ * kernel before it; "fused norm / activation", engines/crit-labs/mtp5-nvfp4-drafts/card.yaml:81):
+ * x_act = QGEMV_MOE_X_SILU_MUL: the rows of x hold 2 K values, gate then up -- the output rows of the gate/up
+ * stage as qgemv_moe_gemv leaves them -- and the GEMV multiplies bf16(silu(gate[k]) * up[k]).  x_act = 0:
+ * qgemv_moe_gemv.  Tensor-core-layout experts only (QGEMV_ERR_UNSUPPORTED_SHAPE otherwise). */
+#define QGEMV_MOE_X_SILU_MUL 1
+int qgemv_moe_gemv_act(qgemv_handle* h, const qgemv_weight* experts, const int32_t* expert_ids,
+                       const void* x_bf16, int T, int topk, int per_slot_input, int x_act, void* out,
+                       int out_dtype, void* stream);
 /* y[t][:] = sum_j expert_w[t][j] * slot_out[t*topk + j][:]  (fixed j order, fp32 accumulate). */
 int qgemv_moe_combine(qgemv_handle* h, const void* slot_out, int slot_dtype, const float* expert_w,
                       int T, int topk, int64_t N, void* y, int y_dtype, void* stream);

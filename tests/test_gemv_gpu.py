@@ -432,6 +432,36 @@ def test_moe_gemv_repeated_and_bad_ids(qg, handle, fmt_name):
     w.unload()
 
 
+@pytest.mark.parametrize("T", [1, 8, 64])
+def test_moe_down_stage_with_silu_mul(qg, handle, T):
+    """The experts' down stage fed with the gate/up stage's output rows: the launch multiplies bf16(silu(gate) * up) of
+    rows that hold 2 K values (tensor-core layout); the lane-order layout refuses the option."""
+    import torch
+    E, topk, N, K = 32, 4, 256, 192
+    codes, scales, ts = _experts(E, N, K, seed=611)
+    w = handle.load_stacked(np.stack([qg.pack(qg.FMT_NVFP4_TC, codes[e], scales[e], float(ts[e])) for e in range(E)]))
+    ids, _ = _route(T, E, topk, seed=T + 9)
+    gu = O.make_x(T * topk, 2 * K, seed=T + 10)           # per slot: K gate values, then K up values
+    v = O.bf16_decode(gu).astype(np.float64)
+    act = O.bf16_encode((v[:, :K] / (1.0 + np.exp(-v[:, :K])) * v[:, K:]).astype(np.float32))
+    ref = O.moe_gemv_nvfp4_f64(codes, scales, ts, ids, act, per_slot_input=True)
+    gd, idd = U.dev_u16(gu), torch.from_numpy(ids).cuda()
+    out = torch.full((T * topk, N), float("nan"), dtype=torch.float32, device="cuda")
+    handle.moe_gemv(w, idd.data_ptr(), gd.data_ptr(), T, topk, True, out.data_ptr(), qg.OUT_F32, x_act=qg.MOE_X_SILU_MUL)
+    torch.cuda.synchronize()
+    U.status_ok(handle)
+    got = out.cpu().numpy()
+    assert not np.isnan(got).any()
+    assert O.rel_l2(got, ref) < 2e-4      # the device's fast exponential may round a bf16 product the other way
+    w.unload()
+    if T == 1:
+        wl = handle.load_stacked(np.stack([qg.pack(qg.FMT_NVFP4, codes[e], scales[e], float(ts[e])) for e in range(E)]))
+        with pytest.raises(qg.QgemvError) as e:
+            handle.moe_gemv(wl, idd.data_ptr(), gd.data_ptr(), T, topk, True, out.data_ptr(), qg.OUT_F32, x_act=qg.MOE_X_SILU_MUL)
+        assert e.value.status == qg.ERR_UNSUPPORTED_SHAPE
+        wl.unload()
+
+
 def test_moe_gemv_tc_many_experts_and_limits(qg, handle):
     """Tensor-core layout: 300 experts with top-1 routing (every problem a single row, most experts untouched), bf16
     output; a stacked weight of more than 512 experts is refused by the expert-list launch."""
