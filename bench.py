@@ -599,6 +599,7 @@ def run_moe(args, T=None):
     T = T or (args.tokens if args.tokens <= 512 and args.tokens != 256 else 8)
     tc = getattr(args, "moe_layout", "tc") == "tc"   # tensor-core layout: the expert list runs on the sequence kernel
     fmt = qg.FMT_NVFP4_TC if tc else qg.FMT_NVFP4
+    one_launch = tc and not getattr(args, "moe_two_launches", False)
     h = qg.QGemv(device=0, use_pdl=True)
     host0 = {}
 
@@ -634,6 +635,9 @@ def run_moe(args, T=None):
 
     def layers(st):
         for l in range(L):
+            if one_launch:   # both stages of the layer's expert MLP (gate/up, silu(gate) * up, down) as one launch
+                h.moe_mlp(gu[l], dn[l], ids.data_ptr(), x.data_ptr(), T, topk, hbufs[l].data_ptr(), outs[l].data_ptr(), qg.OUT_F32, st)
+                continue
             h.moe_gemv(gu[l], ids.data_ptr(), x.data_ptr(), T, topk, False, hbufs[l].data_ptr(), qg.OUT_BF16, st)
             if tc:   # the real data flow: the down stage reads the gate/up rows, silu(gate) * up applied inside the launch
                 h.moe_gemv(dn[l], ids.data_ptr(), hbufs[l].data_ptr(), T, topk, True, outs[l].data_ptr(), qg.OUT_F32, st,
@@ -697,22 +701,24 @@ def run_moe(args, T=None):
         "warmup": warmup, "ms_per_step": round(ms / args.steps, 5), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16 (fp32 accumulate)", "data": "synthetic",
         "config": {"workload": f"MoE grouped GEMV: {E} experts, top-{topk}, hidden {hidden}, expert width {inter}, NVFP4, "
-                               f"{T} tokens, {L} layers (gate/up + down) in one CUDA graph, {'tensor-core' if tc else 'lane-order'} layout",
+                               f"{T} tokens, {L} layers (gate/up + down) in one CUDA graph, {'tensor-core' if tc else 'lane-order'} layout"
+                               + (", one launch per layer (gate/up, silu x up, down)" if one_launch else ""),
                    "tokens": T, "distinct_experts": distinct, "touched_weight_bytes_per_step": nbytes,
                    "us_per_layer": round(ms * 1e3 / args.steps / L, 2),
                    "cache": "four layers of distinct experts; at 1 token the touched experts (21 MB per layer) fit L2"},
         "roofline": {"bound": "hbm", "achieved": round(gbs, 2), "peak": peak, "unit": UNIT, "frac": round(gbs / peak, 4),
-                     "traffic": int((1.04 if tc else 1.01) * (nbytes // (2 * L))),
+                     "traffic": int((1.04 if tc else 1.01) * (nbytes // ((1 if one_launch else 2) * L))),
                      "traffic_source": ("ncu capture at 8 tokens (profiles/moe_expert_list_128experts_t8_traffic.md): DRAM read+write = "
                                         "1.019-1.066 x the touched experts' bytes per launch; scaled by bytes") if tc else
                                        ("ncu capture at 8 tokens (profiles/moe_stream_128experts_t8_traffic.md): DRAM read+write = "
                                         "1.004-1.027 x the touched experts' bytes per launch; scaled by bytes"),
                      "peak_kind": kind, "kernel": "gemv_seq_kernel<4, expert list>" if tc else "moe_stream_kernel<NVFP4>",
-                     "bytes_per_launch": nbytes // (2 * L), "us_per_launch": round(ms * 1e3 / (2 * L * args.steps), 2)},
+                     "bytes_per_launch": nbytes // ((1 if one_launch else 2) * L),
+                     "us_per_launch": round(ms * 1e3 / ((1 if one_launch else 2) * L * args.steps), 2)},
         "e2e": {"value": round(nbytes * args.steps / (ms_host * 1e-3) / 1e9, 2), "unit": UNIT,
                 "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 4,
                 "ms_per_step": round(ms_host / args.steps, 5)},
-        "gpu_launches": (2 if tc else 4) * L * args.steps, "clocks": clocks,
+        "gpu_launches": (1 if one_launch else 2 if tc else 4) * L * args.steps, "clocks": clocks,
         "verified": bool(err_gu < TOL_BF16 and err_dn < tol_dn),
         "verify": {"rel_l2_gate_up_bf16": float(f"{err_gu:.3e}"), "rel_l2_down_f32": float(f"{err_dn:.3e}"),
                    "tol": [TOL_BF16, tol_dn], "checked": f"{len(slots)} sampled (token, expert) slots of layer 0, all rows, fp64 oracle"
@@ -751,6 +757,8 @@ def main():
     ap.add_argument("--no-tp1", action="store_true", help="N > 1: do not time the unsharded stack on rank 0")
     ap.add_argument("--moe-layout", default="tc", choices=["tc", "lane"],
                     help="MoE workload: tc = experts in the tensor-core layout (sequence kernel), lane = lane order (mma.sync streaming kernel)")
+    ap.add_argument("--moe-two-launches", action="store_true",
+                    help="MoE workload, tensor-core layout: gate/up and down as two launches per layer instead of one")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "prefill_a4", "lmhead", "moe"],
                     help="decode: the headline GEMV layer stack; prefill: the skinny GEMM over one 70B-shaped layer; "
                          "lmhead: the FP8 output head; moe: the grouped expert GEMV (--tokens 1/8/64)")

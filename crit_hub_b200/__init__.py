@@ -139,6 +139,7 @@ def _load() -> C.CDLL:
     L.qgemv_noalloc_last_status.argtypes = [vp, C.POINTER(_DevStatus)]
     L.qgemv_moe_gemv.argtypes = [vp, vp, vp, vp, i32, i32, i32, vp, i32, vp]
     L.qgemv_moe_gemv_act.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, vp, i32, vp]
+    L.qgemv_moe_mlp.argtypes = [vp, vp, vp, vp, vp, i32, i32, vp, vp, i32, vp]
     L.qgemv_moe_combine.argtypes = [vp, vp, i32, vp, i32, i32, i64, vp, i32, vp]
     L.qgemv_dequant_f32.argtypes = [vp, vp, i32, vp, vp]
     L.qgemv_last_device_status.argtypes = [vp, vp, C.POINTER(_DevStatus)]
@@ -383,6 +384,12 @@ class QGemv:
             return
         _check(_load().qgemv_moe_gemv(self._ptr, experts._ptr, expert_ids_ptr, x_ptr, T, topk,
                                       1 if per_slot_input else 0, out_ptr, out_dtype, stream), "moe_gemv")
+
+    def moe_mlp(self, gate_up: Weight, down: Weight, expert_ids_ptr: int, x_ptr: int, T: int, topk: int,
+                gate_up_rows_ptr: int, out_ptr: int, out_dtype: int = OUT_F32, stream: int = 0) -> None:
+        """Both stages of the experts' MLP as one launch (tensor-core layout): gate/up, silu(gate) * up, down."""
+        _check(_load().qgemv_moe_mlp(self._ptr, gate_up._ptr, down._ptr, expert_ids_ptr, x_ptr, T, topk,
+                                     gate_up_rows_ptr, out_ptr, out_dtype, stream), "moe_mlp")
 
     def moe_combine(self, slot_out_ptr: int, slot_dtype: int, expert_w_ptr: int, T: int, topk: int, N: int,
                     y_ptr: int, y_dtype: int = OUT_BF16, stream: int = 0) -> None:

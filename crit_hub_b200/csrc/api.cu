@@ -46,6 +46,7 @@ struct qgemv_handle {
     unsigned long long* tc_trace;  // caller's device buffer for phase timestamps, or null
     unsigned int* seq_barrier;     // CTAs that have left a GEMV-sequence launch, zero between launches
     unsigned long long* seq_parts; // its parts buffers: [kSeqPartBufs][2 * grid][8][128] pairs {fp32, tag}
+    unsigned int* moe_cnt;         // expert MLP in one launch: per problem, warps that have stored first-stage rows (zero between launches)
     size_t tc_ws_bytes;
     uint8_t* a4_ws;        // block-scaled prefill: quantised activation items, then the row scales
     size_t a4_ws_bytes;
@@ -380,13 +381,14 @@ int qgemv_init(const qgemv_config* cfg, qgemv_handle** out) {
     h->tp_seq_cursor = 0, h->tp_call_high = 0;
     h->gs_ws = nullptr, h->gs_ws_bytes = 0;
     h->chunk_ws = nullptr;
-    h->tc_ws = nullptr, h->tc_trace = nullptr, h->seq_barrier = nullptr, h->seq_parts = nullptr;
+    h->tc_ws = nullptr, h->tc_trace = nullptr, h->seq_barrier = nullptr, h->seq_parts = nullptr, h->moe_cnt = nullptr;
     h->a4_ws = nullptr, h->a4_ws_bytes = 0;
     h->sequences = new (std::nothrow) std::vector<qgemv_sequence*>();
     const size_t tc_ws_bytes = size_t(2) * size_t(std::max(h->sm_count, cfg->grid_override)) * 1024 * 8;
     h->tc_ws_bytes = tc_ws_bytes;
     if (cudaMalloc(&h->tc_ws, tc_ws_bytes) != cudaSuccess || cudaMemset(h->tc_ws, 0, tc_ws_bytes) != cudaSuccess ||
         cudaMalloc(&h->seq_barrier, 256) != cudaSuccess || cudaMemset(h->seq_barrier, 0, 256) != cudaSuccess ||
+        cudaMalloc(&h->moe_cnt, 2048 * 4) != cudaSuccess || cudaMemset(h->moe_cnt, 0, 2048 * 4) != cudaSuccess ||
         cudaMalloc(&h->seq_parts, size_t(qg::kSeqPartBufs) * size_t(2) * size_t(std::max(h->sm_count, cfg->grid_override)) * 8192) != cudaSuccess ||
         cudaMalloc(&h->chunk_ws, kChunkWsBytes) != cudaSuccess ||
         cudaMalloc(&h->status_dev, 4 * sizeof(int32_t)) != cudaSuccess ||
@@ -445,6 +447,7 @@ int qgemv_destroy(qgemv_handle* h) {
     cudaFree(h->tc_ws);
     cudaFree(h->seq_barrier);
     cudaFree(h->seq_parts);
+    cudaFree(h->moe_cnt);
     cudaFree(h->a4_ws);
     delete h->sequences;
     cudaFree(h->status_dev);
@@ -1126,8 +1129,10 @@ int qgemv_gemm_skinny(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16
 namespace {
 // The experts of a router table on the tensor-core layout: the sequence kernel in its expert-list mode, ONE
 // cooperative launch (every CTA walks the top-k lists for itself).  Problems hold at most B activation rows.
-int moe_tc(qgemv_handle* h, const qgemv_weight* w, const int32_t* expert_ids, const void* x_bf16, int T, int topk,
-           int per_slot_input, int x_act, void* out, int out_dtype, cudaStream_t s) {
+// `w2` (nullable): the experts' second stage in the same launch -- w is then the gate/up stage, writing its bf16
+// rows to `mid` [T * topk][w->N], and w2 the down stage, which reads them through silu(gate) * up.
+int moe_tc(qgemv_handle* h, const qgemv_weight* w, const qgemv_weight* w2, const int32_t* expert_ids, const void* x_bf16,
+           int T, int topk, int per_slot_input, int x_act, void* mid, void* out, int out_dtype, cudaStream_t s) {
     const int grid = gemv_grid(h);
     if (grid > h->sm_count) return QGEMV_ERR_UNSUPPORTED_SHAPE;  // the CTAs wait on one another: one per SM at most
     const int slots = T * topk;
@@ -1138,7 +1143,7 @@ int moe_tc(qgemv_handle* h, const qgemv_weight* w, const int32_t* expert_ids, co
     constexpr int kStage = 4;
     constexpr int kWalk = (qg::kMoeSmemBytes + 127) / 128 * 128;   // the CTA's problem table, behind the ring
     const int cap = (h->cfg.tc_smem_kb > 0 ? std::min(h->cfg.tc_smem_kb, 227) : 227) * 1024 - kWalk;
-    const int x_slots = int(w->units);   // a CTA's share of an expert may span a whole row tile
+    const int x_slots = int(w2 ? std::max(w->units, w2->units) : w->units);   // a CTA's share of an expert may span a whole row tile
     int B = std::min(QGEMV_MAX_BATCH, T), npad = 0, nbuf = 1, ring = 0;
     for (;; B = (B + 1) / 2) {
         npad = (8 * B + 15) / 16 * 16;
@@ -1154,7 +1159,7 @@ int moe_tc(qgemv_handle* h, const qgemv_weight* w, const int32_t* expert_ids, co
     if (ring < 2 || ring * kStage * qg::kTcItemBytes < qg::kMoeWalkBytes)
         return QGEMV_ERR_UNSUPPORTED_SHAPE;  // K too long for the digit planes of one row beside a ring
     const int64_t most_prob = std::min<int64_t>(w->n_stack, slots) + slots / B;   // problems the lists can make
-    if ((most_prob + grid - 1) / grid + 1 > qg::kMoeLocalJobs) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+    if (((most_prob + grid - 1) / grid + 1) * (w2 ? 2 : 1) > qg::kMoeLocalJobs || most_prob >= 2048) return QGEMV_ERR_UNSUPPORTED_SHAPE;
     qg::SeqParams P;
     std::memset(&P, 0, sizeof P);
     qg::SeqJob& mj = P.moe_job;
@@ -1170,6 +1175,25 @@ int moe_tc(qgemv_handle* h, const qgemv_weight* w, const int32_t* expert_ids, co
     mj.dep = -1, mj.xoff = -1, mj.pub_off = -1, mj.src_off = -1, mj.src_job = -1;
     const int64_t per = int64_t(mj.tiles) * mj.kt;
     if ((most_prob * per + 1) * grid >= (int64_t(1) << 32)) return QGEMV_ERR_UNSUPPORTED_SHAPE;  // 32-bit split arithmetic
+    P.n_phases = 1;
+    if (w2) {
+        mj.y = mid, mj.y_dtype = QGEMV_OUT_BF16;
+        qg::SeqJob& m2 = P.moe_job2;
+        m2 = mj;
+        m2.payload = w2->dev_blob + QG_HEADER_BYTES + w2->aux_bytes;
+        m2.x = static_cast<const uint16_t*>(mid);
+        m2.y = out, m2.y_dtype = out_dtype;
+        m2.N = int32_t(w2->N), m2.K = int32_t(w2->K);
+        m2.tiles = int32_t(w2->n_panels / 8), m2.kt = int32_t(w2->units);
+        m2.x_stride = int32_t(w->N);
+        m2.act = 1;
+        const int64_t per2 = int64_t(m2.tiles) * m2.kt;
+        if ((most_prob * per2 + 1) * grid >= (int64_t(1) << 32)) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+        P.n_phases = 2;
+        P.expert_ts2 = w2->dev_tensor_scale;
+        P.expert_stride2 = w2->blob_bytes;
+        P.moe_cnt = h->moe_cnt;
+    }
     P.ws = h->seq_parts;
     P.barrier = h->seq_barrier;
     P.fin = reinterpret_cast<unsigned int*>(w->counters);  // [0]: launches with this weight (nothing else of a job list's counters is used)
@@ -1214,7 +1238,7 @@ int qgemv_moe_gemv_act(qgemv_handle* h, const qgemv_weight* experts, const int32
     if (out_dtype != QGEMV_OUT_BF16 && out_dtype != QGEMV_OUT_F32) return QGEMV_ERR_INVALID_ARG;
     if ((reinterpret_cast<uintptr_t>(x_bf16) & 15u) != 0) return QGEMV_ERR_INVALID_ARG;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (experts->fmt == QGEMV_FMT_NVFP4_TC) return moe_tc(h, experts, expert_ids, x_bf16, T, topk, per_slot_input, x_act, out, out_dtype, s);
+    if (experts->fmt == QGEMV_FMT_NVFP4_TC) return moe_tc(h, experts, nullptr, expert_ids, x_bf16, T, topk, per_slot_input, x_act, nullptr, out, out_dtype, s);
     const int threads = 1024;
     cudaError_t err = launch(h, qg::moe_prep_kernel, dim3(1), dim3(threads),
                              size_t(experts->n_stack) * 12 + size_t(T) * topk * 4 + 16, s, expert_ids, T, topk, experts->n_stack,
@@ -1255,6 +1279,17 @@ int qgemv_moe_gemv_act(qgemv_handle* h, const qgemv_weight* experts, const int32
     err = launch(h, qg::chunk_sum_kernel, dim3(unsigned((slice + 255) / 256)), dim3(256), 0, s,
                  static_cast<const float*>(h->chunk_ws), int(n_chunks), slice, out, out_dtype);
     return err == cudaSuccess ? QGEMV_OK : QGEMV_ERR_CUDA;
+}
+
+int qgemv_moe_mlp(qgemv_handle* h, const qgemv_weight* gate_up, const qgemv_weight* down, const int32_t* expert_ids,
+                  const void* x_bf16, int T, int topk, void* gate_up_rows, void* out, int out_dtype, void* stream) {
+    if (!h || !gate_up || !down || !expert_ids || !x_bf16 || !gate_up_rows || !out) return QGEMV_ERR_INVALID_ARG;
+    if (T < 1 || topk < 1 || int64_t(T) * topk > kMaxMoeSlots) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+    if (out_dtype != QGEMV_OUT_BF16 && out_dtype != QGEMV_OUT_F32) return QGEMV_ERR_INVALID_ARG;
+    if (((reinterpret_cast<uintptr_t>(x_bf16) | reinterpret_cast<uintptr_t>(gate_up_rows)) & 15u) != 0) return QGEMV_ERR_INVALID_ARG;
+    if (gate_up->fmt != QGEMV_FMT_NVFP4_TC || down->fmt != QGEMV_FMT_NVFP4_TC) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+    if (gate_up->n_stack != down->n_stack || gate_up->N != 2 * down->K) return QGEMV_ERR_INVALID_ARG;
+    return moe_tc(h, gate_up, down, expert_ids, x_bf16, T, topk, 0, 0, gate_up_rows, out, out_dtype, static_cast<cudaStream_t>(stream));
 }
 
 int qgemv_moe_combine(qgemv_handle* h, const void* slot_out, int slot_dtype, const float* expert_w,
@@ -1310,6 +1345,7 @@ int qgemv_last_device_status(qgemv_handle* h, void* stream, qgemv_dev_status* ou
         QG_CUDA(cudaMemset(h->status_dev, 0, sizeof v));
         // a kernel that gave up may have left hand-over flags and the arrival counter behind
         QG_CUDA(cudaMemset(h->tc_ws, 0, h->tc_ws_bytes));
+        QG_CUDA(cudaMemset(h->moe_cnt, 0, 2048 * 4));
         // ... and tagged words under the tags of a launch that never counted itself: count it here
         unsigned int cnt[3];
         QG_CUDA(cudaMemcpy(cnt, h->seq_barrier, sizeof cnt, cudaMemcpyDeviceToHost));

@@ -104,6 +104,16 @@ struct SeqParams {
     int32_t slots, topk, n_experts, per_slot;  // per_slot: activation row = the entry's index (else its token)
     int32_t moe_smem;                          // offset of the CTA's problem table in shared memory (behind the ring)
     SeqJob moe_job;
+    // Two stages in one launch (n_phases == 2; an expert MLP): moe_job is the gate/up stage, which writes its
+    // bf16 rows [slots][N] to moe_job.y, and moe_job2 the down stage, which reads them (with its activation
+    // function) as soon as the problem's gate/up tiles are counted complete in moe_cnt.  Each stage's items are
+    // a split space of their own, dealt evenly to all CTAs; a CTA works through its share of the first, then
+    // of the second.
+    int32_t n_phases;
+    const float* expert_ts2;
+    uint64_t expert_stride2;
+    SeqJob moe_job2;
+    unsigned int* moe_cnt;                     // [problems] warps that have stored rows of a gate/up problem; zero between launches
 };
 constexpr int kMoeMaxExperts = 512;   // experts of a stacked weight that the expert-list mode takes
 constexpr int kMoeLocalJobs = 32;     // problems that one CTA's range may touch
@@ -355,9 +365,9 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
     // space instead -- the problems' items laid end to end and dealt evenly -- so a CTA works on the one to three
     // experts its range touches, goes through those jobs only, and hands over at most two split row tiles.
     int j_lo = 0, j_hi = P.n_jobs;
-    int32_t g_total = 0, g_begin = 0, g_end = 0, g_per = 1;
-    int g_gj = grid;
     const int* m_tab = nullptr;  // expert list: the problems this CTA's range touches, kProbInts ints each
+    const volatile int* m_ph = nullptr;  // expert list: the stages' split spaces, five ints each
+    int m_nprob = 0;             // expert list: problems of the router's table
     uint32_t m_launch_no = 0, m_run_no = 0;  // expert list: the launch counts, fetched while the lists are walked
     if constexpr (MOE) {
         // ---- the router walk: entries per expert (shared-memory histogram), problems per expert and their prefix
@@ -368,8 +378,9 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
         int* m_base = m_counts + kMoeMaxExperts;                       // [n_experts] first problem
         int* m_ids = m_base + kMoeMaxExperts;                          // [slots] the lists
         int* tab = reinterpret_cast<int*>(sq_smem + P.moe_smem);       // [kMoeLocalJobs][kProbInts]
-        volatile int* m_misc = tab + kMoeLocalJobs * kProbInts;        // [0] problems, [1] an id out of range
+        volatile int* m_misc = tab + kMoeLocalJobs * kProbInts;        // [0] problems, [1] an id out of range, [2..11] the stages
         m_tab = tab;
+        m_ph = m_misc + 2;
         const int E = P.n_experts, slots = P.slots, cap = P.B;
         if (P.trace && threadIdx.x == 0) P.trace[size_t(grid) * P.trace_jobs * 8 + size_t(cta) * 4 + 0] = globaltimer_ns();
         pdl_wait();  // the lists are the work of whatever ran before this launch
@@ -409,32 +420,55 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
             }
         }
         __syncthreads();
-        g_per = P.moe_job.tiles * P.moe_job.kt;
-        g_total = m_misc[0] * g_per;
-        g_gj = seq_job_grid(g_total, grid);
-        seq_range(g_total, cta, g_gj, g_begin, g_end);
-        j_lo = g_begin / g_per;
-        j_hi = g_end > g_begin ? (g_end - 1) / g_per + 1 : j_lo;
-        if (j_hi - j_lo > kMoeLocalJobs) {  // (the host refuses shapes that could come here)
+        // Per stage (one, or two for an expert MLP): its split space and this CTA's share.  m_misc[2 + 5 q ..]:
+        // items, first and last + 1 item of this CTA, items per problem, CTAs that share the space.
+        m_nprob = m_misc[0];
+        int lo[2] = {0, 0}, hi[2] = {0, 0};
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            if (q < P.n_phases) {
+                const SeqJob& tj = q ? P.moe_job2 : P.moe_job;
+                const int32_t per = tj.tiles * tj.kt, total = m_nprob * per;
+                const int gjq = seq_job_grid(total, grid);
+                int32_t bg, en;
+                seq_range(total, cta, gjq, bg, en);
+                lo[q] = bg / per;
+                hi[q] = en > bg ? (en - 1) / per + 1 : lo[q];
+                if (threadIdx.x == 0) {
+                    volatile int* z = m_misc + 2 + 5 * q;
+                    z[0] = total, z[1] = bg, z[2] = en, z[3] = per, z[4] = gjq;
+                }
+            }
+        }
+        const int n_first = hi[0] - lo[0];
+        j_lo = 0;
+        j_hi = n_first + (hi[1] - lo[1]);   // from here on a job is named by its place in this CTA's list
+        if (j_hi > kMoeLocalJobs) {  // (the host refuses shapes that could come here)
             if (threadIdx.x == 0) {
-                report(P.status, QGEMV_ERR_BOUNDS, 20, j_hi - j_lo);
+                report(P.status, QGEMV_ERR_BOUNDS, 20, j_hi);
                 *abort_flag = 1;
             }
-            j_hi = j_lo;
+            j_hi = 0;
         }
         for (int e = threadIdx.x; e < E; e += kSeqThreads) {
             const int cnt = m_counts[e];
             const int b0 = m_base[e], np = (cnt + cap - 1) / cap;
-            for (int j = max(j_lo, b0); j < min(j_hi, b0 + np); ++j) {
-                int* t = tab + (j - j_lo) * kProbInts;
-                const int q = j - b0;
-                t[0] = e, t[1] = min(cap, cnt - q * cap), t[18] = q;
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                if (j_hi == 0) break;
+                for (int j = max(lo[q], b0); j < min(hi[q], b0 + np); ++j) {
+                    int* t = tab + ((q ? n_first : 0) + j - lo[q]) * kProbInts;
+                    const int qi = j - b0;
+                    t[0] = e, t[1] = min(cap, cnt - qi * cap), t[18] = qi, t[19] = j | (q << 16);
+                }
             }
         }
         __syncthreads();
-        for (int jl = warp; jl < j_hi - j_lo; jl += kSeqThreads / 32) {
+        for (int jl = warp; jl < j_hi; jl += kSeqThreads / 32) {
             int* t = tab + jl * kProbInts;
             const int e = t[0], rows = t[1], r0 = t[18] * cap;
+            // activation rows: the entry's token, or the entry itself (the second stage of an MLP reads the first one's rows)
+            const bool own_row = P.n_phases == 2 ? (t[19] >> 16) != 0 : P.per_slot != 0;
             int seen = 0;
             for (int i0 = 0; i0 < slots && seen < r0 + rows; i0 += 32) {
                 const int i = i0 + lane;
@@ -442,7 +476,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 const unsigned m = __ballot_sync(0xFFFFFFFFu, id == e);
                 const int r = seen + __popc(m & ((1u << lane) - 1u)) - r0;
                 if (id == e && r >= 0 && r < rows) {
-                    t[2 + r] = P.per_slot ? i : i / P.topk;
+                    t[2 + r] = own_row ? i : i / P.topk;
                     t[10 + r] = i;
                 }
                 seen += __popc(m);
@@ -454,13 +488,18 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
     if constexpr (MOE) {
         if (P.trace && threadIdx.x == 0) P.trace[size_t(grid) * P.trace_jobs * 8 + size_t(cta) * 4 + 1] = globaltimer_ns();
     }
+    // expert list: stage and problem of job j of this CTA's list; the stage's split space
+    auto moe_info = [&](int j, int& ph, int& prob) {
+        const int v = m_tab[j * kProbInts + 19];
+        ph = v >> 16, prob = v & 0xFFFF;
+    };
     auto job_at = [&](int j) -> SeqJob {
         if constexpr (MOE) {
-            SeqJob job = P.moe_job;
-            const int* t = m_tab + (j - j_lo) * kProbInts;
-            const int e = t[0];
-            job.payload += uint64_t(e) * P.expert_stride;
-            job.tensor_scale = __ldg(P.expert_ts + e);
+            const int* t = m_tab + j * kProbInts;
+            const int e = t[0], ph = t[19] >> 16;
+            SeqJob job = ph ? P.moe_job2 : P.moe_job;
+            job.payload += uint64_t(e) * (ph ? P.expert_stride2 : P.expert_stride);
+            job.tensor_scale = __ldg((ph ? P.expert_ts2 : P.expert_ts) + e);
             job.rows = t[1];
             job.rowmap = t + 2;
             return job;
@@ -471,8 +510,11 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
     // this CTA's range [rb, re) of job j, in the job's own (tile, item) space
     auto job_range = [&](const SeqJob& job, int j, int32_t& rb, int32_t& re) {
         if constexpr (MOE) {
-            const int32_t base = j * g_per;
-            rb = min(max(g_begin - base, 0), g_per), re = min(max(g_end - base, 0), g_per);
+            int ph, prob;
+            moe_info(j, ph, prob);
+            const volatile int* z = m_ph + 5 * ph;
+            const int32_t per = z[3], base = prob * per;
+            rb = min(max(z[1] - base, 0), per), re = min(max(z[2] - base, 0), per);
         } else {
             const int32_t total = job.tiles * job.kt;
             seq_range(total, cta, seq_job_grid(total, grid), rb, re);
@@ -481,7 +523,10 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
     // the CTA that holds item idx of job j; the parts slot of CTA c for row tile `tile` of job j
     auto job_cta_of = [&](const SeqJob& job, int j, int32_t idx) -> int32_t {
         if constexpr (MOE) {
-            return seq_cta_of(j * g_per + idx, g_total, g_gj);
+            int ph, prob;
+            moe_info(j, ph, prob);
+            const volatile int* z = m_ph + 5 * ph;
+            return seq_cta_of(prob * z[3] + idx, z[0], z[4]);
         } else {
             const int32_t total = job.tiles * job.kt;
             return seq_cta_of(idx, total, seq_job_grid(total, grid));
@@ -489,15 +534,29 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
     };
     auto job_slot = [&](const SeqJob& job, int j, int32_t c, int32_t tile) -> int32_t {
         if constexpr (MOE) {
-            return seq_slot(c, j * job.tiles + tile, job.kt, g_total, g_gj);
+            int ph, prob;
+            moe_info(j, ph, prob);
+            const volatile int* z = m_ph + 5 * ph;
+            return seq_slot(c, prob * job.tiles + tile, job.kt, z[0], z[4]);
         } else {
             const int32_t total = job.tiles * job.kt;
             return seq_slot(c, tile, job.kt, total, seq_job_grid(total, grid));
         }
     };
+    // what tells a job's tagged partial sums from another job's: the job's index in a list; stage and problem of an
+    // expert list (the same on every CTA)
+    auto job_tag = [&](int j) -> int {
+        if constexpr (MOE) {
+            int ph, prob;
+            moe_info(j, ph, prob);
+            return ph * 2048 + prob;
+        } else {
+            return j;
+        }
+    };
     // the parts buffer of job j: the jobs of a list take eight in turn; a router table's CTAs each hand over at
-    // most two split tiles in the whole launch, so one buffer serves
-    auto job_parts = [&](int j) -> size_t { return MOE ? size_t(0) : size_t(j & (kSeqPartBufs - 1)); };
+    // most two split tiles per stage, so one buffer per stage serves
+    auto job_parts = [&](int j) -> size_t { return MOE ? size_t(m_tab[j * kProbInts + 19] >> 16) : size_t(j & (kSeqPartBufs - 1)); };
 
     if (warp == kTcWarpProd) {
         // ================= packed-weight producer: runs through the whole job list =================
@@ -750,6 +809,26 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                     *abort_flag = 1;
                 }
                 if (job.dep >= 0) poll_all(P.fin + job.dep, 80, j);  // an earlier job's buffers are involved
+                if constexpr (MOE) {
+                    // the second stage of an expert MLP reads the rows its problem's first stage wrote: all of that
+                    // problem's row tiles must be counted (four warps each, on whichever CTAs held them)
+                    if (P.n_phases == 2 && gt == 0) {
+                        int ph, prob;
+                        moe_info(j, ph, prob);
+                        if (ph == 1) {
+                            const unsigned want_warps = 4u * unsigned(P.moe_job.tiles);
+                            uint64_t t0 = 0;
+                            for (int64_t it = 0; ld_acquire(P.moe_cnt + prob) < want_warps; ++it) {
+                                if (*abort_flag) break;
+                                if (out_of_time(it, t0)) {
+                                    seq_report(P.status, 86, prob);
+                                    *abort_flag = 1;
+                                    break;
+                                }
+                            }
+                        }
+                    }
+                }
                 if (!group_alive()) break;
                 SEQ_PPROF(0);
                 if (P.trace && gt == 0) P.trace[(size_t(cta) * P.trace_jobs + (j - j_lo)) * 8 + 0] = globaltimer_ns();
@@ -1105,7 +1184,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                     }
                 }
                 if (!group_alive()) break;
-                const uint32_t part_tag = seq_part_tag(launch_no, j), pub_tag = seq_pub_tag(run_no, j) << 16;
+                const uint32_t part_tag = seq_part_tag(launch_no, job_tag(j)), pub_tag = seq_pub_tag(run_no, j) << 16;
                 GsWalker wk;
                 wk.units = kt_len, wk.pos = rb, wk.end = re;
                 GsSeg sg;
@@ -1165,6 +1244,13 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(sbase + SeqSmem::kBarDFree + 8 * acc);  // the accumulator may be overwritten
+                    if constexpr (MOE) {
+                        if (P.n_phases == 2 && whole && lane == 0) {   // this warp's rows of a first-stage tile are stored
+                            int ph, prob;
+                            moe_info(j, ph, prob);
+                            if (ph == 0) red_release_add(P.moe_cnt + prob, 1u);
+                        }
+                    }
                     ++nseg;
                 }
                 if (P.trace && gt == 0) P.trace[(size_t(cta) * P.trace_jobs + (j - j_lo)) * 8 + 2] = globaltimer_ns();
@@ -1236,7 +1322,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 if (pending) {
                     const int n = tile * 128 + gt;
                     const unsigned long long* parts = P.ws + job_parts(j) * size_t(2 * grid) * 1024 + gt;
-                    const uint32_t part_tag = seq_part_tag(launch_no, j), pub_tag = seq_pub_tag(run_no, j) << 16;
+                    const uint32_t part_tag = seq_part_tag(launch_no, job_tag(j)), pub_tag = seq_pub_tag(run_no, j) << 16;
                     if (n < job.N && !*abort_flag) {
                         bool have = true;
                         uint64_t t0 = 0;
@@ -1311,6 +1397,16 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                         }
                     }
                 }
+                if constexpr (MOE) {
+                    if (P.n_phases == 2 && pending) {   // (uniform over the group)
+                        __syncwarp();
+                        if (lane == 0 && !*abort_flag) {
+                            int ph, prob;
+                            moe_info(j, ph, prob);
+                            if (ph == 0) red_release_add(P.moe_cnt + prob, 1u);
+                        }
+                    }
+                }
                 if (P.trace && gt == 0) P.trace[(size_t(cta) * P.trace_jobs + (j - j_lo)) * 8 + 6] = globaltimer_ns();
                 // (the epilogues of the job are through, see above: fin[j] == grid means that all of y is there)
                 named_bar_sync(bar_id, 128);
@@ -1326,6 +1422,10 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
     }
     if (threadIdx.x == 0 && !*abort_flag && atom_release_add(P.barrier, 1u) == unsigned(grid) - 1u) {
         for (int i = 0; i < P.n_jobs; ++i) P.fin[i] = 0u;  // nobody polls any more
+        if constexpr (MOE) {
+            if (P.n_phases == 2)
+                for (int i = 0; i < m_nprob; ++i) P.moe_cnt[i] = 0u;
+        }
         P.barrier[0] = 0u;
         if (P.world > 1) P.barrier[1] = P.barrier[1] + 1u;  // the tag of the next launch's exchange
         P.barrier[2] = P.barrier[2] + 1u;                   // of the next launch's partial sums

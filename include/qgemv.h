@@ -395,6 +395,15 @@ int qgemv_moe_gemv(qgemv_handle* h, const qgemv_weight* experts, const int32_t* 
 int qgemv_moe_gemv_act(qgemv_handle* h, const qgemv_weight* experts, const int32_t* expert_ids,
                        const void* x_bf16, int T, int topk, int per_slot_input, int x_act, void* out,
                        int out_dtype, void* stream);
+/* Both stages of the experts' MLP as ONE launch: out[t*topk + j][:] = W_down[e] . bf16(silu(g) * u) with
+ * (g, u) = W_gate_up[e] . x[t][:], e = expert_ids[t][j] -- what qgemv_moe_gemv (gate/up, bf16 rows) followed by
+ * qgemv_moe_gemv_act (down, QGEMV_MOE_X_SILU_MUL) computes, bit for bit, without the second launch: every CTA
+ * works through its share of the gate/up items and then of the down items, and a down problem starts as soon as
+ * its expert's gate/up rows are there.  gate_up: stacked [2 I][H], down: stacked [N][I], both in the tensor-core
+ * layout with the same number of experts.  gate_up_rows: device bf16 [T*topk][2 I], 16-byte aligned, written by
+ * the first stage and read by the second (the caller's scratch).  Limits as for qgemv_moe_gemv. */
+int qgemv_moe_mlp(qgemv_handle* h, const qgemv_weight* gate_up, const qgemv_weight* down, const int32_t* expert_ids,
+                  const void* x_bf16, int T, int topk, void* gate_up_rows, void* out, int out_dtype, void* stream);
 /* y[t][:] = sum_j expert_w[t][j] * slot_out[t*topk + j][:]  (fixed j order, fp32 accumulate). */
 int qgemv_moe_combine(qgemv_handle* h, const void* slot_out, int slot_dtype, const float* expert_w,
                       int T, int topk, int64_t N, void* y, int y_dtype, void* stream);

@@ -462,6 +462,44 @@ def test_moe_down_stage_with_silu_mul(qg, handle, T):
         wl.unload()
 
 
+@pytest.mark.parametrize("T", [1, 3, 8, 64])
+def test_moe_mlp_one_launch(qg, handle, T):
+    """Gate/up, silu(gate) * up and down of the routed experts as ONE launch: the same bits as the two launches it
+    replaces (gate/up rows and results), and within the bound of the fp64 oracle fed with the device's gate/up rows."""
+    import torch
+    E, topk, H, I, N2 = 32, 4, 256, 128, 320
+    cg, sg, tg = _experts(E, 2 * I, H, seed=801)
+    cd, sd, td = _experts(E, N2, I, seed=802)
+    wg = handle.load_stacked(np.stack([qg.pack(qg.FMT_NVFP4_TC, cg[e], sg[e], float(tg[e])) for e in range(E)]))
+    wd = handle.load_stacked(np.stack([qg.pack(qg.FMT_NVFP4_TC, cd[e], sd[e], float(td[e])) for e in range(E)]))
+    ids, _ = _route(T, E, topk, seed=T + 21)
+    x = O.make_x(T, H, seed=T + 22)
+    xd, idd = U.dev_u16(x), torch.from_numpy(ids).cuda()
+    S = T * topk
+    mid2 = torch.zeros((S, 2 * I), dtype=torch.bfloat16, device="cuda")
+    out2 = torch.full((S, N2), float("nan"), dtype=torch.float32, device="cuda")
+    handle.moe_gemv(wg, idd.data_ptr(), xd.data_ptr(), T, topk, False, mid2.data_ptr(), qg.OUT_BF16)
+    handle.moe_gemv(wd, idd.data_ptr(), mid2.data_ptr(), T, topk, True, out2.data_ptr(), qg.OUT_F32, x_act=qg.MOE_X_SILU_MUL)
+    torch.cuda.synchronize()
+    U.status_ok(handle)
+    for rep in range(2):      # twice: the stage counters are back at zero after a launch
+        mid1 = torch.zeros((S, 2 * I), dtype=torch.bfloat16, device="cuda")
+        out1 = torch.full((S, N2), float("nan"), dtype=torch.float32, device="cuda")
+        handle.moe_mlp(wg, wd, idd.data_ptr(), xd.data_ptr(), T, topk, mid1.data_ptr(), out1.data_ptr(), qg.OUT_F32)
+        torch.cuda.synchronize()
+        U.status_ok(handle)
+        assert torch.equal(mid1.view(torch.int16), mid2.view(torch.int16)), rep
+        assert torch.equal(out1.view(torch.int32), out2.view(torch.int32)), rep
+    v = mid2.float().cpu().numpy().astype(np.float64)
+    act = O.bf16_encode((v[:, :I] / (1.0 + np.exp(-v[:, :I])) * v[:, I:]).astype(np.float32))
+    ref = O.moe_gemv_nvfp4_f64(cd, sd, td, ids, act, per_slot_input=True)
+    assert O.rel_l2(out1.cpu().numpy(), ref) < 5e-4
+    refg = O.moe_gemv_nvfp4_f64(cg, sg, tg, ids, x, per_slot_input=False)
+    assert O.rel_l2(v, refg) < TOL_BF16
+    wg.unload()
+    wd.unload()
+
+
 def test_moe_gemv_tc_many_experts_and_limits(qg, handle):
     """Tensor-core layout: 300 experts with top-1 routing (every problem a single row, most experts untouched), bf16
     output; a stacked weight of more than 512 experts is refused by the expert-list launch."""
