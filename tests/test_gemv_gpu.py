@@ -500,6 +500,43 @@ def test_moe_mlp_one_launch(qg, handle, T):
     wd.unload()
 
 
+def test_moe_mlp_bounded_waits(qg):
+    """Host-set injection (no weight copy is ever issued): the waits of the one-launch expert MLP run out -- also the
+    second stage's wait for the first stage's rows -- the status word says so, twice in a row (the counters of the
+    abandoned launch are cleared with the status), and nothing hangs; a handle without the injection then computes."""
+    import torch
+    E, topk, T, H, I, N2 = 8, 2, 4, 128, 64, 128
+    cg, sg, tg = _experts(E, 2 * I, H, seed=901)
+    cd, sd, td = _experts(E, N2, I, seed=902)
+    ids, _ = _route(T, E, topk, seed=31)
+    x = O.make_x(T, H, seed=32)
+    S = T * topk
+    outs = []
+    for inject in (True, False):
+        h = qg.QGemv(device=0, spin_limit=2000, inject_drop_copies=inject)
+        wg = h.load_stacked(np.stack([qg.pack(qg.FMT_NVFP4_TC, cg[e], sg[e], float(tg[e])) for e in range(E)]))
+        wd = h.load_stacked(np.stack([qg.pack(qg.FMT_NVFP4_TC, cd[e], sd[e], float(td[e])) for e in range(E)]))
+        xd, idd = U.dev_u16(x), torch.from_numpy(ids).cuda()
+        mid = torch.zeros((S, 2 * I), dtype=torch.bfloat16, device="cuda")
+        out = torch.zeros((S, N2), dtype=torch.float32, device="cuda")
+        for _ in range(2):
+            h.moe_mlp(wg, wd, idd.data_ptr(), xd.data_ptr(), T, topk, mid.data_ptr(), out.data_ptr(), qg.OUT_F32)
+            torch.cuda.synchronize()
+            st = h.device_status()
+            if inject:
+                assert st.code == qg.ERR_TIMEOUT and 71 <= st.where <= 86
+            else:
+                assert st.code == 0
+        outs.append(out.cpu().numpy())
+        wg.unload(), wd.unload()
+        h.close()
+    act_ref = O.moe_gemv_nvfp4_f64(cg, sg, tg, ids, x, per_slot_input=False)
+    g = O.bf16_decode(O.bf16_encode(act_ref.astype(np.float32))).astype(np.float64)
+    act = O.bf16_encode((g[:, :I] / (1.0 + np.exp(-g[:, :I])) * g[:, I:]).astype(np.float32))
+    ref = O.moe_gemv_nvfp4_f64(cd, sd, td, ids, act, per_slot_input=True)
+    assert O.rel_l2(outs[1], ref) < 5e-3    # (the oracle's own gate/up rows here: bf16 roundings may differ from the device's)
+
+
 def test_moe_gemv_tc_many_experts_and_limits(qg, handle):
     """Tensor-core layout: 300 experts with top-1 routing (every problem a single row, most experts untouched), bf16
     output; a stacked weight of more than 512 experts is refused by the expert-list launch."""
