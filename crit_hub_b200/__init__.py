@@ -39,6 +39,12 @@ ERR_BOUNDS = -7
 ERR_NO_DEVICE = -8
 
 
+class MoePlan(C.Structure):
+    _fields_ = [("rows_per_problem", C.c_int32), ("plane_buffers", C.c_int32), ("plane_slots", C.c_int32),
+                ("ring_stages", C.c_int32), ("stage_items", C.c_int32), ("max_problems", C.c_int32),
+                ("table_offset", C.c_int32), ("smem_bytes", C.c_int32)]
+
+
 class SkinnyPlan(C.Structure):
     """qgemv_skinny_plan: how qgemv_gemm_skinny would run a shape."""
     _fields_ = [("run_units", C.c_int32), ("x_stage_units", C.c_int32), ("x_stages", C.c_int32),
@@ -129,6 +135,7 @@ def _load() -> C.CDLL:
     L.qgemv_gemm_skinny.argtypes = [vp, vp, vp, i32, vp, i32, i32, vp]
     L.qgemv_quantize_a4.argtypes = [vp, vp, i32, i64, vp, vp, vp, vp]
     L.qgemv_gemm_skinny_plan.argtypes = [i32, i64, i64, i32, i32, C.POINTER(SkinnyPlan)]
+    L.qgemv_moe_plan.argtypes = [i64, i64, i32, i32, i32, i32, i32, C.POINTER(MoePlan)]
     L.qgemv_tp_create.argtypes = [vp, i32, i32, i64, vp]
     L.qgemv_tp_connect.argtypes = [vp, vp]
     L.qgemv_tp_allreduce.argtypes = [vp, vp, i32, i64, vp]
@@ -450,6 +457,14 @@ def noalloc_last_status(stream: int = 0) -> DeviceStatus:
     st = _DevStatus()
     _check(_load().qgemv_noalloc_last_status(stream, C.byref(st)), "noalloc_last_status")
     return DeviceStatus(st.code, st.where, st.block, st.extra)
+
+
+def moe_plan(K: int, n_experts: int, T: int, topk: int, K2: int = 0, ctas: int = 148, smem_kb: int = 0) -> MoePlan:
+    """How an expert-list launch (moe_gemv / moe_mlp on tensor-core-layout experts) would be laid out; host arithmetic,
+    no device needed.  K2: the second stage's K for moe_mlp.  Raises QgemvError where the launch would refuse."""
+    plan = MoePlan()
+    _check(_load().qgemv_moe_plan(K, K2, n_experts, T, topk, ctas, smem_kb, C.byref(plan)), "moe_plan")
+    return plan
 
 
 def gemm_skinny_plan(fmt: int, N: int, K: int, M: int, sm_count: int = 148) -> SkinnyPlan:

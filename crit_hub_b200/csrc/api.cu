@@ -1126,24 +1126,18 @@ int qgemv_gemm_skinny(qgemv_handle* h, const qgemv_weight* w, const void* x_bf16
     return err == cudaSuccess ? QGEMV_OK : QGEMV_ERR_CUDA;
 }
 
-namespace {
-// The experts of a router table on the tensor-core layout: the sequence kernel in its expert-list mode, ONE
-// cooperative launch (every CTA walks the top-k lists for itself).  Problems hold at most B activation rows.
-// `w2` (nullable): the experts' second stage in the same launch -- w is then the gate/up stage, writing its bf16
-// rows to `mid` [T * topk][w->N], and w2 the down stage, which reads them through silu(gate) * up.
-int moe_tc(qgemv_handle* h, const qgemv_weight* w, const qgemv_weight* w2, const int32_t* expert_ids, const void* x_bf16,
-           int T, int topk, int per_slot_input, int x_act, void* mid, void* out, int out_dtype, cudaStream_t s) {
-    const int grid = gemv_grid(h);
-    if (grid > h->sm_count) return QGEMV_ERR_UNSUPPORTED_SHAPE;  // the CTAs wait on one another: one per SM at most
-    const int slots = T * topk;
-    if (w->n_stack > qg::kMoeMaxExperts || slots > qg::kMoeMaxSlots) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+int qgemv_moe_plan(int64_t K, int64_t K2, int n_experts, int T, int topk, int ctas, int smem_kb, qgemv_moe_plan_t* out) {
+    if (!out || K < 64 || K % 64 != 0 || K2 < 0 || K2 % 64 != 0 || n_experts < 1 || T < 1 || topk < 1 || ctas < 1)
+        return QGEMV_ERR_INVALID_ARG;
+    const int64_t slots = int64_t(T) * topk;
+    if (n_experts > qg::kMoeMaxExperts || slots > qg::kMoeMaxSlots) return QGEMV_ERR_UNSUPPORTED_SHAPE;
     // Rows per problem (B): no more than there are tokens, and as many of eight as leave a weight ring of three
     // stages beside the digit planes of B rows x K (halved until they do: a long K gets problems of fewer
     // rows, and an expert with more entries is then read once per problem).
     constexpr int kStage = 4;
     constexpr int kWalk = (qg::kMoeSmemBytes + 127) / 128 * 128;   // the CTA's problem table, behind the ring
-    const int cap = (h->cfg.tc_smem_kb > 0 ? std::min(h->cfg.tc_smem_kb, 227) : 227) * 1024 - kWalk;
-    const int x_slots = int(w2 ? std::max(w->units, w2->units) : w->units);   // a CTA's share of an expert may span a whole row tile
+    const int cap = (smem_kb > 0 ? std::min(smem_kb, 227) : 227) * 1024 - kWalk;
+    const int x_slots = int(std::max(K, K2) / 64);   // a CTA's share of an expert may span a whole row tile
     int B = std::min(QGEMV_MAX_BATCH, T), npad = 0, nbuf = 1, ring = 0;
     for (;; B = (B + 1) / 2) {
         npad = (8 * B + 15) / 16 * 16;
@@ -1158,8 +1152,36 @@ int moe_tc(qgemv_handle* h, const qgemv_weight* w, const qgemv_weight* w2, const
     }
     if (ring < 2 || ring * kStage * qg::kTcItemBytes < qg::kMoeWalkBytes)
         return QGEMV_ERR_UNSUPPORTED_SHAPE;  // K too long for the digit planes of one row beside a ring
-    const int64_t most_prob = std::min<int64_t>(w->n_stack, slots) + slots / B;   // problems the lists can make
-    if (((most_prob + grid - 1) / grid + 1) * (w2 ? 2 : 1) > qg::kMoeLocalJobs || most_prob >= 2048) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+    const int64_t most_prob = std::min<int64_t>(n_experts, slots) + slots / B;   // problems the lists can make
+    if (((most_prob + ctas - 1) / ctas + 1) * (K2 > 0 ? 2 : 1) > qg::kMoeLocalJobs || most_prob >= 2048) return QGEMV_ERR_UNSUPPORTED_SHAPE;
+    out->rows_per_problem = B;
+    out->plane_buffers = nbuf;
+    out->plane_slots = x_slots;
+    out->ring_stages = ring;
+    out->stage_items = kStage;
+    out->max_problems = int32_t(most_prob);
+    out->table_offset = (qg::SeqSmem::total(x_slots, npad, nbuf, ring, kStage) + 127) / 128 * 128;
+    out->smem_bytes = out->table_offset + kWalk;
+    return QGEMV_OK;
+}
+
+namespace {
+// The experts of a router table on the tensor-core layout: the sequence kernel in its expert-list mode, ONE
+// cooperative launch (every CTA walks the top-k lists for itself).  Problems hold at most B activation rows.
+// `w2` (nullable): the experts' second stage in the same launch -- w is then the gate/up stage, writing its bf16
+// rows to `mid` [T * topk][w->N], and w2 the down stage, which reads them through silu(gate) * up.
+int moe_tc(qgemv_handle* h, const qgemv_weight* w, const qgemv_weight* w2, const int32_t* expert_ids, const void* x_bf16,
+           int T, int topk, int per_slot_input, int x_act, void* mid, void* out, int out_dtype, cudaStream_t s) {
+    const int grid = gemv_grid(h);
+    if (grid > h->sm_count) return QGEMV_ERR_UNSUPPORTED_SHAPE;  // the CTAs wait on one another: one per SM at most
+    const int slots = T * topk;
+    qgemv_moe_plan_t pl;
+    const int rcp = qgemv_moe_plan(w->K, w2 ? w2->K : 0, w->n_stack, T, topk, grid, h->cfg.tc_smem_kb, &pl);
+    if (rcp != QGEMV_OK) return rcp;
+    const int B = pl.rows_per_problem, npad = (8 * B + 15) / 16 * 16, nbuf = pl.plane_buffers, ring = pl.ring_stages;
+    const int x_slots = pl.plane_slots;
+    const int64_t most_prob = pl.max_problems;
+    constexpr int kStage = 4;
     qg::SeqParams P;
     std::memset(&P, 0, sizeof P);
     qg::SeqJob& mj = P.moe_job;
@@ -1213,8 +1235,8 @@ int moe_tc(qgemv_handle* h, const qgemv_weight* w, const qgemv_weight* w2, const
     P.expert_ts = w->dev_tensor_scale;
     P.expert_stride = w->blob_bytes;
     P.ring = ring;
-    P.moe_smem = (qg::SeqSmem::total(P.x_slots, P.npad, P.nbuf, ring, kStage) + 127) / 128 * 128;
-    const size_t smem = size_t(P.moe_smem) + kWalk;
+    P.moe_smem = pl.table_offset;
+    const size_t smem = size_t(pl.smem_bytes);
     g_launch_cooperative = (h->cfg.debug & 2048) != 0;
     const cudaError_t err = launch(h, qg::gemv_seq_kernel<kStage, qg::kSeqMoe>, dim3(unsigned(grid)), dim3(qg::kSeqThreads), smem, s, P);
     return err == cudaSuccess ? QGEMV_OK : QGEMV_ERR_CUDA;

@@ -404,6 +404,20 @@ int qgemv_moe_gemv_act(qgemv_handle* h, const qgemv_weight* experts, const int32
  * the first stage and read by the second (the caller's scratch).  Limits as for qgemv_moe_gemv. */
 int qgemv_moe_mlp(qgemv_handle* h, const qgemv_weight* gate_up, const qgemv_weight* down, const int32_t* expert_ids,
                   const void* x_bf16, int T, int topk, void* gate_up_rows, void* out, int out_dtype, void* stream);
+/* How an expert-list launch would be laid out (host arithmetic only, no device needed): K of the experts, K2 of
+ * a second stage in the same launch (0: none), experts, tokens, top-k, CTAs (one per SM), shared memory per CTA
+ * in KB (0: 227).  QGEMV_ERR_UNSUPPORTED_SHAPE when qgemv_moe_gemv / qgemv_moe_mlp would refuse the shape. */
+typedef struct qgemv_moe_plan_t {
+    int32_t rows_per_problem; /* an expert's entries are worked on this many activation rows at a time */
+    int32_t plane_buffers;    /* buffers of digit planes (problems the conversion may run ahead) */
+    int32_t plane_slots;      /* 64-K items of planes per buffer */
+    int32_t ring_stages;      /* stages of the weight ring */
+    int32_t stage_items;      /* items per stage (4608 bytes each) */
+    int32_t max_problems;     /* most problems the lists can make */
+    int32_t table_offset;     /* offset of the CTA's problem table in shared memory */
+    int32_t smem_bytes;       /* dynamic shared memory per CTA */
+} qgemv_moe_plan_t;
+int qgemv_moe_plan(int64_t K, int64_t K2, int n_experts, int T, int topk, int ctas, int smem_kb, qgemv_moe_plan_t* out);
 /* y[t][:] = sum_j expert_w[t][j] * slot_out[t*topk + j][:]  (fixed j order, fp32 accumulate). */
 int qgemv_moe_combine(qgemv_handle* h, const void* slot_out, int slot_dtype, const float* expert_w,
                       int T, int topk, int64_t N, void* y, int y_dtype, void* stream);
