@@ -829,9 +829,6 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                         }
                     }
                 }
-                if (!group_alive()) break;
-                SEQ_PPROF(0);
-                if (P.trace && gt == 0) P.trace[(size_t(cta) * P.trace_jobs + (j - j_lo)) * 8 + 0] = globaltimer_ns();
                 const int32_t kt_len = job.kt;
                 const int Bj = MOE ? job.rows : Bl;  // activation rows of this job
                 int32_t r_begin, r_end;
@@ -845,7 +842,9 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                     rg[0] = r_begin, rg[1] = r_end;
                 }
                 if (gt < 32) all_max[gt] = 0u;
-                named_bar_sync(bar_id, 128);
+                if (!group_alive()) break;   // (its barrier also publishes the cleared maxima)
+                SEQ_PPROF(0);
+                if (P.trace && gt == 0) P.trace[(size_t(cta) * P.trace_jobs + (j - j_lo)) * 8 + 0] = globaltimer_ns();
                 const int n_work = n_slots * Bj * 8;
                 constexpr int kKeep = 4;
                 const bool from_pub = job.src_off >= 0;
