@@ -4,7 +4,8 @@
     python bench.py --workload prefill [--tokens M]      (one secondary workload alone: skinny GEMM)
     python bench.py --workload prefill_a4 [--tokens M]   (block-scaled prefill, NVFP4 activations)
     python bench.py --workload lmhead [--batch B]        (FP8 output head)
-    python bench.py --workload moe [--tokens T]          (grouped MoE GEMV)
+    python bench.py --workload moe [--tokens T]          (the experts' MLP of an MoE layer: gate/up, silu x up, down;
+                                                          --moe-layout lane | --moe-two-launches for the other forms)
 
 A "step" is one pass of the hot path over the whole layer stack (four weight-streaming GEMVs per
 layer) at decode batch B.  By default the stack runs as ONE persistent launch per step
