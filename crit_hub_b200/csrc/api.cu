@@ -722,6 +722,9 @@ int qgemv_sequence_create(qgemv_handle* h, const qgemv_job* jobs, int n_jobs, in
         x_slots = std::max(x_slots, std::min<int64_t>(sj.kt, (total + grid - 1) / grid));
     }
     if (n_jobs > 4094) return QGEMV_ERR_UNSUPPORTED_SHAPE;  // the job index is part of a 12-bit tag
+    // a job whose counter a later job waits for (dep) bumps it with release semantics
+    for (int i = 0; i < n_jobs; ++i)
+        if (tab[size_t(i)].dep >= 0) tab[size_t(tab[size_t(i)].dep)].fin_release = 1;
     // published outputs: one block of B * N words for every job that a later job reads the fast way
     int64_t pub_words = 0;
     for (int i = 0; i < n_jobs; ++i) {

@@ -40,7 +40,7 @@
 
 namespace qg {
 
-constexpr int kSeqPartBufs = 8;
+constexpr int kSeqPartBufs = 16;
 constexpr int kSeqPlaneBufsMax = 3;  // buffers of digit planes (1..3, as many as leave room for a ring): the PLANES group
                                      // may be that many jobs ahead of the epilogues  // jobs a CTA may run ahead of the slowest one before it waits for its parts buffer
 
@@ -68,7 +68,8 @@ struct SeqJob {               // 80 bytes, device memory
     const void* residual;     // [B][N] in y's dtype or null: added to the result before it is rounded
     const int32_t* rowmap;    // expert list only: [16] row of x for each of the job's activation rows, then row of y (shared memory)
     int32_t rows;             // expert list only: activation rows of this job (<= B)
-    int32_t pad;
+    int32_t fin_release;      // 1: a later job waits for this one's counter (dep), so the counter is bumped with release
+                              // semantics; 0: nobody reads what this job wrote on the strength of its counter
 };
 static_assert(sizeof(SeqJob) == 112, "SeqJob layout");
 
@@ -154,6 +155,9 @@ struct SeqSmem {
 
 __device__ __forceinline__ void red_release_add(unsigned int* p, unsigned int v) {
     asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void red_relaxed_add(unsigned int* p, unsigned int v) {
+    asm volatile("red.relaxed.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 __device__ __forceinline__ unsigned int atom_release_add(unsigned int* p, unsigned int v) {
     unsigned int old;
@@ -1150,6 +1154,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
             const uint32_t lane_base = uint32_t(32 * q) << 16;
             const int row = 32 * q + lane;
             uint32_t nseg = 0;
+            int seen_all = -1;  // this thread's own knowledge of how far all CTAs have added their tiles up
             SeqJob job = P.moe_job;
             if (j_lo < j_hi) job = job_at(j_lo);
             int pb = 0;
@@ -1169,16 +1174,28 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 const volatile int* rg = reinterpret_cast<const volatile int*>(sq_smem + SeqSmem::kRange) + pb * 2;
                 const int32_t rb = rg[0], re = rg[1];
                 // A split tile's parts go to buffer j % kSeqPartBufs, last used by job j - kSeqPartBufs: every
-                // CTA must have added that job's tiles up (the FINISH group publishes how far that has come)
-                if (!MOE && re > rb && (rb % kt_len != 0 || re % kt_len != 0) && j >= kSeqPartBufs && gt == 0) {
-                    uint64_t t0 = 0;
-                    for (int64_t it = 0; *fin_all < j - kSeqPartBufs; ++it) {
-                        // (asked directly: this CTA's FINISH group may itself be waiting for the part written below)
-                        if (*abort_flag || ld_acquire(P.fin + (j - kSeqPartBufs)) >= unsigned(grid)) break;
-                        if (out_of_time(it, t0)) {
-                            seq_report(P.status, 79, j);
-                            *abort_flag = 1;
-                            break;
+                // CTA must have added that job's tiles up.  The FINISH group publishes how far that has come while
+                // it waits; when its word is old this thread asks global memory itself -- first about a job half a
+                // round of buffers later, so that one look serves the next eight jobs (a look per job would sit in
+                // the MMA issuer's way: it waits for the accumulator this group has not read yet).
+                if (!MOE && re > rb && (rb % kt_len != 0 || re % kt_len != 0) && j >= kSeqPartBufs && gt == 0 &&
+                    max(int(*fin_all), seen_all) < j - kSeqPartBufs) {
+                    if (ld_acquire(P.fin + (j - kSeqPartBufs / 2)) >= unsigned(grid)) {
+                        seen_all = j - kSeqPartBufs / 2;
+                    } else {
+                        uint64_t t0 = 0;
+                        for (int64_t it = 0;; ++it) {
+                            // (asked directly: this CTA's FINISH group may itself be waiting for the part written below)
+                            if (*abort_flag) break;
+                            if (ld_acquire(P.fin + (j - kSeqPartBufs)) >= unsigned(grid)) {
+                                seen_all = j - kSeqPartBufs;
+                                break;
+                            }
+                            if (out_of_time(it, t0)) {
+                                seq_report(P.status, 79, j);
+                                *abort_flag = 1;
+                                break;
+                            }
                         }
                     }
                 }
@@ -1268,6 +1285,15 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
         } else {
             // ---------------- FINISH ----------------
             int known = -1;  // jobs up to here are added up on every CTA (published in fin_all)
+#ifdef QGEMV_SEQ_PROFILE
+            long long fprof[4] = {0, 0, 0, 0};  // cycles of this group's first thread: waiting for the epilogues, partial sums, push, gather
+            long long ft = clock64();
+#define SEQ_FPROF(slot) if (gt == 0) { const long long now_ = clock64(); fprof[slot] += now_ - ft; ft = now_; }
+#define SEQ_FPROF_MARK() if (gt == 0) ft = clock64()
+#else
+#define SEQ_FPROF(slot)
+#define SEQ_FPROF_MARK()
+#endif
             SeqJob job = P.moe_job;
             if (j_lo < j_hi) job = job_at(j_lo);
             TpExchange X;
@@ -1298,6 +1324,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 // global memory themselves -- is looked up below while this group waits anyway: a probe here would put
                 // a round trip to L2 into every job of a group whose time per job bounds the small jobs)
                 if (!group_alive()) break;
+                SEQ_FPROF_MARK();
                 // this CTA's own part of the tile comes first, and the other contributors finish at about the same
                 // time: nothing is asked of global memory before this CTA's epilogues are through with the job
                 if (gt == 0) {
@@ -1318,6 +1345,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                     }
                 }
                 named_bar_sync(bar_id, 128);
+                SEQ_FPROF(0);
                 if (pending) {
                     const int n = tile * 128 + gt;
                     const unsigned long long* parts = P.ws + job_parts(j) * size_t(2 * grid) * 1024 + gt;
@@ -1366,12 +1394,15 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                             }
                             if (!have) break;
                             const int64_t idx = (MOE ? int64_t(job.rowmap[8 + b]) : int64_t(b)) * job.N + n;
+                            SEQ_FPROF(1);
                             if (job.xoff >= 0) {
                                 // this rank's partial sum out to every rank, then the ranks' sums for this row, added in rank order
                                 X.push(int64_t(job.xoff) + idx, a);
+                                SEQ_FPROF(2);
                                 float part[kTpMaxWorld];
                                 int missing = 0;
                                 if (X.gather(int64_t(job.xoff) + idx, part, P.spin_limit, missing)) {
+                                    SEQ_FPROF(3);
                                     a = part[0];
                                     for (int r = 1; r < P.world; ++r) a += part[r];
                                 } else {
@@ -1409,9 +1440,24 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
                 if (P.trace && gt == 0) P.trace[(size_t(cta) * P.trace_jobs + (j - j_lo)) * 8 + 6] = globaltimer_ns();
                 // (the epilogues of the job are through, see above: fin[j] == grid means that all of y is there)
                 named_bar_sync(bar_id, 128);
-                if (!MOE && gt == 0) red_release_add(P.fin + j, 1u);
+                // The counter is what a later job with a `dep` on this one waits for before it reads this job's rows, and
+                // what the epilogues ask before they reuse a parts buffer.  Only the first needs release semantics: the
+                // partial sums this group read have arrived (their values are in the rows) whatever the order of the
+                // bump.  A release here would also wait for the exchange's stores to the other ranks to be
+                // acknowledged over the link -- microseconds, in the group whose time per job bounds small jobs.
+                if (!MOE && gt == 0) {
+                    if (job.fin_release) {
+                        red_release_add(P.fin + j, 1u);
+                    } else {
+                        red_relaxed_add(P.fin + j, 1u);
+                    }
+                }
                 job = next;
             }
+#ifdef QGEMV_SEQ_PROFILE
+            if (P.trace && gt == 0)
+                for (int z = 0; z < 4; ++z) P.trace[size_t(gridDim.x) * P.trace_jobs * 8 + size_t(gridDim.x) * 8 + size_t(cta) * 4 + z] = (unsigned long long)fprof[z];
+#endif
         }
     }
     // ---- every role is through (or has given up): the last CTA to leave puts the counters back to zero ----
