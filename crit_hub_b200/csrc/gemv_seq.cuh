@@ -20,7 +20,7 @@
 //             compares the address ranges of every job's x and y with those of the jobs before it,
 //             or the caller says so -- first waits until fin[that job] has been bumped by every CTA.
 //   EPILOGUE  accumulators -> y rows (a CTA that holds a whole row tile) or fp32 partial sums in the
-//             CTA's slot of a parts buffer (eight buffers, taken in turn by the jobs); then bumps
+//             CTA's slot of a parts buffer (sixteen buffers, taken in turn by the jobs); then bumps
 //             done[j] with release semantics.
 //   FINISH    once done[j] shows every CTA: the first contributor of a split row tile adds the parts
 //             in CTA order -- a fixed order -- and stores the rows; then bumps fin[j].  Nothing here
@@ -40,9 +40,9 @@
 
 namespace qg {
 
-constexpr int kSeqPartBufs = 16;
+constexpr int kSeqPartBufs = 16;     // parts buffers: jobs a CTA may run ahead of the slowest CTA's split-tile sums
 constexpr int kSeqPlaneBufsMax = 3;  // buffers of digit planes (1..3, as many as leave room for a ring): the PLANES group
-                                     // may be that many jobs ahead of the epilogues  // jobs a CTA may run ahead of the slowest one before it waits for its parts buffer
+                                     // may be that many jobs ahead of the epilogues
 
 struct SeqJob {               // 80 bytes, device memory
     const uint8_t* payload;   // items of the weight: (tile * kt + item) * 4608
@@ -558,7 +558,7 @@ __global__ void __launch_bounds__(kSeqThreads, 1) gemv_seq_kernel(const SeqParam
             return j;
         }
     };
-    // the parts buffer of job j: the jobs of a list take eight in turn; a router table's CTAs each hand over at
+    // the parts buffer of job j: the jobs of a list take sixteen in turn; a router table's CTAs each hand over at
     // most two split tiles per stage, so one buffer per stage serves
     auto job_parts = [&](int j) -> size_t { return MOE ? size_t(m_tab[j * kProbInts + 19] >> 16) : size_t(j & (kSeqPartBufs - 1)); };
 
